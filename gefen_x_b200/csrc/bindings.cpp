@@ -1,0 +1,271 @@
+// torch operator registrations (namespace gefenx) for the sm_100a kernels.
+//
+// The kernel files carry no torch headers; this file only unwraps tensors into
+// raw pointers, checks devices / dtypes / contiguity, picks the current stream
+// and calls the launchers.  Every launcher returns its cudaError_t, which is
+// turned into a C++ exception here (the reference validates on the host before
+// each raw-pointer launch as well, reference
+// src/gefen/kernels/automatic_gefen_fused_kernel.cu:2102-2231).
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/library.h>
+
+#include "model_ops.h"
+#include "quant.h"
+#include "update.h"
+
+namespace {
+
+using at::Tensor;
+
+inline void check(cudaError_t e, const char* what) {
+    TORCH_CHECK(e == cudaSuccess, "gefenx::", what, " failed: ", cudaGetErrorString(e));
+}
+
+inline int dtype_code(at::ScalarType t) {
+    switch (t) {
+        case at::kFloat: return gx::kF32;
+        case at::kBFloat16: return gx::kBF16;
+        case at::kHalf: return gx::kF16;
+        default: TORCH_CHECK(false, "gefenx: unsupported dtype ", t); return -1;
+    }
+}
+
+inline int sm_count() { return at::cuda::getCurrentDeviceProperties()->multiProcessorCount; }
+
+inline cudaStream_t stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+int64_t desc_size() { return (int64_t)sizeof(gx::TensorDesc); }
+
+gx::LaunchCommon make_common(const Tensor& descs, const Tensor& tile_start, int64_t n_tensors,
+                             int64_t total_tiles, const Tensor& codebook, const Tensor& lut,
+                             const c10::optional<Tensor>& gscale, const c10::optional<Tensor>& status,
+                             int64_t sr_seed, bool stochastic, int64_t wait_iters) {
+    TORCH_CHECK(descs.is_cuda() && descs.scalar_type() == at::kByte && descs.is_contiguous(),
+                "descs must be a contiguous CUDA uint8 tensor");
+    TORCH_CHECK(descs.numel() >= n_tensors * (int64_t)sizeof(gx::TensorDesc), "descs too small");
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(descs.data_ptr()) % 16 == 0, "descs must be 16-byte aligned");
+    TORCH_CHECK(tile_start.is_cuda() && tile_start.scalar_type() == at::kInt &&
+                    tile_start.numel() >= n_tensors + 1,
+                "tile_start must be CUDA int32 [n_tensors + 1]");
+    TORCH_CHECK(codebook.is_cuda() && codebook.scalar_type() == at::kFloat && codebook.numel() == 256 &&
+                    codebook.is_contiguous(),
+                "codebook must be CUDA fp32 [256]");
+    TORCH_CHECK(lut.is_cuda() && lut.scalar_type() == at::kInt && lut.numel() == 4096 && lut.is_contiguous(),
+                "lut must be CUDA int32 [4096]");
+    gx::LaunchCommon c{};
+    c.descs = reinterpret_cast<const gx::TensorDesc*>(descs.data_ptr());
+    c.tile_start = tile_start.data_ptr<int>();
+    c.n_tensors = (int)n_tensors;
+    c.total_tiles = (int)total_tiles;
+    c.codebook = codebook.data_ptr<float>();
+    c.lut = reinterpret_cast<const uint32_t*>(lut.data_ptr<int>());
+    c.gscale = nullptr;
+    if (gscale.has_value() && gscale->defined()) {
+        TORCH_CHECK(gscale->is_cuda() && gscale->scalar_type() == at::kFloat, "gscale must be CUDA fp32");
+        c.gscale = gscale->data_ptr<float>();
+    }
+    c.status = nullptr;
+    if (status.has_value() && status->defined()) {
+        TORCH_CHECK(status->is_cuda() && status->scalar_type() == at::kInt, "status must be CUDA int32");
+        c.status = status->data_ptr<int>();
+    }
+    c.sr_seed = (unsigned long long)sr_seed;
+    c.stochastic = stochastic ? 1 : 0;
+    c.wait_iters = wait_iters;
+    return c;
+}
+
+void block_update(const Tensor& descs, const Tensor& tile_start, int64_t n_tensors, int64_t total_tiles,
+                  const Tensor& codebook, const Tensor& lut, const c10::optional<Tensor>& gscale,
+                  const c10::optional<Tensor>& status, int64_t dtype, int64_t sr_seed, bool stochastic) {
+    c10::cuda::CUDAGuard guard(descs.device());
+    auto c = make_common(descs, tile_start, n_tensors, total_tiles, codebook, lut, gscale, status,
+                         sr_seed, stochastic, 0);
+    check(gx::launch_block_update(c, (int)dtype, sm_count(), stream()), "block_update");
+}
+
+void factored_update(const Tensor& descs, const Tensor& tile_start, int64_t n_tensors,
+                     int64_t total_tiles, const Tensor& codebook, const Tensor& lut,
+                     const c10::optional<Tensor>& gscale, const c10::optional<Tensor>& status,
+                     int64_t dtype, int64_t sr_seed, bool stochastic, int64_t wait_iters,
+                     int64_t phases) {
+    // phases bit 0: statistics, bit 1: EMA (+ exchange), bit 2: apply + finalize
+    c10::cuda::CUDAGuard guard(descs.device());
+    auto c = make_common(descs, tile_start, n_tensors, total_tiles, codebook, lut, gscale, status,
+                         sr_seed, stochastic, wait_iters);
+    const int sms = sm_count();
+    auto st = stream();
+    if (phases & 1) check(gx::launch_factored_stats(c, (int)dtype, sms, st), "factored_stats");
+    if (phases & 2) check(gx::launch_factored_ema(c, st), "factored_ema");
+    if (phases & 4) {
+        check(gx::launch_factored_apply(c, (int)dtype, sms, st), "factored_apply");
+        check(gx::launch_finalize_magnitude(c, sms, st), "finalize_magnitude");
+    }
+}
+
+void reduce_sources(const c10::optional<Tensor>& out, at::IntArrayRef src_ptrs, int64_t numel,
+                    double scale, const c10::optional<Tensor>& partials, int64_t dtype,
+                    int64_t device_index) {
+    c10::cuda::CUDAGuard guard((c10::DeviceIndex)device_index);
+    TORCH_CHECK(src_ptrs.size() >= 1 && src_ptrs.size() <= (size_t)gx::kDescMaxSrc, "1..8 sources");
+    const void* src[gx::kDescMaxSrc];
+    for (size_t i = 0; i < src_ptrs.size(); ++i) src[i] = reinterpret_cast<const void*>(src_ptrs[i]);
+    void* o = nullptr;
+    if (out.has_value() && out->defined()) {
+        TORCH_CHECK(out->is_cuda() && out->is_contiguous() && out->numel() >= numel, "bad out");
+        o = out->data_ptr();
+    }
+    float* part = nullptr;
+    int n_part = 0;
+    if (partials.has_value() && partials->defined()) {
+        TORCH_CHECK(partials->is_cuda() && partials->scalar_type() == at::kFloat, "partials fp32");
+        part = partials->data_ptr<float>();
+        n_part = (int)partials->numel();
+    }
+    check(gx::launch_reduce_sources(o, src, (int)src_ptrs.size(), numel, (float)scale, part, n_part,
+                                    (int)dtype, stream()),
+          "reduce_sources");
+}
+
+void clip_coef(const Tensor& partials, double max_norm, Tensor coef) {
+    c10::cuda::CUDAGuard guard(partials.device());
+    TORCH_CHECK(partials.is_cuda() && partials.scalar_type() == at::kFloat && partials.is_contiguous());
+    TORCH_CHECK(coef.is_cuda() && coef.scalar_type() == at::kFloat && coef.numel() >= 2);
+    check(gx::launch_clip_coef(partials.data_ptr<float>(), (int)partials.numel(), (float)max_norm,
+                               coef.data_ptr<float>(), stream()),
+          "clip_coef");
+}
+
+void histogram(const Tensor& flat, int64_t period, Tensor counts) {
+    c10::cuda::CUDAGuard guard(flat.device());
+    TORCH_CHECK(flat.is_cuda() && flat.is_contiguous(), "flat must be contiguous CUDA");
+    TORCH_CHECK(counts.is_cuda() && counts.scalar_type() == at::kLong && counts.is_contiguous());
+    TORCH_CHECK(period > 0 && flat.numel() % period == 0, "period must divide numel");
+    TORCH_CHECK(counts.numel() * sizeof(int) <= 48 * 1024, "too many bins for shared memory");
+    check(gx::launch_histogram(flat.data_ptr(), dtype_code(flat.scalar_type()), flat.numel(),
+                               (int)period, (int)counts.numel(),
+                               reinterpret_cast<unsigned long long*>(counts.data_ptr<int64_t>()),
+                               sm_count(), stream()),
+          "histogram");
+}
+
+Tensor period_errors(const Tensor& flat, const Tensor& divisors_dev, bool input_is_squared) {
+    c10::cuda::CUDAGuard guard(flat.device());
+    TORCH_CHECK(flat.is_cuda() && flat.is_contiguous(), "flat must be contiguous CUDA");
+    TORCH_CHECK(divisors_dev.is_cuda() && divisors_dev.scalar_type() == at::kLong);
+    const int n_div = (int)divisors_dev.numel();
+    const int ctas = sm_count() * 2;
+    auto partials = at::zeros({n_div, ctas}, flat.options().dtype(at::kDouble));
+    check(gx::launch_period_errors(flat.data_ptr(), dtype_code(flat.scalar_type()), flat.numel(),
+                                   reinterpret_cast<const long long*>(divisors_dev.data_ptr<int64_t>()),
+                                   n_div, input_is_squared, partials.data_ptr<double>(), ctas, stream()),
+          "period_errors");
+    return partials;
+}
+
+// ---------------------------------------------------------------------------
+// model operators (model_ops.cu)
+// ---------------------------------------------------------------------------
+void rmsnorm_fwd(const Tensor& x, const Tensor& w, Tensor y, Tensor rstd, double eps) {
+    c10::cuda::CUDAGuard guard(x.device());
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous() && y.is_contiguous() && w.is_contiguous());
+    const int64_t d = x.size(-1);
+    check(gx::launch_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(),
+                                 x.numel() / d, (int)d, (float)eps, dtype_code(x.scalar_type()), stream()),
+          "rmsnorm_fwd");
+}
+
+void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, Tensor dx,
+                 Tensor dw_partial) {
+    c10::cuda::CUDAGuard guard(x.device());
+    TORCH_CHECK(dy.is_contiguous() && x.is_contiguous() && dx.is_contiguous());
+    const int64_t d = x.size(-1);
+    check(gx::launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(),
+                                 dx.data_ptr(), dw_partial.data_ptr<float>(), (int)dw_partial.size(0),
+                                 x.numel() / d, (int)d, dtype_code(x.scalar_type()), stream()),
+          "rmsnorm_bwd");
+}
+
+int64_t rmsnorm_bwd_partials(int64_t rows, int64_t d) { return gx::rmsnorm_bwd_partials(rows, (int)d); }
+
+void rope(Tensor x, const Tensor& cos, const Tensor& sin, int64_t seq_len, int64_t n_heads,
+          int64_t head_dim, bool inverse, bool interleaved) {
+    c10::cuda::CUDAGuard guard(x.device());
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous() && cos.scalar_type() == at::kFloat);
+    check(gx::launch_rope(x.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(),
+                          x.numel() / (n_heads * head_dim), (int)seq_len, (int)n_heads, (int)head_dim,
+                          inverse, interleaved, dtype_code(x.scalar_type()), stream()),
+          "rope");
+}
+
+void swiglu_fwd(const Tensor& gate_up, Tensor out) {
+    c10::cuda::CUDAGuard guard(out.device());
+    TORCH_CHECK(gate_up.is_contiguous() && out.is_contiguous());
+    const int64_t f = out.size(-1);
+    check(gx::launch_swiglu_fwd(gate_up.data_ptr(), out.data_ptr(), out.numel() / f, (int)f,
+                                dtype_code(out.scalar_type()), stream()),
+          "swiglu_fwd");
+}
+
+void swiglu_bwd(const Tensor& gate_up, const Tensor& dout, Tensor dgate_up) {
+    c10::cuda::CUDAGuard guard(dout.device());
+    TORCH_CHECK(gate_up.is_contiguous() && dout.is_contiguous() && dgate_up.is_contiguous());
+    const int64_t f = dout.size(-1);
+    check(gx::launch_swiglu_bwd(gate_up.data_ptr(), dout.data_ptr(), dgate_up.data_ptr(),
+                                dout.numel() / f, (int)f, dtype_code(dout.scalar_type()), stream()),
+          "swiglu_bwd");
+}
+
+void xent_fwd_bwd(Tensor logits, const Tensor& targets, Tensor loss_rows, double grad_scale,
+                  int64_t ignore_index) {
+    c10::cuda::CUDAGuard guard(logits.device());
+    TORCH_CHECK(logits.is_contiguous() && targets.scalar_type() == at::kLong);
+    const int64_t v = logits.size(-1);
+    check(gx::launch_xent_fwd_bwd(logits.data_ptr(), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()),
+                                  loss_rows.data_ptr<float>(), logits.numel() / v, (int)v,
+                                  (float)grad_scale, ignore_index, dtype_code(logits.scalar_type()),
+                                  stream()),
+          "xent_fwd_bwd");
+}
+
+}  // namespace
+
+TORCH_LIBRARY(gefenx, m) {
+    m.def("desc_size() -> int", &desc_size);
+    m.def("rmsnorm_bwd_partials(int rows, int d) -> int", &rmsnorm_bwd_partials);
+    m.def("block_update(Tensor descs, Tensor tile_start, int n_tensors, int total_tiles, Tensor codebook, "
+          "Tensor lut, Tensor? gscale, Tensor? status, int dtype, int sr_seed, bool stochastic) -> ()");
+    m.def("factored_update(Tensor descs, Tensor tile_start, int n_tensors, int total_tiles, Tensor codebook, "
+          "Tensor lut, Tensor? gscale, Tensor? status, int dtype, int sr_seed, bool stochastic, "
+          "int wait_iters, int phases) -> ()");
+    m.def("reduce_sources(Tensor? out, int[] src_ptrs, int numel, float scale, Tensor? partials, "
+          "int dtype, int device_index) -> ()", &reduce_sources);
+    m.def("clip_coef(Tensor partials, float max_norm, Tensor(a!) coef) -> ()");
+    m.def("histogram(Tensor flat, int period, Tensor(a!) counts) -> ()");
+    m.def("period_errors(Tensor flat, Tensor divisors, bool input_is_squared) -> Tensor");
+    m.def("rmsnorm_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!) rstd, float eps) -> ()");
+    m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor(a!) dx, Tensor(b!) dw_partial) -> ()");
+    m.def("rope(Tensor(a!) x, Tensor cos, Tensor sin, int seq_len, int n_heads, int head_dim, "
+          "bool inverse, bool interleaved) -> ()");
+    m.def("swiglu_fwd(Tensor gate_up, Tensor(a!) out) -> ()");
+    m.def("swiglu_bwd(Tensor gate_up, Tensor dout, Tensor(a!) dgate_up) -> ()");
+    m.def("xent_fwd_bwd(Tensor(a!) logits, Tensor targets, Tensor(b!) loss_rows, float grad_scale, "
+          "int ignore_index) -> ()");
+}
+
+TORCH_LIBRARY_IMPL(gefenx, CUDA, m) {
+    m.impl("block_update", &block_update);
+    m.impl("factored_update", &factored_update);
+    m.impl("clip_coef", &clip_coef);
+    m.impl("histogram", &histogram);
+    m.impl("period_errors", &period_errors);
+    m.impl("rmsnorm_fwd", &rmsnorm_fwd);
+    m.impl("rmsnorm_bwd", &rmsnorm_bwd);
+    m.impl("rope", &rope);
+    m.impl("swiglu_fwd", &swiglu_fwd);
+    m.impl("swiglu_bwd", &swiglu_bwd);
+    m.impl("xent_fwd_bwd", &xent_fwd_bwd);
+}

@@ -1,0 +1,169 @@
+// Shared device helpers for the sm_100a kernels: typed vector loads/stores,
+// rounding-pinned arithmetic, the codebook search and bounded waits.
+//
+// Rounding is pinned (__fmul_rn/__fadd_rn, no fused multiply-add) wherever a
+// value feeds the quantised momentum, so that the kernels reproduce the torch
+// statement of the math (optim/functional.py) bit for bit.  The reference pins
+// its rounding for the same reason (reference
+// src/gefen/kernels/automatic_gefen_fused_kernel.cu:410-418, :598-603).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gx {
+
+constexpr int kMaxSrc = 8;          // gradient sources (peer slices) summed in-kernel
+constexpr int kCodewords = 256;
+constexpr int kLutBuckets = 4096;
+
+// ---- status word: kernels never trap; they record why they gave up --------
+enum Status : int {
+    kOk = 0,
+    kWaitTimeout = 1,   // a bounded wait on a peer flag / mbarrier ran out
+    kBadArgument = 2,
+};
+
+// ---- scalar conversions ----------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+
+// round-trip through the storage type (what writing and re-reading would give)
+template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f<T>(from_f<T>(v)); }
+
+// ---- 8-element vector access -----------------------------------------------
+template <typename T> struct Vec8 {
+    // 16-bit types: one 16-byte transaction
+    static __device__ __forceinline__ void load(const T* p, float (&o)[8]) {
+        uint4 r = *reinterpret_cast<const uint4*>(p);
+        const T* e = reinterpret_cast<const T*>(&r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = to_f<T>(e[i]);
+    }
+    static __device__ __forceinline__ void store(T* p, const float (&v)[8]) {
+        uint4 r;
+        T* e = reinterpret_cast<T*>(&r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] = from_f<T>(v[i]);
+        *reinterpret_cast<uint4*>(p) = r;
+    }
+};
+template <> struct Vec8<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&o)[8]) {
+        float4 a = *reinterpret_cast<const float4*>(p);
+        float4 b = *reinterpret_cast<const float4*>(p + 4);
+        o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w;
+        o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+
+__device__ __forceinline__ void load_idx8(const uint8_t* p, int (&o)[8]) {
+    uint2 r = *reinterpret_cast<const uint2*>(p);
+    o[0] = r.x & 0xff; o[1] = (r.x >> 8) & 0xff; o[2] = (r.x >> 16) & 0xff; o[3] = r.x >> 24;
+    o[4] = r.y & 0xff; o[5] = (r.y >> 8) & 0xff; o[6] = (r.y >> 16) & 0xff; o[7] = r.y >> 24;
+}
+__device__ __forceinline__ void store_idx8(uint8_t* p, const int (&v)[8]) {
+    uint2 r;
+    r.x = (uint32_t)v[0] | ((uint32_t)v[1] << 8) | ((uint32_t)v[2] << 16) | ((uint32_t)v[3] << 24);
+    r.y = (uint32_t)v[4] | ((uint32_t)v[5] << 8) | ((uint32_t)v[6] << 16) | ((uint32_t)v[7] << 24);
+    *reinterpret_cast<uint2*>(p) = r;
+}
+
+// ---- codebook search --------------------------------------------------------
+// cb: 256 sorted fp32 codewords; lut: 4096 words, low 16 bits = number of
+// codewords in lower buckets, high 16 bits = the same for the next bucket, so
+// the insertion point of v lies in [lo, hi].  Result: nearest codeword, equal
+// distances resolve to the lower index.  NaN maps to index 0.
+__device__ __forceinline__ int nearest_index(float v, const float* __restrict__ cb,
+                                             const uint32_t* __restrict__ lut) {
+    float t = __fmul_rn(__fadd_rn(v, 1.0f), (float)(kLutBuckets / 2));
+    int b = (t >= 0.0f) ? ((t < (float)kLutBuckets) ? (int)t : kLutBuckets - 1) : 0;
+    uint32_t e = lut[b];
+    int i = (int)(e & 0xffffu);
+    const int hi = (int)(e >> 16);
+    while (i < hi && cb[i] < v) ++i;
+    const int r = min(i, kCodewords - 1);
+    const int l = max(i - 1, 0);
+    const float dl = fabsf(__fsub_rn(v, cb[l]));
+    const float dr = fabsf(__fsub_rn(v, cb[r]));
+    return (dl <= dr) ? l : r;
+}
+
+// SplitMix64 finaliser of (seed, element index) -> 24 uniform bits in [0, 1).
+__device__ __forceinline__ float sr_uniform(uint64_t seed, uint64_t elem) {
+    uint64_t z = seed * 0x9E3779B97F4A7C15ull + elem + 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z = z ^ (z >> 31);
+    return (float)(uint32_t)(z >> 40) * (1.0f / 16777216.0f);
+}
+
+// Stochastic variant: between the two neighbouring codewords lo <= v <= hi pick
+// hi with probability (v - lo) / (hi - lo).
+__device__ __forceinline__ int stochastic_index(float v, const float* __restrict__ cb,
+                                                const uint32_t* __restrict__ lut, float u) {
+    float t = __fmul_rn(__fadd_rn(v, 1.0f), (float)(kLutBuckets / 2));
+    int b = (t >= 0.0f) ? ((t < (float)kLutBuckets) ? (int)t : kLutBuckets - 1) : 0;
+    uint32_t e = lut[b];
+    int i = (int)(e & 0xffffu);
+    const int hi = (int)(e >> 16);
+    while (i < hi && cb[i] < v) ++i;
+    const int r = min(i, kCodewords - 1);
+    const int l = max(i - 1, 0);
+    const float lo_v = cb[l], hi_v = cb[r];
+    if (!(hi_v > lo_v) || v <= lo_v) return (v >= hi_v) ? r : l;
+    if (v >= hi_v) return r;
+    const float pr = (v - lo_v) / (hi_v - lo_v);
+    return (u < pr) ? r : l;
+}
+
+// ---- block reductions -------------------------------------------------------
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// float atomic max for non-negative values (their int bit patterns order alike)
+__device__ __forceinline__ void atomic_max_nonneg(float* addr, float v) {
+    atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
+}
+
+// ---- bounded waits on flags written by another GPU --------------------------
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Spin until *flag >= want or the iteration budget runs out.  Returns false on
+// timeout; the caller records kWaitTimeout and leaves without touching peers.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want,
+                                             long long max_iters) {
+    for (long long it = 0; it < max_iters; ++it) {
+        if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) return true;
+        __nanosleep(64);
+    }
+    return false;
+}
+
+}  // namespace gx

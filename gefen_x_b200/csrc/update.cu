@@ -1,0 +1,660 @@
+// Multi-tensor Gefen update kernels for sm_100a.
+//
+// Replaces the reference's per-parameter kernel families (reference
+// src/gefen/kernels/automatic_gefen_fused_kernel.cu: block path :474-760 and
+// :979-1470, factored path :1596-1990, vmean :40-120 of
+// automatic_vmean_kernel.cu) with four persistent, descriptor-driven kernels:
+//
+//   block_update    one worker (thread / warp / CTA) owns a whole block:
+//                   statistics, second-moment EMA, requantisation and the
+//                   parameter write in one launch for every tensor of the plan.
+//   factored_stats  one pass over grad + indices: per-block |m| maximum, row and
+//                   column sums of g^2.
+//   factored_ema    one CTA per tensor: v_row / v_col EMAs, the cross-shard sum
+//                   of the column statistics (peer loads over NVLink with
+//                   bounded waits) and the per-row / per-column step factors.
+//   factored_apply  requantise + parameter write with the per-element step
+//                   rfac[i] * cfac[j].
+//
+// The gradient of a tensor may be given as up to eight sources (the slices of
+// this rank's shard inside every peer's unsharded bf16 gradient buffer); they
+// are summed in fp32 and rounded to the gradient dtype, which is what a
+// reduce-scatter would have delivered, so the collective is fused into the
+// update.  HBM-bound: 16-byte vector loads, 8 elements per thread, several rows
+// in flight per thread, persistent CTAs walking a contiguous tile range so that
+// column partial sums are flushed once per column tile.
+#include "common.cuh"
+#include "update.h"
+#include <type_traits>
+
+namespace gx {
+namespace {
+
+constexpr int kThreads = 256;
+
+struct Smem {
+    float cb[kCodewords];
+    uint32_t lut[kLutBuckets];
+    float red[kThreads / 32 * 2];
+    float bcast[4];
+};
+
+__device__ __forceinline__ void load_tables(Smem& s, const LaunchCommon& c) {
+    for (int i = threadIdx.x; i < kCodewords; i += blockDim.x) s.cb[i] = c.codebook[i];
+    for (int i = threadIdx.x; i < kLutBuckets; i += blockDim.x) s.lut[i] = c.lut[i];
+    __syncthreads();
+}
+
+__device__ __forceinline__ int find_tensor(const int* __restrict__ start, int n, int tile) {
+    int lo = 0, hi = n;  // start[lo] <= tile < start[hi]
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (start[mid] <= tile) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+// Gradient chunk of 8 (VEC=8) or 1 element: sum of the sources in fp32, scaled,
+// rounded to the storage type when more than one source contributed.
+template <typename T, int VEC>
+__device__ __forceinline__ void load_grad(const TensorDesc& d, long long off, float gs, float (&g)[VEC]) {
+    if constexpr (VEC == 8) {
+        Vec8<T>::load(reinterpret_cast<const T*>(d.g[0]) + off, g);
+        if (d.n_src > 1) {
+            for (int s = 1; s < d.n_src; ++s) {
+                float t[8];
+                Vec8<T>::load(reinterpret_cast<const T*>(d.g[s]) + off, t);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) g[e] += t[e];
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) g[e] = round_to<T>(__fmul_rn(g[e], d.src_scale));
+        }
+    } else {
+        float a = to_f<T>(reinterpret_cast<const T*>(d.g[0])[off]);
+        if (d.n_src > 1) {
+            for (int s = 1; s < d.n_src; ++s) a += to_f<T>(reinterpret_cast<const T*>(d.g[s])[off]);
+            a = round_to<T>(__fmul_rn(a, d.src_scale));
+        }
+        g[0] = a;
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) g[e] = __fmul_rn(g[e], gs);
+}
+
+template <int VEC>
+__device__ __forceinline__ void load_index(const uint8_t* p, int (&o)[VEC]) {
+    if constexpr (VEC == 8) load_idx8(p, o);
+    else o[0] = p[0];
+}
+template <int VEC>
+__device__ __forceinline__ void store_index(uint8_t* p, const int (&v)[VEC]) {
+    if constexpr (VEC == 8) store_idx8(p, v);
+    else p[0] = (uint8_t)v[0];
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void load_param(const T* p, float (&o)[VEC]) {
+    if constexpr (VEC == 8) Vec8<T>::load(p, o);
+    else o[0] = to_f<T>(p[0]);
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void store_param(T* p, const float (&v)[VEC]) {
+    if constexpr (VEC == 8) Vec8<T>::store(p, v);
+    else p[0] = from_f<T>(v[0]);
+}
+
+__device__ __forceinline__ float ema_momentum(float cbv, float mag_old, float g, float b1, float omb1) {
+    return __fadd_rn(__fmul_rn(__fmul_rn(cbv, mag_old), b1), __fmul_rn(g, omb1));
+}
+
+template <typename T>
+__device__ __forceinline__ float apply_one(float pf, float q, float step, float lr, float wdf) {
+    if (wdf != 1.0f) pf = round_to<T>(__fmul_rn(pf, wdf));
+    return __fsub_rn(pf, __fmul_rn(__fmul_rn(q, step), lr));
+}
+
+__device__ __forceinline__ int quantise(float n, const Smem& s, const LaunchCommon& c, long long elem) {
+    if (c.stochastic) return stochastic_index(n, s.cb, s.lut, sr_uniform(c.sr_seed, (uint64_t)elem));
+    return nearest_index(n, s.cb, s.lut);
+}
+
+// ---------------------------------------------------------------------------
+// block path
+// ---------------------------------------------------------------------------
+// One worker of NL lanes owns block `blk` of tensor d.  MODE 0: NL = 1 thread,
+// 1: a warp, 2: the CTA.
+template <typename T, int VEC, int MODE>
+__device__ void block_worker(const TensorDesc& d, const LaunchCommon& c, Smem& s, long long blk,
+                             bool valid, float gs) {
+    const int lane = (MODE == 0) ? 0 : (MODE == 1 ? (threadIdx.x & 31) : threadIdx.x);
+    const int nl = (MODE == 0) ? 1 : (MODE == 1 ? 32 : kThreads);
+    const int P = d.period;
+    const long long base = valid ? blk * (long long)P : 0;
+    // state of the block is read before the reduction barrier and written after it
+    const float mag_old = valid ? d.mag[blk] : 0.f;
+    const float v_old = valid ? d.v0[blk] : 0.f;
+    T* p = reinterpret_cast<T*>(d.p);
+    float amax = 0.f, ssq = 0.f;
+    if (valid) {
+        for (int e0 = lane * VEC; e0 < P; e0 += nl * VEC) {
+            float g[VEC];
+            int ix[VEC];
+            load_grad<T, VEC>(d, base + e0, gs, g);
+            load_index<VEC>(d.idx + base + e0, ix);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                float m = ema_momentum(s.cb[ix[e]], mag_old, g[e], d.beta1, d.omb1);
+                amax = fmaxf(amax, fabsf(m));
+                ssq += g[e] * g[e];
+            }
+        }
+    }
+    if (MODE == 1) {
+        amax = warp_max(amax);
+        ssq = warp_sum(ssq);
+    } else if (MODE == 2) {
+        amax = warp_max(amax);
+        ssq = warp_sum(ssq);
+        const int w = threadIdx.x >> 5;
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) { s.red[w] = amax; s.red[8 + w] = ssq; }
+        __syncthreads();
+        amax = s.red[0];
+        ssq = s.red[8];
+#pragma unroll
+        for (int i = 1; i < kThreads / 32; ++i) { amax = fmaxf(amax, s.red[i]); ssq += s.red[8 + i]; }
+    }
+    if (!valid) return;
+    const float lr = d.scal[0], s2 = d.scal[1], inv_bc1 = d.scal[2], wdf = d.scal[3];
+    const float ms = __fmul_rn(ssq, 1.0f / (float)P);
+    const float v = __fadd_rn(__fmul_rn(v_old, d.beta2), __fmul_rn(ms, d.omb2));
+    const float h = __fadd_rn(__fmul_rn(__fsqrt_rn(v), s2), d.eps);
+    const float step = __fmul_rn(__frcp_rn(h), inv_bc1);
+    const float inv = amax > 0.f ? __frcp_rn(amax) : 0.f;
+    if (MODE == 1) __syncwarp();
+    if (lane == 0) { d.v0[blk] = v; d.mag[blk] = amax; }
+    for (int e0 = lane * VEC; e0 < P; e0 += nl * VEC) {
+        float g[VEC], pf[VEC];
+        int ix[VEC];
+        load_grad<T, VEC>(d, base + e0, gs, g);
+        load_index<VEC>(d.idx + base + e0, ix);
+        load_param<T, VEC>(p + base + e0, pf);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            float m = ema_momentum(s.cb[ix[e]], mag_old, g[e], d.beta1, d.omb1);
+            int k = quantise(__fmul_rn(m, inv), s, c, base + e0 + e);
+            ix[e] = k;
+            pf[e] = apply_one<T>(pf[e], __fmul_rn(s.cb[k], amax), step, lr, wdf);
+        }
+        store_index<VEC>(d.idx + base + e0, ix);
+        store_param<T, VEC>(p + base + e0, pf);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) block_update_kernel(LaunchCommon c) {
+    __shared__ Smem s;
+    load_tables(s, c);
+    const float gs = c.gscale ? *c.gscale : 1.0f;
+    for (int tile = blockIdx.x; tile < c.total_tiles; tile += gridDim.x) {
+        const int ti = find_tensor(c.tile_start, c.n_tensors, tile);
+        const TensorDesc& d = c.descs[ti];
+        const long long local = tile - c.tile_start[ti];
+        if (d.mode == 2) {
+            if (d.vec) block_worker<T, 8, 2>(d, c, s, local, local < d.nb, gs);
+            else block_worker<T, 1, 2>(d, c, s, local, local < d.nb, gs);
+        } else if (d.mode == 1) {
+            const long long blk = local * (kThreads / 32) + (threadIdx.x >> 5);
+            if (d.vec) block_worker<T, 8, 1>(d, c, s, blk, blk < d.nb, gs);
+            else block_worker<T, 1, 1>(d, c, s, blk, blk < d.nb, gs);
+        } else {
+            const long long blk = local * kThreads + threadIdx.x;
+            block_worker<T, 1, 0>(d, c, s, blk, blk < d.nb, gs);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// factored path
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ long long block_of(const TensorDesc& d, int r, int c0) {
+    switch (d.blk_mode) {
+        case 0: return r;
+        case 1: return (long long)r * (d.cols / d.period) + c0 / d.period;
+        case 2: return r / (d.period / d.cols);
+        default: return ((long long)r * d.cols + c0) / d.period;
+    }
+}
+
+struct TileCursor {
+    int ti, ct;          // tensor, column tile
+    int r0, r1;          // row range of the tile
+};
+
+__device__ __forceinline__ TileCursor locate(const LaunchCommon& c, int tile) {
+    TileCursor t;
+    t.ti = find_tensor(c.tile_start, c.n_tensors, tile);
+    const TensorDesc& d = c.descs[t.ti];
+    const int local = tile - c.tile_start[t.ti];
+    const int n_row_tiles = (d.rows + d.rows_per_tile - 1) / d.rows_per_tile;
+    t.ct = local / n_row_tiles;
+    const int rt = local - t.ct * n_row_tiles;
+    t.r0 = rt * d.rows_per_tile;
+    t.r1 = min(d.rows, t.r0 + d.rows_per_tile);
+    return t;
+}
+
+template <typename T, int VEC, int U>
+__device__ void stats_tile(const TensorDesc& d, const Smem& s, const TileCursor& t, float gs,
+                           float (&csum)[VEC], bool uniform) {
+    const int tx = threadIdx.x % d.tcols, ty = threadIdx.x / d.tcols;
+    const int c0 = (t.ct * d.tcols + tx) * VEC;
+    const bool act = c0 < d.cols;
+    for (int rb = t.r0 + ty; rb < t.r1; rb += d.trows * U) {
+        float g[U][VEC];
+        int ix[U][VEC];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int r = rb + u * d.trows;
+            if (act && r < t.r1) {
+                const long long off = (long long)r * d.cols + c0;
+                load_grad<T, VEC>(d, off, gs, g[u]);
+                load_index<VEC>(d.idx + off, ix[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int r = rb + u * d.trows;
+            if (r >= t.r1) break;  // uniform across the warp: a warp shares ty
+            float amax = 0.f, rs = 0.f;
+            long long blk = 0;
+            if (act) {
+                blk = block_of(d, r, c0);
+                const float mo = d.mag[blk];
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    float m = ema_momentum(s.cb[ix[u][e]], mo, g[u][e], d.beta1, d.omb1);
+                    amax = fmaxf(amax, fabsf(m));
+                    const float sq = g[u][e] * g[u][e];
+                    rs += sq;
+                    csum[e] += sq;
+                }
+            }
+            rs = warp_sum(rs);
+            if ((threadIdx.x & 31) == 0 && act) atomicAdd(d.row_sq + r, rs);
+            if (uniform) {
+                amax = warp_max(amax);
+                if ((threadIdx.x & 31) == 0 && act) atomic_max_nonneg(d.mag_new + blk, amax);
+            } else if (act) {
+                atomic_max_nonneg(d.mag_new + blk, amax);
+            }
+        }
+    }
+}
+
+template <int VEC>
+__device__ __forceinline__ void flush_cols(const TensorDesc& d, int ct, float (&csum)[VEC]) {
+    const int tx = threadIdx.x % d.tcols;
+    const int c0 = (ct * d.tcols + tx) * VEC;
+    if (c0 < d.cols) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            if (csum[e] != 0.f) atomicAdd(d.col_sq + c0 + e, csum[e]);
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) csum[e] = 0.f;
+}
+
+__device__ __forceinline__ bool warp_uniform_blocks(const TensorDesc& d, int vec) {
+    if (d.blk_mode == 0 || d.blk_mode == 2) return true;
+    if (d.blk_mode == 1) return (d.period % (32 * vec)) == 0;
+    return false;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) factored_stats_kernel(LaunchCommon c) {
+    __shared__ Smem s;
+    for (int i = threadIdx.x; i < kCodewords; i += blockDim.x) s.cb[i] = c.codebook[i];
+    __syncthreads();
+    const float gs = c.gscale ? *c.gscale : 1.0f;
+    const long long T0 = (long long)c.total_tiles * blockIdx.x / gridDim.x;
+    const long long T1 = (long long)c.total_tiles * (blockIdx.x + 1) / gridDim.x;
+    float csum8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    float csum1[1] = {0};
+    int cur_ti = -1, cur_ct = -1;
+    for (long long tile = T0; tile < T1; ++tile) {
+        const TileCursor t = locate(c, (int)tile);
+        if (cur_ti >= 0 && (t.ti != cur_ti || t.ct != cur_ct)) {
+            const TensorDesc& pd = c.descs[cur_ti];
+            if (pd.vec) flush_cols<8>(pd, cur_ct, csum8); else flush_cols<1>(pd, cur_ct, csum1);
+        }
+        cur_ti = t.ti; cur_ct = t.ct;
+        const TensorDesc& d = c.descs[t.ti];
+        if (d.vec) {
+            const bool uni = warp_uniform_blocks(d, 8);
+            if (d.n_src > 1) stats_tile<T, 8, 1>(d, s, t, gs, csum8, uni);
+            else stats_tile<T, 8, 4>(d, s, t, gs, csum8, uni);
+        } else {
+            stats_tile<T, 1, 4>(d, s, t, gs, csum1, warp_uniform_blocks(d, 1));
+        }
+    }
+    if (cur_ti >= 0) {
+        const TensorDesc& pd = c.descs[cur_ti];
+        if (pd.vec) flush_cols<8>(pd, cur_ct, csum8); else flush_cols<1>(pd, cur_ct, csum1);
+    }
+}
+
+// One CTA (1024 threads) per tensor.
+constexpr int kEmaThreads = 1024;
+
+__device__ __forceinline__ float cta_sum_1024(float v, float* red) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < kEmaThreads / 32; ++i) t += red[i];
+    return t;
+}
+
+__global__ void __launch_bounds__(kEmaThreads) factored_ema_kernel(LaunchCommon c) {
+    __shared__ float red[kEmaThreads / 32];
+    __shared__ int ok_s;
+    const int ti = blockIdx.x;
+    if (ti >= c.n_tensors) return;
+    const TensorDesc& d = c.descs[ti];
+    const float inv_cols = 1.0f / (float)d.cols;
+    const float inv_rows = 1.0f / (float)d.total_rows;
+    const float inv_bc2 = d.scal[1];
+    // rows: EMA and the sum of the new v_row (fixed order: strided per thread, tree per CTA)
+    float part = 0.f;
+    for (int i = threadIdx.x; i < d.rows; i += kEmaThreads) {
+        const float ms = __fmul_rn(d.row_sq[i], inv_cols);
+        const float v = __fadd_rn(__fmul_rn(d.v0[i], d.beta2), __fmul_rn(ms, d.omb2));
+        d.v0[i] = v;
+        d.row_sq[i] = 0.f;
+        part += v;
+    }
+    float sum_v = cta_sum_1024(part, red);
+    bool exchanged = false;
+    if (d.world > 1) {
+        // publish this shard's column partials and sum(v_row), then wait for every peer
+        for (int j = threadIdx.x; j < d.cols; j += kEmaThreads) d.xchg_local[j] = d.col_sq[j];
+        if (threadIdx.x == 0) d.xchg_local[d.cols] = sum_v;
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x < d.world) st_release_sys(d.flag_peer[threadIdx.x] + d.rank, d.epoch);
+        if (threadIdx.x == 0) ok_s = 1;
+        __syncthreads();
+        if (threadIdx.x < d.world) {
+            if (!wait_flag_ge(d.flag_local + threadIdx.x, d.epoch, c.wait_iters)) {
+                ok_s = 0;
+                if (c.status) atomicExch(c.status, (int)kWaitTimeout);
+            }
+        }
+        __syncthreads();
+        exchanged = ok_s != 0;
+        if (exchanged) {
+            float t = 0.f;
+            for (int r = 0; r < d.world; ++r) t += d.xchg_peer[r][d.cols];
+            sum_v = t;
+        }
+    }
+    const float mean = fmaxf(__fmul_rn(sum_v, inv_rows), 1.17549435e-38f);
+    const float inv_mean = __frcp_rn(mean);
+    for (int i = threadIdx.x; i < d.rows; i += kEmaThreads)
+        d.rfac[i] = __fsqrt_rn(__fmul_rn(__fmul_rn(d.v0[i], inv_mean), inv_bc2));
+    for (int j = threadIdx.x; j < d.cols; j += kEmaThreads) {
+        float cs;
+        if (exchanged) {
+            cs = 0.f;
+            for (int r = 0; r < d.world; ++r) cs += d.xchg_peer[r][j];
+        } else {
+            cs = d.col_sq[j];
+        }
+        const float ms = __fmul_rn(cs, inv_rows);
+        const float v = __fadd_rn(__fmul_rn(d.v1[j], d.beta2), __fmul_rn(ms, d.omb2));
+        d.v1[j] = v;
+        d.col_sq[j] = 0.f;
+        d.cfac[j] = __fsqrt_rn(v);
+    }
+}
+
+template <typename T, int VEC, int U>
+__device__ void apply_tile(const TensorDesc& d, const LaunchCommon& c, const Smem& s,
+                           const TileCursor& t, float gs, const float (&cf)[VEC]) {
+    const int tx = threadIdx.x % d.tcols, ty = threadIdx.x / d.tcols;
+    const int c0 = (t.ct * d.tcols + tx) * VEC;
+    if (c0 >= d.cols) return;
+    const float lr = d.scal[0], inv_bc1 = d.scal[2], wdf = d.scal[3];
+    T* p = reinterpret_cast<T*>(d.p);
+    for (int rb = t.r0 + ty; rb < t.r1; rb += d.trows * U) {
+        float g[U][VEC], pf[U][VEC];
+        int ix[U][VEC];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int r = rb + u * d.trows;
+            if (r < t.r1) {
+                const long long off = (long long)r * d.cols + c0;
+                load_grad<T, VEC>(d, off, gs, g[u]);
+                load_index<VEC>(d.idx + off, ix[u]);
+                load_param<T, VEC>(p + off, pf[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int r = rb + u * d.trows;
+            if (r >= t.r1) break;
+            const long long off = (long long)r * d.cols + c0;
+            const long long blk = block_of(d, r, c0);
+            const float mo = d.mag[blk], mn = d.mag_new[blk];
+            const float inv = mn > 0.f ? __frcp_rn(mn) : 0.f;
+            const float rf = d.rfac[r];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                float m = ema_momentum(s.cb[ix[u][e]], mo, g[u][e], d.beta1, d.omb1);
+                int k = quantise(__fmul_rn(m, inv), s, c, off + e);
+                ix[u][e] = k;
+                const float h = __fadd_rn(__fmul_rn(rf, cf[e]), d.eps);
+                const float step = __fmul_rn(__frcp_rn(h), inv_bc1);
+                pf[u][e] = apply_one<T>(pf[u][e], __fmul_rn(s.cb[k], mn), step, lr, wdf);
+            }
+            store_index<VEC>(d.idx + off, ix[u]);
+            store_param<T, VEC>(p + off, pf[u]);
+        }
+    }
+}
+
+template <int VEC>
+__device__ __forceinline__ void load_cfac(const TensorDesc& d, int ct, float (&cf)[VEC]) {
+    const int tx = threadIdx.x % d.tcols;
+    const int c0 = (ct * d.tcols + tx) * VEC;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) cf[e] = (c0 + e < d.cols) ? d.cfac[c0 + e] : 0.f;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) factored_apply_kernel(LaunchCommon c) {
+    __shared__ Smem s;
+    load_tables(s, c);
+    const float gs = c.gscale ? *c.gscale : 1.0f;
+    const long long T0 = (long long)c.total_tiles * blockIdx.x / gridDim.x;
+    const long long T1 = (long long)c.total_tiles * (blockIdx.x + 1) / gridDim.x;
+    float cf8[8], cf1[1];
+    int cur_ti = -1, cur_ct = -1;
+    for (long long tile = T0; tile < T1; ++tile) {
+        const TileCursor t = locate(c, (int)tile);
+        const TensorDesc& d = c.descs[t.ti];
+        if (t.ti != cur_ti || t.ct != cur_ct) {
+            if (d.vec) load_cfac<8>(d, t.ct, cf8); else load_cfac<1>(d, t.ct, cf1);
+            cur_ti = t.ti; cur_ct = t.ct;
+        }
+        if (d.vec) {
+            if (d.n_src > 1) apply_tile<T, 8, 1>(d, c, s, t, gs, cf8);
+            else apply_tile<T, 8, 2>(d, c, s, t, gs, cf8);
+        } else {
+            apply_tile<T, 1, 2>(d, c, s, t, gs, cf1);
+        }
+    }
+}
+
+// mag <- mag_new ; mag_new <- 0, for every tensor of the plan
+__global__ void __launch_bounds__(kThreads) finalize_magnitude_kernel(LaunchCommon c) {
+    for (int ti = 0; ti < c.n_tensors; ++ti) {
+        const TensorDesc& d = c.descs[ti];
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < d.nb;
+             i += (long long)gridDim.x * blockDim.x) {
+            d.mag[i] = d.mag_new[i];
+            d.mag_new[i] = 0.f;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// gradient reduction (reduce-scatter by peer loads) and clipping coefficient
+// ---------------------------------------------------------------------------
+struct SrcList { const void* p[kDescMaxSrc]; };
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) reduce_sources_kernel(T* __restrict__ out, SrcList src, int n_src,
+                                                                   long long numel, float scale,
+                                                                   float* __restrict__ partials) {
+    __shared__ float red[kThreads / 32];
+    float ssq = 0.f;
+    const long long n8 = numel / 8;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
+         i += (long long)gridDim.x * blockDim.x) {
+        float a[8];
+        Vec8<T>::load(reinterpret_cast<const T*>(src.p[0]) + i * 8, a);
+        for (int s = 1; s < n_src; ++s) {
+            float t[8];
+            Vec8<T>::load(reinterpret_cast<const T*>(src.p[s]) + i * 8, t);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[e] += t[e];
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            a[e] = (n_src > 1 || scale != 1.0f) ? round_to<T>(__fmul_rn(a[e], scale)) : a[e];
+            ssq += a[e] * a[e];
+        }
+        if (out) Vec8<T>::store(out + i * 8, a);
+    }
+    // tail
+    for (long long i = n8 * 8 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < numel;
+         i += (long long)gridDim.x * blockDim.x) {
+        float a = to_f<T>(reinterpret_cast<const T*>(src.p[0])[i]);
+        for (int s = 1; s < n_src; ++s) a += to_f<T>(reinterpret_cast<const T*>(src.p[s])[i]);
+        a = (n_src > 1 || scale != 1.0f) ? round_to<T>(__fmul_rn(a, scale)) : a;
+        ssq += a * a;
+        if (out) out[i] = from_f<T>(a);
+    }
+    if (partials) {
+        ssq = warp_sum(ssq);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ssq;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.f;
+#pragma unroll
+            for (int i = 0; i < kThreads / 32; ++i) t += red[i];
+            partials[blockIdx.x] += t;
+        }
+    }
+}
+
+__global__ void clip_coef_kernel(const float* __restrict__ partials, int n, float max_norm,
+                                 float* __restrict__ coef) {
+    __shared__ double red[32];
+    double acc = 0.0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) acc += (double)partials[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += red[i];
+        const float norm = (float)sqrt(t);
+        coef[1] = norm;
+        coef[0] = (max_norm > 0.f) ? fminf(1.0f, max_norm / (norm + 1e-6f)) : 1.0f;
+    }
+}
+
+template <typename F>
+cudaError_t dispatch(int dtype, F&& f) {
+    switch (dtype) {
+        case kF32: return f((float*)nullptr);
+        case kBF16: return f((__nv_bfloat16*)nullptr);
+        case kF16: return f((__half*)nullptr);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_block_update(const LaunchCommon& c, int dtype, int sm_count, cudaStream_t st) {
+    if (c.total_tiles <= 0) return cudaSuccess;
+    const int grid = min(c.total_tiles, sm_count * 4);
+    return dispatch(dtype, [&](auto* tag) {
+        using T = std::remove_pointer_t<decltype(tag)>;
+        block_update_kernel<T><<<grid, kThreads, 0, st>>>(c);
+        return cudaGetLastError();
+    });
+}
+
+cudaError_t launch_factored_stats(const LaunchCommon& c, int dtype, int sm_count, cudaStream_t st) {
+    if (c.total_tiles <= 0) return cudaSuccess;
+    const int grid = min(c.total_tiles, sm_count * 4);
+    return dispatch(dtype, [&](auto* tag) {
+        using T = std::remove_pointer_t<decltype(tag)>;
+        factored_stats_kernel<T><<<grid, kThreads, 0, st>>>(c);
+        return cudaGetLastError();
+    });
+}
+
+cudaError_t launch_factored_ema(const LaunchCommon& c, cudaStream_t st) {
+    if (c.n_tensors <= 0) return cudaSuccess;
+    factored_ema_kernel<<<c.n_tensors, kEmaThreads, 0, st>>>(c);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_factored_apply(const LaunchCommon& c, int dtype, int sm_count, cudaStream_t st) {
+    if (c.total_tiles <= 0) return cudaSuccess;
+    const int grid = min(c.total_tiles, sm_count * 3);
+    return dispatch(dtype, [&](auto* tag) {
+        using T = std::remove_pointer_t<decltype(tag)>;
+        factored_apply_kernel<T><<<grid, kThreads, 0, st>>>(c);
+        return cudaGetLastError();
+    });
+}
+
+cudaError_t launch_finalize_magnitude(const LaunchCommon& c, int sm_count, cudaStream_t st) {
+    if (c.n_tensors <= 0) return cudaSuccess;
+    finalize_magnitude_kernel<<<sm_count, kThreads, 0, st>>>(c);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_reduce_sources(void* out, const void* const* src, int n_src, long long numel,
+                                  float scale, float* partials, int n_partials, int dtype,
+                                  cudaStream_t st) {
+    if (numel <= 0) return cudaSuccess;
+    if (n_src < 1 || n_src > kDescMaxSrc) return cudaErrorInvalidValue;
+    SrcList sl;
+    for (int i = 0; i < kDescMaxSrc; ++i) sl.p[i] = i < n_src ? src[i] : nullptr;
+    long long want = (numel / 8 + kThreads - 1) / kThreads;
+    int grid = (int)max(1LL, min(want, (long long)(n_partials > 0 ? n_partials : 1184)));
+    return dispatch(dtype, [&](auto* tag) {
+        using T = std::remove_pointer_t<decltype(tag)>;
+        reduce_sources_kernel<T><<<grid, kThreads, 0, st>>>((T*)out, sl, n_src, numel, scale, partials);
+        return cudaGetLastError();
+    });
+}
+
+cudaError_t launch_clip_coef(const float* partials, int n, float max_norm, float* coef,
+                             cudaStream_t st) {
+    clip_coef_kernel<<<1, 1024, 0, st>>>(partials, n, max_norm, coef);
+    return cudaGetLastError();
+}
+
+}  // namespace gx

@@ -1,0 +1,355 @@
+"""Host side of the multi-tensor update kernels (``csrc/update.cu``).
+
+A *plan* is the device-resident description of every tensor that one launch
+sequence updates: an array of ``TensorDesc`` records, the tile prefix table and
+one scratch arena.  Plans are cached by the optimizer and rebuilt only when a
+pointer or a geometry changes, so a steady-state step costs one small pinned
+host->device copy of the per-step scalars plus one operator call per plan.
+
+The reference steps one parameter per kernel launch sequence through pybind
+entry points (reference ``src/gefen/kernels/automatic_gefen_fused.py:581-771``).
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ._ext import DTYPE_CODE, available, ops
+
+MAX_SRC = 8
+_THREADS = 256
+DEFAULT_WAIT_ITERS = 4_000_000  # ~1 s of polling with 64 ns back-off
+
+
+class TensorDesc(ctypes.Structure):
+    """Mirror of ``gx::TensorDesc`` (csrc/update.h); size checked against the library."""
+
+    _fields_ = [
+        ("p", ctypes.c_void_p),
+        ("g", ctypes.c_void_p * MAX_SRC),
+        ("idx", ctypes.c_void_p),
+        ("mag", ctypes.c_void_p),
+        ("mag_new", ctypes.c_void_p),
+        ("v0", ctypes.c_void_p),
+        ("v1", ctypes.c_void_p),
+        ("row_sq", ctypes.c_void_p),
+        ("col_sq", ctypes.c_void_p),
+        ("rfac", ctypes.c_void_p),
+        ("cfac", ctypes.c_void_p),
+        ("scal", ctypes.c_void_p),
+        ("xchg_local", ctypes.c_void_p),
+        ("xchg_peer", ctypes.c_void_p * MAX_SRC),
+        ("flag_local", ctypes.c_void_p),
+        ("flag_peer", ctypes.c_void_p * MAX_SRC),
+        ("numel", ctypes.c_longlong),
+        ("nb", ctypes.c_longlong),
+        ("rows", ctypes.c_int),
+        ("cols", ctypes.c_int),
+        ("period", ctypes.c_int),
+        ("total_rows", ctypes.c_int),
+        ("n_src", ctypes.c_int),
+        ("blk_mode", ctypes.c_int),
+        ("tcols", ctypes.c_int),
+        ("trows", ctypes.c_int),
+        ("n_col_tiles", ctypes.c_int),
+        ("rows_per_tile", ctypes.c_int),
+        ("mode", ctypes.c_int),
+        ("vec", ctypes.c_int),
+        ("world", ctypes.c_int),
+        ("rank", ctypes.c_int),
+        ("epoch", ctypes.c_uint32),
+        ("beta1", ctypes.c_float),
+        ("omb1", ctypes.c_float),
+        ("beta2", ctypes.c_float),
+        ("omb2", ctypes.c_float),
+        ("eps", ctypes.c_float),
+        ("src_scale", ctypes.c_float),
+    ]
+
+
+def _desc_stride() -> int:
+    n = ctypes.sizeof(TensorDesc)
+    return (n + 15) // 16 * 16
+
+
+_checked = False
+
+
+def _check_layout() -> None:
+    global _checked
+    if _checked:
+        return
+    want = int(ops().desc_size())
+    if want != _desc_stride():
+        raise RuntimeError(
+            "TensorDesc layout mismatch: python {} bytes, library {} bytes".format(
+                _desc_stride(), want))
+    _checked = True
+
+
+@dataclass
+class PeerGrad:
+    """A gradient given as slices inside several (peer) buffers.
+
+    ``ptrs[s]`` is the device address of this rank's slice inside source ``s``;
+    the kernels use ``round(sum_s src_s * scale)``.  ``materialize`` returns that
+    value as a local tensor (used for the first-step analysis and the CPU path).
+    """
+
+    ptrs: Sequence[int]
+    shape: Tuple[int, ...]
+    dtype: torch.dtype
+    device: torch.device
+    scale: float = 1.0
+    _cache: Any = None
+
+    def numel(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+    def materialize(self) -> torch.Tensor:
+        out = torch.empty(self.shape, dtype=self.dtype, device=self.device)
+        ops().reduce_sources(out, list(self.ptrs), out.numel(), float(self.scale), None,
+                             DTYPE_CODE[self.dtype], self.device.index or 0)
+        return out
+
+
+@dataclass
+class ShardExchange:
+    """Where a ``Shard(0)`` factored tensor publishes / reads its column statistics."""
+
+    total_rows: int
+    world: int = 1
+    rank: int = 0
+    xchg_local: int = 0
+    xchg_peer: Sequence[int] = ()
+    flag_local: int = 0
+    flag_peer: Sequence[int] = ()
+    epoch: int = 0
+    # host-side reductions for the decomposed path
+    reduce_cols: Any = None
+    reduce_scalar: Any = None
+
+
+@dataclass
+class Item:
+    """One tensor of a plan."""
+
+    p: torch.Tensor                   # contiguous local parameter (shard)
+    grad: Any                         # torch.Tensor (contiguous) or PeerGrad
+    state: Dict[str, Any]
+    period: int
+    beta1: float
+    beta2: float
+    eps: float
+    scalars: Tuple[float, float, float, float] = (0.0, 1.0, 1.0, 1.0)
+    scal_ptr: int = 0                 # device address of the scalar row (capturable), or 0
+    shard: Optional[ShardExchange] = None
+
+
+def _aligned(ptr: int, n: int) -> bool:
+    return ptr % n == 0
+
+
+def _pick_tcols(chunks: int) -> int:
+    best, best_waste = 256, None
+    for t in (256, 128, 64, 32):
+        waste = (chunks + t - 1) // t * t - chunks
+        if best_waste is None or waste < best_waste:
+            best, best_waste = t, waste
+    return best
+
+
+class Plan:
+    """Device tables for one (device, kind, dtype) group of tensors."""
+
+    def __init__(self, kind: str, items: List[Item], device: torch.device, dtype: torch.dtype):
+        _check_layout()
+        self.kind = kind
+        self.device = device
+        self.dtype = dtype
+        self.n = len(items)
+        self.signature = self.signature_of(items)
+        stride = _desc_stride()
+        # scratch arena
+        sizes = []
+        for it in items:
+            if kind == "factored":
+                rows, cols = it.p.shape
+                nb = it.p.numel() // it.period
+                sizes.append((nb, rows, cols, rows, cols))
+            else:
+                sizes.append((0, 0, 0, 0, 0))
+        total = sum(sum(s) for s in sizes)
+        self.scratch = torch.zeros(max(total, 1), dtype=torch.float32, device=device)
+        self.scal_host = torch.zeros(self.n, 4, dtype=torch.float32).pin_memory() \
+            if torch.cuda.is_available() else torch.zeros(self.n, 4, dtype=torch.float32)
+        self.scal_dev = torch.zeros(self.n, 4, dtype=torch.float32, device=device)
+        buf = (ctypes.c_ubyte * (stride * self.n))()
+        tile_start = [0]
+        base = self.scratch.data_ptr()
+        cursor = 0
+        self._keepalive = []
+        for i, it in enumerate(items):
+            d = TensorDesc.from_buffer(buf, i * stride)
+            p = it.p
+            st = it.state
+            d.p = p.data_ptr()
+            if isinstance(it.grad, PeerGrad):
+                srcs = list(it.grad.ptrs)
+                d.src_scale = float(it.grad.scale)
+            else:
+                srcs = [it.grad.data_ptr()]
+                d.src_scale = 1.0
+            if not 1 <= len(srcs) <= MAX_SRC:
+                raise ValueError("a gradient needs 1..{} sources".format(MAX_SRC))
+            for s, ptr in enumerate(srcs):
+                d.g[s] = ptr
+            d.n_src = len(srcs)
+            d.idx = st["m_codebook"].data_ptr()
+            d.mag = st["m_magnitude"].data_ptr()
+            d.numel = p.numel()
+            d.period = it.period
+            d.nb = p.numel() // it.period
+            d.beta1 = it.beta1
+            d.omb1 = 1.0 - it.beta1
+            d.beta2 = it.beta2
+            d.omb2 = 1.0 - it.beta2
+            d.eps = it.eps
+            d.scal = it.scal_ptr if it.scal_ptr else self.scal_dev.data_ptr() + 16 * i
+            esz = p.element_size()
+            ptr_ok = _aligned(p.data_ptr(), 16) and all(_aligned(s, 16) for s in srcs) and \
+                _aligned(st["m_codebook"].data_ptr(), 8)
+            if kind == "factored":
+                rows, cols = p.shape
+                nb, nr, nc, _, _ = sizes[i]
+                d.rows, d.cols = rows, cols
+                d.total_rows = it.shard.total_rows if it.shard is not None else rows
+                d.v0 = st["v_row"].data_ptr()
+                d.v1 = st["v_col"].data_ptr()
+                d.mag_new = base + 4 * cursor; cursor += nb
+                d.row_sq = base + 4 * cursor; cursor += nr
+                d.col_sq = base + 4 * cursor; cursor += nc
+                d.rfac = base + 4 * cursor; cursor += nr
+                d.cfac = base + 4 * cursor; cursor += nc
+                P = it.period
+                if P == cols:
+                    d.blk_mode = 0
+                elif cols % P == 0:
+                    d.blk_mode = 1
+                elif P % cols == 0:
+                    d.blk_mode = 2
+                else:
+                    d.blk_mode = 3
+                vec = ptr_ok and cols % 8 == 0 and P % 8 == 0 and (cols * esz) % 16 == 0
+                d.vec = int(vec)
+                unit = 8 if vec else 1
+                chunks = (cols + unit - 1) // unit
+                d.tcols = _pick_tcols(chunks)
+                d.trows = _THREADS // d.tcols
+                d.n_col_tiles = (chunks + d.tcols - 1) // d.tcols
+                d.rows_per_tile = d.trows * 8
+                n_row_tiles = (rows + d.rows_per_tile - 1) // d.rows_per_tile
+                tiles = d.n_col_tiles * n_row_tiles
+                sh = it.shard
+                if sh is not None and sh.world > 1:
+                    d.world, d.rank, d.epoch = sh.world, sh.rank, sh.epoch
+                    d.xchg_local = sh.xchg_local
+                    d.flag_local = sh.flag_local
+                    for r in range(sh.world):
+                        d.xchg_peer[r] = sh.xchg_peer[r]
+                        d.flag_peer[r] = sh.flag_peer[r]
+                else:
+                    d.world, d.rank, d.epoch = 1, 0, 0
+            else:
+                d.v0 = st["vmean"].data_ptr()
+                d.rows, d.cols = int(d.nb), it.period
+                d.total_rows = int(d.nb)
+                P = it.period
+                if P < 32:
+                    d.mode = 0
+                    tiles = (d.nb + _THREADS - 1) // _THREADS
+                elif P < 1024:
+                    d.mode = 1
+                    tiles = (d.nb + 7) // 8
+                else:
+                    d.mode = 2
+                    tiles = d.nb
+                d.vec = int(ptr_ok and P % 8 == 0 and d.mode > 0)
+                d.world, d.rank = 1, 0
+            if tile_start[-1] + tiles >= 2 ** 31:
+                raise ValueError("plan too large for 32-bit tile indices")
+            tile_start.append(tile_start[-1] + int(tiles))
+        self.total_tiles = tile_start[-1]
+        host = torch.frombuffer(buf, dtype=torch.uint8).clone()
+        self.descs = host.to(device)
+        self.tile_start = torch.tensor(tile_start, dtype=torch.int32).to(device)
+        self.uses_host_scalars = any(not it.scal_ptr for it in items)
+
+    @staticmethod
+    def signature_of(items: List[Item]):
+        sig = []
+        for it in items:
+            g = it.grad
+            gp = tuple(g.ptrs) if isinstance(g, PeerGrad) else (g.data_ptr(),)
+            st = it.state
+            sig.append((it.p.data_ptr(), gp, st["m_codebook"].data_ptr(), st["m_magnitude"].data_ptr(),
+                        it.period, it.scal_ptr, tuple(it.p.shape), it.beta1, it.beta2, it.eps,
+                        (it.shard.epoch if it.shard is not None else 0)))
+        return tuple(sig)
+
+    def run(self, items: List[Item], codebook: torch.Tensor, lut: torch.Tensor, *,
+            gscale: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
+            sr_seed: Optional[int] = None, wait_iters: int = DEFAULT_WAIT_ITERS,
+            phases: int = 7) -> None:
+        if self.uses_host_scalars and (phases & 1 or self.kind == "block"):
+            h = self.scal_host
+            for i, it in enumerate(items):
+                h[i, 0], h[i, 1], h[i, 2], h[i, 3] = it.scalars
+            self.scal_dev.copy_(h, non_blocking=True)
+        code = DTYPE_CODE[self.dtype]
+        seed = 0 if sr_seed is None else int(sr_seed)
+        if self.kind == "factored":
+            ops().factored_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, lut,
+                                  gscale, status, code, seed, sr_seed is not None, int(wait_iters),
+                                  int(phases))
+        else:
+            ops().block_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, lut,
+                               gscale, status, code, seed, sr_seed is not None)
+
+
+class PlanCache:
+    """Plans keyed by (kind, device, dtype); rebuilt when a signature changes."""
+
+    def __init__(self):
+        self._plans: Dict[Any, Plan] = {}
+        self.rebuilds = 0
+
+    def get(self, kind: str, items: List[Item]) -> Plan:
+        p0 = items[0].p
+        key = (kind, p0.device, p0.dtype)
+        sig = Plan.signature_of(items)
+        plan = self._plans.get(key)
+        if plan is None or plan.signature != sig:
+            plan = Plan(kind, items, p0.device, p0.dtype)
+            self._plans[key] = plan
+            self.rebuilds += 1
+        return plan
+
+    def clear(self) -> None:
+        self._plans.clear()
+
+
+def reduce_sources(out: Optional[torch.Tensor], ptrs: Sequence[int], numel: int, scale: float,
+                   partials: Optional[torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
+    ops().reduce_sources(out, list(ptrs), int(numel), float(scale), partials, DTYPE_CODE[dtype],
+                         device.index or 0)
+
+
+def clip_coef(partials: torch.Tensor, max_norm: float, coef: torch.Tensor) -> None:
+    ops().clip_coef(partials, float(max_norm), coef)

@@ -1,0 +1,1 @@
+"""Subpackage of gefen_x_b200."""
