@@ -12,6 +12,7 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
 
+#include "comm.h"
 #include "model_ops.h"
 #include "quant.h"
 #include "update.h"
@@ -91,11 +92,12 @@ void factored_update(const Tensor& descs, const Tensor& tile_start, int64_t n_te
                      int64_t total_tiles, const Tensor& codebook, const Tensor& lut,
                      const c10::optional<Tensor>& gscale, const c10::optional<Tensor>& status,
                      int64_t dtype, int64_t sr_seed, bool stochastic, int64_t wait_iters,
-                     int64_t phases) {
+                     int64_t phases, int64_t epoch) {
     // phases bit 0: statistics, bit 1: EMA (+ exchange), bit 2: apply + finalize
     c10::cuda::CUDAGuard guard(descs.device());
     auto c = make_common(descs, tile_start, n_tensors, total_tiles, codebook, lut, gscale, status,
                          sr_seed, stochastic, wait_iters);
+    c.epoch = (uint32_t)epoch;
     const int sms = sm_count();
     auto st = stream();
     if (phases & 1) check(gx::launch_factored_stats(c, (int)dtype, sms, st), "factored_stats");
@@ -164,6 +166,64 @@ Tensor period_errors(const Tensor& flat, const Tensor& divisors_dev, bool input_
                                    n_div, input_is_squared, partials.data_ptr<double>(), ctas, stream()),
           "period_errors");
     return partials;
+}
+
+// ---------------------------------------------------------------------------
+// peer-memory communication (comm.cu)
+// ---------------------------------------------------------------------------
+inline void to_ptrs(at::IntArrayRef v, void** out) {
+    TORCH_CHECK(v.size() >= 1 && v.size() <= 8, "1..8 ranks");
+    for (size_t i = 0; i < v.size(); ++i) out[i] = reinterpret_cast<void*>(v[i]);
+}
+
+void comm_signal(at::IntArrayRef flag_ptrs, int64_t slot, int64_t value, int64_t device_index) {
+    c10::cuda::CUDAGuard guard((c10::DeviceIndex)device_index);
+    void* p[8];
+    to_ptrs(flag_ptrs, p);
+    check(gx::launch_signal(p, (int)flag_ptrs.size(), (int)slot, (unsigned)value, stream()), "signal");
+}
+
+void comm_wait(const Tensor& flags, int64_t n, int64_t value, int64_t max_iters,
+               const c10::optional<Tensor>& status) {
+    c10::cuda::CUDAGuard guard(flags.device());
+    TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == at::kInt && flags.numel() >= n);
+    int* st = (status.has_value() && status->defined()) ? status->data_ptr<int>() : nullptr;
+    check(gx::launch_wait(reinterpret_cast<const unsigned*>(flags.data_ptr<int>()), (int)n, (unsigned)value,
+                          max_iters, st, stream()),
+          "wait");
+}
+
+void comm_gather(at::IntArrayRef src_base, const Tensor& segs, int64_t n_segs, Tensor dst,
+                 const Tensor& unit_prefix, int64_t total_units, int64_t ctas) {
+    c10::cuda::CUDAGuard guard(dst.device());
+    TORCH_CHECK(segs.is_cuda() && segs.scalar_type() == at::kByte && segs.is_contiguous());
+    TORCH_CHECK(segs.numel() >= n_segs * (int64_t)sizeof(gx::GatherSeg));
+    TORCH_CHECK(unit_prefix.is_cuda() && unit_prefix.scalar_type() == at::kLong &&
+                unit_prefix.numel() >= n_segs + 1);
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(dst.data_ptr()) % 16 == 0);
+    void* p[8];
+    to_ptrs(src_base, p);
+    check(gx::launch_gather(p, (int)src_base.size(), reinterpret_cast<const gx::GatherSeg*>(segs.data_ptr()),
+                            (int)n_segs, dst.data_ptr(),
+                            reinterpret_cast<const long long*>(unit_prefix.data_ptr<int64_t>()),
+                            total_units, (int)ctas, stream()),
+          "gather");
+}
+
+void comm_allreduce_scalar(at::IntArrayRef slot_ptrs, at::IntArrayRef flag_ptrs, int64_t rank,
+                           const Tensor& local_val, Tensor out, int64_t epoch, int64_t max_iters,
+                           const c10::optional<Tensor>& status) {
+    c10::cuda::CUDAGuard guard(out.device());
+    TORCH_CHECK(local_val.is_cuda() && local_val.scalar_type() == at::kFloat);
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kFloat);
+    void* s[8];
+    void* f[8];
+    to_ptrs(slot_ptrs, s);
+    to_ptrs(flag_ptrs, f);
+    int* st = (status.has_value() && status->defined()) ? status->data_ptr<int>() : nullptr;
+    check(gx::launch_allreduce_scalar(s, f, (int)slot_ptrs.size(), (int)rank, local_val.data_ptr<float>(),
+                                      out.data_ptr<float>(), (unsigned)epoch, max_iters, st, stream()),
+          "allreduce_scalar");
 }
 
 // ---------------------------------------------------------------------------
@@ -240,12 +300,18 @@ TORCH_LIBRARY(gefenx, m) {
           "Tensor lut, Tensor? gscale, Tensor? status, int dtype, int sr_seed, bool stochastic) -> ()");
     m.def("factored_update(Tensor descs, Tensor tile_start, int n_tensors, int total_tiles, Tensor codebook, "
           "Tensor lut, Tensor? gscale, Tensor? status, int dtype, int sr_seed, bool stochastic, "
-          "int wait_iters, int phases) -> ()");
+          "int wait_iters, int phases, int epoch) -> ()");
     m.def("reduce_sources(Tensor? out, int[] src_ptrs, int numel, float scale, Tensor? partials, "
           "int dtype, int device_index) -> ()", &reduce_sources);
     m.def("clip_coef(Tensor partials, float max_norm, Tensor(a!) coef) -> ()");
     m.def("histogram(Tensor flat, int period, Tensor(a!) counts) -> ()");
     m.def("period_errors(Tensor flat, Tensor divisors, bool input_is_squared) -> Tensor");
+    m.def("comm_signal(int[] flag_ptrs, int slot, int value, int device_index) -> ()", &comm_signal);
+    m.def("comm_wait(Tensor flags, int n, int value, int max_iters, Tensor? status) -> ()");
+    m.def("comm_gather(int[] src_base, Tensor segs, int n_segs, Tensor(a!) dst, Tensor unit_prefix, "
+          "int total_units, int ctas) -> ()");
+    m.def("comm_allreduce_scalar(int[] slot_ptrs, int[] flag_ptrs, int rank, Tensor local_val, "
+          "Tensor(a!) out, int epoch, int max_iters, Tensor? status) -> ()");
     m.def("rmsnorm_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!) rstd, float eps) -> ()");
     m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor(a!) dx, Tensor(b!) dw_partial) -> ()");
     m.def("rope(Tensor(a!) x, Tensor cos, Tensor sin, int seq_len, int n_heads, int head_dim, "
@@ -262,6 +328,9 @@ TORCH_LIBRARY_IMPL(gefenx, CUDA, m) {
     m.impl("clip_coef", &clip_coef);
     m.impl("histogram", &histogram);
     m.impl("period_errors", &period_errors);
+    m.impl("comm_wait", &comm_wait);
+    m.impl("comm_gather", &comm_gather);
+    m.impl("comm_allreduce_scalar", &comm_allreduce_scalar);
     m.impl("rmsnorm_fwd", &rmsnorm_fwd);
     m.impl("rmsnorm_bwd", &rmsnorm_bwd);
     m.impl("rope", &rope);

@@ -1,0 +1,134 @@
+// Peer-memory communication primitives over NVLink / NVSwitch.
+//
+// Every rank maps every peer's symmetric arena; these kernels move data with
+// plain peer loads / stores and synchronise with release/acquire flags that
+// live in the arenas.  Every wait is bounded: when the iteration budget runs out
+// the kernel writes kWaitTimeout into the status word and returns, so a missing
+// peer surfaces as a host-side error instead of a hung GPU.
+//
+// The reference has no custom collective; it relies on torch FSDP2's NCCL
+// all-gather / reduce-scatter (reference SURVEY of collectives:
+// src/gefen/gefen.py:3496-3499, src/gefen/gefen_muon.py:1849-1896).
+#include "comm.h"
+#include "common.cuh"
+
+namespace gx {
+namespace {
+
+struct PtrList { void* p[kMaxSrc]; };
+
+// Publish `value` into slot `slot` of every peer's flag array (own included).
+__global__ void signal_kernel(PtrList flags, int world, int slot, uint32_t value) {
+    __threadfence_system();
+    if (threadIdx.x < world)
+        st_release_sys(reinterpret_cast<uint32_t*>(flags.p[threadIdx.x]) + slot, value);
+}
+
+// Wait until flags[0..n) >= value (bounded).
+__global__ void wait_kernel(const uint32_t* flags, int n, uint32_t value, long long max_iters, int* status) {
+    if (threadIdx.x < n) {
+        if (!wait_flag_ge(flags + threadIdx.x, value, max_iters)) {
+            if (status) atomicExch(status, (int)kWaitTimeout);
+        }
+    }
+}
+
+// Segment copy: dst[seg.dst_off ...] = src_base[seg.src_rank][seg.src_off ...], 16-byte units.
+__global__ void __launch_bounds__(256) gather_kernel(PtrList src_base, const GatherSeg* __restrict__ segs,
+                                                     int n_segs, char* __restrict__ dst,
+                                                     const long long* __restrict__ unit_prefix) {
+    // unit_prefix[i] = number of 16-byte units in segments [0, i)
+    const long long total = unit_prefix[n_segs];
+    int seg = 0;
+    for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < total;
+         u += (long long)gridDim.x * blockDim.x) {
+        // binary search of the segment holding unit u
+        int lo = 0, hi = n_segs;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (unit_prefix[mid] <= u) lo = mid; else hi = mid;
+        }
+        seg = lo;
+        const GatherSeg s = segs[seg];
+        const long long k = u - unit_prefix[seg];
+        const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(src_base.p[s.src_rank]) + s.src_off) + k;
+        uint4* dp = reinterpret_cast<uint4*>(dst + s.dst_off) + k;
+        *dp = *sp;
+    }
+}
+
+// out[0] = sum over ranks of slot[rank][epoch & 1] after everybody has published;
+// each rank first stores its own value into its slot (two slots alternate so that a
+// fast rank's next reduction cannot overwrite a value a slow rank still has to read).
+__global__ void allreduce_scalar_kernel(PtrList slots, PtrList flags, int world, int rank,
+                                        const float* __restrict__ local_val, float* __restrict__ out,
+                                        uint32_t epoch, long long max_iters, int* status) {
+    __shared__ int ok;
+    if (threadIdx.x == 0) {
+        ok = 1;
+        reinterpret_cast<float*>(slots.p[rank])[epoch & 1u] = local_val[0];
+        __threadfence_system();
+    }
+    __syncthreads();
+    if (threadIdx.x < world)
+        st_release_sys(reinterpret_cast<uint32_t*>(flags.p[threadIdx.x]) + rank, epoch);
+    if (threadIdx.x < world) {
+        if (!wait_flag_ge(reinterpret_cast<const uint32_t*>(flags.p[rank]) + threadIdx.x, epoch, max_iters)) {
+            ok = 0;
+            if (status) atomicExch(status, (int)kWaitTimeout);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        if (ok) {
+            for (int r = 0; r < world; ++r) t += reinterpret_cast<const volatile float*>(slots.p[r])[epoch & 1u];
+        } else {
+            t = local_val[0];
+        }
+        out[0] = t;
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_signal(void* const* flag_ptrs, int world, int slot, unsigned value, cudaStream_t st) {
+    if (world < 1 || world > kMaxSrc) return cudaErrorInvalidValue;
+    PtrList l{};
+    for (int i = 0; i < world; ++i) l.p[i] = flag_ptrs[i];
+    signal_kernel<<<1, 32, 0, st>>>(l, world, slot, value);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_wait(const unsigned* flags, int n, unsigned value, long long max_iters, int* status,
+                        cudaStream_t st) {
+    if (n < 1 || n > 32) return cudaErrorInvalidValue;
+    wait_kernel<<<1, 32, 0, st>>>(flags, n, value, max_iters, status);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gather(void* const* src_base, int world, const GatherSeg* segs_dev, int n_segs,
+                          void* dst, const long long* unit_prefix_dev, long long total_units, int ctas,
+                          cudaStream_t st) {
+    if (world < 1 || world > kMaxSrc) return cudaErrorInvalidValue;
+    if (n_segs <= 0 || total_units <= 0) return cudaSuccess;
+    PtrList l{};
+    for (int i = 0; i < world; ++i) l.p[i] = src_base[i];
+    long long want = (total_units + 255) / 256;
+    int grid = (int)(want < ctas ? want : ctas);
+    if (grid < 1) grid = 1;
+    gather_kernel<<<grid, 256, 0, st>>>(l, segs_dev, n_segs, reinterpret_cast<char*>(dst), unit_prefix_dev);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_allreduce_scalar(void* const* slot_ptrs, void* const* flag_ptrs, int world, int rank,
+                                    const float* local_val, float* out, unsigned epoch,
+                                    long long max_iters, int* status, cudaStream_t st) {
+    if (world < 1 || world > kMaxSrc) return cudaErrorInvalidValue;
+    PtrList s{}, f{};
+    for (int i = 0; i < world; ++i) { s.p[i] = slot_ptrs[i]; f.p[i] = flag_ptrs[i]; }
+    allreduce_scalar_kernel<<<1, 32, 0, st>>>(s, f, world, rank, local_val, out, epoch, max_iters, status);
+    return cudaGetLastError();
+}
+
+}  // namespace gx

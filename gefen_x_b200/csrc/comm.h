@@ -1,0 +1,28 @@
+// Host-visible declarations of the peer-memory communication kernels (comm.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace gx {
+
+struct GatherSeg {
+    long long src_off;   // byte offset inside the source rank's arena
+    long long dst_off;   // byte offset inside the local destination buffer
+    int src_rank;
+    int pad;
+};
+
+// flag_ptrs[r]: base of rank r's flag array; writes `value` to element `slot` on every rank.
+cudaError_t launch_signal(void* const* flag_ptrs, int world, int slot, unsigned value, cudaStream_t st);
+// bounded wait until flags[0..n) >= value
+cudaError_t launch_wait(const unsigned* flags, int n, unsigned value, long long max_iters, int* status,
+                        cudaStream_t st);
+// copy segments (16-byte units) from the ranks' arenas into dst
+cudaError_t launch_gather(void* const* src_base, int world, const GatherSeg* segs_dev, int n_segs,
+                          void* dst, const long long* unit_prefix_dev, long long total_units, int ctas,
+                          cudaStream_t st);
+// out = sum_r value_r ; slot_ptrs[r] / flag_ptrs[r] are rank r's slot and flag array
+cudaError_t launch_allreduce_scalar(void* const* slot_ptrs, void* const* flag_ptrs, int world, int rank,
+                                    const float* local_val, float* out, unsigned epoch,
+                                    long long max_iters, int* status, cudaStream_t st);
+
+}  // namespace gx

@@ -379,17 +379,18 @@ __global__ void __launch_bounds__(kEmaThreads) factored_ema_kernel(LaunchCommon 
     }
     float sum_v = cta_sum_1024(part, red);
     bool exchanged = false;
+    const long long xo = (long long)(c.epoch & 1u) * (d.cols + 1);  // slot parity of this step
     if (d.world > 1) {
         // publish this shard's column partials and sum(v_row), then wait for every peer
-        for (int j = threadIdx.x; j < d.cols; j += kEmaThreads) d.xchg_local[j] = d.col_sq[j];
-        if (threadIdx.x == 0) d.xchg_local[d.cols] = sum_v;
+        for (int j = threadIdx.x; j < d.cols; j += kEmaThreads) d.xchg_local[xo + j] = d.col_sq[j];
+        if (threadIdx.x == 0) d.xchg_local[xo + d.cols] = sum_v;
         __threadfence_system();
         __syncthreads();
-        if (threadIdx.x < d.world) st_release_sys(d.flag_peer[threadIdx.x] + d.rank, d.epoch);
+        if (threadIdx.x < d.world) st_release_sys(d.flag_peer[threadIdx.x] + d.rank, c.epoch);
         if (threadIdx.x == 0) ok_s = 1;
         __syncthreads();
         if (threadIdx.x < d.world) {
-            if (!wait_flag_ge(d.flag_local + threadIdx.x, d.epoch, c.wait_iters)) {
+            if (!wait_flag_ge(d.flag_local + threadIdx.x, c.epoch, c.wait_iters)) {
                 ok_s = 0;
                 if (c.status) atomicExch(c.status, (int)kWaitTimeout);
             }
@@ -398,7 +399,7 @@ __global__ void __launch_bounds__(kEmaThreads) factored_ema_kernel(LaunchCommon 
         exchanged = ok_s != 0;
         if (exchanged) {
             float t = 0.f;
-            for (int r = 0; r < d.world; ++r) t += d.xchg_peer[r][d.cols];
+            for (int r = 0; r < d.world; ++r) t += d.xchg_peer[r][xo + d.cols];
             sum_v = t;
         }
     }
@@ -410,7 +411,7 @@ __global__ void __launch_bounds__(kEmaThreads) factored_ema_kernel(LaunchCommon 
         float cs;
         if (exchanged) {
             cs = 0.f;
-            for (int r = 0; r < d.world; ++r) cs += d.xchg_peer[r][j];
+            for (int r = 0; r < d.world; ++r) cs += d.xchg_peer[r][xo + j];
         } else {
             cs = d.col_sq[j];
         }

@@ -30,7 +30,7 @@ struct alignas(16) TensorDesc {
     float* cfac;                      // scratch [cols]
     const float* scal;                // device scalars [lr, s2, 1/bc1, 1-lr*wd]
     // cross-shard exchange of the factored statistics (Shard(0) row shards)
-    float* xchg_local;                // this rank's slot [cols + 1] in symmetric memory
+    float* xchg_local;                // this rank's two slots [2][cols + 1] in symmetric memory (epoch parity)
     const float* xchg_peer[kDescMaxSrc];  // every rank's slot (own included), rank order
     uint32_t* flag_local;             // [world] arrival flags in this rank's memory
     uint32_t* flag_peer[kDescMaxSrc]; // the same array on every rank
@@ -47,7 +47,7 @@ struct alignas(16) TensorDesc {
     int mode;                         // block path: 0 thread/block, 1 warp/block, 2 CTA/block
     int vec;                          // 1: 8-wide vector path allowed, 0: scalar path
     int world, rank;                  // exchange participants (world <= 1: no exchange)
-    uint32_t epoch;                   // value the exchange flags must reach this step
+    uint32_t reserved0;
     float beta1, omb1, beta2, omb2, eps, src_scale;
 };
 
@@ -63,6 +63,7 @@ struct LaunchCommon {
     unsigned long long sr_seed;
     int stochastic;
     long long wait_iters;             // bound of every peer wait
+    uint32_t epoch;                   // value the exchange flags must reach in this launch
 };
 
 // All launchers return the cudaError_t of the launch.

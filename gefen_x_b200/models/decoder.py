@@ -212,10 +212,16 @@ def layer_backward(cfg: ModelConfig, w: Dict[str, torch.Tensor], gw: Dict[str, t
 
 
 class _LayerFn(torch.autograd.Function):
-    """One decoder layer as a single autograd node (manual backward)."""
+    """One decoder layer as a single autograd node (manual backward).
+
+    The layer's Parameters are passed as inputs so that autograd routes their
+    gradients; they all alias ``flat`` (the layer's packed weight buffer), which
+    is what the kernels read.  The gradients returned are row-slice views of one
+    freshly written flat gradient buffer.
+    """
 
     @staticmethod
-    def forward(ctx, x, flat, cfg, cos, sin, grad_flat_holder):
+    def forward(ctx, x, flat, cfg, cos, sin, *params):
         w = layer_views(cfg, flat)
         y, saved = layer_forward(cfg, w, x, cos, sin, save=True)
         ctx.cfg, ctx.saved, ctx.cos, ctx.sin = cfg, saved, cos, sin
@@ -231,7 +237,8 @@ class _LayerFn(torch.autograd.Function):
         gw = layer_views(cfg, gflat)
         dx = layer_backward(cfg, w, gw, ctx.saved, dy.contiguous(), ctx.cos, ctx.sin)
         ctx.saved = None
-        return dx, gflat, None, None, None, None
+        grads = tuple(gw[name] for name in layer_param_specs(cfg))
+        return (dx, None, None, None, None) + grads
 
 
 # --------------------------------------------------------------------------
@@ -276,6 +283,10 @@ class DecoderLM(nn.Module):
     ``forward(tokens, targets)`` returns the mean next-token cross-entropy when
     ``targets`` is given, else the logits.  ``impl="auto"`` uses the kernel path
     for CUDA half-precision weights and the plain torch path otherwise.
+
+    Every matrix is its own ``nn.Parameter`` (``model.layers.0.self_attn.q_proj.weight``
+    ...), and all Parameters of a layer are row-slice views of one packed buffer
+    so that the fused QKV / gate-up GEMMs read them without a copy.
     """
 
     def __init__(self, cfg: ModelConfig, device=None, dtype=torch.float32, impl: str = "auto",
@@ -293,32 +304,66 @@ class DecoderLM(nn.Module):
             t.normal_(0.0, cfg.init_std, generator=gen)
             return t
 
-        self.embed_tokens = nn.Embedding(V, H, device=device, dtype=dtype)
+        self.model = nn.Module()
+        self.model.embed_tokens = nn.Embedding(V, H, device=device, dtype=dtype)
         with torch.no_grad():
-            self.embed_tokens.weight.copy_(init((V, H)))
-        self._layer_flat: List[torch.Tensor] = []
-        self.layer_params = nn.ModuleList()
+            self.model.embed_tokens.weight.copy_(init((V, H)))
+        self._flats: List[torch.Tensor] = []
+        self.model.layers = nn.ModuleList()
         n = layer_numel(cfg)
         for _ in range(cfg.n_layers):
             flat = torch.empty(n, device=device, dtype=dtype)
             views = layer_views(cfg, flat)
-            holder = nn.ParameterDict()
             with torch.no_grad():
                 for name, (_, shape) in layer_param_specs(cfg).items():
                     if name.endswith("norm.weight") or "layernorm" in name:
                         views[name].fill_(1.0)
                     else:
                         views[name].copy_(init(shape))
-            # one Parameter per layer buffer; HF-style names are exposed through
-            # named_parameters() below as row-slice views that share its storage.
-            holder["flat"] = nn.Parameter(flat)
-            self.layer_params.append(holder)
-        self.norm_weight = nn.Parameter(torch.ones(H, device=device, dtype=dtype))
+            self._flats.append(flat)
+            self.model.layers.append(self._make_layer(views))
+        self.model.norm = nn.Module()
+        self.model.norm.weight = nn.Parameter(torch.ones(H, device=device, dtype=dtype))
         if cfg.tie_embeddings:
-            self.lm_head_weight = None
+            self.lm_head = None
         else:
-            self.lm_head_weight = nn.Parameter(init((V, H)).to(device=device, dtype=dtype))
+            self.lm_head = nn.Module()
+            self.lm_head.weight = nn.Parameter(init((V, H)).to(device=device, dtype=dtype))
         self._rope_cache = {}
+
+    def _make_layer(self, views: Dict[str, torch.Tensor]) -> nn.Module:
+        layer = nn.Module()
+        for name in layer_param_specs(self.cfg):
+            parts = name.split(".")
+            mod = layer
+            for part in parts[:-1]:
+                if not hasattr(mod, part):
+                    setattr(mod, part, nn.Module())
+                mod = getattr(mod, part)
+            setattr(mod, parts[-1], nn.Parameter(views[name]))
+        return layer
+
+    def _layer_param(self, layer: nn.Module, name: str) -> nn.Parameter:
+        obj = layer
+        for part in name.split("."):
+            obj = getattr(obj, part)
+        return obj
+
+    def _apply(self, fn, *args, **kwargs):
+        """Device / dtype moves re-pack every layer so that its Parameters alias one buffer again."""
+        out = super()._apply(fn, *args, **kwargs)
+        with torch.no_grad():
+            for i, layer in enumerate(self.model.layers):
+                first = self._layer_param(layer, next(iter(layer_param_specs(self.cfg))))
+                flat = torch.empty(layer_numel(self.cfg), device=first.device, dtype=first.dtype)
+                views = layer_views(self.cfg, flat)
+                for name in layer_param_specs(self.cfg):
+                    p = self._layer_param(layer, name)
+                    views[name].copy_(p.data)
+                    p.data = views[name]
+                self._flats[i] = flat
+        self._rope_cache = {}
+        return out
 
     # -- rope tables ------------------------------------------------------
     def rope(self, seq_len: int, device):
@@ -328,7 +373,7 @@ class DecoderLM(nn.Module):
         return self._rope_cache[key]
 
     def head_weight(self) -> torch.Tensor:
-        return self.embed_tokens.weight if self.lm_head_weight is None else self.lm_head_weight
+        return self.model.embed_tokens.weight if self.lm_head is None else self.lm_head.weight
 
     def _kernel_path(self, x: torch.Tensor) -> bool:
         if self.impl == "torch":
@@ -340,62 +385,20 @@ class DecoderLM(nn.Module):
     def forward(self, tokens: torch.Tensor, targets: Optional[torch.Tensor] = None):
         cfg = self.cfg
         B, S = tokens.shape
-        x = self.embed_tokens(tokens)
+        x = self.model.embed_tokens(tokens)
         cos, sin = self.rope(S, x.device)
         kernel = self._kernel_path(x)
-        for holder in self.layer_params:
-            flat = holder["flat"]
+        names = list(layer_param_specs(cfg))
+        for flat, layer in zip(self._flats, self.model.layers):
+            params = [self._layer_param(layer, n) for n in names]
             if kernel:
-                x = _LayerFn.apply(x, flat, cfg, cos, sin, None)
+                x = _LayerFn.apply(x, flat, cfg, cos, sin, *params)
             else:
-                x = layer_forward_torch(cfg, layer_views(cfg, flat), x, cos, sin)
+                x = layer_forward_torch(cfg, dict(zip(names, params)), x, cos, sin)
         xf = x.float()
         hN = (xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + cfg.rms_eps)
-              * self.norm_weight.float()).to(x.dtype)
+              * self.model.norm.weight.float()).to(x.dtype)
         logits = F.linear(hN, self.head_weight())
         if targets is None:
             return logits
         return F.cross_entropy(logits.float().view(B * S, -1), targets.reshape(-1))
-
-    # -- HF-style named views for optimizers -------------------------------
-    def named_matrices(self):
-        """``(hf_name, tensor_view)`` for every logical parameter (views into the flat buffers)."""
-        out = [("model.embed_tokens.weight", self.embed_tokens.weight)]
-        for i, holder in enumerate(self.layer_params):
-            views = layer_views(self.cfg, holder["flat"])
-            for name in layer_param_specs(self.cfg):
-                out.append(("model.layers.{}.{}".format(i, name), views[name]))
-        out.append(("model.norm.weight", self.norm_weight))
-        if self.lm_head_weight is not None:
-            out.append(("lm_head.weight", self.lm_head_weight))
-        return out
-
-
-def split_flat_parameters(model: DecoderLM):
-    """Re-register a model's logical matrices as individual leaf Parameters.
-
-    Optimizers need one Parameter per logical matrix (own period, own row/column
-    statistics).  Each returned Parameter aliases a row slice of its layer's flat
-    buffer, and its ``.grad`` is bound to the matching slice of the flat
-    gradient by :func:`bind_flat_grads` after ``backward``.
-    """
-    named = []
-    for name, view in model.named_matrices():
-        if isinstance(view, nn.Parameter):
-            named.append((name, view))
-        else:
-            p = nn.Parameter(view.detach(), requires_grad=True)
-            named.append((name, p))
-    return named
-
-
-def bind_flat_grads(model: DecoderLM, named) -> None:
-    """Point every split Parameter's ``.grad`` at its slice of the flat layer gradient."""
-    by_name = dict(named)
-    for i, holder in enumerate(model.layer_params):
-        g = holder["flat"].grad
-        if g is None:
-            continue
-        gv = layer_views(model.cfg, g)
-        for name in layer_param_specs(model.cfg):
-            by_name["model.layers.{}.{}".format(i, name)].grad = gv[name]

@@ -60,7 +60,7 @@ class TensorDesc(ctypes.Structure):
         ("vec", ctypes.c_int),
         ("world", ctypes.c_int),
         ("rank", ctypes.c_int),
-        ("epoch", ctypes.c_uint32),
+        ("reserved0", ctypes.c_uint32),
         ("beta1", ctypes.c_float),
         ("omb1", ctypes.c_float),
         ("beta2", ctypes.c_float),
@@ -119,6 +119,16 @@ class PeerGrad:
         return out
 
 
+class LocalGrad:
+    """A gradient that already is a local tensor, handed to the optimizer out of band."""
+
+    def __init__(self, tensor: torch.Tensor):
+        self.tensor = tensor
+
+    def materialize(self) -> torch.Tensor:
+        return self.tensor
+
+
 @dataclass
 class ShardExchange:
     """Where a ``Shard(0)`` factored tensor publishes / reads its column statistics."""
@@ -130,7 +140,6 @@ class ShardExchange:
     xchg_peer: Sequence[int] = ()
     flag_local: int = 0
     flag_peer: Sequence[int] = ()
-    epoch: int = 0
     # host-side reductions for the decomposed path
     reduce_cols: Any = None
     reduce_scalar: Any = None
@@ -187,8 +196,6 @@ class Plan:
                 sizes.append((0, 0, 0, 0, 0))
         total = sum(sum(s) for s in sizes)
         self.scratch = torch.zeros(max(total, 1), dtype=torch.float32, device=device)
-        self.scal_host = torch.zeros(self.n, 4, dtype=torch.float32).pin_memory() \
-            if torch.cuda.is_available() else torch.zeros(self.n, 4, dtype=torch.float32)
         self.scal_dev = torch.zeros(self.n, 4, dtype=torch.float32, device=device)
         buf = (ctypes.c_ubyte * (stride * self.n))()
         tile_start = [0]
@@ -258,14 +265,14 @@ class Plan:
                 tiles = d.n_col_tiles * n_row_tiles
                 sh = it.shard
                 if sh is not None and sh.world > 1:
-                    d.world, d.rank, d.epoch = sh.world, sh.rank, sh.epoch
+                    d.world, d.rank = sh.world, sh.rank
                     d.xchg_local = sh.xchg_local
                     d.flag_local = sh.flag_local
                     for r in range(sh.world):
                         d.xchg_peer[r] = sh.xchg_peer[r]
                         d.flag_peer[r] = sh.flag_peer[r]
                 else:
-                    d.world, d.rank, d.epoch = 1, 0, 0
+                    d.world, d.rank = 1, 0
             else:
                 d.v0 = st["vmean"].data_ptr()
                 d.rows, d.cols = int(d.nb), it.period
@@ -299,25 +306,25 @@ class Plan:
             gp = tuple(g.ptrs) if isinstance(g, PeerGrad) else (g.data_ptr(),)
             st = it.state
             sig.append((it.p.data_ptr(), gp, st["m_codebook"].data_ptr(), st["m_magnitude"].data_ptr(),
-                        it.period, it.scal_ptr, tuple(it.p.shape), it.beta1, it.beta2, it.eps,
-                        (it.shard.epoch if it.shard is not None else 0)))
+                        (st.get("v_row") if "v_row" in st else st["vmean"]).data_ptr(),
+                        it.period, it.scal_ptr, tuple(it.p.shape), it.beta1, it.beta2, it.eps))
         return tuple(sig)
 
     def run(self, items: List[Item], codebook: torch.Tensor, lut: torch.Tensor, *,
             gscale: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
             sr_seed: Optional[int] = None, wait_iters: int = DEFAULT_WAIT_ITERS,
-            phases: int = 7) -> None:
+            phases: int = 7, epoch: int = 0) -> None:
         if self.uses_host_scalars and (phases & 1 or self.kind == "block"):
-            h = self.scal_host
-            for i, it in enumerate(items):
-                h[i, 0], h[i, 1], h[i, 2], h[i, 3] = it.scalars
+            # A fresh pageable tensor per step: the runtime stages it before the call
+            # returns, so the host may run ahead of the device without racing on it.
+            h = torch.tensor([it.scalars for it in items], dtype=torch.float32)
             self.scal_dev.copy_(h, non_blocking=True)
         code = DTYPE_CODE[self.dtype]
         seed = 0 if sr_seed is None else int(sr_seed)
         if self.kind == "factored":
             ops().factored_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, lut,
                                   gscale, status, code, seed, sr_seed is not None, int(wait_iters),
-                                  int(phases))
+                                  int(phases), int(epoch) & 0x7FFFFFFF)
         else:
             ops().block_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, lut,
                                gscale, status, code, seed, sr_seed is not None)

@@ -268,6 +268,7 @@ class Gefen(torch.optim.Optimizer):
         self._shard_info = None
         self._histogram_reducer = None
         self._external_grad_scale: Optional[torch.Tensor] = None
+        self._exchange_epoch = 0
         self._plan_cache = None
         self._fused_items: Dict[Any, list] = {}
         self._fused_copyback: list = []
@@ -793,7 +794,9 @@ class Gefen(torch.optim.Optimizer):
     def _step_param(self, group, name: str, p: torch.Tensor) -> None:
         src = self._grad_source(p) if self._grad_source is not None else None
         grad = None
-        if src is None:
+        if src is not None and hasattr(src, "tensor"):
+            grad, src = src.tensor, None
+        elif src is None:
             if p.grad is None:
                 return
             grad = _local(p.grad).detach()
@@ -808,7 +811,8 @@ class Gefen(torch.optim.Optimizer):
             state["step"] += 1
             state[vkey] += 1
         beta1, beta2, eps = group["beta1"], group["beta2"], group["eps"]
-        gscale = self._pending_grad_scale
+        gscale = self._external_grad_scale if self._external_grad_scale is not None \
+            else self._pending_grad_scale
         use_kernel = self._fused_for(p_local)
         shard = self._shard_info(p) if (self._shard_info is not None and factored) else None
 
@@ -887,7 +891,8 @@ class Gefen(torch.optim.Optimizer):
             gscale = self._grad_scale_tensor(dev)
             plan = self._plan_cache.get(kind, items)
             plan.run(items, cb, lut, gscale=gscale, status=self._status_word(dev),
-                     sr_seed=self._kernel_rng_seed() if self._stochastic_round else None)
+                     sr_seed=self._kernel_rng_seed() if self._stochastic_round else None,
+                     epoch=self._exchange_epoch)
         for dst, work in self._fused_copyback:
             dst.copy_(work)
 

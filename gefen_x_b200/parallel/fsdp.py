@@ -1,0 +1,556 @@
+"""Sharded training runtime (ZeRO-3 / FSDP2-style ``Shard(0)``) over peer memory.
+
+One process per GPU.  Every logical parameter is split by rows over the ranks
+(the placement torch FSDP2 uses); a rank stores its row slices, the optimizer
+state for them, and an unsharded bf16 gradient staging buffer per layer group in
+a symmetric arena that every peer maps.  A step is
+
+* forward / backward, layer by layer, on the manual layer functions of
+  ``models.decoder``; the weights of the next layer are pulled from the peers'
+  shards by a copy kernel on a side stream while the current layer computes
+  (all-gather by peer loads, no library collective);
+* gradient reduction fused into the optimizer: this rank's slices of every
+  peer's staging buffer are summed inside the update kernels
+  (``rs_mode="fused"``), or once, overlapped with backward, into a bf16 shard
+  stash together with the sum of squares needed for global-norm clipping
+  (``rs_mode="stash"``, the default when clipping is on);
+* one multi-tensor ``Gefen`` step on the shards, with the column statistics of
+  the factored second moment summed across the shards inside the kernel.
+
+The reference has no runtime of its own: its FSDP2 runs use torch's
+``fully_shard`` (reference ``src/gefen/tools/find_lr.py:467-474``,
+``benchmarks/sharding-sweep/fsdp2_convergence.py:196-201``) and step the local
+shards after backward (``src/gefen/gefen.py:3496-3499``).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..models.decoder import (ModelConfig, layer_backward, layer_forward, layer_numel,
+                              layer_param_specs, layer_views)
+from ..ops import gemm as G
+from ..ops import model as M
+from ..ops import update as U
+from ..ops._ext import DTYPE_CODE, ops
+from .symm import FlagBoard, SymmetricArena
+
+
+@dataclass
+class ParamSpec:
+    name: str
+    shape: Tuple[int, ...]
+    full_off: int            # element offset inside the group's unsharded buffer
+    rows: int
+    cols: int                # elements per row
+    rows_per: int            # ceil(rows / world)
+    shard_off: List[int]     # per rank: element offset inside that rank's shard buffer
+    shard_rows: List[int]    # per rank: rows held
+
+
+class Group:
+    """A set of parameters gathered / reduced together (one decoder layer, or the embeddings)."""
+
+    def __init__(self, name: str, named_shapes: List[Tuple[str, Tuple[int, ...]]], world: int):
+        self.name = name
+        self.specs: List[ParamSpec] = []
+        off = 0
+        shard_cursor = [0] * world
+        for pname, shape in named_shapes:
+            rows = int(shape[0])
+            cols = int(math.prod(shape[1:])) if len(shape) > 1 else 1
+            rows_per = (rows + world - 1) // world
+            s_off, s_rows = [], []
+            for r in range(world):
+                r0 = min(rows, r * rows_per)
+                r1 = min(rows, (r + 1) * rows_per)
+                s_off.append(shard_cursor[r])
+                s_rows.append(r1 - r0)
+                shard_cursor[r] += (r1 - r0) * cols
+            self.specs.append(ParamSpec(pname, tuple(shape), off, rows, cols, rows_per, s_off, s_rows))
+            off += rows * cols
+        self.full_numel = off
+        self.shard_numel = shard_cursor          # per rank
+        self.max_shard = max(shard_cursor)
+        # tensors, filled by the trainer
+        self.shard_w: Optional[torch.Tensor] = None
+        self.shard_w_off = 0
+        self.full_w: Optional[torch.Tensor] = None
+        self.full_g: Optional[torch.Tensor] = None
+        self.full_g_off = 0
+        self.stash_g: Optional[torch.Tensor] = None
+        self.gather_tables = None
+
+    def local_slice(self, spec: ParamSpec, rank: int) -> Tuple[int, int]:
+        """Element range of ``rank``'s rows of ``spec`` inside the unsharded buffer."""
+        r0 = min(spec.rows, rank * spec.rows_per)
+        return spec.full_off + r0 * spec.cols, spec.shard_rows[rank] * spec.cols
+
+
+class _GatherSeg(ctypes.Structure):
+    _fields_ = [("src_off", ctypes.c_longlong), ("dst_off", ctypes.c_longlong),
+                ("src_rank", ctypes.c_int), ("pad", ctypes.c_int)]
+
+
+def embed_group_shapes(cfg: ModelConfig) -> List[Tuple[str, Tuple[int, ...]]]:
+    shapes = [("model.embed_tokens.weight", (cfg.vocab_size, cfg.hidden)),
+              ("model.norm.weight", (cfg.hidden,))]
+    if not cfg.tie_embeddings:
+        shapes.append(("lm_head.weight", (cfg.vocab_size, cfg.hidden)))
+    return shapes
+
+
+class ShardedTrainer:
+    """Train a :class:`~gefen_x_b200.models.decoder.ModelConfig` decoder on ``world`` GPUs.
+
+    ``step(tokens, targets)`` takes host (ideally pinned) or device int64 tensors of
+    shape ``[B, S]`` holding this rank's micro-batch, runs forward, backward,
+    gradient reduction, clipping and the optimizer step, and returns the mean loss
+    of the local batch as a 0-dim device tensor.
+    """
+
+    def __init__(self, cfg: ModelConfig, *, device=None, dtype=torch.bfloat16, world: int = 1,
+                 rank: int = 0, group=None, lr: float = 6e-6, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.0, clip_grad_norm: Optional[float] = 1.0,
+                 factored_v_2d: bool = True, rs_mode: Optional[str] = None, seed: int = 0,
+                 optimizer: str = "gefen", global_codebook: bool = True, gather_ctas: int = 32,
+                 wait_iters: int = 8_000_000, opt_kwargs: Optional[dict] = None):
+        self.cfg = cfg
+        self.world, self.rank = int(world), int(rank)
+        self.device = torch.device(device if device is not None else
+                                   ("cuda" if torch.cuda.is_available() else "cpu"))
+        self.dtype = dtype
+        self.clip = clip_grad_norm
+        self.rs_mode = rs_mode or ("stash" if (clip_grad_norm or self.world == 1) else "fused")
+        if self.rs_mode not in ("stash", "fused"):
+            raise ValueError("rs_mode must be 'stash' or 'fused'")
+        self.gather_ctas = gather_ctas
+        self.step_count = 0
+        self.process_group = group
+        cuda = self.device.type == "cuda"
+        esz = torch.empty((), dtype=dtype).element_size()
+        if world > U.MAX_SRC:
+            raise ValueError("at most {} ranks per node".format(U.MAX_SRC))
+
+        # ---- layout ------------------------------------------------------
+        layer_shapes = [(n, s) for n, (_, s) in layer_param_specs(cfg).items()]
+        self.groups: List[Group] = []
+        for i in range(cfg.n_layers):
+            self.groups.append(Group("layers.{}".format(i),
+                                     [("model.layers.{}.{}".format(i, n), s) for n, s in layer_shapes],
+                                     world))
+        self.embed_group = Group("embed", embed_group_shapes(cfg), world)
+        self.all_groups = self.groups + [self.embed_group]
+        for g in self.all_groups:
+            for sp in g.specs:
+                for r in range(world):
+                    if (sp.shard_rows[r] * sp.cols * esz) % 16 and world > 1:
+                        raise ValueError(
+                            "shard of {} on rank {} is not a multiple of 16 bytes; pick a world "
+                            "size that divides its rows".format(sp.name, r))
+
+        # ---- arena ---------------------------------------------------------
+        n2d = sum(1 for g in self.all_groups for sp in g.specs if len(sp.shape) == 2)
+        xchg_floats = sum(2 * (sp.cols + 1) for g in self.all_groups for sp in g.specs
+                          if len(sp.shape) == 2)
+        n_flag_slots = len(self.all_groups) + 4 + n2d
+        arena_bytes = 0
+        if world > 1:
+            arena_bytes += sum((g.max_shard + g.full_numel) * esz + 1024 for g in self.all_groups)
+            arena_bytes += xchg_floats * 4 + n_flag_slots * world * 4 + (1 << 16)
+        else:
+            arena_bytes = 1 << 12
+        self.arena = SymmetricArena(arena_bytes, self.device, world, rank, group)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.flags = FlagBoard(self.arena, n_flag_slots, self.status, wait_iters)
+        self.wait_iters = int(wait_iters)
+        # flag slots: [0, n_groups) gradients of group ready; then named slots
+        self.SLOT_PARAMS = len(self.all_groups)
+        self.SLOT_NORM = len(self.all_groups) + 1
+        self._next_param_slot = len(self.all_groups) + 4
+
+        # ---- buffers -------------------------------------------------------
+        for g in self.all_groups:
+            if world > 1:
+                g.shard_w, g.shard_w_off = self.arena.alloc(g.max_shard, dtype)
+                g.full_g, g.full_g_off = self.arena.alloc(g.full_numel, dtype)
+                g.stash_g = torch.zeros(g.shard_numel[rank], dtype=dtype, device=self.device) \
+                    if self.rs_mode == "stash" else None
+            else:
+                g.shard_w = torch.empty(g.full_numel, dtype=dtype, device=self.device)
+                g.full_w = g.shard_w
+                g.full_g = torch.zeros(g.full_numel, dtype=dtype, device=self.device)
+        if world > 1:
+            n_ring = min(3, cfg.n_layers)
+            self.ring = [torch.empty(self.groups[0].full_numel, dtype=dtype, device=self.device)
+                         for _ in range(n_ring)]
+            self.ring_owner = [-1] * n_ring
+            self.embed_group.full_w = torch.empty(self.embed_group.full_numel, dtype=dtype,
+                                                  device=self.device)
+            self.norm_slot, self.norm_slot_off = self.arena.alloc(2, torch.float32)
+        self._init_weights(seed)
+        if world > 1:
+            for g in self.all_groups:
+                self._build_gather_tables(g)
+
+        # ---- streams -------------------------------------------------------
+        if cuda:
+            self.comm_stream = torch.cuda.Stream(device=self.device)
+            self.reduce_stream = torch.cuda.Stream(device=self.device)
+        else:
+            self.comm_stream = self.reduce_stream = None
+        self._layer_done: Dict[int, torch.cuda.Event] = {}
+        self._gather_done: Dict[int, torch.cuda.Event] = {}
+        self.norm_partials = torch.zeros(2048, dtype=torch.float32, device=self.device)
+        self.norm_local = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.norm_total = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.clip_coef = torch.ones(2, dtype=torch.float32, device=self.device)
+        self._rope = None
+        self._tok_dev = None
+
+        # ---- optimizer -----------------------------------------------------
+        self._build_optimizer(optimizer, lr, betas, eps, weight_decay, factored_v_2d,
+                              global_codebook, opt_kwargs or {})
+        if world > 1:
+            self.arena.barrier()
+
+    # ------------------------------------------------------------------
+    def _init_weights(self, seed: int) -> None:
+        """Same full-model random init on every rank (seeded), each rank keeps its rows."""
+        cfg = self.cfg
+        gen = torch.Generator(device=self.device).manual_seed(int(seed))
+        for gi, g in enumerate(self.all_groups):
+            full = torch.empty(g.full_numel, dtype=torch.float32, device=self.device)
+            for sp in g.specs:
+                seg = full[sp.full_off:sp.full_off + sp.rows * sp.cols]
+                if sp.name.endswith("norm.weight") or "layernorm" in sp.name:
+                    seg.fill_(1.0)
+                else:
+                    seg.normal_(0.0, cfg.init_std, generator=gen)
+            full = full.to(self.dtype)
+            if self.world == 1:
+                g.shard_w.copy_(full)
+            else:
+                for sp in g.specs:
+                    src_off, n = g.local_slice(sp, self.rank)
+                    dst = sp.shard_off[self.rank]
+                    g.shard_w[dst:dst + n].copy_(full[src_off:src_off + n])
+            del full
+
+    def _build_gather_tables(self, g: Group) -> None:
+        esz = torch.empty((), dtype=self.dtype).element_size()
+        segs, prefix = [], [0]
+        for sp in g.specs:
+            for r in range(self.world):
+                n = sp.shard_rows[r] * sp.cols
+                if n == 0:
+                    continue
+                dst_off, _ = g.local_slice(sp, r)
+                segs.append((g.shard_w_off + sp.shard_off[r] * esz, dst_off * esz, r))
+                prefix.append(prefix[-1] + n * esz // 16)
+        arr = (_GatherSeg * len(segs))()
+        for i, (so, do, r) in enumerate(segs):
+            arr[i].src_off, arr[i].dst_off, arr[i].src_rank = so, do, r
+        host = torch.frombuffer(arr, dtype=torch.uint8).clone()
+        g.gather_tables = (host.to(self.device), len(segs),
+                           torch.tensor(prefix, dtype=torch.int64, device=self.device), prefix[-1])
+
+    # ------------------------------------------------------------------
+    # optimizer wiring
+    # ------------------------------------------------------------------
+    def _build_optimizer(self, kind, lr, betas, eps, weight_decay, factored_v_2d, global_codebook,
+                         opt_kwargs) -> None:
+        from ..optim.gefen import Gefen
+
+        named = []
+        self._param_meta: Dict[torch.Tensor, Tuple[Group, ParamSpec]] = {}
+        for g in self.all_groups:
+            for sp in g.specs:
+                rows = sp.shard_rows[self.rank]
+                off = sp.shard_off[self.rank]
+                view = g.shard_w[off:off + rows * sp.cols]
+                view = view.view(rows, *sp.shape[1:]) if len(sp.shape) > 1 else view
+                named.append((sp.name, view))
+                self._param_meta[view] = (g, sp)
+        self.named_shards = named
+        if kind != "gefen":
+            raise ValueError("ShardedTrainer drives the Gefen optimizer; got {!r}".format(kind))
+        fused = self.device.type == "cuda"
+        self.opt = Gefen(named, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
+                         factored_v_2d=factored_v_2d, fused=fused, **opt_kwargs)
+        self.opt._grad_source = self._grad_source
+        self.opt._external_grad_scale = self.clip_coef[0:1] if self.clip else None
+        if self.world > 1:
+            self._exchange: Dict[torch.Tensor, U.ShardExchange] = {}
+            for view, (g, sp) in self._param_meta.items():
+                if len(sp.shape) != 2:
+                    continue
+                slot, slot_off = self.arena.alloc(2 * (sp.cols + 1), torch.float32)
+                flag_slot = self._next_param_slot
+                self._next_param_slot += 1
+                row = self.flags.row_ptrs(flag_slot)
+                self._exchange[view] = U.ShardExchange(
+                    total_rows=sp.rows, world=self.world, rank=self.rank,
+                    xchg_local=slot.data_ptr(), xchg_peer=self.arena.peer_ptrs(slot_off),
+                    flag_local=row[self.rank], flag_peer=row,
+                    reduce_cols=self._host_allreduce, reduce_scalar=self._host_allreduce)
+            self.opt._shard_info = lambda p: self._exchange.get(p)
+            if global_codebook:
+                self.opt._histogram_reducer = self._host_allreduce
+
+    def _host_allreduce(self, t: torch.Tensor) -> torch.Tensor:
+        import torch.distributed as dist
+
+        if self.world == 1:
+            return t
+        dev = t.device
+        backend = str(dist.get_backend(self.process_group)).lower()
+        work = t.to(self.device) if ("nccl" in backend and "gloo" not in backend) else t.cpu()
+        dist.all_reduce(work, group=self.process_group)
+        return work.to(dev)
+
+    def _grad_source(self, p):
+        """Gradient of shard ``p``: a local tensor, or the peers' slices to be summed in-kernel."""
+        meta = self._param_meta.get(p)
+        if meta is None:
+            return None
+        g, sp = meta
+        rows = sp.shard_rows[self.rank]
+        n = rows * sp.cols
+        shape = (rows,) + tuple(sp.shape[1:])
+        if self.world == 1:
+            return _LocalGrad(g.full_g[sp.full_off:sp.full_off + n].view(shape))
+        if self.rs_mode == "stash":
+            off = sp.shard_off[self.rank]
+            return _LocalGrad(g.stash_g[off:off + n].view(shape))
+        esz = p.element_size()
+        src_off, _ = g.local_slice(sp, self.rank)
+        ptrs = self.arena.peer_ptrs(g.full_g_off + src_off * esz)
+        return U.PeerGrad(ptrs=ptrs, shape=shape, dtype=p.dtype, device=self.device,
+                          scale=1.0 / self.world)
+
+    # ------------------------------------------------------------------
+    # parameter gather (all-gather by peer loads)
+    # ------------------------------------------------------------------
+    def _gather_into(self, g: Group, dst: torch.Tensor) -> None:
+        segs, n_segs, prefix, total = g.gather_tables
+        ops().comm_gather(self.arena.base_ptrs, segs, n_segs, dst, prefix, total, self.gather_ctas)
+
+    def _ensure_layer(self, li: int) -> torch.Tensor:
+        """Make layer ``li``'s unsharded weights available; returns the flat buffer.
+
+        The copy runs on the communication stream; the compute stream waits on
+        its event.  A ring slot is reused only after the layer that last
+        occupied it has finished computing.
+        """
+        g = self.groups[li]
+        if self.world == 1:
+            return g.full_w
+        slot = li % len(self.ring)
+        if self.ring_owner[slot] != li:
+            prev = self.ring_owner[slot]
+            with torch.cuda.stream(self.comm_stream):
+                if prev >= 0 and prev in self._layer_done:
+                    self.comm_stream.wait_event(self._layer_done[prev])
+                self._gather_into(g, self.ring[slot])
+                ev = torch.cuda.Event()
+                ev.record(self.comm_stream)
+                self._gather_done[li] = ev
+            self.ring_owner[slot] = li
+        return self.ring[slot]
+
+    def _wait_layer(self, li: int) -> None:
+        if self.world > 1 and li in self._gather_done:
+            torch.cuda.current_stream().wait_event(self._gather_done[li])
+
+    def _mark_layer_done(self, li: int) -> None:
+        if self.world > 1:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            self._layer_done[li] = ev
+
+    # ------------------------------------------------------------------
+    # gradient reduction (reduce-scatter by peer loads) and the clip norm
+    # ------------------------------------------------------------------
+    def _reduce_group(self, gi: int) -> None:
+        g = self.all_groups[gi]
+        t = self.step_count
+        code_dev = self.device
+        if self.world == 1:
+            if self.clip and self.device.type != "cuda":
+                self.norm_partials[0] += g.full_g.float().square().sum()
+            elif self.clip:
+                U.reduce_sources(None, [g.full_g.data_ptr()], g.full_numel, 1.0, self.norm_partials,
+                                 self.dtype, code_dev)
+            return
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        with torch.cuda.stream(self.reduce_stream):
+            self.reduce_stream.wait_event(ev)
+            self.flags.signal(gi, t)
+            self.flags.wait(gi, t)
+            if self.rs_mode == "stash" or self.clip:
+                esz = g.full_g.element_size()
+                for sp in g.specs:
+                    n = sp.shard_rows[self.rank] * sp.cols
+                    if n == 0:
+                        continue
+                    src_off, _ = g.local_slice(sp, self.rank)
+                    ptrs = self.arena.peer_ptrs(g.full_g_off + src_off * esz)
+                    out = None
+                    if self.rs_mode == "stash":
+                        off = sp.shard_off[self.rank]
+                        out = g.stash_g[off:off + n]
+                    U.reduce_sources(out, ptrs, n, 1.0 / self.world,
+                                     self.norm_partials if self.clip else None, self.dtype, code_dev)
+
+    def _finish_norm(self) -> None:
+        """Global gradient norm -> clip coefficient on the device (no host sync)."""
+        if not self.clip:
+            return
+        if self.world == 1 and self.device.type != "cuda":
+            norm = self.norm_partials.sum().sqrt()
+            self.clip_coef[1] = norm
+            self.clip_coef[0] = torch.clamp(float(self.clip) / (norm + 1e-6), max=1.0)
+            return
+        if self.world == 1:
+            U.clip_coef(self.norm_partials, float(self.clip), self.clip_coef)
+            return
+        with torch.cuda.stream(self.reduce_stream):
+            torch.sum(self.norm_partials, dim=0, keepdim=True, out=self.norm_local)
+            ops().comm_allreduce_scalar(self.arena.peer_ptrs(self.norm_slot_off),
+                                        self.flags.row_ptrs(self.SLOT_NORM), self.rank,
+                                        self.norm_local, self.norm_total, self.step_count,
+                                        self.wait_iters, self.status)
+            U.clip_coef(self.norm_total, float(self.clip), self.clip_coef)
+
+    # ------------------------------------------------------------------
+    # one training step
+    # ------------------------------------------------------------------
+    def _to_device(self, t: torch.Tensor) -> torch.Tensor:
+        if t.device == self.device:
+            return t
+        return t.to(self.device, non_blocking=True)
+
+    def _embed_views(self, flat: torch.Tensor) -> Dict[str, torch.Tensor]:
+        out = {}
+        for sp in self.embed_group.specs:
+            out[sp.name] = flat[sp.full_off:sp.full_off + sp.rows * sp.cols].view(sp.shape)
+        return out
+
+    @torch.no_grad()
+    def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        cfg, L = self.cfg, self.cfg.n_layers
+        self.step_count += 1
+        t = self.step_count
+        tok = self._to_device(tokens)
+        tgt = self._to_device(targets)
+        B, S = tok.shape
+        T = B * S
+        if self._rope is None or self._rope[0] != S:
+            self._rope = (S,) + M.rope_tables(S, cfg.head_dim, cfg.rope_theta, self.device)
+        cos, sin = self._rope[1], self._rope[2]
+        multi = self.world > 1
+        eg = self.embed_group
+        if self.clip:
+            if multi:
+                with torch.cuda.stream(self.reduce_stream):
+                    self.norm_partials.zero_()
+            else:
+                self.norm_partials.zero_()
+        if multi:
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_stream(torch.cuda.current_stream())
+                if t > 1:
+                    self.flags.wait(self.SLOT_PARAMS, t - 1)
+                self._gather_into(eg, eg.full_w)
+                ev = torch.cuda.Event()
+                ev.record(self.comm_stream)
+            self._ensure_layer(0)
+            torch.cuda.current_stream().wait_event(ev)
+        ew = self._embed_views(eg.full_w)
+        egrad = self._embed_views(eg.full_g)
+        emb_w = ew["model.embed_tokens.weight"]
+        head_w = emb_w if cfg.tie_embeddings else ew["lm_head.weight"]
+
+        # ---- forward ---------------------------------------------------
+        x = emb_w.index_select(0, tok.reshape(-1)).view(B, S, cfg.hidden)
+        saved: List[Optional[dict]] = []
+        for li in range(L):
+            flat = self._ensure_layer(li)
+            if li + 1 < L:
+                self._ensure_layer(li + 1)
+            self._wait_layer(li)
+            x, sv = layer_forward(cfg, layer_views(cfg, flat), x, cos, sin, save=True)
+            saved.append(sv)
+            self._mark_layer_done(li)
+
+        # ---- head: final norm, logits, loss, and their backward -----------
+        x2d = x.reshape(T, cfg.hidden)
+        hN, rstdN = M.rmsnorm_fwd(x2d, ew["model.norm.weight"], cfg.rms_eps)
+        logits = G.mm_nt(hN, head_w)
+        loss_rows = M.xent_fwd_bwd_(logits, tgt, 1.0 / T)
+        loss = loss_rows.sum() / T
+        dhN = G.mm_nn(logits, head_w)
+        head_grad = egrad["model.embed_tokens.weight"] if cfg.tie_embeddings else egrad["lm_head.weight"]
+        G.mm_tn(logits, hN, out=head_grad)
+        del logits
+        if not cfg.tie_embeddings:
+            egrad["model.embed_tokens.weight"].zero_()
+        dx2d, dnorm = M.rmsnorm_bwd(dhN, x2d, ew["model.norm.weight"], rstdN)
+        egrad["model.norm.weight"].copy_(dnorm)
+        dx = dx2d.view(B, S, cfg.hidden)
+
+        # ---- backward ----------------------------------------------------
+        for li in range(L - 1, -1, -1):
+            flat = self._ensure_layer(li)
+            if li - 1 >= 0:
+                self._ensure_layer(li - 1)
+            self._wait_layer(li)
+            g = self.groups[li]
+            dx = layer_backward(cfg, layer_views(cfg, flat), layer_views(cfg, g.full_g), saved[li],
+                                dx, cos, sin)
+            saved[li] = None
+            self._mark_layer_done(li)
+            self._reduce_group(li)
+        egrad["model.embed_tokens.weight"].index_add_(0, tok.reshape(-1), dx.reshape(T, cfg.hidden))
+        self._reduce_group(len(self.all_groups) - 1)
+        self._finish_norm()
+        if multi:
+            torch.cuda.current_stream().wait_stream(self.reduce_stream)
+
+        # ---- optimizer ---------------------------------------------------
+        self.opt._exchange_epoch = t
+        self.opt.step()
+        if multi:
+            self.flags.signal(self.SLOT_PARAMS, t)
+            self.ring_owner = [-1] * len(self.ring)
+            self._gather_done.clear()
+            self._layer_done.clear()
+        return loss
+
+    def check_status(self) -> None:
+        """Raise if any kernel recorded a timed-out peer wait (reads one int from the device)."""
+        code = int(self.status.item())
+        for dev, c in self.opt.kernel_status().items():
+            code = max(code, c)
+        if code != 0:
+            raise RuntimeError(
+                "gefen_x_b200: a bounded wait on a peer ran out (status {}); a rank is missing "
+                "or far behind".format(code))
+
+    def num_params(self) -> int:
+        return sum(g.full_numel for g in self.all_groups)
+
+    def state_bytes_per_param(self) -> float:
+        """Optimizer-state bytes held by this rank divided by the parameters it owns."""
+        own = sum(g.shard_numel[self.rank] for g in self.all_groups)
+        return self.opt.state_bytes() / max(1, own)
+
+
+class _LocalGrad(U.LocalGrad):
+    pass

@@ -1,0 +1,226 @@
+"""GPU parity tests: every sm_100a kernel against a plain torch fp32 statement of the same op.
+
+Model: reference tests/test_fused_update_v2_full_parity.py (bit patterns for the
+quantised momentum, tolerance where reduction order differs),
+tests/test_gefen_factored_v.py, tests/test_factored_v_ema_parity.py,
+tests/test_find_period_backend.py.
+"""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _pair(shape, dtype, seed):
+    """Two optimizers (kernel vs decomposed torch) on identical params."""
+    from gefen_x_b200 import Gefen
+
+    g = torch.Generator().manual_seed(seed)
+    base = (torch.randn(shape, generator=g) * 0.05).to(dtype)
+    pa = base.clone().to(_dev()).requires_grad_()
+    pb = base.clone().to(_dev()).requires_grad_()
+    return pa, pb, g
+
+
+@pytest.mark.parametrize("shape,dtype", [
+    ((256, 512), torch.bfloat16), ((96, 1000), torch.float32), ((64, 24), torch.bfloat16),
+    ((300, 328), torch.float16), ((8, 4096), torch.bfloat16), ((33, 7), torch.float32),
+])
+@pytest.mark.parametrize("factored", [True, False])
+def test_update_kernels_match_decomposed(shape, dtype, factored):
+    from gefen_x_b200 import Gefen
+
+    pa, pb, g = _pair(shape, dtype, 1)
+    kw = dict(lr=1e-2, weight_decay=0.05, factored_v_2d=factored)
+    oa = Gefen([("w", pa)], fused=True, **kw)
+    ob = Gefen([("w", pb)], fused=False, **kw)
+    for step in range(4):
+        grad = (torch.randn(shape, generator=g) * 1e-3).to(dtype).to(_dev())
+        pa.grad = grad.clone()
+        pb.grad = grad.clone()
+        if step == 0:
+            ob.step()
+            # share the first-step analysis so that both sides use one codebook / period
+            oa._set_codebook(ob._gefen_codebook.clone())
+            oa.state[pa]["automatic_period"] = ob.state[pb]["automatic_period"]
+            oa.step()
+        else:
+            oa.step()
+            ob.step()
+        sa, sb = oa.state[pa], ob.state[pb]
+        assert sa["automatic_period"] == sb["automatic_period"]
+        assert torch.equal(sa["m_magnitude"], sb["m_magnitude"]), "magnitudes differ at step %d" % step
+        mism = (sa["m_codebook"] != sb["m_codebook"]).float().mean().item()
+        assert mism == 0.0, "index mismatch fraction %g at step %d" % (mism, step)
+        if factored and len(shape) == 2:
+            assert torch.allclose(sa["v_row"], sb["v_row"], rtol=2e-5, atol=1e-12)
+            assert torch.allclose(sa["v_col"], sb["v_col"], rtol=2e-5, atol=1e-12)
+        else:
+            assert torch.allclose(sa["vmean"], sb["vmean"], rtol=2e-5, atol=1e-12)
+        tol = 1e-6 if dtype == torch.float32 else 1e-2
+        assert torch.allclose(pa.float(), pb.float(), rtol=tol, atol=tol * 0.05)
+    torch.cuda.synchronize()
+    assert all(v == 0 for v in oa.kernel_status().values())
+
+
+def test_first_step_analysis_on_gpu_matches_cpu():
+    from gefen_x_b200.ops import quant as Q
+    from gefen_x_b200.quant import codebook as C
+    from gefen_x_b200.quant import partitioning as P
+
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(96 * 80, generator=g) * 1e-3)
+    xd = x.to(_dev())
+    for period in (1, 8, 80, 96 * 80 // 2):
+        want = C.block_normalised_histogram(x, period)
+        got = Q.histogram(xd, period).cpu()
+        assert torch.equal(want, got), period
+    for dt in (torch.bfloat16, torch.float32):
+        xs = x.to(dt)
+        divs = P.divisors(xs.numel())
+        want = P.block_variance_errors(xs.float().square().double(), divs)
+        got = Q.period_errors(xs.to(_dev()), divs, input_is_squared=False)
+        for a, b in zip(want, got):
+            assert abs(a - b) <= 1e-6 * max(abs(a), 1e-12) + 1e-14
+    # end to end: same period on both backends
+    p_cpu = P.find_period_by_block_variance(x.square(), print_results=False, backend="cpu",
+                                            parameter_shape=(96, 80))
+    p_gpu = P.find_period_by_block_variance(xd, print_results=False, backend="cuda_kernel",
+                                            parameter_shape=(96, 80), input_is_squared=False)
+    assert p_cpu == p_gpu
+
+
+def test_multi_source_gradient_and_clip_scale():
+    """Peer-slice summation (here: 4 local buffers) fused into the update == update on their mean."""
+    from gefen_x_b200 import Gefen
+    from gefen_x_b200.ops import update as U
+
+    shape = (128, 256)
+    g = torch.Generator().manual_seed(5)
+    base = (torch.randn(shape, generator=g) * 0.05).bfloat16()
+    pa = base.clone().to(_dev())
+    pb = base.clone().to(_dev())
+    srcs = [(torch.randn(shape, generator=g) * 1e-3).bfloat16().to(_dev()) for _ in range(4)]
+    mean = (sum(s.float() for s in srcs) * 0.25).bfloat16()
+    coef = torch.tensor([0.5], device=_dev())
+    oa = Gefen([("w", pa)], lr=1e-2)
+    ob = Gefen([("w", pb)], lr=1e-2)
+    peer = U.PeerGrad(ptrs=[s.data_ptr() for s in srcs], shape=shape, dtype=torch.bfloat16,
+                      device=_dev(), scale=0.25)
+    assert torch.equal(peer.materialize(), mean)
+    oa._grad_source = lambda p: peer
+    ob._grad_source = lambda p: U.LocalGrad(mean)
+    oa._external_grad_scale = coef
+    ob._external_grad_scale = coef
+    for _ in range(3):
+        oa.step()
+        ob.step()
+    assert torch.equal(oa.state[pa]["m_codebook"], ob.state[pb]["m_codebook"])
+    assert torch.equal(pa, pb)
+    # partial sums of squares + clip coefficient
+    partials = torch.zeros(512, device=_dev())
+    out = torch.empty(shape, dtype=torch.bfloat16, device=_dev())
+    U.reduce_sources(out, [s.data_ptr() for s in srcs], out.numel(), 0.25, partials,
+                     torch.bfloat16, _dev())
+    assert torch.equal(out, mean)
+    cc = torch.zeros(2, device=_dev())
+    U.clip_coef(partials, 1e-3, cc)
+    norm = mean.float().square().sum().sqrt().item()
+    assert abs(cc[1].item() - norm) < 1e-4 * norm
+    assert abs(cc[0].item() - min(1.0, 1e-3 / (norm + 1e-6))) < 1e-5
+
+
+def test_model_kernels_match_torch():
+    from gefen_x_b200.ops import model as M
+
+    g = torch.Generator().manual_seed(7)
+    dev = _dev()
+    for d, rows in ((2560, 37), (128, 1000), (4096, 16), (64, 5)):
+        x = torch.randn(rows, d, generator=g).bfloat16().to(dev)
+        w = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16().to(dev)
+        dy = torch.randn(rows, d, generator=g).bfloat16().to(dev)
+        y, rstd = M.rmsnorm_fwd(x, w, 1e-6)
+        ref = M.rmsnorm_ref(x.float(), w.float(), 1e-6)
+        assert torch.allclose(y.float(), ref, rtol=2e-2, atol=2e-2)
+        dx, dw = M.rmsnorm_bwd(dy, x, w, rstd)
+        xr = x.float().requires_grad_()
+        wr = w.float().requires_grad_()
+        M.rmsnorm_ref(xr, wr, 1e-6).backward(dy.float())
+        assert torch.allclose(dx.float(), xr.grad, rtol=3e-2, atol=3e-2)
+        assert torch.allclose(dw, wr.grad, rtol=2e-2, atol=5e-2)
+    # rope (both layouts, forward then inverse is the identity up to bf16 rounding)
+    B, S, n, hd = 2, 33, 4, 128
+    cos, sin = M.rope_tables(S, hd, 1e6, dev)
+    for inter in (False, True):
+        x = torch.randn(B, S, n, hd, generator=g).to(dev)
+        ref = M.rope_ref(x, cos, sin, interleaved=inter)
+        got = M.rope_(x.clone(), cos, sin, interleaved=inter)
+        assert torch.allclose(got, ref, atol=1e-5)
+        back = M.rope_(got.clone(), cos, sin, inverse=True, interleaved=inter)
+        assert torch.allclose(back, x, atol=1e-5)
+    # swiglu
+    gu = torch.randn(50, 2 * 688, generator=g).bfloat16().to(dev)
+    dz = torch.randn(50, 688, generator=g).bfloat16().to(dev)
+    gur = gu.float().requires_grad_()
+    out_ref = torch.nn.functional.silu(gur[:, :688]) * gur[:, 688:]
+    out_ref.backward(dz.float())
+    assert torch.allclose(M.swiglu_fwd(gu).float(), out_ref, rtol=2e-2, atol=2e-2)
+    assert torch.allclose(M.swiglu_bwd(gu, dz).float(), gur.grad, rtol=3e-2, atol=3e-2)
+    # cross-entropy forward + in-place gradient
+    for V in (1024, 151936, 1003):
+        T = 9
+        logits = (torch.randn(T, V, generator=g) * 2).bfloat16().to(dev)
+        tgt = torch.randint(0, V, (T,), generator=g).to(dev)
+        tgt[3] = -100
+        lr = logits.float().requires_grad_()
+        loss_ref = torch.nn.functional.cross_entropy(lr, tgt, ignore_index=-100, reduction="none")
+        (loss_ref.sum() * 0.125).backward()
+        work = logits.clone()
+        loss = M.xent_fwd_bwd_(work, tgt, 0.125)
+        assert torch.allclose(loss, loss_ref, rtol=1e-3, atol=1e-3)
+        assert torch.allclose(work.float(), lr.grad, rtol=2e-2, atol=2e-3)
+
+
+def test_decoder_kernel_path_matches_torch_path():
+    from gefen_x_b200.models.decoder import DecoderLM, get_config
+
+    cfg = get_config("tiny-llama", qk_norm=True)
+    ref = DecoderLM(cfg, device=_dev(), dtype=torch.float32, impl="torch", seed=3)
+    ker = DecoderLM(cfg, device=_dev(), dtype=torch.bfloat16, impl="kernel", seed=3)
+    g = torch.Generator().manual_seed(9)
+    tok = torch.randint(0, 1024, (2, 65), generator=g).to(_dev())
+    l_ref = ref(tok[:, :-1], tok[:, 1:])
+    l_ker = ker(tok[:, :-1], tok[:, 1:])
+    l_ref.backward()
+    l_ker.backward()
+    assert abs(l_ref.item() - l_ker.item()) < 3e-2
+    for (n, a), (_, b) in zip(ref.named_parameters(), ker.named_parameters()):
+        denom = a.grad.abs().max().item() + 1e-6
+        assert (a.grad - b.grad.float()).abs().max().item() / denom < 0.08, n
+
+
+def test_sharded_trainer_single_gpu_tracks_cpu_fp32():
+    from gefen_x_b200.models.decoder import get_config
+    from gefen_x_b200.parallel.fsdp import ShardedTrainer
+
+    cfg = get_config("tiny-llama")
+    g = torch.Generator().manual_seed(2)
+    tok = torch.randint(0, 1024, (4, 129), generator=g)
+    cpu = ShardedTrainer(cfg, device="cpu", dtype=torch.float32, lr=6e-4, weight_decay=0.01,
+                         clip_grad_norm=1.0, seed=5)
+    gpu = ShardedTrainer(cfg, device=_dev(), dtype=torch.bfloat16, lr=6e-4, weight_decay=0.01,
+                         clip_grad_norm=1.0, seed=5)
+    lc, lg = [], []
+    for _ in range(20):
+        lc.append(cpu.step(tok[:, :-1], tok[:, 1:]).item())
+        lg.append(gpu.step(tok[:, :-1].pin_memory(), tok[:, 1:].pin_memory()).item())
+    gpu.check_status()
+    assert lg[-1] < lg[0] - 0.5
+    assert abs(lc[-1] - lg[-1]) / lc[-1] < 0.05, (lc, lg)
+    assert gpu.state_bytes_per_param() < 1.1

@@ -1,0 +1,169 @@
+"""CPU tests of the period search and codebook machinery.
+
+Model: reference tests/test_partitioning_quantization_cpu.py,
+tests/test_codebook_indices_parity.py, tests/test_dequant_indices_parity.py.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from gefen_x_b200.quant import codebook as C
+from gefen_x_b200.quant import partitioning as P
+
+
+def test_divisors_proper_and_sorted():
+    assert P.divisors(12) == [1, 2, 3, 4, 6]
+    assert P.divisors(7) == [1]
+    assert P.divisors(1) == []
+    assert P.divisors(16) == [1, 2, 4, 8]
+
+
+def test_block_variance_matches_numpy():
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal(240) ** 2
+    for p in P.divisors(240):
+        want = math.sqrt(x.reshape(-1, p).var(axis=1).mean())
+        got = P.average_within_block_variance_cpu(x, p)
+        assert abs(want - got) < 1e-12
+
+
+def test_period_search_matches_direct_statement():
+    """find_period == argmin over divisors of err[p] - err[previous p], computed directly."""
+    rng = np.random.default_rng(3)
+    for n in (96, 360, 1024):
+        g2 = rng.standard_normal(n) ** 2
+        divs = P.divisors(n)
+        errs = [math.sqrt(g2.reshape(-1, p).var(axis=1).mean()) for p in divs]
+        scores = [1e-12] + [errs[i] - errs[i - 1] for i in range(1, len(errs))]
+        best = min(zip(scores, divs))[1]
+        want = 1 if best < 8 else best
+        if want == 1:
+            want = P.memory_safe_fallback_period(n, (n,))
+        got = P.find_period_by_block_variance(torch.from_numpy(g2), print_results=False,
+                                              parameter_shape=(n,), backend="cpu")
+        assert got == want
+
+
+def test_small_winner_collapses_and_fallback():
+    # a flat curve has no structure: the winner is tiny -> 1 -> memory-safe fallback
+    assert P.select_period([(1, 0.5), (2, 0.5), (4, 0.5)]) == 1
+    assert P.memory_safe_fallback_period(4096 * 64, (4096, 64)) == 2048
+    assert P.memory_safe_fallback_period(4096 * 4096, (4096, 4096)) == 4096
+    assert P.memory_safe_fallback_period(7, (7,)) == 1
+    assert P.memory_safe_fallback_period(2560, (2560,)) == 1280
+    old = P.MEMORY_SAFE_FALLBACK
+    try:
+        P.MEMORY_SAFE_FALLBACK = False
+        x = torch.ones(64)
+        assert P.find_period_by_block_variance(x, print_results=False) == 1
+    finally:
+        P.MEMORY_SAFE_FALLBACK = old
+
+
+def test_select_period_tie_prefers_smaller():
+    assert P.select_period([(1, 1.0), (8, 0.5), (16, 0.0), (32, -0.5)]) == 8
+
+
+def _brute_force_kmeans(xs, ws, k):
+    """Exhaustive optimal contiguous partition for tiny inputs (endpoints pinned)."""
+    import itertools
+
+    n = len(xs)
+    best = (float("inf"), None)
+    for cuts in itertools.combinations(range(1, n), k - 1):
+        b = (0,) + cuts + (n,)
+        cost, cents = 0.0, []
+        for c in range(k):
+            seg_x, seg_w = xs[b[c]:b[c + 1]], ws[b[c]:b[c + 1]]
+            if c == 0:
+                cen = -1.0
+            elif c == k - 1:
+                cen = 1.0
+            else:
+                cen = float((seg_x * seg_w).sum() / seg_w.sum())
+            cost += float((seg_w * (seg_x - cen) ** 2).sum())
+            cents.append(cen)
+        if cost < best[0] - 1e-15:
+            best = (cost, cents)
+    return best
+
+
+def test_exact_dp_is_optimal_and_backends_agree():
+    rng = np.random.default_rng(1)
+    xs = np.sort(rng.uniform(-1, 1, 12)).astype(np.float32)
+    ws = rng.integers(1, 20, 12).astype(np.float32)
+    stats = {"active_centers": torch.from_numpy(xs), "active_counts": torch.from_numpy(ws)}
+    cb = C.exact_dp(stats, 4, True)
+    _, cents = _brute_force_kmeans(xs.astype(np.float64), ws.astype(np.float64), 4)
+    assert torch.allclose(cb, torch.tensor(sorted(cents), dtype=torch.float32), atol=1e-6)
+    # numpy fallback == C++ solver
+    w = torch.from_numpy(ws).double()
+    x = torch.from_numpy(xs).double()
+    pw = torch.cat([torch.zeros(1, dtype=torch.float64), torch.cumsum(w, 0)]).numpy()
+    pwx = torch.cat([torch.zeros(1, dtype=torch.float64), torch.cumsum(w * x, 0)]).numpy()
+    pwx2 = torch.cat([torch.zeros(1, dtype=torch.float64), torch.cumsum(w * x * x, 0)]).numpy()
+    alt = np.sort(C._exact_dp_numpy(pw, pwx, pwx2, 4, True))
+    assert np.allclose(alt, cb.numpy(), atol=1e-7)
+
+
+def test_exact_dp_pads_when_few_points():
+    stats = {"active_centers": torch.tensor([-0.5, 0.25]), "active_counts": torch.tensor([3.0, 1.0])}
+    cb = C.exact_dp(stats, 8, True)
+    assert cb.numel() == 8 and cb[0] == -1.0 and cb[-1] == 1.0
+    assert torch.all(cb[1:] >= cb[:-1])
+
+
+def test_learned_codebook_is_sorted_with_endpoints():
+    torch.manual_seed(0)
+    g = torch.randn(64, 256) * 1e-3
+    cb = C.learn_codebook_from_grad_periods([("w", g.reshape(-1), 256, g)], "cpu")
+    assert cb.shape == (256,) and cb.dtype == torch.float32
+    assert cb[0] == -1.0 and cb[-1] == 1.0
+    assert torch.all(cb[1:] >= cb[:-1])
+
+
+def test_nearest_index_ties_go_low_and_match_brute_force():
+    cb = torch.tensor([-1.0, -0.5, 0.0, 0.5, 1.0])
+    v = torch.tensor([-2.0, -0.75, -0.25, 0.25, 0.1, 0.75, 3.0, 0.0])
+    got = C.nearest_codebook_indices(cb, v)
+    assert got.tolist() == [0, 0, 1, 2, 2, 3, 4, 2]
+    torch.manual_seed(1)
+    cb = torch.sort(torch.rand(256) * 2 - 1).values
+    cb[0], cb[-1] = -1.0, 1.0
+    v = torch.rand(5000) * 2.2 - 1.1
+    brute = (v[:, None] - cb[None, :]).abs().argmin(dim=1)
+    got = C.nearest_codebook_indices(cb, v).long()
+    assert torch.equal((v - cb[got]).abs(), (v - cb[brute]).abs())
+
+
+def test_dequantize_round_trip():
+    cb = torch.linspace(-1, 1, 256)
+    idx = torch.randint(0, 256, (7, 33), dtype=torch.uint8)
+    out = C.dequantize_indices(cb, idx, torch.float32)
+    assert torch.equal(out, cb[idx.long()])
+    assert torch.equal(C.nearest_codebook_indices(cb, out), idx)
+
+
+def test_search_lut_brackets_every_value():
+    torch.manual_seed(2)
+    cb = torch.sort(torch.rand(256) * 2 - 1).values
+    cb[0], cb[-1] = -1.0, 1.0
+    lut = C.codebook_search_lut(cb).long()
+    assert lut.numel() == 4097 and lut[0] == 0 and lut[-1] == 256
+    v = torch.rand(20000) * 2 - 1
+    b = torch.floor((v + 1.0) * 2048).clamp(0, 4095).long()
+    ins = torch.bucketize(v, cb)
+    assert torch.all(ins >= lut[b]) and torch.all(ins <= lut[b + 1])
+    packed = C.packed_search_lut(cb)
+    assert packed.dtype == torch.int32 and packed.numel() == 4096
+    assert torch.equal(packed & 0xFFFF, lut[:-1].int()) and torch.equal(packed >> 16, lut[1:].int())
+
+
+def test_histogram_counts_total_and_symmetry():
+    g = torch.tensor([1.0, -1.0, 0.5, 0.0, 2.0, -2.0, 0.0, 0.0])
+    counts = C.block_normalised_histogram(g, 4)
+    assert counts.sum().item() == 8
+    assert counts[4095].item() == 2          # +1.0 of each block clamps into the last bin
+    assert counts[0].item() == 2             # -1.0
