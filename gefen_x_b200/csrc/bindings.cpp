@@ -41,8 +41,8 @@ inline cudaStream_t stream() { return c10::cuda::getCurrentCUDAStream().stream()
 int64_t desc_size() { return (int64_t)sizeof(gx::TensorDesc); }
 
 gx::LaunchCommon make_common(const Tensor& descs, const Tensor& tile_start, int64_t n_tensors,
-                             int64_t total_tiles, const Tensor& codebook, const Tensor& lut,
-                             const c10::optional<Tensor>& gscale, const c10::optional<Tensor>& status,
+                             int64_t total_tiles, const Tensor& codebook, const Tensor& thr,
+                             const Tensor& lut, const c10::optional<Tensor>& gscale, const c10::optional<Tensor>& status,
                              int64_t sr_seed, bool stochastic, int64_t wait_iters) {
     TORCH_CHECK(descs.is_cuda() && descs.scalar_type() == at::kByte && descs.is_contiguous(),
                 "descs must be a contiguous CUDA uint8 tensor");
@@ -61,7 +61,10 @@ gx::LaunchCommon make_common(const Tensor& descs, const Tensor& tile_start, int6
     c.tile_start = tile_start.data_ptr<int>();
     c.n_tensors = (int)n_tensors;
     c.total_tiles = (int)total_tiles;
+    TORCH_CHECK(thr.is_cuda() && thr.scalar_type() == at::kFloat && thr.numel() == 256 && thr.is_contiguous(),
+                "thresholds must be CUDA fp32 [256]");
     c.codebook = codebook.data_ptr<float>();
+    c.thresholds = thr.data_ptr<float>();
     c.lut = reinterpret_cast<const uint32_t*>(lut.data_ptr<int>());
     c.gscale = nullptr;
     if (gscale.has_value() && gscale->defined()) {
@@ -80,22 +83,23 @@ gx::LaunchCommon make_common(const Tensor& descs, const Tensor& tile_start, int6
 }
 
 void block_update(const Tensor& descs, const Tensor& tile_start, int64_t n_tensors, int64_t total_tiles,
-                  const Tensor& codebook, const Tensor& lut, const c10::optional<Tensor>& gscale,
-                  const c10::optional<Tensor>& status, int64_t dtype, int64_t sr_seed, bool stochastic) {
+                  const Tensor& codebook, const Tensor& thr, const Tensor& lut,
+                  const c10::optional<Tensor>& gscale, const c10::optional<Tensor>& status,
+                  int64_t dtype, int64_t sr_seed, bool stochastic) {
     c10::cuda::CUDAGuard guard(descs.device());
-    auto c = make_common(descs, tile_start, n_tensors, total_tiles, codebook, lut, gscale, status,
+    auto c = make_common(descs, tile_start, n_tensors, total_tiles, codebook, thr, lut, gscale, status,
                          sr_seed, stochastic, 0);
     check(gx::launch_block_update(c, (int)dtype, sm_count(), stream()), "block_update");
 }
 
 void factored_update(const Tensor& descs, const Tensor& tile_start, int64_t n_tensors,
-                     int64_t total_tiles, const Tensor& codebook, const Tensor& lut,
+                     int64_t total_tiles, const Tensor& codebook, const Tensor& thr, const Tensor& lut,
                      const c10::optional<Tensor>& gscale, const c10::optional<Tensor>& status,
                      int64_t dtype, int64_t sr_seed, bool stochastic, int64_t wait_iters,
                      int64_t phases, int64_t epoch) {
     // phases bit 0: statistics, bit 1: EMA (+ exchange), bit 2: apply + finalize
     c10::cuda::CUDAGuard guard(descs.device());
-    auto c = make_common(descs, tile_start, n_tensors, total_tiles, codebook, lut, gscale, status,
+    auto c = make_common(descs, tile_start, n_tensors, total_tiles, codebook, thr, lut, gscale, status,
                          sr_seed, stochastic, wait_iters);
     c.epoch = (uint32_t)epoch;
     const int sms = sm_count();
@@ -297,9 +301,9 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("desc_size() -> int", &desc_size);
     m.def("rmsnorm_bwd_partials(int rows, int d) -> int", &rmsnorm_bwd_partials);
     m.def("block_update(Tensor descs, Tensor tile_start, int n_tensors, int total_tiles, Tensor codebook, "
-          "Tensor lut, Tensor? gscale, Tensor? status, int dtype, int sr_seed, bool stochastic) -> ()");
+          "Tensor thr, Tensor lut, Tensor? gscale, Tensor? status, int dtype, int sr_seed, bool stochastic) -> ()");
     m.def("factored_update(Tensor descs, Tensor tile_start, int n_tensors, int total_tiles, Tensor codebook, "
-          "Tensor lut, Tensor? gscale, Tensor? status, int dtype, int sr_seed, bool stochastic, "
+          "Tensor thr, Tensor lut, Tensor? gscale, Tensor? status, int dtype, int sr_seed, bool stochastic, "
           "int wait_iters, int phases, int epoch) -> ()");
     m.def("reduce_sources(Tensor? out, int[] src_ptrs, int numel, float scale, Tensor? partials, "
           "int dtype, int device_index) -> ()", &reduce_sources);

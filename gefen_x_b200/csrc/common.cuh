@@ -82,23 +82,39 @@ __device__ __forceinline__ void store_idx8(uint8_t* p, const int (&v)[8]) {
 }
 
 // ---- codebook search --------------------------------------------------------
-// cb: 256 sorted fp32 codewords; lut: 4096 words, low 16 bits = number of
-// codewords in lower buckets, high 16 bits = the same for the next bucket, so
-// the insertion point of v lies in [lo, hi].  Result: nearest codeword, equal
-// distances resolve to the lower index.  NaN maps to index 0.
-__device__ __forceinline__ int nearest_index(float v, const float* __restrict__ cb,
-                                             const uint32_t* __restrict__ lut) {
-    float t = __fmul_rn(__fadd_rn(v, 1.0f), (float)(kLutBuckets / 2));
-    int b = (t >= 0.0f) ? ((t < (float)kLutBuckets) ? (int)t : kLutBuckets - 1) : 0;
-    uint32_t e = lut[b];
+// The nearest codeword of v is found with the 255 decision thresholds
+// thr[i] = fp32((cb[i] + cb[i + 1]) / 2):  index = #{ i : thr[i] < v }, so a value on
+// a threshold goes to the lower codeword.  A 4096-bucket table narrows the
+// search: lut[b] packs (number of thresholds in lower buckets) | (the same for
+// the next bucket) << 16, with bucket(x) = floor(fma(x, 2048, 2048)) clamped to
+// [0, 4095].  Most buckets hold no threshold, so the common case is one table
+// load and no compare.  NaN maps to index 0.
+//
+// Shared-memory tables are replicated per lane (entry i of lane l at
+// [i * 32 + l]) so that the data-dependent loads of a warp never collide on a
+// bank.
+struct QuantTables {
+    const float* cb;          // [256 * 32] lane-replicated codebook
+    const float* thr;         // [256 * 32] lane-replicated thresholds (entry 255 = +inf)
+    const uint32_t* lut;      // [4096]
+};
+
+__device__ __forceinline__ float rep_load(const float* t, int i) {
+    return t[(i << 5) | (threadIdx.x & 31)];
+}
+
+__device__ __forceinline__ int lut_bucket(float v) {
+    const float t = fminf(fmaxf(__fmaf_rn(v, (float)(kLutBuckets / 2), (float)(kLutBuckets / 2)), 0.0f),
+                          (float)(kLutBuckets - 1));
+    return (int)t;   // NaN: fmaxf(NaN, 0) = 0
+}
+
+__device__ __forceinline__ int nearest_index(float v, const QuantTables& q) {
+    const uint32_t e = q.lut[lut_bucket(v)];
     int i = (int)(e & 0xffffu);
     const int hi = (int)(e >> 16);
-    while (i < hi && cb[i] < v) ++i;
-    const int r = min(i, kCodewords - 1);
-    const int l = max(i - 1, 0);
-    const float dl = fabsf(__fsub_rn(v, cb[l]));
-    const float dr = fabsf(__fsub_rn(v, cb[r]));
-    return (dl <= dr) ? l : r;
+    while (i < hi && rep_load(q.thr, i) < v) ++i;
+    return i;
 }
 
 // SplitMix64 finaliser of (seed, element index) -> 24 uniform bits in [0, 1).
@@ -112,17 +128,13 @@ __device__ __forceinline__ float sr_uniform(uint64_t seed, uint64_t elem) {
 
 // Stochastic variant: between the two neighbouring codewords lo <= v <= hi pick
 // hi with probability (v - lo) / (hi - lo).
-__device__ __forceinline__ int stochastic_index(float v, const float* __restrict__ cb,
-                                                const uint32_t* __restrict__ lut, float u) {
-    float t = __fmul_rn(__fadd_rn(v, 1.0f), (float)(kLutBuckets / 2));
-    int b = (t >= 0.0f) ? ((t < (float)kLutBuckets) ? (int)t : kLutBuckets - 1) : 0;
-    uint32_t e = lut[b];
-    int i = (int)(e & 0xffffu);
-    const int hi = (int)(e >> 16);
-    while (i < hi && cb[i] < v) ++i;
-    const int r = min(i, kCodewords - 1);
-    const int l = max(i - 1, 0);
-    const float lo_v = cb[l], hi_v = cb[r];
+__device__ __forceinline__ int stochastic_index(float v, const QuantTables& q, float u) {
+    const int n = nearest_index(v, q);
+    const float c = rep_load(q.cb, n);
+    int l, r;
+    if (v >= c) { l = n; r = min(n + 1, kCodewords - 1); }
+    else { l = max(n - 1, 0); r = n; }
+    const float lo_v = rep_load(q.cb, l), hi_v = rep_load(q.cb, r);
     if (!(hi_v > lo_v) || v <= lo_v) return (v >= hi_v) ? r : l;
     if (v >= hi_v) return r;
     const float pr = (v - lo_v) / (hi_v - lo_v);

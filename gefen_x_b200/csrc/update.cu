@@ -32,17 +32,39 @@ namespace {
 
 constexpr int kThreads = 256;
 
+// Dynamic shared memory of a CTA: lane-replicated codebook (and, for kernels that
+// requantise, thresholds + bucket table) followed by a small reduction scratch.
 struct Smem {
-    float cb[kCodewords];
-    uint32_t lut[kLutBuckets];
-    float red[kThreads / 32 * 2];
-    float bcast[4];
+    float* cb;         // [256 * 32]
+    float* thr;        // [256 * 32] or null
+    uint32_t* lut;     // [4096] or null
+    float* red;        // [16]
+    QuantTables q;
 };
 
-__device__ __forceinline__ void load_tables(Smem& s, const LaunchCommon& c) {
-    for (int i = threadIdx.x; i < kCodewords; i += blockDim.x) s.cb[i] = c.codebook[i];
-    for (int i = threadIdx.x; i < kLutBuckets; i += blockDim.x) s.lut[i] = c.lut[i];
+constexpr int kRepFloats = kCodewords * 32;
+constexpr size_t kSmemStats = (size_t)(kRepFloats + 16) * sizeof(float);
+constexpr size_t kSmemFull = (size_t)(2 * kRepFloats + kLutBuckets + 16) * sizeof(float);
+
+extern __shared__ __align__(16) unsigned char gx_smem_raw[];
+
+__device__ __forceinline__ Smem load_tables(const LaunchCommon& c, bool full) {
+    Smem s;
+    float* base = reinterpret_cast<float*>(gx_smem_raw);
+    s.red = base;
+    s.cb = base + 16;
+    s.thr = full ? s.cb + kRepFloats : nullptr;
+    s.lut = full ? reinterpret_cast<uint32_t*>(s.thr + kRepFloats) : nullptr;
+    for (int i = threadIdx.x; i < kRepFloats; i += blockDim.x) s.cb[i] = c.codebook[i >> 5];
+    if (full) {
+        for (int i = threadIdx.x; i < kRepFloats; i += blockDim.x) s.thr[i] = c.thresholds[i >> 5];
+        for (int i = threadIdx.x; i < kLutBuckets; i += blockDim.x) s.lut[i] = c.lut[i];
+    }
+    s.q.cb = s.cb;
+    s.q.thr = s.thr;
+    s.q.lut = s.lut;
     __syncthreads();
+    return s;
 }
 
 __device__ __forceinline__ int find_tensor(const int* __restrict__ start, int n, int tile) {
@@ -54,16 +76,49 @@ __device__ __forceinline__ int find_tensor(const int* __restrict__ start, int n,
     return lo;
 }
 
+// The fields of a descriptor that the tile kernels use, copied into registers when a
+// CTA moves to a new tensor (a reference into global memory would be re-read after
+// every store or atomic, since the compiler must assume they alias).
+struct Hot {
+    void* p;
+    const void* g0;
+    const TensorDesc* full;   // for the rarely used arrays (extra gradient sources)
+    uint8_t* idx;
+    float* mag;
+    float* mag_new;
+    float* row_sq;
+    float* col_sq;
+    const float* rfac;
+    const float* cfac;
+    const float* scal;
+    int rows, cols, period, n_src, blk_mode, tcols, trows, n_col_tiles, rows_per_tile, vec, row_only;
+    float beta1, omb1, eps, src_scale;
+};
+
+__device__ __forceinline__ Hot load_hot(const TensorDesc* t) {
+    Hot h;
+    h.p = t->p; h.g0 = t->g[0]; h.full = t; h.idx = t->idx; h.mag = t->mag; h.mag_new = t->mag_new;
+    h.row_sq = t->row_sq; h.col_sq = t->col_sq; h.rfac = t->rfac; h.cfac = t->cfac; h.scal = t->scal;
+    h.rows = t->rows; h.cols = t->cols; h.period = t->period; h.n_src = t->n_src;
+    h.blk_mode = t->blk_mode; h.tcols = t->tcols; h.trows = t->trows; h.n_col_tiles = t->n_col_tiles;
+    h.rows_per_tile = t->rows_per_tile; h.vec = t->vec; h.row_only = t->row_only;
+    h.beta1 = t->beta1; h.omb1 = t->omb1; h.eps = t->eps; h.src_scale = t->src_scale;
+    return h;
+}
+
 // Gradient chunk of 8 (VEC=8) or 1 element: sum of the sources in fp32, scaled,
 // rounded to the storage type when more than one source contributed.
-template <typename T, int VEC>
-__device__ __forceinline__ void load_grad(const TensorDesc& d, long long off, float gs, float (&g)[VEC]) {
+__device__ __forceinline__ const void* grad_src(const TensorDesc& d, int s) { return d.g[s]; }
+__device__ __forceinline__ const void* grad_src(const Hot& d, int s) { return s == 0 ? d.g0 : d.full->g[s]; }
+
+template <typename T, int VEC, typename D>
+__device__ __forceinline__ void load_grad(const D& d, long long off, float gs, float (&g)[VEC]) {
     if constexpr (VEC == 8) {
-        Vec8<T>::load(reinterpret_cast<const T*>(d.g[0]) + off, g);
+        Vec8<T>::load(reinterpret_cast<const T*>(grad_src(d, 0)) + off, g);
         if (d.n_src > 1) {
             for (int s = 1; s < d.n_src; ++s) {
                 float t[8];
-                Vec8<T>::load(reinterpret_cast<const T*>(d.g[s]) + off, t);
+                Vec8<T>::load(reinterpret_cast<const T*>(grad_src(d, s)) + off, t);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) g[e] += t[e];
             }
@@ -71,9 +126,9 @@ __device__ __forceinline__ void load_grad(const TensorDesc& d, long long off, fl
             for (int e = 0; e < 8; ++e) g[e] = round_to<T>(__fmul_rn(g[e], d.src_scale));
         }
     } else {
-        float a = to_f<T>(reinterpret_cast<const T*>(d.g[0])[off]);
+        float a = to_f<T>(reinterpret_cast<const T*>(grad_src(d, 0))[off]);
         if (d.n_src > 1) {
-            for (int s = 1; s < d.n_src; ++s) a += to_f<T>(reinterpret_cast<const T*>(d.g[s])[off]);
+            for (int s = 1; s < d.n_src; ++s) a += to_f<T>(reinterpret_cast<const T*>(grad_src(d, s))[off]);
             a = round_to<T>(__fmul_rn(a, d.src_scale));
         }
         g[0] = a;
@@ -114,8 +169,8 @@ __device__ __forceinline__ float apply_one(float pf, float q, float step, float 
 }
 
 __device__ __forceinline__ int quantise(float n, const Smem& s, const LaunchCommon& c, long long elem) {
-    if (c.stochastic) return stochastic_index(n, s.cb, s.lut, sr_uniform(c.sr_seed, (uint64_t)elem));
-    return nearest_index(n, s.cb, s.lut);
+    if (c.stochastic) return stochastic_index(n, s.q, sr_uniform(c.sr_seed, (uint64_t)elem));
+    return nearest_index(n, s.q);
 }
 
 // ---------------------------------------------------------------------------
@@ -124,7 +179,7 @@ __device__ __forceinline__ int quantise(float n, const Smem& s, const LaunchComm
 // One worker of NL lanes owns block `blk` of tensor d.  MODE 0: NL = 1 thread,
 // 1: a warp, 2: the CTA.
 template <typename T, int VEC, int MODE>
-__device__ void block_worker(const TensorDesc& d, const LaunchCommon& c, Smem& s, long long blk,
+__device__ void block_worker(const TensorDesc& d, const LaunchCommon& c, const Smem& s, long long blk,
                              bool valid, float gs) {
     const int lane = (MODE == 0) ? 0 : (MODE == 1 ? (threadIdx.x & 31) : threadIdx.x);
     const int nl = (MODE == 0) ? 1 : (MODE == 1 ? 32 : kThreads);
@@ -143,7 +198,7 @@ __device__ void block_worker(const TensorDesc& d, const LaunchCommon& c, Smem& s
             load_index<VEC>(d.idx + base + e0, ix);
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
-                float m = ema_momentum(s.cb[ix[e]], mag_old, g[e], d.beta1, d.omb1);
+                float m = ema_momentum(rep_load(s.cb, ix[e]), mag_old, g[e], d.beta1, d.omb1);
                 amax = fmaxf(amax, fabsf(m));
                 ssq += g[e] * g[e];
             }
@@ -181,10 +236,10 @@ __device__ void block_worker(const TensorDesc& d, const LaunchCommon& c, Smem& s
         load_param<T, VEC>(p + base + e0, pf);
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-            float m = ema_momentum(s.cb[ix[e]], mag_old, g[e], d.beta1, d.omb1);
+            float m = ema_momentum(rep_load(s.cb, ix[e]), mag_old, g[e], d.beta1, d.omb1);
             int k = quantise(__fmul_rn(m, inv), s, c, base + e0 + e);
             ix[e] = k;
-            pf[e] = apply_one<T>(pf[e], __fmul_rn(s.cb[k], amax), step, lr, wdf);
+            pf[e] = apply_one<T>(pf[e], __fmul_rn(rep_load(s.cb, k), amax), step, lr, wdf);
         }
         store_index<VEC>(d.idx + base + e0, ix);
         store_param<T, VEC>(p + base + e0, pf);
@@ -193,12 +248,11 @@ __device__ void block_worker(const TensorDesc& d, const LaunchCommon& c, Smem& s
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads) block_update_kernel(LaunchCommon c) {
-    __shared__ Smem s;
-    load_tables(s, c);
+    const Smem s = load_tables(c, true);
     const float gs = c.gscale ? *c.gscale : 1.0f;
     for (int tile = blockIdx.x; tile < c.total_tiles; tile += gridDim.x) {
         const int ti = find_tensor(c.tile_start, c.n_tensors, tile);
-        const TensorDesc& d = c.descs[ti];
+        const TensorDesc d = c.descs[ti];   // local copy: stores cannot force re-reads of it
         const long long local = tile - c.tile_start[ti];
         if (d.mode == 2) {
             if (d.vec) block_worker<T, 8, 2>(d, c, s, local, local < d.nb, gs);
@@ -217,7 +271,7 @@ __global__ void __launch_bounds__(kThreads) block_update_kernel(LaunchCommon c) 
 // ---------------------------------------------------------------------------
 // factored path
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ long long block_of(const TensorDesc& d, int r, int c0) {
+__device__ __forceinline__ long long block_of(const Hot& d, int r, int c0) {
     switch (d.blk_mode) {
         case 0: return r;
         case 1: return (long long)r * (d.cols / d.period) + c0 / d.period;
@@ -244,12 +298,35 @@ __device__ __forceinline__ TileCursor locate(const LaunchCommon& c, int tile) {
     return t;
 }
 
+// Running maximum of |m| for the block a thread (or, when every lane of a warp
+// is in the same block, the warp) is currently inside.  It is flushed with one
+// atomic when the block changes, so a block that spans many rows or tiles costs
+// one atomic per warp instead of one per row.
+struct RunMax {
+    float* dst;        // mag_new of the tensor the run belongs to
+    long long blk;     // -1: empty
+    float val;
+    int uniform;
+};
+
+__device__ __forceinline__ void runmax_flush(RunMax& r) {
+    if (r.uniform) {
+        const float m = warp_max(r.val);
+        if ((threadIdx.x & 31) == 0 && r.blk >= 0) atomic_max_nonneg(r.dst + r.blk, m);
+    } else if (r.blk >= 0) {
+        atomic_max_nonneg(r.dst + r.blk, r.val);
+    }
+    r.blk = -1;
+    r.val = 0.f;
+}
+
 template <typename T, int VEC, int U>
-__device__ void stats_tile(const TensorDesc& d, const Smem& s, const TileCursor& t, float gs,
-                           float (&csum)[VEC], bool uniform) {
+__device__ void stats_tile(const Hot& d, const Smem& s, const TileCursor& t, float gs,
+                           float (&csum)[VEC], RunMax& run) {
     const int tx = threadIdx.x % d.tcols, ty = threadIdx.x / d.tcols;
     const int c0 = (t.ct * d.tcols + tx) * VEC;
     const bool act = c0 < d.cols;
+    const bool uniform = run.uniform != 0;
     for (int rb = t.r0 + ty; rb < t.r1; rb += d.trows * U) {
         float g[U][VEC];
         int ix[U][VEC];
@@ -267,13 +344,13 @@ __device__ void stats_tile(const TensorDesc& d, const Smem& s, const TileCursor&
             const int r = rb + u * d.trows;
             if (r >= t.r1) break;  // uniform across the warp: a warp shares ty
             float amax = 0.f, rs = 0.f;
-            long long blk = 0;
+            long long blk = -1;
             if (act) {
                 blk = block_of(d, r, c0);
                 const float mo = d.mag[blk];
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) {
-                    float m = ema_momentum(s.cb[ix[u][e]], mo, g[u][e], d.beta1, d.omb1);
+                    float m = ema_momentum(rep_load(s.cb, ix[u][e]), mo, g[u][e], d.beta1, d.omb1);
                     amax = fmaxf(amax, fabsf(m));
                     const float sq = g[u][e] * g[u][e];
                     rs += sq;
@@ -283,17 +360,21 @@ __device__ void stats_tile(const TensorDesc& d, const Smem& s, const TileCursor&
             rs = warp_sum(rs);
             if ((threadIdx.x & 31) == 0 && act) atomicAdd(d.row_sq + r, rs);
             if (uniform) {
-                amax = warp_max(amax);
-                if ((threadIdx.x & 31) == 0 && act) atomic_max_nonneg(d.mag_new + blk, amax);
+                const long long b0 = __shfl_sync(0xffffffffu, blk, 0);   // lane 0 has the lowest column
+                if (b0 >= 0) {
+                    if (b0 != run.blk) { runmax_flush(run); run.blk = b0; }
+                    run.val = fmaxf(run.val, amax);
+                }
             } else if (act) {
-                atomic_max_nonneg(d.mag_new + blk, amax);
+                if (blk != run.blk) { runmax_flush(run); run.blk = blk; }
+                run.val = fmaxf(run.val, amax);
             }
         }
     }
 }
 
 template <int VEC>
-__device__ __forceinline__ void flush_cols(const TensorDesc& d, int ct, float (&csum)[VEC]) {
+__device__ __forceinline__ void flush_cols(const Hot& d, int ct, float (&csum)[VEC]) {
     const int tx = threadIdx.x % d.tcols;
     const int c0 = (ct * d.tcols + tx) * VEC;
     if (c0 < d.cols) {
@@ -306,42 +387,83 @@ __device__ __forceinline__ void flush_cols(const TensorDesc& d, int ct, float (&
     for (int e = 0; e < VEC; ++e) csum[e] = 0.f;
 }
 
-__device__ __forceinline__ bool warp_uniform_blocks(const TensorDesc& d, int vec) {
+__device__ __forceinline__ bool warp_uniform_blocks(const Hot& d, int vec) {
     if (d.blk_mode == 0 || d.blk_mode == 2) return true;
     if (d.blk_mode == 1) return (d.period % (32 * vec)) == 0;
     return false;
 }
 
+// Walks the contiguous tile range of a CTA.  The descriptor of the current tensor is
+// held in a local copy (so that stores and atomics cannot force it to be re-read)
+// and the (tensor, column tile, row tile) position advances incrementally; only
+// the first tile of the range needs the binary search.
+struct TileWalk {
+    int ti, ct, rt, n_row_tiles;
+};
+
+__device__ __forceinline__ void walk_begin(const LaunchCommon& c, long long tile, TileWalk& w, Hot& d) {
+    w.ti = find_tensor(c.tile_start, c.n_tensors, (int)tile);
+    d = load_hot(c.descs + w.ti);
+    const int local = (int)tile - c.tile_start[w.ti];
+    w.n_row_tiles = (d.rows + d.rows_per_tile - 1) / d.rows_per_tile;
+    w.ct = local / w.n_row_tiles;
+    w.rt = local - w.ct * w.n_row_tiles;
+}
+
+__device__ __forceinline__ TileCursor walk_cursor(const TileWalk& w, const Hot& d) {
+    TileCursor t;
+    t.ti = w.ti;
+    t.ct = w.ct;
+    t.r0 = w.rt * d.rows_per_tile;
+    t.r1 = min(d.rows, t.r0 + d.rows_per_tile);
+    return t;
+}
+
 template <typename T>
-__global__ void __launch_bounds__(kThreads) factored_stats_kernel(LaunchCommon c) {
-    __shared__ Smem s;
-    for (int i = threadIdx.x; i < kCodewords; i += blockDim.x) s.cb[i] = c.codebook[i];
-    __syncthreads();
+__global__ void __launch_bounds__(kThreads, 2) factored_stats_kernel(LaunchCommon c) {
+    const Smem s = load_tables(c, false);
     const float gs = c.gscale ? *c.gscale : 1.0f;
     const long long T0 = (long long)c.total_tiles * blockIdx.x / gridDim.x;
     const long long T1 = (long long)c.total_tiles * (blockIdx.x + 1) / gridDim.x;
+    if (T0 >= T1) return;
     float csum8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     float csum1[1] = {0};
-    int cur_ti = -1, cur_ct = -1;
+    RunMax run{nullptr, -1, 0.f, 0};
+    Hot d;
+    TileWalk w;
+    walk_begin(c, T0, w, d);
+    run.dst = d.mag_new;
+    run.uniform = warp_uniform_blocks(d, d.vec ? 8 : 1) ? 1 : 0;
     for (long long tile = T0; tile < T1; ++tile) {
-        const TileCursor t = locate(c, (int)tile);
-        if (cur_ti >= 0 && (t.ti != cur_ti || t.ct != cur_ct)) {
-            const TensorDesc& pd = c.descs[cur_ti];
-            if (pd.vec) flush_cols<8>(pd, cur_ct, csum8); else flush_cols<1>(pd, cur_ct, csum1);
-        }
-        cur_ti = t.ti; cur_ct = t.ct;
-        const TensorDesc& d = c.descs[t.ti];
+        const TileCursor t = walk_cursor(w, d);
         if (d.vec) {
-            const bool uni = warp_uniform_blocks(d, 8);
-            if (d.n_src > 1) stats_tile<T, 8, 1>(d, s, t, gs, csum8, uni);
-            else stats_tile<T, 8, 4>(d, s, t, gs, csum8, uni);
+            if (d.n_src > 1) stats_tile<T, 8, 1>(d, s, t, gs, csum8, run);
+            else stats_tile<T, 8, 4>(d, s, t, gs, csum8, run);
         } else {
-            stats_tile<T, 1, 4>(d, s, t, gs, csum1, warp_uniform_blocks(d, 1));
+            stats_tile<T, 1, 4>(d, s, t, gs, csum1, run);
         }
-    }
-    if (cur_ti >= 0) {
-        const TensorDesc& pd = c.descs[cur_ti];
-        if (pd.vec) flush_cols<8>(pd, cur_ct, csum8); else flush_cols<1>(pd, cur_ct, csum1);
+        // advance; flush the column partials when the column tile (or the tensor) changes
+        bool col_change = false, tensor_change = false;
+        if (++w.rt == w.n_row_tiles) {
+            w.rt = 0;
+            col_change = true;
+            if (++w.ct == d.n_col_tiles) { w.ct = 0; tensor_change = true; }
+        }
+        const bool last = tile + 1 == T1;
+        if (col_change || last) {
+            if (!d.row_only) {
+                const int ct_done = col_change ? (tensor_change ? d.n_col_tiles - 1 : w.ct - 1) : w.ct;
+                if (d.vec) flush_cols<8>(d, ct_done, csum8); else flush_cols<1>(d, ct_done, csum1);
+            }
+        }
+        if (tensor_change || last) runmax_flush(run);
+        if (tensor_change && !last) {
+            ++w.ti;
+            d = load_hot(c.descs + w.ti);
+            w.n_row_tiles = (d.rows + d.rows_per_tile - 1) / d.rows_per_tile;
+            run.dst = d.mag_new;
+            run.uniform = warp_uniform_blocks(d, d.vec ? 8 : 1) ? 1 : 0;
+        }
     }
 }
 
@@ -368,6 +490,17 @@ __global__ void __launch_bounds__(kEmaThreads) factored_ema_kernel(LaunchCommon 
     const float inv_cols = 1.0f / (float)d.cols;
     const float inv_rows = 1.0f / (float)d.total_rows;
     const float inv_bc2 = d.scal[1];
+    if (d.row_only) {
+        // block path seen as [nb, period]: one second-moment value per row, no column factor
+        for (int i = threadIdx.x; i < d.rows; i += kEmaThreads) {
+            const float ms = __fmul_rn(d.row_sq[i], inv_cols);
+            const float v = __fadd_rn(__fmul_rn(d.v0[i], d.beta2), __fmul_rn(ms, d.omb2));
+            d.v0[i] = v;
+            d.row_sq[i] = 0.f;
+            d.rfac[i] = __fmul_rn(__fsqrt_rn(v), inv_bc2);   // scal[1] is 1/sqrt(bc2) here
+        }
+        return;
+    }
     // rows: EMA and the sum of the new v_row (fixed order: strided per thread, tree per CTA)
     float part = 0.f;
     for (int i = threadIdx.x; i < d.rows; i += kEmaThreads) {
@@ -424,7 +557,7 @@ __global__ void __launch_bounds__(kEmaThreads) factored_ema_kernel(LaunchCommon 
 }
 
 template <typename T, int VEC, int U>
-__device__ void apply_tile(const TensorDesc& d, const LaunchCommon& c, const Smem& s,
+__device__ void apply_tile(const Hot& d, const LaunchCommon& c, const Smem& s,
                            const TileCursor& t, float gs, const float (&cf)[VEC]) {
     const int tx = threadIdx.x % d.tcols, ty = threadIdx.x / d.tcols;
     const int c0 = (t.ct * d.tcols + tx) * VEC;
@@ -455,12 +588,12 @@ __device__ void apply_tile(const TensorDesc& d, const LaunchCommon& c, const Sme
             const float rf = d.rfac[r];
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
-                float m = ema_momentum(s.cb[ix[u][e]], mo, g[u][e], d.beta1, d.omb1);
+                float m = ema_momentum(rep_load(s.cb, ix[u][e]), mo, g[u][e], d.beta1, d.omb1);
                 int k = quantise(__fmul_rn(m, inv), s, c, off + e);
                 ix[u][e] = k;
                 const float h = __fadd_rn(__fmul_rn(rf, cf[e]), d.eps);
-                const float step = __fmul_rn(__frcp_rn(h), inv_bc1);
-                pf[u][e] = apply_one<T>(pf[u][e], __fmul_rn(s.cb[k], mn), step, lr, wdf);
+                const float step = __fdividef(inv_bc1, h);
+                pf[u][e] = apply_one<T>(pf[u][e], __fmul_rn(rep_load(s.cb, k), mn), step, lr, wdf);
             }
             store_index<VEC>(d.idx + off, ix[u]);
             store_param<T, VEC>(p + off, pf[u]);
@@ -469,34 +602,48 @@ __device__ void apply_tile(const TensorDesc& d, const LaunchCommon& c, const Sme
 }
 
 template <int VEC>
-__device__ __forceinline__ void load_cfac(const TensorDesc& d, int ct, float (&cf)[VEC]) {
+__device__ __forceinline__ void load_cfac(const Hot& d, int ct, float (&cf)[VEC]) {
     const int tx = threadIdx.x % d.tcols;
     const int c0 = (ct * d.tcols + tx) * VEC;
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) cf[e] = (c0 + e < d.cols) ? d.cfac[c0 + e] : 0.f;
+    for (int e = 0; e < VEC; ++e) cf[e] = d.row_only ? 1.0f : ((c0 + e < d.cols) ? d.cfac[c0 + e] : 0.f);
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads) factored_apply_kernel(LaunchCommon c) {
-    __shared__ Smem s;
-    load_tables(s, c);
+__global__ void __launch_bounds__(kThreads, 2) factored_apply_kernel(LaunchCommon c) {
+    const Smem s = load_tables(c, true);
     const float gs = c.gscale ? *c.gscale : 1.0f;
     const long long T0 = (long long)c.total_tiles * blockIdx.x / gridDim.x;
     const long long T1 = (long long)c.total_tiles * (blockIdx.x + 1) / gridDim.x;
+    if (T0 >= T1) return;
     float cf8[8], cf1[1];
-    int cur_ti = -1, cur_ct = -1;
+    Hot d;
+    TileWalk w;
+    walk_begin(c, T0, w, d);
+    bool reload = true;
     for (long long tile = T0; tile < T1; ++tile) {
-        const TileCursor t = locate(c, (int)tile);
-        const TensorDesc& d = c.descs[t.ti];
-        if (t.ti != cur_ti || t.ct != cur_ct) {
-            if (d.vec) load_cfac<8>(d, t.ct, cf8); else load_cfac<1>(d, t.ct, cf1);
-            cur_ti = t.ti; cur_ct = t.ct;
+        if (reload) {
+            if (d.vec) load_cfac<8>(d, w.ct, cf8); else load_cfac<1>(d, w.ct, cf1);
+            reload = false;
         }
+        const TileCursor t = walk_cursor(w, d);
         if (d.vec) {
             if (d.n_src > 1) apply_tile<T, 8, 1>(d, c, s, t, gs, cf8);
             else apply_tile<T, 8, 2>(d, c, s, t, gs, cf8);
         } else {
             apply_tile<T, 1, 2>(d, c, s, t, gs, cf1);
+        }
+        if (++w.rt == w.n_row_tiles) {
+            w.rt = 0;
+            reload = true;
+            if (++w.ct == d.n_col_tiles) {
+                w.ct = 0;
+                if (tile + 1 < T1) {
+                    ++w.ti;
+                    d = load_hot(c.descs + w.ti);
+                    w.n_row_tiles = (d.rows + d.rows_per_tile - 1) / d.rows_per_tile;
+                }
+            }
         }
     }
 }
@@ -599,7 +746,8 @@ cudaError_t launch_block_update(const LaunchCommon& c, int dtype, int sm_count, 
     const int grid = min(c.total_tiles, sm_count * 4);
     return dispatch(dtype, [&](auto* tag) {
         using T = std::remove_pointer_t<decltype(tag)>;
-        block_update_kernel<T><<<grid, kThreads, 0, st>>>(c);
+        cudaFuncSetAttribute(block_update_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemFull);
+        block_update_kernel<T><<<grid, kThreads, kSmemFull, st>>>(c);
         return cudaGetLastError();
     });
 }
@@ -609,7 +757,7 @@ cudaError_t launch_factored_stats(const LaunchCommon& c, int dtype, int sm_count
     const int grid = min(c.total_tiles, sm_count * 4);
     return dispatch(dtype, [&](auto* tag) {
         using T = std::remove_pointer_t<decltype(tag)>;
-        factored_stats_kernel<T><<<grid, kThreads, 0, st>>>(c);
+        factored_stats_kernel<T><<<grid, kThreads, kSmemStats, st>>>(c);
         return cudaGetLastError();
     });
 }
@@ -622,10 +770,11 @@ cudaError_t launch_factored_ema(const LaunchCommon& c, cudaStream_t st) {
 
 cudaError_t launch_factored_apply(const LaunchCommon& c, int dtype, int sm_count, cudaStream_t st) {
     if (c.total_tiles <= 0) return cudaSuccess;
-    const int grid = min(c.total_tiles, sm_count * 3);
+    const int grid = min(c.total_tiles, sm_count * 2);
     return dispatch(dtype, [&](auto* tag) {
         using T = std::remove_pointer_t<decltype(tag)>;
-        factored_apply_kernel<T><<<grid, kThreads, 0, st>>>(c);
+        cudaFuncSetAttribute(factored_apply_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemFull);
+        factored_apply_kernel<T><<<grid, kThreads, kSmemFull, st>>>(c);
         return cudaGetLastError();
     });
 }

@@ -47,7 +47,7 @@ struct alignas(16) TensorDesc {
     int mode;                         // block path: 0 thread/block, 1 warp/block, 2 CTA/block
     int vec;                          // 1: 8-wide vector path allowed, 0: scalar path
     int world, rank;                  // exchange participants (world <= 1: no exchange)
-    uint32_t reserved0;
+    int row_only;                     // 1: second moment per row only (block path as [nb, period])
     float beta1, omb1, beta2, omb2, eps, src_scale;
 };
 
@@ -57,7 +57,8 @@ struct LaunchCommon {
     int n_tensors;
     int total_tiles;
     const float* codebook;            // [256]
-    const uint32_t* lut;              // [4096] packed search table
+    const float* thresholds;          // [256]: midpoints of neighbouring codewords, last = +inf
+    const uint32_t* lut;              // [4096] packed bucket table over the thresholds
     const float* gscale;              // optional device scalar multiplying every gradient
     int* status;                      // device status word (Status enum), may be null
     unsigned long long sr_seed;

@@ -60,7 +60,7 @@ class TensorDesc(ctypes.Structure):
         ("vec", ctypes.c_int),
         ("world", ctypes.c_int),
         ("rank", ctypes.c_int),
-        ("reserved0", ctypes.c_uint32),
+        ("row_only", ctypes.c_int),
         ("beta1", ctypes.c_float),
         ("omb1", ctypes.c_float),
         ("beta2", ctypes.c_float),
@@ -159,6 +159,13 @@ class Item:
     scalars: Tuple[float, float, float, float] = (0.0, 1.0, 1.0, 1.0)
     scal_ptr: int = 0                 # device address of the scalar row (capturable), or 0
     shard: Optional[ShardExchange] = None
+    row_only: bool = False            # block-path tensor run through the two-phase kernels
+
+
+def two_phase_block(period: int, nb: int) -> bool:
+    """Block-path tensors whose blocks are long and few go through the two-phase kernels
+    (many CTAs per block) instead of the one-worker-per-block kernel."""
+    return period >= 1024 and nb < 2048
 
 
 def _aligned(ptr: int, n: int) -> bool:
@@ -189,8 +196,8 @@ class Plan:
         sizes = []
         for it in items:
             if kind == "factored":
-                rows, cols = it.p.shape
                 nb = it.p.numel() // it.period
+                rows, cols = (nb, it.period) if it.row_only else it.p.shape
                 sizes.append((nb, rows, cols, rows, cols))
             else:
                 sizes.append((0, 0, 0, 0, 0))
@@ -233,12 +240,18 @@ class Plan:
             ptr_ok = _aligned(p.data_ptr(), 16) and all(_aligned(s, 16) for s in srcs) and \
                 _aligned(st["m_codebook"].data_ptr(), 8)
             if kind == "factored":
-                rows, cols = p.shape
                 nb, nr, nc, _, _ = sizes[i]
+                rows, cols = nr, nc
                 d.rows, d.cols = rows, cols
-                d.total_rows = it.shard.total_rows if it.shard is not None else rows
-                d.v0 = st["v_row"].data_ptr()
-                d.v1 = st["v_col"].data_ptr()
+                d.row_only = int(it.row_only)
+                if it.row_only:
+                    d.total_rows = rows
+                    d.v0 = st["vmean"].data_ptr()
+                    d.v1 = st["vmean"].data_ptr()
+                else:
+                    d.total_rows = it.shard.total_rows if it.shard is not None else rows
+                    d.v0 = st["v_row"].data_ptr()
+                    d.v1 = st["v_col"].data_ptr()
                 d.mag_new = base + 4 * cursor; cursor += nb
                 d.row_sq = base + 4 * cursor; cursor += nr
                 d.col_sq = base + 4 * cursor; cursor += nc
@@ -263,7 +276,7 @@ class Plan:
                 d.rows_per_tile = d.trows * 8
                 n_row_tiles = (rows + d.rows_per_tile - 1) // d.rows_per_tile
                 tiles = d.n_col_tiles * n_row_tiles
-                sh = it.shard
+                sh = None if it.row_only else it.shard
                 if sh is not None and sh.world > 1:
                     d.world, d.rank = sh.world, sh.rank
                     d.xchg_local = sh.xchg_local
@@ -307,10 +320,10 @@ class Plan:
             st = it.state
             sig.append((it.p.data_ptr(), gp, st["m_codebook"].data_ptr(), st["m_magnitude"].data_ptr(),
                         (st.get("v_row") if "v_row" in st else st["vmean"]).data_ptr(),
-                        it.period, it.scal_ptr, tuple(it.p.shape), it.beta1, it.beta2, it.eps))
+                        it.period, it.scal_ptr, tuple(it.p.shape), it.beta1, it.beta2, it.eps, it.row_only))
         return tuple(sig)
 
-    def run(self, items: List[Item], codebook: torch.Tensor, lut: torch.Tensor, *,
+    def run(self, items: List[Item], codebook: torch.Tensor, thr: torch.Tensor, lut: torch.Tensor, *,
             gscale: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
             sr_seed: Optional[int] = None, wait_iters: int = DEFAULT_WAIT_ITERS,
             phases: int = 7, epoch: int = 0) -> None:
@@ -322,11 +335,11 @@ class Plan:
         code = DTYPE_CODE[self.dtype]
         seed = 0 if sr_seed is None else int(sr_seed)
         if self.kind == "factored":
-            ops().factored_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, lut,
+            ops().factored_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, thr, lut,
                                   gscale, status, code, seed, sr_seed is not None, int(wait_iters),
                                   int(phases), int(epoch) & 0x7FFFFFFF)
         else:
-            ops().block_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, lut,
+            ops().block_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, thr, lut,
                                gscale, status, code, seed, sr_seed is not None)
 
 

@@ -256,6 +256,7 @@ class Gefen(torch.optim.Optimizer):
         self._gefen_codebook: Optional[torch.Tensor] = None
         self._gefen_codebook_by_device: Dict[torch.device, torch.Tensor] = {}
         self._gefen_codebook_lut_by_device: Dict[torch.device, torch.Tensor] = {}
+        self._gefen_thresholds_by_device: Dict[torch.device, torch.Tensor] = {}
         self._gefen_global_step = 0
         self._gefen_global_step_by_device: Dict[torch.device, torch.Tensor] = {}
         self._sr_seed_by_device: Dict[torch.device, torch.Tensor] = {}
@@ -269,6 +270,9 @@ class Gefen(torch.optim.Optimizer):
         self._histogram_reducer = None
         self._external_grad_scale: Optional[torch.Tensor] = None
         self._exchange_epoch = 0
+        self._fast = None
+        self._fused_meta: Dict[Any, list] = {}
+        self._slow_params = 0
         self._plan_cache = None
         self._fused_items: Dict[Any, list] = {}
         self._fused_copyback: list = []
@@ -397,6 +401,7 @@ class Gefen(torch.optim.Optimizer):
             self._synthesized_param_names[p] = s
             self.state[p]["name"] = n
         self._capt.clear()
+        self._fast = None
 
     def _param_name(self, p) -> str:
         n = self._param_names.get(p)
@@ -465,10 +470,19 @@ class Gefen(torch.optim.Optimizer):
             self._gefen_codebook_lut_by_device[device] = lut
         return lut
 
+    def _gefen_thresholds_on(self, device) -> torch.Tensor:
+        device = torch.device(device)
+        thr = self._gefen_thresholds_by_device.get(device)
+        if thr is None:
+            thr = _cbk.padded_thresholds(self._gefen_codebook_on(device))
+            self._gefen_thresholds_by_device[device] = thr
+        return thr
+
     def _set_codebook(self, cb: Optional[torch.Tensor]) -> None:
         self._gefen_codebook = cb
         self._gefen_codebook_by_device.clear()
         self._gefen_codebook_lut_by_device.clear()
+        self._gefen_thresholds_by_device.clear()
 
     def _resolve_automatic_period(self, name: str, p: torch.Tensor, grad: torch.Tensor) -> int:
         if self._force_1d_period_one and p.ndim == 1:
@@ -839,13 +853,16 @@ class Gefen(torch.optim.Optimizer):
                 gsrc = grad.contiguous()
             if factored and work.dim() != 2:
                 raise ValueError("factored update expects a 2-D parameter")
+            row_only = (not factored) and _u.two_phase_block(period, work.numel() // period)
             item = _u.Item(p=work, grad=gsrc, state=state, period=period, beta1=beta1, beta2=beta2,
-                           eps=eps, scalars=host, scal_ptr=scal_ptr, shard=shard)
-            key = ("factored" if factored else "block", dev, work.dtype)
+                           eps=eps, scalars=host, scal_ptr=scal_ptr, shard=shard, row_only=row_only)
+            key = ("factored" if (factored or row_only) else "block", dev, work.dtype)
             self._fused_items.setdefault(key, []).append(item)
+            self._fused_meta.setdefault(key, []).append((p, group, state, vkey, factored))
             return
 
         # decomposed path (CPU, fp64, fused disabled)
+        self._slow_params += 1
         if grad is None:
             grad = src.materialize()
         cb = self._gefen_codebook_on(p_local.device)
@@ -890,11 +907,77 @@ class Gefen(torch.optim.Optimizer):
             lut = self._gefen_codebook_lut_on(dev)
             gscale = self._grad_scale_tensor(dev)
             plan = self._plan_cache.get(kind, items)
-            plan.run(items, cb, lut, gscale=gscale, status=self._status_word(dev),
+            plan.run(items, cb, self._gefen_thresholds_on(dev), lut, gscale=gscale, status=self._status_word(dev),
                      sr_seed=self._kernel_rng_seed() if self._stochastic_round else None,
                      epoch=self._exchange_epoch)
         for dst, work in self._fused_copyback:
             dst.copy_(work)
+
+    # -- steady-state fast path ------------------------------------------------
+    def _grad_identity(self, p):
+        """Cheap identity of the gradient storage of ``p`` (None when it has no gradient)."""
+        if self._grad_source is not None:
+            src = self._grad_source(p)
+            if src is not None:
+                t = getattr(src, "tensor", None)
+                return t.data_ptr() if t is not None else tuple(src.ptrs)
+        g = p.grad
+        if g is None:
+            return None
+        return _local(g).data_ptr()
+
+    def _remember_fast_path(self, active) -> None:
+        """After a step in which every stepping parameter went through the kernels with no
+        staging copies, remember the plans so that the next steps only refresh scalars."""
+        self._fast = None
+        if (self.capturable or self._slow_params or self._fused_copyback or not self._fused_items
+                or self._codebook_refresh_every or self._plan_cache is None):
+            return
+        idents = {}
+        for g in self.param_groups:
+            for p in g["params"]:
+                idents[p] = self._grad_identity(p)
+        plans = []
+        for key, items in self._fused_items.items():
+            plan = self._plan_cache._plans.get(key)
+            if plan is None:
+                return
+            plans.append((key, plan, items, self._fused_meta[key]))
+        self._fast = dict(idents=idents, plans=plans, n_groups=len(self.param_groups),
+                          n_params=sum(len(g["params"]) for g in self.param_groups))
+
+    def _fast_step(self) -> bool:
+        f = self._fast
+        if f["n_groups"] != len(self.param_groups) or self._pending_grad_scale is not None:
+            self._fast = None
+            return False
+        idents = f["idents"]
+        n = 0
+        for g in self.param_groups:
+            for p in g["params"]:
+                n += 1
+                if idents.get(p, 0) != self._grad_identity(p):
+                    self._fast = None
+                    return False
+        if n != f["n_params"]:
+            self._fast = None
+            return False
+        for (kind, dev, _dt), plan, items, metas in f["plans"]:
+            for it, (p, group, state, vkey, factored) in zip(items, metas):
+                state["step"] += 1
+                state[vkey] += 1
+                lr = self._lr_scalar(group)
+                b1, b2 = group["beta1"], group["beta2"]
+                bc1 = 1.0 - b1 ** state["step"]
+                bc2 = 1.0 - b2 ** state[vkey]
+                it.scalars = (lr, (1.0 / bc2) if factored else (1.0 / math.sqrt(bc2)), 1.0 / bc1,
+                              1.0 - lr * group["weight_decay"])
+            plan.run(items, self._gefen_codebook_on(dev), self._gefen_thresholds_on(dev),
+                     self._gefen_codebook_lut_on(dev),
+                     gscale=self._grad_scale_tensor(dev), status=self._status_word(dev),
+                     sr_seed=self._kernel_rng_seed() if self._stochastic_round else None,
+                     epoch=self._exchange_epoch)
+        return True
 
     def _grad_scale_tensor(self, device) -> Optional[torch.Tensor]:
         """Device scalar that multiplies every gradient (AMP unscale and/or clip coefficient)."""
@@ -940,6 +1023,9 @@ class Gefen(torch.optim.Optimizer):
                     and self._gefen_global_step % self._codebook_refresh_every == 0):
                 self._refresh_codebook_with_requant()
 
+            if self._fast is not None and self._fast_step():
+                self._advance_gefen_global_step()
+                return loss
             active = [(g, n, p) for g in self.param_groups
                       for n, p in self._iter_group_params_with_names(g) if self._has_grad(p)]
             if self.capturable:
@@ -955,9 +1041,12 @@ class Gefen(torch.optim.Optimizer):
                     self._capt_refresh(dev, plist)
             self._fused_items = {}
             self._fused_copyback = []
+            self._fused_meta = {}
+            self._slow_params = 0
             for g, n, p in active:
                 self._step_param(g, n, p)
             self._flush_fused()
+            self._remember_fast_path(active)
         finally:
             self._pending_grad_scale = None
             self._fused_items = {}
@@ -1134,6 +1223,7 @@ class Gefen(torch.optim.Optimizer):
         target._gefen_codebook = cb
         target._gefen_codebook_by_device = {}
         target._gefen_codebook_lut_by_device = {}
+        target._gefen_thresholds_by_device = {}
         # torch casts every floating state tensor to the parameter's dtype; put
         # the fp32 moments and uint8 indices back in their saved dtypes.
         id_map = dict(zip(chain.from_iterable(g["params"] for g in sd["param_groups"]),
@@ -1202,11 +1292,14 @@ class Gefen(torch.optim.Optimizer):
         shadow.param_groups = [dict(g, params=list(g["params"])) for g in self.param_groups]
         self._restore_into(shadow, sd, step, cb)
         # publish
+        self._fast = None
+        if self._plan_cache is not None:
+            self._plan_cache.clear()
         self.state = shadow.state
         self.param_groups = shadow.param_groups
         for attr in ("_gefen_global_step", "_gefen_global_step_by_device", "_sr_seed_by_device",
                      "_capt", "_gefen_codebook", "_gefen_codebook_by_device",
-                     "_gefen_codebook_lut_by_device", "_param_names", "_synthesized_param_names"):
+                     "_gefen_codebook_lut_by_device", "_gefen_thresholds_by_device", "_param_names", "_synthesized_param_names"):
             setattr(self, attr, getattr(shadow, attr))
 
     # ------------------------------------------------------------------

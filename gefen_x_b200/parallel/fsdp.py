@@ -268,6 +268,7 @@ class ShardedTrainer:
 
         named = []
         self._param_meta: Dict[torch.Tensor, Tuple[Group, ParamSpec]] = {}
+        self._grad_cache: Dict[torch.Tensor, object] = {}
         for g in self.all_groups:
             for sp in g.specs:
                 rows = sp.shard_rows[self.rank]
@@ -315,9 +316,17 @@ class ShardedTrainer:
 
     def _grad_source(self, p):
         """Gradient of shard ``p``: a local tensor, or the peers' slices to be summed in-kernel."""
+        cached = self._grad_cache.get(p)
+        if cached is not None:
+            return cached
         meta = self._param_meta.get(p)
         if meta is None:
             return None
+        src = self._make_grad_source(p, meta)
+        self._grad_cache[p] = src
+        return src
+
+    def _make_grad_source(self, p, meta):
         g, sp = meta
         rows = sp.shard_rows[self.rank]
         n = rows * sp.cols

@@ -224,8 +224,19 @@ def learn_codebook_from_grad_periods(
 _SEARCH_CHUNK = 1 << 23
 
 
+def decision_thresholds(codebook: torch.Tensor) -> torch.Tensor:
+    """``thr[i] = fp32((cb[i] + cb[i + 1]) * 0.5)`` for the 255 neighbouring pairs."""
+    cb = codebook.detach().float()
+    return (cb[:-1] + cb[1:]) * 0.5
+
+
 def nearest_codebook_indices(codebook: torch.Tensor, normalized: torch.Tensor) -> torch.Tensor:
-    """uint8 index of the nearest codeword; equal distances pick the lower index."""
+    """uint8 index of the nearest codeword: ``#{i : thr[i] < v}`` over the decision
+    thresholds, so a value exactly between two codewords goes to the lower one.
+
+    The reference compares the two fp32 distances instead (``gefen.py:288-335``);
+    the two rules differ only for values within an ulp of a midpoint.
+    """
     if codebook.device != normalized.device:
         raise ValueError(
             "Gefen codebook device {} does not match normalized_vals device {}.".format(
@@ -234,14 +245,12 @@ def nearest_codebook_indices(codebook: torch.Tensor, normalized: torch.Tensor) -
     out = torch.empty(normalized.shape, dtype=torch.uint8, device=normalized.device)
     if k <= 1:
         return out.zero_()
+    thr = decision_thresholds(codebook)
     src = normalized.reshape(-1)
     dst = out.view(-1)
     for s in range(0, src.numel(), _SEARCH_CHUNK):
         v = src[s:s + _SEARCH_CHUNK].float()
-        hi = torch.bucketize(v, codebook).clamp_(max=k - 1)       # first entry >= v
-        lo = (hi - 1).clamp_(min=0)
-        pick_lo = (v - codebook[lo]).abs() <= (v - codebook[hi]).abs()
-        dst[s:s + _SEARCH_CHUNK] = torch.where(pick_lo, lo, hi).to(torch.uint8)
+        dst[s:s + _SEARCH_CHUNK] = torch.bucketize(v, thr).to(torch.uint8)
     return out
 
 
@@ -260,20 +269,26 @@ def dequantize_indices(codebook: torch.Tensor, indices: torch.Tensor,
     return out
 
 
-def codebook_search_lut(codebook: torch.Tensor, buckets: int = LUT_BUCKETS) -> torch.Tensor:
-    """Bucket table that narrows the nearest-codeword search.
-
-    ``lut[b]`` = number of codewords whose bucket ``floor((c + 1) * buckets/2)``
-    is below ``b`` (int16, ``buckets + 1`` entries), so that the insertion point
-    of any value in bucket ``b`` lies in ``[lut[b], lut[b + 1]]``.  It is an
-    accelerator only: the search result is bit-identical with or without it.
-    Same table layout as the reference (``kernels/automatic_gefen_fused.py:81-121``).
-    """
-    cb = codebook.detach().float()
+def _bucket(values: torch.Tensor, buckets: int) -> torch.Tensor:
+    """``floor(fma(x, buckets/2, buckets/2))`` clamped to ``[0, buckets - 1]`` (fp32 fma, as on the device)."""
     half = float(buckets // 2)
-    b = torch.floor((cb + 1.0) * half).clamp_(0, buckets - 1).to(torch.long)
-    hist = torch.bincount(b, minlength=buckets)
-    lut = torch.zeros(buckets + 1, dtype=torch.long, device=cb.device)
+    t = (values.double() * half + half).float()          # exact product and sum, one rounding
+    return t.clamp_(0.0, float(buckets - 1)).floor_().to(torch.long)
+
+
+def codebook_search_lut(codebook: torch.Tensor, buckets: int = LUT_BUCKETS) -> torch.Tensor:
+    """Bucket table that narrows the threshold search.
+
+    ``lut[b]`` = number of decision thresholds whose bucket is below ``b`` (int16,
+    ``buckets + 1`` entries), so the insertion point of any value of bucket ``b``
+    among the thresholds lies in ``[lut[b], lut[b + 1]]``.  It is an accelerator
+    only: the result is identical with or without it.  Same idea as the
+    reference's table (``kernels/automatic_gefen_fused.py:81-121``), built over the
+    thresholds instead of the codewords.
+    """
+    thr = decision_thresholds(codebook)
+    hist = torch.bincount(_bucket(thr, buckets), minlength=buckets)
+    lut = torch.zeros(buckets + 1, dtype=torch.long, device=thr.device)
     lut[1:] = torch.cumsum(hist, 0)
     return lut.to(torch.int16)
 
@@ -282,3 +297,9 @@ def packed_search_lut(codebook: torch.Tensor, buckets: int = LUT_BUCKETS) -> tor
     """The table the kernels load: ``lut[b] | lut[b + 1] << 16`` as int32[buckets]."""
     lut = codebook_search_lut(codebook, buckets).to(torch.int32)
     return (lut[:-1] | (lut[1:] << 16)).contiguous()
+
+
+def padded_thresholds(codebook: torch.Tensor) -> torch.Tensor:
+    """The 255 thresholds followed by ``+inf`` (fp32[256]), the layout the kernels load."""
+    thr = decision_thresholds(codebook)
+    return torch.cat([thr, torch.full((1,), float("inf"), dtype=torch.float32, device=thr.device)]).contiguous()

@@ -150,15 +150,19 @@ def test_search_lut_brackets_every_value():
     torch.manual_seed(2)
     cb = torch.sort(torch.rand(256) * 2 - 1).values
     cb[0], cb[-1] = -1.0, 1.0
+    thr = C.decision_thresholds(cb)
+    assert thr.numel() == 255
     lut = C.codebook_search_lut(cb).long()
-    assert lut.numel() == 4097 and lut[0] == 0 and lut[-1] == 256
-    v = torch.rand(20000) * 2 - 1
-    b = torch.floor((v + 1.0) * 2048).clamp(0, 4095).long()
-    ins = torch.bucketize(v, cb)
+    assert lut.numel() == 4097 and lut[0] == 0 and lut[-1] == 255
+    v = torch.rand(20000) * 2.4 - 1.2
+    b = C._bucket(v, 4096)
+    ins = torch.bucketize(v, thr)                 # the index the search must return
     assert torch.all(ins >= lut[b]) and torch.all(ins <= lut[b + 1])
     packed = C.packed_search_lut(cb)
     assert packed.dtype == torch.int32 and packed.numel() == 4096
     assert torch.equal(packed & 0xFFFF, lut[:-1].int()) and torch.equal(packed >> 16, lut[1:].int())
+    pt = C.padded_thresholds(cb)
+    assert pt.numel() == 256 and torch.isinf(pt[-1]) and torch.equal(pt[:-1], thr)
 
 
 def test_histogram_counts_total_and_symmetry():
