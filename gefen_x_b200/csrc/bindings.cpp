@@ -13,6 +13,7 @@
 #include <torch/library.h>
 
 #include "comm.h"
+#include "gemm_sm100.h"
 #include "model_ops.h"
 #include "quant.h"
 #include "update.h"
@@ -54,8 +55,8 @@ gx::LaunchCommon make_common(const Tensor& descs, const Tensor& tile_start, int6
     TORCH_CHECK(codebook.is_cuda() && codebook.scalar_type() == at::kFloat && codebook.numel() == 256 &&
                     codebook.is_contiguous(),
                 "codebook must be CUDA fp32 [256]");
-    TORCH_CHECK(lut.is_cuda() && lut.scalar_type() == at::kInt && lut.numel() == 4096 && lut.is_contiguous(),
-                "lut must be CUDA int32 [4096]");
+    TORCH_CHECK(lut.is_cuda() && lut.scalar_type() == at::kShort && lut.numel() == 16384 && lut.is_contiguous(),
+                "lut must be CUDA int16 [16384]");
     gx::LaunchCommon c{};
     c.descs = reinterpret_cast<const gx::TensorDesc*>(descs.data_ptr());
     c.tile_start = tile_start.data_ptr<int>();
@@ -65,7 +66,7 @@ gx::LaunchCommon make_common(const Tensor& descs, const Tensor& tile_start, int6
                 "thresholds must be CUDA fp32 [256]");
     c.codebook = codebook.data_ptr<float>();
     c.thresholds = thr.data_ptr<float>();
-    c.lut = reinterpret_cast<const uint32_t*>(lut.data_ptr<int>());
+    c.lut = reinterpret_cast<const uint16_t*>(lut.data_ptr<int16_t>());
     c.gscale = nullptr;
     if (gscale.has_value() && gscale->defined()) {
         TORCH_CHECK(gscale->is_cuda() && gscale->scalar_type() == at::kFloat, "gscale must be CUDA fp32");
@@ -170,6 +171,53 @@ Tensor period_errors(const Tensor& flat, const Tensor& divisors_dev, bool input_
                                    n_div, input_is_squared, partials.data_ptr<double>(), ctas, stream()),
           "period_errors");
     return partials;
+}
+
+// ---------------------------------------------------------------------------
+// tcgen05 GEMM (gemm_sm100.cu)
+// ---------------------------------------------------------------------------
+// c[b] = alpha * op(a[b]) op(b[b]) + beta * d[b]; a is [B, M, K] (or [B, K, M] when a_t),
+// b is [B, N, K] (or [B, K, N] when b_t); 2-D tensors are a batch of one.
+void gemm_bf16(const Tensor& a, const Tensor& b, Tensor c, const c10::optional<Tensor>& d, bool a_t,
+               bool b_t, double alpha, double beta, const c10::optional<Tensor>& status) {
+    c10::cuda::CUDAGuard guard(a.device());
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && c.is_cuda(), "gemm_bf16: CUDA tensors required");
+    TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 &&
+                    c.scalar_type() == at::kBFloat16,
+                "gemm_bf16: bf16 tensors required");
+    TORCH_CHECK(a.dim() == b.dim() && a.dim() == c.dim() && (a.dim() == 2 || a.dim() == 3));
+    const bool batched = a.dim() == 3;
+    auto dimof = [&](const Tensor& t, int i) { return t.size(batched ? i + 1 : i); };
+    auto ldof = [&](const Tensor& t) { return t.stride(batched ? 1 : 0); };
+    auto bsof = [&](const Tensor& t) { return batched ? t.stride(0) : (int64_t)0; };
+    TORCH_CHECK(a.stride(-1) == 1 && b.stride(-1) == 1 && c.stride(-1) == 1, "innermost stride must be 1");
+    gx::GemmParams p{};
+    p.batch = batched ? (int)a.size(0) : 1;
+    p.M = (int)(a_t ? dimof(a, 1) : dimof(a, 0));
+    p.K = (int)(a_t ? dimof(a, 0) : dimof(a, 1));
+    p.N = (int)(b_t ? dimof(b, 1) : dimof(b, 0));
+    TORCH_CHECK((b_t ? dimof(b, 0) : dimof(b, 1)) == p.K, "gemm_bf16: inner dimensions differ");
+    TORCH_CHECK(dimof(c, 0) == p.M && dimof(c, 1) == p.N, "gemm_bf16: bad output shape");
+    TORCH_CHECK(!batched || (b.size(0) == p.batch && c.size(0) == p.batch));
+    p.a_mn_major = a_t ? 1 : 0;
+    p.b_mn_major = b_t ? 1 : 0;
+    p.alpha = (float)alpha;
+    p.beta = (float)beta;
+    p.C = reinterpret_cast<__nv_bfloat16*>(c.data_ptr());
+    p.ldc = ldof(c);
+    p.batch_stride_c = bsof(c);
+    p.D = nullptr;
+    if (d.has_value() && d->defined()) {
+        TORCH_CHECK(d->scalar_type() == at::kBFloat16 && d->sizes() == c.sizes() && d->stride(-1) == 1);
+        p.D = reinterpret_cast<const __nv_bfloat16*>(d->data_ptr());
+        p.ldd = ldof(*d);
+        p.batch_stride_d = bsof(*d);
+    }
+    p.status = (status.has_value() && status->defined()) ? status->data_ptr<int>() : nullptr;
+    check(gx::launch_gemm_bf16(reinterpret_cast<const __nv_bfloat16*>(a.data_ptr()), ldof(a), bsof(a),
+                               reinterpret_cast<const __nv_bfloat16*>(b.data_ptr()), ldof(b), bsof(b), p,
+                               sm_count(), stream()),
+          "gemm_bf16");
 }
 
 // ---------------------------------------------------------------------------
@@ -310,6 +358,8 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("clip_coef(Tensor partials, float max_norm, Tensor(a!) coef) -> ()");
     m.def("histogram(Tensor flat, int period, Tensor(a!) counts) -> ()");
     m.def("period_errors(Tensor flat, Tensor divisors, bool input_is_squared) -> Tensor");
+    m.def("gemm_bf16(Tensor a, Tensor b, Tensor(a!) c, Tensor? d, bool a_t, bool b_t, float alpha, "
+          "float beta, Tensor? status) -> ()");
     m.def("comm_signal(int[] flag_ptrs, int slot, int value, int device_index) -> ()", &comm_signal);
     m.def("comm_wait(Tensor flags, int n, int value, int max_iters, Tensor? status) -> ()");
     m.def("comm_gather(int[] src_base, Tensor segs, int n_segs, Tensor(a!) dst, Tensor unit_prefix, "
@@ -332,6 +382,7 @@ TORCH_LIBRARY_IMPL(gefenx, CUDA, m) {
     m.impl("clip_coef", &clip_coef);
     m.impl("histogram", &histogram);
     m.impl("period_errors", &period_errors);
+    m.impl("gemm_bf16", &gemm_bf16);
     m.impl("comm_wait", &comm_wait);
     m.impl("comm_gather", &comm_gather);
     m.impl("comm_allreduce_scalar", &comm_allreduce_scalar);

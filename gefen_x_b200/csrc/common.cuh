@@ -16,7 +16,7 @@ namespace gx {
 
 constexpr int kMaxSrc = 8;          // gradient sources (peer slices) summed in-kernel
 constexpr int kCodewords = 256;
-constexpr int kLutBuckets = 4096;
+constexpr int kLutBuckets = 16384;
 
 // ---- status word: kernels never trap; they record why they gave up --------
 enum Status : int {
@@ -56,6 +56,29 @@ template <typename T> struct Vec8 {
         *reinterpret_cast<uint4*>(p) = r;
     }
 };
+// bf16: packed conversions (two elements per instruction)
+template <> struct Vec8<__nv_bfloat16> {
+    static __device__ __forceinline__ void unpack(const uint4& r, float (&o)[8]) {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            o[2 * i] = __uint_as_float(w[i] << 16);
+            o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&o)[8]) {
+        unpack(*reinterpret_cast<const uint4*>(p), o);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
 template <> struct Vec8<float> {
     static __device__ __forceinline__ void load(const float* p, float (&o)[8]) {
         float4 a = *reinterpret_cast<const float4*>(p);
@@ -69,6 +92,10 @@ template <> struct Vec8<float> {
     }
 };
 
+__device__ __forceinline__ void unpack_idx8(const uint2& r, int (&o)[8]) {
+    o[0] = r.x & 0xff; o[1] = (r.x >> 8) & 0xff; o[2] = (r.x >> 16) & 0xff; o[3] = r.x >> 24;
+    o[4] = r.y & 0xff; o[5] = (r.y >> 8) & 0xff; o[6] = (r.y >> 16) & 0xff; o[7] = r.y >> 24;
+}
 __device__ __forceinline__ void load_idx8(const uint8_t* p, int (&o)[8]) {
     uint2 r = *reinterpret_cast<const uint2*>(p);
     o[0] = r.x & 0xff; o[1] = (r.x >> 8) & 0xff; o[2] = (r.x >> 16) & 0xff; o[3] = r.x >> 24;
@@ -81,22 +108,70 @@ __device__ __forceinline__ void store_idx8(uint8_t* p, const int (&v)[8]) {
     *reinterpret_cast<uint2*>(p) = r;
 }
 
+// Raw (unconverted) chunk of VEC elements: loaded early to keep many requests in
+// flight at a low register cost, converted to fp32 only when consumed.
+template <typename T, int VEC> struct RawVec {
+    static constexpr int kWords = (VEC == 8) ? (int)(sizeof(T) * 2) : 1;
+    uint32_t w[kWords];
+    __device__ __forceinline__ void load(const T* p) {
+        if constexpr (VEC == 8) {
+            const uint4* q = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+            for (int i = 0; i < kWords / 4; ++i) {
+                const uint4 r = q[i];
+                w[4 * i] = r.x; w[4 * i + 1] = r.y; w[4 * i + 2] = r.z; w[4 * i + 3] = r.w;
+            }
+        } else {
+            w[0] = __float_as_uint(to_f<T>(p[0]));
+        }
+    }
+    __device__ __forceinline__ void get(float (&o)[VEC]) const {
+        if constexpr (VEC == 8) {
+            if constexpr (sizeof(T) == 4) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(w[i]);
+            } else {
+                const T* e = reinterpret_cast<const T*>(w);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = to_f<T>(e[i]);
+            }
+        } else {
+            o[0] = __uint_as_float(w[0]);
+        }
+    }
+};
+template <int VEC> struct RawIdx {
+    uint32_t w[(VEC == 8) ? 2 : 1];
+    __device__ __forceinline__ void load(const uint8_t* p) {
+        if constexpr (VEC == 8) {
+            const uint2 r = *reinterpret_cast<const uint2*>(p);
+            w[0] = r.x; w[1] = r.y;
+        } else {
+            w[0] = p[0];
+        }
+    }
+    __device__ __forceinline__ void get(int (&o)[VEC]) const {
+        if constexpr (VEC == 8) unpack_idx8(make_uint2(w[0], w[1]), o);
+        else o[0] = (int)w[0];
+    }
+};
+
 // ---- codebook search --------------------------------------------------------
 // The nearest codeword of v is found with the 255 decision thresholds
 // thr[i] = fp32((cb[i] + cb[i + 1]) / 2):  index = #{ i : thr[i] < v }, so a value on
-// a threshold goes to the lower codeword.  A 4096-bucket table narrows the
-// search: lut[b] packs (number of thresholds in lower buckets) | (the same for
-// the next bucket) << 16, with bucket(x) = floor(fma(x, 2048, 2048)) clamped to
-// [0, 4095].  Most buckets hold no threshold, so the common case is one table
-// load and no compare.  NaN maps to index 0.
+// a threshold goes to the lower codeword.  A 16384-bucket table resolves almost
+// every value with one load: lut[b] = (thresholds in lower buckets) | (thresholds
+// inside bucket b) << 8, with bucket(x) = floor(fma(x, 8192, 8192)) clamped to
+// [0, 16383]; only values whose bucket holds a threshold compare against it.
+// NaN maps to index 0.
 //
-// Shared-memory tables are replicated per lane (entry i of lane l at
-// [i * 32 + l]) so that the data-dependent loads of a warp never collide on a
-// bank.
+// The codebook itself is replicated per lane in shared memory (entry i of lane l at
+// [i * 32 + l]) so that the two data-dependent codeword loads per element never
+// collide on a bank.
 struct QuantTables {
     const float* cb;          // [256 * 32] lane-replicated codebook
-    const float* thr;         // [256 * 32] lane-replicated thresholds (entry 255 = +inf)
-    const uint32_t* lut;      // [4096]
+    const float* thr;         // [256] thresholds (entry 255 = +inf)
+    const uint16_t* lut;      // [16384]
 };
 
 __device__ __forceinline__ float rep_load(const float* t, int i) {
@@ -111,9 +186,15 @@ __device__ __forceinline__ int lut_bucket(float v) {
 
 __device__ __forceinline__ int nearest_index(float v, const QuantTables& q) {
     const uint32_t e = q.lut[lut_bucket(v)];
-    int i = (int)(e & 0xffffu);
-    const int hi = (int)(e >> 16);
-    while (i < hi && rep_load(q.thr, i) < v) ++i;
+    int i = (int)(e & 0xffu);
+    const int cnt = (int)(e >> 8);
+    if (cnt) {
+        const int hi = i + cnt;
+        do {
+            if (!(q.thr[i] < v)) break;
+            ++i;
+        } while (i < hi);
+    }
     return i;
 }
 

@@ -1,0 +1,411 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), TMA-fed.
+//
+//   C[b] = alpha * op(A[b]) * op(B[b]) + beta * D[b]        (fp32 accumulate, bf16 out)
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer: cp.async.bulk.tensor (no multicast) into a 4-stage ring of
+//               128B-swizzled shared-memory tiles, completion on mbarriers
+//   warp 1      MMA issuer: one elected lane issues tcgen05.mma (cta_group::1,
+//               kind::f16, M=128, N=BN, K=16) reading shared-memory descriptors and
+//               accumulating into one of two TMEM buffers; tcgen05.commit frees the
+//               stage / publishes the accumulator
+//   warps 2-5   epilogue: tcgen05.ld (32x32b.x32) the finished accumulator, scale, add
+//               beta * D, convert and store, while the MMA warp already works on the
+//               next tile in the other TMEM buffer
+//
+// Operands may be K-major (row-major [rows, K]) or MN-major (row-major [K, rows]),
+// which gives the NT / NN / TN products used by the Newton-Schulz chain
+// (reference src/gefen/gefen_muon.py:278-287 calls cuBLAS through torch.addmm for
+// these) and by the all-gather-fused projection.  Every mbarrier wait is bounded:
+// on time-out the kernel raises an abort flag, records kWaitTimeout in the status
+// word, drains, frees its TMEM and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+#include "gemm_sm100.h"
+
+namespace gx {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kGemmThreads = 192;      // 6 warps
+constexpr uint32_t kTmemCols = 512;
+constexpr long long kSpinLimit = 1ll << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// ---- mbarrier ---------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the budget ran out or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (long long it = 0; it < kSpinLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 1023) == 1023 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+// ---- TMA ----------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// ---- tcgen05 ----------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(smem_dst)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2, descriptor version 1).
+//   K-major tile : rows of 128 B (64 bf16 along K), 8-row groups 1024 B apart (SBO).
+//   MN-major tile: rows of 128 B (64 bf16 along M/N) indexed by K, 8-row groups 1024 B
+//                  apart (SBO); the next 64 elements along M/N start LBO bytes further.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;          // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;          // SWIZZLE_128B
+    return d;
+}
+
+struct SharedStorage {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 GemmParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // carve: [stages x A tile][stages x B tile][barriers]
+    constexpr uint32_t kABytes = BM * BK * 2;
+    constexpr uint32_t kBBytes = BN * BK * 2;
+    unsigned char* base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* smA = base;
+    unsigned char* smB = base + kStages * kABytes;
+    SharedStorage* ss = reinterpret_cast<SharedStorage*>(smB + kStages * kBBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    volatile int* abort_flag = &ss->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kStages; ++i) { mbar_init(&ss->full[i], 1); mbar_init(&ss->empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&ss->tmem_full[i], 1); mbar_init(&ss->tmem_empty[i], 4); }
+        ss->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+    }
+    if (warp == 1) tmem_alloc(&ss->tmem_base, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ss->tmem_base;
+
+    const int k_blocks = (p.K + BK - 1) / BK;
+    const int tiles_per_batch = p.m_tiles * p.n_tiles;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+                const int b = tile / tiles_per_batch;
+                const int t = tile - b * tiles_per_batch;
+                const int m0 = (t % p.m_tiles) * BM;
+                const int n0 = (t / p.m_tiles) * BN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&ss->empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(&ss->full[stage], kABytes + kBBytes);
+                    unsigned char* a_dst = smA + stage * kABytes;
+                    unsigned char* b_dst = smB + stage * kBBytes;
+                    const int k0 = kb * BK;
+                    if (!p.a_mn_major) {
+                        tma_load_3d(a_dst, &tmA, &ss->full[stage], k0, m0, b);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BM / 64; ++j)
+                            tma_load_3d(a_dst + j * (BK * 128), &tmA, &ss->full[stage], m0 + 64 * j, k0, b);
+                    }
+                    if (!p.b_mn_major) {
+                        tma_load_3d(b_dst, &tmB, &ss->full[stage], k0, n0, b);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_3d(b_dst + j * (BK * 128), &tmB, &ss->full[stage], n0 + 64 * j, k0, b);
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer --------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                   ((uint32_t)(p.a_mn_major ? 1 : 0) << 15) |
+                                   ((uint32_t)(p.b_mn_major ? 1 : 0) << 16) |
+                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(&ss->tmem_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&ss->full[stage], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smA + stage * kABytes);
+                    const uint32_t b_addr = smem_u32(smB + stage * kBBytes);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t ad = p.a_mn_major
+                            ? make_desc(a_addr + k * (UMMA_K * 128), BK * 128, 1024)
+                            : make_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
+                        const uint64_t bd = p.b_mn_major
+                            ? make_desc(b_addr + k * (UMMA_K * 128), BK * 128, 1024)
+                            : make_desc(b_addr + k * (UMMA_K * 2), 16, 1024);
+                        umma_bf16(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&ss->empty[stage]);            // stage reusable once these MMAs retire
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(&ss->tmem_full[acc]);              // accumulator complete
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        // --------------------------------- epilogue ----------------------------------
+        const int q = warp & 3;                                // TMEM lane quadrant of this warp
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+            const int b = tile / tiles_per_batch;
+            const int t = tile - b * tiles_per_batch;
+            const int m0 = (t % p.m_tiles) * BM;
+            const int n0 = (t / p.m_tiles) * BN;
+            if (!mbar_wait(&ss->tmem_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            __nv_bfloat16* crow = p.C + (long long)b * p.batch_stride_c + (long long)row * p.ldc;
+            const __nv_bfloat16* drow =
+                p.D ? p.D + (long long)b * p.batch_stride_d + (long long)row * p.ldd : nullptr;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c), r);
+                tmem_ld_wait();
+                const int col0 = n0 + c;
+                if (row < p.M && col0 < p.N) {
+#pragma unroll
+                    for (int v8 = 0; v8 < 4; ++v8) {
+                        const int col = col0 + v8 * 8;
+                        float f[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v8 * 8 + e]) * p.alpha;
+                        if (col + 8 <= p.N && p.vec_ok) {
+                            if (drow) {
+                                float dd[8];
+                                Vec8<__nv_bfloat16>::load(drow + col, dd);
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) f[e] += p.beta * dd[e];
+                            }
+                            Vec8<__nv_bfloat16>::store(crow + col, f);
+                        } else {
+                            for (int e = 0; e < 8; ++e) {
+                                if (col + e < p.N) {
+                                    float v = f[e];
+                                    if (drow) v += p.beta * __bfloat162float(drow[col + e]);
+                                    crow[col + e] = __float2bfloat16_rn(v);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ss->tmem_empty[acc]);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+
+    // teardown: everybody meets, the allocating warp frees TMEM
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && ss->abort_flag && p.status) atomicExch(p.status, (int)kWaitTimeout);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// Operand stored row-major [batch, outer, inner] with leading dimension ld (elements).
+bool make_map(CUtensorMap* map, const __nv_bfloat16* base, long long inner, long long outer, long long batch,
+              long long ld, long long batch_stride, int box_inner, int box_outer) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    if (batch_stride <= 0) batch_stride = outer * ld;
+    cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)batch};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)batch_stride * 2};
+    cuuint32_t box[3] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<__nv_bfloat16*>(base), dims, strides,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <int BN>
+cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, int sm_count,
+                      cudaStream_t st) {
+    constexpr size_t smem = (size_t)kStages * (BM * BK * 2 + BN * BK * 2) + sizeof(SharedStorage) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return e;
+    p.m_tiles = (p.M + BM - 1) / BM;
+    p.n_tiles = (p.N + BN - 1) / BN;
+    p.total_tiles = p.m_tiles * p.n_tiles * p.batch;
+    const int grid = p.total_tiles < sm_count ? p.total_tiles : sm_count;
+    gemm_bf16_kernel<BN><<<grid, kGemmThreads, smem, st>>>(ta, tb, p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_gemm_bf16(const __nv_bfloat16* A, long long lda, long long batch_stride_a,
+                             const __nv_bfloat16* B, long long ldb, long long batch_stride_b,
+                             GemmParams p, int sm_count, cudaStream_t st) {
+    if (p.M <= 0 || p.N <= 0 || p.K <= 0 || p.batch <= 0) return cudaSuccess;
+    if ((lda % 8) || (ldb % 8) || (batch_stride_a % 8) || (batch_stride_b % 8)) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(B) % 16)) return cudaErrorInvalidValue;
+    const long long tiles256 = (long long)((p.M + BM - 1) / BM) * ((p.N + 255) / 256) * p.batch;
+    const bool use128 = p.N <= 128 || tiles256 < sm_count;
+    const int bn = use128 ? 128 : 256;
+    CUtensorMap ta, tb;
+    bool ok = p.a_mn_major ? make_map(&ta, A, p.M, p.K, p.batch, lda, batch_stride_a, 64, BK)
+                           : make_map(&ta, A, p.K, p.M, p.batch, lda, batch_stride_a, BK, BM);
+    ok = ok && (p.b_mn_major ? make_map(&tb, B, p.N, p.K, p.batch, ldb, batch_stride_b, 64, BK)
+                             : make_map(&tb, B, p.K, p.N, p.batch, ldb, batch_stride_b, BK, bn));
+    if (!ok) return cudaErrorInvalidValue;
+    p.vec_ok = (p.ldc % 8 == 0) && (reinterpret_cast<uintptr_t>(p.C) % 16 == 0) && (p.batch_stride_c % 8 == 0) &&
+               (!p.D || ((p.ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(p.D) % 16 == 0) &&
+                         (p.batch_stride_d % 8 == 0)));
+    return use128 ? launch_bn<128>(ta, tb, p, sm_count, st) : launch_bn<256>(ta, tb, p, sm_count, st);
+}
+
+}  // namespace gx

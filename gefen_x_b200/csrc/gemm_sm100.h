@@ -1,0 +1,28 @@
+// Host-visible declarations of the tcgen05 / TMEM bf16 GEMM (gemm_sm100.cu).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace gx {
+
+struct GemmParams {
+    int M, N, K, batch;
+    int a_mn_major, b_mn_major;     // 0: operand stored [rows, K]; 1: stored [K, rows]
+    float alpha, beta;
+    __nv_bfloat16* C;
+    const __nv_bfloat16* D;         // optional addend (may be null)
+    long long ldc, ldd, batch_stride_c, batch_stride_d;
+    int* status;                    // device status word, may be null
+    int m_tiles, n_tiles, total_tiles;
+    int vec_ok;                     // rows of C / D are 16-byte aligned
+};
+
+// C[b] = alpha * op(A[b]) op(B[b]) + beta * D[b], bf16 in/out, fp32 accumulate.
+// A: a_mn_major ? [batch, K, M] : [batch, M, K] with leading dimension lda (elements), etc.
+// All leading dimensions and batch strides must be multiples of 8 elements and the base
+// pointers 16-byte aligned (TMA requirements).  Returns cudaErrorInvalidValue otherwise.
+cudaError_t launch_gemm_bf16(const __nv_bfloat16* A, long long lda, long long batch_stride_a,
+                             const __nv_bfloat16* B, long long ldb, long long batch_stride_b,
+                             GemmParams p, int sm_count, cudaStream_t st);
+
+}  // namespace gx

@@ -32,19 +32,17 @@ namespace {
 
 constexpr int kThreads = 256;
 
-// Dynamic shared memory of a CTA: lane-replicated codebook (and, for kernels that
-// requantise, thresholds + bucket table) followed by a small reduction scratch.
+// Dynamic shared memory of a CTA: reduction scratch, lane-replicated codebook and, for
+// kernels that requantise, the thresholds and the bucket table.
 struct Smem {
     float* cb;         // [256 * 32]
-    float* thr;        // [256 * 32] or null
-    uint32_t* lut;     // [4096] or null
     float* red;        // [16]
     QuantTables q;
 };
 
 constexpr int kRepFloats = kCodewords * 32;
 constexpr size_t kSmemStats = (size_t)(kRepFloats + 16) * sizeof(float);
-constexpr size_t kSmemFull = (size_t)(2 * kRepFloats + kLutBuckets + 16) * sizeof(float);
+constexpr size_t kSmemFull = kSmemStats + kCodewords * sizeof(float) + kLutBuckets * sizeof(uint16_t);
 
 extern __shared__ __align__(16) unsigned char gx_smem_raw[];
 
@@ -53,16 +51,18 @@ __device__ __forceinline__ Smem load_tables(const LaunchCommon& c, bool full) {
     float* base = reinterpret_cast<float*>(gx_smem_raw);
     s.red = base;
     s.cb = base + 16;
-    s.thr = full ? s.cb + kRepFloats : nullptr;
-    s.lut = full ? reinterpret_cast<uint32_t*>(s.thr + kRepFloats) : nullptr;
+    float* thr = s.cb + kRepFloats;
+    uint16_t* lut = reinterpret_cast<uint16_t*>(thr + kCodewords);
     for (int i = threadIdx.x; i < kRepFloats; i += blockDim.x) s.cb[i] = c.codebook[i >> 5];
     if (full) {
-        for (int i = threadIdx.x; i < kRepFloats; i += blockDim.x) s.thr[i] = c.thresholds[i >> 5];
-        for (int i = threadIdx.x; i < kLutBuckets; i += blockDim.x) s.lut[i] = c.lut[i];
+        for (int i = threadIdx.x; i < kCodewords; i += blockDim.x) thr[i] = c.thresholds[i];
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(c.lut);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(lut);
+        for (int i = threadIdx.x; i < kLutBuckets / 2; i += blockDim.x) dst[i] = src[i];
     }
     s.q.cb = s.cb;
-    s.q.thr = s.thr;
-    s.q.lut = s.lut;
+    s.q.thr = full ? thr : nullptr;
+    s.q.lut = full ? lut : nullptr;
     __syncthreads();
     return s;
 }
@@ -92,6 +92,7 @@ struct Hot {
     const float* cfac;
     const float* scal;
     int rows, cols, period, n_src, blk_mode, tcols, trows, n_col_tiles, rows_per_tile, vec, row_only;
+    int small;                // numel < 2^31: 32-bit index arithmetic
     float beta1, omb1, eps, src_scale;
 };
 
@@ -102,6 +103,7 @@ __device__ __forceinline__ Hot load_hot(const TensorDesc* t) {
     h.rows = t->rows; h.cols = t->cols; h.period = t->period; h.n_src = t->n_src;
     h.blk_mode = t->blk_mode; h.tcols = t->tcols; h.trows = t->trows; h.n_col_tiles = t->n_col_tiles;
     h.rows_per_tile = t->rows_per_tile; h.vec = t->vec; h.row_only = t->row_only;
+    h.small = t->numel < 2147483647LL ? 1 : 0;
     h.beta1 = t->beta1; h.omb1 = t->omb1; h.eps = t->eps; h.src_scale = t->src_scale;
     return h;
 }
@@ -276,7 +278,9 @@ __device__ __forceinline__ long long block_of(const Hot& d, int r, int c0) {
         case 0: return r;
         case 1: return (long long)r * (d.cols / d.period) + c0 / d.period;
         case 2: return r / (d.period / d.cols);
-        default: return ((long long)r * d.cols + c0) / d.period;
+        default:
+            if (d.small) return (long long)(((unsigned)r * (unsigned)d.cols + (unsigned)c0) / (unsigned)d.period);
+            return ((long long)r * d.cols + c0) / d.period;
     }
 }
 
@@ -327,16 +331,20 @@ __device__ void stats_tile(const Hot& d, const Smem& s, const TileCursor& t, flo
     const int c0 = (t.ct * d.tcols + tx) * VEC;
     const bool act = c0 < d.cols;
     const bool uniform = run.uniform != 0;
+    const bool multi = d.n_src > 1;
+    const T* g0 = reinterpret_cast<const T*>(d.g0);
     for (int rb = t.r0 + ty; rb < t.r1; rb += d.trows * U) {
-        float g[U][VEC];
-        int ix[U][VEC];
+        RawVec<T, VEC> rg[U];
+        RawIdx<VEC> ri[U];
+        if (!multi) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int r = rb + u * d.trows;
-            if (act && r < t.r1) {
-                const long long off = (long long)r * d.cols + c0;
-                load_grad<T, VEC>(d, off, gs, g[u]);
-                load_index<VEC>(d.idx + off, ix[u]);
+            for (int u = 0; u < U; ++u) {
+                const int r = rb + u * d.trows;
+                if (act && r < t.r1) {
+                    const long long off = (long long)r * d.cols + c0;
+                    rg[u].load(g0 + off);
+                    ri[u].load(d.idx + off);
+                }
             }
         }
 #pragma unroll
@@ -346,13 +354,25 @@ __device__ void stats_tile(const Hot& d, const Smem& s, const TileCursor& t, flo
             float amax = 0.f, rs = 0.f;
             long long blk = -1;
             if (act) {
+                float g[VEC];
+                int ix[VEC];
+                if (multi) {
+                    const long long off = (long long)r * d.cols + c0;
+                    load_grad<T, VEC>(d, off, gs, g);
+                    load_index<VEC>(d.idx + off, ix);
+                } else {
+                    rg[u].get(g);
+                    ri[u].get(ix);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) g[e] = __fmul_rn(g[e], gs);
+                }
                 blk = block_of(d, r, c0);
                 const float mo = d.mag[blk];
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) {
-                    float m = ema_momentum(rep_load(s.cb, ix[u][e]), mo, g[u][e], d.beta1, d.omb1);
+                    float m = ema_momentum(rep_load(s.cb, ix[e]), mo, g[e], d.beta1, d.omb1);
                     amax = fmaxf(amax, fabsf(m));
-                    const float sq = g[u][e] * g[u][e];
+                    const float sq = g[e] * g[e];
                     rs += sq;
                     csum[e] += sq;
                 }
@@ -438,7 +458,7 @@ __global__ void __launch_bounds__(kThreads, 2) factored_stats_kernel(LaunchCommo
         const TileCursor t = walk_cursor(w, d);
         if (d.vec) {
             if (d.n_src > 1) stats_tile<T, 8, 1>(d, s, t, gs, csum8, run);
-            else stats_tile<T, 8, 4>(d, s, t, gs, csum8, run);
+            else stats_tile<T, 8, 8>(d, s, t, gs, csum8, run);
         } else {
             stats_tile<T, 1, 4>(d, s, t, gs, csum1, run);
         }
@@ -563,18 +583,20 @@ __device__ void apply_tile(const Hot& d, const LaunchCommon& c, const Smem& s,
     const int c0 = (t.ct * d.tcols + tx) * VEC;
     if (c0 >= d.cols) return;
     const float lr = d.scal[0], inv_bc1 = d.scal[2], wdf = d.scal[3];
+    const bool multi = d.n_src > 1;
     T* p = reinterpret_cast<T*>(d.p);
+    const T* g0 = reinterpret_cast<const T*>(d.g0);
     for (int rb = t.r0 + ty; rb < t.r1; rb += d.trows * U) {
-        float g[U][VEC], pf[U][VEC];
-        int ix[U][VEC];
+        RawVec<T, VEC> rg[U], rp[U];
+        RawIdx<VEC> ri[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int r = rb + u * d.trows;
             if (r < t.r1) {
                 const long long off = (long long)r * d.cols + c0;
-                load_grad<T, VEC>(d, off, gs, g[u]);
-                load_index<VEC>(d.idx + off, ix[u]);
-                load_param<T, VEC>(p + off, pf[u]);
+                if (!multi) rg[u].load(g0 + off);
+                ri[u].load(d.idx + off);
+                rp[u].load(p + off);
             }
         }
 #pragma unroll
@@ -582,21 +604,32 @@ __device__ void apply_tile(const Hot& d, const LaunchCommon& c, const Smem& s,
             const int r = rb + u * d.trows;
             if (r >= t.r1) break;
             const long long off = (long long)r * d.cols + c0;
+            float g[VEC], pf[VEC];
+            int ix[VEC];
+            if (multi) {
+                load_grad<T, VEC>(d, off, gs, g);
+            } else {
+                rg[u].get(g);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) g[e] = __fmul_rn(g[e], gs);
+            }
+            ri[u].get(ix);
+            rp[u].get(pf);
             const long long blk = block_of(d, r, c0);
             const float mo = d.mag[blk], mn = d.mag_new[blk];
             const float inv = mn > 0.f ? __frcp_rn(mn) : 0.f;
             const float rf = d.rfac[r];
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
-                float m = ema_momentum(rep_load(s.cb, ix[u][e]), mo, g[u][e], d.beta1, d.omb1);
+                float m = ema_momentum(rep_load(s.cb, ix[e]), mo, g[e], d.beta1, d.omb1);
                 int k = quantise(__fmul_rn(m, inv), s, c, off + e);
-                ix[u][e] = k;
+                ix[e] = k;
                 const float h = __fadd_rn(__fmul_rn(rf, cf[e]), d.eps);
                 const float step = __fdividef(inv_bc1, h);
-                pf[u][e] = apply_one<T>(pf[u][e], __fmul_rn(rep_load(s.cb, k), mn), step, lr, wdf);
+                pf[e] = apply_one<T>(pf[e], __fmul_rn(rep_load(s.cb, k), mn), step, lr, wdf);
             }
-            store_index<VEC>(d.idx + off, ix[u]);
-            store_param<T, VEC>(p + off, pf[u]);
+            store_index<VEC>(d.idx + off, ix);
+            store_param<T, VEC>(p + off, pf);
         }
     }
 }
@@ -629,7 +662,7 @@ __global__ void __launch_bounds__(kThreads, 2) factored_apply_kernel(LaunchCommo
         const TileCursor t = walk_cursor(w, d);
         if (d.vec) {
             if (d.n_src > 1) apply_tile<T, 8, 1>(d, c, s, t, gs, cf8);
-            else apply_tile<T, 8, 2>(d, c, s, t, gs, cf8);
+            else apply_tile<T, 8, 4>(d, c, s, t, gs, cf8);
         } else {
             apply_tile<T, 1, 2>(d, c, s, t, gs, cf1);
         }

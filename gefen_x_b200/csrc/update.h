@@ -58,7 +58,7 @@ struct LaunchCommon {
     int total_tiles;
     const float* codebook;            // [256]
     const float* thresholds;          // [256]: midpoints of neighbouring codewords, last = +inf
-    const uint32_t* lut;              // [4096] packed bucket table over the thresholds
+    const uint16_t* lut;              // [16384] bucket table over the thresholds (count below | count inside << 8)
     const float* gscale;              // optional device scalar multiplying every gradient
     int* status;                      // device status word (Status enum), may be null
     unsigned long long sr_seed;

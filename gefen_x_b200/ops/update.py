@@ -273,7 +273,7 @@ class Plan:
                 d.tcols = _pick_tcols(chunks)
                 d.trows = _THREADS // d.tcols
                 d.n_col_tiles = (chunks + d.tcols - 1) // d.tcols
-                d.rows_per_tile = d.trows * 8
+                d.rows_per_tile = d.trows * 16
                 n_row_tiles = (rows + d.rows_per_tile - 1) // d.rows_per_tile
                 tiles = d.n_col_tiles * n_row_tiles
                 sh = None if it.row_only else it.shard

@@ -22,7 +22,7 @@ import torch
 
 NUM_CODEWORDS = 256
 HISTOGRAM_BINS = NUM_CODEWORDS * 16
-LUT_BUCKETS = 4096
+LUT_BUCKETS = 16384
 
 
 # --------------------------------------------------------------------------
@@ -294,9 +294,12 @@ def codebook_search_lut(codebook: torch.Tensor, buckets: int = LUT_BUCKETS) -> t
 
 
 def packed_search_lut(codebook: torch.Tensor, buckets: int = LUT_BUCKETS) -> torch.Tensor:
-    """The table the kernels load: ``lut[b] | lut[b + 1] << 16`` as int32[buckets]."""
+    """The table the kernels load: ``lut[b] | (lut[b + 1] - lut[b]) << 8`` as int16[buckets]
+    (bit pattern of an unsigned 16-bit value: thresholds below the bucket, thresholds inside it)."""
     lut = codebook_search_lut(codebook, buckets).to(torch.int32)
-    return (lut[:-1] | (lut[1:] << 16)).contiguous()
+    packed = lut[:-1] | ((lut[1:] - lut[:-1]) << 8)
+    packed = torch.where(packed >= 32768, packed - 65536, packed)
+    return packed.to(torch.int16).contiguous()
 
 
 def padded_thresholds(codebook: torch.Tensor) -> torch.Tensor:

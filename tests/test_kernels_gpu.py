@@ -258,3 +258,42 @@ def test_sharded_trainer_single_gpu_tracks_cpu_fp32():
     assert lg[-1] < lg[0] - 0.5
     assert abs(lc[-1] - lg[-1]) / lc[-1] < 0.12, (lc, lg)   # bf16 vs fp32 after 20 steps
     assert gpu.state_bytes_per_param() < 1.1
+
+
+@pytest.mark.parametrize("m,n,k,a_t,b_t", [
+    (256, 512, 128, False, False), (128, 256, 64, False, False), (300, 264, 200, False, False),
+    (2048, 6144, 2560, False, False), (256, 512, 128, False, True), (256, 512, 128, True, False),
+    (256, 512, 128, True, True), (1024, 1024, 4096, False, True), (520, 136, 328, True, True),
+])
+def test_tcgen05_gemm_matches_fp32(m, n, k, a_t, b_t):
+    from gefen_x_b200.ops import tcgemm
+
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn((k, m) if a_t else (m, k), generator=g).bfloat16().to(_dev())
+    b = torch.randn((k, n) if b_t else (n, k), generator=g).bfloat16().to(_dev())
+    d = torch.randn(m, n, generator=g).bfloat16().to(_dev())
+    af = a.float().t() if a_t else a.float()
+    bf = b.float() if b_t else b.float().t()
+    ref = af @ bf
+    out = tcgemm.gemm(a, b, a_t=a_t, b_t=b_t)
+    torch.cuda.synchronize()
+    assert int(tcgemm.status_word(_dev()).item()) == 0
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item() + 1e-2, err
+    out2 = tcgemm.gemm(a, b, a_t=a_t, b_t=b_t, alpha=0.5, beta=-2.0, d=d)
+    ref2 = 0.5 * ref - 2.0 * d.float()
+    err2 = (out2.float() - ref2).abs().max().item()
+    assert err2 <= 2e-2 * ref2.abs().max().item() + 1e-2, err2
+
+
+def test_tcgen05_gemm_batched():
+    from gefen_x_b200.ops import tcgemm
+
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn(5, 192, 320, generator=g).bfloat16().to(_dev())
+    b = torch.randn(5, 136, 320, generator=g).bfloat16().to(_dev())
+    out = tcgemm.gemm(a, b)
+    ref = torch.bmm(a.float(), b.float().transpose(1, 2))
+    torch.cuda.synchronize()
+    assert int(tcgemm.status_word(_dev()).item()) == 0
+    assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2

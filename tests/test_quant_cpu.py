@@ -153,14 +153,15 @@ def test_search_lut_brackets_every_value():
     thr = C.decision_thresholds(cb)
     assert thr.numel() == 255
     lut = C.codebook_search_lut(cb).long()
-    assert lut.numel() == 4097 and lut[0] == 0 and lut[-1] == 255
+    assert lut.numel() == C.LUT_BUCKETS + 1 and lut[0] == 0 and lut[-1] == 255
     v = torch.rand(20000) * 2.4 - 1.2
-    b = C._bucket(v, 4096)
+    b = C._bucket(v, C.LUT_BUCKETS)
     ins = torch.bucketize(v, thr)                 # the index the search must return
     assert torch.all(ins >= lut[b]) and torch.all(ins <= lut[b + 1])
     packed = C.packed_search_lut(cb)
-    assert packed.dtype == torch.int32 and packed.numel() == 4096
-    assert torch.equal(packed & 0xFFFF, lut[:-1].int()) and torch.equal(packed >> 16, lut[1:].int())
+    assert packed.dtype == torch.int16 and packed.numel() == C.LUT_BUCKETS
+    u = packed.int() & 0xFFFF
+    assert torch.equal(u & 0xFF, lut[:-1].int()) and torch.equal(u >> 8, (lut[1:] - lut[:-1]).int())
     pt = C.padded_thresholds(cb)
     assert pt.numel() == 256 and torch.isinf(pt[-1]) and torch.equal(pt[:-1], thr)
 
