@@ -3,7 +3,7 @@
 //   C[b] = alpha * op(A[b]) * op(B[b]) + beta * D[b]        (fp32 accumulate, bf16 out)
 //
 // One persistent CTA per SM, warp-specialised:
-//   warp 0      TMA producer: cp.async.bulk.tensor (no multicast) into a 4-stage ring of
+//   warp 0      TMA producer: per-CTA cp.async.bulk.tensor loads into a 4-stage ring of
 //               128B-swizzled shared-memory tiles, completion on mbarriers
 //   warp 1      MMA issuer: one elected lane issues tcgen05.mma (cta_group::1,
 //               kind::f16, M=128, N=BN, K=16) reading shared-memory descriptors and

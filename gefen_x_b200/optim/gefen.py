@@ -270,6 +270,7 @@ class Gefen(torch.optim.Optimizer):
         self._histogram_reducer = None
         self._external_grad_scale: Optional[torch.Tensor] = None
         self._exchange_epoch = 0
+        self._pre_launch_hook = None
         self._fast = None
         self._fused_meta: Dict[Any, list] = {}
         self._slow_params = 0
@@ -900,6 +901,8 @@ class Gefen(torch.optim.Optimizer):
 
         if self._plan_cache is None:
             self._plan_cache = _u.PlanCache()
+        if self._pre_launch_hook is not None:
+            self._pre_launch_hook()
         for (kind, dev, _dt), items in self._fused_items.items():
             cb = self._gefen_codebook_on(dev)
             if cb is None:

@@ -161,7 +161,7 @@ class ShardedTrainer:
         arena_bytes = 0
         if world > 1:
             arena_bytes += sum((g.max_shard + g.full_numel) * esz + 1024 for g in self.all_groups)
-            arena_bytes += xchg_floats * 4 + n_flag_slots * world * 4 + (1 << 16)
+            arena_bytes += xchg_floats * 4 + n_flag_slots * world * 4 + n2d * 512 + (1 << 20)
         else:
             arena_bytes = 1 << 12
         self.arena = SymmetricArena(arena_bytes, self.device, world, rank, group)
@@ -284,6 +284,7 @@ class ShardedTrainer:
         self.opt = Gefen(named, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                          factored_v_2d=factored_v_2d, fused=fused, **opt_kwargs)
         self.opt._grad_source = self._grad_source
+        self.opt._pre_launch_hook = self._align_ranks
         self.opt._external_grad_scale = self.clip_coef[0:1] if self.clip else None
         if self.world > 1:
             self._exchange: Dict[torch.Tensor, U.ShardExchange] = {}
@@ -302,6 +303,19 @@ class ShardedTrainer:
             self.opt._shard_info = lambda p: self._exchange.get(p)
             if global_codebook:
                 self.opt._histogram_reducer = self._host_allreduce
+
+    def _align_ranks(self) -> None:
+        """Host barrier before the kernels of a step whose preparation ran on the host.
+
+        The first step (period search, codebook learning) and any step that rebuilds the
+        plans can take seconds of host time that differs between ranks; the kernels that
+        follow wait for their peers with a bounded budget, so the ranks are aligned first.
+        """
+        if self.world > 1:
+            import torch.distributed as dist
+
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.process_group)
 
     def _host_allreduce(self, t: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist

@@ -1,0 +1,34 @@
+"""CPU tests of the sharded runtime's host-side layout arithmetic (no GPU, no process group)."""
+import torch
+
+from gefen_x_b200.models.decoder import get_config, layer_param_specs
+from gefen_x_b200.parallel.fsdp import Group, embed_group_shapes
+
+
+def test_row_shards_partition_every_parameter():
+    cfg = get_config("tiny-llama", qk_norm=True)
+    shapes = [("l." + n, s) for n, (_, s) in layer_param_specs(cfg).items()]
+    for world in (1, 2, 3, 8):
+        g = Group("layer", shapes, world)
+        full = torch.arange(g.full_numel, dtype=torch.float64)
+        rebuilt = torch.full_like(full, -1)
+        for r in range(world):
+            shard = torch.empty(g.shard_numel[r], dtype=torch.float64)
+            for sp in g.specs:
+                src, n = g.local_slice(sp, r)
+                shard[sp.shard_off[r]:sp.shard_off[r] + n] = full[src:src + n]
+            # what the gather kernel does: copy each rank's segments back to their place
+            for sp in g.specs:
+                dst, n = g.local_slice(sp, r)
+                rebuilt[dst:dst + n] = shard[sp.shard_off[r]:sp.shard_off[r] + n]
+        assert torch.equal(rebuilt, full)
+        assert sum(g.shard_numel) == g.full_numel
+        for sp in g.specs:
+            assert sum(sp.shard_rows) == sp.rows
+
+
+def test_embed_group_follows_tying():
+    tied = embed_group_shapes(get_config("qwen3-4b"))
+    untied = embed_group_shapes(get_config("llama3-8b"))
+    assert [n for n, _ in tied] == ["model.embed_tokens.weight", "model.norm.weight"]
+    assert [n for n, _ in untied][-1] == "lm_head.weight"

@@ -1,0 +1,58 @@
+"""Multi-GPU tests of the sharded runtime: 2 ranks must follow the 1-GPU trajectory.
+
+Ranks are child processes started with torch.distributed.run on one node.  The
+reference's multi-rank tests follow the same "single-process oracle on the same
+seeded full tensors" pattern (reference tests/test_muon_fsdp2_parity.py:60-70).
+"""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _single_gpu_losses(world, clip):
+    from gefen_x_b200.models.decoder import get_config
+    from gefen_x_b200.parallel.fsdp import ShardedTrainer
+
+    cfg = get_config("tiny-llama", qk_norm=True, hidden=256, ffn=512, n_layers=3)
+    dev = torch.device("cuda", 0)
+    tr = ShardedTrainer(cfg, device=dev, dtype=torch.bfloat16, lr=6e-4, weight_decay=0.01,
+                        clip_grad_norm=clip, seed=5)
+    g = torch.Generator().manual_seed(2)
+    tok = torch.randint(0, cfg.vocab_size, (world * 2, 129), generator=g).to(dev)
+    return [float(tr.step(tok[:, :-1], tok[:, 1:]).item()) for _ in range(12)]
+
+
+@pytest.mark.parametrize("rs_mode,clip", [("stash", "1.0"), ("fused", "none")])
+def test_two_ranks_track_single_gpu(tmp_path, rs_mode, clip):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    out = tmp_path / "losses.json"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(ROOT, "tests", "_fsdp_worker.py"), str(out), rs_mode, clip]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    multi = json.load(open(out))
+    ref = _single_gpu_losses(2, None if clip == "none" else float(clip))
+    got = multi["mean_loss"]
+    assert got[-1] < got[0] - 0.5
+    for a, b in zip(ref, got):
+        assert abs(a - b) < 0.05 * max(1.0, abs(a)), (ref, got)
+    assert multi["state_bytes_per_param"] < 1.2
