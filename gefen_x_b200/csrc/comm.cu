@@ -34,26 +34,34 @@ __global__ void wait_kernel(const uint32_t* flags, int n, uint32_t value, long l
 }
 
 // Segment copy: dst[seg.dst_off ...] = src_base[seg.src_rank][seg.src_off ...], 16-byte units.
+// All CTAs walk the segments together; within a segment every thread keeps eight
+// 16-byte peer loads in flight before it stores them (an NVLink round trip is a few
+// microseconds, so the bandwidth a CTA reaches is set by the bytes it has in flight).
+constexpr int kGatherUnroll = 8;
+
 __global__ void __launch_bounds__(256) gather_kernel(PtrList src_base, const GatherSeg* __restrict__ segs,
                                                      int n_segs, char* __restrict__ dst,
                                                      const long long* __restrict__ unit_prefix) {
-    // unit_prefix[i] = number of 16-byte units in segments [0, i)
-    const long long total = unit_prefix[n_segs];
-    int seg = 0;
-    for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < total;
-         u += (long long)gridDim.x * blockDim.x) {
-        // binary search of the segment holding unit u
-        int lo = 0, hi = n_segs;
-        while (hi - lo > 1) {
-            const int mid = (lo + hi) >> 1;
-            if (unit_prefix[mid] <= u) lo = mid; else hi = mid;
-        }
-        seg = lo;
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long nthreads = (long long)gridDim.x * blockDim.x;
+    for (int seg = 0; seg < n_segs; ++seg) {
         const GatherSeg s = segs[seg];
-        const long long k = u - unit_prefix[seg];
-        const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(src_base.p[s.src_rank]) + s.src_off) + k;
-        uint4* dp = reinterpret_cast<uint4*>(dst + s.dst_off) + k;
-        *dp = *sp;
+        const long long units = unit_prefix[seg + 1] - unit_prefix[seg];
+        const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(src_base.p[s.src_rank]) + s.src_off);
+        uint4* dp = reinterpret_cast<uint4*>(dst + s.dst_off);
+        for (long long u0 = tid; u0 < units; u0 += nthreads * kGatherUnroll) {
+            uint4 v[kGatherUnroll];
+#pragma unroll
+            for (int j = 0; j < kGatherUnroll; ++j) {
+                const long long u = u0 + j * nthreads;
+                if (u < units) v[j] = sp[u];
+            }
+#pragma unroll
+            for (int j = 0; j < kGatherUnroll; ++j) {
+                const long long u = u0 + j * nthreads;
+                if (u < units) dp[u] = v[j];
+            }
+        }
     }
 }
 
@@ -114,7 +122,7 @@ cudaError_t launch_gather(void* const* src_base, int world, const GatherSeg* seg
     if (n_segs <= 0 || total_units <= 0) return cudaSuccess;
     PtrList l{};
     for (int i = 0; i < world; ++i) l.p[i] = src_base[i];
-    long long want = (total_units + 255) / 256;
+    long long want = (total_units + 256 * kGatherUnroll - 1) / (256 * kGatherUnroll);
     int grid = (int)(want < ctas ? want : ctas);
     if (grid < 1) grid = 1;
     gather_kernel<<<grid, 256, 0, st>>>(l, segs_dev, n_segs, reinterpret_cast<char*>(dst), unit_prefix_dev);

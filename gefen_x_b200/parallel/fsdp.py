@@ -117,7 +117,7 @@ class ShardedTrainer:
                  rank: int = 0, group=None, lr: float = 6e-6, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.0, clip_grad_norm: Optional[float] = 1.0,
                  factored_v_2d: bool = True, rs_mode: Optional[str] = None, seed: int = 0,
-                 optimizer: str = "gefen", global_codebook: bool = True, gather_ctas: int = 32,
+                 optimizer: str = "gefen", global_codebook: bool = True, gather_ctas: int = 64,
                  wait_iters: int = 8_000_000, opt_kwargs: Optional[dict] = None):
         self.cfg = cfg
         self.world, self.rank = int(world), int(rank)
