@@ -1,0 +1,327 @@
+"""``GefenMuonHybrid``: Muon for hidden matrices + a backup optimizer for everything else.
+
+The composite owns two child optimizers (``GefenMuon`` and either ``Gefen`` or
+``torch.optim.AdamW``) and presents them as one ``torch.optim.Optimizer``-like
+object: ``param_groups`` is the live concatenation of the children's groups (LR
+schedulers work on it), ``step`` runs the backup then Muon after a joint
+pre-collective failure agreement, checkpoints are ``{"muon", "backup",
+"backup_optimizer"}`` and are loaded in two phases so that a failure in either
+half leaves both untouched.
+
+Parity: reference ``src/gefen/hybrid.py`` (constructor forms ``:228-329``, routing
+view ``:91``, step ``:693-776``, checkpoint ``:778-1000``, ``from_model``
+``:1020-1032``).
+"""
+from __future__ import annotations
+
+import copy
+from typing import Any, Dict, Iterable, List, Optional
+
+import torch
+import torch.nn as nn
+
+from ..parallel.control import raise_if_any_rank_failed
+from .gefen import Gefen
+from .muon import GefenMuon
+from .params import (DEFAULT_BACKUP_SUBSTRINGS, split_named_for_muon, split_params_for_muon,
+                     validate_split)
+
+
+class _MergedState:
+    """Read-mostly view routing ``state[param]`` to the child that owns ``param``."""
+
+    def __init__(self, children):
+        self._children = children
+
+    def _owner(self, p):
+        for c in self._children:
+            if c is not None and any(p is q for g in c.param_groups for q in g["params"]):
+                return c
+        raise KeyError(p)
+
+    def __getitem__(self, p):
+        return self._owner(p).state[p]
+
+    def get(self, p, default=None):
+        try:
+            return self[p]
+        except KeyError:
+            return default
+
+    def __contains__(self, p):
+        return any(c is not None and p in c.state for c in self._children)
+
+    def __iter__(self):
+        for c in self._children:
+            if c is not None:
+                yield from c.state
+
+    def __len__(self):
+        return sum(len(c.state) for c in self._children if c is not None)
+
+    def items(self):
+        for c in self._children:
+            if c is not None:
+                yield from c.state.items()
+
+    def values(self):
+        for c in self._children:
+            if c is not None:
+                yield from c.state.values()
+
+    def keys(self):
+        return iter(self)
+
+
+class GefenMuonHybrid:
+    """See the module docstring.  Call forms: ``(muon_named, backup_named, lr=...)``,
+    ``(model, lr=...)`` or ``(named_parameters_iterable, lr=...)``."""
+
+    def __init__(self, muon_named_params, backup_named_params=None, *, lr, backup_substrings=None,
+                 muon_lr=None, backup_lr=None, backup_optimizer: str = "gefen",
+                 weight_decay: float = 0.0, muon_weight_decay=None, backup_weight_decay=None,
+                 no_decay_substrings=(), backup_1d_period_one: bool = False,
+                 backup_2d_period_one: bool = False, betas=(0.9, 0.999), eps: float = 1e-8,
+                 fused: bool = True, momentum: float = 0.95, nesterov: bool = True, ns_steps: int = 5,
+                 ns_schedule: Optional[str] = "tuned3", adjust_lr_fn: Optional[str] = "match_rms_adamw",
+                 sharded_mode: str = "exact", fp8_ns: bool = False, fp8_ns_compile: bool = True,
+                 batched_ns: bool = False, batched_ns_workspace_bytes: int = 256 << 20,
+                 stochastic_round: bool = False, deterministic: bool = False, normuon: bool = True,
+                 normuon_beta2: float = 0.95, normuon_eps: float = 1e-8, cautious: bool = False,
+                 capturable: bool = False, verbose: bool = False):
+        if not isinstance(deterministic, bool):
+            raise TypeError("deterministic must be a bool")
+        if backup_optimizer not in ("gefen", "adamw"):
+            raise ValueError("backup_optimizer must be 'gefen' or 'adamw', got {!r}".format(backup_optimizer))
+        model = None
+        if backup_named_params is None:
+            subs = DEFAULT_BACKUP_SUBSTRINGS if backup_substrings is None else tuple(backup_substrings)
+            if isinstance(muon_named_params, nn.Module):
+                model = muon_named_params
+                muon_named, backup_named = split_params_for_muon(model, subs)
+            else:
+                items = list(muon_named_params)
+                if items and isinstance(items[0], torch.Tensor):
+                    raise TypeError(
+                        "GefenMuonHybrid cannot route bare tensors; pass (name, param) pairs, a model, "
+                        "or use GefenMuonHybrid.from_model(model, ...)")
+                muon_named, backup_named = split_named_for_muon(items, subs)
+        else:
+            if backup_substrings is not None:
+                raise ValueError("backup_substrings only applies to the single-argument form")
+            muon_named, backup_named = list(muon_named_params), list(backup_named_params)
+        muon_named, backup_named = validate_split(muon_named, backup_named, model)
+        if not muon_named and not backup_named:
+            raise ValueError("optimizer got an empty parameter list")
+
+        self.backup_optimizer = backup_optimizer
+        self.defaults = dict(lr=lr, weight_decay=weight_decay)
+        m_lr = lr if muon_lr is None else muon_lr
+        b_lr = lr if backup_lr is None else backup_lr
+        m_wd = weight_decay if muon_weight_decay is None else muon_weight_decay
+        b_wd = weight_decay if backup_weight_decay is None else backup_weight_decay
+
+        self.muon: Optional[GefenMuon] = None
+        if muon_named:
+            self.muon = GefenMuon(
+                muon_named, lr=m_lr, weight_decay=m_wd, momentum=momentum, nesterov=nesterov,
+                ns_steps=ns_steps, ns_schedule=ns_schedule, adjust_lr_fn=adjust_lr_fn, fused=fused,
+                sharded_mode=sharded_mode, fp8_ns=fp8_ns, fp8_ns_compile=fp8_ns_compile,
+                batched_ns=batched_ns, batched_ns_workspace_bytes=batched_ns_workspace_bytes,
+                stochastic_round=stochastic_round, deterministic=deterministic, normuon=normuon,
+                normuon_beta2=normuon_beta2, normuon_eps=normuon_eps, cautious=cautious,
+                capturable=capturable, verbose=verbose)
+        self.backup = None
+        if backup_named:
+            nd = tuple(s.lower() for s in no_decay_substrings)
+            decay = [(n, p) for n, p in backup_named if not any(s in n.lower() for s in nd)]
+            no_decay = [(n, p) for n, p in backup_named if any(s in n.lower() for s in nd)]
+            if backup_optimizer == "gefen":
+                groups = []
+                if decay:
+                    groups.append({"params": decay, "weight_decay": b_wd})
+                if no_decay:
+                    groups.append({"params": no_decay, "weight_decay": 0.0})
+                # the backup never uses the factored second moment: embeddings / heads are sharded
+                # by rows under FSDP and the reference pins it off as well (hybrid.py:515-518)
+                self.backup = Gefen(groups, lr=b_lr, betas=betas, eps=eps, fused=fused,
+                                    factored_v_2d=False, force_1d_period_one=backup_1d_period_one,
+                                    force_2d_period_one=backup_2d_period_one,
+                                    stochastic_round=stochastic_round, deterministic=deterministic,
+                                    capturable=capturable, verbose=verbose)
+            else:
+                groups = []
+                if decay:
+                    groups.append({"params": [p for _, p in decay], "weight_decay": b_wd})
+                if no_decay:
+                    groups.append({"params": [p for _, p in no_decay], "weight_decay": 0.0})
+                kw = {}
+                if fused and all(p.is_cuda for _, p in backup_named):
+                    kw["fused"] = True
+                if capturable:
+                    kw["capturable"] = True
+                self.backup = torch.optim.AdamW(groups, lr=b_lr, betas=betas, eps=eps, **kw)
+        self.state = _MergedState([self.muon, self.backup])
+        self._pre_hooks: List[Any] = []
+        self._post_hooks: List[Any] = []
+
+    @classmethod
+    def from_model(cls, model: nn.Module, **kwargs) -> "GefenMuonHybrid":
+        subs = kwargs.pop("backup_substrings", DEFAULT_BACKUP_SUBSTRINGS)
+        muon_named, backup_named = split_params_for_muon(model, subs)
+        validate_split(muon_named, backup_named, model)
+        return cls(muon_named, backup_named, **kwargs)
+
+    # ------------------------------------------------------------------
+    @property
+    def children(self):
+        return [c for c in (self.muon, self.backup) if c is not None]
+
+    @property
+    def param_groups(self):
+        """Live concatenation of the children's groups (mutating a group dict reaches the child)."""
+        out = []
+        for c in self.children:
+            out.extend(c.param_groups)
+        return out
+
+    def add_param_group(self, param_group):
+        raise NotImplementedError(
+            "GefenMuonHybrid routes parameters at construction; build a new hybrid to add parameters")
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for c in self.children:
+            c.zero_grad(set_to_none=set_to_none)
+
+    def register_step_pre_hook(self, hook):
+        self._pre_hooks.append(hook)
+        return hook
+
+    def register_step_post_hook(self, hook):
+        self._post_hooks.append(hook)
+        return hook
+
+    def _process_groups(self):
+        pgs, seen = [], set()
+        for c in self.children:
+            for g in c.param_groups:
+                for p in g["params"]:
+                    mesh = getattr(p, "device_mesh", None)
+                    if mesh is None:
+                        continue
+                    for d in range(mesh.ndim):
+                        pg = mesh.get_group(d)
+                        if id(pg) not in seen:
+                            seen.add(id(pg))
+                            pgs.append(pg)
+        return pgs
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        for h in self._pre_hooks:
+            h(self, (), {})
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        # one agreement over the union of both children's meshes before either mutates
+        local_exc = None
+        try:
+            from .gefen import _assert_gradients_structurally_valid
+
+            for c in self.children:
+                _assert_gradients_structurally_valid(c)
+        except Exception as exc:  # noqa: BLE001
+            local_exc = exc
+        pgs = self._process_groups()
+        if pgs:
+            raise_if_any_rank_failed(local_exc, pgs, "GefenMuonHybrid step")
+        elif local_exc is not None:
+            raise local_exc
+        # AMP controls attached to the composite are forwarded to the children
+        for attr in ("found_inf", "grad_scale"):
+            if hasattr(self, attr):
+                for c in self.children:
+                    setattr(c, attr, getattr(self, attr))
+        try:
+            if self.backup is not None:
+                self.backup.step()
+            if self.muon is not None:
+                self.muon._gefen_hybrid_precollective_preflight = True
+                try:
+                    self.muon.step()
+                finally:
+                    self.muon._gefen_hybrid_precollective_preflight = False
+        finally:
+            for attr in ("found_inf", "grad_scale"):
+                for c in self.children:
+                    if hasattr(c, attr) and hasattr(self, attr):
+                        delattr(c, attr)
+        for h in self._post_hooks:
+            h(self, (), {})
+        return loss
+
+    @property
+    def _step_supports_amp_scaling(self) -> bool:
+        return any(getattr(c, "_step_supports_amp_scaling", False) for c in self.children)
+
+    # ------------------------------------------------------------------
+    def state_dict(self) -> Dict[str, Any]:
+        return {
+            "muon": self.muon.state_dict() if self.muon is not None else None,
+            "backup": self.backup.state_dict() if self.backup is not None else None,
+            "backup_optimizer": self.backup_optimizer,
+        }
+
+    def load_state_dict(self, state_dict) -> None:
+        """Two-phase load: both halves are restored on shadow copies first; only when both
+        succeeded are the results swapped in."""
+        if not isinstance(state_dict, dict) or "muon" not in state_dict or "backup" not in state_dict:
+            raise ValueError("not a GefenMuonHybrid checkpoint (expected keys 'muon' and 'backup')")
+        saved_kind = state_dict.get("backup_optimizer", "gefen")
+        if saved_kind != self.backup_optimizer:
+            raise ValueError(
+                "checkpoint was written with backup_optimizer={!r} but this hybrid uses {!r}".format(
+                    saved_kind, self.backup_optimizer))
+        if (state_dict["muon"] is None) != (self.muon is None) or \
+                (state_dict["backup"] is None) != (self.backup is None):
+            raise ValueError("checkpoint halves do not match this hybrid's muon/backup split")
+        staged = []
+        for child, sd in ((self.muon, state_dict["muon"]), (self.backup, state_dict["backup"])):
+            if child is None:
+                continue
+            if isinstance(child, Gefen):
+                shadow = object.__new__(type(child))
+                shadow.__dict__.update(child.__dict__)
+                shadow.state = copy.copy(child.state)
+                shadow.param_groups = [dict(g, params=list(g["params"])) for g in child.param_groups]
+                shadow._fast = None
+                shadow._plan_cache = None
+                shadow.load_state_dict(sd)
+                staged.append((child, shadow))
+            else:
+                snapshot = copy.deepcopy(child.state_dict())
+                staged.append((child, ("torch", sd, snapshot)))
+        done = []
+        try:
+            for child, shadow in staged:
+                if isinstance(shadow, tuple):
+                    child.load_state_dict(shadow[1])
+                    done.append((child, shadow[2]))
+        except Exception:
+            for child, snap in done:
+                child.load_state_dict(snap)
+            raise
+        for child, shadow in staged:
+            if not isinstance(shadow, tuple):
+                child.__dict__.update(shadow.__dict__)
+
+    def state_bytes(self) -> int:
+        total = 0
+        for c in self.children:
+            if isinstance(c, Gefen):
+                total += c.state_bytes()
+            else:
+                for st in c.state.values():
+                    total += sum(v.numel() * v.element_size() for v in st.values() if torch.is_tensor(v))
+        return total

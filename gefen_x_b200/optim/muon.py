@@ -1,0 +1,435 @@
+"""``GefenMuon``: Muon (orthogonalised momentum) with Gefen's quantised momentum state.
+
+For every 2-D hidden matrix: advance the codebook-quantised momentum EMA
+(``beta = momentum``), take the dense momentum (plus the Nesterov look-ahead),
+orthogonalise it with Newton–Schulz, optionally apply NorMuon row normalisation
+and the cautious mask, and apply it with the shape-dependent lr ratio.  There is
+no second moment, so the state is ~1 byte per parameter.
+
+Sharded parameters (DTensor ``Shard(0)``):
+
+* ``sharded_mode="exact"`` – every rank gathers the full gradient, runs the full
+  Newton–Schulz redundantly and keeps its rows of the result;
+* ``"distributed"`` – matrix ``i`` is owned by rank ``i mod world``: owners
+  compute, the bf16 update is broadcast, every rank keeps its rows;
+* ``"approx"`` – Newton–Schulz on the local row shard, no collectives.
+
+Parity: reference ``src/gefen/gefen_muon.py`` (constructor ``:546-573``, momentum
+``:1064-1190``, NorMuon ``:1192-1230``, apply ``:1234-1300``, modes ``:1821-2050``,
+step ``:2944-3030``).  The Newton–Schulz products run on the tcgen05 GEMM
+(``optim/newton_schulz.py``) instead of cuBLAS.
+"""
+from __future__ import annotations
+
+import math
+import warnings
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+
+from ..parallel.control import raise_if_any_rank_failed, synchronize_step_failure
+from ..quant import codebook as _cbk
+from . import functional as F_
+from . import newton_schulz as NS
+from .gefen import Gefen, _local, _assert_gradients_structurally_valid, _amp_prepare_optimizer_step
+
+EPS = NS.EPS
+BATCHED_NS_MIN_BATCH = 8
+BATCHED_NS_MAX_MIN_DIM = 512
+BATCHED_NS_MAX_NUMEL = 1 << 20
+BATCHED_NS_DEFAULT_WORKSPACE_BYTES = 256 << 20
+_SHARDED_MODES = ("exact", "distributed", "approx")
+
+
+def stable_distributed_owner(stable_index: int, world: int) -> int:
+    """Owner rank of the ``stable_index``-th Muon matrix (``index mod world``)."""
+    if world <= 0:
+        raise ValueError("world must be positive, got {}".format(world))
+    if stable_index < 0:
+        raise ValueError("stable_index must be non-negative, got {}".format(stable_index))
+    return stable_index % world
+
+
+def adjust_lr_ratio(adjust_lr_fn: Optional[str], shape) -> float:
+    rows, cols = shape[:2]
+    if adjust_lr_fn is None or adjust_lr_fn == "original":
+        return math.sqrt(max(1, rows / cols))
+    if adjust_lr_fn == "match_rms_adamw":
+        return 0.2 * math.sqrt(max(rows, cols))
+    return 1.0
+
+
+def cautious_mask_(update: torch.Tensor, grad: torch.Tensor) -> torch.Tensor:
+    """Zero the coordinates whose sign disagrees with the gradient; rescale by 1/mean(mask)."""
+    mask = (update * grad) > 0
+    agree = mask.sum()
+    scale = mask.numel() / agree.clamp(min=1).to(torch.float32)
+    return update.mul_(mask.to(update.dtype)).mul_(scale.to(update.dtype))
+
+
+def batched_ns_shape_eligible(rows: int, cols: int) -> bool:
+    return rows > 0 and cols > 0 and min(rows, cols) <= BATCHED_NS_MAX_MIN_DIM \
+        and rows * cols <= BATCHED_NS_MAX_NUMEL
+
+
+class GefenMuon(Gefen):
+    """Muon on 2-D matrices with codebook-quantised momentum (see module docstring)."""
+
+    def __init__(self, params, lr=1e-3, weight_decay: float = 0.1, momentum: float = 0.95,
+                 nesterov: bool = True, ns_coefficients=(NS.DEFAULT_A, NS.DEFAULT_B, NS.DEFAULT_C),
+                 eps: float = EPS, ns_steps: int = NS.DEFAULT_NS_STEPS, ns_schedule: Optional[str] = None,
+                 adjust_lr_fn: Optional[str] = None, *, fused: bool = True,
+                 sharded_mode: str = "exact", fp8_ns: bool = False, fp8_ns_compile: bool = True,
+                 batched_ns: bool = False,
+                 batched_ns_workspace_bytes: int = BATCHED_NS_DEFAULT_WORKSPACE_BYTES,
+                 stochastic_round: bool = False, deterministic: bool = False, normuon: bool = False,
+                 normuon_beta2: float = 0.95, normuon_eps: float = 1e-8, cautious: bool = False,
+                 capturable: bool = False, verbose: bool = False):
+        if sharded_mode not in _SHARDED_MODES:
+            raise ValueError("sharded_mode must be one of {}, got {!r}".format(_SHARDED_MODES, sharded_mode))
+        if not 0.0 <= momentum < 1.0:
+            raise ValueError("Invalid momentum value: {}".format(momentum))
+        if adjust_lr_fn not in (None, "original", "match_rms_adamw"):
+            raise ValueError("Unknown adjust_lr_fn {!r}".format(adjust_lr_fn))
+        if ns_steps < 1:
+            raise ValueError("ns_steps must be >= 1")
+        NS.resolve_schedule(ns_schedule, ns_coefficients, ns_steps)      # validates
+        if fp8_ns:
+            warnings.warn("fp8_ns=True is accepted for configuration compatibility; the "
+                          "Newton-Schulz products run in bf16 on the tcgen05 GEMM.", RuntimeWarning,
+                          stacklevel=2)
+        self._muon_defaults = dict(momentum=momentum, nesterov=nesterov,
+                                   ns_coefficients=tuple(ns_coefficients), ns_steps=ns_steps,
+                                   ns_schedule=ns_schedule, adjust_lr_fn=adjust_lr_fn,
+                                   normuon=normuon, normuon_beta2=normuon_beta2,
+                                   normuon_eps=normuon_eps, cautious=cautious, muon_eps=eps)
+        self.sharded_mode = sharded_mode
+        self.fp8_ns, self.fp8_ns_compile = fp8_ns, fp8_ns_compile
+        self.batched_ns = batched_ns
+        self.batched_ns_workspace_bytes = int(batched_ns_workspace_bytes)
+        super().__init__(params, lr=lr, betas=(momentum, 0.999), eps=1e-8, weight_decay=weight_decay,
+                         fused=fused, factored_v_2d=False, stochastic_round=stochastic_round,
+                         deterministic=deterministic, capturable=capturable, verbose=verbose)
+
+    # ------------------------------------------------------------------
+    def add_param_group(self, param_group):
+        extra = dict(getattr(self, "_muon_defaults", {}))
+        for k in list(extra):
+            if k in param_group:
+                extra[k] = param_group[k]
+        merged = dict(param_group)
+        merged.update(extra)
+        for _, p in self._iter_params_with_names(merged["params"]):
+            if p.ndim != 2:
+                raise ValueError(
+                    "GefenMuon optimizes 2D matrices only; got a {}-D parameter of shape {}. "
+                    "Route embeddings, heads, norms and biases to a backup optimizer "
+                    "(GefenMuonHybrid does this).".format(p.ndim, tuple(p.shape)))
+        super().add_param_group(merged)
+
+    def _is_factored(self, p) -> bool:
+        return False
+
+    # ------------------------------------------------------------------
+    # momentum
+    # ------------------------------------------------------------------
+    def _muon_state(self, name: str, p: torch.Tensor, grad: torch.Tensor) -> Dict[str, Any]:
+        """State sized to ``grad`` (the full matrix in exact/distributed mode, the shard in approx)."""
+        state = self.state[p]
+        numel = grad.numel()
+        if "step" not in state:
+            if "automatic_period" in state:
+                period = state["automatic_period"]
+            elif numel == 1:
+                period = 1
+            else:
+                period = self._resolve_automatic_period(name, p, grad)
+            if numel % period:
+                raise ValueError(
+                    "Automatic partition period {} does not divide parameter {} with numel {}".format(
+                        period, name, numel))
+            state["automatic_period"] = period
+            state["step"] = self._new_step_counter(grad.device)
+            state["m_codebook"] = torch.zeros(numel // period, period, dtype=torch.uint8, device=grad.device)
+            state["m_magnitude"] = torch.zeros(numel // period, 1, dtype=torch.float32, device=grad.device)
+        self._colocate_param_state_(state, grad.device)
+        return state
+
+    def _prepare_muon_momentum(self, group, name: str, p: torch.Tensor, grad: torch.Tensor) -> torch.Tensor:
+        """Advance the quantised momentum with ``grad``; return the dense Newton–Schulz input."""
+        state = self._muon_state(name, p, grad)
+        state["step"] += 1
+        beta = group["momentum"]
+        cb = self._gefen_codebook_on(grad.device)
+        if cb is None:
+            raise ValueError("Expected Gefen codebook to be initialized before the Muon momentum update.")
+        gv = F_.partition_view(grad.reshape(-1), state["automatic_period"])
+        q = F_.momentum_requantize_(cb, state["m_codebook"], state["m_magnitude"], gv, beta,
+                                    self._pending_grad_scale)
+        m = q.view(grad.shape)
+        if group["nesterov"]:
+            g = grad.float()
+            if self._pending_grad_scale is not None:
+                g = g * self._pending_grad_scale
+            m = m * beta + g * (1.0 - beta)
+        return m.to(torch.bfloat16 if grad.dtype != torch.float64 else grad.dtype)
+
+    def _iter_gefen_grad_periods(self, reuse_existing_periods: bool = False):
+        """Codebook learning sees what the momentum will see: full matrices unless ``approx``."""
+        for group in self.param_groups:
+            for name, p in self._iter_group_params_with_names(group):
+                if p.grad is None:
+                    continue
+                grad = self._momentum_grad(p)
+                flat = grad.reshape(-1)
+                if flat.numel() == 0:
+                    continue
+                state = self.state[p]
+                if reuse_existing_periods:
+                    if "automatic_period" not in state:
+                        raise ValueError(
+                            "Expected automatic_period to exist for {} before refreshing Gefen "
+                            "codebook at optimizer step {}".format(name, self._gefen_global_step))
+                    period = state["automatic_period"]
+                elif flat.numel() == 1:
+                    period = 1
+                else:
+                    period = self._resolve_automatic_period(name, p, grad)
+                state["automatic_period"] = period
+                yield name, flat, period, grad
+
+    def _momentum_grad(self, p: torch.Tensor) -> torch.Tensor:
+        g = p.grad
+        if hasattr(g, "full_tensor") and self.sharded_mode != "approx":
+            return g.full_tensor().detach()
+        return _local(g).detach()
+
+    # ------------------------------------------------------------------
+    # update pieces
+    # ------------------------------------------------------------------
+    def _normuon_normalize(self, state, ortho: torch.Tensor, beta2: float, eps: float) -> torch.Tensor:
+        v = state.get("normuon_v")
+        if v is None or v.shape[0] != ortho.shape[0]:
+            v = torch.zeros(ortho.shape[0], 1, dtype=torch.float32, device=ortho.device)
+            state["normuon_v"] = v
+            state["normuon_step"] = self._new_step_counter(ortho.device)
+        row_norm = torch.linalg.vector_norm(ortho, dim=1, keepdim=True, dtype=torch.float32)
+        row_sq = row_norm.square()
+        v.mul_(beta2).add_(row_sq, alpha=(1 - beta2) / ortho.shape[1])
+        state["normuon_step"] += 1
+        bc = 1 - beta2 ** state["normuon_step"]
+        denom = (v / bc).sqrt_().add_(eps)
+        frob = row_sq.sum().sqrt_() / torch.linalg.vector_norm(row_norm / denom).clamp(
+            min=torch.finfo(torch.float32).tiny)
+        return ortho.mul_((frob / denom).to(ortho.dtype))
+
+    def _orthogonalize(self, group, m: torch.Tensor) -> torch.Tensor:
+        sched = NS.resolve_schedule(group["ns_schedule"], group["ns_coefficients"], group["ns_steps"])
+        return NS.zeropower_via_newtonschulz(m, sched, len(sched), group["muon_eps"])
+
+    def _compute_muon_update(self, group, name, p, grad) -> torch.Tensor:
+        m = self._prepare_muon_momentum(group, name, p, grad)
+        update = self._orthogonalize(group, m)
+        if not update.is_contiguous():
+            update = update.contiguous()
+        state = self.state[p]
+        if group["normuon"]:
+            update = self._normuon_normalize(state, update, group["normuon_beta2"], group["normuon_eps"])
+        if group["cautious"]:
+            update = cautious_mask_(update, grad.to(update.dtype))
+        return update
+
+    @staticmethod
+    def _shard_like(full_update: torch.Tensor, p: torch.Tensor) -> torch.Tensor:
+        """Rows of ``full_update`` that this rank's ``Shard(0)`` local tensor holds."""
+        local = p.to_local()
+        mesh = p.device_mesh
+        world = mesh.size(0)
+        rank = mesh.get_local_rank(0)
+        rows = full_update.shape[0]
+        per = (rows + world - 1) // world
+        r0 = min(rows, rank * per)
+        return full_update[r0:r0 + local.shape[0]]
+
+    def _apply_muon_update(self, group, p: torch.Tensor, update: torch.Tensor, sharded: bool,
+                           approx: bool) -> None:
+        lr = self._lr_scalar(group)
+        ratio = adjust_lr_ratio(group["adjust_lr_fn"], p.shape)
+        target = p.to_local() if sharded else p
+        if group["weight_decay"] > 0.0:
+            target.mul_(1 - lr * group["weight_decay"])
+        if target.numel() == 0:
+            return
+        local_update = update if (approx or not sharded) else self._shard_like(update, p)
+        target.add_(local_update.to(target.dtype), alpha=-(lr * ratio))
+
+    # ------------------------------------------------------------------
+    # the step
+    # ------------------------------------------------------------------
+    def _process_group_of(self, p):
+        mesh = getattr(p, "device_mesh", None)
+        if mesh is None:
+            return None, 1, 0
+        if mesh.ndim != 1:
+            return None, 0, 0           # multi-dim mesh: fall back to exact
+        return mesh.get_group(0), mesh.size(0), mesh.get_local_rank(0)
+
+    def _assert_sharded_grad_presence_consistent(self, items) -> None:
+        """Every rank must step the same matrices in the same order before any collective."""
+        import torch.distributed as dist
+
+        by_pg: Dict[int, Tuple[Any, List[int]]] = {}
+        for idx, (_g, _n, p) in enumerate(items):
+            pg, world, _ = self._process_group_of(p)
+            if pg is None or world < 2:
+                continue
+            by_pg.setdefault(id(pg), (pg, []))[1].append(idx)
+        for pg, idxs in by_pg.values():
+            n_total = sum(len(g["params"]) for g in self.param_groups)
+            mask = torch.zeros(n_total + 1, dtype=torch.int32)
+            pos = {p: i for i, p in enumerate(q for g in self.param_groups for q in g["params"])}
+            for i in idxs:
+                mask[pos[items[i][2]]] = 1
+            mask[-1] = len(idxs)
+            from ..parallel.control import control_device
+
+            dev = control_device(pg)
+            lo = mask.to(dev).clone()
+            hi = mask.to(dev).clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=pg)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=pg)
+            if not torch.equal(lo.cpu(), hi.cpu()):
+                raise RuntimeError(
+                    "GefenMuon: ranks disagree on which sharded parameters have gradients this "
+                    "step; refusing to enter the gather collectives")
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        self._assert_capturable_if_capturing()
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        local_exc = None
+        try:
+            _assert_gradients_structurally_valid(self)
+            for g in self.param_groups:
+                for p in g["params"]:
+                    if p.ndim != 2:
+                        raise RuntimeError(
+                            "GefenMuon found a {}-D parameter (shape {}) in its param groups at step "
+                            "time; an optimizer wrapper replaced param_groups[*]['params'] (DeepSpeed "
+                            "ZeRO does this). Use plain Gefen there.".format(p.ndim, tuple(p.shape)))
+        except Exception as exc:           # noqa: BLE001 - fanned out below
+            local_exc = exc
+        pgs = []
+        seen = set()
+        for g in self.param_groups:
+            for p in g["params"]:
+                pg, world, _ = self._process_group_of(p)
+                if pg is not None and world > 1 and id(pg) not in seen:
+                    seen.add(id(pg))
+                    pgs.append(pg)
+        if pgs and not getattr(self, "_gefen_hybrid_precollective_preflight", False):
+            raise_if_any_rank_failed(local_exc, pgs, "GefenMuon step")
+        elif local_exc is not None:
+            raise local_exc
+        self._pending_grad_scale = None
+        if (hasattr(self, "found_inf") or hasattr(self, "grad_scale")) and \
+                not _amp_prepare_optimizer_step(self):
+            return loss
+
+        items = [(g, n, p) for g in self.param_groups
+                 for n, p in self._iter_group_params_with_names(g) if p.grad is not None]
+        if pgs:
+            self._assert_sharded_grad_presence_consistent(items)
+        try:
+            self._maybe_refresh_gefen_codebook()
+            regular, distributed = [], []
+            stable = {p: i for i, p in enumerate(q for g in self.param_groups for q in g["params"])}
+            for g, n, p in items:
+                pg, world, _ = self._process_group_of(p)
+                if self.sharded_mode == "distributed" and pg is not None and world > 1:
+                    distributed.append((g, n, p))
+                else:
+                    regular.append((g, n, p))
+            self._step_regular(regular)
+            if distributed:
+                self._step_distributed(distributed, stable)
+        finally:
+            self._pending_grad_scale = None
+        self._advance_gefen_global_step()
+        return loss
+
+    def _step_regular(self, items) -> None:
+        batches: Dict[Any, list] = {}
+        for g, n, p in items:
+            sharded = hasattr(p, "to_local")
+            approx = sharded and self.sharded_mode == "approx"
+            grad = self._momentum_grad(p)
+            if grad.numel() == 0:
+                continue
+            if (self.batched_ns and not sharded and not g["normuon"] and not g["cautious"]
+                    and batched_ns_shape_eligible(*grad.shape)):
+                key = (tuple(grad.shape), grad.device, id(g))
+                batches.setdefault(key, []).append((g, n, p, grad))
+                continue
+            update = self._compute_muon_update(g, n, p, grad)
+            self._apply_muon_update(g, p, update, sharded, approx)
+        for (_shape, _dev, _gid), members in batches.items():
+            g = members[0][0]
+            if len(members) < BATCHED_NS_MIN_BATCH:
+                for g_, n, p, grad in members:
+                    self._apply_muon_update(g_, p, self._compute_muon_update(g_, n, p, grad), False, False)
+                continue
+            moms = [self._prepare_muon_momentum(g_, n, p, grad) for g_, n, p, grad in members]
+            sched = NS.resolve_schedule(g["ns_schedule"], g["ns_coefficients"], g["ns_steps"])
+            per = max(1, self.batched_ns_workspace_bytes // max(1, 16 * moms[0].numel()))
+            for s in range(0, len(moms), per):
+                outs = NS.zeropower_batched(moms[s:s + per], sched, len(sched), g["muon_eps"])
+                for (g_, n, p, grad), upd in zip(members[s:s + per], outs):
+                    self._apply_muon_update(g_, p, upd.contiguous(), False, False)
+
+    def _step_distributed(self, items, stable) -> None:
+        """Parallel-Muon: owners orthogonalise, the bf16 update is broadcast, everyone keeps its rows."""
+        import torch.distributed as dist
+
+        for g, n, p in items:
+            pg, world, rank = self._process_group_of(p)
+            owner = stable_distributed_owner(stable[p], world)
+            full_grad = p.grad.full_tensor().detach()          # all-gather
+            update = torch.empty(full_grad.shape, dtype=torch.bfloat16, device=full_grad.device)
+            if rank == owner:
+                update.copy_(self._compute_muon_update(g, n, p, full_grad))
+            dist.broadcast(update, src=dist.get_global_rank(pg, owner), group=pg)
+            self._apply_muon_update(g, p, update, True, False)
+
+    # ------------------------------------------------------------------
+    # checkpoint: distributed mode keeps momentum on the owner only
+    # ------------------------------------------------------------------
+    def state_dict(self):
+        sd = super().state_dict()
+        if self.sharded_mode == "distributed":
+            groups = []
+            stable = 0
+            for g in self.param_groups:
+                entries = []
+                for p in g["params"]:
+                    _pg, world, _r = self._process_group_of(p)
+                    st = self.state.get(p, {})
+                    entries.append({"saved_id": stable, "name": self._param_name(p),
+                                    "shape": tuple(p.shape),
+                                    "owner": stable_distributed_owner(stable, max(1, world)),
+                                    "state_keys": sorted(k for k in st if k != "name"),
+                                    "initialized": "step" in st})
+                    stable += 1
+                groups.append({"world_size": max((self._process_group_of(p)[1] for p in g["params"]),
+                                                 default=1), "params": entries})
+            sd["gefen_muon_distributed"] = {"version": 2, "ownership": "stable_full_param_index_v1",
+                                            "consolidated": False, "groups": groups}
+        return sd
+
+    def load_state_dict(self, state_dict) -> None:
+        sd = dict(state_dict)
+        sd.pop("gefen_muon_distributed", None)
+        super().load_state_dict(sd)
