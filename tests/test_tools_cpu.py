@@ -1,0 +1,67 @@
+"""CPU tests of the lr tooling (model: reference tests/test_find_lr.py, tests/test_lr_calibration.py)."""
+import torch
+import torch.nn as nn
+
+from gefen_x_b200 import Gefen, GefenMuonHybrid
+from gefen_x_b200.models.decoder import DecoderLM, get_config
+from gefen_x_b200.tools import (calibrate_relative, calibrate_vs_adamw, lr_range_test,
+                                measure_update_rms)
+from gefen_x_b200.tools.find_lr import distribute_lrs, find_lr, main
+
+
+def _setup(hybrid=False):
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(16, 32), nn.Tanh(), nn.Linear(32, 8))
+    x, y = torch.randn(32, 16), torch.randn(32, 8)
+
+    def closure():
+        loss = ((model(x) - y) ** 2).mean()
+        loss.backward()
+        return loss.detach()
+
+    opt = GefenMuonHybrid(list(model.named_parameters()), lr=1e-2, fused=False) if hybrid else \
+        Gefen(model.named_parameters(), lr=1e-2, fused=False)
+    return model, opt, closure
+
+
+def test_probes_are_non_destructive():
+    for hybrid in (False, True):
+        model, opt, closure = _setup(hybrid)
+        for _ in range(2):
+            opt.zero_grad()
+            closure()
+            opt.step()
+        before = [p.detach().clone() for p in model.parameters()]
+        stats = measure_update_rms(opt, closure, num_steps=6, warmup=2)
+        assert len(stats) == len(opt.param_groups) and all(s.update_rms > 0 for s in stats)
+        rel = calibrate_relative(opt, closure, num_steps=6, warmup=2)
+        assert abs(rel.multipliers[rel.reference_label] - 1.0) < 1e-9
+        vs = calibrate_vs_adamw(opt, closure, num_steps=6, warmup=2)
+        assert len(vs) == 4 and all(v.ratio > 0 for v in vs)
+        for a, b in zip(before, model.parameters()):
+            assert torch.equal(a, b)
+
+
+def test_range_test_and_find_lr():
+    model, opt, closure = _setup()
+    res = lr_range_test(opt, closure, start_lr=1e-5, end_lr=10.0, num_iter=40)
+    assert 1e-5 <= res.suggested_lr <= 10.0 and len(res.lrs) == len(res.losses)
+    cfg = get_config("tiny-llama", n_layers=1, hidden=64, ffn=128, vocab_size=128)
+    lm = DecoderLM(cfg, seed=0)
+    g = torch.Generator().manual_seed(0)
+    blocks = torch.randint(0, 128, (24, 17), generator=g)
+    w0 = [p.detach().clone() for p in lm.parameters()]
+    r = find_lr(lm, blocks, optimizer="gefen", num_iter=12, bs=4, fused=False, verbose=False)
+    assert r.lr > 0 and len(r.curve) > 3
+    r2 = find_lr(lm, blocks[4:], optimizer="gefen_muon", method="sweep", eval_blocks=blocks[:4],
+                 sweep_lrs=[1e-3, 1e-2], sweep_steps=4, warmup=2, bs=4, fused=False, verbose=False)
+    assert r2.lr in (1e-3, 1e-2)
+    for a, b in zip(w0, lm.parameters()):
+        assert torch.equal(a, b)
+    assert distribute_lrs([1, 2, 3], ["a", "b"]) == {"a": [1, 3], "b": [2]}
+
+
+def test_cli_runs(capsys):
+    assert main(["--model", "tiny-llama", "--num-iter", "4", "--num-blocks", "12", "--seq-len", "16",
+                 "--bs", "2", "--device", "cpu", "--json"]) == 0
+    assert '"lr"' in capsys.readouterr().out
