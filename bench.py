@@ -44,6 +44,7 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count")
     ap.add_argument("--rs-mode", default=None)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--ag-gemm", action="store_true", help="all-gather fused into the QKV projection")
     return ap.parse_args()
 
 
@@ -111,7 +112,7 @@ def run_ours(args):
     S = args.seq_len
     trainer = ShardedTrainer(cfg, device=dev, dtype=torch.bfloat16, world=world, rank=rank,
                              lr=6e-6, clip_grad_norm=1.0, factored_v_2d=True, seed=1234,
-                             rs_mode=args.rs_mode)
+                             rs_mode=args.rs_mode, ag_gemm=args.ag_gemm)
     gen = torch.Generator().manual_seed(1000 + rank)
     n_batches = max(args.steps, 4)
     host_tok = [torch.randint(0, cfg.vocab_size, (B, S + 1), generator=gen).pin_memory()
@@ -182,7 +183,7 @@ def run_ours(args):
                    "global_batch": world * B, "seq_len": S,
                    "parallelism": "fsdp{}".format(world) if world > 1 else "single",
                    "optimizer": "Gefen factored_v_2d lr6e-6 clip1.0",
-                   "rs_mode": trainer.rs_mode,
+                   "rs_mode": trainer.rs_mode, "ag_gemm": trainer.ag_gemm,
                    "l2": "working set per step (weights+grads, GBs) exceeds the 126 MB L2"},
     }
     if rank == 0:

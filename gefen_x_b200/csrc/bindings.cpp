@@ -220,6 +220,54 @@ void gemm_bf16(const Tensor& a, const Tensor& b, Tensor c, const c10::optional<T
           "gemm_bf16");
 }
 
+inline void to_ptrs(at::IntArrayRef v, void** out);
+
+// c = a [M, K] @ bstage [N, K]^T where bstage is filled inside the launch from the peers'
+// row shards (segments in arrival order); see gemm_sm100.h.
+void gemm_ag_bf16(const Tensor& a, Tensor bstage, Tensor c, at::IntArrayRef peer_bases, const Tensor& segs,
+                  const Tensor& seg_meta, const Tensor& tile_order, Tensor flags, Tensor count,
+                  int64_t epoch, int64_t count_target, int64_t fetch_ctas,
+                  const c10::optional<Tensor>& status) {
+    c10::cuda::CUDAGuard guard(a.device());
+    TORCH_CHECK(a.scalar_type() == at::kBFloat16 && bstage.scalar_type() == at::kBFloat16 &&
+                c.scalar_type() == at::kBFloat16, "gemm_ag_bf16: bf16 tensors required");
+    TORCH_CHECK(a.dim() == 2 && bstage.dim() == 2 && c.dim() == 2 && a.stride(1) == 1 &&
+                bstage.stride(1) == 1 && c.stride(1) == 1);
+    TORCH_CHECK(a.size(1) == bstage.size(1) && c.size(0) == a.size(0) && c.size(1) == bstage.size(0));
+    const int64_t n_segs = seg_meta.size(0);
+    TORCH_CHECK(segs.scalar_type() == at::kByte && segs.numel() >= n_segs * (int64_t)sizeof(gx::GatherSeg));
+    TORCH_CHECK(seg_meta.scalar_type() == at::kLong && seg_meta.is_contiguous() && seg_meta.size(1) == 3);
+    TORCH_CHECK(tile_order.scalar_type() == at::kInt && tile_order.numel() >= (bstage.size(0) + 255) / 256);
+    TORCH_CHECK(flags.scalar_type() == at::kInt && flags.numel() >= n_segs && count.scalar_type() == at::kInt &&
+                count.numel() >= n_segs);
+    gx::GemmParams p{};
+    p.M = (int)a.size(0);
+    p.K = (int)a.size(1);
+    p.N = (int)bstage.size(0);
+    p.alpha = 1.0f;
+    p.beta = 0.0f;
+    p.C = reinterpret_cast<__nv_bfloat16*>(c.data_ptr());
+    p.ldc = c.stride(0);
+    p.status = (status.has_value() && status->defined()) ? status->data_ptr<int>() : nullptr;
+    gx::AgParams ag{};
+    ag.fetch_ctas = (int)fetch_ctas;
+    ag.n_segs = (int)n_segs;
+    ag.segs = reinterpret_cast<const gx::GatherSeg*>(segs.data_ptr());
+    ag.seg_meta = reinterpret_cast<const long long*>(seg_meta.data_ptr<int64_t>());
+    ag.tile_order = tile_order.data_ptr<int>();
+    ag.dst_base = reinterpret_cast<char*>(bstage.data_ptr());
+    ag.flags = reinterpret_cast<uint32_t*>(flags.data_ptr<int>());
+    ag.count = reinterpret_cast<uint32_t*>(count.data_ptr<int>());
+    ag.epoch = (uint32_t)epoch;
+    ag.count_target = (uint32_t)count_target;
+    void* bases[8];
+    to_ptrs(peer_bases, bases);
+    check(gx::launch_gemm_ag_bf16(reinterpret_cast<const __nv_bfloat16*>(a.data_ptr()), a.stride(0),
+                                  reinterpret_cast<const __nv_bfloat16*>(bstage.data_ptr()), bstage.stride(0),
+                                  p, ag, bases, (int)peer_bases.size(), sm_count(), stream()),
+          "gemm_ag_bf16");
+}
+
 // ---------------------------------------------------------------------------
 // peer-memory communication (comm.cu)
 // ---------------------------------------------------------------------------
@@ -360,6 +408,9 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("period_errors(Tensor flat, Tensor divisors, bool input_is_squared) -> Tensor");
     m.def("gemm_bf16(Tensor a, Tensor b, Tensor(a!) c, Tensor? d, bool a_t, bool b_t, float alpha, "
           "float beta, Tensor? status) -> ()");
+    m.def("gemm_ag_bf16(Tensor a, Tensor(a!) bstage, Tensor(b!) c, int[] peer_bases, Tensor segs, "
+          "Tensor seg_meta, Tensor tile_order, Tensor(c!) flags, Tensor(d!) count, int epoch, "
+          "int count_target, int fetch_ctas, Tensor? status) -> ()");
     m.def("comm_signal(int[] flag_ptrs, int slot, int value, int device_index) -> ()", &comm_signal);
     m.def("comm_wait(Tensor flags, int n, int value, int max_iters, Tensor? status) -> ()");
     m.def("comm_gather(int[] src_base, Tensor segs, int n_segs, Tensor(a!) dst, Tensor unit_prefix, "
@@ -383,6 +434,7 @@ TORCH_LIBRARY_IMPL(gefenx, CUDA, m) {
     m.impl("histogram", &histogram);
     m.impl("period_errors", &period_errors);
     m.impl("gemm_bf16", &gemm_bf16);
+    m.impl("gemm_ag_bf16", &gemm_ag_bf16);
     m.impl("comm_wait", &comm_wait);
     m.impl("comm_gather", &comm_gather);
     m.impl("comm_allreduce_scalar", &comm_allreduce_scalar);

@@ -154,10 +154,69 @@ struct SharedStorage {
     int abort_flag;
 };
 
+struct PeerBases { const void* p[kMaxSrc]; };
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// The first `fetch_ctas` CTAs of an all-gather-fused launch: they pull the peers' row
+// shards of B into the local staging matrix segment by segment (own rows first, then the
+// peers in ring order) and publish one flag per segment once every fetch CTA has
+// finished its part of it.
+__device__ void ag_fetch_role(const AgParams& ag, PeerBases bases) {
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long nthreads = (long long)ag.fetch_ctas * blockDim.x;
+    constexpr int U = 8;
+    for (int s = 0; s < ag.n_segs; ++s) {
+        const GatherSeg seg = ag.segs[s];
+        const long long units = ag.seg_meta[3 * s];
+        const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(bases.p[seg.src_rank]) + seg.src_off);
+        uint4* dp = reinterpret_cast<uint4*>(ag.dst_base + seg.dst_off);
+        for (long long u0 = tid; u0 < units; u0 += nthreads * U) {
+            uint4 v[U];
+#pragma unroll
+            for (int j = 0; j < U; ++j) { const long long u = u0 + j * nthreads; if (u < units) v[j] = sp[u]; }
+#pragma unroll
+            for (int j = 0; j < U; ++j) { const long long u = u0 + j * nthreads; if (u < units) dp[u] = v[j]; }
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const uint32_t prev = atomicAdd(ag.count + s, 1u);
+            if (prev + 1u == ag.count_target) st_release_gpu(ag.flags + s, ag.epoch);
+        }
+    }
+}
+
+// Producer side: before the first B tile of column block n0 is loaded, every segment that
+// overlaps rows [n0, n0 + BN) of the staging matrix must have landed (bounded wait).
+__device__ bool ag_wait_rows(const AgParams& ag, int n0, int bn, volatile int* abort_flag) {
+    for (int s = 0; s < ag.n_segs; ++s) {
+        const long long r0 = ag.seg_meta[3 * s + 1], nr = ag.seg_meta[3 * s + 2];
+        if (r0 < n0 + bn && r0 + nr > n0) {
+            bool ok = false;
+            for (long long it = 0; it < kSpinLimit; ++it) {
+                if ((int32_t)(ld_acquire_gpu(ag.flags + s) - ag.epoch) >= 0) { ok = true; break; }
+                if ((it & 255) == 255 && *abort_flag) return false;
+                __nanosleep(100);
+            }
+            if (!ok) { *abort_flag = 1; return false; }
+        }
+    }
+    asm volatile("fence.proxy.async;" ::: "memory");   // peer data written through the generic proxy -> TMA reads
+    return true;
+}
+
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 GemmParams p) {
+                 GemmParams p, AgParams ag, PeerBases bases) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // carve: [stages x A tile][stages x B tile][barriers]
     constexpr uint32_t kABytes = BM * BK * 2;
@@ -188,18 +247,37 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
     const int k_blocks = (p.K + BK - 1) / BK;
     const int tiles_per_batch = p.m_tiles * p.n_tiles;
+    // all-gather-fused launches reserve the first CTAs for fetching; the others share the tiles
+    const int first_worker = ag.enabled ? ag.fetch_ctas : 0;
+    const int worker = (int)blockIdx.x - first_worker;
+    const int n_workers = (int)gridDim.x - first_worker;
+    const bool is_fetch = ag.enabled && (int)blockIdx.x < ag.fetch_ctas;
+    // tile -> (batch, m0, n0); fused launches visit the column blocks in arrival order
+    auto coords = [&](int tile, int& b, int& m0, int& n0) {
+        b = tile / tiles_per_batch;
+        const int t = tile - b * tiles_per_batch;
+        m0 = (t % p.m_tiles) * BM;
+        int nt = t / p.m_tiles;
+        if (ag.enabled) nt = ag.tile_order[nt];
+        n0 = nt * BN;
+    };
 
-    if (warp == 0) {
+    if (is_fetch) {
+        ag_fetch_role(ag, bases);
+    } else if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-                const int b = tile / tiles_per_batch;
-                const int t = tile - b * tiles_per_batch;
-                const int m0 = (t % p.m_tiles) * BM;
-                const int n0 = (t / p.m_tiles) * BN;
+            int waited_n0 = -1;
+            for (int tile = worker; tile < p.total_tiles && ok; tile += n_workers) {
+                int b, m0, n0;
+                coords(tile, b, m0, n0);
+                if (ag.enabled && n0 != waited_n0) {
+                    if (!ag_wait_rows(ag, n0, BN, abort_flag)) { ok = false; break; }
+                    waited_n0 = n0;
+                }
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(&ss->empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
                     mbar_expect_tx(&ss->full[stage], kABytes + kBBytes);
@@ -236,7 +314,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+            for (int tile = worker; tile < p.total_tiles && ok; tile += n_workers) {
                 if (!mbar_wait(&ss->tmem_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -269,11 +347,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-            const int b = tile / tiles_per_batch;
-            const int t = tile - b * tiles_per_batch;
-            const int m0 = (t % p.m_tiles) * BM;
-            const int n0 = (t / p.m_tiles) * BN;
+        for (int tile = worker; tile < p.total_tiles && ok; tile += n_workers) {
+            int b, m0, n0;
+            coords(tile, b, m0, n0);
             if (!mbar_wait(&ss->tmem_full[acc], acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
@@ -381,11 +457,44 @@ cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p
     p.n_tiles = (p.N + BN - 1) / BN;
     p.total_tiles = p.m_tiles * p.n_tiles * p.batch;
     const int grid = p.total_tiles < sm_count ? p.total_tiles : sm_count;
-    gemm_bf16_kernel<BN><<<grid, kGemmThreads, smem, st>>>(ta, tb, p);
+    AgParams ag{};
+    PeerBases pb{};
+    gemm_bf16_kernel<BN><<<grid, kGemmThreads, smem, st>>>(ta, tb, p, ag, pb);
     return cudaGetLastError();
 }
 
 }  // namespace
+
+cudaError_t launch_gemm_ag_bf16(const __nv_bfloat16* A, long long lda, const __nv_bfloat16* Bstage, long long ldb,
+                                GemmParams p, AgParams ag, const void* const* peer_bases, int world,
+                                int sm_count, cudaStream_t st) {
+    if (p.M <= 0 || p.N <= 0 || p.K <= 0) return cudaSuccess;
+    if ((lda % 8) || (ldb % 8) || world < 1 || world > kMaxSrc) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(Bstage) % 16)) return cudaErrorInvalidValue;
+    if (ag.fetch_ctas < 1 || ag.fetch_ctas >= sm_count) return cudaErrorInvalidValue;
+    constexpr int BN = 256;
+    p.batch = 1;
+    p.a_mn_major = 0;
+    p.b_mn_major = 0;
+    CUtensorMap ta, tb;
+    if (!make_map(&ta, A, p.K, p.M, 1, lda, 0, BK, BM) || !make_map(&tb, Bstage, p.K, p.N, 1, ldb, 0, BK, BN))
+        return cudaErrorInvalidValue;
+    p.vec_ok = (p.ldc % 8 == 0) && (reinterpret_cast<uintptr_t>(p.C) % 16 == 0);
+    p.D = nullptr;
+    constexpr size_t smem = (size_t)kStages * (BM * BK * 2 + BN * BK * 2) + sizeof(SharedStorage) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return e;
+    p.m_tiles = (p.M + BM - 1) / BM;
+    p.n_tiles = (p.N + BN - 1) / BN;
+    p.total_tiles = p.m_tiles * p.n_tiles;
+    ag.enabled = 1;
+    PeerBases pb{};
+    for (int i = 0; i < world; ++i) pb.p[i] = peer_bases[i];
+    // every CTA must be resident at once: the GEMM CTAs wait on flags the fetch CTAs set
+    gemm_bf16_kernel<BN><<<sm_count, kGemmThreads, smem, st>>>(ta, tb, p, ag, pb);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_gemm_bf16(const __nv_bfloat16* A, long long lda, long long batch_stride_a,
                              const __nv_bfloat16* B, long long ldb, long long batch_stride_b,

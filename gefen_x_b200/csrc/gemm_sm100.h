@@ -2,6 +2,9 @@
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "comm.h"
 
 namespace gx {
 
@@ -16,6 +19,28 @@ struct GemmParams {
     int m_tiles, n_tiles, total_tiles;
     int vec_ok;                     // rows of C / D are 16-byte aligned
 };
+
+// All-gather fused into the GEMM: rows of B live as row shards on several ranks; the launch
+// pulls them into the local staging matrix while the tensor cores already work on the
+// column blocks whose rows have arrived.
+struct AgParams {
+    int enabled;
+    int fetch_ctas;                 // CTAs that copy instead of multiplying
+    int n_segs;
+    const GatherSeg* segs;          // in arrival order: own rank first, then ring order
+    const long long* seg_meta;      // [n_segs][3]: 16-byte units, first staging row, rows
+    const int* tile_order;          // [n_tiles]: column blocks sorted by arrival
+    char* dst_base;                 // staging matrix base (bytes)
+    uint32_t* flags;                // [n_segs], set to `epoch` when a segment has landed
+    uint32_t* count;                // [n_segs], monotonic arrival counters
+    uint32_t epoch;
+    uint32_t count_target;          // value of count[s] that completes segment s in this launch
+};
+
+// C = A[M,K] @ Bstage[N,K]^T with Bstage filled from the peers by the launch itself.
+cudaError_t launch_gemm_ag_bf16(const __nv_bfloat16* A, long long lda, const __nv_bfloat16* Bstage,
+                                long long ldb, GemmParams p, AgParams ag, const void* const* peer_bases,
+                                int world, int sm_count, cudaStream_t st);
 
 // C[b] = alpha * op(A[b]) op(B[b]) + beta * D[b], bf16 in/out, fp32 accumulate.
 // A: a_mn_major ? [batch, K, M] : [batch, M, K] with leading dimension lda (elements), etc.

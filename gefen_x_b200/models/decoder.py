@@ -124,14 +124,15 @@ def layer_numel(cfg: ModelConfig) -> int:
 # manual layer forward / backward (kernels)
 # --------------------------------------------------------------------------
 def layer_forward(cfg: ModelConfig, w: Dict[str, torch.Tensor], x: torch.Tensor, cos, sin,
-                  save: bool = True):
-    """x: [B, S, H].  Returns (y, saved)."""
+                  save: bool = True, qkv_fn=None):
+    """x: [B, S, H].  Returns (y, saved).  ``qkv_fn(h1) -> [T, q + 2kv]`` replaces the fused QKV
+    projection (the sharded runtime passes its all-gather-fused GEMM here)."""
     B, S, H = x.shape
     T = B * S
     hd, nq, nkv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
     x2d = x.reshape(T, H)
     h1, rstd1 = M.rmsnorm_fwd(x2d, w["input_layernorm.weight"], cfg.rms_eps)
-    qkv = G.mm_nt(h1, w["wqkv"])                                   # [T, q + 2kv]
+    qkv = qkv_fn(h1) if qkv_fn is not None else G.mm_nt(h1, w["wqkv"])   # [T, q + 2kv]
     q = qkv[:, :cfg.q_dim].reshape(B, S, nq, hd)
     k = qkv[:, cfg.q_dim:cfg.q_dim + cfg.kv_dim].reshape(B, S, nkv, hd)
     v = qkv[:, cfg.q_dim + cfg.kv_dim:].reshape(B, S, nkv, hd)

@@ -118,7 +118,8 @@ class ShardedTrainer:
                  weight_decay: float = 0.0, clip_grad_norm: Optional[float] = 1.0,
                  factored_v_2d: bool = True, rs_mode: Optional[str] = None, seed: int = 0,
                  optimizer: str = "gefen", global_codebook: bool = True, gather_ctas: int = 64,
-                 wait_iters: int = 8_000_000, opt_kwargs: Optional[dict] = None):
+                 wait_iters: int = 8_000_000, opt_kwargs: Optional[dict] = None,
+                 ag_gemm: bool = False, ag_fetch_ctas: int = 16):
         self.cfg = cfg
         self.world, self.rank = int(world), int(rank)
         self.device = torch.device(device if device is not None else
@@ -129,6 +130,8 @@ class ShardedTrainer:
         if self.rs_mode not in ("stash", "fused"):
             raise ValueError("rs_mode must be 'stash' or 'fused'")
         self.gather_ctas = gather_ctas
+        self.ag_gemm = bool(ag_gemm) and int(world) > 1
+        self.ag_fetch_ctas = int(ag_fetch_ctas)
         self.step_count = 0
         self.process_group = group
         cuda = self.device.type == "cuda"
@@ -196,6 +199,13 @@ class ShardedTrainer:
         if world > 1:
             for g in self.all_groups:
                 self._build_gather_tables(g)
+            if self.ag_gemm:
+                for g in self.groups:
+                    self._build_ag_tables(g)
+                n = self.groups[0].ag_tables["n_segs"]
+                self._ag_flags = [torch.zeros(n, dtype=torch.int32, device=self.device) for _ in self.ring]
+                self._ag_count = [torch.zeros(n, dtype=torch.int32, device=self.device) for _ in self.ring]
+                self._ag_launches = [0] * len(self.ring)
 
         # ---- streams -------------------------------------------------------
         if cuda:
@@ -241,10 +251,72 @@ class ShardedTrainer:
                     g.shard_w[dst:dst + n].copy_(full[src_off:src_off + n])
             del full
 
+    _QKV = ("self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight")
+
+    def _build_ag_tables(self, g: Group) -> None:
+        """Tables of the all-gather-fused QKV projection of one layer: the q/k/v row shards in
+        arrival order (own rank first, then ring order), where they land in the staging matrix,
+        and the order in which the GEMM visits its column blocks."""
+        esz = torch.empty((), dtype=self.dtype).element_size()
+        H = self.cfg.hidden
+        qkv = [sp for sp in g.specs if sp.name.endswith(self._QKV)]
+        segs, meta = [], []
+        for d in range(self.world):
+            r = (self.rank + d) % self.world
+            for sp in qkv:
+                n = sp.shard_rows[r] * sp.cols
+                if n == 0:
+                    continue
+                dst_off, _ = g.local_slice(sp, r)
+                row0 = dst_off // H
+                segs.append((g.shard_w_off + sp.shard_off[r] * esz, dst_off * esz, r))
+                meta.append((n * esz // 16, row0, sp.shard_rows[r]))
+        n_rows = self.cfg.q_dim + 2 * self.cfg.kv_dim
+        n_tiles = (n_rows + 255) // 256
+        arrival = []
+        for t in range(n_tiles):
+            lo, hi = t * 256, min(n_rows, (t + 1) * 256)
+            last = max(i for i, (_u, r0, nr) in enumerate(meta) if r0 < hi and r0 + nr > lo)
+            arrival.append((last, t))
+        order = [t for _a, t in sorted(arrival)]
+        arr = (_GatherSeg * len(segs))()
+        for i, (so, do, r) in enumerate(segs):
+            arr[i].src_off, arr[i].dst_off, arr[i].src_rank = so, do, r
+        g.ag_tables = dict(
+            segs=torch.frombuffer(arr, dtype=torch.uint8).clone().to(self.device), n_segs=len(segs),
+            meta=torch.tensor(meta, dtype=torch.int64, device=self.device),
+            order=torch.tensor(order, dtype=torch.int32, device=self.device), n_rows=n_rows)
+
+    def _qkv_fn(self, li: int, flat: torch.Tensor):
+        """The fused projection of layer ``li``: fetches the q/k/v shards into ``flat`` and
+        multiplies as they arrive."""
+        g = self.groups[li]
+        slot = li % len(self.ring)
+        tab = g.ag_tables
+        wqkv = flat[:tab["n_rows"] * self.cfg.hidden].view(tab["n_rows"], self.cfg.hidden)
+
+        def fn(h1: torch.Tensor) -> torch.Tensor:
+            self._ag_launches[slot] += 1
+            k = self._ag_launches[slot]
+            out = torch.empty(h1.shape[0], tab["n_rows"], dtype=h1.dtype, device=h1.device)
+            ops().gemm_ag_bf16(h1, wqkv, out, self.arena.base_ptrs, tab["segs"], tab["meta"], tab["order"],
+                               self._ag_flags[slot], self._ag_count[slot], k, k * self.ag_fetch_ctas,
+                               self.ag_fetch_ctas, self.status)
+            return out
+
+        return fn
+
     def _build_gather_tables(self, g: Group) -> None:
         esz = torch.empty((), dtype=self.dtype).element_size()
+        if self.ag_gemm and g is not self.embed_group:
+            g.gather_tables_rest = self._gather_table_for(
+                g, [sp for sp in g.specs if not sp.name.endswith(self._QKV)])
+        g.gather_tables = self._gather_table_for(g, g.specs)
+
+    def _gather_table_for(self, g: Group, specs):
+        esz = torch.empty((), dtype=self.dtype).element_size()
         segs, prefix = [], [0]
-        for sp in g.specs:
+        for sp in specs:
             for r in range(self.world):
                 n = sp.shard_rows[r] * sp.cols
                 if n == 0:
@@ -256,8 +328,8 @@ class ShardedTrainer:
         for i, (so, do, r) in enumerate(segs):
             arr[i].src_off, arr[i].dst_off, arr[i].src_rank = so, do, r
         host = torch.frombuffer(arr, dtype=torch.uint8).clone()
-        g.gather_tables = (host.to(self.device), len(segs),
-                           torch.tensor(prefix, dtype=torch.int64, device=self.device), prefix[-1])
+        return (host.to(self.device), len(segs),
+                torch.tensor(prefix, dtype=torch.int64, device=self.device), prefix[-1])
 
     # ------------------------------------------------------------------
     # optimizer wiring
@@ -359,11 +431,11 @@ class ShardedTrainer:
     # ------------------------------------------------------------------
     # parameter gather (all-gather by peer loads)
     # ------------------------------------------------------------------
-    def _gather_into(self, g: Group, dst: torch.Tensor) -> None:
-        segs, n_segs, prefix, total = g.gather_tables
+    def _gather_into(self, g: Group, dst: torch.Tensor, rest_only: bool = False) -> None:
+        segs, n_segs, prefix, total = g.gather_tables_rest if rest_only else g.gather_tables
         ops().comm_gather(self.arena.base_ptrs, segs, n_segs, dst, prefix, total, self.gather_ctas)
 
-    def _ensure_layer(self, li: int) -> torch.Tensor:
+    def _ensure_layer(self, li: int, rest_only: bool = False) -> torch.Tensor:
         """Make layer ``li``'s unsharded weights available; returns the flat buffer.
 
         The copy runs on the communication stream; the compute stream waits on
@@ -379,7 +451,7 @@ class ShardedTrainer:
             with torch.cuda.stream(self.comm_stream):
                 if prev >= 0 and prev in self._layer_done:
                     self.comm_stream.wait_event(self._layer_done[prev])
-                self._gather_into(g, self.ring[slot])
+                self._gather_into(g, self.ring[slot], rest_only)
                 ev = torch.cuda.Event()
                 ev.record(self.comm_stream)
                 self._gather_done[li] = ev
@@ -503,12 +575,14 @@ class ShardedTrainer:
         # ---- forward ---------------------------------------------------
         x = emb_w.index_select(0, tok.reshape(-1)).view(B, S, cfg.hidden)
         saved: List[Optional[dict]] = []
+        fused = self.ag_gemm
         for li in range(L):
-            flat = self._ensure_layer(li)
+            flat = self._ensure_layer(li, rest_only=fused)
             if li + 1 < L:
-                self._ensure_layer(li + 1)
+                self._ensure_layer(li + 1, rest_only=fused)
             self._wait_layer(li)
-            x, sv = layer_forward(cfg, layer_views(cfg, flat), x, cos, sin, save=True)
+            x, sv = layer_forward(cfg, layer_views(cfg, flat), x, cos, sin, save=True,
+                                  qkv_fn=self._qkv_fn(li, flat) if fused else None)
             saved.append(sv)
             self._mark_layer_done(li)
 

@@ -38,15 +38,16 @@ def _single_gpu_losses(world, clip):
     return [float(tr.step(tok[:, :-1], tok[:, 1:]).item()) for _ in range(12)]
 
 
-@pytest.mark.parametrize("rs_mode,clip", [("stash", "1.0"), ("fused", "none")])
-def test_two_ranks_track_single_gpu(tmp_path, rs_mode, clip):
+@pytest.mark.parametrize("rs_mode,clip,ag", [("stash", "1.0", "plain"), ("fused", "none", "plain"),
+                                             ("stash", "1.0", "ag")])
+def test_two_ranks_track_single_gpu(tmp_path, rs_mode, clip, ag):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     out = tmp_path / "losses.json"
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
-           os.path.join(ROOT, "tests", "_fsdp_worker.py"), str(out), rs_mode, clip]
+           os.path.join(ROOT, "tests", "_fsdp_worker.py"), str(out), rs_mode, clip, ag]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     multi = json.load(open(out))
