@@ -96,7 +96,11 @@ def _run(args) -> None:
         for layer in model.model.layers:
             fully_shard(layer)
         fully_shard(model)
-    opt = gefen.Gefen(list(model.named_parameters()), lr=6e-6, factored_v_2d=True)
+    if getattr(args, "optimizer", "gefen") == "muon_hybrid":
+        opt = gefen.GefenMuonHybrid(model, lr=6e-6, ns_schedule="standard", ns_steps=5,
+                                    sharded_mode="distributed" if world > 1 else "exact")
+    else:
+        opt = gefen.Gefen(list(model.named_parameters()), lr=6e-6, factored_v_2d=True)
 
     gen = torch.Generator().manual_seed(1000 + rank)
     n_batches = max(args.steps, 4)
@@ -172,10 +176,12 @@ def _run(args) -> None:
     e2e_ms = timed(e2e)
     state_bytes = 0
     own = 0
-    for p, st in opt.state.items():
-        for v in st.values():
-            if torch.is_tensor(v):
-                state_bytes += v.numel() * v.element_size()
+    children = [c for c in (getattr(opt, "muon", None), getattr(opt, "backup", None)) if c is not None] or [opt]
+    for child in children:
+        for p, st in child.state.items():
+            for v in st.values():
+                if torch.is_tensor(v):
+                    state_bytes += v.numel() * v.element_size()
     for p in model.parameters():
         pl = p.to_local() if hasattr(p, "to_local") else p
         own += pl.numel()
@@ -193,7 +199,7 @@ def _run(args) -> None:
         "config": {"model": args.model, "layers": spec["num_hidden_layers"], "params": n_params,
                    "global_batch": world * B, "seq_len": S,
                    "parallelism": "fsdp{}".format(world) if world > 1 else "single",
-                   "optimizer": "reference gefen.Gefen factored_v_2d lr6e-6 clip1.0",
+                   "optimizer": "reference gefen.{} lr6e-6 clip1.0".format(type(opt).__name__),
                    "model_impl": "transformers {} sdpa".format(kind)},
     }
     if rank == 0:

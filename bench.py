@@ -45,6 +45,7 @@ def parse_args():
     ap.add_argument("--rs-mode", default=None)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--ag-gemm", action="store_true", help="all-gather fused into the QKV projection")
+    ap.add_argument("--optimizer", default="gefen", choices=["gefen", "muon_hybrid"])
     return ap.parse_args()
 
 
@@ -112,7 +113,8 @@ def run_ours(args):
     S = args.seq_len
     trainer = ShardedTrainer(cfg, device=dev, dtype=torch.bfloat16, world=world, rank=rank,
                              lr=6e-6, clip_grad_norm=1.0, factored_v_2d=True, seed=1234,
-                             rs_mode=args.rs_mode, ag_gemm=args.ag_gemm)
+                             rs_mode=args.rs_mode, ag_gemm=args.ag_gemm, optimizer=args.optimizer,
+                             muon_kwargs=dict(ns_schedule="standard", ns_steps=5) if args.optimizer == "muon_hybrid" else None)
     gen = torch.Generator().manual_seed(1000 + rank)
     n_batches = max(args.steps, 4)
     host_tok = [torch.randint(0, cfg.vocab_size, (B, S + 1), generator=gen).pin_memory()
@@ -137,6 +139,7 @@ def run_ours(args):
     # optimizer-step time: CUDA events around opt.step inside the timed steps
     opt_ms = []
     orig_step = trainer.opt.step
+    orig_muon = trainer.muon.step if trainer.muon is not None else None
 
     def timed_opt_step(*a, **k):
         a0 = torch.cuda.Event(enable_timing=True)
@@ -148,6 +151,17 @@ def run_ours(args):
         return r
 
     trainer.opt.step = timed_opt_step
+    if orig_muon is not None:
+        def timed_muon_step(*a, **k):
+            a0 = torch.cuda.Event(enable_timing=True)
+            a1 = torch.cuda.Event(enable_timing=True)
+            a0.record()
+            r = orig_muon(*a, **k)
+            a1.record()
+            opt_ms.append((a0, a1))
+            return r
+
+        trainer.muon.step = timed_muon_step
     sampler = ClockSampler(gpu_index=local)
     if rank == 0:
         sampler.start()
@@ -156,7 +170,9 @@ def run_ours(args):
     launches = _ext.kernel_launches() - l0
     clocks = sampler.stop() if rank == 0 else {}
     trainer.opt.step = orig_step
-    opt_step_ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in opt_ms) / max(1, len(opt_ms)), world)
+    if orig_muon is not None:
+        trainer.muon.step = orig_muon
+    opt_step_ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in opt_ms) / max(1, args.steps), world)
     trainer.check_status()
 
     e2e = None
@@ -182,7 +198,9 @@ def run_ours(args):
         "config": {"model": args.model, "layers": cfg.n_layers, "params": trainer.num_params(),
                    "global_batch": world * B, "seq_len": S,
                    "parallelism": "fsdp{}".format(world) if world > 1 else "single",
-                   "optimizer": "Gefen factored_v_2d lr6e-6 clip1.0",
+                   "optimizer": ("Gefen factored_v_2d lr6e-6 clip1.0" if args.optimizer == "gefen" else
+                                 "GefenMuonHybrid (Muon NS-5 standard, quantized momentum; Gefen backup) "
+                                 "lr6e-6 clip1.0"),
                    "rs_mode": trainer.rs_mode, "ag_gemm": trainer.ag_gemm,
                    "l2": "working set per step (weights+grads, GBs) exceeds the 126 MB L2"},
     }

@@ -310,6 +310,19 @@ void comm_gather(at::IntArrayRef src_base, const Tensor& segs, int64_t n_segs, T
           "gather");
 }
 
+void comm_scatter_apply(const Tensor& segs, int64_t n_segs, const Tensor& unit_prefix, int64_t total_units,
+                        int64_t ctas) {
+    c10::cuda::CUDAGuard guard(segs.device());
+    TORCH_CHECK(segs.is_cuda() && segs.scalar_type() == at::kByte &&
+                segs.numel() >= n_segs * (int64_t)sizeof(gx::ApplySeg));
+    TORCH_CHECK(unit_prefix.is_cuda() && unit_prefix.scalar_type() == at::kLong &&
+                unit_prefix.numel() >= n_segs + 1);
+    check(gx::launch_scatter_apply(reinterpret_cast<const gx::ApplySeg*>(segs.data_ptr()), (int)n_segs,
+                                   reinterpret_cast<const long long*>(unit_prefix.data_ptr<int64_t>()),
+                                   total_units, (int)ctas, stream()),
+          "scatter_apply");
+}
+
 void comm_allreduce_scalar(at::IntArrayRef slot_ptrs, at::IntArrayRef flag_ptrs, int64_t rank,
                            const Tensor& local_val, Tensor out, int64_t epoch, int64_t max_iters,
                            const c10::optional<Tensor>& status) {
@@ -415,6 +428,7 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("comm_wait(Tensor flags, int n, int value, int max_iters, Tensor? status) -> ()");
     m.def("comm_gather(int[] src_base, Tensor segs, int n_segs, Tensor(a!) dst, Tensor unit_prefix, "
           "int total_units, int ctas) -> ()");
+    m.def("comm_scatter_apply(Tensor segs, int n_segs, Tensor unit_prefix, int total_units, int ctas) -> ()");
     m.def("comm_allreduce_scalar(int[] slot_ptrs, int[] flag_ptrs, int rank, Tensor local_val, "
           "Tensor(a!) out, int epoch, int max_iters, Tensor? status) -> ()");
     m.def("rmsnorm_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!) rstd, float eps) -> ()");
@@ -437,6 +451,7 @@ TORCH_LIBRARY_IMPL(gefenx, CUDA, m) {
     m.impl("gemm_ag_bf16", &gemm_ag_bf16);
     m.impl("comm_wait", &comm_wait);
     m.impl("comm_gather", &comm_gather);
+    m.impl("comm_scatter_apply", &comm_scatter_apply);
     m.impl("comm_allreduce_scalar", &comm_allreduce_scalar);
     m.impl("rmsnorm_fwd", &rmsnorm_fwd);
     m.impl("rmsnorm_bwd", &rmsnorm_bwd);

@@ -98,7 +98,45 @@ __global__ void allreduce_scalar_kernel(PtrList slots, PtrList flags, int world,
     }
 }
 
+// p[i] = round(p[i] * wd_factor) - alpha * u[i] for every entry of a table; u may live in a
+// peer's arena (the rows of an orthogonalised Muon update that this rank's shard holds).
+__global__ void __launch_bounds__(256) scatter_apply_kernel(const ApplySeg* __restrict__ segs, int n_segs,
+                                                            const long long* __restrict__ unit_prefix) {
+    const long long total = unit_prefix[n_segs];
+    for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < total;
+         u += (long long)gridDim.x * blockDim.x) {
+        int lo = 0, hi = n_segs;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (unit_prefix[mid] <= u) lo = mid; else hi = mid;
+        }
+        const ApplySeg s = segs[lo];
+        const long long k = (u - unit_prefix[lo]) * 8;
+        float pf[8], uf[8];
+        __nv_bfloat16* pp = reinterpret_cast<__nv_bfloat16*>(s.p) + k;
+        Vec8<__nv_bfloat16>::load(pp, pf);
+        Vec8<__nv_bfloat16>::load(reinterpret_cast<const __nv_bfloat16*>(s.u) + k, uf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float v = pf[e];
+            if (s.wd_factor != 1.0f) v = round_to<__nv_bfloat16>(v * s.wd_factor);
+            pf[e] = v - s.alpha * uf[e];
+        }
+        Vec8<__nv_bfloat16>::store(pp, pf);
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_scatter_apply(const ApplySeg* segs_dev, int n_segs, const long long* unit_prefix_dev,
+                                 long long total_units, int ctas, cudaStream_t st) {
+    if (n_segs <= 0 || total_units <= 0) return cudaSuccess;
+    long long want = (total_units + 255) / 256;
+    int grid = (int)(want < ctas ? want : ctas);
+    if (grid < 1) grid = 1;
+    scatter_apply_kernel<<<grid, 256, 0, st>>>(segs_dev, n_segs, unit_prefix_dev);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_signal(void* const* flag_ptrs, int world, int slot, unsigned value, cudaStream_t st) {
     if (world < 1 || world > kMaxSrc) return cudaErrorInvalidValue;

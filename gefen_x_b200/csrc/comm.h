@@ -11,6 +11,18 @@ struct GatherSeg {
     int pad;
 };
 
+// One parameter shard and the (possibly remote) rows of the update that belong to it.
+struct ApplySeg {
+    void* p;             // local bf16 parameter shard
+    const void* u;       // bf16 update rows (local or in a peer's arena), same length
+    float alpha;         // lr * shape ratio
+    float wd_factor;     // 1 - lr * weight_decay
+};
+
+// p = round(p * wd_factor) - alpha * u over a table of shards (8-element units, bf16).
+cudaError_t launch_scatter_apply(const ApplySeg* segs_dev, int n_segs, const long long* unit_prefix_dev,
+                                 long long total_units, int ctas, cudaStream_t st);
+
 // flag_ptrs[r]: base of rank r's flag array; writes `value` to element `slot` on every rank.
 cudaError_t launch_signal(void* const* flag_ptrs, int world, int slot, unsigned value, cudaStream_t st);
 // bounded wait until flags[0..n) >= value

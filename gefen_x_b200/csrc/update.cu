@@ -510,6 +510,11 @@ __global__ void __launch_bounds__(kEmaThreads) factored_ema_kernel(LaunchCommon 
     const float inv_cols = 1.0f / (float)d.cols;
     const float inv_rows = 1.0f / (float)d.total_rows;
     const float inv_bc2 = d.scal[1];
+    if (d.row_only >= 2) {
+        // momentum-emit tensors keep no second moment: only clear the statistics scratch
+        for (int i = threadIdx.x; i < d.rows; i += kEmaThreads) d.row_sq[i] = 0.f;
+        return;
+    }
     if (d.row_only) {
         // block path seen as [nb, period]: one second-moment value per row, no column factor
         for (int i = threadIdx.x; i < d.rows; i += kEmaThreads) {
@@ -582,7 +587,10 @@ __device__ void apply_tile(const Hot& d, const LaunchCommon& c, const Smem& s,
     const int tx = threadIdx.x % d.tcols, ty = threadIdx.x / d.tcols;
     const int c0 = (t.ct * d.tcols + tx) * VEC;
     if (c0 >= d.cols) return;
-    const float lr = d.scal[0], inv_bc1 = d.scal[2], wdf = d.scal[3];
+    // emit mode (Muon momentum): no parameter update, d.p receives the dense new momentum
+    // (row_only == 3: with the Nesterov look-ahead beta * m + (1 - beta) * g)
+    const bool emit = d.row_only >= 2;
+    const float lr = emit ? 0.f : d.scal[0], inv_bc1 = emit ? 0.f : d.scal[2], wdf = emit ? 1.f : d.scal[3];
     const bool multi = d.n_src > 1;
     T* p = reinterpret_cast<T*>(d.p);
     const T* g0 = reinterpret_cast<const T*>(d.g0);
@@ -596,7 +604,7 @@ __device__ void apply_tile(const Hot& d, const LaunchCommon& c, const Smem& s,
                 const long long off = (long long)r * d.cols + c0;
                 if (!multi) rg[u].load(g0 + off);
                 ri[u].load(d.idx + off);
-                rp[u].load(p + off);
+                if (!emit) rp[u].load(p + off);
             }
         }
 #pragma unroll
@@ -614,19 +622,24 @@ __device__ void apply_tile(const Hot& d, const LaunchCommon& c, const Smem& s,
                 for (int e = 0; e < VEC; ++e) g[e] = __fmul_rn(g[e], gs);
             }
             ri[u].get(ix);
-            rp[u].get(pf);
+            if (!emit) rp[u].get(pf);
             const long long blk = block_of(d, r, c0);
             const float mo = d.mag[blk], mn = d.mag_new[blk];
             const float inv = mn > 0.f ? __frcp_rn(mn) : 0.f;
-            const float rf = d.rfac[r];
+            const float rf = emit ? 0.f : d.rfac[r];
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
                 float m = ema_momentum(rep_load(s.cb, ix[e]), mo, g[e], d.beta1, d.omb1);
                 int k = quantise(__fmul_rn(m, inv), s, c, off + e);
                 ix[e] = k;
-                const float h = __fadd_rn(__fmul_rn(rf, cf[e]), d.eps);
-                const float step = __fdividef(inv_bc1, h);
-                pf[e] = apply_one<T>(pf[e], __fmul_rn(rep_load(s.cb, k), mn), step, lr, wdf);
+                const float q = __fmul_rn(rep_load(s.cb, k), mn);
+                if (emit) {
+                    pf[e] = (d.row_only == 3) ? __fadd_rn(__fmul_rn(q, d.beta1), __fmul_rn(g[e], d.omb1)) : q;
+                } else {
+                    const float h = __fadd_rn(__fmul_rn(rf, cf[e]), d.eps);
+                    const float step = __fdividef(inv_bc1, h);
+                    pf[e] = apply_one<T>(pf[e], q, step, lr, wdf);
+                }
             }
             store_index<VEC>(d.idx + off, ix);
             store_param<T, VEC>(p + off, pf);

@@ -47,7 +47,9 @@ struct alignas(16) TensorDesc {
     int mode;                         // block path: 0 thread/block, 1 warp/block, 2 CTA/block
     int vec;                          // 1: 8-wide vector path allowed, 0: scalar path
     int world, rank;                  // exchange participants (world <= 1: no exchange)
-    int row_only;                     // 1: second moment per row only (block path as [nb, period])
+    int row_only;                     // 1: second moment per row only (block path as [nb, period]);
+                                      // 2 / 3: momentum emit (Muon): no second moment, p receives the dense
+                                      // new momentum (3: with the Nesterov look-ahead)
     float beta1, omb1, beta2, omb2, eps, src_scale;
 };
 

@@ -160,6 +160,7 @@ class Item:
     scal_ptr: int = 0                 # device address of the scalar row (capturable), or 0
     shard: Optional[ShardExchange] = None
     row_only: bool = False            # block-path tensor run through the two-phase kernels
+    emit: int = 0                     # 2: write the dense new momentum into p (Muon); 3: + Nesterov
 
 
 def two_phase_block(period: int, nb: int) -> bool:
@@ -197,7 +198,7 @@ class Plan:
         for it in items:
             if kind == "factored":
                 nb = it.p.numel() // it.period
-                rows, cols = (nb, it.period) if it.row_only else it.p.shape
+                rows, cols = (nb, it.period) if (it.row_only or it.emit) else it.p.shape
                 sizes.append((nb, rows, cols, rows, cols))
             else:
                 sizes.append((0, 0, 0, 0, 0))
@@ -243,8 +244,12 @@ class Plan:
                 nb, nr, nc, _, _ = sizes[i]
                 rows, cols = nr, nc
                 d.rows, d.cols = rows, cols
-                d.row_only = int(it.row_only)
-                if it.row_only:
+                d.row_only = int(it.emit) if it.emit else int(it.row_only)
+                if it.emit:
+                    d.total_rows = rows
+                    d.v0 = st["m_magnitude"].data_ptr()      # unused by the emit path
+                    d.v1 = st["m_magnitude"].data_ptr()
+                elif it.row_only:
                     d.total_rows = rows
                     d.v0 = st["vmean"].data_ptr()
                     d.v1 = st["vmean"].data_ptr()
@@ -276,7 +281,7 @@ class Plan:
                 d.rows_per_tile = d.trows * 16
                 n_row_tiles = (rows + d.rows_per_tile - 1) // d.rows_per_tile
                 tiles = d.n_col_tiles * n_row_tiles
-                sh = None if it.row_only else it.shard
+                sh = None if (it.row_only or it.emit) else it.shard
                 if sh is not None and sh.world > 1:
                     d.world, d.rank = sh.world, sh.rank
                     d.xchg_local = sh.xchg_local
@@ -319,8 +324,8 @@ class Plan:
             gp = tuple(g.ptrs) if isinstance(g, PeerGrad) else (g.data_ptr(),)
             st = it.state
             sig.append((it.p.data_ptr(), gp, st["m_codebook"].data_ptr(), st["m_magnitude"].data_ptr(),
-                        (st.get("v_row") if "v_row" in st else st["vmean"]).data_ptr(),
-                        it.period, it.scal_ptr, tuple(it.p.shape), it.beta1, it.beta2, it.eps, it.row_only))
+                        (st["v_row"] if "v_row" in st else st.get("vmean", st["m_magnitude"])).data_ptr(),
+                        it.period, it.scal_ptr, tuple(it.p.shape), it.beta1, it.beta2, it.eps, it.row_only, it.emit))
         return tuple(sig)
 
     def run(self, items: List[Item], codebook: torch.Tensor, thr: torch.Tensor, lut: torch.Tensor, *,
@@ -361,8 +366,35 @@ class PlanCache:
             self.rebuilds += 1
         return plan
 
+    def get_keyed(self, key, kind: str, items: List[Item]) -> Plan:
+        """Like :meth:`get` but with a caller-chosen cache key (one plan per tensor)."""
+        sig = Plan.signature_of(items)
+        plan = self._plans.get(key)
+        if plan is None or plan.signature != sig:
+            plan = Plan(kind, items, items[0].p.device, items[0].p.dtype)
+            self._plans[key] = plan
+            self.rebuilds += 1
+        return plan
+
     def clear(self) -> None:
         self._plans.clear()
+
+
+_EMIT_CACHE = PlanCache()
+
+
+def momentum_emit(grad, state: Dict[str, Any], out: torch.Tensor, codebook: torch.Tensor,
+                  thr: torch.Tensor, lut: torch.Tensor, *, beta: float, nesterov: bool,
+                  gscale: Optional[torch.Tensor] = None, cache: Optional["PlanCache"] = None) -> torch.Tensor:
+    """Muon momentum on the GPU: advance the quantised EMA of ``grad`` (in ``state``) and write the
+    dense new momentum (with the Nesterov look-ahead if asked) into ``out`` (same dtype as grad)."""
+    item = Item(p=out.view(-1), grad=grad.reshape(-1) if torch.is_tensor(grad) else grad, state=state,
+                period=int(state["automatic_period"]), beta1=beta, beta2=0.0, eps=0.0,
+                emit=3 if nesterov else 2)
+    cache = cache if cache is not None else _EMIT_CACHE
+    plan = cache.get_keyed(("emit", id(state)), "factored", [item])
+    plan.run([item], codebook, thr, lut, gscale=gscale)
+    return out
 
 
 def reduce_sources(out: Optional[torch.Tensor], ptrs: Sequence[int], numel: int, scale: float,

@@ -163,6 +163,16 @@ class GefenMuon(Gefen):
         cb = self._gefen_codebook_on(grad.device)
         if cb is None:
             raise ValueError("Expected Gefen codebook to be initialized before the Muon momentum update.")
+        if self._fused_for(grad) and grad.dtype in (torch.bfloat16, torch.float16, torch.float32):
+            # one multi-pass-free kernel sequence: block maxima, then requantise + dense emit
+            from ..ops import update as _u
+
+            dev = grad.device
+            out = torch.empty(grad.shape, dtype=grad.dtype, device=dev)
+            _u.momentum_emit(grad.contiguous(), state, out, cb, self._gefen_thresholds_on(dev),
+                             self._gefen_codebook_lut_on(dev), beta=beta, nesterov=bool(group["nesterov"]),
+                             gscale=self._grad_scale_tensor(dev))
+            return out if out.dtype == torch.bfloat16 else out.to(torch.bfloat16)
         gv = F_.partition_view(grad.reshape(-1), state["automatic_period"])
         q = F_.momentum_requantize_(cb, state["m_codebook"], state["m_magnitude"], gv, beta,
                                     self._pending_grad_scale)

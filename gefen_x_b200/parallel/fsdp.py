@@ -119,7 +119,7 @@ class ShardedTrainer:
                  factored_v_2d: bool = True, rs_mode: Optional[str] = None, seed: int = 0,
                  optimizer: str = "gefen", global_codebook: bool = True, gather_ctas: int = 64,
                  wait_iters: int = 8_000_000, opt_kwargs: Optional[dict] = None,
-                 ag_gemm: bool = False, ag_fetch_ctas: int = 16):
+                 ag_gemm: bool = False, ag_fetch_ctas: int = 16, muon_kwargs: Optional[dict] = None):
         self.cfg = cfg
         self.world, self.rank = int(world), int(rank)
         self.device = torch.device(device if device is not None else
@@ -167,6 +167,13 @@ class ShardedTrainer:
             arena_bytes += xchg_floats * 4 + n_flag_slots * world * 4 + n2d * 512 + (1 << 20)
         else:
             arena_bytes = 1 << 12
+        self.hybrid = optimizer == "muon_hybrid"
+        muon_region_bytes = 0
+        if self.hybrid:
+            from .muon_sharded import owned_bytes
+
+            muon_region_bytes = owned_bytes(self.all_groups, world, esz)
+            arena_bytes += muon_region_bytes + 4096
         self.arena = SymmetricArena(arena_bytes, self.device, world, rank, group)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.flags = FlagBoard(self.arena, n_flag_slots, self.status, wait_iters)
@@ -174,6 +181,10 @@ class ShardedTrainer:
         # flag slots: [0, n_groups) gradients of group ready; then named slots
         self.SLOT_PARAMS = len(self.all_groups)
         self.SLOT_NORM = len(self.all_groups) + 1
+        self.SLOT_MUON = len(self.all_groups) + 2
+        self._muon_region = None
+        if self.hybrid:
+            self._muon_region, self._muon_region_off = self.arena.alloc(max(muon_region_bytes, 256), torch.uint8)
         self._next_param_slot = len(self.all_groups) + 4
 
         # ---- buffers -------------------------------------------------------
@@ -223,8 +234,9 @@ class ShardedTrainer:
         self._tok_dev = None
 
         # ---- optimizer -----------------------------------------------------
+        self.muon = None
         self._build_optimizer(optimizer, lr, betas, eps, weight_decay, factored_v_2d,
-                              global_codebook, opt_kwargs or {})
+                              global_codebook, opt_kwargs or {}, muon_kwargs or {})
         if world > 1:
             self.arena.barrier()
 
@@ -335,14 +347,19 @@ class ShardedTrainer:
     # optimizer wiring
     # ------------------------------------------------------------------
     def _build_optimizer(self, kind, lr, betas, eps, weight_decay, factored_v_2d, global_codebook,
-                         opt_kwargs) -> None:
+                         opt_kwargs, muon_kwargs) -> None:
         from ..optim.gefen import Gefen
+        from ..optim.params import is_muon_param
 
         named = []
         self._param_meta: Dict[torch.Tensor, Tuple[Group, ParamSpec]] = {}
         self._grad_cache: Dict[torch.Tensor, object] = {}
+        self._muon_names = set()
         for g in self.all_groups:
             for sp in g.specs:
+                if self.hybrid and len(sp.shape) == 2 and is_muon_param(sp.name, torch.empty(0, 0)):
+                    self._muon_names.add(sp.name)
+                    continue
                 rows = sp.shard_rows[self.rank]
                 off = sp.shard_off[self.rank]
                 view = g.shard_w[off:off + rows * sp.cols]
@@ -350,9 +367,21 @@ class ShardedTrainer:
                 named.append((sp.name, view))
                 self._param_meta[view] = (g, sp)
         self.named_shards = named
-        if kind != "gefen":
-            raise ValueError("ShardedTrainer drives the Gefen optimizer; got {!r}".format(kind))
+        if kind not in ("gefen", "muon_hybrid"):
+            raise ValueError("ShardedTrainer drives 'gefen' or 'muon_hybrid'; got {!r}".format(kind))
         fused = self.device.type == "cuda"
+        if self.hybrid:
+            # Muon on the hidden matrices (owner-computed, see parallel.muon_sharded); the Gefen
+            # backup (embeddings, head, norms) keeps the block second moment as in the reference
+            from .muon_sharded import ShardedMuon
+
+            mk = dict(ns_schedule="tuned3", adjust_lr_fn="match_rms_adamw", normuon=True)
+            mk.update(muon_kwargs)
+            m_lr = mk.pop("lr", lr)
+            m_wd = mk.pop("weight_decay", weight_decay)
+            factored_v_2d = False
+            self.muon = ShardedMuon(self, lr=m_lr, weight_decay=m_wd, region=self._muon_region,
+                                    region_off=self._muon_region_off, **mk)
         self.opt = Gefen(named, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                          factored_v_2d=factored_v_2d, fused=fused, **opt_kwargs)
         self.opt._grad_source = self._grad_source
@@ -476,7 +505,15 @@ class ShardedTrainer:
         t = self.step_count
         code_dev = self.device
         if self.world == 1:
-            if self.clip and self.device.type != "cuda":
+            if self.hybrid:
+                esz = g.full_g.element_size()
+                if self.clip:
+                    for sp in g.specs:
+                        if sp.name not in self._muon_names:
+                            U.reduce_sources(None, [g.full_g.data_ptr() + sp.full_off * esz],
+                                             sp.rows * sp.cols, 1.0, self.norm_partials, self.dtype, code_dev)
+                self.muon.reduce_group(gi)
+            elif self.clip and self.device.type != "cuda":
                 self.norm_partials[0] += g.full_g.float().square().sum()
             elif self.clip:
                 U.reduce_sources(None, [g.full_g.data_ptr()], g.full_numel, 1.0, self.norm_partials,
@@ -492,7 +529,7 @@ class ShardedTrainer:
                 esz = g.full_g.element_size()
                 for sp in g.specs:
                     n = sp.shard_rows[self.rank] * sp.cols
-                    if n == 0:
+                    if n == 0 or sp.name in self._muon_names:
                         continue
                     src_off, _ = g.local_slice(sp, self.rank)
                     ptrs = self.arena.peer_ptrs(g.full_g_off + src_off * esz)
@@ -502,6 +539,8 @@ class ShardedTrainer:
                         out = g.stash_g[off:off + n]
                     U.reduce_sources(out, ptrs, n, 1.0 / self.world,
                                      self.norm_partials if self.clip else None, self.dtype, code_dev)
+            if self.hybrid:
+                self.muon.reduce_group(gi)
 
     def _finish_norm(self) -> None:
         """Global gradient norm -> clip coefficient on the device (no host sync)."""
@@ -623,6 +662,8 @@ class ShardedTrainer:
         # ---- optimizer ---------------------------------------------------
         self.opt._exchange_epoch = t
         self.opt.step()
+        if self.muon is not None:
+            self.muon.step(t)
         if multi:
             self.flags.signal(self.SLOT_PARAMS, t)
             self.ring_owner = [-1] * len(self.ring)
@@ -646,7 +687,8 @@ class ShardedTrainer:
     def state_bytes_per_param(self) -> float:
         """Optimizer-state bytes held by this rank divided by the parameters it owns."""
         own = sum(g.shard_numel[self.rank] for g in self.all_groups)
-        return self.opt.state_bytes() / max(1, own)
+        total = self.opt.state_bytes() + (self.muon.state_bytes() if self.muon is not None else 0)
+        return total / max(1, own)
 
 
 class _LocalGrad(U.LocalGrad):

@@ -3,7 +3,7 @@
 Trains a small decoder on WORLD_SIZE GPUs through ``ShardedTrainer`` and writes the
 per-step losses of every rank (gathered on rank 0) to the JSON file given as argv[1].
 argv[2]: rs_mode ("stash" | "fused"), argv[3]: clip ("1.0" or "none"), argv[4]: "ag" turns the
-all-gather-fused QKV projection on.
+all-gather-fused QKV projection on, "hybrid" trains with the sharded Muon hybrid.
 """
 import json
 import os
@@ -22,6 +22,7 @@ from gefen_x_b200.parallel.fsdp import ShardedTrainer  # noqa: E402
 def main():
     out_path, rs_mode, clip = sys.argv[1], sys.argv[2], sys.argv[3]
     ag = len(sys.argv) > 4 and sys.argv[4] == "ag"
+    hybrid = len(sys.argv) > 4 and sys.argv[4] == "hybrid"
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
     local = int(os.environ["LOCAL_RANK"])
@@ -31,7 +32,8 @@ def main():
     cfg = get_config("tiny-llama", qk_norm=True, hidden=256, ffn=512, n_layers=3)
     tr = ShardedTrainer(cfg, device=dev, dtype=torch.bfloat16, world=world, rank=rank, lr=6e-4,
                         weight_decay=0.01, clip_grad_norm=None if clip == "none" else float(clip),
-                        rs_mode=rs_mode, seed=5, wait_iters=20_000_000, ag_gemm=ag)
+                        rs_mode=rs_mode, seed=5, wait_iters=20_000_000, ag_gemm=ag,
+                        optimizer="muon_hybrid" if hybrid else "gefen")
     g = torch.Generator().manual_seed(2)
     tok_all = torch.randint(0, cfg.vocab_size, (world * 2, 129), generator=g)
     tok = tok_all[rank * 2:(rank + 1) * 2].to(dev)

@@ -25,21 +25,21 @@ def _free_port():
     return port
 
 
-def _single_gpu_losses(world, clip):
+def _single_gpu_losses(world, clip, optimizer="gefen"):
     from gefen_x_b200.models.decoder import get_config
     from gefen_x_b200.parallel.fsdp import ShardedTrainer
 
     cfg = get_config("tiny-llama", qk_norm=True, hidden=256, ffn=512, n_layers=3)
     dev = torch.device("cuda", 0)
     tr = ShardedTrainer(cfg, device=dev, dtype=torch.bfloat16, lr=6e-4, weight_decay=0.01,
-                        clip_grad_norm=clip, seed=5)
+                        clip_grad_norm=clip, seed=5, optimizer=optimizer)
     g = torch.Generator().manual_seed(2)
     tok = torch.randint(0, cfg.vocab_size, (world * 2, 129), generator=g).to(dev)
     return [float(tr.step(tok[:, :-1], tok[:, 1:]).item()) for _ in range(12)]
 
 
 @pytest.mark.parametrize("rs_mode,clip,ag", [("stash", "1.0", "plain"), ("fused", "none", "plain"),
-                                             ("stash", "1.0", "ag")])
+                                             ("stash", "1.0", "ag"), ("stash", "1.0", "hybrid")])
 def test_two_ranks_track_single_gpu(tmp_path, rs_mode, clip, ag):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
@@ -51,7 +51,8 @@ def test_two_ranks_track_single_gpu(tmp_path, rs_mode, clip, ag):
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     multi = json.load(open(out))
-    ref = _single_gpu_losses(2, None if clip == "none" else float(clip))
+    ref = _single_gpu_losses(2, None if clip == "none" else float(clip),
+                             "muon_hybrid" if ag == "hybrid" else "gefen")
     got = multi["mean_loss"]
     assert got[-1] < got[0] - 0.5
     for a, b in zip(ref, got):
