@@ -97,12 +97,13 @@ void factored_update(const Tensor& descs, const Tensor& tile_start, int64_t n_te
                      int64_t total_tiles, const Tensor& codebook, const Tensor& thr, const Tensor& lut,
                      const c10::optional<Tensor>& gscale, const c10::optional<Tensor>& status,
                      int64_t dtype, int64_t sr_seed, bool stochastic, int64_t wait_iters,
-                     int64_t phases, int64_t epoch) {
+                     int64_t phases, int64_t epoch, bool fast) {
     // phases bit 0: statistics, bit 1: EMA (+ exchange), bit 2: apply + finalize
     c10::cuda::CUDAGuard guard(descs.device());
     auto c = make_common(descs, tile_start, n_tensors, total_tiles, codebook, thr, lut, gscale, status,
                          sr_seed, stochastic, wait_iters);
     c.epoch = (uint32_t)epoch;
+    c.fast = fast ? 1 : 0;
     const int sms = sm_count();
     auto st = stream();
     if (phases & 1) check(gx::launch_factored_stats(c, (int)dtype, sms, st), "factored_stats");
@@ -413,7 +414,7 @@ TORCH_LIBRARY(gefenx, m) {
           "Tensor thr, Tensor lut, Tensor? gscale, Tensor? status, int dtype, int sr_seed, bool stochastic) -> ()");
     m.def("factored_update(Tensor descs, Tensor tile_start, int n_tensors, int total_tiles, Tensor codebook, "
           "Tensor thr, Tensor lut, Tensor? gscale, Tensor? status, int dtype, int sr_seed, bool stochastic, "
-          "int wait_iters, int phases, int epoch) -> ()");
+          "int wait_iters, int phases, int epoch, bool fast) -> ()");
     m.def("reduce_sources(Tensor? out, int[] src_ptrs, int numel, float scale, Tensor? partials, "
           "int dtype, int device_index) -> ()", &reduce_sources);
     m.def("clip_coef(Tensor partials, float max_norm, Tensor(a!) coef) -> ()");

@@ -188,12 +188,12 @@ __device__ __forceinline__ int nearest_index(float v, const QuantTables& q) {
     const uint32_t e = q.lut[lut_bucket(v)];
     int i = (int)(e & 0xffu);
     const int cnt = (int)(e >> 8);
-    if (cnt) {
-        const int hi = i + cnt;
-        do {
-            if (!(q.thr[i] < v)) break;
-            ++i;
-        } while (i < hi);
+    // first probe without a branch (thr[255] = +inf never compares below v); buckets with
+    // more than one threshold are rare and finish in the loop
+    i += (cnt > 0 && q.thr[i] < v) ? 1 : 0;
+    if (cnt > 1) {
+        const int hi = (int)(e & 0xffu) + cnt;
+        while (i < hi && i > (int)(e & 0xffu) && q.thr[i] < v) ++i;
     }
     return i;
 }

@@ -170,7 +170,9 @@ __device__ __forceinline__ float apply_one(float pf, float q, float step, float 
     return __fsub_rn(pf, __fmul_rn(__fmul_rn(q, step), lr));
 }
 
+template <bool FAST = false>
 __device__ __forceinline__ int quantise(float n, const Smem& s, const LaunchCommon& c, long long elem) {
+    if constexpr (FAST) return nearest_index(n, s.q);
     if (c.stochastic) return stochastic_index(n, s.q, sr_uniform(c.sr_seed, (uint64_t)elem));
     return nearest_index(n, s.q);
 }
@@ -324,14 +326,14 @@ __device__ __forceinline__ void runmax_flush(RunMax& r) {
     r.val = 0.f;
 }
 
-template <typename T, int VEC, int U>
+template <typename T, int VEC, int U, bool FAST = false>
 __device__ void stats_tile(const Hot& d, const Smem& s, const TileCursor& t, float gs,
                            float (&csum)[VEC], RunMax& run) {
     const int tx = threadIdx.x % d.tcols, ty = threadIdx.x / d.tcols;
     const int c0 = (t.ct * d.tcols + tx) * VEC;
     const bool act = c0 < d.cols;
     const bool uniform = run.uniform != 0;
-    const bool multi = d.n_src > 1;
+    const bool multi = FAST ? false : d.n_src > 1;
     const T* g0 = reinterpret_cast<const T*>(d.g0);
     for (int rb = t.r0 + ty; rb < t.r1; rb += d.trows * U) {
         RawVec<T, VEC> rg[U];
@@ -439,7 +441,9 @@ __device__ __forceinline__ TileCursor walk_cursor(const TileWalk& w, const Hot& 
     return t;
 }
 
-template <typename T>
+// FAST: every tensor of the plan takes the 8-wide single-source path (checked on the host),
+// so the scalar and multi-source code is not even instantiated: smaller code, fewer registers.
+template <typename T, bool FAST>
 __global__ void __launch_bounds__(kThreads, 2) factored_stats_kernel(LaunchCommon c) {
     const Smem s = load_tables(c, false);
     const float gs = c.gscale ? *c.gscale : 1.0f;
@@ -456,7 +460,9 @@ __global__ void __launch_bounds__(kThreads, 2) factored_stats_kernel(LaunchCommo
     run.uniform = warp_uniform_blocks(d, d.vec ? 8 : 1) ? 1 : 0;
     for (long long tile = T0; tile < T1; ++tile) {
         const TileCursor t = walk_cursor(w, d);
-        if (d.vec) {
+        if constexpr (FAST) {
+            stats_tile<T, 8, 8, true>(d, s, t, gs, csum8, run);
+        } else if (d.vec) {
             if (d.n_src > 1) stats_tile<T, 8, 1>(d, s, t, gs, csum8, run);
             else stats_tile<T, 8, 8>(d, s, t, gs, csum8, run);
         } else {
@@ -581,7 +587,7 @@ __global__ void __launch_bounds__(kEmaThreads) factored_ema_kernel(LaunchCommon 
     }
 }
 
-template <typename T, int VEC, int U>
+template <typename T, int VEC, int U, bool FAST = false>
 __device__ void apply_tile(const Hot& d, const LaunchCommon& c, const Smem& s,
                            const TileCursor& t, float gs, const float (&cf)[VEC]) {
     const int tx = threadIdx.x % d.tcols, ty = threadIdx.x / d.tcols;
@@ -591,7 +597,7 @@ __device__ void apply_tile(const Hot& d, const LaunchCommon& c, const Smem& s,
     // (row_only == 3: with the Nesterov look-ahead beta * m + (1 - beta) * g)
     const bool emit = d.row_only >= 2;
     const float lr = emit ? 0.f : d.scal[0], inv_bc1 = emit ? 0.f : d.scal[2], wdf = emit ? 1.f : d.scal[3];
-    const bool multi = d.n_src > 1;
+    const bool multi = FAST ? false : d.n_src > 1;
     T* p = reinterpret_cast<T*>(d.p);
     const T* g0 = reinterpret_cast<const T*>(d.g0);
     for (int rb = t.r0 + ty; rb < t.r1; rb += d.trows * U) {
@@ -630,7 +636,7 @@ __device__ void apply_tile(const Hot& d, const LaunchCommon& c, const Smem& s,
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
                 float m = ema_momentum(rep_load(s.cb, ix[e]), mo, g[e], d.beta1, d.omb1);
-                int k = quantise(__fmul_rn(m, inv), s, c, off + e);
+                int k = quantise<FAST>(__fmul_rn(m, inv), s, c, off + e);
                 ix[e] = k;
                 const float q = __fmul_rn(rep_load(s.cb, k), mn);
                 if (emit) {
@@ -655,7 +661,7 @@ __device__ __forceinline__ void load_cfac(const Hot& d, int ct, float (&cf)[VEC]
     for (int e = 0; e < VEC; ++e) cf[e] = d.row_only ? 1.0f : ((c0 + e < d.cols) ? d.cfac[c0 + e] : 0.f);
 }
 
-template <typename T>
+template <typename T, bool FAST>
 __global__ void __launch_bounds__(kThreads, 2) factored_apply_kernel(LaunchCommon c) {
     const Smem s = load_tables(c, true);
     const float gs = c.gscale ? *c.gscale : 1.0f;
@@ -673,7 +679,9 @@ __global__ void __launch_bounds__(kThreads, 2) factored_apply_kernel(LaunchCommo
             reload = false;
         }
         const TileCursor t = walk_cursor(w, d);
-        if (d.vec) {
+        if constexpr (FAST) {
+            apply_tile<T, 8, 4, true>(d, c, s, t, gs, cf8);
+        } else if (d.vec) {
             if (d.n_src > 1) apply_tile<T, 8, 1>(d, c, s, t, gs, cf8);
             else apply_tile<T, 8, 4>(d, c, s, t, gs, cf8);
         } else {
@@ -803,7 +811,8 @@ cudaError_t launch_factored_stats(const LaunchCommon& c, int dtype, int sm_count
     const int grid = min(c.total_tiles, sm_count * 4);
     return dispatch(dtype, [&](auto* tag) {
         using T = std::remove_pointer_t<decltype(tag)>;
-        factored_stats_kernel<T><<<grid, kThreads, kSmemStats, st>>>(c);
+        if (c.fast) factored_stats_kernel<T, true><<<grid, kThreads, kSmemStats, st>>>(c);
+        else factored_stats_kernel<T, false><<<grid, kThreads, kSmemStats, st>>>(c);
         return cudaGetLastError();
     });
 }
@@ -819,8 +828,13 @@ cudaError_t launch_factored_apply(const LaunchCommon& c, int dtype, int sm_count
     const int grid = min(c.total_tiles, sm_count * 2);
     return dispatch(dtype, [&](auto* tag) {
         using T = std::remove_pointer_t<decltype(tag)>;
-        cudaFuncSetAttribute(factored_apply_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemFull);
-        factored_apply_kernel<T><<<grid, kThreads, kSmemFull, st>>>(c);
+        if (c.fast && !c.stochastic) {
+            cudaFuncSetAttribute(factored_apply_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemFull);
+            factored_apply_kernel<T, true><<<grid, kThreads, kSmemFull, st>>>(c);
+        } else {
+            cudaFuncSetAttribute(factored_apply_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemFull);
+            factored_apply_kernel<T, false><<<grid, kThreads, kSmemFull, st>>>(c);
+        }
         return cudaGetLastError();
     });
 }

@@ -67,6 +67,7 @@ struct LaunchCommon {
     int stochastic;
     long long wait_iters;             // bound of every peer wait
     uint32_t epoch;                   // value the exchange flags must reach in this launch
+    int fast;                         // every tensor: 8-wide path, one gradient source
 };
 
 // All launchers return the cudaError_t of the launch.

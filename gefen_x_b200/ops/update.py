@@ -315,6 +315,10 @@ class Plan:
         self.descs = host.to(device)
         self.tile_start = torch.tensor(tile_start, dtype=torch.int32).to(device)
         self.uses_host_scalars = any(not it.scal_ptr for it in items)
+        stride_ = _desc_stride()
+        self.fast = kind == "factored" and all(
+            TensorDesc.from_buffer(buf, i * stride_).vec == 1 and TensorDesc.from_buffer(buf, i * stride_).n_src == 1
+            for i in range(self.n))
 
     @staticmethod
     def signature_of(items: List[Item]):
@@ -342,7 +346,7 @@ class Plan:
         if self.kind == "factored":
             ops().factored_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, thr, lut,
                                   gscale, status, code, seed, sr_seed is not None, int(wait_iters),
-                                  int(phases), int(epoch) & 0x7FFFFFFF)
+                                  int(phases), int(epoch) & 0x7FFFFFFF, bool(self.fast))
         else:
             ops().block_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, thr, lut,
                                gscale, status, code, seed, sr_seed is not None)
