@@ -8,8 +8,8 @@ Metric (the reference's headline, see its harness conventions at reference
 ``benchmarks/microbench/bench_muon_fsdp2.py:134-142``): training tokens per second
 of the whole job (all GPUs), device-timed with CUDA events as the max over ranks,
 plus the optimizer-step time and the optimizer-state bytes per parameter.
-Weak scaling: one sequence of 2048 uniform-random tokens per GPU (two for
-llama3-8b), random-init bf16 weights, Gefen with the factored second moment,
+Default model: the Llama-3-8B shape (the headline configuration), two sequences of 2048
+uniform-random tokens per GPU (one for qwen3-4b), weak scaling, random-init bf16 weights, Gefen with the factored second moment,
 lr 6e-6, global-norm clipping at 1.0.  One JSON line is printed by rank 0.
 
 For N > 1 launch with ``python -m torch.distributed.run --nproc-per-node N ...``.
@@ -38,7 +38,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="qwen3-4b")
+    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "qwen3-4b", "qwen3-1.7b", "qwen3-0.6b", "tiny-llama"])
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--batch", type=int, default=0, help="sequences per GPU (0 = the config's)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count")
@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--ag-gemm", action="store_true", help="all-gather fused into the QKV projection")
     ap.add_argument("--optimizer", default="gefen", choices=["gefen", "muon_hybrid"])
+    ap.add_argument("--gather", default="ce", choices=["ce", "kernel"],
+                    help="parameter all-gather by copy engines or by a peer-load kernel")
+    ap.add_argument("--reduce-ctas", type=int, default=148)
     return ap.parse_args()
 
 
@@ -114,6 +117,7 @@ def run_ours(args):
     trainer = ShardedTrainer(cfg, device=dev, dtype=torch.bfloat16, world=world, rank=rank,
                              lr=6e-6, clip_grad_norm=1.0, factored_v_2d=True, seed=1234,
                              rs_mode=args.rs_mode, ag_gemm=args.ag_gemm, optimizer=args.optimizer,
+                             gather_mode=args.gather, reduce_ctas=args.reduce_ctas,
                              muon_kwargs=dict(ns_schedule="standard", ns_steps=5) if args.optimizer == "muon_hybrid" else None)
     gen = torch.Generator().manual_seed(1000 + rank)
     n_batches = max(args.steps, 4)
@@ -202,6 +206,7 @@ def run_ours(args):
                                  "GefenMuonHybrid (Muon NS-5 standard, quantized momentum; Gefen backup) "
                                  "lr6e-6 clip1.0"),
                    "rs_mode": trainer.rs_mode, "ag_gemm": trainer.ag_gemm,
+                   "gather": trainer.gather_mode, "reduce_ctas": trainer.reduce_ctas,
                    "l2": "working set per step (weights+grads, GBs) exceeds the 126 MB L2"},
     }
     if rank == 0:

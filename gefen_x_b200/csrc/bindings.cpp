@@ -311,6 +311,46 @@ void comm_gather(at::IntArrayRef src_base, const Tensor& segs, int64_t n_segs, T
           "gather");
 }
 
+void comm_reduce_segments(at::IntArrayRef src_base, const Tensor& segs, int64_t n_segs,
+                          const Tensor& unit_prefix, int64_t total_units, double scale,
+                          const c10::optional<Tensor>& partials, int64_t ctas, int64_t dtype) {
+    c10::cuda::CUDAGuard guard(segs.device());
+    TORCH_CHECK(segs.is_cuda() && segs.scalar_type() == at::kByte && segs.is_contiguous());
+    TORCH_CHECK(segs.numel() >= n_segs * (int64_t)sizeof(gx::ReduceSeg));
+    TORCH_CHECK(unit_prefix.is_cuda() && unit_prefix.scalar_type() == at::kLong &&
+                unit_prefix.numel() >= n_segs + 1);
+    float* part = nullptr;
+    if (partials.has_value() && partials->defined()) {
+        TORCH_CHECK(partials->is_cuda() && partials->scalar_type() == at::kFloat &&
+                    partials->numel() >= ctas, "partials: fp32, at least `ctas` entries");
+        part = partials->data_ptr<float>();
+    }
+    void* p[8];
+    to_ptrs(src_base, p);
+    check(gx::launch_reduce_segments(p, (int)src_base.size(),
+                                     reinterpret_cast<const gx::ReduceSeg*>(segs.data_ptr()), (int)n_segs,
+                                     reinterpret_cast<const long long*>(unit_prefix.data_ptr<int64_t>()),
+                                     total_units, (float)scale, part, (int)ctas, (int)dtype, stream()),
+          "reduce_segments");
+}
+
+// One asynchronous device-to-device copy per row of a host table [n, 3] = (dst, src, bytes) on
+// the current stream: the copies run on the copy engines, so a parameter all-gather from the
+// peers' arenas takes no SM away from the GEMMs it overlaps with.
+void comm_copy_list(const Tensor& table, int64_t device_index) {
+    c10::cuda::CUDAGuard guard((c10::DeviceIndex)device_index);
+    TORCH_CHECK(!table.is_cuda() && table.scalar_type() == at::kLong && table.is_contiguous() &&
+                table.dim() == 2 && table.size(1) == 3, "table: CPU int64 [n, 3]");
+    const int64_t* t = table.data_ptr<int64_t>();
+    cudaStream_t st = stream();
+    for (int64_t i = 0; i < table.size(0); ++i) {
+        if (t[3 * i + 2] <= 0) continue;
+        check(cudaMemcpyAsync(reinterpret_cast<void*>(t[3 * i]), reinterpret_cast<const void*>(t[3 * i + 1]),
+                              (size_t)t[3 * i + 2], cudaMemcpyDeviceToDevice, st),
+              "copy_list");
+    }
+}
+
 void comm_scatter_apply(const Tensor& segs, int64_t n_segs, const Tensor& unit_prefix, int64_t total_units,
                         int64_t ctas) {
     c10::cuda::CUDAGuard guard(segs.device());
@@ -430,6 +470,9 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("comm_gather(int[] src_base, Tensor segs, int n_segs, Tensor(a!) dst, Tensor unit_prefix, "
           "int total_units, int ctas) -> ()");
     m.def("comm_scatter_apply(Tensor segs, int n_segs, Tensor unit_prefix, int total_units, int ctas) -> ()");
+    m.def("comm_reduce_segments(int[] src_base, Tensor segs, int n_segs, Tensor unit_prefix, int total_units, "
+          "float scale, Tensor? partials, int ctas, int dtype) -> ()");
+    m.def("comm_copy_list(Tensor table, int device_index) -> ()", &comm_copy_list);
     m.def("comm_allreduce_scalar(int[] slot_ptrs, int[] flag_ptrs, int rank, Tensor local_val, "
           "Tensor(a!) out, int epoch, int max_iters, Tensor? status) -> ()");
     m.def("rmsnorm_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!) rstd, float eps) -> ()");
@@ -453,6 +496,7 @@ TORCH_LIBRARY_IMPL(gefenx, CUDA, m) {
     m.impl("comm_wait", &comm_wait);
     m.impl("comm_gather", &comm_gather);
     m.impl("comm_scatter_apply", &comm_scatter_apply);
+    m.impl("comm_reduce_segments", &comm_reduce_segments);
     m.impl("comm_allreduce_scalar", &comm_allreduce_scalar);
     m.impl("rmsnorm_fwd", &rmsnorm_fwd);
     m.impl("rmsnorm_bwd", &rmsnorm_bwd);

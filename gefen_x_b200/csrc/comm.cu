@@ -65,6 +65,78 @@ __global__ void __launch_bounds__(256) gather_kernel(PtrList src_base, const Gat
     }
 }
 
+// Reduce-scatter of a table of slices: every thread keeps two 16-byte units of every source in
+// flight (2 * world peer loads), sums them in fp32 in rank order, scales, rounds to the storage
+// type and stores; the CTA adds its sum of squares into partials[blockIdx.x].
+constexpr int kReduceUnroll = 2;
+
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_segments_kernel(PtrList src_base, int world,
+                                                              const ReduceSeg* __restrict__ segs, int n_segs,
+                                                              const long long* __restrict__ unit_prefix,
+                                                              float scale, float* __restrict__ partials) {
+    constexpr int kPer = 16 / (int)sizeof(T);     // elements per 16-byte unit
+    __shared__ float red[8];
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long nthreads = (long long)gridDim.x * blockDim.x;
+    float ssq = 0.f;
+    for (int seg = 0; seg < n_segs; ++seg) {
+        const ReduceSeg s = segs[seg];
+        const long long units = unit_prefix[seg + 1] - unit_prefix[seg];
+        uint4* dp = reinterpret_cast<uint4*>(s.dst);
+        for (long long u0 = tid; u0 < units; u0 += nthreads * kReduceUnroll) {
+            uint4 v[kReduceUnroll][kMaxSrc];
+#pragma unroll
+            for (int j = 0; j < kReduceUnroll; ++j) {
+                const long long u = u0 + j * nthreads;
+#pragma unroll
+                for (int r = 0; r < kMaxSrc; ++r) {
+                    if (r < world && u < units)
+                        v[j][r] = reinterpret_cast<const uint4*>(
+                            reinterpret_cast<const char*>(src_base.p[r]) + s.src_off)[u];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kReduceUnroll; ++j) {
+                const long long u = u0 + j * nthreads;
+                if (u >= units) continue;
+                float acc[kPer];
+                const T* e0 = reinterpret_cast<const T*>(&v[j][0]);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) acc[e] = to_f<T>(e0[e]);
+#pragma unroll
+                for (int r = 1; r < kMaxSrc; ++r) {
+                    if (r < world) {
+                        const T* er = reinterpret_cast<const T*>(&v[j][r]);
+#pragma unroll
+                        for (int e = 0; e < kPer; ++e) acc[e] += to_f<T>(er[e]);
+                    }
+                }
+                uint4 o;
+                T* eo = reinterpret_cast<T*>(&o);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) {
+                    const float a = (world > 1 || scale != 1.0f) ? round_to<T>(__fmul_rn(acc[e], scale)) : acc[e];
+                    ssq += a * a;
+                    eo[e] = from_f<T>(a);
+                }
+                if (dp) dp[u] = o;
+            }
+        }
+    }
+    if (partials) {
+        ssq = warp_sum(ssq);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ssq;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t += red[i];
+            partials[blockIdx.x] += t;
+        }
+    }
+}
+
 // out[0] = sum over ranks of slot[rank][epoch & 1] after everybody has published;
 // each rank first stores its own value into its slot (two slots alternate so that a
 // fast rank's next reduction cannot overwrite a value a slow rank still has to read).
@@ -164,6 +236,32 @@ cudaError_t launch_gather(void* const* src_base, int world, const GatherSeg* seg
     int grid = (int)(want < ctas ? want : ctas);
     if (grid < 1) grid = 1;
     gather_kernel<<<grid, 256, 0, st>>>(l, segs_dev, n_segs, reinterpret_cast<char*>(dst), unit_prefix_dev);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_reduce_segments(void* const* src_base, int world, const ReduceSeg* segs_dev, int n_segs,
+                                   const long long* unit_prefix_dev, long long total_units, float scale,
+                                   float* partials, int ctas, int dtype, cudaStream_t st) {
+    if (world < 1 || world > kMaxSrc) return cudaErrorInvalidValue;
+    if (n_segs <= 0 || total_units <= 0) return cudaSuccess;
+    PtrList l{};
+    for (int i = 0; i < world; ++i) l.p[i] = src_base[i];
+    long long want = (total_units + 256 * kReduceUnroll - 1) / (256 * kReduceUnroll);
+    int grid = (int)(want < ctas ? want : ctas);
+    if (grid < 1) grid = 1;
+    switch (dtype) {
+        case 0:
+            reduce_segments_kernel<float><<<grid, 256, 0, st>>>(l, world, segs_dev, n_segs, unit_prefix_dev, scale, partials);
+            break;
+        case 1:
+            reduce_segments_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(l, world, segs_dev, n_segs, unit_prefix_dev, scale, partials);
+            break;
+        case 2:
+            reduce_segments_kernel<__half><<<grid, 256, 0, st>>>(l, world, segs_dev, n_segs, unit_prefix_dev, scale, partials);
+            break;
+        default:
+            return cudaErrorInvalidValue;
+    }
     return cudaGetLastError();
 }
 

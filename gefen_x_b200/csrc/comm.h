@@ -11,6 +11,12 @@ struct GatherSeg {
     int pad;
 };
 
+// One slice of this rank's gradient shard inside every rank's unsharded gradient buffer.
+struct ReduceSeg {
+    long long src_off;   // byte offset of the slice inside every rank's arena
+    void* dst;           // local output (same dtype) or null: only the sum of squares is wanted
+};
+
 // One parameter shard and the (possibly remote) rows of the update that belong to it.
 struct ApplySeg {
     void* p;             // local bf16 parameter shard
@@ -32,6 +38,13 @@ cudaError_t launch_wait(const unsigned* flags, int n, unsigned value, long long 
 cudaError_t launch_gather(void* const* src_base, int world, const GatherSeg* segs_dev, int n_segs,
                           void* dst, const long long* unit_prefix_dev, long long total_units, int ctas,
                           cudaStream_t st);
+// Reduce-scatter by peer loads, one launch for every slice of a table:
+// dst[i] = round(sum_r base[r][src_off + i] * scale) in 16-byte units, and (optionally) the sum
+// of squares of the rounded result, one partial per CTA, added into partials[blockIdx.x]
+// (partials must hold at least `ctas` floats).  dtype: 0 fp32, 1 bf16, 2 fp16.
+cudaError_t launch_reduce_segments(void* const* src_base, int world, const ReduceSeg* segs_dev, int n_segs,
+                                   const long long* unit_prefix_dev, long long total_units, float scale,
+                                   float* partials, int ctas, int dtype, cudaStream_t st);
 // out = sum_r value_r ; slot_ptrs[r] / flag_ptrs[r] are rank r's slot and flag array
 cudaError_t launch_allreduce_scalar(void* const* slot_ptrs, void* const* flag_ptrs, int world, int rank,
                                     const float* local_val, float* out, unsigned epoch,

@@ -93,6 +93,7 @@ struct Hot {
     const float* scal;
     int rows, cols, period, n_src, blk_mode, tcols, trows, n_col_tiles, rows_per_tile, vec, row_only;
     int small;                // numel < 2^31: 32-bit index arithmetic
+    unsigned step_blk, step_rem;   // (trows * cols) / period and % period: block advance of one row step
     float beta1, omb1, eps, src_scale;
 };
 
@@ -104,6 +105,11 @@ __device__ __forceinline__ Hot load_hot(const TensorDesc* t) {
     h.blk_mode = t->blk_mode; h.tcols = t->tcols; h.trows = t->trows; h.n_col_tiles = t->n_col_tiles;
     h.rows_per_tile = t->rows_per_tile; h.vec = t->vec; h.row_only = t->row_only;
     h.small = t->numel < 2147483647LL ? 1 : 0;
+    {
+        const unsigned long long step = (unsigned long long)h.trows * (unsigned)h.cols;
+        h.step_blk = (unsigned)(step / (unsigned)h.period);
+        h.step_rem = (unsigned)(step % (unsigned)h.period);
+    }
     h.beta1 = t->beta1; h.omb1 = t->omb1; h.eps = t->eps; h.src_scale = t->src_scale;
     return h;
 }
@@ -380,7 +386,7 @@ __device__ void stats_tile(const Hot& d, const Smem& s, const TileCursor& t, flo
                 }
             }
             rs = warp_sum(rs);
-            if ((threadIdx.x & 31) == 0 && act) atomicAdd(d.row_sq + r, rs);
+            if ((threadIdx.x & 31) == 0 && act) atomicAdd(d.row_sq + (d.row_only ? blk : (long long)r), rs);
             if (uniform) {
                 const long long b0 = __shfl_sync(0xffffffffu, blk, 0);   // lane 0 has the lowest column
                 if (b0 >= 0) {
@@ -441,10 +447,235 @@ __device__ __forceinline__ TileCursor walk_cursor(const TileWalk& w, const Hot& 
     return t;
 }
 
+
+// ---------------------------------------------------------------------------
+// fast tile loops (every tensor of the plan: 8-wide chunks, one gradient source, fewer
+// than 2^31 elements, nearest rounding)
+// ---------------------------------------------------------------------------
+// A thread walks the rows of its column chunk with a register ring of raw (unconverted)
+// chunks: the loads of the rows ahead are in flight while the current row is computed, and
+// the loop body is one chunk of eight elements, small enough to stay in the instruction
+// cache.  The block of a chunk advances incrementally (no division per row).
+struct BlockIter {
+    unsigned off;      // element offset of the chunk the iterator points at
+    int blk;           // its block
+    unsigned rem;      // off - blk * period
+};
+
+__device__ __forceinline__ BlockIter block_iter(const Hot& d, int r, int c0) {
+    BlockIter it;
+    it.off = (unsigned)r * (unsigned)d.cols + (unsigned)c0;
+    it.blk = (int)(it.off / (unsigned)d.period);
+    it.rem = it.off - (unsigned)it.blk * (unsigned)d.period;
+    return it;
+}
+__device__ __forceinline__ void block_iter_next(const Hot& d, BlockIter& it) {
+    it.off += (unsigned)d.trows * (unsigned)d.cols;
+    it.blk += (int)d.step_blk;
+    it.rem += d.step_rem;
+    if (it.rem >= (unsigned)d.period) { it.rem -= (unsigned)d.period; ++it.blk; }
+}
+
+template <typename T> struct StatsChunk {
+    RawVec<T, 8> g;
+    RawIdx<8> i;
+    int blk;
+};
+
+constexpr int kFastCtas = 3;     // resident CTAs per SM of the fast kernels
+constexpr int kStatsAhead = 2;   // rows in flight beyond the current one
+constexpr int kApplyAhead = 1;
+
+template <typename T>
+__device__ __forceinline__ void stats_tile_fast(const Hot& d, const Smem& s, const TileCursor& t, float gs,
+                                float (&csum)[8], RunMax& run) {
+    const int tx = threadIdx.x % d.tcols, ty = threadIdx.x / d.tcols;
+    const int c0 = (t.ct * d.tcols + tx) * 8;
+    const bool act = c0 < d.cols;
+    const bool uniform = run.uniform != 0;
+    const T* g0 = reinterpret_cast<const T*>(d.g0);
+    const int stride = d.trows;
+    int r = t.r0 + ty;
+    BlockIter it = block_iter(d, r, act ? c0 : 0);
+    int rf = r;                                   // row of the next fetch
+    StatsChunk<T> q[kStatsAhead + 1];
+    auto fetch = [&](StatsChunk<T>& c) {
+        if (act && rf < t.r1) {
+            c.g.load(g0 + it.off);
+            c.i.load(d.idx + it.off);
+            c.blk = it.blk;
+        } else {
+            c.blk = -1;
+        }
+        block_iter_next(d, it);
+        rf += stride;
+    };
+#pragma unroll
+    for (int k = 0; k < kStatsAhead; ++k) fetch(q[k]);
+#pragma unroll 1
+    for (; r < t.r1; r += stride) {
+        fetch(q[kStatsAhead]);
+        float amax = 0.f, rs = 0.f;
+        const int blk = q[0].blk;
+        if (act) {
+            float g[8];
+            int ix[8];
+            q[0].g.get(g);
+            q[0].i.get(ix);
+            const float mo = d.mag[blk];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float ge = __fmul_rn(g[e], gs);
+                const float m = ema_momentum(rep_load(s.cb, ix[e]), mo, ge, d.beta1, d.omb1);
+                amax = fmaxf(amax, fabsf(m));
+                const float sq = ge * ge;
+                rs += sq;
+                csum[e] += sq;
+            }
+        }
+        rs = warp_sum(rs);
+        if ((threadIdx.x & 31) == 0 && act) atomicAdd(d.row_sq + (d.row_only ? blk : r), rs);
+        if (uniform) {
+            const int b0 = __shfl_sync(0xffffffffu, blk, 0);   // lane 0 has the lowest column
+            if (b0 >= 0) {
+                if ((long long)b0 != run.blk) { runmax_flush(run); run.blk = b0; }
+                run.val = fmaxf(run.val, amax);
+            }
+        } else if (act) {
+            if ((long long)blk != run.blk) { runmax_flush(run); run.blk = blk; }
+            run.val = fmaxf(run.val, amax);
+        }
+#pragma unroll
+        for (int k = 0; k < kStatsAhead; ++k) q[k] = q[k + 1];
+    }
+}
+
+template <typename T> struct ApplyChunk {
+    RawVec<T, 8> g, p;
+    RawIdx<8> i;
+    int blk;
+};
+
+// element e (dynamic) of a raw chunk; only the rare fix-up loop uses it
+template <typename T>
+__device__ __forceinline__ float raw_elem(const RawVec<T, 8>& v, int e) {
+    if constexpr (sizeof(T) == 4) {
+        uint32_t w = v.w[0];
+#pragma unroll
+        for (int k = 1; k < 8; ++k) w = (e == k) ? v.w[k] : w;
+        return __uint_as_float(w);
+    } else {
+        uint32_t w = v.w[0];
+#pragma unroll
+        for (int k = 1; k < 4; ++k) w = ((e >> 1) == k) ? v.w[k] : w;
+        const unsigned short h = (unsigned short)((e & 1) ? (w >> 16) : (w & 0xffffu));
+        T x;
+        *reinterpret_cast<unsigned short*>(&x) = h;
+        return to_f<T>(x);
+    }
+}
+
+// MODE 0: parameter update; 2: momentum emit; 3: emit with the Nesterov look-ahead
+template <typename T, int MODE>
+__device__ __forceinline__ void apply_tile_fast(const Hot& d, const Smem& s, const TileCursor& t, float gs,
+                                const float (&cf)[8]) {
+    const int tx = threadIdx.x % d.tcols, ty = threadIdx.x / d.tcols;
+    const int c0 = (t.ct * d.tcols + tx) * 8;
+    if (c0 >= d.cols) return;
+    constexpr bool emit = MODE >= 2;
+    const float lr = emit ? 0.f : d.scal[0], inv_bc1 = emit ? 0.f : d.scal[2], wdf = emit ? 1.f : d.scal[3];
+    const float b1 = d.beta1, omb1 = d.omb1, eps = d.eps;
+    T* p = reinterpret_cast<T*>(d.p);
+    const T* g0 = reinterpret_cast<const T*>(d.g0);
+    const int stride = d.trows;
+    int r = t.r0 + ty;
+    BlockIter it = block_iter(d, r, c0);
+    int rfetch = r;
+    ApplyChunk<T> q0, q1;
+    auto fetch = [&](ApplyChunk<T>& c) {
+        if (rfetch < t.r1) {
+            c.g.load(g0 + it.off);
+            c.i.load(d.idx + it.off);
+            if (!emit) c.p.load(p + it.off);
+            c.blk = it.blk;
+        }
+        block_iter_next(d, it);
+        rfetch += stride;
+    };
+    unsigned off = it.off;                         // offset of the chunk being computed
+    const unsigned off_step = (unsigned)stride * (unsigned)d.cols;
+    static_assert(kApplyAhead == 1, "the register ring below holds one chunk ahead");
+    fetch(q0);
+#pragma unroll 1
+    for (; r < t.r1; r += stride) {
+        fetch(q1);
+        const ApplyChunk<T> c = q0;
+        const float mo = d.mag[c.blk], mn = d.mag_new[c.blk];
+        const float rf = emit ? 0.f : d.rfac[d.row_only ? c.blk : r];
+        const float inv = mn > 0.f ? __frcp_rn(mn) : 0.f;
+        float g[8], pf[8];
+        int ix[8];
+        c.g.get(g);
+        c.i.get(ix);
+        if (!emit) c.p.get(pf);
+        uint32_t many = 0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float ge = __fmul_rn(g[e], gs);
+            const float m = ema_momentum(rep_load(s.cb, ix[e]), mo, ge, b1, omb1);
+            const float v = __fmul_rn(m, inv);
+            const uint32_t en = s.q.lut[lut_bucket(v)];
+            const int lo = (int)(en & 0xffu);
+            const uint32_t cnt = en >> 8;
+            many |= cnt;
+            const int k = lo + ((cnt != 0u && s.q.thr[lo] < v) ? 1 : 0);
+            ix[e] = k;
+            const float qv = __fmul_rn(rep_load(s.cb, k), mn);
+            if (emit) {
+                pf[e] = (MODE == 3) ? __fadd_rn(__fmul_rn(qv, b1), __fmul_rn(ge, omb1)) : qv;
+            } else {
+                const float h = __fadd_rn(__fmul_rn(rf, cf[e]), eps);
+                const float step = __fdividef(inv_bc1, h);
+                pf[e] = apply_one<T>(pf[e], qv, step, lr, wdf);
+            }
+        }
+        store_index<8>(d.idx + off, ix);
+        store_param<T, 8>(p + off, pf);
+        if (many > 1u) {
+            // some bucket of this chunk holds more than one threshold: redo those elements with
+            // the full search (rare: the buckets are far narrower than the codeword spacing)
+#pragma unroll 1
+            for (int e = 0; e < 8; ++e) {
+                const float ge = __fmul_rn(raw_elem<T>(c.g, e), gs);
+                const int i0 = (int)(((e < 4 ? c.i.w[0] : c.i.w[1]) >> (8 * (e & 3))) & 0xffu);
+                const float m = ema_momentum(rep_load(s.cb, i0), mo, ge, b1, omb1);
+                const float v = __fmul_rn(m, inv);
+                if ((s.q.lut[lut_bucket(v)] >> 8) <= 1u) continue;
+                const int k = nearest_index(v, s.q);
+                const float qv = __fmul_rn(rep_load(s.cb, k), mn);
+                float o;
+                if (emit) {
+                    o = (MODE == 3) ? __fadd_rn(__fmul_rn(qv, b1), __fmul_rn(ge, omb1)) : qv;
+                } else {
+                    float cfe = cf[0];
+#pragma unroll
+                    for (int k2 = 1; k2 < 8; ++k2) cfe = (e == k2) ? cf[k2] : cfe;
+                    const float h = __fadd_rn(__fmul_rn(rf, cfe), eps);
+                    o = apply_one<T>(raw_elem<T>(c.p, e), qv, __fdividef(inv_bc1, h), lr, wdf);
+                }
+                d.idx[off + e] = (uint8_t)k;
+                p[off + e] = from_f<T>(o);
+            }
+        }
+        q0 = q1;
+        off += off_step;
+    }
+}
+
 // FAST: every tensor of the plan takes the 8-wide single-source path (checked on the host),
 // so the scalar and multi-source code is not even instantiated: smaller code, fewer registers.
 template <typename T, bool FAST>
-__global__ void __launch_bounds__(kThreads, 2) factored_stats_kernel(LaunchCommon c) {
+__global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_stats_kernel(LaunchCommon c) {
     const Smem s = load_tables(c, false);
     const float gs = c.gscale ? *c.gscale : 1.0f;
     const long long T0 = (long long)c.total_tiles * blockIdx.x / gridDim.x;
@@ -461,7 +692,7 @@ __global__ void __launch_bounds__(kThreads, 2) factored_stats_kernel(LaunchCommo
     for (long long tile = T0; tile < T1; ++tile) {
         const TileCursor t = walk_cursor(w, d);
         if constexpr (FAST) {
-            stats_tile<T, 8, 8, true>(d, s, t, gs, csum8, run);
+            stats_tile_fast<T>(d, s, t, gs, csum8, run);
         } else if (d.vec) {
             if (d.n_src > 1) stats_tile<T, 8, 1>(d, s, t, gs, csum8, run);
             else stats_tile<T, 8, 8>(d, s, t, gs, csum8, run);
@@ -518,13 +749,15 @@ __global__ void __launch_bounds__(kEmaThreads) factored_ema_kernel(LaunchCommon 
     const float inv_bc2 = d.scal[1];
     if (d.row_only >= 2) {
         // momentum-emit tensors keep no second moment: only clear the statistics scratch
-        for (int i = threadIdx.x; i < d.rows; i += kEmaThreads) d.row_sq[i] = 0.f;
+        for (long long i = threadIdx.x; i < d.nb; i += kEmaThreads) d.row_sq[i] = 0.f;
         return;
     }
     if (d.row_only) {
-        // block path seen as [nb, period]: one second-moment value per row, no column factor
-        for (int i = threadIdx.x; i < d.rows; i += kEmaThreads) {
-            const float ms = __fmul_rn(d.row_sq[i], inv_cols);
+        // block path seen as a matrix whose rows tile the blocks: one second-moment value per
+        // block (the row statistics are accumulated per block), no column factor
+        const float inv_period = 1.0f / (float)d.period;
+        for (long long i = threadIdx.x; i < d.nb; i += kEmaThreads) {
+            const float ms = __fmul_rn(d.row_sq[i], inv_period);
             const float v = __fadd_rn(__fmul_rn(d.v0[i], d.beta2), __fmul_rn(ms, d.omb2));
             d.v0[i] = v;
             d.row_sq[i] = 0.f;
@@ -632,7 +865,7 @@ __device__ void apply_tile(const Hot& d, const LaunchCommon& c, const Smem& s,
             const long long blk = block_of(d, r, c0);
             const float mo = d.mag[blk], mn = d.mag_new[blk];
             const float inv = mn > 0.f ? __frcp_rn(mn) : 0.f;
-            const float rf = emit ? 0.f : d.rfac[r];
+            const float rf = emit ? 0.f : d.rfac[d.row_only ? blk : (long long)r];
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
                 float m = ema_momentum(rep_load(s.cb, ix[e]), mo, g[e], d.beta1, d.omb1);
@@ -662,7 +895,7 @@ __device__ __forceinline__ void load_cfac(const Hot& d, int ct, float (&cf)[VEC]
 }
 
 template <typename T, bool FAST>
-__global__ void __launch_bounds__(kThreads, 2) factored_apply_kernel(LaunchCommon c) {
+__global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_apply_kernel(LaunchCommon c) {
     const Smem s = load_tables(c, true);
     const float gs = c.gscale ? *c.gscale : 1.0f;
     const long long T0 = (long long)c.total_tiles * blockIdx.x / gridDim.x;
@@ -680,7 +913,9 @@ __global__ void __launch_bounds__(kThreads, 2) factored_apply_kernel(LaunchCommo
         }
         const TileCursor t = walk_cursor(w, d);
         if constexpr (FAST) {
-            apply_tile<T, 8, 4, true>(d, c, s, t, gs, cf8);
+            if (d.row_only < 2) apply_tile_fast<T, 0>(d, s, t, gs, cf8);
+            else if (d.row_only == 2) apply_tile_fast<T, 2>(d, s, t, gs, cf8);
+            else apply_tile_fast<T, 3>(d, s, t, gs, cf8);
         } else if (d.vec) {
             if (d.n_src > 1) apply_tile<T, 8, 1>(d, c, s, t, gs, cf8);
             else apply_tile<T, 8, 4>(d, c, s, t, gs, cf8);
@@ -808,7 +1043,7 @@ cudaError_t launch_block_update(const LaunchCommon& c, int dtype, int sm_count, 
 
 cudaError_t launch_factored_stats(const LaunchCommon& c, int dtype, int sm_count, cudaStream_t st) {
     if (c.total_tiles <= 0) return cudaSuccess;
-    const int grid = min(c.total_tiles, sm_count * 4);
+    const int grid = min(c.total_tiles, sm_count * (c.fast ? kFastCtas : 4));
     return dispatch(dtype, [&](auto* tag) {
         using T = std::remove_pointer_t<decltype(tag)>;
         if (c.fast) factored_stats_kernel<T, true><<<grid, kThreads, kSmemStats, st>>>(c);
@@ -825,10 +1060,11 @@ cudaError_t launch_factored_ema(const LaunchCommon& c, cudaStream_t st) {
 
 cudaError_t launch_factored_apply(const LaunchCommon& c, int dtype, int sm_count, cudaStream_t st) {
     if (c.total_tiles <= 0) return cudaSuccess;
-    const int grid = min(c.total_tiles, sm_count * 2);
+    const bool fast = c.fast && !c.stochastic;
+    const int grid = min(c.total_tiles, sm_count * (fast ? kFastCtas : 2));
     return dispatch(dtype, [&](auto* tag) {
         using T = std::remove_pointer_t<decltype(tag)>;
-        if (c.fast && !c.stochastic) {
+        if (fast) {
             cudaFuncSetAttribute(factored_apply_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemFull);
             factored_apply_kernel<T, true><<<grid, kThreads, kSmemFull, st>>>(c);
         } else {

@@ -173,6 +173,24 @@ def _aligned(ptr: int, n: int) -> bool:
     return ptr % n == 0
 
 
+def _row_only_cols(period: int) -> int:
+    """Column count of the matrix view of a row-only tensor: a divisor of the period, so that a
+    row never straddles two blocks, near 2048 elements (one 256-thread row of 8-wide chunks)
+    so that long blocks are cut into many rows and every CTA tile holds full 16-row columns."""
+    if period <= 4096 or period % 8:
+        return period
+    best = None
+    for c in range(4096, 255, -8):
+        if period % c == 0:
+            chunks = c // 8
+            waste = min((chunks + t - 1) // t * t - chunks for t in (256, 128, 64, 32))
+            if best is None or waste < best[0]:
+                best = (waste, c)
+                if waste == 0:
+                    break
+    return best[1] if best is not None else period
+
+
 def _pick_tcols(chunks: int) -> int:
     best, best_waste = 256, None
     for t in (256, 128, 64, 32):
@@ -198,11 +216,16 @@ class Plan:
         for it in items:
             if kind == "factored":
                 nb = it.p.numel() // it.period
-                rows, cols = (nb, it.period) if (it.row_only or it.emit) else it.p.shape
-                sizes.append((nb, rows, cols, rows, cols))
+                if it.row_only or it.emit:
+                    cols = _row_only_cols(it.period)
+                    rows = it.p.numel() // cols
+                    sizes.append((nb, nb, cols, nb, cols, rows))   # row statistics are per block
+                else:
+                    rows, cols = it.p.shape
+                    sizes.append((nb, rows, cols, rows, cols, rows))
             else:
-                sizes.append((0, 0, 0, 0, 0))
-        total = sum(sum(s) for s in sizes)
+                sizes.append((0, 0, 0, 0, 0, 0))
+        total = sum(sum(s[:5]) for s in sizes)
         self.scratch = torch.zeros(max(total, 1), dtype=torch.float32, device=device)
         self.scal_dev = torch.zeros(self.n, 4, dtype=torch.float32, device=device)
         buf = (ctypes.c_ubyte * (stride * self.n))()
@@ -241,8 +264,8 @@ class Plan:
             ptr_ok = _aligned(p.data_ptr(), 16) and all(_aligned(s, 16) for s in srcs) and \
                 _aligned(st["m_codebook"].data_ptr(), 8)
             if kind == "factored":
-                nb, nr, nc, _, _ = sizes[i]
-                rows, cols = nr, nc
+                nb, nr, nc, _, _, rows = sizes[i]
+                cols = nc
                 d.rows, d.cols = rows, cols
                 d.row_only = int(it.emit) if it.emit else int(it.row_only)
                 if it.emit:
@@ -318,6 +341,7 @@ class Plan:
         stride_ = _desc_stride()
         self.fast = kind == "factored" and all(
             TensorDesc.from_buffer(buf, i * stride_).vec == 1 and TensorDesc.from_buffer(buf, i * stride_).n_src == 1
+            and TensorDesc.from_buffer(buf, i * stride_).numel < 2 ** 31 - 1
             for i in range(self.n))
 
     @staticmethod

@@ -91,6 +91,10 @@ class Group:
         return spec.full_off + r0 * spec.cols, spec.shard_rows[rank] * spec.cols
 
 
+class _ReduceSeg(ctypes.Structure):
+    _fields_ = [("src_off", ctypes.c_longlong), ("dst", ctypes.c_void_p)]
+
+
 class _GatherSeg(ctypes.Structure):
     _fields_ = [("src_off", ctypes.c_longlong), ("dst_off", ctypes.c_longlong),
                 ("src_rank", ctypes.c_int), ("pad", ctypes.c_int)]
@@ -119,7 +123,8 @@ class ShardedTrainer:
                  factored_v_2d: bool = True, rs_mode: Optional[str] = None, seed: int = 0,
                  optimizer: str = "gefen", global_codebook: bool = True, gather_ctas: int = 64,
                  wait_iters: int = 8_000_000, opt_kwargs: Optional[dict] = None,
-                 ag_gemm: bool = False, ag_fetch_ctas: int = 16, muon_kwargs: Optional[dict] = None):
+                 ag_gemm: bool = False, ag_fetch_ctas: int = 16, muon_kwargs: Optional[dict] = None,
+                 gather_mode: str = "ce", reduce_ctas: int = 148):
         self.cfg = cfg
         self.world, self.rank = int(world), int(rank)
         self.device = torch.device(device if device is not None else
@@ -130,6 +135,11 @@ class ShardedTrainer:
         if self.rs_mode not in ("stash", "fused"):
             raise ValueError("rs_mode must be 'stash' or 'fused'")
         self.gather_ctas = gather_ctas
+        if gather_mode not in ("ce", "kernel"):
+            raise ValueError("gather_mode must be 'ce' (copy engines) or 'kernel' (peer loads)")
+        self.gather_mode = gather_mode
+        self.reduce_ctas = max(1, min(int(reduce_ctas), 2048))
+        self._copy_tables: Dict[Tuple[int, int, bool], torch.Tensor] = {}
         self.ag_gemm = bool(ag_gemm) and int(world) > 1
         self.ag_fetch_ctas = int(ag_fetch_ctas)
         self.step_count = 0
@@ -340,8 +350,32 @@ class ShardedTrainer:
         for i, (so, do, r) in enumerate(segs):
             arr[i].src_off, arr[i].dst_off, arr[i].src_rank = so, do, r
         host = torch.frombuffer(arr, dtype=torch.uint8).clone()
+        copies = [(do, r, so, (prefix[i + 1] - prefix[i]) * 16) for i, (so, do, r) in enumerate(segs)]
         return (host.to(self.device), len(segs),
-                torch.tensor(prefix, dtype=torch.int64, device=self.device), prefix[-1])
+                torch.tensor(prefix, dtype=torch.int64, device=self.device), prefix[-1], copies)
+
+    def _build_reduce_table(self, g: Group) -> None:
+        """Slices of this rank's shard inside every rank's unsharded gradient buffer (one launch
+        reduces them all); Muon-routed matrices are reduced by their owners instead."""
+        esz = torch.empty((), dtype=self.dtype).element_size()
+        segs, prefix = [], [0]
+        for sp in g.specs:
+            n = sp.shard_rows[self.rank] * sp.cols
+            if n == 0 or sp.name in self._muon_names:
+                continue
+            src_off, _ = g.local_slice(sp, self.rank)
+            dst = 0
+            if self.rs_mode == "stash":
+                off = sp.shard_off[self.rank]
+                dst = g.stash_g.data_ptr() + off * esz
+            segs.append((g.full_g_off + src_off * esz, dst))
+            prefix.append(prefix[-1] + n * esz // 16)
+        arr = (_ReduceSeg * max(1, len(segs)))()
+        for i, (so, d) in enumerate(segs):
+            arr[i].src_off, arr[i].dst = so, d
+        host = torch.frombuffer(arr, dtype=torch.uint8).clone()
+        g.reduce_table = (host.to(self.device), len(segs),
+                          torch.tensor(prefix, dtype=torch.int64, device=self.device), prefix[-1])
 
     # ------------------------------------------------------------------
     # optimizer wiring
@@ -461,7 +495,17 @@ class ShardedTrainer:
     # parameter gather (all-gather by peer loads)
     # ------------------------------------------------------------------
     def _gather_into(self, g: Group, dst: torch.Tensor, rest_only: bool = False) -> None:
-        segs, n_segs, prefix, total = g.gather_tables_rest if rest_only else g.gather_tables
+        segs, n_segs, prefix, total, copies = g.gather_tables_rest if rest_only else g.gather_tables
+        if self.gather_mode == "ce":
+            key = (id(g), dst.data_ptr(), bool(rest_only))
+            table = self._copy_tables.get(key)
+            if table is None:
+                base = self.arena.base_ptrs
+                table = torch.tensor([[dst.data_ptr() + do, base[r] + so, nb] for do, r, so, nb in copies],
+                                     dtype=torch.int64).reshape(-1, 3)
+                self._copy_tables[key] = table
+            ops().comm_copy_list(table, self.device.index or 0)
+            return
         ops().comm_gather(self.arena.base_ptrs, segs, n_segs, dst, prefix, total, self.gather_ctas)
 
     def _ensure_layer(self, li: int, rest_only: bool = False) -> torch.Tensor:
@@ -526,19 +570,13 @@ class ShardedTrainer:
             self.flags.signal(gi, t)
             self.flags.wait(gi, t)
             if self.rs_mode == "stash" or self.clip:
-                esz = g.full_g.element_size()
-                for sp in g.specs:
-                    n = sp.shard_rows[self.rank] * sp.cols
-                    if n == 0 or sp.name in self._muon_names:
-                        continue
-                    src_off, _ = g.local_slice(sp, self.rank)
-                    ptrs = self.arena.peer_ptrs(g.full_g_off + src_off * esz)
-                    out = None
-                    if self.rs_mode == "stash":
-                        off = sp.shard_off[self.rank]
-                        out = g.stash_g[off:off + n]
-                    U.reduce_sources(out, ptrs, n, 1.0 / self.world,
-                                     self.norm_partials if self.clip else None, self.dtype, code_dev)
+                if not hasattr(g, "reduce_table"):
+                    self._build_reduce_table(g)
+                segs, n_segs, prefix, total = g.reduce_table
+                if n_segs:
+                    ops().comm_reduce_segments(self.arena.base_ptrs, segs, n_segs, prefix, total,
+                                               1.0 / self.world, self.norm_partials if self.clip else None,
+                                               self.reduce_ctas, U.DTYPE_CODE[self.dtype])
             if self.hybrid:
                 self.muon.reduce_group(gi)
 

@@ -3,7 +3,8 @@
 Trains a small decoder on WORLD_SIZE GPUs through ``ShardedTrainer`` and writes the
 per-step losses of every rank (gathered on rank 0) to the JSON file given as argv[1].
 argv[2]: rs_mode ("stash" | "fused"), argv[3]: clip ("1.0" or "none"), argv[4]: "ag" turns the
-all-gather-fused QKV projection on, "hybrid" trains with the sharded Muon hybrid.
+all-gather-fused QKV projection on, "hybrid" trains with the sharded Muon hybrid, "kgather"
+gathers the parameters with the peer-load kernel instead of the copy engines.
 """
 import json
 import os
@@ -23,6 +24,7 @@ def main():
     out_path, rs_mode, clip = sys.argv[1], sys.argv[2], sys.argv[3]
     ag = len(sys.argv) > 4 and sys.argv[4] == "ag"
     hybrid = len(sys.argv) > 4 and sys.argv[4] == "hybrid"
+    kgather = len(sys.argv) > 4 and sys.argv[4] == "kgather"
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
     local = int(os.environ["LOCAL_RANK"])
@@ -33,7 +35,8 @@ def main():
     tr = ShardedTrainer(cfg, device=dev, dtype=torch.bfloat16, world=world, rank=rank, lr=6e-4,
                         weight_decay=0.01, clip_grad_norm=None if clip == "none" else float(clip),
                         rs_mode=rs_mode, seed=5, wait_iters=20_000_000, ag_gemm=ag,
-                        optimizer="muon_hybrid" if hybrid else "gefen")
+                        optimizer="muon_hybrid" if hybrid else "gefen",
+                        gather_mode="kernel" if kgather else "ce", reduce_ctas=8 if kgather else 148)
     g = torch.Generator().manual_seed(2)
     tok_all = torch.randint(0, cfg.vocab_size, (world * 2, 129), generator=g)
     tok = tok_all[rank * 2:(rank + 1) * 2].to(dev)

@@ -39,7 +39,8 @@ def _single_gpu_losses(world, clip, optimizer="gefen"):
 
 
 @pytest.mark.parametrize("rs_mode,clip,ag", [("stash", "1.0", "plain"), ("fused", "none", "plain"),
-                                             ("stash", "1.0", "ag"), ("stash", "1.0", "hybrid")])
+                                             ("stash", "1.0", "ag"), ("stash", "1.0", "hybrid"),
+                                             ("stash", "1.0", "kgather")])
 def test_two_ranks_track_single_gpu(tmp_path, rs_mode, clip, ag):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
