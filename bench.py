@@ -49,6 +49,10 @@ def parse_args():
     ap.add_argument("--gather", default="ce", choices=["ce", "kernel"],
                     help="parameter all-gather by copy engines or by a peer-load kernel")
     ap.add_argument("--reduce-ctas", type=int, default=148)
+    ap.add_argument("--reduce", default="ce", choices=["ce", "kernel"],
+                    help="gradient reduce-scatter: copy engines + local sum, or peer loads in the kernel")
+    ap.add_argument("--trace", action="store_true",
+                    help="after the timed loops, print the per-phase device times of one more step (stderr)")
     return ap.parse_args()
 
 
@@ -117,7 +121,7 @@ def run_ours(args):
     trainer = ShardedTrainer(cfg, device=dev, dtype=torch.bfloat16, world=world, rank=rank,
                              lr=6e-6, clip_grad_norm=1.0, factored_v_2d=True, seed=1234,
                              rs_mode=args.rs_mode, ag_gemm=args.ag_gemm, optimizer=args.optimizer,
-                             gather_mode=args.gather, reduce_ctas=args.reduce_ctas,
+                             gather_mode=args.gather, reduce_ctas=args.reduce_ctas, reduce_mode=args.reduce,
                              muon_kwargs=dict(ns_schedule="standard", ns_steps=5) if args.optimizer == "muon_hybrid" else None)
     gen = torch.Generator().manual_seed(1000 + rank)
     n_batches = max(args.steps, 4)
@@ -187,6 +191,11 @@ def run_ours(args):
                "h2d_bytes_per_step": int(2 * B * S * 8), "d2h_bytes_per_step": 4,
                "ms_per_step": e2e_ms / args.steps, "last_loss": losses[-1] if losses else None}
     trainer.check_status()
+    if args.trace:
+        t = dev_tok[0]
+        _, phases = trainer.traced_step(t[:, :-1], t[:, 1:])
+        print("rank {} phases {}".format(rank, json.dumps({k: round(v, 2) for k, v in phases.items()})),
+              file=sys.stderr, flush=True)
     tokens = world * B * S * args.steps
     out = {
         "metric": METRIC, "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
@@ -206,7 +215,7 @@ def run_ours(args):
                                  "GefenMuonHybrid (Muon NS-5 standard, quantized momentum; Gefen backup) "
                                  "lr6e-6 clip1.0"),
                    "rs_mode": trainer.rs_mode, "ag_gemm": trainer.ag_gemm,
-                   "gather": trainer.gather_mode, "reduce_ctas": trainer.reduce_ctas,
+                   "gather": trainer.gather_mode, "reduce": trainer.reduce_mode, "reduce_ctas": trainer.reduce_ctas,
                    "l2": "working set per step (weights+grads, GBs) exceeds the 126 MB L2"},
     }
     if rank == 0:

@@ -311,7 +311,7 @@ void comm_gather(at::IntArrayRef src_base, const Tensor& segs, int64_t n_segs, T
           "gather");
 }
 
-void comm_reduce_segments(at::IntArrayRef src_base, const Tensor& segs, int64_t n_segs,
+void comm_reduce_segments(int64_t world, const Tensor& segs, int64_t n_segs,
                           const Tensor& unit_prefix, int64_t total_units, double scale,
                           const c10::optional<Tensor>& partials, int64_t ctas, int64_t dtype) {
     c10::cuda::CUDAGuard guard(segs.device());
@@ -325,9 +325,7 @@ void comm_reduce_segments(at::IntArrayRef src_base, const Tensor& segs, int64_t 
                     partials->numel() >= ctas, "partials: fp32, at least `ctas` entries");
         part = partials->data_ptr<float>();
     }
-    void* p[8];
-    to_ptrs(src_base, p);
-    check(gx::launch_reduce_segments(p, (int)src_base.size(),
+    check(gx::launch_reduce_segments((int)world,
                                      reinterpret_cast<const gx::ReduceSeg*>(segs.data_ptr()), (int)n_segs,
                                      reinterpret_cast<const long long*>(unit_prefix.data_ptr<int64_t>()),
                                      total_units, (float)scale, part, (int)ctas, (int)dtype, stream()),
@@ -470,7 +468,7 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("comm_gather(int[] src_base, Tensor segs, int n_segs, Tensor(a!) dst, Tensor unit_prefix, "
           "int total_units, int ctas) -> ()");
     m.def("comm_scatter_apply(Tensor segs, int n_segs, Tensor unit_prefix, int total_units, int ctas) -> ()");
-    m.def("comm_reduce_segments(int[] src_base, Tensor segs, int n_segs, Tensor unit_prefix, int total_units, "
+    m.def("comm_reduce_segments(int world, Tensor segs, int n_segs, Tensor unit_prefix, int total_units, "
           "float scale, Tensor? partials, int ctas, int dtype) -> ()");
     m.def("comm_copy_list(Tensor table, int device_index) -> ()", &comm_copy_list);
     m.def("comm_allreduce_scalar(int[] slot_ptrs, int[] flag_ptrs, int rank, Tensor local_val, "

@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(256) gather_kernel(PtrList src_base, const Gat
 constexpr int kReduceUnroll = 2;
 
 template <typename T>
-__global__ void __launch_bounds__(256) reduce_segments_kernel(PtrList src_base, int world,
+__global__ void __launch_bounds__(256) reduce_segments_kernel(int world,
                                                               const ReduceSeg* __restrict__ segs, int n_segs,
                                                               const long long* __restrict__ unit_prefix,
                                                               float scale, float* __restrict__ partials) {
@@ -91,9 +91,7 @@ __global__ void __launch_bounds__(256) reduce_segments_kernel(PtrList src_base, 
                 const long long u = u0 + j * nthreads;
 #pragma unroll
                 for (int r = 0; r < kMaxSrc; ++r) {
-                    if (r < world && u < units)
-                        v[j][r] = reinterpret_cast<const uint4*>(
-                            reinterpret_cast<const char*>(src_base.p[r]) + s.src_off)[u];
+                    if (r < world && u < units) v[j][r] = reinterpret_cast<const uint4*>(s.src[r])[u];
                 }
             }
 #pragma unroll
@@ -239,25 +237,23 @@ cudaError_t launch_gather(void* const* src_base, int world, const GatherSeg* seg
     return cudaGetLastError();
 }
 
-cudaError_t launch_reduce_segments(void* const* src_base, int world, const ReduceSeg* segs_dev, int n_segs,
+cudaError_t launch_reduce_segments(int world, const ReduceSeg* segs_dev, int n_segs,
                                    const long long* unit_prefix_dev, long long total_units, float scale,
                                    float* partials, int ctas, int dtype, cudaStream_t st) {
     if (world < 1 || world > kMaxSrc) return cudaErrorInvalidValue;
     if (n_segs <= 0 || total_units <= 0) return cudaSuccess;
-    PtrList l{};
-    for (int i = 0; i < world; ++i) l.p[i] = src_base[i];
     long long want = (total_units + 256 * kReduceUnroll - 1) / (256 * kReduceUnroll);
     int grid = (int)(want < ctas ? want : ctas);
     if (grid < 1) grid = 1;
     switch (dtype) {
         case 0:
-            reduce_segments_kernel<float><<<grid, 256, 0, st>>>(l, world, segs_dev, n_segs, unit_prefix_dev, scale, partials);
+            reduce_segments_kernel<float><<<grid, 256, 0, st>>>(world, segs_dev, n_segs, unit_prefix_dev, scale, partials);
             break;
         case 1:
-            reduce_segments_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(l, world, segs_dev, n_segs, unit_prefix_dev, scale, partials);
+            reduce_segments_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(world, segs_dev, n_segs, unit_prefix_dev, scale, partials);
             break;
         case 2:
-            reduce_segments_kernel<__half><<<grid, 256, 0, st>>>(l, world, segs_dev, n_segs, unit_prefix_dev, scale, partials);
+            reduce_segments_kernel<__half><<<grid, 256, 0, st>>>(world, segs_dev, n_segs, unit_prefix_dev, scale, partials);
             break;
         default:
             return cudaErrorInvalidValue;

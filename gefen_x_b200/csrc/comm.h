@@ -11,10 +11,12 @@ struct GatherSeg {
     int pad;
 };
 
-// One slice of this rank's gradient shard inside every rank's unsharded gradient buffer.
+// One slice of this rank's gradient shard and where every rank's contribution to it lies: in
+// the peers' unsharded gradient buffers (summed by peer loads) or in local staging that the copy
+// engines filled from them.
 struct ReduceSeg {
-    long long src_off;   // byte offset of the slice inside every rank's arena
-    void* dst;           // local output (same dtype) or null: only the sum of squares is wanted
+    void* dst;               // local output (same dtype) or null: only the sum of squares is wanted
+    const void* src[8];      // one source per rank, rank order
 };
 
 // One parameter shard and the (possibly remote) rows of the update that belong to it.
@@ -39,10 +41,10 @@ cudaError_t launch_gather(void* const* src_base, int world, const GatherSeg* seg
                           void* dst, const long long* unit_prefix_dev, long long total_units, int ctas,
                           cudaStream_t st);
 // Reduce-scatter by peer loads, one launch for every slice of a table:
-// dst[i] = round(sum_r base[r][src_off + i] * scale) in 16-byte units, and (optionally) the sum
-// of squares of the rounded result, one partial per CTA, added into partials[blockIdx.x]
-// (partials must hold at least `ctas` floats).  dtype: 0 fp32, 1 bf16, 2 fp16.
-cudaError_t launch_reduce_segments(void* const* src_base, int world, const ReduceSeg* segs_dev, int n_segs,
+// dst[i] = round(sum_r src[r][i] * scale) in 16-byte units, and (optionally) the sum of squares
+// of the rounded result, one partial per CTA, added into partials[blockIdx.x] (partials must
+// hold at least `ctas` floats).  dtype: 0 fp32, 1 bf16, 2 fp16.
+cudaError_t launch_reduce_segments(int world, const ReduceSeg* segs_dev, int n_segs,
                                    const long long* unit_prefix_dev, long long total_units, float scale,
                                    float* partials, int ctas, int dtype, cudaStream_t st);
 // out = sum_r value_r ; slot_ptrs[r] / flag_ptrs[r] are rank r's slot and flag array

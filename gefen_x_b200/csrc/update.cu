@@ -53,12 +53,21 @@ __device__ __forceinline__ Smem load_tables(const LaunchCommon& c, bool full) {
     s.cb = base + 16;
     float* thr = s.cb + kRepFloats;
     uint16_t* lut = reinterpret_cast<uint16_t*>(thr + kCodewords);
-    for (int i = threadIdx.x; i < kRepFloats; i += blockDim.x) s.cb[i] = c.codebook[i >> 5];
+    // each thread fetches codewords once and writes their 32 lane copies; the bucket table is
+    // copied in 16-byte pieces (few dependent global loads: this prologue is pure latency)
+    for (int i = threadIdx.x; i < kCodewords; i += blockDim.x) {
+        const float v = c.codebook[i];
+        float4* row = reinterpret_cast<float4*>(s.cb + i * 32);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) row[k] = make_float4(v, v, v, v);
+    }
     if (full) {
         for (int i = threadIdx.x; i < kCodewords; i += blockDim.x) thr[i] = c.thresholds[i];
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(c.lut);
-        uint32_t* dst = reinterpret_cast<uint32_t*>(lut);
-        for (int i = threadIdx.x; i < kLutBuckets / 2; i += blockDim.x) dst[i] = src[i];
+        const uint4* src = reinterpret_cast<const uint4*>(c.lut);
+        uint4* dst = reinterpret_cast<uint4*>(lut);
+        constexpr int kPieces = kLutBuckets * (int)sizeof(uint16_t) / 16;
+#pragma unroll 4
+        for (int i = threadIdx.x; i < kPieces; i += blockDim.x) dst[i] = src[i];
     }
     s.q.cb = s.cb;
     s.q.thr = full ? thr : nullptr;
@@ -316,8 +325,10 @@ __device__ __forceinline__ TileCursor locate(const LaunchCommon& c, int tile) {
 // one atomic per warp instead of one per row.
 struct RunMax {
     float* dst;        // mag_new of the tensor the run belongs to
+    float* sum_dst;    // row-only tensors: per-block sum of g^2 (null otherwise)
     long long blk;     // -1: empty
     float val;
+    float sum;         // per-lane partial of the block's sum of squares (row-only tensors)
     int uniform;
 };
 
@@ -325,11 +336,16 @@ __device__ __forceinline__ void runmax_flush(RunMax& r) {
     if (r.uniform) {
         const float m = warp_max(r.val);
         if ((threadIdx.x & 31) == 0 && r.blk >= 0) atomic_max_nonneg(r.dst + r.blk, m);
+        if (r.sum_dst) {
+            const float t = warp_sum(r.sum);
+            if ((threadIdx.x & 31) == 0 && r.blk >= 0) atomicAdd(r.sum_dst + r.blk, t);
+        }
     } else if (r.blk >= 0) {
         atomic_max_nonneg(r.dst + r.blk, r.val);
     }
     r.blk = -1;
     r.val = 0.f;
+    r.sum = 0.f;
 }
 
 template <typename T, int VEC, int U, bool FAST = false>
@@ -385,17 +401,21 @@ __device__ void stats_tile(const Hot& d, const Smem& s, const TileCursor& t, flo
                     csum[e] += sq;
                 }
             }
-            rs = warp_sum(rs);
-            if ((threadIdx.x & 31) == 0 && act) atomicAdd(d.row_sq + (d.row_only ? blk : (long long)r), rs);
+            if (!run.sum_dst) {
+                rs = warp_sum(rs);
+                if ((threadIdx.x & 31) == 0 && act) atomicAdd(d.row_sq + r, rs);
+            }
             if (uniform) {
                 const long long b0 = __shfl_sync(0xffffffffu, blk, 0);   // lane 0 has the lowest column
                 if (b0 >= 0) {
                     if (b0 != run.blk) { runmax_flush(run); run.blk = b0; }
                     run.val = fmaxf(run.val, amax);
+                    run.sum += rs;
                 }
             } else if (act) {
                 if (blk != run.blk) { runmax_flush(run); run.blk = blk; }
                 run.val = fmaxf(run.val, amax);
+                if (run.sum_dst) atomicAdd(run.sum_dst + blk, rs);
             }
         }
     }
@@ -438,12 +458,14 @@ __device__ __forceinline__ void walk_begin(const LaunchCommon& c, long long tile
     w.rt = local - w.ct * w.n_row_tiles;
 }
 
-__device__ __forceinline__ TileCursor walk_cursor(const TileWalk& w, const Hot& d) {
+// Cursor over `n` consecutive row tiles of the current column tile (one long row range: the
+// pipelined loops then fill and drain once per range instead of once per tile).
+__device__ __forceinline__ TileCursor walk_cursor(const TileWalk& w, const Hot& d, int n = 1) {
     TileCursor t;
     t.ti = w.ti;
     t.ct = w.ct;
     t.r0 = w.rt * d.rows_per_tile;
-    t.r1 = min(d.rows, t.r0 + d.rows_per_tile);
+    t.r1 = (int)min((long long)d.rows, (long long)t.r0 + (long long)n * d.rows_per_tile);
     return t;
 }
 
@@ -533,17 +555,21 @@ __device__ __forceinline__ void stats_tile_fast(const Hot& d, const Smem& s, con
                 csum[e] += sq;
             }
         }
-        rs = warp_sum(rs);
-        if ((threadIdx.x & 31) == 0 && act) atomicAdd(d.row_sq + (d.row_only ? blk : r), rs);
+        if (!run.sum_dst) {
+            rs = warp_sum(rs);
+            if ((threadIdx.x & 31) == 0 && act) atomicAdd(d.row_sq + r, rs);
+        }
         if (uniform) {
             const int b0 = __shfl_sync(0xffffffffu, blk, 0);   // lane 0 has the lowest column
             if (b0 >= 0) {
                 if ((long long)b0 != run.blk) { runmax_flush(run); run.blk = b0; }
                 run.val = fmaxf(run.val, amax);
+                run.sum += rs;       // only read when sum_dst is set (a row lies inside one block)
             }
         } else if (act) {
             if ((long long)blk != run.blk) { runmax_flush(run); run.blk = blk; }
             run.val = fmaxf(run.val, amax);
+            if (run.sum_dst) atomicAdd(run.sum_dst + blk, rs);
         }
 #pragma unroll
         for (int k = 0; k < kStatsAhead; ++k) q[k] = q[k + 1];
@@ -683,14 +709,16 @@ __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_stats
     if (T0 >= T1) return;
     float csum8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     float csum1[1] = {0};
-    RunMax run{nullptr, -1, 0.f, 0};
+    RunMax run{nullptr, nullptr, -1, 0.f, 0.f, 0};
     Hot d;
     TileWalk w;
     walk_begin(c, T0, w, d);
     run.dst = d.mag_new;
+    run.sum_dst = d.row_only ? d.row_sq : nullptr;
     run.uniform = warp_uniform_blocks(d, d.vec ? 8 : 1) ? 1 : 0;
-    for (long long tile = T0; tile < T1; ++tile) {
-        const TileCursor t = walk_cursor(w, d);
+    for (long long tile = T0; tile < T1;) {
+        const int n = (int)min(T1 - tile, (long long)(w.n_row_tiles - w.rt));
+        const TileCursor t = walk_cursor(w, d, n);
         if constexpr (FAST) {
             stats_tile_fast<T>(d, s, t, gs, csum8, run);
         } else if (d.vec) {
@@ -699,14 +727,16 @@ __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_stats
         } else {
             stats_tile<T, 1, 4>(d, s, t, gs, csum1, run);
         }
+        tile += n;
+        w.rt += n;
         // advance; flush the column partials when the column tile (or the tensor) changes
         bool col_change = false, tensor_change = false;
-        if (++w.rt == w.n_row_tiles) {
+        if (w.rt == w.n_row_tiles) {
             w.rt = 0;
             col_change = true;
             if (++w.ct == d.n_col_tiles) { w.ct = 0; tensor_change = true; }
         }
-        const bool last = tile + 1 == T1;
+        const bool last = tile == T1;
         if (col_change || last) {
             if (!d.row_only) {
                 const int ct_done = col_change ? (tensor_change ? d.n_col_tiles - 1 : w.ct - 1) : w.ct;
@@ -719,6 +749,7 @@ __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_stats
             d = load_hot(c.descs + w.ti);
             w.n_row_tiles = (d.rows + d.rows_per_tile - 1) / d.rows_per_tile;
             run.dst = d.mag_new;
+            run.sum_dst = d.row_only ? d.row_sq : nullptr;
             run.uniform = warp_uniform_blocks(d, d.vec ? 8 : 1) ? 1 : 0;
         }
     }
@@ -906,12 +937,13 @@ __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_apply
     TileWalk w;
     walk_begin(c, T0, w, d);
     bool reload = true;
-    for (long long tile = T0; tile < T1; ++tile) {
+    for (long long tile = T0; tile < T1;) {
         if (reload) {
             if (d.vec) load_cfac<8>(d, w.ct, cf8); else load_cfac<1>(d, w.ct, cf1);
             reload = false;
         }
-        const TileCursor t = walk_cursor(w, d);
+        const int n = (int)min(T1 - tile, (long long)(w.n_row_tiles - w.rt));
+        const TileCursor t = walk_cursor(w, d, n);
         if constexpr (FAST) {
             if (d.row_only < 2) apply_tile_fast<T, 0>(d, s, t, gs, cf8);
             else if (d.row_only == 2) apply_tile_fast<T, 2>(d, s, t, gs, cf8);
@@ -922,12 +954,14 @@ __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_apply
         } else {
             apply_tile<T, 1, 2>(d, c, s, t, gs, cf1);
         }
-        if (++w.rt == w.n_row_tiles) {
+        tile += n;
+        w.rt += n;
+        if (w.rt == w.n_row_tiles) {
             w.rt = 0;
             reload = true;
             if (++w.ct == d.n_col_tiles) {
                 w.ct = 0;
-                if (tile + 1 < T1) {
+                if (tile < T1) {
                     ++w.ti;
                     d = load_hot(c.descs + w.ti);
                     w.n_row_tiles = (d.rows + d.rows_per_tile - 1) / d.rows_per_tile;

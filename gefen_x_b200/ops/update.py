@@ -226,6 +226,22 @@ class Plan:
             else:
                 sizes.append((0, 0, 0, 0, 0, 0))
         total = sum(sum(s[:5]) for s in sizes)
+        # Work tiles: 256 threads x 8 elements x tile_k rows, the same for every tensor of the plan so
+        # that equal tile counts mean equal work.  CTAs take contiguous tile ranges (consecutive row
+        # tiles of a column tile run as one pipelined loop), so small tiles cost nothing: the tile is
+        # shrunk until the plan has enough tiles to balance the CTAs.
+        tile_k = 16
+        if kind == "factored":
+            def _tiles(k):
+                t = 0
+                for (_nb, _nr, nc, _a, _b, rows) in sizes:
+                    chunks = (nc + 7) // 8
+                    tc = _pick_tcols(chunks)
+                    tr = _THREADS // tc
+                    t += ((chunks + tc - 1) // tc) * ((rows + tr * k - 1) // (tr * k))
+                return t
+            while tile_k > 1 and _tiles(tile_k) < 8192:
+                tile_k //= 2
         self.scratch = torch.zeros(max(total, 1), dtype=torch.float32, device=device)
         self.scal_dev = torch.zeros(self.n, 4, dtype=torch.float32, device=device)
         buf = (ctypes.c_ubyte * (stride * self.n))()
@@ -301,7 +317,7 @@ class Plan:
                 d.tcols = _pick_tcols(chunks)
                 d.trows = _THREADS // d.tcols
                 d.n_col_tiles = (chunks + d.tcols - 1) // d.tcols
-                d.rows_per_tile = d.trows * 16
+                d.rows_per_tile = d.trows * tile_k
                 n_row_tiles = (rows + d.rows_per_tile - 1) // d.rows_per_tile
                 tiles = d.n_col_tiles * n_row_tiles
                 sh = None if (it.row_only or it.emit) else it.shard

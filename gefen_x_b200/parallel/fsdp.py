@@ -92,7 +92,7 @@ class Group:
 
 
 class _ReduceSeg(ctypes.Structure):
-    _fields_ = [("src_off", ctypes.c_longlong), ("dst", ctypes.c_void_p)]
+    _fields_ = [("dst", ctypes.c_void_p), ("src", ctypes.c_void_p * 8)]
 
 
 class _GatherSeg(ctypes.Structure):
@@ -124,7 +124,7 @@ class ShardedTrainer:
                  optimizer: str = "gefen", global_codebook: bool = True, gather_ctas: int = 64,
                  wait_iters: int = 8_000_000, opt_kwargs: Optional[dict] = None,
                  ag_gemm: bool = False, ag_fetch_ctas: int = 16, muon_kwargs: Optional[dict] = None,
-                 gather_mode: str = "ce", reduce_ctas: int = 148):
+                 gather_mode: str = "ce", reduce_ctas: int = 148, reduce_mode: str = "ce"):
         self.cfg = cfg
         self.world, self.rank = int(world), int(rank)
         self.device = torch.device(device if device is not None else
@@ -138,6 +138,10 @@ class ShardedTrainer:
         if gather_mode not in ("ce", "kernel"):
             raise ValueError("gather_mode must be 'ce' (copy engines) or 'kernel' (peer loads)")
         self.gather_mode = gather_mode
+        if reduce_mode not in ("ce", "kernel"):
+            raise ValueError("reduce_mode must be 'ce' (copy engines + local sum) or 'kernel' (peer loads)")
+        self.reduce_mode = reduce_mode
+        self._reduce_stage: Optional[torch.Tensor] = None
         self.reduce_ctas = max(1, min(int(reduce_ctas), 2048))
         self._copy_tables: Dict[Tuple[int, int, bool], torch.Tensor] = {}
         self.ag_gemm = bool(ag_gemm) and int(world) > 1
@@ -242,6 +246,7 @@ class ShardedTrainer:
         self.clip_coef = torch.ones(2, dtype=torch.float32, device=self.device)
         self._rope = None
         self._tok_dev = None
+        self._trace: Optional[List[Tuple[str, "torch.cuda.Event"]]] = None
 
         # ---- optimizer -----------------------------------------------------
         self.muon = None
@@ -356,26 +361,57 @@ class ShardedTrainer:
 
     def _build_reduce_table(self, g: Group) -> None:
         """Slices of this rank's shard inside every rank's unsharded gradient buffer (one launch
-        reduces them all); Muon-routed matrices are reduced by their owners instead."""
+        reduces them all); Muon-routed matrices are reduced by their owners instead.
+
+        ``reduce_mode="kernel"``: the kernel sums the slices with peer loads.  ``"ce"``: the copy
+        engines first bring the peers' slices into local staging (no SM is taken from the backward
+        GEMMs while the bytes cross NVLink), then the same kernel sums local memory."""
         esz = torch.empty((), dtype=self.dtype).element_size()
-        segs, prefix = [], [0]
+        base = self.arena.base_ptrs
+        staged = self.reduce_mode == "ce"
+        if staged and self._reduce_stage is None:
+            need = 0
+            for gg in self.all_groups:
+                own = sum(sp.shard_rows[self.rank] * sp.cols for sp in gg.specs
+                          if sp.name not in self._muon_names)
+                need = max(need, (own * esz + 255) // 256 * 256 + 256 * len(gg.specs))
+            self._reduce_stage = torch.empty(max(1, (self.world - 1) * need), dtype=torch.uint8,
+                                             device=self.device)
+            self._reduce_stage_stride = need
+        segs, prefix, copies = [], [0], []
+        cursor = 0
         for sp in g.specs:
             n = sp.shard_rows[self.rank] * sp.cols
             if n == 0 or sp.name in self._muon_names:
                 continue
             src_off, _ = g.local_slice(sp, self.rank)
+            arena_off = g.full_g_off + src_off * esz
             dst = 0
             if self.rs_mode == "stash":
                 off = sp.shard_off[self.rank]
                 dst = g.stash_g.data_ptr() + off * esz
-            segs.append((g.full_g_off + src_off * esz, dst))
+            srcs = []
+            slot = 0
+            for r in range(self.world):
+                if r == self.rank or not staged:
+                    srcs.append(base[r] + arena_off)
+                else:
+                    sptr = self._reduce_stage.data_ptr() + slot * self._reduce_stage_stride + cursor
+                    copies.append((sptr, base[r] + arena_off, n * esz))
+                    srcs.append(sptr)
+                    slot += 1
+            cursor += (n * esz + 255) // 256 * 256
+            segs.append((dst, srcs))
             prefix.append(prefix[-1] + n * esz // 16)
         arr = (_ReduceSeg * max(1, len(segs)))()
-        for i, (so, d) in enumerate(segs):
-            arr[i].src_off, arr[i].dst = so, d
+        for i, (d, srcs) in enumerate(segs):
+            arr[i].dst = d
+            for r, ptr in enumerate(srcs):
+                arr[i].src[r] = ptr
         host = torch.frombuffer(arr, dtype=torch.uint8).clone()
+        copy_table = torch.tensor(copies, dtype=torch.int64).reshape(-1, 3) if copies else None
         g.reduce_table = (host.to(self.device), len(segs),
-                          torch.tensor(prefix, dtype=torch.int64, device=self.device), prefix[-1])
+                          torch.tensor(prefix, dtype=torch.int64, device=self.device), prefix[-1], copy_table)
 
     # ------------------------------------------------------------------
     # optimizer wiring
@@ -572,9 +608,11 @@ class ShardedTrainer:
             if self.rs_mode == "stash" or self.clip:
                 if not hasattr(g, "reduce_table"):
                     self._build_reduce_table(g)
-                segs, n_segs, prefix, total = g.reduce_table
+                segs, n_segs, prefix, total, copy_table = g.reduce_table
+                if copy_table is not None:
+                    ops().comm_copy_list(copy_table, self.device.index or 0)
                 if n_segs:
-                    ops().comm_reduce_segments(self.arena.base_ptrs, segs, n_segs, prefix, total,
+                    ops().comm_reduce_segments(self.world, segs, n_segs, prefix, total,
                                                1.0 / self.world, self.norm_partials if self.clip else None,
                                                self.reduce_ctas, U.DTYPE_CODE[self.dtype])
             if self.hybrid:
@@ -614,6 +652,55 @@ class ShardedTrainer:
             out[sp.name] = flat[sp.full_off:sp.full_off + sp.rows * sp.cols].view(sp.shape)
         return out
 
+    # ------------------------------------------------------------------
+    # device-side step trace (CUDA events on the compute stream)
+    # ------------------------------------------------------------------
+    def _mark(self, name: str) -> None:
+        if self._trace is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream())
+            self._trace.append((name, ev))
+
+    def traced_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> Tuple[torch.Tensor, Dict[str, float]]:
+        """One step with CUDA events at every phase boundary of the compute stream.
+
+        Returns the loss and milliseconds per phase: ``fwd_compute`` / ``bwd_compute`` (inside the
+        layers), ``fwd_wait`` / ``bwd_wait`` (compute stream idle until a layer's gathered weights
+        arrived), ``embed_wait``, ``head``, ``tail_wait`` (waiting for the last gradient reductions
+        and the clip norm), ``optimizer`` and ``total``.  Synchronises the device.
+        """
+        if self.device.type != "cuda":
+            raise RuntimeError("traced_step needs a CUDA device")
+        self._trace = []
+        try:
+            loss = self.step(tokens, targets)
+            torch.cuda.synchronize(self.device)
+            marks = self._trace
+        finally:
+            self._trace = None
+        out: Dict[str, float] = {k: 0.0 for k in ("embed_wait", "fwd_wait", "fwd_compute", "head", "bwd_wait",
+                                                  "bwd_compute", "tail_wait", "optimizer")}
+        for (n0, e0), (n1, e1) in zip(marks[:-1], marks[1:]):
+            dt = e0.elapsed_time(e1)
+            if n1 == "embed_ready":
+                out["embed_wait"] += dt
+            elif n1.startswith("f.start"):
+                out["fwd_wait"] += dt
+            elif n1.startswith("f.end"):
+                out["fwd_compute"] += dt
+            elif n1 == "head.end":
+                out["head"] += dt
+            elif n1.startswith("b.start"):
+                out["bwd_wait"] += dt
+            elif n1.startswith("b.end") or n1 == "bwd.end":
+                out["bwd_compute"] += dt
+            elif n1 == "reduce.done":
+                out["tail_wait"] += dt
+            elif n1 == "opt.end":
+                out["optimizer"] += dt
+        out["total"] = marks[0][1].elapsed_time(marks[-1][1])
+        return loss, out
+
     @torch.no_grad()
     def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         cfg, L = self.cfg, self.cfg.n_layers
@@ -628,6 +715,7 @@ class ShardedTrainer:
         cos, sin = self._rope[1], self._rope[2]
         multi = self.world > 1
         eg = self.embed_group
+        self._mark("begin")
         if self.clip:
             if multi:
                 with torch.cuda.stream(self.reduce_stream):
@@ -644,6 +732,7 @@ class ShardedTrainer:
                 ev.record(self.comm_stream)
             self._ensure_layer(0)
             torch.cuda.current_stream().wait_event(ev)
+        self._mark("embed_ready")
         ew = self._embed_views(eg.full_w)
         egrad = self._embed_views(eg.full_g)
         emb_w = ew["model.embed_tokens.weight"]
@@ -658,9 +747,11 @@ class ShardedTrainer:
             if li + 1 < L:
                 self._ensure_layer(li + 1, rest_only=fused)
             self._wait_layer(li)
+            self._mark("f.start")
             x, sv = layer_forward(cfg, layer_views(cfg, flat), x, cos, sin, save=True,
                                   qkv_fn=self._qkv_fn(li, flat) if fused else None)
             saved.append(sv)
+            self._mark("f.end")
             self._mark_layer_done(li)
 
         # ---- head: final norm, logits, loss, and their backward -----------
@@ -678,6 +769,7 @@ class ShardedTrainer:
         dx2d, dnorm = M.rmsnorm_bwd(dhN, x2d, ew["model.norm.weight"], rstdN)
         egrad["model.norm.weight"].copy_(dnorm)
         dx = dx2d.view(B, S, cfg.hidden)
+        self._mark("head.end")
 
         # ---- backward ----------------------------------------------------
         for li in range(L - 1, -1, -1):
@@ -685,23 +777,28 @@ class ShardedTrainer:
             if li - 1 >= 0:
                 self._ensure_layer(li - 1)
             self._wait_layer(li)
+            self._mark("b.start")
             g = self.groups[li]
             dx = layer_backward(cfg, layer_views(cfg, flat), layer_views(cfg, g.full_g), saved[li],
                                 dx, cos, sin)
             saved[li] = None
+            self._mark("b.end")
             self._mark_layer_done(li)
             self._reduce_group(li)
         egrad["model.embed_tokens.weight"].index_add_(0, tok.reshape(-1), dx.reshape(T, cfg.hidden))
+        self._mark("bwd.end")
         self._reduce_group(len(self.all_groups) - 1)
         self._finish_norm()
         if multi:
             torch.cuda.current_stream().wait_stream(self.reduce_stream)
+        self._mark("reduce.done")
 
         # ---- optimizer ---------------------------------------------------
         self.opt._exchange_epoch = t
         self.opt.step()
         if self.muon is not None:
             self.muon.step(t)
+        self._mark("opt.end")
         if multi:
             self.flags.signal(self.SLOT_PARAMS, t)
             self.ring_owner = [-1] * len(self.ring)

@@ -4,7 +4,7 @@ Trains a small decoder on WORLD_SIZE GPUs through ``ShardedTrainer`` and writes 
 per-step losses of every rank (gathered on rank 0) to the JSON file given as argv[1].
 argv[2]: rs_mode ("stash" | "fused"), argv[3]: clip ("1.0" or "none"), argv[4]: "ag" turns the
 all-gather-fused QKV projection on, "hybrid" trains with the sharded Muon hybrid, "kgather"
-gathers the parameters with the peer-load kernel instead of the copy engines.
+gathers the parameters and reduces the gradients with the peer-load kernels instead of the copy engines.
 """
 import json
 import os
@@ -36,7 +36,8 @@ def main():
                         weight_decay=0.01, clip_grad_norm=None if clip == "none" else float(clip),
                         rs_mode=rs_mode, seed=5, wait_iters=20_000_000, ag_gemm=ag,
                         optimizer="muon_hybrid" if hybrid else "gefen",
-                        gather_mode="kernel" if kgather else "ce", reduce_ctas=8 if kgather else 148)
+                        gather_mode="kernel" if kgather else "ce", reduce_ctas=8 if kgather else 148,
+                        reduce_mode="kernel" if kgather else "ce")
     g = torch.Generator().manual_seed(2)
     tok_all = torch.randint(0, cfg.vocab_size, (world * 2, 129), generator=g)
     tok = tok_all[rank * 2:(rank + 1) * 2].to(dev)
