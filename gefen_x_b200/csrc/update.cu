@@ -25,6 +25,7 @@
 // column partial sums are flushed once per column tile.
 #include "common.cuh"
 #include "update.h"
+#include <cstdlib>
 #include <type_traits>
 
 namespace gx {
@@ -348,6 +349,45 @@ __device__ __forceinline__ void runmax_flush(RunMax& r) {
     r.sum = 0.f;
 }
 
+// CTA-wide flush at a point every thread of the CTA reaches (end of a tensor or of the CTA's tile
+// range): the warps' runs are merged in shared memory first, so that blocks spanning the whole
+// range (a few huge blocks per tensor) cost one atomic per CTA instead of one per warp.
+__device__ __forceinline__ void runmax_flush_cta(RunMax& r) {
+    __shared__ long long sh_blk[kThreads / 32];
+    __shared__ float sh_val[kThreads / 32], sh_sum[kThreads / 32];
+    if (!r.uniform) {
+        runmax_flush(r);
+        return;
+    }
+    const float m = warp_max(r.val);
+    const float t = r.sum_dst ? warp_sum(r.sum) : 0.f;
+    const int w = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0) { sh_blk[w] = r.blk; sh_val[w] = m; sh_sum[w] = t; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        long long cur = -1;
+        float cv = 0.f, cs = 0.f;
+        for (int i = 0; i <= kThreads / 32; ++i) {
+            const long long b = i < kThreads / 32 ? sh_blk[i] : -2;
+            if (b == cur && b >= 0) {
+                cv = fmaxf(cv, sh_val[i]);
+                cs += sh_sum[i];
+                continue;
+            }
+            if (cur >= 0) {
+                atomic_max_nonneg(r.dst + cur, cv);
+                if (r.sum_dst) atomicAdd(r.sum_dst + cur, cs);
+            }
+            cur = b;
+            if (b >= 0) { cv = sh_val[i]; cs = sh_sum[i]; }
+        }
+    }
+    __syncthreads();
+    r.blk = -1;
+    r.val = 0.f;
+    r.sum = 0.f;
+}
+
 template <typename T, int VEC, int U, bool FAST = false>
 __device__ void stats_tile(const Hot& d, const Smem& s, const TileCursor& t, float gs,
                            float (&csum)[VEC], RunMax& run) {
@@ -426,9 +466,16 @@ __device__ __forceinline__ void flush_cols(const Hot& d, int ct, float (&csum)[V
     const int tx = threadIdx.x % d.tcols;
     const int c0 = (ct * d.tcols + tx) * VEC;
     if (c0 < d.cols) {
+        if constexpr (VEC == 8) {
+            // col_sq is 16-byte aligned (the plan aligns every scratch array) and c0 % 8 == 0
+            float4* dst = reinterpret_cast<float4*>(d.col_sq + c0);
+            atomicAdd(dst, make_float4(csum[0], csum[1], csum[2], csum[3]));
+            atomicAdd(dst + 1, make_float4(csum[4], csum[5], csum[6], csum[7]));
+        } else {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-            if (csum[e] != 0.f) atomicAdd(d.col_sq + c0 + e, csum[e]);
+            for (int e = 0; e < VEC; ++e) {
+                if (csum[e] != 0.f) atomicAdd(d.col_sq + c0 + e, csum[e]);
+            }
         }
     }
 #pragma unroll
@@ -501,14 +548,14 @@ __device__ __forceinline__ void block_iter_next(const Hot& d, BlockIter& it) {
 template <typename T> struct StatsChunk {
     RawVec<T, 8> g;
     RawIdx<8> i;
+    float mo;          // old magnitude of the chunk's block (fetched with the chunk)
     int blk;
 };
 
 constexpr int kFastCtas = 3;     // resident CTAs per SM of the fast kernels
-constexpr int kStatsAhead = 2;   // rows in flight beyond the current one
 constexpr int kApplyAhead = 1;
 
-template <typename T>
+template <typename T, int kStatsAhead>
 __device__ __forceinline__ void stats_tile_fast(const Hot& d, const Smem& s, const TileCursor& t, float gs,
                                 float (&csum)[8], RunMax& run) {
     const int tx = threadIdx.x % d.tcols, ty = threadIdx.x / d.tcols;
@@ -525,6 +572,7 @@ __device__ __forceinline__ void stats_tile_fast(const Hot& d, const Smem& s, con
         if (act && rf < t.r1) {
             c.g.load(g0 + it.off);
             c.i.load(d.idx + it.off);
+            c.mo = d.mag[it.blk];
             c.blk = it.blk;
         } else {
             c.blk = -1;
@@ -544,7 +592,7 @@ __device__ __forceinline__ void stats_tile_fast(const Hot& d, const Smem& s, con
             int ix[8];
             q[0].g.get(g);
             q[0].i.get(ix);
-            const float mo = d.mag[blk];
+            const float mo = q[0].mo;
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const float ge = __fmul_rn(g[e], gs);
@@ -700,7 +748,8 @@ __device__ __forceinline__ void apply_tile_fast(const Hot& d, const Smem& s, con
 
 // FAST: every tensor of the plan takes the 8-wide single-source path (checked on the host),
 // so the scalar and multi-source code is not even instantiated: smaller code, fewer registers.
-template <typename T, bool FAST>
+// AHEAD: rows a thread keeps in flight beyond the current one (fast loops only)
+template <typename T, bool FAST, int AHEAD = 2>
 __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_stats_kernel(LaunchCommon c) {
     const Smem s = load_tables(c, false);
     const float gs = c.gscale ? *c.gscale : 1.0f;
@@ -720,7 +769,7 @@ __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_stats
         const int n = (int)min(T1 - tile, (long long)(w.n_row_tiles - w.rt));
         const TileCursor t = walk_cursor(w, d, n);
         if constexpr (FAST) {
-            stats_tile_fast<T>(d, s, t, gs, csum8, run);
+            stats_tile_fast<T, AHEAD>(d, s, t, gs, csum8, run);
         } else if (d.vec) {
             if (d.n_src > 1) stats_tile<T, 8, 1>(d, s, t, gs, csum8, run);
             else stats_tile<T, 8, 8>(d, s, t, gs, csum8, run);
@@ -743,7 +792,7 @@ __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_stats
                 if (d.vec) flush_cols<8>(d, ct_done, csum8); else flush_cols<1>(d, ct_done, csum1);
             }
         }
-        if (tensor_change || last) runmax_flush(run);
+        if (tensor_change || last) runmax_flush_cta(run);
         if (tensor_change && !last) {
             ++w.ti;
             d = load_hot(c.descs + w.ti);
@@ -1080,7 +1129,12 @@ cudaError_t launch_factored_stats(const LaunchCommon& c, int dtype, int sm_count
     const int grid = min(c.total_tiles, sm_count * (c.fast ? kFastCtas : 4));
     return dispatch(dtype, [&](auto* tag) {
         using T = std::remove_pointer_t<decltype(tag)>;
-        if (c.fast) factored_stats_kernel<T, true><<<grid, kThreads, kSmemStats, st>>>(c);
+        static const int ahead = []() {
+            const char* e = getenv("GEFENX_STATS_AHEAD");   // tuning knob: 1 (default) or 2 rows in flight
+            return (e && e[0] == '2') ? 2 : 1;
+        }();
+        if (c.fast && ahead == 1) factored_stats_kernel<T, true, 1><<<grid, kThreads, kSmemStats, st>>>(c);
+        else if (c.fast) factored_stats_kernel<T, true, 2><<<grid, kThreads, kSmemStats, st>>>(c);
         else factored_stats_kernel<T, false><<<grid, kThreads, kSmemStats, st>>>(c);
         return cudaGetLastError();
     });

@@ -225,7 +225,8 @@ class Plan:
                     sizes.append((nb, rows, cols, rows, cols, rows))
             else:
                 sizes.append((0, 0, 0, 0, 0, 0))
-        total = sum(sum(s[:5]) for s in sizes)
+        _up4 = lambda n: (n + 3) // 4 * 4                    # every scratch array starts 16-byte aligned
+        total = sum(sum(_up4(x) for x in s[:5]) for s in sizes)
         # Work tiles: 256 threads x 8 elements x tile_k rows, the same for every tensor of the plan so
         # that equal tile counts mean equal work.  CTAs take contiguous tile ranges (consecutive row
         # tiles of a column tile run as one pipelined loop), so small tiles cost nothing: the tile is
@@ -296,11 +297,11 @@ class Plan:
                     d.total_rows = it.shard.total_rows if it.shard is not None else rows
                     d.v0 = st["v_row"].data_ptr()
                     d.v1 = st["v_col"].data_ptr()
-                d.mag_new = base + 4 * cursor; cursor += nb
-                d.row_sq = base + 4 * cursor; cursor += nr
-                d.col_sq = base + 4 * cursor; cursor += nc
-                d.rfac = base + 4 * cursor; cursor += nr
-                d.cfac = base + 4 * cursor; cursor += nc
+                d.mag_new = base + 4 * cursor; cursor += _up4(nb)
+                d.row_sq = base + 4 * cursor; cursor += _up4(nr)
+                d.col_sq = base + 4 * cursor; cursor += _up4(nc)
+                d.rfac = base + 4 * cursor; cursor += _up4(nr)
+                d.cfac = base + 4 * cursor; cursor += _up4(nc)
                 P = it.period
                 if P == cols:
                     d.blk_mode = 0

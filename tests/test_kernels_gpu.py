@@ -156,7 +156,9 @@ def test_multi_source_gradient_and_clip_scale():
         oa.step()
         ob.step()
     assert torch.equal(oa.state[pa]["m_codebook"], ob.state[pb]["m_codebook"])
-    assert torch.equal(pa, pb)
+    # the column statistics are summed with atomics across CTAs (order not fixed), so the second
+    # moment, and with it the parameters, may differ in the last bit between two runs
+    torch.testing.assert_close(pa.float(), pb.float(), rtol=1.6e-2, atol=1e-5)
     # partial sums of squares + clip coefficient
     partials = torch.zeros(512, device=_dev())
     out = torch.empty(shape, dtype=torch.bfloat16, device=_dev())
