@@ -6,10 +6,11 @@ operands (tens to hundreds of MB) are rotated so that consecutive launches do no
 reuse L2-resident data.  Reports TFLOP/s and the fraction of the measured cuBLAS
 bf16 peak (``MEASURED_PEAKS.json``).
 
-    python benchmarks/microbench_gemm.py
+    python benchmarks/microbench_gemm.py [--only M,N,K] [--iters 20] [--warmup 5] [--no-library]
 """
 from __future__ import annotations
 
+import argparse
 import json
 import os
 import sys
@@ -50,9 +51,19 @@ def time_fn(fn, n_rot, iters=20, warmup=5):
 def main():
     from gefen_x_b200.ops import tcgemm
 
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="", help="M,N,K: time only this shape (NT)")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--no-library", action="store_true", help="skip the vendor-library timing")
+    args = ap.parse_args()
+    shapes = SHAPES
+    if args.only:
+        m, n, k = (int(v) for v in args.only.split(","))
+        shapes = [(m, n, k, False, False)]
     dev = torch.device("cuda", 0)
     peak = peak_tflops()
-    for m, n, k, a_t, b_t in SHAPES:
+    for m, n, k, a_t, b_t in shapes:
         n_rot = 3
         a = [torch.randn((k, m) if a_t else (m, k), device=dev).bfloat16() for _ in range(n_rot)]
         b = [torch.randn((k, n) if b_t else (n, k), device=dev).bfloat16() for _ in range(n_rot)]
@@ -66,8 +77,8 @@ def main():
             y = b[i] if b_t else b[i].t()
             torch.matmul(x, y, out=out)
 
-        t_ours = time_fn(ours, n_rot)
-        t_lib = time_fn(lib, n_rot)
+        t_ours = time_fn(ours, n_rot, args.iters, args.warmup)
+        t_lib = float("nan") if args.no_library else time_fn(lib, n_rot, args.iters, args.warmup)
         flops = 2.0 * m * n * k
         print(json.dumps({"M": m, "N": n, "K": k, "a_t": a_t, "b_t": b_t,
                           "ours_ms": t_ours, "ours_tflops": flops / t_ours / 1e9,
