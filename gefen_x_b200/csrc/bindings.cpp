@@ -403,13 +403,21 @@ void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tenso
 
 int64_t rmsnorm_bwd_partials(int64_t rows, int64_t d) { return gx::rmsnorm_bwd_partials(rows, (int)d); }
 
-void rope(Tensor x, const Tensor& cos, const Tensor& sin, int64_t seq_len, int64_t n_heads,
-          int64_t head_dim, bool inverse, bool interleaved) {
-    c10::cuda::CUDAGuard guard(x.device());
-    TORCH_CHECK(x.is_cuda() && x.is_contiguous() && cos.scalar_type() == at::kFloat);
-    check(gx::launch_rope(x.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(),
-                          x.numel() / (n_heads * head_dim), (int)seq_len, (int)n_heads, (int)head_dim,
-                          inverse, interleaved, dtype_code(x.scalar_type()), stream()),
+// dst, src: 2-D views [tokens, n_heads * head_dim] whose rows may be strided (column slices of a
+// fused projection buffer); dst may be src.
+void rope(Tensor dst, const Tensor& src, const Tensor& cos, const Tensor& sin, int64_t seq_len,
+          int64_t n_heads, int64_t head_dim, bool inverse, bool interleaved) {
+    c10::cuda::CUDAGuard guard(dst.device());
+    TORCH_CHECK(dst.is_cuda() && src.is_cuda() && cos.scalar_type() == at::kFloat && cos.is_contiguous() &&
+                sin.is_contiguous());
+    TORCH_CHECK(dst.dim() == 2 && src.dim() == 2 && dst.size(0) == src.size(0) &&
+                dst.size(1) == n_heads * head_dim && src.size(1) == n_heads * head_dim &&
+                dst.stride(1) == 1 && src.stride(1) == 1 && dst.scalar_type() == src.scalar_type(),
+                "rope: [tokens, n_heads * head_dim] views with unit inner stride");
+    check(gx::launch_rope(dst.data_ptr(), src.data_ptr(), dst.stride(0), src.stride(0),
+                          cos.data_ptr<float>(), sin.data_ptr<float>(), dst.size(0), (int)seq_len,
+                          (int)n_heads, (int)head_dim, inverse, interleaved,
+                          dtype_code(dst.scalar_type()), stream()),
           "rope");
 }
 
@@ -475,7 +483,7 @@ TORCH_LIBRARY(gefenx, m) {
           "Tensor(a!) out, int epoch, int max_iters, Tensor? status) -> ()");
     m.def("rmsnorm_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!) rstd, float eps) -> ()");
     m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor(a!) dx, Tensor(b!) dw_partial) -> ()");
-    m.def("rope(Tensor(a!) x, Tensor cos, Tensor sin, int seq_len, int n_heads, int head_dim, "
+    m.def("rope(Tensor(a!) dst, Tensor src, Tensor cos, Tensor sin, int seq_len, int n_heads, int head_dim, "
           "bool inverse, bool interleaved) -> ()");
     m.def("swiglu_fwd(Tensor gate_up, Tensor(a!) out) -> ()");
     m.def("swiglu_bwd(Tensor gate_up, Tensor dout, Tensor(a!) dgate_up) -> ()");

@@ -135,12 +135,17 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_bwd_kernel(const T* __restri
     }
 }
 
-// x: [tokens, n_heads, head_dim]; position = token % seq_len; cos/sin: [seq_len, head_dim/2]
+// Rotary embedding.  src: [tokens, n_heads, head_dim] with `src_stride` elements between tokens
+// (a column slice of a fused projection output), dst likewise with `dst_stride` (dst may be src);
+// position = token % seq_len; cos/sin: [seq_len, head_dim/2].
+// Scalar form (any even head_dim, any alignment):
 template <typename T>
-__global__ void __launch_bounds__(kThreads) rope_kernel(T* __restrict__ x, const float* __restrict__ cs,
-                                                        const float* __restrict__ sn, long long tokens,
-                                                        int seq_len, int n_heads, int head_dim, float sign,
-                                                        bool interleaved) {
+__global__ void __launch_bounds__(kThreads) rope_scalar_kernel(T* __restrict__ dst, const T* __restrict__ src,
+                                                               long long dst_stride, long long src_stride,
+                                                               const float* __restrict__ cs,
+                                                               const float* __restrict__ sn, long long tokens,
+                                                               int seq_len, int n_heads, int head_dim, float sign,
+                                                               bool interleaved) {
     const int half = head_dim >> 1;
     const long long pairs = tokens * n_heads * half;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < pairs;
@@ -148,15 +153,76 @@ __global__ void __launch_bounds__(kThreads) rope_kernel(T* __restrict__ x, const
         const int j = (int)(i % half);
         const long long th = i / half;             // token * n_heads + head
         const long long tok = th / n_heads;
+        const int head = (int)(th - tok * n_heads);
         const int pos = (int)(tok % seq_len);
         const float c = cs[(long long)pos * half + j];
         const float s = sn[(long long)pos * half + j] * sign;
-        T* base = x + th * head_dim;
+        const T* sb = src + tok * src_stride + (long long)head * head_dim;
+        T* db = dst + tok * dst_stride + (long long)head * head_dim;
         const int i0 = interleaved ? 2 * j : j;
         const int i1 = interleaved ? 2 * j + 1 : j + half;
-        const float a = to_f<T>(base[i0]), b = to_f<T>(base[i1]);
-        base[i0] = from_f<T>(a * c - b * s);
-        base[i1] = from_f<T>(b * c + a * s);
+        const float a = to_f<T>(sb[i0]), b = to_f<T>(sb[i1]);
+        db[i0] = from_f<T>(a * c - b * s);
+        db[i1] = from_f<T>(b * c + a * s);
+    }
+}
+
+// Vector form: a thread rotates eight pairs with 16-byte accesses (head_dim % 16 == 0, strides
+// and pointers 16-byte aligned).  Half-rotation layout: elements [j, j + 8) with
+// [j + half, j + half + 8); interleaved layout: two neighbouring 8-element vectors.
+template <typename T, bool INTERLEAVED>
+__global__ void __launch_bounds__(kThreads) rope_vec_kernel(T* __restrict__ dst, const T* __restrict__ src,
+                                                            long long dst_stride, long long src_stride,
+                                                            const float* __restrict__ cs,
+                                                            const float* __restrict__ sn, long long tokens,
+                                                            int seq_len, int n_heads, int head_dim, float sign) {
+    const int half = head_dim >> 1;
+    const int upr = half >> 3;                       // units (eight pairs) per head
+    const long long units = tokens * n_heads * upr;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < units;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int u = (int)(i % upr);
+        const long long th = i / upr;
+        const long long tok = th / n_heads;
+        const int head = (int)(th - tok * n_heads);
+        const int pos = (int)(tok % seq_len);
+        const int j = u * 8;                         // first pair of the unit
+        float c[8], s[8];
+        {
+            const float4* cp = reinterpret_cast<const float4*>(cs + (long long)pos * half + j);
+            const float4* sp = reinterpret_cast<const float4*>(sn + (long long)pos * half + j);
+            const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+            c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+            s[0] = s0.x; s[1] = s0.y; s[2] = s0.z; s[3] = s0.w; s[4] = s1.x; s[5] = s1.y; s[6] = s1.z; s[7] = s1.w;
+        }
+        const T* sb = src + tok * src_stride + (long long)head * head_dim;
+        T* db = dst + tok * dst_stride + (long long)head * head_dim;
+        const int o0 = INTERLEAVED ? 2 * j : j;
+        const int o1 = INTERLEAVED ? 2 * j + 8 : j + half;
+        float a[8], b[8];
+        Vec8<T>::load(sb + o0, a);
+        Vec8<T>::load(sb + o1, b);
+        if constexpr (INTERLEAVED) {
+            // pairs (a0,a1) (a2,a3) ... (b6,b7): pair p of the unit uses c[p]
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                const float x0 = a[2 * p], x1 = a[2 * p + 1];
+                a[2 * p] = x0 * c[p] - x1 * s[p] * sign;
+                a[2 * p + 1] = x1 * c[p] + x0 * s[p] * sign;
+                const float y0 = b[2 * p], y1 = b[2 * p + 1];
+                b[2 * p] = y0 * c[4 + p] - y1 * s[4 + p] * sign;
+                b[2 * p + 1] = y1 * c[4 + p] + y0 * s[4 + p] * sign;
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float x0 = a[e], x1 = b[e];
+                a[e] = x0 * c[e] - x1 * s[e] * sign;
+                b[e] = x1 * c[e] + x0 * s[e] * sign;
+            }
+        }
+        Vec8<T>::store(db + o0, a);
+        Vec8<T>::store(db + o1, b);
     }
 }
 
@@ -323,13 +389,30 @@ cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
     return cudaGetLastError();
 }
 
-cudaError_t launch_rope(void* x, const float* cs, const float* sn, long long tokens, int seq_len,
+cudaError_t launch_rope(void* dst, const void* src, long long dst_stride, long long src_stride,
+                        const float* cs, const float* sn, long long tokens, int seq_len,
                         int n_heads, int head_dim, bool inverse, bool interleaved, int dtype,
                         cudaStream_t st) {
     if (tokens <= 0) return cudaSuccess;
+    if (head_dim % 2) return cudaErrorInvalidValue;
+    const float sign = inverse ? -1.f : 1.f;
+    const int esz = dtype == 0 ? 4 : 2;
+    const bool vec = head_dim % 16 == 0 && (dst_stride * esz) % 16 == 0 && (src_stride * esz) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(dst) % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(cs) % 16 == 0 && reinterpret_cast<uintptr_t>(sn) % 16 == 0;
+    if (vec) {
+        const long long units = tokens * n_heads * (head_dim / 16);
+        const int grid = grid_for(units, kThreads, 148 * 16);
+        if (interleaved) {
+            GX_DISPATCH(dtype, (rope_vec_kernel<T, true><<<grid, kThreads, 0, st>>>((T*)dst, (const T*)src, dst_stride, src_stride, cs, sn, tokens, seq_len, n_heads, head_dim, sign)));
+        } else {
+            GX_DISPATCH(dtype, (rope_vec_kernel<T, false><<<grid, kThreads, 0, st>>>((T*)dst, (const T*)src, dst_stride, src_stride, cs, sn, tokens, seq_len, n_heads, head_dim, sign)));
+        }
+        return cudaGetLastError();
+    }
     const long long pairs = tokens * n_heads * (head_dim / 2);
     const int grid = grid_for(pairs, kThreads * 4, 148 * 16);
-    GX_DISPATCH(dtype, rope_kernel<T><<<grid, kThreads, 0, st>>>((T*)x, cs, sn, tokens, seq_len, n_heads, head_dim, inverse ? -1.f : 1.f, interleaved));
+    GX_DISPATCH(dtype, rope_scalar_kernel<T><<<grid, kThreads, 0, st>>>((T*)dst, (const T*)src, dst_stride, src_stride, cs, sn, tokens, seq_len, n_heads, head_dim, sign, interleaved));
     return cudaGetLastError();
 }
 

@@ -11,7 +11,10 @@ int rmsnorm_bwd_partials(long long rows, int d);
 cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
                                float* dw_partial, int n_partial, long long rows, int d, int dtype,
                                cudaStream_t st);
-cudaError_t launch_rope(void* x, const float* cs, const float* sn, long long tokens, int seq_len,
+// dst / src: [tokens, n_heads, head_dim] with dst_stride / src_stride elements between tokens
+// (dst may alias src)
+cudaError_t launch_rope(void* dst, const void* src, long long dst_stride, long long src_stride,
+                        const float* cs, const float* sn, long long tokens, int seq_len,
                         int n_heads, int head_dim, bool inverse, bool interleaved, int dtype,
                         cudaStream_t st);
 cudaError_t launch_swiglu_fwd(const void* gate_up, void* out, long long rows, int f, int dtype,

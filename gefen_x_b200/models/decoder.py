@@ -143,10 +143,15 @@ def layer_forward(cfg: ModelConfig, w: Dict[str, torch.Tensor], x: torch.Tensor,
         kn, k_rstd = M.rmsnorm_fwd(kc, w["self_attn.k_norm.weight"], cfg.rms_eps)
         qn_ctx = (qc, q_rstd, kc, k_rstd)
         q, k = qn, kn
+        M.rope_(q, cos, sin)
+        M.rope_(k, cos, sin)
     else:
-        q, k = q.contiguous(), k.contiguous()
-    M.rope_(q, cos, sin)
-    M.rope_(k, cos, sin)
+        # rotate straight out of the fused projection buffer (no separate unpacking copy)
+        qr = torch.empty(B, S, nq, hd, dtype=qkv.dtype, device=qkv.device)
+        kr = torch.empty(B, S, nkv, hd, dtype=qkv.dtype, device=qkv.device)
+        M.rope_into(qr.view(T, cfg.q_dim), qkv[:, :cfg.q_dim], cos, sin, S, nq, hd)
+        M.rope_into(kr.view(T, cfg.kv_dim), qkv[:, cfg.q_dim:cfg.q_dim + cfg.kv_dim], cos, sin, S, nkv, hd)
+        q, k = qr, kr
     a, actx = M.attention_fwd(q, k, v)
     a2d = a.reshape(T, cfg.q_dim)
     x2 = x2d + G.mm_nt(a2d, w["self_attn.o_proj.weight"])
@@ -195,16 +200,23 @@ def layer_backward(cfg: ModelConfig, w: Dict[str, torch.Tensor], gw: Dict[str, t
     wgrad("self_attn.o_proj.weight", dx2, saved["a"])
     da = G.mm_nn(dx2, w["self_attn.o_proj.weight"]).reshape(B, S, nq, hd)
     dq, dk, dv = M.attention_bwd(saved["actx"], da)
-    dq, dk = dq.contiguous(), dk.contiguous()
-    M.rope_(dq, cos, sin, inverse=True)
-    M.rope_(dk, cos, sin, inverse=True)
     if cfg.qk_norm:
+        dq, dk = dq.contiguous(), dk.contiguous()
+        M.rope_(dq, cos, sin, inverse=True)
+        M.rope_(dk, cos, sin, inverse=True)
         qc, q_rstd, kc, k_rstd = saved["qn"]
         dq, dwq = M.rmsnorm_bwd(dq, qc, w["self_attn.q_norm.weight"], q_rstd)
         dk, dwk = M.rmsnorm_bwd(dk, kc, w["self_attn.k_norm.weight"], k_rstd)
         put("self_attn.q_norm.weight", dwq)
         put("self_attn.k_norm.weight", dwk)
-    dqkv = torch.cat((dq.reshape(T, -1), dk.reshape(T, -1), dv.reshape(T, -1)), dim=1)
+        dqkv = torch.cat((dq.reshape(T, -1), dk.reshape(T, -1), dv.reshape(T, -1)), dim=1)
+    else:
+        # inverse rotation written straight into the fused gradient buffer
+        qd, kd = cfg.q_dim, cfg.kv_dim
+        dqkv = torch.empty(T, qd + 2 * kd, dtype=dq.dtype, device=dq.device)
+        M.rope_into(dqkv[:, :qd], dq.reshape(T, qd), cos, sin, S, nq, hd, inverse=True)
+        M.rope_into(dqkv[:, qd:qd + kd], dk.reshape(T, kd), cos, sin, S, nkv, hd, inverse=True)
+        dqkv[:, qd + kd:].copy_(dv.reshape(T, kd))
     wgrad("wqkv", dqkv, saved["h1"])
     dh1 = G.mm_nn(dqkv, w["wqkv"])
     dx1n, dw = M.rmsnorm_bwd(dh1, saved["x"], w["input_layernorm.weight"], saved["rstd1"])

@@ -92,10 +92,25 @@ def rope_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, inverse: bool =
     """In-place rotary embedding of a contiguous [B, S, n, hd] tensor."""
     if _use_kernel(x) and x.is_contiguous():
         B, S, n, hd = x.shape
-        ops().rope(x, cos, sin, S, n, hd, bool(inverse), bool(interleaved))
+        x2 = x.view(B * S, n * hd)
+        ops().rope(x2, x2, cos, sin, S, n, hd, bool(inverse), bool(interleaved))
         return x
     x.copy_(rope_ref(x, cos, sin, inverse, interleaved))
     return x
+
+
+def rope_into(dst2d: torch.Tensor, src2d: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq_len: int,
+              n_heads: int, head_dim: int, inverse: bool = False, interleaved: bool = False) -> torch.Tensor:
+    """``dst2d = rope(src2d)`` for ``[tokens, n_heads * head_dim]`` views whose rows may be strided
+    (column slices of a fused projection buffer): rotation and (un)packing in one pass."""
+    if _use_kernel(src2d) and src2d.stride(1) == 1 and dst2d.stride(1) == 1:
+        ops().rope(dst2d, src2d, cos, sin, int(seq_len), int(n_heads), int(head_dim), bool(inverse),
+                   bool(interleaved))
+        return dst2d
+    T = src2d.shape[0]
+    x = src2d.reshape(T // seq_len, seq_len, n_heads, head_dim)
+    dst2d.copy_(rope_ref(x, cos, sin, inverse, interleaved).reshape(T, n_heads * head_dim))
+    return dst2d
 
 
 # ---------------------------------------------------------------- SwiGLU

@@ -200,6 +200,17 @@ def test_model_kernels_match_torch():
         assert torch.allclose(got, ref, atol=1e-5)
         back = M.rope_(got.clone(), cos, sin, inverse=True, interleaved=inter)
         assert torch.allclose(back, x, atol=1e-5)
+        # strided source / destination (column slices of a fused buffer), bf16, and an odd head size
+        for dt, hd2 in ((torch.bfloat16, 128), (torch.float32, 24)):
+            c2, s2 = M.rope_tables(S, hd2, 1e6, dev)
+            fused = torch.randn(B * S, 3 * n * hd2 + 8, generator=g).to(dt).to(dev)
+            src = fused[:, n * hd2:2 * n * hd2]
+            out = torch.zeros(B * S, 2 * n * hd2, dtype=dt, device=dev)
+            M.rope_into(out[:, n * hd2:], src, c2, s2, S, n, hd2, interleaved=inter)
+            want = M.rope_ref(src.reshape(B, S, n, hd2), c2, s2, interleaved=inter).reshape(B * S, n * hd2)
+            tol = 2e-2 if dt == torch.bfloat16 else 1e-5
+            assert torch.allclose(out[:, n * hd2:].float(), want.float(), atol=tol)
+            assert float(out[:, :n * hd2].abs().max()) == 0.0
     # swiglu
     gu = torch.randn(50, 2 * 688, generator=g).bfloat16().to(dev)
     dz = torch.randn(50, 688, generator=g).bfloat16().to(dev)
