@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--reduce-ctas", type=int, default=148)
     ap.add_argument("--reduce", default="ce", choices=["ce", "kernel"],
                     help="gradient reduce-scatter: copy engines + local sum, or peer loads in the kernel")
+    ap.add_argument("--attn", default="sdpa", choices=["sdpa", "tcgen05"],
+                    help="attention: fused library kernel, or tcgen05 GEMMs + own row kernels")
     ap.add_argument("--trace", action="store_true",
                     help="after the timed loops, print the per-phase device times of one more step (stderr)")
     return ap.parse_args()
@@ -114,6 +116,10 @@ def run_ours(args):
 
     rank, world, local = dist_setup(args.gpus)
     dev = torch.device("cuda", local)
+    if args.attn != "sdpa":
+        from gefen_x_b200.ops import model as _model_ops
+
+        _model_ops.set_attention_impl(args.attn)
     over = {"n_layers": args.layers} if args.layers else {}
     cfg = get_config(args.model, **over)
     B = args.batch or BATCH_PER_GPU.get(args.model, 1)
@@ -214,7 +220,7 @@ def run_ours(args):
                    "optimizer": ("Gefen factored_v_2d lr6e-6 clip1.0" if args.optimizer == "gefen" else
                                  "GefenMuonHybrid (Muon NS-5 standard, quantized momentum; Gefen backup) "
                                  "lr6e-6 clip1.0"),
-                   "rs_mode": trainer.rs_mode, "ag_gemm": trainer.ag_gemm,
+                   "rs_mode": trainer.rs_mode, "ag_gemm": trainer.ag_gemm, "attention": args.attn,
                    "gather": trainer.gather_mode, "reduce": trainer.reduce_mode, "reduce_ctas": trainer.reduce_ctas,
                    "l2": "working set per step (weights+grads, GBs) exceeds the 126 MB L2"},
     }

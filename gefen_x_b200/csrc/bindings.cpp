@@ -12,6 +12,7 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
 
+#include "attention.h"
 #include "comm.h"
 #include "gemm_sm100.h"
 #include "model_ops.h"
@@ -421,6 +422,40 @@ void rope(Tensor dst, const Tensor& src, const Tensor& cos, const Tensor& sin, i
           "rope");
 }
 
+void attn_softmax(Tensor scores, Tensor lse, int64_t seq_q, double scale) {
+    c10::cuda::CUDAGuard guard(scores.device());
+    TORCH_CHECK(scores.is_cuda() && scores.is_contiguous() && scores.scalar_type() == at::kBFloat16);
+    TORCH_CHECK(lse.is_cuda() && lse.scalar_type() == at::kFloat && lse.is_contiguous());
+    const int64_t n_keys = scores.size(-1), rows = scores.numel() / n_keys;
+    TORCH_CHECK(lse.numel() == rows && rows % seq_q == 0);
+    check(gx::launch_causal_softmax(scores.data_ptr(), lse.data_ptr<float>(), rows, (int)n_keys, (int)seq_q,
+                                    (float)scale, stream()),
+          "attn_softmax");
+}
+
+void attn_row_dot(const Tensor& a, const Tensor& b, Tensor out) {
+    c10::cuda::CUDAGuard guard(a.device());
+    TORCH_CHECK(a.is_cuda() && a.is_contiguous() && b.is_contiguous() && a.sizes() == b.sizes() &&
+                a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16);
+    const int64_t d = a.size(-1), rows = a.numel() / d;
+    TORCH_CHECK(out.scalar_type() == at::kFloat && out.is_contiguous() && out.numel() == rows);
+    check(gx::launch_row_dot(a.data_ptr(), b.data_ptr(), out.data_ptr<float>(), rows, (int)d, stream()),
+          "attn_row_dot");
+}
+
+void attn_bwd_rows(Tensor scores, Tensor dprob, const Tensor& lse, const Tensor& delta, int64_t seq_q,
+                   double scale) {
+    c10::cuda::CUDAGuard guard(scores.device());
+    TORCH_CHECK(scores.is_contiguous() && dprob.is_contiguous() && scores.sizes() == dprob.sizes() &&
+                scores.scalar_type() == at::kBFloat16 && dprob.scalar_type() == at::kBFloat16);
+    const int64_t n_keys = scores.size(-1), rows = scores.numel() / n_keys;
+    TORCH_CHECK(lse.scalar_type() == at::kFloat && delta.scalar_type() == at::kFloat && lse.numel() == rows &&
+                delta.numel() == rows && lse.is_contiguous() && delta.is_contiguous());
+    check(gx::launch_attn_bwd_rows(scores.data_ptr(), dprob.data_ptr(), lse.data_ptr<float>(),
+                                   delta.data_ptr<float>(), rows, (int)n_keys, (int)seq_q, (float)scale, stream()),
+          "attn_bwd_rows");
+}
+
 void swiglu_fwd(const Tensor& gate_up, Tensor out) {
     c10::cuda::CUDAGuard guard(out.device());
     TORCH_CHECK(gate_up.is_contiguous() && out.is_contiguous());
@@ -485,6 +520,9 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor(a!) dx, Tensor(b!) dw_partial) -> ()");
     m.def("rope(Tensor(a!) dst, Tensor src, Tensor cos, Tensor sin, int seq_len, int n_heads, int head_dim, "
           "bool inverse, bool interleaved) -> ()");
+    m.def("attn_softmax(Tensor(a!) scores, Tensor(b!) lse, int seq_q, float scale) -> ()");
+    m.def("attn_row_dot(Tensor a, Tensor b, Tensor(a!) out) -> ()");
+    m.def("attn_bwd_rows(Tensor(a!) scores, Tensor(b!) dprob, Tensor lse, Tensor delta, int seq_q, float scale) -> ()");
     m.def("swiglu_fwd(Tensor gate_up, Tensor(a!) out) -> ()");
     m.def("swiglu_bwd(Tensor gate_up, Tensor dout, Tensor(a!) dgate_up) -> ()");
     m.def("xent_fwd_bwd(Tensor(a!) logits, Tensor targets, Tensor(b!) loss_rows, float grad_scale, "
@@ -507,6 +545,9 @@ TORCH_LIBRARY_IMPL(gefenx, CUDA, m) {
     m.impl("rmsnorm_fwd", &rmsnorm_fwd);
     m.impl("rmsnorm_bwd", &rmsnorm_bwd);
     m.impl("rope", &rope);
+    m.impl("attn_softmax", &attn_softmax);
+    m.impl("attn_row_dot", &attn_row_dot);
+    m.impl("attn_bwd_rows", &attn_bwd_rows);
     m.impl("swiglu_fwd", &swiglu_fwd);
     m.impl("swiglu_bwd", &swiglu_bwd);
     m.impl("xent_fwd_bwd", &xent_fwd_bwd);

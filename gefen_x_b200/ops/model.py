@@ -165,11 +165,33 @@ def xent_fwd_bwd_(logits: torch.Tensor, targets: torch.Tensor, grad_scale: float
 
 
 # ---------------------------------------------------------------- attention
+_ATTN_IMPL = "sdpa"
+
+
+def set_attention_impl(name: str) -> None:
+    """``"sdpa"``: the fused library kernel (default); ``"tcgen05"``: the tcgen05 GEMM plus own row
+    kernels of :mod:`gefen_x_b200.ops.attention` (bf16 CUDA tensors; others fall back to sdpa)."""
+    global _ATTN_IMPL
+    if name not in ("sdpa", "tcgen05"):
+        raise ValueError("attention implementation must be 'sdpa' or 'tcgen05'")
+    _ATTN_IMPL = name
+
+
+def attention_impl() -> str:
+    return _ATTN_IMPL
+
+
 def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
     """Causal GQA attention on [B, S, n, hd] tensors.
 
     Returns ``(out [B, S, nq, hd], ctx)``; ``ctx`` feeds :func:`attention_bwd`.
     """
+    if _ATTN_IMPL == "tcgen05":
+        from . import attention as _att
+
+        if _att.supported(q, k):
+            out, ctx = _att.attention_fwd(q, k, v)
+            return out, ("tcgen05", ctx)
     with torch.enable_grad():
         ql = q.detach().requires_grad_(True)
         kl = k.detach().requires_grad_(True)
@@ -183,5 +205,9 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
 
 
 def attention_bwd(ctx, dout: torch.Tensor):
+    if len(ctx) == 2 and isinstance(ctx[0], str):
+        from . import attention as _att
+
+        return _att.attention_bwd(ctx[1], dout)
     ql, kl, vl, o = ctx
     return torch.autograd.grad(o, (ql, kl, vl), dout)

@@ -353,3 +353,52 @@ def test_sharded_trainer_muon_hybrid_single_gpu():
     assert losses[-1] < losses[0] - 0.5, losses
     assert len(tr.muon.owned) == cfg.n_layers * 7
     assert tr.state_bytes_per_param() < 1.2
+
+
+@pytest.mark.parametrize("B,S,nq,nkv,hd", [(2, 128, 8, 2, 64), (1, 256, 4, 4, 128), (2, 72, 6, 3, 128)])
+def test_gemm_composed_attention_matches_sdpa(B, S, nq, nkv, hd):
+    """tcgen05 GEMM + own softmax / backward row kernels against fp32 SDPA (forward and gradients)."""
+    import torch.nn.functional as F
+
+    from gefen_x_b200.ops import attention as A
+
+    dev = _dev()
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(B, S, nq, hd, generator=g).bfloat16().to(dev)
+    k = torch.randn(B, S, nkv, hd, generator=g).bfloat16().to(dev)
+    v = torch.randn(B, S, nkv, hd, generator=g).bfloat16().to(dev)
+    do = torch.randn(B, S, nq, hd, generator=g).bfloat16().to(dev)
+    assert A.supported(q, k)
+    out, ctx = A.attention_fwd(q, k, v)
+    dq, dk, dv = A.attention_bwd(ctx, do)
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    ref = F.scaled_dot_product_attention(qr.transpose(1, 2), kr.transpose(1, 2), vr.transpose(1, 2),
+                                         is_causal=True, enable_gqa=nq != nkv).transpose(1, 2)
+    ref.backward(do.float())
+    assert torch.allclose(out.float(), ref, atol=3e-2, rtol=3e-2)
+    for got, want in ((dq, qr.grad), (dk, kr.grad), (dv, vr.grad)):
+        err = (got.float() - want).abs().max().item()
+        assert err < 0.06 * max(1.0, want.abs().max().item()), err
+
+
+def test_decoder_trains_with_gemm_composed_attention():
+    from gefen_x_b200.models.decoder import get_config
+    from gefen_x_b200.ops import model as M
+    from gefen_x_b200.parallel.fsdp import ShardedTrainer
+
+    cfg = get_config("tiny-llama", hidden=256, ffn=512, n_layers=2)
+    g = torch.Generator().manual_seed(2)
+    tok = torch.randint(0, cfg.vocab_size, (2, 129), generator=g).to(_dev())
+
+    def run(impl):
+        M.set_attention_impl(impl)
+        try:
+            tr = ShardedTrainer(cfg, device=_dev(), dtype=torch.bfloat16, lr=6e-4, clip_grad_norm=1.0, seed=5)
+            return [float(tr.step(tok[:, :-1], tok[:, 1:]).item()) for _ in range(8)]
+        finally:
+            M.set_attention_impl("sdpa")
+
+    a, b = run("sdpa"), run("tcgen05")
+    assert b[-1] < b[0] - 0.3
+    for x, y in zip(a, b):
+        assert abs(x - y) < 0.05 * max(1.0, abs(x)), (a, b)
