@@ -40,6 +40,12 @@ def dense_momentum(codebook: torch.Tensor, state: Dict[str, Any], shape) -> torc
     """fp32 momentum of a local shard: ``codebook[idx] * magnitude``."""
     idx = state["m_codebook"]
     cb = codebook.to(idx.device)
+    if idx.is_cuda and idx.is_contiguous():
+        from ..ops import _ext, quant as _q
+
+        if _ext.available():
+            period = idx.numel() // max(1, state["m_magnitude"].numel())
+            return _q.dequantize(idx, state["m_magnitude"], cb, period, torch.float32).reshape(shape)
     return (_cbk.dequantize_indices(cb, idx, torch.float32) * state["m_magnitude"]).reshape(shape)
 
 

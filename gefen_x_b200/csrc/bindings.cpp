@@ -148,6 +148,28 @@ void clip_coef(const Tensor& partials, double max_norm, Tensor coef) {
           "clip_coef");
 }
 
+void remap_indices(Tensor idx, const Tensor& map) {
+    c10::cuda::CUDAGuard guard(idx.device());
+    TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kByte && idx.is_contiguous());
+    TORCH_CHECK(map.is_cuda() && map.scalar_type() == at::kByte && map.is_contiguous() && map.numel() == 256);
+    check(gx::launch_remap_indices(idx.data_ptr<uint8_t>(), map.data_ptr<uint8_t>(), idx.numel(), sm_count(),
+                                   stream()),
+          "remap_indices");
+}
+
+void dequantize(const Tensor& idx, const Tensor& mag, const Tensor& codebook, int64_t period, Tensor out) {
+    c10::cuda::CUDAGuard guard(idx.device());
+    TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kByte && idx.is_contiguous());
+    TORCH_CHECK(mag.is_cuda() && mag.scalar_type() == at::kFloat && mag.is_contiguous());
+    TORCH_CHECK(codebook.is_cuda() && codebook.scalar_type() == at::kFloat && codebook.numel() == 256);
+    TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.numel() == idx.numel());
+    TORCH_CHECK(period > 0 && idx.numel() % period == 0 && mag.numel() * period == idx.numel());
+    check(gx::launch_dequantize(idx.data_ptr<uint8_t>(), mag.data_ptr<float>(), codebook.data_ptr<float>(),
+                                idx.numel(), period, out.data_ptr(), dtype_code(out.scalar_type()), sm_count(),
+                                stream()),
+          "dequantize");
+}
+
 void histogram(const Tensor& flat, int64_t period, Tensor counts) {
     c10::cuda::CUDAGuard guard(flat.device());
     TORCH_CHECK(flat.is_cuda() && flat.is_contiguous(), "flat must be contiguous CUDA");
@@ -500,6 +522,8 @@ TORCH_LIBRARY(gefenx, m) {
           "int dtype, int device_index) -> ()", &reduce_sources);
     m.def("clip_coef(Tensor partials, float max_norm, Tensor(a!) coef) -> ()");
     m.def("histogram(Tensor flat, int period, Tensor(a!) counts) -> ()");
+    m.def("remap_indices(Tensor(a!) idx, Tensor map) -> ()");
+    m.def("dequantize(Tensor idx, Tensor mag, Tensor codebook, int period, Tensor(a!) out) -> ()");
     m.def("period_errors(Tensor flat, Tensor divisors, bool input_is_squared) -> Tensor");
     m.def("gemm_bf16(Tensor a, Tensor b, Tensor(a!) c, Tensor? d, bool a_t, bool b_t, float alpha, "
           "float beta, Tensor? status) -> ()");
@@ -534,6 +558,8 @@ TORCH_LIBRARY_IMPL(gefenx, CUDA, m) {
     m.impl("factored_update", &factored_update);
     m.impl("clip_coef", &clip_coef);
     m.impl("histogram", &histogram);
+    m.impl("remap_indices", &remap_indices);
+    m.impl("dequantize", &dequantize);
     m.impl("period_errors", &period_errors);
     m.impl("gemm_bf16", &gemm_bf16);
     m.impl("gemm_ag_bf16", &gemm_ag_bf16);

@@ -170,6 +170,62 @@ __global__ void __launch_bounds__(kThreads) period_errors_kernel(const T* __rest
     }
 }
 
+// idx[i] <- map[idx[i]] in place: moves stored momentum indices onto a re-learned codebook
+// (map[c] = nearest new codeword of old codeword c).  16 indices per access.
+__global__ void __launch_bounds__(kThreads) remap_indices_kernel(uint8_t* __restrict__ idx,
+                                                                 const uint8_t* __restrict__ map,
+                                                                 long long numel) {
+    __shared__ uint8_t m[256];
+    if (threadIdx.x < 256) m[threadIdx.x] = map[threadIdx.x];
+    __syncthreads();
+    const long long n16 = numel / 16;
+    uint4* v = reinterpret_cast<uint4*>(idx);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16;
+         i += (long long)gridDim.x * blockDim.x) {
+        uint4 r = v[i];
+        uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            w[k] = (uint32_t)m[w[k] & 0xff] | ((uint32_t)m[(w[k] >> 8) & 0xff] << 8) |
+                   ((uint32_t)m[(w[k] >> 16) & 0xff] << 16) | ((uint32_t)m[w[k] >> 24] << 24);
+        }
+        v[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    for (long long i = n16 * 16 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < numel;
+         i += (long long)gridDim.x * blockDim.x)
+        idx[i] = m[idx[i]];
+}
+
+// out[i] = codebook[idx[i]] * mag[i / period]: the dense momentum of a tensor (checkpoint
+// export, resharding).  Eight elements per thread when period % 8 == 0.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) dequantize_kernel(const uint8_t* __restrict__ idx,
+                                                              const float* __restrict__ mag,
+                                                              const float* __restrict__ codebook,
+                                                              long long numel, long long period,
+                                                              T* __restrict__ out, int vec) {
+    __shared__ float cb[256];
+    if (threadIdx.x < 256) cb[threadIdx.x] = codebook[threadIdx.x];
+    __syncthreads();
+    if (vec) {
+        const long long n8 = numel / 8;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
+             i += (long long)gridDim.x * blockDim.x) {
+            int ix[8];
+            load_idx8(idx + i * 8, ix);
+            const float m = mag[(i * 8) / period];
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = cb[ix[e]] * m;
+            Vec8<T>::store(out + i * 8, v);
+        }
+        return;
+    }
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < numel;
+         i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_f<T>(cb[idx[i]] * mag[i / period]);
+}
+
 }  // namespace
 
 cudaError_t launch_histogram(const void* x, int dtype, long long numel, int period, int bins,
@@ -200,6 +256,34 @@ cudaError_t launch_period_errors(const void* x, int dtype, long long numel, cons
         case 0: period_errors_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, numel, divisors_dev, squared, partials); break;
         case 1: period_errors_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, numel, divisors_dev, squared, partials); break;
         case 2: period_errors_kernel<__half><<<grid, kThreads, 0, st>>>((const __half*)x, numel, divisors_dev, squared, partials); break;
+        default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_remap_indices(uint8_t* idx, const uint8_t* map, long long numel, int sm_count,
+                                 cudaStream_t st) {
+    if (numel <= 0) return cudaSuccess;
+    if (reinterpret_cast<uintptr_t>(idx) % 16) return cudaErrorInvalidValue;
+    const long long want = (numel / 16 + kThreads - 1) / kThreads;
+    const int grid = (int)max(1LL, min(want, (long long)sm_count * 8));
+    remap_indices_kernel<<<grid, kThreads, 0, st>>>(idx, map, numel);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_dequantize(const uint8_t* idx, const float* mag, const float* codebook, long long numel,
+                              long long period, void* out, int dtype, int sm_count, cudaStream_t st) {
+    if (numel <= 0) return cudaSuccess;
+    if (period <= 0) return cudaErrorInvalidValue;
+    const int esz = dtype == 0 ? 4 : 2;
+    const int vec = (period % 8 == 0 && numel % 8 == 0 && reinterpret_cast<uintptr_t>(idx) % 8 == 0 &&
+                     reinterpret_cast<uintptr_t>(out) % (8 * esz) == 0) ? 1 : 0;
+    const long long want = ((vec ? numel / 8 : numel) + kThreads - 1) / kThreads;
+    const int grid = (int)max(1LL, min(want, (long long)sm_count * 8));
+    switch (dtype) {
+        case 0: dequantize_kernel<float><<<grid, kThreads, 0, st>>>(idx, mag, codebook, numel, period, (float*)out, vec); break;
+        case 1: dequantize_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>(idx, mag, codebook, numel, period, (__nv_bfloat16*)out, vec); break;
+        case 2: dequantize_kernel<__half><<<grid, kThreads, 0, st>>>(idx, mag, codebook, numel, period, (__half*)out, vec); break;
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();

@@ -38,3 +38,23 @@ def period_errors(flat: torch.Tensor, divisors: Sequence[int], input_is_squared:
     partials = ops().period_errors(flat, divs, bool(input_is_squared))
     sums = partials.sum(dim=1).cpu().tolist()
     return [math.sqrt(max(s, 0.0) / (n // p)) for s, p in zip(sums, divisors)]
+
+
+def remap_indices_(idx: torch.Tensor, index_map: torch.Tensor) -> torch.Tensor:
+    """``idx[i] = index_map[idx[i]]`` in place on a contiguous uint8 CUDA tensor (no temporaries).
+
+    Moves stored momentum indices onto a re-learned codebook: ``index_map[c]`` is the nearest new
+    codeword of old codeword ``c`` (reference ``src/gefen/gefen.py:3020-3061`` dequantises and
+    re-searches every element instead)."""
+    ops().remap_indices(idx, index_map.to(device=idx.device, dtype=torch.uint8).contiguous())
+    return idx
+
+
+def dequantize(idx: torch.Tensor, mag: torch.Tensor, codebook: torch.Tensor, period: int,
+               dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Dense momentum ``codebook[idx] * mag[block]`` of a contiguous uint8 CUDA index tensor
+    (reference ``src/gefen/dcp.py:54-81``); ``mag`` holds one value per block of ``period``."""
+    out = torch.empty(idx.shape, dtype=dtype, device=idx.device)
+    ops().dequantize(idx, mag.reshape(-1).contiguous(), codebook.to(idx.device, torch.float32).contiguous(),
+                     int(period), out)
+    return out

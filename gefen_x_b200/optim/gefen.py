@@ -175,6 +175,12 @@ def _local(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
+def _ext_available() -> bool:
+    from ..ops._ext import available
+
+    return available()
+
+
 class Gefen(torch.optim.Optimizer):
     """Memory-efficient AdamW replacement (quantised momentum, shared/factored v).
 
@@ -601,10 +607,20 @@ class Gefen(torch.optim.Optimizer):
                 if not st or "m_codebook" not in st:
                     continue
                 dev = st["m_codebook"].device
+                if dev.type == "cuda" and st["m_codebook"].is_contiguous() and _ext_available():
+                    staged.append((st["m_codebook"], None))        # remapped in place below (no temporaries)
+                    continue
                 coeffs = _cbk.dequantize_indices(old.to(dev), st["m_codebook"], torch.float32)
                 staged.append((st["m_codebook"], _cbk.nearest_codebook_indices(new.to(dev), coeffs)))
+        # the new index of a stored value depends only on its old index: one 256-entry table
+        index_map = _cbk.nearest_codebook_indices(new.cpu(), old.cpu().float()).to(torch.uint8)
         for dst, idx in staged:
-            dst.copy_(idx)
+            if idx is None:
+                from ..ops import quant as _q
+
+                _q.remap_indices_(dst, index_map)
+            else:
+                dst.copy_(idx)
         self._set_codebook(new)
 
     # ------------------------------------------------------------------

@@ -156,3 +156,39 @@ def test_stochastic_rounding_is_seeded_by_step_and_stays_close_to_nearest():
         assert int((ia - ib).abs().max()) <= 16         # nearby codewords (the runs drift apart a little)
         assert (cb[ia] - cb[ib]).abs().mean().item() < 0.02
     assert moved > 0
+
+
+def test_requantise_and_dense_dequantise_kernels():
+    """Index remap onto a new codebook and the dense momentum export against their torch statements."""
+    from gefen_x_b200 import Gefen
+    from gefen_x_b200.ckpt.dcp import dense_momentum
+    from gefen_x_b200.ops import quant as Q
+    from gefen_x_b200.quant import codebook as C
+
+    dev = _dev()
+    g = torch.Generator().manual_seed(4)
+    for numel, period in ((1 << 16, 256), (1000 * 24, 24), (4099 * 3, 3)):
+        idx = torch.randint(0, 256, (numel,), generator=g, dtype=torch.uint8).to(dev)
+        mag = torch.rand(numel // period, generator=g).to(dev)
+        cb = torch.sort(torch.rand(256, generator=g) * 2 - 1).values.to(dev)
+        for dt in (torch.float32, torch.bfloat16):
+            got = Q.dequantize(idx, mag, cb, period, dt)
+            want = (cb[idx.long()].view(-1, period) * mag[:, None]).reshape(-1)
+            assert torch.allclose(got.float(), want.to(dt).float(), atol=0, rtol=0)
+        perm = torch.randperm(256, generator=g).to(torch.uint8)
+        want = perm.to(dev)[idx.long()]
+        assert torch.equal(Q.remap_indices_(idx.clone(), perm), want)
+    # through the optimizer: a refresh re-learns the codebook and remaps in place
+    ps = _params()
+    opt = Gefen(ps, lr=1e-2, codebook_refresh_every=2)
+    for step in range(4):
+        for (_, p), gr in zip(ps, _grads(ps, step)):
+            p.grad = gr
+        before = {n: opt.state[p]["m_codebook"].clone() for n, p in ps} if step == 2 else None
+        old_cb = opt._gefen_codebook.clone() if step == 2 else None
+        opt.step()
+    assert opt._gefen_global_step == 4
+    st = opt.state[ps[0][1]]
+    dm = dense_momentum(opt._gefen_codebook, st, ps[0][1].shape)
+    want = C.dequantize_indices(opt._gefen_codebook.to(dev), st["m_codebook"]) * st["m_magnitude"]
+    assert torch.equal(dm.reshape(-1), want.reshape(-1))
