@@ -444,6 +444,31 @@ void rope(Tensor dst, const Tensor& src, const Tensor& cos, const Tensor& sin, i
           "rope");
 }
 
+void flash_attention_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor out, Tensor lse,
+                         int64_t seq, double scale, const c10::optional<Tensor>& status) {
+    c10::cuda::CUDAGuard guard(q.device());
+    TORCH_CHECK(q.is_cuda() && q.dim() == 3 && k.dim() == 3 && v.dim() == 3 && q.is_contiguous() &&
+                k.is_contiguous() && v.is_contiguous() && out.is_contiguous() && lse.is_contiguous());
+    TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 &&
+                v.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16 &&
+                lse.scalar_type() == at::kFloat);
+    TORCH_CHECK(k.sizes() == v.sizes() && k.size(0) == q.size(0) && k.size(1) == seq && k.size(2) == q.size(2) &&
+                out.sizes() == q.sizes() && lse.numel() == q.size(0) * q.size(1));
+    gx::FlashParams p{};
+    p.seq = (int)seq;
+    p.rows = (int)q.size(1);
+    p.batch = (int)q.size(0);
+    p.scale = (float)scale;
+    p.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+    p.lse = lse.data_ptr<float>();
+    p.status = (status.has_value() && status->defined()) ? status->data_ptr<int>() : nullptr;
+    check(gx::launch_flash_attention_fwd(reinterpret_cast<const __nv_bfloat16*>(q.data_ptr()),
+                                         reinterpret_cast<const __nv_bfloat16*>(k.data_ptr()),
+                                         reinterpret_cast<const __nv_bfloat16*>(v.data_ptr()), (int)q.size(2), p,
+                                         stream()),
+          "flash_attention_fwd");
+}
+
 void attn_softmax(Tensor scores, Tensor lse, int64_t seq_q, double scale) {
     c10::cuda::CUDAGuard guard(scores.device());
     TORCH_CHECK(scores.is_cuda() && scores.is_contiguous() && scores.scalar_type() == at::kBFloat16);
@@ -544,6 +569,8 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor(a!) dx, Tensor(b!) dw_partial) -> ()");
     m.def("rope(Tensor(a!) dst, Tensor src, Tensor cos, Tensor sin, int seq_len, int n_heads, int head_dim, "
           "bool inverse, bool interleaved) -> ()");
+    m.def("flash_attention_fwd(Tensor q, Tensor k, Tensor v, Tensor(a!) out, Tensor(b!) lse, int seq, "
+          "float scale, Tensor? status) -> ()");
     m.def("attn_softmax(Tensor(a!) scores, Tensor(b!) lse, int seq_q, float scale) -> ()");
     m.def("attn_row_dot(Tensor a, Tensor b, Tensor(a!) out) -> ()");
     m.def("attn_bwd_rows(Tensor(a!) scores, Tensor(b!) dprob, Tensor lse, Tensor delta, int seq_q, float scale) -> ()");
@@ -571,6 +598,7 @@ TORCH_LIBRARY_IMPL(gefenx, CUDA, m) {
     m.impl("rmsnorm_fwd", &rmsnorm_fwd);
     m.impl("rmsnorm_bwd", &rmsnorm_bwd);
     m.impl("rope", &rope);
+    m.impl("flash_attention_fwd", &flash_attention_fwd);
     m.impl("attn_softmax", &attn_softmax);
     m.impl("attn_row_dot", &attn_row_dot);
     m.impl("attn_bwd_rows", &attn_bwd_rows);

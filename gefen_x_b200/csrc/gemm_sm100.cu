@@ -406,6 +406,238 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
 }
 
+// ---------------------------------------------------------------------------
+// Causal attention forward on the same building blocks (flash form: the score tile lives in
+// TMEM, the probabilities go through shared memory straight into the second product, nothing
+// of size S x S touches HBM).
+//
+//   one CTA (128 threads) per 128 query rows of one (sequence, KV head); the group's query heads
+//   are stacked along the rows, so row r belongs to head r / seq and query position r % seq;
+//   per 128-key tile:  TMA K, V  ->  S = Q K^T (tcgen05, TMEM cols 0..127)
+//                      thread t owns row t: running maximum, p = exp2((s - m) * scale * log2e),
+//                      P (bf16) written in the 128-byte-swizzled K-major layout the MMA reads
+//                      PV (tcgen05, TMEM cols 128..) -> o = o * alpha + PV in registers
+//   epilogue: o / l -> bf16, log-sum-exp per row.
+// Every mbarrier wait is bounded; a time-out is voted CTA-wide and ends the kernel cleanly.
+struct FlashShared {
+    uint64_t bar_q, bar_kv[2], bar_s, bar_o;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(128, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, FlashParams p) {
+    constexpr int KB = HD / 64;                       // 64-wide head-dimension blocks
+    constexpr uint32_t kBlk = 128 * 128;              // one [128 rows x 128 B] operand block
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sQ = base;                         // [KB][128 x 128 B]   K-major A
+    constexpr uint32_t kKV = KB * kBlk;               // bytes of one K (or V) tile
+    unsigned char* sK = sQ + KB * kBlk;               // [2 buffers][KB][128 x 128 B]   K-major B
+    unsigned char* sV = sK + 2 * kKV;                 // [2 buffers][2][KB][64 keys x 128 B]  MN-major B
+    unsigned char* sP = sV + 2 * kKV;                 // [2][128 x 128 B]   K-major A (keys along K)
+    FlashShared* ss = reinterpret_cast<FlashShared*>(sP + 2 * kBlk);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    volatile int* abort_flag = &ss->abort_flag;
+    const int n_row_tiles = p.rows / 128;
+    const int rt = n_row_tiles - 1 - (int)blockIdx.x;          // long rows first
+    const int b = blockIdx.y;
+    const int r0 = rt * 128;
+    const int s0 = r0 % p.seq;                                 // query position of the tile's first row
+    const int n_kv = s0 / 128 + 1;
+
+    if (tid == 0) {
+        mbar_init(&ss->bar_q, 1);
+        mbar_init(&ss->bar_kv[0], 1);
+        mbar_init(&ss->bar_kv[1], 1);
+        mbar_init(&ss->bar_s, 1);
+        mbar_init(&ss->bar_o, 1);
+        ss->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&tmQ);
+        prefetch_tmap(&tmK);
+        prefetch_tmap(&tmV);
+    }
+    if (warp == 0) tmem_alloc(&ss->tmem_base, 256);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ss->tmem_base;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+
+    if (tid == 0) {
+        mbar_expect_tx(&ss->bar_q, KB * kBlk);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) tma_load_3d(sQ + kb * kBlk, &tmQ, &ss->bar_q, 64 * kb, r0, b);
+    }
+    const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) |
+                             ((uint32_t)(128 >> 4) << 24);
+    const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
+                             ((uint32_t)(128 >> 4) << 24);
+    const float sl = p.scale * 1.4426950408889634f;
+    float o[HD];
+#pragma unroll
+    for (int e = 0; e < HD; ++e) o[e] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    uint32_t ph_s = 0, ph_o = 0;
+    // K / V tiles are double-buffered: tile j + 1 is fetched while tile j is being processed
+    auto fetch_kv = [&](int j) {
+        const int bf = j & 1;
+        mbar_expect_tx(&ss->bar_kv[bf], 2 * kKV);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+            tma_load_3d(sK + bf * kKV + kb * kBlk, &tmK, &ss->bar_kv[bf], 64 * kb, 128 * j, b);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int jn = 0; jn < KB; ++jn)
+                tma_load_3d(sV + bf * kKV + (h * KB + jn) * 8192, &tmV, &ss->bar_kv[bf], 64 * jn,
+                            128 * j + 64 * h, b);
+    };
+    int issued[2] = {0, 0}, landed[2] = {0, 0};     // per buffer: loads started / seen complete
+    if (tid == 0) { fetch_kv(0); issued[0] = 1; }
+    bool ok = mbar_wait(&ss->bar_q, 0, abort_flag);
+    ok = __syncthreads_and(ok);
+
+    for (int j = 0; j < n_kv && ok; ++j) {
+        const int bf = j & 1;
+        // buffer (j + 1) & 1 held tile j - 1, whose products have retired (bar_o of that tile)
+        if (tid == 0 && j + 1 < n_kv) { fetch_kv(j + 1); ++issued[bf ^ 1]; }
+        ok = mbar_wait(&ss->bar_kv[bf], (uint32_t)((j >> 1) & 1), abort_flag);
+        if (ok) ++landed[bf];
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        const unsigned char* cK = sK + bf * kKV;
+        const unsigned char* cV = sV + bf * kKV;
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem_base, make_desc(smem_u32(sQ + kb * kBlk) + k * 32, 16, 1024),
+                              make_desc(smem_u32(cK + kb * kBlk) + k * 32, 16, 1024), idesc_s,
+                              (kb > 0 || k > 0) ? 1u : 0u);
+            umma_commit(&ss->bar_s);
+        }
+        ok = mbar_wait(&ss->bar_s, ph_s, abort_flag);
+        ph_s ^= 1;
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        tc_fence_after();
+
+        // ---- softmax of this thread's row --------------------------------------------------
+        const bool diag = (j == n_kv - 1);
+        const int qpos = s0 + tid;
+        float mx = m;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(lane_base + (uint32_t)(c * 32), r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                const int col = 128 * j + c * 32 + e;
+                const float v = (diag && col > qpos) ? -INFINITY : __uint_as_float(r[e]);
+                mx = fmaxf(mx, v);
+            }
+        }
+        const float alpha = exp2f((m - mx) * sl);          // 0 on the first tile (m = -inf)
+        float rs = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(lane_base + (uint32_t)(c * 32), r);
+            tmem_ld_wait();
+            uint32_t w[16];
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+                const int col = 128 * j + c * 32 + e;
+                float p0 = exp2f((__uint_as_float(r[e]) - mx) * sl);
+                float p1 = exp2f((__uint_as_float(r[e + 1]) - mx) * sl);
+                if (diag && col > qpos) p0 = 0.f;
+                if (diag && col + 1 > qpos) p1 = 0.f;
+                const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                // the row sum uses the rounded probabilities, like the product that consumes them
+                rs += __low2float(h) + __high2float(h);
+                w[e >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const int cc = c * 4 + q4;                 // 16-byte chunk of the 128-key row
+                const int kb = cc >> 3, ci = cc & 7;
+                uint4* dst = reinterpret_cast<uint4*>(sP + kb * kBlk + tid * 128 + ((ci ^ (tid & 7)) << 4));
+                *dst = make_uint4(w[4 * q4], w[4 * q4 + 1], w[4 * q4 + 2], w[4 * q4 + 3]);
+            }
+        }
+        l = l * alpha + rs;
+        m = mx;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P: generic writes -> MMA reads
+        tc_fence_before();
+        __syncthreads();
+
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem_base + 128, make_desc(smem_u32(sP + h * kBlk) + k * 32, 16, 1024),
+                              make_desc(smem_u32(cV + h * KB * 8192) + k * 2048, 8192, 1024), idesc_o,
+                              (h > 0 || k > 0) ? 1u : 0u);
+            umma_commit(&ss->bar_o);
+        }
+        ok = mbar_wait(&ss->bar_o, ph_o, abort_flag);
+        ph_o ^= 1;
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(lane_base + (uint32_t)(128 + c * 32), r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[c * 32 + e] = o[c * 32 + e] * alpha + __uint_as_float(r[e]);
+        }
+        tc_fence_before();
+        __syncthreads();          // K, V, P and both TMEM regions are free for the next tile
+    }
+
+    if (ok) {
+        const float inv = 1.0f / l;
+        const long long row = (long long)b * p.rows + r0 + tid;
+        __nv_bfloat16* orow = p.out + row * HD;
+#pragma unroll
+        for (int v8 = 0; v8 < HD / 8; ++v8) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = o[v8 * 8 + e] * inv;
+            Vec8<__nv_bfloat16>::store(orow + v8 * 8, f);
+        }
+        p.lse[row] = m * p.scale + logf(l);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && ss->abort_flag) {
+        // a load may still be in flight: give it one more bounded chance to land before the
+        // shared memory it targets is released
+        volatile int no_abort = 0;
+        for (int bf = 0; bf < 2; ++bf)
+            if (issued[bf] > landed[bf]) mbar_wait(&ss->bar_kv[bf], (uint32_t)(landed[bf] & 1), &no_abort);
+        if (p.status) atomicExch(p.status, (int)kWaitTimeout);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 256);
+    }
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------
@@ -515,6 +747,34 @@ cudaError_t launch_gemm_bf16(const __nv_bfloat16* A, long long lda, long long ba
                (!p.D || ((p.ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(p.D) % 16 == 0) &&
                          (p.batch_stride_d % 8 == 0)));
     return use128 ? launch_bn<128>(ta, tb, p, sm_count, st) : launch_bn<256>(ta, tb, p, sm_count, st);
+}
+
+cudaError_t launch_flash_attention_fwd(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
+                                       int head_dim, FlashParams p, cudaStream_t st) {
+    if (p.batch <= 0 || p.rows <= 0) return cudaSuccess;
+    if ((head_dim != 64 && head_dim != 128) || p.seq % 128 || p.rows % p.seq) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(q) % 16) || (reinterpret_cast<uintptr_t>(k) % 16) ||
+        (reinterpret_cast<uintptr_t>(v) % 16) || (reinterpret_cast<uintptr_t>(p.out) % 16))
+        return cudaErrorInvalidValue;
+    CUtensorMap tq, tk, tv;
+    if (!make_map(&tq, q, head_dim, p.rows, p.batch, head_dim, (long long)p.rows * head_dim, 64, 128) ||
+        !make_map(&tk, k, head_dim, p.seq, p.batch, head_dim, (long long)p.seq * head_dim, 64, 128) ||
+        !make_map(&tv, v, head_dim, p.seq, p.batch, head_dim, (long long)p.seq * head_dim, 64, 64))
+        return cudaErrorInvalidValue;
+    const int kb = head_dim / 64;
+    const size_t smem = (size_t)(kb * 16384 + 4 * kb * 16384 + 2 * 16384) + sizeof(FlashShared) + 1024;
+    dim3 grid(p.rows / 128, p.batch);
+    cudaError_t e;
+    if (head_dim == 128) {
+        e = cudaFuncSetAttribute(flash_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        flash_fwd_kernel<128><<<grid, 128, smem, st>>>(tq, tk, tv, p);
+    } else {
+        e = cudaFuncSetAttribute(flash_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        flash_fwd_kernel<64><<<grid, 128, smem, st>>>(tq, tk, tv, p);
+    }
+    return cudaGetLastError();
 }
 
 }  // namespace gx

@@ -50,4 +50,17 @@ cudaError_t launch_gemm_bf16(const __nv_bfloat16* A, long long lda, long long ba
                              const __nv_bfloat16* B, long long ldb, long long batch_stride_b,
                              GemmParams p, int sm_count, cudaStream_t st);
 
+// Causal attention forward (flash form) on heads-first operands: q [batch, rows, hd] with
+// rows = group * seq (the query heads of one KV head stacked along the rows), k / v
+// [batch, seq, hd], out [batch, rows, hd], lse [batch * rows].  hd in {64, 128}, seq % 128 == 0.
+struct FlashParams {
+    int seq, rows, batch;
+    float scale;
+    __nv_bfloat16* out;
+    float* lse;
+    int* status;                    // device status word, may be null
+};
+cudaError_t launch_flash_attention_fwd(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
+                                       int head_dim, FlashParams p, cudaStream_t st);
+
 }  // namespace gx

@@ -1,6 +1,11 @@
-"""Causal GQA attention composed of the tcgen05 GEMM and own row kernels (no library attention).
+"""Causal GQA attention on own kernels (no library attention).
 
-Forward:  S = Q K^T (batched tcgen05 GEMM, one batch entry per (sequence, KV head) with the
+Forward, fused ("flash") form, when the sequence length is a multiple of 128 and the head size is
+64 or 128: ``flash_fwd_kernel`` (``csrc/gemm_sm100.cu``) keeps the score tile in TMEM and feeds the
+probabilities through shared memory into the second tcgen05 product; only O and the row
+log-sum-exp reach HBM.  Otherwise the forward is composed like the backward:
+
+Forward (composed):  S = Q K^T (batched tcgen05 GEMM, one batch entry per (sequence, KV head) with the
 group's query heads stacked along the rows), P = causal softmax(S / sqrt(d)) in place
 (``attention.cu``), O = P V (GEMM).  Only O and the row log-sum-exp are kept.
 Backward: S and P are recomputed, dP = dO V^T, dS = P * (dP - rowsum(dO * O)) / sqrt(d) in place,
@@ -41,12 +46,21 @@ def _heads_last(x: torch.Tensor, B: int, S: int, n: int) -> torch.Tensor:
     return x.view(B, n, S, hd).permute(0, 2, 1, 3).contiguous()
 
 
-def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> Tuple[torch.Tensor, tuple]:
+def flash_supported(S: int, hd: int) -> bool:
+    return S % 128 == 0 and hd in (64, 128)
+
+
+def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, flash: bool = True) -> Tuple[torch.Tensor, tuple]:
     """q: [B, S, nq, hd], k / v: [B, S, nkv, hd] (bf16).  Returns (out [B, S, nq, hd], ctx)."""
     B, S, nq, hd = q.shape
     nkv = k.shape[2]
     scale = 1.0 / math.sqrt(hd)
     qh, kh, vh = _heads_first(q, nkv), _heads_first(k, nkv), _heads_first(v, nkv)
+    if flash and flash_supported(S, hd):
+        oh = torch.empty_like(qh)
+        lse = torch.empty(qh.shape[0] * qh.shape[1], dtype=torch.float32, device=q.device)
+        ops().flash_attention_fwd(qh, kh, vh, oh, lse, S, scale, tcgemm.status_word(q.device))
+        return _heads_last(oh, B, S, nq), (qh, kh, vh, oh, lse, (B, S, nq, nkv, hd, scale))
     scores = tcgemm.gemm(qh, kh)                                   # [B*nkv, G*S, S]
     lse = torch.empty(scores.shape[0] * scores.shape[1], dtype=torch.float32, device=q.device)
     ops().attn_softmax(scores, lse, S, scale)

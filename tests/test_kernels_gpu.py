@@ -355,9 +355,13 @@ def test_sharded_trainer_muon_hybrid_single_gpu():
     assert tr.state_bytes_per_param() < 1.2
 
 
-@pytest.mark.parametrize("B,S,nq,nkv,hd", [(2, 128, 8, 2, 64), (1, 256, 4, 4, 128), (2, 72, 6, 3, 128)])
-def test_gemm_composed_attention_matches_sdpa(B, S, nq, nkv, hd):
-    """tcgen05 GEMM + own softmax / backward row kernels against fp32 SDPA (forward and gradients)."""
+@pytest.mark.parametrize("B,S,nq,nkv,hd,flash", [(2, 128, 8, 2, 64, False), (1, 256, 4, 4, 128, False),
+                                                 (2, 72, 6, 3, 128, False), (2, 128, 8, 2, 64, True),
+                                                 (1, 384, 4, 4, 128, True), (2, 512, 8, 2, 128, True),
+                                                 (1, 256, 6, 1, 64, True)])
+def test_own_attention_matches_sdpa(B, S, nq, nkv, hd, flash):
+    """Own attention (fused tcgen05 forward or GEMM-composed forward; GEMM-composed backward with own
+    row kernels) against fp32 SDPA: output and all three gradients."""
     import torch.nn.functional as F
 
     from gefen_x_b200.ops import attention as A
@@ -369,8 +373,12 @@ def test_gemm_composed_attention_matches_sdpa(B, S, nq, nkv, hd):
     v = torch.randn(B, S, nkv, hd, generator=g).bfloat16().to(dev)
     do = torch.randn(B, S, nq, hd, generator=g).bfloat16().to(dev)
     assert A.supported(q, k)
-    out, ctx = A.attention_fwd(q, k, v)
+    assert not flash or A.flash_supported(S, hd)
+    out, ctx = A.attention_fwd(q, k, v, flash=flash)
     dq, dk, dv = A.attention_bwd(ctx, do)
+    from gefen_x_b200.ops import tcgemm
+
+    assert int(tcgemm.status_word(dev).item()) == 0
     qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
     ref = F.scaled_dot_product_attention(qr.transpose(1, 2), kr.transpose(1, 2), vr.transpose(1, 2),
                                          is_causal=True, enable_gqa=nq != nkv).transpose(1, 2)
