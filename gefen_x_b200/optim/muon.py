@@ -418,14 +418,20 @@ class GefenMuon(Gefen):
     # checkpoint: distributed mode keeps momentum on the owner only
     # ------------------------------------------------------------------
     def state_dict(self):
+        """Native state dict; in ``distributed`` mode the owners' momentum is gathered so that every
+        rank returns the same, complete (consolidated) checkpoint, loadable at any world size
+        (reference ``gefen_muon.py:2110-2284``).  Collective: every rank of the mesh must call it."""
         sd = super().state_dict()
         if self.sharded_mode == "distributed":
             groups = []
             stable = 0
+            pgs = {}
             for g in self.param_groups:
                 entries = []
                 for p in g["params"]:
-                    _pg, world, _r = self._process_group_of(p)
+                    pg, world, _r = self._process_group_of(p)
+                    if pg is not None and world > 1:
+                        pgs[id(pg)] = (pg, world)
                     st = self.state.get(p, {})
                     entries.append({"saved_id": stable, "name": self._param_name(p),
                                     "shape": tuple(p.shape),
@@ -435,11 +441,48 @@ class GefenMuon(Gefen):
                     stable += 1
                 groups.append({"world_size": max((self._process_group_of(p)[1] for p in g["params"]),
                                                  default=1), "params": entries})
+            consolidated = False
+            if len(pgs) == 1:
+                import torch.distributed as dist
+
+                (pg, world), = pgs.values()
+
+                def to_cpu(v):
+                    return v.detach().cpu() if torch.is_tensor(v) else v
+
+                mine = {k: {kk: to_cpu(vv) for kk, vv in st.items()} for k, st in sd["state"].items()}
+                gathered = [None] * world
+                dist.all_gather_object(gathered, mine, group=pg)
+                merged = {}
+                for part in gathered:                      # non-owners may hold a few scalar keys:
+                    for k, st in part.items():             # the owner's entry wins
+                        merged.setdefault(k, st)
+                for k in list(merged):
+                    own = gathered[stable_distributed_owner(int(k), world)].get(k)
+                    if own is not None:
+                        merged[k] = own
+                sd["state"] = {k: merged[k] for k in sorted(merged)}
+                for grp in groups:
+                    for e in grp["params"]:
+                        st = merged.get(e["saved_id"], {})
+                        e["state_keys"] = sorted(k for k in st if k != "name")
+                        e["initialized"] = "step" in st
+                consolidated = True
             sd["gefen_muon_distributed"] = {"version": 2, "ownership": "stable_full_param_index_v1",
-                                            "consolidated": False, "groups": groups}
+                                            "consolidated": consolidated, "groups": groups}
         return sd
 
     def load_state_dict(self, state_dict) -> None:
+        """Loads a native checkpoint; after a consolidated ``distributed`` checkpoint every rank
+        keeps only the momentum of the matrices it owns at the current world size."""
         sd = dict(state_dict)
         sd.pop("gefen_muon_distributed", None)
         super().load_state_dict(sd)
+        if self.sharded_mode == "distributed":
+            stable = 0
+            for g in self.param_groups:
+                for p in g["params"]:
+                    pg, world, rank = self._process_group_of(p)
+                    if pg is not None and world > 1 and stable_distributed_owner(stable, world) != rank:
+                        self.state.pop(p, None)
+                    stable += 1
