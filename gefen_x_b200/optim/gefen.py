@@ -48,6 +48,7 @@ FUSE_GEFEN_AUTOMATIC_STEP = True
 FUSE_HISTOGRAM_FOR_EXACT = True
 
 _SYNTH_KEY = "param_names_synthesized"
+_RANK_LOCAL_KEY = "gefen_rank_local"
 _META_KEY = "_gefen_checkpoint_metadata"
 _COUNTER_KEYS = ("step", "vmean_step", "factored_step", "normuon_step")
 _SCRATCH_KEYS = ("stepsize", "_h_buf", "_capt_row", "_capt_dev", "_fx_scratch")
@@ -1125,7 +1126,84 @@ class Gefen(torch.optim.Optimizer):
         }
         for g in sd["param_groups"]:
             g[_META_KEY] = meta
+        ctx = None if getattr(self, "_local_state_dict_only", False) else self._rank_local_context()
+        if ctx is not None:
+            sd = self._attach_rank_local_payloads(sd, *ctx)
         return sd
+
+    def local_state_dict(self) -> Dict[str, Any]:
+        """This rank's native state dict without any collective (snapshots, rollbacks)."""
+        self._local_state_dict_only = True
+        try:
+            return self.state_dict()
+        finally:
+            self._local_state_dict_only = False
+
+    # -- rank-local checkpoints of row-sharded (DTensor) parameters ---------------------------
+    def _rank_local_checkpoint_applies(self) -> bool:
+        """Whether per-rank state differs between ranks (plain Gefen on shards: yes)."""
+        return True
+
+    def _rank_local_context(self):
+        """(process group, world, rank) when parameters are DTensors sharded over more than one
+        rank of a 1-D mesh, else None.  Multi-dimensional meshes are refused (reference
+        ``gefen.py:4127-4131``)."""
+        if not self._rank_local_checkpoint_applies():
+            return None
+        for g in self.param_groups:
+            for p in g["params"]:
+                mesh = getattr(p, "device_mesh", None)
+                if mesh is None:
+                    continue
+                if mesh.ndim != 1:
+                    raise ValueError("Gefen rank-local checkpoints need a 1-D device mesh; use "
+                                     "GefenDCPState for other layouts")
+                if mesh.size(0) > 1:
+                    return mesh.get_group(0), mesh.size(0), mesh.get_local_rank(0)
+        return None
+
+    @staticmethod
+    def _attach_rank_local_payloads(sd, pg, world, rank):
+        """Every rank's whole local checkpoint travels in every rank's state dict, so that the file
+        one rank writes restores all of them on the same topology (format ``rank_local_dtensor_v2``,
+        reference ``gefen.py:4408-4556``).  Collective over ``pg``."""
+        import io
+
+        import torch.distributed as dist
+
+        def to_cpu(v):
+            if torch.is_tensor(v):
+                return v.detach().cpu()
+            if isinstance(v, dict):
+                return {k: to_cpu(x) for k, x in v.items()}
+            if isinstance(v, (list, tuple)):
+                return type(v)(to_cpu(x) for x in v)
+            return v
+
+        buf = io.BytesIO()
+        torch.save(to_cpu(sd), buf)
+        payloads = [None] * world
+        dist.all_gather_object(payloads, buf.getvalue(), group=pg)
+        out = dict(sd)
+        out[_RANK_LOCAL_KEY] = {"format": "rank_local_dtensor_v2", "metadata_version": 3,
+                                "world_size": world, "payloads": payloads}
+        return out
+
+    def _select_rank_local_payload(self, state_dict):
+        """The local checkpoint of this rank out of a ``rank_local_dtensor_v2`` state dict."""
+        rl = state_dict.get(_RANK_LOCAL_KEY) if isinstance(state_dict, dict) else None
+        if rl is None:
+            return state_dict
+        import io
+
+        if rl.get("format") != "rank_local_dtensor_v2":
+            raise ValueError("unknown Gefen rank-local checkpoint format {!r}".format(rl.get("format")))
+        ctx = self._rank_local_context()
+        if ctx is None or ctx[1] != rl["world_size"]:
+            raise ValueError(
+                "this checkpoint holds the rank-local state of {} ranks and restores only on the same "
+                "topology; use GefenDCPState to reshard".format(rl["world_size"]))
+        return torch.load(io.BytesIO(rl["payloads"][ctx[2]]), weights_only=False)
 
     @staticmethod
     def _same_codebook(a, b) -> bool:
@@ -1302,6 +1380,7 @@ class Gefen(torch.optim.Optimizer):
         so a failing load leaves the live optimizer untouched (reference
         ``gefen.py:4818-4856``).
         """
+        state_dict = self._select_rank_local_payload(state_dict)
         sd, step, cb = self._parse_checkpoint_header(state_dict)
         shadow = object.__new__(type(self))
         shadow.__dict__.update(self.__dict__)

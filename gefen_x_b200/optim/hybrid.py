@@ -300,7 +300,7 @@ class GefenMuonHybrid:
                 shadow.load_state_dict(sd)
                 staged.append((child, shadow))
             else:
-                snapshot = copy.deepcopy(child.state_dict())
+                snapshot = copy.deepcopy(child.local_state_dict() if hasattr(child, "local_state_dict") else child.state_dict())
                 staged.append((child, ("torch", sd, snapshot)))
         done = []
         try:

@@ -417,6 +417,10 @@ class GefenMuon(Gefen):
     # ------------------------------------------------------------------
     # checkpoint: distributed mode keeps momentum on the owner only
     # ------------------------------------------------------------------
+    def _rank_local_checkpoint_applies(self) -> bool:
+        # exact: every rank holds the same full-matrix state; distributed: consolidated below
+        return self.sharded_mode == "approx"
+
     def state_dict(self):
         """Native state dict; in ``distributed`` mode the owners' momentum is gathered so that every
         rank returns the same, complete (consolidated) checkpoint, loadable at any world size

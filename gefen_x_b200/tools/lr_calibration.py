@@ -49,7 +49,8 @@ def _snapshot(optimizer):
     params = [p for g in optimizer.param_groups for p in g["params"]]
     return {
         "params": [_local(p).detach().clone() for p in params],
-        "state": copy.deepcopy(optimizer.state_dict()),
+        "state": copy.deepcopy(optimizer.local_state_dict() if hasattr(optimizer, "local_state_dict")
+                               else optimizer.state_dict()),
         "hypers": [{k: v for k, v in g.items() if k != "params"} for g in optimizer.param_groups],
     }
 

@@ -136,3 +136,86 @@ def test_rank_leaving_between_steps_is_seen_on_the_host():
         pr.join(timeout=60)
     assert results[1] == "left"
     assert results[0] == "peer gone: skip collective"
+
+
+def _rank_local_worker(rank, world, port, path, q):
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+
+    from gefen_x_b200 import Gefen
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        mesh = init_device_mesh("cpu", (world,))
+
+        def full(seed, shape):
+            return torch.randn(shape, generator=torch.Generator().manual_seed(seed)) * 0.1
+
+        def make():
+            ps = [("w", distribute_tensor(full(0, (16, 24)), mesh, [Shard(0)]).requires_grad_(True)),
+                  ("b", distribute_tensor(full(1, (16,)), mesh, [Shard(0)]).requires_grad_(True))]
+            return ps, Gefen(ps, lr=1e-2, fused=False, factored_v_2d=False)
+
+        def step(ps, opt, k):
+            for i, (n, p) in enumerate(ps):
+                p.grad = distribute_tensor(full(100 + 10 * k + i, tuple(p.shape)), mesh, [Shard(0)])
+            opt.step()
+
+        ps, opt = make()
+        for k in range(3):
+            step(ps, opt, k)
+        sd = opt.state_dict()                                  # collective: carries every rank's payload
+        rl = sd["gefen_rank_local"]
+        weights = {n: p.full_tensor().detach().clone() for n, p in ps}
+        if rank == 0:
+            torch.save({"sd": sd, "weights": weights}, path)
+        dist.barrier()
+        blob = torch.load(path, weights_only=False)            # both ranks read the file rank 0 wrote
+        ps2, opt2 = make()
+        for n, p in ps2:
+            p.data.copy_(distribute_tensor(blob["weights"][n], mesh, [Shard(0)]))
+        opt2.load_state_dict(blob["sd"])
+        same_idx = all(torch.equal(opt.state[a]["m_codebook"], opt2.state[b]["m_codebook"])
+                       for (_, a), (_, b) in zip(ps, ps2))
+        step(ps, opt, 3)
+        step(ps2, opt2, 3)
+        same_w = all(torch.equal(a.to_local(), b.to_local()) for (_, a), (_, b) in zip(ps, ps2))
+        # a single-process optimizer refuses the rank-local file
+        refused = False
+        try:
+            Gefen([("w", full(0, (16, 24)).requires_grad_(True))], lr=1e-2, fused=False).load_state_dict(blob["sd"])
+        except ValueError as e:
+            refused = "same" in str(e)
+        q.put((rank, dict(fmt=rl["format"], world=rl["world_size"], n_payloads=len(rl["payloads"]),
+                          same_idx=same_idx, same_w=same_w, refused=refused)))
+    except Exception:  # pragma: no cover - reported to the parent
+        import traceback
+
+        q.put((rank, {"error": traceback.format_exc()}))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_rank_local_checkpoint_of_sharded_parameters_round_trips():
+    import tempfile
+
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    with tempfile.TemporaryDirectory() as d:
+        procs = [ctx.Process(target=_rank_local_worker, args=(r, world, port, os.path.join(d, "opt.pt"), q))
+                 for r in range(world)]
+        for pr in procs:
+            pr.start()
+        results = dict(q.get(timeout=300) for _ in range(world))
+        for pr in procs:
+            pr.join(timeout=60)
+    for r in range(world):
+        assert "error" not in results[r], results[r].get("error")
+        o = results[r]
+        assert o["fmt"] == "rank_local_dtensor_v2" and o["world"] == 2 and o["n_payloads"] == 2
+        assert o["same_idx"] and o["same_w"] and o["refused"]
