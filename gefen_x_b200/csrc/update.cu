@@ -561,7 +561,6 @@ __device__ __forceinline__ void stats_tile_fast(const Hot& d, const Smem& s, con
     const int tx = threadIdx.x % d.tcols, ty = threadIdx.x / d.tcols;
     const int c0 = (t.ct * d.tcols + tx) * 8;
     const bool act = c0 < d.cols;
-    const bool uniform = run.uniform != 0;
     const T* g0 = reinterpret_cast<const T*>(d.g0);
     const int stride = d.trows;
     int r = t.r0 + ty;
@@ -603,21 +602,27 @@ __device__ __forceinline__ void stats_tile_fast(const Hot& d, const Smem& s, con
                 csum[e] += sq;
             }
         }
+        const float rs_lane = rs;
         if (!run.sum_dst) {
             rs = warp_sum(rs);
             if ((threadIdx.x & 31) == 0 && act) atomicAdd(d.row_sq + r, rs);
         }
-        if (uniform) {
-            const int b0 = __shfl_sync(0xffffffffu, blk, 0);   // lane 0 has the lowest column
-            if (b0 >= 0) {
+        // Blocks are contiguous in memory, so the warp's 256 columns of this row lie in one block
+        // iff its first and its last active lane do (checked every row: with a period that is not
+        // a multiple of the row length only the few rows a block boundary crosses differ).  The
+        // warp then shares one running maximum; on a boundary row every lane posts its own value.
+        const unsigned live = __ballot_sync(0xffffffffu, act);
+        if (live) {
+            const int b0 = __shfl_sync(0xffffffffu, blk, 0);               // lane 0 has the lowest column
+            const int b1 = __shfl_sync(0xffffffffu, blk, 31 - __clz((int)live));
+            if (b0 == b1) {
                 if ((long long)b0 != run.blk) { runmax_flush(run); run.blk = b0; }
                 run.val = fmaxf(run.val, amax);
-                run.sum += rs;       // only read when sum_dst is set (a row lies inside one block)
+                run.sum += rs_lane;   // only read when sum_dst is set
+            } else if (act) {
+                atomic_max_nonneg(run.dst + blk, amax);
+                if (run.sum_dst) atomicAdd(run.sum_dst + blk, rs_lane);
             }
-        } else if (act) {
-            if ((long long)blk != run.blk) { runmax_flush(run); run.blk = blk; }
-            run.val = fmaxf(run.val, amax);
-            if (run.sum_dst) atomicAdd(run.sum_dst + blk, rs);
         }
 #pragma unroll
         for (int k = 0; k < kStatsAhead; ++k) q[k] = q[k + 1];
@@ -764,7 +769,7 @@ __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_stats
     walk_begin(c, T0, w, d);
     run.dst = d.mag_new;
     run.sum_dst = d.row_only ? d.row_sq : nullptr;
-    run.uniform = warp_uniform_blocks(d, d.vec ? 8 : 1) ? 1 : 0;
+    run.uniform = (FAST || warp_uniform_blocks(d, d.vec ? 8 : 1)) ? 1 : 0;
     for (long long tile = T0; tile < T1;) {
         const int n = (int)min(T1 - tile, (long long)(w.n_row_tiles - w.rt));
         const TileCursor t = walk_cursor(w, d, n);
@@ -799,7 +804,7 @@ __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_stats
             w.n_row_tiles = (d.rows + d.rows_per_tile - 1) / d.rows_per_tile;
             run.dst = d.mag_new;
             run.sum_dst = d.row_only ? d.row_sq : nullptr;
-            run.uniform = warp_uniform_blocks(d, d.vec ? 8 : 1) ? 1 : 0;
+            run.uniform = (FAST || warp_uniform_blocks(d, d.vec ? 8 : 1)) ? 1 : 0;
         }
     }
 }

@@ -74,6 +74,8 @@ def test_update_kernels_match_decomposed(shape, dtype, factored):
     ((64, 4096), 131072, False),     # same through the two-phase block path
     ((1 << 20,), 1 << 19, False),    # flat tensor, two long blocks
     ((48, 2048), 1024, True),        # period divides the row
+    ((96, 2048), 3072, True),        # vector path, block boundaries fall inside rows (and inside warps)
+    ((96, 4096), 6144, True),        # same with two warps per row
     ((100, 24), 40, True),           # scalar path, blocks straddle rows
 ])
 def test_update_kernels_forced_periods(shape, period, factored):
