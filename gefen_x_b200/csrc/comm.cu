@@ -7,7 +7,7 @@
 // peer surfaces as a host-side error instead of a hung GPU.
 //
 // The reference has no custom collective; it relies on torch FSDP2's NCCL
-// all-gather / reduce-scatter (reference SURVEY of collectives:
+// all-gather / reduce-scatter (reference collective call sites:
 // src/gefen/gefen.py:3496-3499, src/gefen/gefen_muon.py:1849-1896).
 #include "comm.h"
 #include "common.cuh"

@@ -20,9 +20,12 @@
 // this rank's shard inside every peer's unsharded bf16 gradient buffer); they
 // are summed in fp32 and rounded to the gradient dtype, which is what a
 // reduce-scatter would have delivered, so the collective is fused into the
-// update.  HBM-bound: 16-byte vector loads, 8 elements per thread, several rows
-// in flight per thread, persistent CTAs walking a contiguous tile range so that
-// column partial sums are flushed once per column tile.
+// update.  HBM-bound by design: 16-byte vector loads, 8 elements per thread and
+// row, persistent CTAs walking a contiguous range of equally sized work tiles so
+// that column partial sums are flushed once per column tile.  Plans whose tensors
+// all take the 8-wide single-source path run the "fast" tile loops: one row per
+// iteration with the next row's raw chunk prefetched into registers, a loop body
+// small enough for the instruction cache, 80 registers and three CTAs per SM.
 #include "common.cuh"
 #include "update.h"
 #include <cstdlib>
@@ -306,19 +309,6 @@ struct TileCursor {
     int ti, ct;          // tensor, column tile
     int r0, r1;          // row range of the tile
 };
-
-__device__ __forceinline__ TileCursor locate(const LaunchCommon& c, int tile) {
-    TileCursor t;
-    t.ti = find_tensor(c.tile_start, c.n_tensors, tile);
-    const TensorDesc& d = c.descs[t.ti];
-    const int local = tile - c.tile_start[t.ti];
-    const int n_row_tiles = (d.rows + d.rows_per_tile - 1) / d.rows_per_tile;
-    t.ct = local / n_row_tiles;
-    const int rt = local - t.ct * n_row_tiles;
-    t.r0 = rt * d.rows_per_tile;
-    t.r1 = min(d.rows, t.r0 + d.rows_per_tile);
-    return t;
-}
 
 // Running maximum of |m| for the block a thread (or, when every lane of a warp
 // is in the same block, the warp) is currently inside.  It is flushed with one

@@ -442,6 +442,10 @@ class Gefen(torch.optim.Optimizer):
             return False
         if not t.is_cuda or t.dtype == torch.float64:
             return False
+        if self._deterministic and self._factored_v_2d and t.dim() == 2:
+            # the two-phase kernels sum row / column statistics with atomics (order not fixed);
+            # the replica-exact policy takes the fixed-order torch statement for those tensors
+            return False
         if self._fused_build_ok is None:
             from ..ops import update as _u
 
@@ -871,7 +875,8 @@ class Gefen(torch.optim.Optimizer):
                 gsrc = grad.contiguous()
             if factored and work.dim() != 2:
                 raise ValueError("factored update expects a 2-D parameter")
-            row_only = (not factored) and _u.two_phase_block(period, work.numel() // period)
+            row_only = (not factored) and not self._deterministic and \
+                _u.two_phase_block(period, work.numel() // period)
             item = _u.Item(p=work, grad=gsrc, state=state, period=period, beta1=beta1, beta2=beta2,
                            eps=eps, scalars=host, scal_ptr=scal_ptr, shard=shard, row_only=row_only)
             key = ("factored" if (factored or row_only) else "block", dev, work.dtype)

@@ -59,3 +59,35 @@ def test_two_ranks_track_single_gpu(tmp_path, rs_mode, clip, ag):
     for a, b in zip(ref, got):
         assert abs(a - b) < 0.05 * max(1.0, abs(a)), (ref, got)
     assert multi["state_bytes_per_param"] < 1.2
+
+
+def test_one_optimizer_over_two_devices_matches_single_device():
+    """Layer-wise model parallel (parameters of one optimizer on two GPUs): per-device codebook,
+    threshold and bucket-table copies; same trajectory as all parameters on one device
+    (reference tests/test_codebook_multi_device.py)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from gefen_x_b200 import Gefen
+
+    def params(devs):
+        g = torch.Generator().manual_seed(0)
+        shapes = [("a.weight", (64, 256)), ("b.weight", (128, 64)), ("norm.weight", (256,)), ("c.weight", (32, 512))]
+        return [(n, (torch.randn(s, generator=g) * 0.05).bfloat16().to(devs[i % len(devs)]).requires_grad_())
+                for i, (n, s) in enumerate(shapes)]
+
+    d0, d1 = torch.device("cuda", 0), torch.device("cuda", 1)
+    pa, pb = params([d0]), params([d0, d1])
+    oa, ob = Gefen(pa, lr=1e-2, weight_decay=0.01), Gefen(pb, lr=1e-2, weight_decay=0.01)
+    for step in range(4):
+        g = torch.Generator().manual_seed(100 + step)
+        for (_, a), (_, b) in zip(pa, pb):
+            gr = (torch.randn(a.shape, generator=g) * 1e-2).bfloat16()
+            a.grad = gr.to(a.device)
+            b.grad = gr.to(b.device)
+        oa.step()
+        ob.step()
+    assert {p.device for _, p in pb} == {d0, d1}
+    for (n, a), (_, b) in zip(pa, pb):
+        assert torch.equal(oa.state[a]["m_codebook"].cpu(), ob.state[b]["m_codebook"].cpu()), n
+        torch.testing.assert_close(a.float().cpu(), b.float().cpu(), rtol=0, atol=1e-3, msg=n)
+    assert all(v == 0 for v in ob.kernel_status().values())

@@ -192,3 +192,30 @@ def test_requantise_and_dense_dequantise_kernels():
     dm = dense_momentum(opt._gefen_codebook, st, ps[0][1].shape)
     want = C.dequantize_indices(opt._gefen_codebook.to(dev), st["m_codebook"]) * st["m_magnitude"]
     assert torch.equal(dm.reshape(-1), want.reshape(-1))
+
+
+def test_deterministic_policy_is_replica_exact():
+    """deterministic=True: two replicas stepping the same data agree bit for bit, run after run
+    (reference tests/test_deterministic_mode.py: replica hashes)."""
+    from gefen_x_b200 import Gefen
+
+    def run():
+        g = torch.Generator().manual_seed(0)
+        shapes = [("a.weight", (512, 2048)), ("b.weight", (1024, 512)), ("flat", (1 << 20,)), ("bias", (40,))]
+        ps = [(n, (torch.randn(s, generator=g) * 0.05).bfloat16().to(_dev()).requires_grad_()) for n, s in shapes]
+        opt = Gefen(ps, lr=1e-2, weight_decay=0.01, deterministic=True)
+        for step in range(4):
+            gg = torch.Generator().manual_seed(100 + step)
+            for _, p in ps:
+                p.grad = (torch.randn(p.shape, generator=gg) * 1e-2).bfloat16().to(_dev())
+            opt.step()
+        return ps, opt
+
+    (pa, oa), (pb, ob) = run(), run()
+    for (n, a), (_, b) in zip(pa, pb):
+        assert torch.equal(a, b), n
+        for key in ("m_codebook", "m_magnitude"):
+            assert torch.equal(oa.state[a][key], ob.state[b][key]), (n, key)
+        vk = "v_row" if "v_row" in oa.state[a] else "vmean"
+        assert torch.equal(oa.state[a][vk], ob.state[b][vk]), (n, vk)
+    assert oa.state_dict()["gefen_deterministic"] is True
