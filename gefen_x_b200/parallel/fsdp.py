@@ -143,7 +143,7 @@ class ShardedTrainer:
         self.reduce_mode = reduce_mode
         self._reduce_stage: Optional[torch.Tensor] = None
         self.reduce_ctas = max(1, min(int(reduce_ctas), 2048))
-        self._copy_tables: Dict[Tuple[int, int, bool], torch.Tensor] = {}
+        self._copy_tables: Dict[tuple, torch.Tensor] = {}
         self.ag_gemm = bool(ag_gemm) and int(world) > 1
         self.ag_fetch_ctas = int(ag_fetch_ctas)
         self.step_count = 0
@@ -196,6 +196,7 @@ class ShardedTrainer:
         self.SLOT_PARAMS = len(self.all_groups)
         self.SLOT_NORM = len(self.all_groups) + 1
         self.SLOT_MUON = len(self.all_groups) + 2
+        self.SLOT_HEAD = len(self.all_groups) + 3      # arrival of the head's gradients (early reduction)
         self._muon_region = None
         if self.hybrid:
             self._muon_region, self._muon_region_off = self.arena.alloc(max(muon_region_bytes, 256), torch.uint8)
@@ -339,6 +340,12 @@ class ShardedTrainer:
             g.gather_tables_rest = self._gather_table_for(
                 g, [sp for sp in g.specs if not sp.name.endswith(self._QKV)])
         g.gather_tables = self._gather_table_for(g, g.specs)
+        if g is self.embed_group and not self.cfg.tie_embeddings:
+            # the untied head (and the final norm) are not needed before the end of forward: their
+            # gather is issued behind the first layers', off the critical path of the step start
+            late = [sp for sp in g.specs if sp.name in self._LATE_EMBED]
+            g.gather_tables_first = self._gather_table_for(g, [sp for sp in g.specs if sp not in late])
+            g.gather_tables_late = self._gather_table_for(g, late)
 
     def _gather_table_for(self, g: Group, specs):
         esz = torch.empty((), dtype=self.dtype).element_size()
@@ -359,7 +366,7 @@ class ShardedTrainer:
         return (host.to(self.device), len(segs),
                 torch.tensor(prefix, dtype=torch.int64, device=self.device), prefix[-1], copies)
 
-    def _build_reduce_table(self, g: Group) -> None:
+    def _build_reduce_table(self, g: Group, part: str = "all"):
         """Slices of this rank's shard inside every rank's unsharded gradient buffer (one launch
         reduces them all); Muon-routed matrices are reduced by their owners instead.
 
@@ -383,6 +390,9 @@ class ShardedTrainer:
         for sp in g.specs:
             n = sp.shard_rows[self.rank] * sp.cols
             if n == 0 or sp.name in self._muon_names:
+                continue
+            if (part == "early" and sp.name not in self._LATE_EMBED) or \
+                    (part == "rest" and sp.name in self._LATE_EMBED):
                 continue
             src_off, _ = g.local_slice(sp, self.rank)
             arena_off = g.full_g_off + src_off * esz
@@ -410,8 +420,8 @@ class ShardedTrainer:
                 arr[i].src[r] = ptr
         host = torch.frombuffer(arr, dtype=torch.uint8).clone()
         copy_table = torch.tensor(copies, dtype=torch.int64).reshape(-1, 3) if copies else None
-        g.reduce_table = (host.to(self.device), len(segs),
-                          torch.tensor(prefix, dtype=torch.int64, device=self.device), prefix[-1], copy_table)
+        return (host.to(self.device), len(segs),
+                torch.tensor(prefix, dtype=torch.int64, device=self.device), prefix[-1], copy_table)
 
     # ------------------------------------------------------------------
     # optimizer wiring
@@ -530,10 +540,18 @@ class ShardedTrainer:
     # ------------------------------------------------------------------
     # parameter gather (all-gather by peer loads)
     # ------------------------------------------------------------------
-    def _gather_into(self, g: Group, dst: torch.Tensor, rest_only: bool = False) -> None:
-        segs, n_segs, prefix, total, copies = g.gather_tables_rest if rest_only else g.gather_tables
+    _LATE_EMBED = ("lm_head.weight", "model.norm.weight")
+
+    def _gather_into(self, g: Group, dst: torch.Tensor, rest_only: bool = False, part: str = "all") -> None:
+        if part == "first":
+            tables = g.gather_tables_first
+        elif part == "late":
+            tables = g.gather_tables_late
+        else:
+            tables = g.gather_tables_rest if rest_only else g.gather_tables
+        segs, n_segs, prefix, total, copies = tables
         if self.gather_mode == "ce":
-            key = (id(g), dst.data_ptr(), bool(rest_only))
+            key = (id(g), dst.data_ptr(), bool(rest_only), part)
             table = self._copy_tables.get(key)
             if table is None:
                 base = self.arena.base_ptrs
@@ -580,7 +598,10 @@ class ShardedTrainer:
     # ------------------------------------------------------------------
     # gradient reduction (reduce-scatter by peer loads) and the clip norm
     # ------------------------------------------------------------------
-    def _reduce_group(self, gi: int) -> None:
+    def _reduce_group(self, gi: int, part: str = "all") -> None:
+        """Reduce-scatter the gradients of group ``gi``.  ``part`` splits the embedding group:
+        ``"early"`` = head and final norm (complete right after the head's backward), ``"rest"`` =
+        the token embedding (complete at the very end); each part has its own arrival flags."""
         g = self.all_groups[gi]
         t = self.step_count
         code_dev = self.device
@@ -603,19 +624,22 @@ class ShardedTrainer:
         ev.record(torch.cuda.current_stream())
         with torch.cuda.stream(self.reduce_stream):
             self.reduce_stream.wait_event(ev)
-            self.flags.signal(gi, t)
-            self.flags.wait(gi, t)
+            slot = self.SLOT_HEAD if part == "early" else gi
+            self.flags.signal(slot, t)
+            self.flags.wait(slot, t)
             if self.rs_mode == "stash" or self.clip:
-                if not hasattr(g, "reduce_table"):
-                    self._build_reduce_table(g)
-                segs, n_segs, prefix, total, copy_table = g.reduce_table
+                if not hasattr(g, "reduce_tables"):
+                    g.reduce_tables = {}
+                if part not in g.reduce_tables:
+                    g.reduce_tables[part] = self._build_reduce_table(g, part)
+                segs, n_segs, prefix, total, copy_table = g.reduce_tables[part]
                 if copy_table is not None:
                     ops().comm_copy_list(copy_table, self.device.index or 0)
                 if n_segs:
                     ops().comm_reduce_segments(self.world, segs, n_segs, prefix, total,
                                                1.0 / self.world, self.norm_partials if self.clip else None,
                                                self.reduce_ctas, U.DTYPE_CODE[self.dtype])
-            if self.hybrid:
+            if self.hybrid and part != "early":
                 self.muon.reduce_group(gi)
 
     def _finish_norm(self) -> None:
@@ -722,16 +746,19 @@ class ShardedTrainer:
                     self.norm_partials.zero_()
             else:
                 self.norm_partials.zero_()
+        split_embed = False
         if multi:
             with torch.cuda.stream(self.comm_stream):
                 self.comm_stream.wait_stream(torch.cuda.current_stream())
                 if t > 1:
                     self.flags.wait(self.SLOT_PARAMS, t - 1)
-                self._gather_into(eg, eg.full_w)
+                split_embed = hasattr(eg, "gather_tables_late")
+                self._gather_into(eg, eg.full_w, part="first" if split_embed else "all")
                 ev = torch.cuda.Event()
                 ev.record(self.comm_stream)
             self._ensure_layer(0)
             torch.cuda.current_stream().wait_event(ev)
+        head_ready = None
         self._mark("embed_ready")
         ew = self._embed_views(eg.full_w)
         egrad = self._embed_views(eg.full_g)
@@ -746,6 +773,11 @@ class ShardedTrainer:
             flat = self._ensure_layer(li, rest_only=fused)
             if li + 1 < L:
                 self._ensure_layer(li + 1, rest_only=fused)
+            if multi and split_embed and li == min(1, L - 1):
+                with torch.cuda.stream(self.comm_stream):      # behind the first layers' gathers
+                    self._gather_into(eg, eg.full_w, part="late")
+                    head_ready = torch.cuda.Event()
+                    head_ready.record(self.comm_stream)
             self._wait_layer(li)
             self._mark("f.start")
             x, sv = layer_forward(cfg, layer_views(cfg, flat), x, cos, sin, save=True,
@@ -755,6 +787,8 @@ class ShardedTrainer:
             self._mark_layer_done(li)
 
         # ---- head: final norm, logits, loss, and their backward -----------
+        if head_ready is not None:
+            torch.cuda.current_stream().wait_event(head_ready)
         x2d = x.reshape(T, cfg.hidden)
         hN, rstdN = M.rmsnorm_fwd(x2d, ew["model.norm.weight"], cfg.rms_eps)
         logits = G.mm_nt(hN, head_w)
@@ -769,6 +803,9 @@ class ShardedTrainer:
         dx2d, dnorm = M.rmsnorm_bwd(dhN, x2d, ew["model.norm.weight"], rstdN)
         egrad["model.norm.weight"].copy_(dnorm)
         dx = dx2d.view(B, S, cfg.hidden)
+        if multi and not cfg.tie_embeddings:
+            # the head's and the final norm's gradients are complete: reduce them under backward
+            self._reduce_group(len(self.all_groups) - 1, part="early")
         self._mark("head.end")
 
         # ---- backward ----------------------------------------------------
@@ -787,7 +824,8 @@ class ShardedTrainer:
             self._reduce_group(li)
         egrad["model.embed_tokens.weight"].index_add_(0, tok.reshape(-1), dx.reshape(T, cfg.hidden))
         self._mark("bwd.end")
-        self._reduce_group(len(self.all_groups) - 1)
+        self._reduce_group(len(self.all_groups) - 1,
+                           part="rest" if (multi and not cfg.tie_embeddings) else "all")
         self._finish_norm()
         if multi:
             torch.cuda.current_stream().wait_stream(self.reduce_stream)
