@@ -12,7 +12,9 @@ import tempfile
 import torch
 import torch.multiprocessing as mp
 
-SHAPES = [("a.weight", (16, 24)), ("b.weight", (8, 16)), ("c.weight", (24, 8))]
+SHAPES = [("a.weight", (16, 24)), ("b.weight", (8, 16)), ("c.weight", (24, 8)),
+          ("d.weight", (5, 8)),      # uneven row shards (3 + 2)
+          ("e.weight", (1, 8))]      # rank 1 holds an empty shard
 
 
 def _free_port():
@@ -122,10 +124,10 @@ def test_distributed_muon_matches_exact_and_checkpoint_is_consolidated():
     ref4, _ = _oracle(4)
     r0, r1 = results[0], results[1]
     # ownership: stable index mod world; state only on the owner; both ranks hold the whole checkpoint
-    assert r0["owned"] == ["a.weight", "c.weight"] and r1["owned"] == ["b.weight"]
+    assert r0["owned"] == ["a.weight", "c.weight", "e.weight"] and r1["owned"] == ["b.weight", "d.weight"]
     assert r0["owned2"] == r0["owned"] and r1["owned2"] == r1["owned"]
-    assert r0["consolidated"] and r1["consolidated"] and r0["n_state"] == 3 and r1["n_state"] == 3
-    assert r0["owners"] == [0, 1, 0]
+    assert r0["consolidated"] and r1["consolidated"] and r0["n_state"] == 5 and r1["n_state"] == 5
+    assert r0["owners"] == [0, 1, 0, 1, 0]
     for n, _ in SHAPES:
         assert torch.allclose(torch.from_numpy(r0["after3"][n]), ref3[n], atol=2e-5), n
         assert torch.allclose(torch.from_numpy(r0["cont"][n]), ref4[n], atol=2e-5), n
