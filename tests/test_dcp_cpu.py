@@ -115,12 +115,12 @@ def _run(world, path, mode):
 
 
 @pytest.mark.timeout(600)
-def test_reshard_two_to_one_and_four():
+def _reshard_case(save_world, load_worlds):
     with tempfile.TemporaryDirectory() as d:
         path = os.path.join(d, "ckpt")
-        _tag, saved, step = _run(2, path, "save")
+        _tag, saved, step = _run(save_world, path, "save")
         assert step == 3
-        for world in (1, 4):
+        for world in load_worlds:
             _tag, loaded, step2 = _run(world, path, "load")
             assert step2 == 4
             for k, want in saved.items():
@@ -132,6 +132,17 @@ def test_reshard_two_to_one_and_four():
                 else:
                     # coarser / finer blocks change the shared value, never its scale
                     assert torch.allclose(got.mean(), want.mean(), rtol=0.05, atol=1e-12), (k, world)
+
+
+@pytest.mark.timeout(600)
+def test_reshard_two_to_one_and_four():
+    _reshard_case(2, (1, 4))
+
+
+@pytest.mark.timeout(600)
+def test_reshard_four_to_two():
+    """Save on more ranks, reload on fewer (the 8 -> 4 case of the headline configuration in small)."""
+    _reshard_case(4, (2,))
 
 
 def test_layout_validation_single_process():
