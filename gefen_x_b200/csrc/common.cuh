@@ -188,9 +188,11 @@ __device__ __forceinline__ int nearest_index(float v, const QuantTables& q) {
     const uint32_t e = q.lut[lut_bucket(v)];
     int i = (int)(e & 0xffu);
     const int cnt = (int)(e >> 8);
-    // first probe without a branch (thr[255] = +inf never compares below v); buckets with
-    // more than one threshold are rare and finish in the loop
-    i += (cnt > 0 && q.thr[i] < v) ? 1 : 0;
+    // first probe without a branch: thr[i] is the first threshold not in a lower bucket, so with no
+    // threshold inside this bucket it lies in a higher one and is not below v (the bucket function
+    // is monotonic; thr[255] = +inf); buckets with more than one threshold are rare and finish in
+    // the loop
+    i += (q.thr[i] < v) ? 1 : 0;
     if (cnt > 1) {
         const int hi = (int)(e & 0xffu) + cnt;
         while (i < hi && i > (int)(e & 0xffu) && q.thr[i] < v) ++i;

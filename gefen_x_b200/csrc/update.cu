@@ -697,7 +697,9 @@ __device__ __forceinline__ void apply_tile_fast(const Hot& d, const Smem& s, con
             const int lo = (int)(en & 0xffu);
             const uint32_t cnt = en >> 8;
             many |= cnt;
-            const int k = lo + ((cnt != 0u && s.q.thr[lo] < v) ? 1 : 0);
+            // thr[lo] is the first threshold not in a lower bucket: when this bucket holds none it
+            // lies in a higher bucket and cannot be below v (the bucket function is monotonic)
+            const int k = lo + ((s.q.thr[lo] < v) ? 1 : 0);
             ix[e] = k;
             const float qv = __fmul_rn(rep_load(s.cb, k), mn);
             if (emit) {
