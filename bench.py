@@ -75,6 +75,23 @@ def dist_setup(n_gpus: int):
     return rank, world, local
 
 
+def provenance(dev) -> dict:
+    """Where a number came from: code revision, library versions, device."""
+    import subprocess
+
+    def git(*a):
+        try:
+            return subprocess.run(["git", "-C", ROOT] + list(a), capture_output=True, text=True,
+                                  timeout=10).stdout.strip()
+        except Exception:
+            return ""
+
+    return {"git_commit": git("rev-parse", "--short", "HEAD") or None,
+            "git_dirty": bool(git("status", "--porcelain")) if git("rev-parse", "--short", "HEAD") else None,
+            "torch": torch.__version__, "cuda": torch.version.cuda,
+            "gpu": torch.cuda.get_device_name(dev)}
+
+
 def max_over_ranks(value: float, world: int) -> float:
     if world == 1:
         return value
@@ -203,6 +220,7 @@ def run_ours(args):
         print("rank {} phases {}".format(rank, json.dumps({k: round(v, 2) for k, v in phases.items()})),
               file=sys.stderr, flush=True)
     tokens = world * B * S * args.steps
+    peak_gib = max_over_ranks(torch.cuda.max_memory_allocated(dev) / 2 ** 30, world)
     out = {
         "metric": METRIC, "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
@@ -212,6 +230,8 @@ def run_ours(args):
         "opt_step_ms": opt_step_ms,
         "state_bytes_per_param": trainer.state_bytes_per_param(),
         "gpu_launches": int(launches),
+        "peak_mem_gib": round(peak_gib, 2),
+        "provenance": provenance(dev),
         "clocks": clocks,
         "e2e": e2e,
         "config": {"model": args.model, "layers": cfg.n_layers, "params": trainer.num_params(),

@@ -177,7 +177,7 @@ class ShardedTrainer:
         n_flag_slots = len(self.all_groups) + 4 + n2d
         arena_bytes = 0
         if world > 1:
-            arena_bytes += sum((g.max_shard + g.full_numel) * esz + 1024 for g in self.all_groups)
+            arena_bytes += sum((g.max_shard + g.full_numel) * esz + 2048 for g in self.all_groups)
             arena_bytes += xchg_floats * 4 + n_flag_slots * world * 4 + n2d * 512 + (1 << 20)
         else:
             arena_bytes = 1 << 12
@@ -679,7 +679,11 @@ class ShardedTrainer:
     # ------------------------------------------------------------------
     # device-side step trace (CUDA events on the compute stream)
     # ------------------------------------------------------------------
+    nvtx = False          # set True to emit an NVTX mark at every phase boundary (for timeline tools)
+
     def _mark(self, name: str) -> None:
+        if self.nvtx and self.device.type == "cuda":
+            torch.cuda.nvtx.mark("gefen_x:" + name)
         if self._trace is not None:
             ev = torch.cuda.Event(enable_timing=True)
             ev.record(torch.cuda.current_stream())
@@ -849,6 +853,11 @@ class ShardedTrainer:
         code = int(self.status.item())
         for dev, c in self.opt.kernel_status().items():
             code = max(code, c)
+        broken = self.arena.check_guards()
+        if broken:
+            raise RuntimeError(
+                "gefen_x_b200: {} guard line(s) behind symmetric-arena buffers were overwritten (first "
+                "at byte offset {}): a kernel wrote past its buffer".format(len(broken), broken[0]))
         if code != 0:
             raise RuntimeError(
                 "gefen_x_b200: a bounded wait on a peer ran out (status {}); a rank is missing "

@@ -19,6 +19,8 @@ import torch
 from ..ops._ext import ops
 
 _ALIGN = 256
+_GUARD = 64            # bytes of the guard line behind every arena allocation
+_GUARD_BYTE = 0xA5
 
 
 class SymmetricArena:
@@ -45,18 +47,35 @@ class SymmetricArena:
             self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=self.device)
             self.base_ptrs = [self.buf.data_ptr()]
         self.buf.zero_()
+        self._guards: List[int] = []
 
     def alloc(self, numel: int, dtype: torch.dtype) -> Tuple[torch.Tensor, int]:
-        """Carve ``numel`` elements; returns (local view, byte offset inside the arena)."""
+        """Carve ``numel`` elements; returns (local view, byte offset inside the arena).
+
+        Every allocation is followed by a guard line of ``_GUARD`` bytes holding a fixed pattern:
+        a kernel (local or on a peer) that writes past a buffer lands there, and
+        :meth:`check_guards` finds it on the host."""
         esz = torch.empty((), dtype=dtype).element_size()
         off = (self._cursor + _ALIGN - 1) // _ALIGN * _ALIGN
         nbytes = int(numel) * esz
-        if off + nbytes > self.nbytes:
+        guard = (off + nbytes + 15) // 16 * 16
+        if guard + _GUARD > self.nbytes:
             raise MemoryError("symmetric arena exhausted: need {} more bytes".format(
-                off + nbytes - self.nbytes))
-        self._cursor = off + nbytes
+                guard + _GUARD - self.nbytes))
+        self._cursor = guard + _GUARD
+        self.buf[guard:guard + _GUARD].fill_(_GUARD_BYTE)
+        self._guards.append(guard)
         view = self.buf[off:off + nbytes].view(dtype)
         return view, off
+
+    def check_guards(self) -> List[int]:
+        """Byte offsets of the guard lines that no longer hold their pattern (reads them back)."""
+        if not self._guards:
+            return []
+        idx = torch.tensor(self._guards, dtype=torch.long, device=self.buf.device)
+        lines = self.buf[(idx[:, None] + torch.arange(_GUARD, device=self.buf.device)[None, :]).reshape(-1)]
+        bad = (lines.view(len(self._guards), _GUARD) != _GUARD_BYTE).any(dim=1).cpu().tolist()
+        return [g for g, b in zip(self._guards, bad) if b]
 
     def peer_ptrs(self, byte_offset: int) -> List[int]:
         return [b + int(byte_offset) for b in self.base_ptrs]

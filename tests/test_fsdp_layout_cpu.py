@@ -32,3 +32,19 @@ def test_embed_group_follows_tying():
     untied = embed_group_shapes(get_config("llama3-8b"))
     assert [n for n, _ in tied] == ["model.embed_tokens.weight", "model.norm.weight"]
     assert [n for n, _ in untied][-1] == "lm_head.weight"
+
+
+def test_arena_guard_lines_catch_a_write_past_a_buffer():
+    import torch
+
+    from gefen_x_b200.parallel.symm import SymmetricArena
+
+    arena = SymmetricArena(1 << 14, torch.device("cpu"))
+    a, off_a = arena.alloc(100, torch.float32)
+    b, off_b = arena.alloc(33, torch.bfloat16)
+    a.fill_(1.0)
+    b.fill_(2.0)
+    assert arena.check_guards() == []                     # writing inside the buffers is fine
+    arena.buf[off_b + 33 * 2 + 14] = 0                    # lands in the guard line behind `b`
+    bad = arena.check_guards()
+    assert len(bad) == 1 and off_b + 66 <= bad[0] <= off_b + 66 + 16
