@@ -125,6 +125,8 @@ def host_lib() -> Optional[ctypes.CDLL]:
                 ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                 ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_void_p,
             ]
+            lib.gefen_exact_dp_monotone.restype = ctypes.c_int
+            lib.gefen_exact_dp_monotone.argtypes = list(lib.gefen_exact_dp.argtypes)
             _host_handle = lib
         except Exception:  # pragma: no cover - toolchain missing
             _host_handle = None

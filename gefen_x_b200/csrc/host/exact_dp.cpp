@@ -12,6 +12,7 @@
 // end-index of a row is independent, so the row is split over threads.
 //
 // Plain C ABI so Python can load it with ctypes; no torch headers.
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <limits>
@@ -20,9 +21,10 @@
 extern "C" {
 
 // Returns 0 on success, non-zero on bad arguments.
-int gefen_exact_dp(const double* prefix_w, const double* prefix_wx,
-                   const double* prefix_wx2, int64_t num_points,
-                   int64_t num_codebooks, int force_endpoints, float* codebook_out) {
+static int exact_dp_impl(const double* prefix_w, const double* prefix_wx,
+                         const double* prefix_wx2, int64_t num_points,
+                         int64_t num_codebooks, int force_endpoints, float* codebook_out,
+                         bool use_monotone) {
     if (num_points <= 0 || num_codebooks <= 0 || num_codebooks > num_points) return 1;
     const int64_t n = num_points, k = num_codebooks;
     const double inf = std::numeric_limits<double>::infinity();
@@ -35,6 +37,43 @@ int gefen_exact_dp(const double* prefix_w, const double* prefix_wx,
         const bool pin_hi = force_endpoints && c == k;
         const double centre = pin_lo ? -1.0 : 1.0;
         for (int64_t e = 0; e <= n; ++e) cur[e] = inf;
+        if (use_monotone) {
+            // Divide and conquer over the end index: the segment cost is a sum over points (pinned
+            // rows) or a within-cluster sum of squares (free rows); both satisfy the quadrangle
+            // inequality, so the smallest optimal start is non-decreasing in the end index and
+            // every end only scans the window its neighbours leave open: O(n log n) per row.
+            struct Job { int64_t lo, hi, slo, shi; };
+            std::vector<Job> stack;
+            stack.push_back({c, n, c, n});
+            while (!stack.empty()) {
+                const Job j = stack.back();
+                stack.pop_back();
+                if (j.lo > j.hi) continue;
+                const int64_t e = (j.lo + j.hi) / 2;
+                double best = inf;
+                int64_t best_s = -1;
+                const double we = prefix_w[e], wxe = prefix_wx[e], wx2e = prefix_wx2[e];
+                const int64_t s_end = std::min(e, j.shi);
+                for (int64_t s = std::max(c, j.slo); s <= s_end; ++s) {
+                    const double base = prev[s - 1];
+                    if (!(base < inf)) continue;
+                    const double sw = we - prefix_w[s - 1];
+                    const double swx = wxe - prefix_wx[s - 1];
+                    const double swx2 = wx2e - prefix_wx2[s - 1];
+                    const double seg = (pin_lo || pin_hi) ? swx2 - 2.0 * centre * swx + centre * centre * sw
+                                                          : swx2 - (swx * swx) / sw;
+                    const double cand = base + seg;
+                    if (cand < best) { best = cand; best_s = s; }
+                }
+                cur[e] = best;
+                back[(size_t)e * (size_t)(k + 1) + (size_t)c] = (int32_t)best_s;
+                const int64_t split = best_s < 0 ? j.slo : best_s;
+                stack.push_back({j.lo, e - 1, j.slo, best_s < 0 ? j.shi : split});
+                stack.push_back({e + 1, j.hi, split, j.shi});
+            }
+            prev.swap(cur);
+            continue;
+        }
 #pragma omp parallel for schedule(dynamic, 16)
         for (int64_t e = c; e <= n; ++e) {
             double best = inf;
@@ -74,6 +113,22 @@ int gefen_exact_dp(const double* prefix_w, const double* prefix_wx,
         e = s - 1;
     }
     return 0;
+}
+
+// Full scan of every start for every end: O(n^2 k).
+int gefen_exact_dp(const double* prefix_w, const double* prefix_wx,
+                   const double* prefix_wx2, int64_t num_points,
+                   int64_t num_codebooks, int force_endpoints, float* codebook_out) {
+    return exact_dp_impl(prefix_w, prefix_wx, prefix_wx2, num_points, num_codebooks, force_endpoints,
+                         codebook_out, false);
+}
+
+// Same recurrence, same tie rule (smallest start), monotone-optimum search: O(n k log n).
+int gefen_exact_dp_monotone(const double* prefix_w, const double* prefix_wx,
+                            const double* prefix_wx2, int64_t num_points,
+                            int64_t num_codebooks, int force_endpoints, float* codebook_out) {
+    return exact_dp_impl(prefix_w, prefix_wx, prefix_wx2, num_points, num_codebooks, force_endpoints,
+                         codebook_out, true);
 }
 
 }  // extern "C"

@@ -108,9 +108,20 @@ def _exact_dp_numpy(pw, pwx, pwx2, k: int, force_endpoints: bool) -> np.ndarray:
     return out
 
 
+EXACT_DP_METHOD = "monotone"   # "monotone": divide and conquer; "scan": every start for every end
+
+
 def exact_dp(histogram_stats: dict, num_codebooks: int,
-             force_endpoints: bool = True) -> torch.Tensor:
-    """Exact weighted k-means of the active histogram bins; returns a sorted codebook."""
+             force_endpoints: bool = True, method: Optional[str] = None) -> torch.Tensor:
+    """Exact weighted k-means of the active histogram bins; returns a sorted codebook.
+
+    ``method`` (default: the module flag ``EXACT_DP_METHOD``): ``"scan"`` evaluates every segment
+    start for every end, O(n^2 k), like the reference's solver; ``"monotone"`` uses the
+    monotonicity of the optimal start (the segment cost satisfies the quadrangle inequality) for
+    O(n k log n) with the same tie rule."""
+    method = method or EXACT_DP_METHOD
+    if method not in ("scan", "monotone"):
+        raise ValueError("exact_dp method must be 'scan' or 'monotone'")
     centers = histogram_stats["active_centers"].detach().cpu().to(torch.float32)
     counts = histogram_stats["active_counts"].detach().cpu().to(torch.float32)
     if centers.numel() == 0:
@@ -136,7 +147,8 @@ def exact_dp(histogram_stats: dict, num_codebooks: int,
     if lib is not None:
         a, b, c = (t.contiguous().numpy() for t in (pw, pwx, pwx2))
         out = np.empty(num_codebooks, dtype=np.float32)
-        rc = lib.gefen_exact_dp(
+        solver = lib.gefen_exact_dp_monotone if method == "monotone" else lib.gefen_exact_dp
+        rc = solver(
             a.ctypes.data_as(ctypes.c_void_p), b.ctypes.data_as(ctypes.c_void_p),
             c.ctypes.data_as(ctypes.c_void_p), n, int(num_codebooks),
             int(bool(force_endpoints)), out.ctypes.data_as(ctypes.c_void_p),

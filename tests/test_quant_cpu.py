@@ -172,3 +172,31 @@ def test_histogram_counts_total_and_symmetry():
     assert counts.sum().item() == 8
     assert counts[4095].item() == 2          # +1.0 of each block clamps into the last bin
     assert counts[0].item() == 2             # -1.0
+
+
+def test_monotone_exact_dp_equals_the_full_scan():
+    """The O(n k log n) solver returns the very codebook of the O(n^2 k) scan, ties included."""
+    import torch
+
+    from gefen_x_b200.quant import codebook as C
+
+    g = torch.Generator().manual_seed(0)
+    samples = [
+        (torch.randn(1 << 16, generator=g) * 0.3).clamp(-1, 1),
+        torch.rand(1 << 14, generator=g) * 2 - 1,
+        torch.cat([torch.zeros(20000), (torch.randn(3000, generator=g) * 0.05).clamp(-1, 1)]),
+        (torch.randn(1500, generator=g) * 0.5).clamp(-1, 1),                       # sparse histogram
+        torch.cat([(torch.randn(2000, generator=g) * 0.2).clamp(-1, 1)] * 1
+                  + [-(torch.randn(2000, generator=torch.Generator().manual_seed(0)) * 0.2).clamp(-1, 1)]),
+        torch.randint(0, 400, (8000,), generator=g).float() / 200 - 1,              # few distinct values
+    ]
+    h = (torch.randn(3000, generator=g) * 0.2).clamp(-1, 1)
+    samples.append(torch.cat([h, -h]))                                             # symmetric: exact ties
+    for x in samples:
+        counts = torch.histc(x, bins=C.HISTOGRAM_BINS, min=-1, max=1).long()
+        st = C.histogram_stats_from_counts(counts)
+        for k in (256, 16):
+            a = C.exact_dp(st, k, method="scan")
+            b = C.exact_dp(st, k, method="monotone")
+            assert torch.equal(a, b)
+    assert C.EXACT_DP_METHOD == "monotone"
