@@ -48,3 +48,18 @@ def test_arena_guard_lines_catch_a_write_past_a_buffer():
     arena.buf[off_b + 33 * 2 + 14] = 0                    # lands in the guard line behind `b`
     bad = arena.check_guards()
     assert len(bad) == 1 and off_b + 66 <= bad[0] <= off_b + 66 + 16
+
+
+def test_row_only_matrix_view_keeps_rows_inside_blocks():
+    """A long-block 1-D tensor is viewed as a matrix whose row length divides the period."""
+    from gefen_x_b200.ops.update import _pick_tcols, _row_only_cols, two_phase_block
+
+    for period in (8388608, 3670016, 524288, 49152, 6144, 4096, 2048, 1000, 24):
+        c = _row_only_cols(period)
+        assert period % c == 0
+        if period > 4096 and period % 8 == 0:
+            assert 256 <= c <= 4096 and c % 8 == 0
+        else:
+            assert c == period
+    assert _pick_tcols(512) == 256 and _pick_tcols(48) in (32, 64)
+    assert two_phase_block(1 << 20, 4) and not two_phase_block(64, 4) and not two_phase_block(1 << 20, 4096)
