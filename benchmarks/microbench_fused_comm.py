@@ -111,8 +111,20 @@ def main():
         tcgemm.gemm(h1, wqkv)
 
     ms_seq = timed(gather_then_gemm)
-    report("all-gather fused into the QKV GEMM (gemm_ag_bf16)", ms_fused, flops, remote,
+    report("all-gather fused into the QKV GEMM (gemm_ag_bf16, {} fetch CTAs)".format(tr.ag_fetch_ctas),
+           ms_fused, flops, remote,
            "tcgen05 GEMM alone on local weights: {:.3f} ms; gather kernel then GEMM: {:.3f} ms".format(ms_local, ms_seq))
+    for n_fetch in (4, 8, 32):
+        # the arrival counters are monotonic per launch: start a fresh series for another fetch width
+        torch.cuda.synchronize()
+        dist.barrier()
+        tr._ag_count[0].zero_()
+        tr._ag_flags[0].zero_()
+        tr._ag_launches[0] = 0
+        tr.ag_fetch_ctas = n_fetch
+        f2 = tr._qkv_fn(0, flat)
+        report("all-gather fused into the QKV GEMM (gemm_ag_bf16, {} fetch CTAs)".format(n_fetch),
+               timed(lambda: f2(h1)), flops, remote)
 
     # reduce-scatter of the layer's gradients by peer loads
     segs, n_segs, prefix, total, _copies = tr._build_reduce_table(grp, "all")

@@ -123,7 +123,7 @@ class ShardedTrainer:
                  factored_v_2d: bool = True, rs_mode: Optional[str] = None, seed: int = 0,
                  optimizer: str = "gefen", global_codebook: bool = True, gather_ctas: int = 64,
                  wait_iters: int = 8_000_000, opt_kwargs: Optional[dict] = None,
-                 ag_gemm: bool = False, ag_fetch_ctas: int = 16, muon_kwargs: Optional[dict] = None,
+                 ag_gemm: bool = False, ag_fetch_ctas: int = 32, muon_kwargs: Optional[dict] = None,
                  gather_mode: str = "ce", reduce_ctas: int = 148, reduce_mode: str = "ce"):
         self.cfg = cfg
         self.world, self.rank = int(world), int(rank)
