@@ -63,3 +63,24 @@ def test_row_only_matrix_view_keeps_rows_inside_blocks():
             assert c == period
     assert _pick_tcols(512) == 256 and _pick_tcols(48) in (32, 64)
     assert two_phase_block(1 << 20, 4) and not two_phase_block(64, 4) and not two_phase_block(1 << 20, 4096)
+
+
+def test_trainer_steps_on_cpu_through_the_same_api():
+    """The trainer's step (manual layer backward, clip norm, Gefen update) on CPU tensors: the loss of
+    a repeated batch falls, the state stays near one byte per parameter, the device-only trace refuses."""
+    import pytest
+    import torch
+
+    from gefen_x_b200.models.decoder import get_config
+    from gefen_x_b200.parallel.fsdp import ShardedTrainer
+
+    cfg = get_config("tiny-llama")
+    tr = ShardedTrainer(cfg, device=torch.device("cpu"), dtype=torch.float32, lr=6e-4, weight_decay=0.01,
+                        clip_grad_norm=1.0, seed=3)
+    tok = torch.randint(0, cfg.vocab_size, (4, 129), generator=torch.Generator().manual_seed(0))
+    losses = [float(tr.step(tok[:, :-1], tok[:, 1:])) for _ in range(5)]
+    assert losses[-1] < losses[0] - 1.0, losses
+    assert tr.state_bytes_per_param() < 1.1
+    tr.check_status()
+    with pytest.raises(RuntimeError, match="CUDA"):
+        tr.traced_step(tok[:, :-1], tok[:, 1:])
