@@ -94,10 +94,9 @@ class GefenMuon(Gefen):
         if ns_steps < 1:
             raise ValueError("ns_steps must be >= 1")
         NS.resolve_schedule(ns_schedule, ns_coefficients, ns_steps)      # validates
-        if fp8_ns:
-            warnings.warn("fp8_ns=True is accepted for configuration compatibility; the "
-                          "Newton-Schulz products run in bf16 on the tcgen05 GEMM.", RuntimeWarning,
-                          stacklevel=2)
+        if fp8_ns and torch.cuda.is_available() and not NS.fp8_supported():
+            warnings.warn("fp8_ns=True but this GPU has no fp8 GEMM (compute capability below 8.9); "
+                          "the Newton-Schulz products run in bf16.", RuntimeWarning, stacklevel=2)
         self._muon_defaults = dict(momentum=momentum, nesterov=nesterov,
                                    ns_coefficients=tuple(ns_coefficients), ns_steps=ns_steps,
                                    ns_schedule=ns_schedule, adjust_lr_fn=adjust_lr_fn,
@@ -235,7 +234,8 @@ class GefenMuon(Gefen):
 
     def _orthogonalize(self, group, m: torch.Tensor) -> torch.Tensor:
         sched = NS.resolve_schedule(group["ns_schedule"], group["ns_coefficients"], group["ns_steps"])
-        return NS.zeropower_via_newtonschulz(m, sched, len(sched), group["muon_eps"])
+        return NS.zeropower_via_newtonschulz(m, sched, len(sched), group["muon_eps"],
+                                             use_fp8=group.get("fp8_ns", self.fp8_ns))
 
     def _compute_muon_update(self, group, name, p, grad) -> torch.Tensor:
         m = self._prepare_muon_momentum(group, name, p, grad)
@@ -396,7 +396,8 @@ class GefenMuon(Gefen):
             sched = NS.resolve_schedule(g["ns_schedule"], g["ns_coefficients"], g["ns_steps"])
             per = max(1, self.batched_ns_workspace_bytes // max(1, 16 * moms[0].numel()))
             for s in range(0, len(moms), per):
-                outs = NS.zeropower_batched(moms[s:s + per], sched, len(sched), g["muon_eps"])
+                outs = NS.zeropower_batched(moms[s:s + per], sched, len(sched), g["muon_eps"],
+                                            use_fp8=g.get("fp8_ns", self.fp8_ns))
                 for (g_, n, p, grad), upd in zip(members[s:s + per], outs):
                     self._apply_muon_update(g_, p, upd.contiguous(), False, False)
 

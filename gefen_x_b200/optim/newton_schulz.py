@@ -97,12 +97,68 @@ def _iterate(x: torch.Tensor, schedule: Sequence[Coeffs]) -> torch.Tensor:
     return x
 
 
+FP8_DTYPE = torch.float8_e4m3fn
+FP8_MAX = 448.0                      # largest finite e4m3 magnitude
+FP8_MIN_SCALE = 1e-12
+FP8_MIN_DIM = 1536                   # below this the fp8 products lose to bf16 (reference gefen_muon.py:83-89)
+
+
+def fp8_supported(device=None) -> bool:
+    """fp8 tensor-core GEMMs need compute capability 8.9 or later; the CPU statement always runs."""
+    if device is not None and torch.device(device).type != "cuda":
+        return True
+    if not torch.cuda.is_available():
+        return False
+    return torch.cuda.get_device_capability(device) >= (8, 9)
+
+
+def fp8_applies(shape, use_fp8: bool) -> bool:
+    """Size gate of the fp8 path: both dimensions large enough and multiples of 16 (the
+    library's fp8 GEMM wants 16-byte rows)."""
+    return bool(use_fp8) and min(shape) >= FP8_MIN_DIM and all(int(d) % 16 == 0 for d in shape)
+
+
+def quantize_rowwise_fp8(x: torch.Tensor):
+    """``x[r, :] ~= q[r, :] * scale[r]`` with ``q`` in e4m3 and each row's absmax mapped to 448."""
+    scale = (x.abs().amax(dim=-1, keepdim=True).float() / FP8_MAX).clamp_(min=FP8_MIN_SCALE)
+    q = (x.float() / scale).clamp_(-FP8_MAX, FP8_MAX).to(FP8_DTYPE)
+    return q, scale
+
+
+def _mm_fp8(aq, sa, bq_rows, sb_rows) -> torch.Tensor:
+    """``(aq * sa) @ (bq_rows * sb_rows)^T`` in bf16.  ``bq_rows`` holds the second operand's
+    COLUMNS as rows (so its transpose view is the column-major operand the fp8 GEMM reads and
+    ``sb_rows`` its per-column scales).  CUDA: ``torch._scaled_mm`` with row-wise scales; CPU:
+    the same quantised values multiplied in fp32."""
+    if aq.is_cuda:
+        return torch._scaled_mm(aq, bq_rows.t(), scale_a=sa, scale_b=sb_rows.t(), out_dtype=torch.bfloat16)
+    return ((aq.float() * sa) @ (bq_rows.float() * sb_rows).t()).bfloat16()
+
+
+def _iterate_fp8(x: torch.Tensor, schedule: Sequence[Coeffs]) -> torch.Tensor:
+    """The quintic iterations with the three products in e4m3 and bf16 results (reference
+    ``src/gefen/gefen_muon.py:134-171``).  ``X X^T`` and ``G G`` quantise their operand once (the
+    second operand is the same matrix, by symmetry for ``G``); ``U X`` needs ``X`` quantised along
+    its columns as well."""
+    for a, b, c in schedule:
+        xq, sx = quantize_rowwise_fp8(x)
+        g = _mm_fp8(xq, sx, xq, sx)
+        gq, sg = quantize_rowwise_fp8(g)
+        gg = _mm_fp8(gq, sg, gq, sg)
+        u = b * g + c * gg
+        uq, su = quantize_rowwise_fp8(u)
+        xtq, sxt = quantize_rowwise_fp8(x.t().contiguous())
+        x = _mm_fp8(uq, su, xtq, sxt).add_(x, alpha=a)
+    return x
+
+
 def zeropower_via_newtonschulz(grad: torch.Tensor, ns_coefficients=None,
                                ns_steps: int = DEFAULT_NS_STEPS, eps: float = EPS,
                                use_fp8: bool = False, compile_fp8: bool = True) -> torch.Tensor:
-    """Approximate ``U V^T`` of ``grad = U S V^T`` (2-D).  ``use_fp8`` is accepted and
-    ignored: the products stay bf16 (the reference documents fp8 as an optional
-    accelerator with a bf16 fallback, ``README.md:597``)."""
+    """Approximate ``U V^T`` of ``grad = U S V^T`` (2-D).  ``use_fp8`` runs the products in e4m3
+    for matrices that pass ``fp8_applies`` on a device that has fp8 GEMMs, bf16 otherwise (the
+    reference's gates, ``src/gefen/gefen_muon.py:258-275``).  ``compile_fp8`` is accepted and
+    unused: nothing here goes through a tracing compiler."""
     if grad.dim() != 2:
         raise ValueError("Input tensor gradient must be a 2D matrix")
     schedule = normalize_schedule(ns_coefficients, ns_steps)
@@ -111,18 +167,26 @@ def zeropower_via_newtonschulz(grad: torch.Tensor, ns_coefficients=None,
     if transposed:
         x = x.t()
     x = x / x.norm().clamp(min=eps)
-    x = _iterate(x.contiguous(), schedule)
+    if x.dtype == torch.bfloat16 and fp8_applies(x.shape, use_fp8) and fp8_supported(x.device):
+        x = _iterate_fp8(x.contiguous(), schedule)
+    else:
+        x = _iterate(x.contiguous(), schedule)
     return x.t() if transposed else x
 
 
 def zeropower_batched(mats: Sequence[torch.Tensor], ns_coefficients=None,
-                      ns_steps: int = DEFAULT_NS_STEPS, eps: float = EPS) -> List[torch.Tensor]:
-    """Newton–Schulz on many same-shape matrices at once (one batched GEMM per product)."""
+                      ns_steps: int = DEFAULT_NS_STEPS, eps: float = EPS,
+                      use_fp8: bool = False) -> List[torch.Tensor]:
+    """Newton–Schulz on many same-shape matrices at once (one batched GEMM per product).  With
+    ``use_fp8`` and a shape that passes the gates, each matrix goes through the fp8 path on its
+    own (the library's fp8 GEMM is not batched)."""
     if not mats:
         return []
     shape = mats[0].shape
     if any(m.shape != shape for m in mats):
         raise ValueError("zeropower_batched needs matrices of one shape")
+    if fp8_applies(shape, use_fp8) and fp8_supported(mats[0].device):
+        return [zeropower_via_newtonschulz(m, ns_coefficients, ns_steps, eps, use_fp8=True) for m in mats]
     schedule = normalize_schedule(ns_coefficients, ns_steps)
     x = torch.stack([m.bfloat16() for m in mats])
     transposed = shape[0] > shape[1]

@@ -65,6 +65,39 @@ def test_newton_schulz_orthogonalises():
         assert torch.allclose(o.float(), single.float(), atol=3e-2)
 
 
+def test_fp8_newton_schulz_gates_and_numerics(monkeypatch):
+    """e4m3 products (CPU statement of the quantised values): close to the bf16 iterations,
+    gated by size and 16-element alignment (reference tests/test_gefen_muon.py fp8 cases)."""
+    assert NS.fp8_applies((2048, 4096), True) and not NS.fp8_applies((2048, 4096), False)
+    assert not NS.fp8_applies((1024, 4096), True)              # below the size gate
+    assert not NS.fp8_applies((1544, 4104), True)              # not multiples of 16
+    q, sc = NS.quantize_rowwise_fp8(torch.tensor([[1.0, -2.0, 0.5], [0.0, 0.0, 0.0]]))
+    assert q.dtype == torch.float8_e4m3fn and float(q[0, 1].float()) == -448.0
+    assert torch.allclose(q.float() * sc, torch.tensor([[1.0, -2.0, 0.5], [0.0, 0.0, 0.0]]), rtol=0.07)
+    monkeypatch.setattr(NS, "FP8_MIN_DIM", 64)
+    g = torch.Generator().manual_seed(3)
+    for shape in ((64, 128), (160, 96)):
+        m = torch.randn(shape, generator=g)
+        ref = NS.zeropower_via_newtonschulz(m, ns_steps=5).float()
+        got = NS.zeropower_via_newtonschulz(m, ns_steps=5, use_fp8=True).float()
+        assert got.shape == ref.shape
+        cos = torch.nn.functional.cosine_similarity(got.reshape(-1), ref.reshape(-1), dim=0)
+        assert cos > 0.97, (shape, float(cos))       # e4m3 noise: relative error of 0.1-0.2 at this size
+        s = torch.linalg.svdvals(got.double())
+        assert s.max() < 1.4 and s.min() > 0.3
+    outs = NS.zeropower_batched([torch.randn(64, 128, generator=g) for _ in range(2)], ns_steps=5, use_fp8=True)
+    assert len(outs) == 2 and outs[0].shape == (64, 128)
+    # through the optimizer: the flag reaches the iterations and training still descends
+    calls = []
+    real = NS._iterate_fp8
+    monkeypatch.setattr(NS, "_iterate_fp8", lambda x, sch: (calls.append(tuple(x.shape)), real(x, sch))[1])
+    w = (torch.randn(64, 96, generator=g) * 0.1).requires_grad_()
+    opt = GefenMuon([("w", w)], lr=1e-2, fp8_ns=True, fused=False)
+    w.grad = torch.randn(64, 96, generator=g)
+    opt.step()
+    assert calls == [(64, 96)]
+
+
 def test_lr_ratio_owner_and_cautious():
     assert adjust_lr_ratio(None, (128, 32)) == 2.0
     assert adjust_lr_ratio("original", (32, 128)) == 1.0

@@ -219,3 +219,22 @@ def test_deterministic_policy_is_replica_exact():
         vk = "v_row" if "v_row" in oa.state[a] else "vmean"
         assert torch.equal(oa.state[a][vk], ob.state[b][vk]), (n, vk)
     assert oa.state_dict()["gefen_deterministic"] is True
+
+
+def test_fp8_newton_schulz_on_the_fp8_gemm_tracks_bf16():
+    """fp8_ns: e4m3 products through the library's row-scaled fp8 GEMM against the bf16
+    iterations on the tcgen05 GEMM (reference tests/test_muon_combined_levers.py: a relative
+    difference near 0.11 when fp8 engages, bit-equal results when the size gate turns it off)."""
+    from gefen_x_b200.optim import newton_schulz as NS
+
+    g = torch.Generator().manual_seed(7)
+    for shape in ((2048, 3072), (3072, 1536)):
+        m = torch.randn(shape, generator=g).to(_dev())
+        ref = NS.zeropower_via_newtonschulz(m, ns_steps=5).float()
+        got = NS.zeropower_via_newtonschulz(m, ns_steps=5, use_fp8=True).float()
+        rel = float((got - ref).norm() / ref.norm())
+        assert 1e-4 < rel < 0.2, (shape, rel)             # engaged (not bit-equal) and close
+        assert float(torch.linalg.matrix_norm(got, ord=2)) < 1.4
+    small = torch.randn(512, 1024, generator=g).to(_dev())
+    assert torch.equal(NS.zeropower_via_newtonschulz(small, ns_steps=5, use_fp8=True),
+                       NS.zeropower_via_newtonschulz(small, ns_steps=5))
