@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--shapes", default="4096x4096,4096x14336,1024x4096")
+    ap.add_argument("--breakdown", action="store_true", help="also time the pieces of one e4m3 iteration")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     sched = NS.normalize_schedule(None, 5)
@@ -62,6 +63,22 @@ def main():
         timed("bf16, library matmul", library)
         if NS.fp8_applies((m, n), True) and NS.fp8_supported(dev):
             timed("e4m3, library row-scaled GEMM", lambda x: NS._iterate_fp8(x, sched))
+            if args.breakdown:
+                from gefen_x_b200.ops.quant import quantize_cols_e4m3_t as quant_t, quantize_rows_e4m3 as quant
+
+                flops = 1.0
+                x2 = torch.randn(m, n, device=dev).bfloat16()
+                g = torch.randn(m, m, device=dev).bfloat16()
+                xq, sx, _ = quant(xs[0])
+                gq, sg, _ = quant(g)
+                xtq, sxt = quant_t(xs[0])
+                timed("piece: quantise X", lambda x: quant(x))
+                timed("piece: quantise a X + U X, write X", lambda x: quant(x, x2, 3.4, 1.0, want_y=True))
+                timed("piece: quantise X by columns, transposed", lambda x: quant_t(x))
+                timed("piece: quantise b G + c G G", lambda x: quant(g, g, -4.7, 2.0))
+                timed("piece: fp8 GEMM X X^T", lambda x: NS._mm_fp8(xq, sx, xq, sx))
+                timed("piece: fp8 GEMM G G", lambda x: NS._mm_fp8(gq, sg, gq, sg))
+                timed("piece: fp8 GEMM U X", lambda x: NS._mm_fp8(gq, sg, xtq, sxt))
 
 
 if __name__ == "__main__":

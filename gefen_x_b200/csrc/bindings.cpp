@@ -14,6 +14,7 @@
 
 #include "attention.h"
 #include "comm.h"
+#include "fp8_quant.h"
 #include "gemm_sm100.h"
 #include "model_ops.h"
 #include "quant.h"
@@ -155,6 +156,51 @@ void remap_indices(Tensor idx, const Tensor& map) {
     check(gx::launch_remap_indices(idx.data_ptr<uint8_t>(), map.data_ptr<uint8_t>(), idx.numel(), sm_count(),
                                    stream()),
           "remap_indices");
+}
+
+void quantize_rows_e4m3(const Tensor& x, const c10::optional<Tensor>& x2, double alpha, double beta, Tensor q,
+                        Tensor scale, const c10::optional<Tensor>& y_out) {
+    c10::cuda::CUDAGuard guard(x.device());
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.stride(1) == 1,
+                "x must be a 2-D bf16 CUDA tensor with unit column stride");
+    const int64_t rows = x.size(0), cols = x.size(1);
+    const void* x2p = nullptr;
+    int64_t ld2 = 0;
+    if (x2.has_value()) {
+        TORCH_CHECK(x2->is_cuda() && x2->scalar_type() == at::kBFloat16 && x2->sizes() == x.sizes() &&
+                    x2->stride(1) == 1 && x2->device() == x.device());
+        x2p = x2->data_ptr();
+        ld2 = x2->stride(0);
+    }
+    TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kFloat8_e4m3fn && q.is_contiguous() && q.sizes() == x.sizes());
+    TORCH_CHECK(scale.is_cuda() && scale.scalar_type() == at::kFloat && scale.is_contiguous() && scale.numel() == rows);
+    void* yp = nullptr;
+    if (y_out.has_value()) {
+        TORCH_CHECK(y_out->is_cuda() && y_out->scalar_type() == at::kBFloat16 && y_out->is_contiguous() &&
+                    y_out->sizes() == x.sizes());
+        TORCH_CHECK(y_out->data_ptr() != x.data_ptr() && y_out->data_ptr() != x2p, "y_out must not alias an input");
+        yp = y_out->data_ptr();
+    }
+    check(gx::launch_quantize_rows_e4m3(x.data_ptr(), x.stride(0), x2p, ld2, (float)alpha, (float)beta, rows, cols,
+                                        static_cast<uint8_t*>(q.data_ptr()), scale.data_ptr<float>(), yp, sm_count(),
+                                        stream()),
+          "quantize_rows_e4m3");
+}
+
+void quantize_cols_e4m3_t(const Tensor& x, Tensor colmax, Tensor q_t, Tensor scale_t) {
+    c10::cuda::CUDAGuard guard(x.device());
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.stride(1) == 1,
+                "x must be a 2-D bf16 CUDA tensor with unit column stride");
+    const int64_t rows = x.size(0), cols = x.size(1);
+    TORCH_CHECK(colmax.is_cuda() && colmax.scalar_type() == at::kInt && colmax.is_contiguous() && colmax.numel() == cols);
+    TORCH_CHECK(q_t.is_cuda() && q_t.scalar_type() == at::kFloat8_e4m3fn && q_t.is_contiguous() && q_t.dim() == 2 &&
+                q_t.size(0) == cols && q_t.size(1) == rows);
+    TORCH_CHECK(scale_t.is_cuda() && scale_t.scalar_type() == at::kFloat && scale_t.is_contiguous() &&
+                scale_t.numel() == cols);
+    check(gx::launch_quantize_cols_e4m3_t(x.data_ptr(), x.stride(0), rows, cols,
+                                          reinterpret_cast<unsigned int*>(colmax.data_ptr<int>()),
+                                          static_cast<uint8_t*>(q_t.data_ptr()), scale_t.data_ptr<float>(), stream()),
+          "quantize_cols_e4m3_t");
 }
 
 void dequantize(const Tensor& idx, const Tensor& mag, const Tensor& codebook, int64_t period, Tensor out) {
@@ -548,6 +594,9 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("clip_coef(Tensor partials, float max_norm, Tensor(a!) coef) -> ()");
     m.def("histogram(Tensor flat, int period, Tensor(a!) counts) -> ()");
     m.def("remap_indices(Tensor(a!) idx, Tensor map) -> ()");
+    m.def("quantize_rows_e4m3(Tensor x, Tensor? x2, float alpha, float beta, Tensor(a!) q, Tensor(b!) scale, "
+          "Tensor(c!)? y_out) -> ()");
+    m.def("quantize_cols_e4m3_t(Tensor x, Tensor(a!) colmax, Tensor(b!) q_t, Tensor(c!) scale_t) -> ()");
     m.def("dequantize(Tensor idx, Tensor mag, Tensor codebook, int period, Tensor(a!) out) -> ()");
     m.def("period_errors(Tensor flat, Tensor divisors, bool input_is_squared) -> Tensor");
     m.def("gemm_bf16(Tensor a, Tensor b, Tensor(a!) c, Tensor? d, bool a_t, bool b_t, float alpha, "
@@ -587,6 +636,8 @@ TORCH_LIBRARY_IMPL(gefenx, CUDA, m) {
     m.impl("histogram", &histogram);
     m.impl("remap_indices", &remap_indices);
     m.impl("dequantize", &dequantize);
+    m.impl("quantize_cols_e4m3_t", &quantize_cols_e4m3_t);
+    m.impl("quantize_rows_e4m3", &quantize_rows_e4m3);
     m.impl("period_errors", &period_errors);
     m.impl("gemm_bf16", &gemm_bf16);
     m.impl("gemm_ag_bf16", &gemm_ag_bf16);

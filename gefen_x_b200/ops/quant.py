@@ -58,3 +58,30 @@ def dequantize(idx: torch.Tensor, mag: torch.Tensor, codebook: torch.Tensor, per
     ops().dequantize(idx, mag.reshape(-1).contiguous(), codebook.to(idx.device, torch.float32).contiguous(),
                      int(period), out)
     return out
+
+
+def quantize_rows_e4m3(x: torch.Tensor, x2: torch.Tensor = None, alpha: float = 1.0, beta: float = 0.0,
+                       want_y: bool = False):
+    """Row-wise e4m3 quantisation of ``y = alpha * x + beta * x2`` (``y = x`` without ``x2``), one
+    kernel: returns ``(q, scale, y)`` with ``q`` in ``torch.float8_e4m3fn``, ``scale`` fp32
+    ``[rows, 1]`` such that ``q * scale ~= y`` (each row's absmax maps to 448) and ``y`` in bf16
+    when ``want_y`` (else ``None``).  ``x`` / ``x2``: 2-D bf16 CUDA with unit column stride and a
+    column count that is a multiple of 8 (kernel: ``csrc/fp8_quant.cu``)."""
+    q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    scale = torch.empty(x.shape[0], 1, dtype=torch.float32, device=x.device)
+    y = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device) if want_y else None
+    ops().quantize_rows_e4m3(x, x2, float(alpha), float(beta), q, scale, y)
+    return q, scale, y
+
+
+def quantize_cols_e4m3_t(x: torch.Tensor):
+    """``quantize_rows_e4m3(x.t().contiguous())`` without the transposed copy: returns
+    ``(q_t, scale_t)`` with ``q_t`` ``[cols, rows]`` in e4m3 and ``scale_t`` fp32 ``[cols, 1]``
+    (each column's absmax maps to 448).  ``x``: 2-D bf16 CUDA, unit column stride, rows a multiple
+    of 4 and columns a multiple of 8."""
+    rows, cols = x.shape
+    colmax = torch.zeros(cols, dtype=torch.int32, device=x.device)
+    q_t = torch.empty(cols, rows, dtype=torch.float8_e4m3fn, device=x.device)
+    scale_t = torch.empty(cols, 1, dtype=torch.float32, device=x.device)
+    ops().quantize_cols_e4m3_t(x, colmax, q_t, scale_t)
+    return q_t, scale_t

@@ -139,7 +139,10 @@ def _iterate_fp8(x: torch.Tensor, schedule: Sequence[Coeffs]) -> torch.Tensor:
     """The quintic iterations with the three products in e4m3 and bf16 results (reference
     ``src/gefen/gefen_muon.py:134-171``).  ``X X^T`` and ``G G`` quantise their operand once (the
     second operand is the same matrix, by symmetry for ``G``); ``U X`` needs ``X`` quantised along
-    its columns as well."""
+    its columns as well.  On CUDA every quantisation is one kernel that also does the
+    elementwise combine before it (``b G + c G G``; ``a X + U X`` of the previous iteration)."""
+    if x.is_cuda and _use_kernel(x):
+        return _iterate_fp8_kernels(x, schedule)
     for a, b, c in schedule:
         xq, sx = quantize_rowwise_fp8(x)
         g = _mm_fp8(xq, sx, xq, sx)
@@ -150,6 +153,24 @@ def _iterate_fp8(x: torch.Tensor, schedule: Sequence[Coeffs]) -> torch.Tensor:
         xtq, sxt = quantize_rowwise_fp8(x.t().contiguous())
         x = _mm_fp8(uq, su, xtq, sxt).add_(x, alpha=a)
     return x
+
+
+def _iterate_fp8_kernels(x: torch.Tensor, schedule: Sequence[Coeffs]) -> torch.Tensor:
+    from ..ops.quant import quantize_cols_e4m3_t as quant_t, quantize_rows_e4m3 as quant
+
+    ux, a_prev = None, 0.0                       # U X of the previous iteration, not yet added to a X
+    for a, b, c in schedule:
+        if ux is None:
+            xq, sx, _ = quant(x)
+        else:                                    # X <- a X + U X and its quantisation, one pass
+            xq, sx, x = quant(x, ux, a_prev, 1.0, want_y=True)
+        g = _mm_fp8(xq, sx, xq, sx)
+        gq, sg, _ = quant(g)
+        gg = _mm_fp8(gq, sg, gq, sg)
+        uq, su, _ = quant(g, gg, b, c)           # U = b G + c G G
+        xtq, sxt = quant_t(x)
+        ux, a_prev = _mm_fp8(uq, su, xtq, sxt), a
+    return ux.add_(x, alpha=a_prev)
 
 
 def zeropower_via_newtonschulz(grad: torch.Tensor, ns_coefficients=None,

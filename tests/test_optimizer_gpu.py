@@ -238,3 +238,32 @@ def test_fp8_newton_schulz_on_the_fp8_gemm_tracks_bf16():
     small = torch.randn(512, 1024, generator=g).to(_dev())
     assert torch.equal(NS.zeropower_via_newtonschulz(small, ns_steps=5, use_fp8=True),
                        NS.zeropower_via_newtonschulz(small, ns_steps=5))
+
+
+def test_e4m3_row_quantisation_kernel_matches_the_torch_statement():
+    from gefen_x_b200.ops.quant import quantize_cols_e4m3_t, quantize_rows_e4m3
+    from gefen_x_b200.optim.newton_schulz import quantize_rowwise_fp8
+
+    g = torch.Generator().manual_seed(11)
+    for rows, cols in ((64, 128), (300, 14336), (33, 2056)):
+        wide = (torch.randn(rows, cols + 8, generator=g) * torch.rand(rows, 1, generator=g) * 3).bfloat16().to(_dev())
+        x = wide[:, :cols]                                   # row stride != cols
+        x[0].zero_()                                         # an all-zero row: scale clamps, q = 0
+        q, sc, y = quantize_rows_e4m3(x)
+        qr, sr = quantize_rowwise_fp8(x)
+        assert y is None and torch.equal(sc, sr)
+        assert torch.equal(q.view(torch.uint8), qr.view(torch.uint8))
+        x2 = torch.randn(rows, cols, generator=g).bfloat16().to(_dev())
+        q, sc, y = quantize_rows_e4m3(x, x2, 3.4445, -4.775, want_y=True)
+        want = (3.4445 * x.float() + -4.775 * x2.float()).bfloat16()
+        torch.testing.assert_close(y.float(), want.float(), rtol=1e-2, atol=1e-6)   # fma vs two roundings: 1 ulp
+        qr, sr = quantize_rowwise_fp8(y)
+        assert torch.equal(sc, sr) and torch.equal(q.view(torch.uint8), qr.view(torch.uint8))
+    for rows, cols in ((128, 64), (4096, 1536), (208, 2056), (16, 16)):
+        x = (torch.randn(rows, cols + 8, generator=g) * torch.rand(1, cols + 8, generator=g) * 3).bfloat16().to(_dev())
+        x = x[:, :cols]
+        x[:, 3].zero_()
+        qt, st = quantize_cols_e4m3_t(x)
+        qr, sr = quantize_rowwise_fp8(x.t().contiguous())
+        assert torch.equal(st, sr), (rows, cols)
+        assert torch.equal(qt.view(torch.uint8), qr.view(torch.uint8)), (rows, cols)
