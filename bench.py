@@ -46,6 +46,8 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--ag-gemm", action="store_true", help="all-gather fused into the QKV projection")
     ap.add_argument("--optimizer", default="gefen", choices=["gefen", "muon_hybrid"])
+    ap.add_argument("--fp8-ns", action="store_true",
+                    help="muon_hybrid: Newton-Schulz products in e4m3 (off by default: the benchmark dtype is bf16)")
     ap.add_argument("--gather", default="ce", choices=["ce", "kernel"],
                     help="parameter all-gather by copy engines or by a peer-load kernel")
     ap.add_argument("--reduce-ctas", type=int, default=148)
@@ -145,7 +147,8 @@ def run_ours(args):
                              lr=6e-6, clip_grad_norm=1.0, factored_v_2d=True, seed=1234,
                              rs_mode=args.rs_mode, ag_gemm=args.ag_gemm, optimizer=args.optimizer,
                              gather_mode=args.gather, reduce_ctas=args.reduce_ctas, reduce_mode=args.reduce,
-                             muon_kwargs=dict(ns_schedule="standard", ns_steps=5) if args.optimizer == "muon_hybrid" else None)
+                             muon_kwargs=dict(ns_schedule="standard", ns_steps=5, fp8_ns=args.fp8_ns)
+                             if args.optimizer == "muon_hybrid" else None)
     gen = torch.Generator().manual_seed(1000 + rank)
     n_batches = max(args.steps, 4)
     host_tok = [torch.randint(0, cfg.vocab_size, (B, S + 1), generator=gen).pin_memory()
@@ -224,7 +227,8 @@ def run_ours(args):
     out = {
         "metric": METRIC, "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 (Newton-Schulz products e4m3)" if (args.fp8_ns and args.optimizer == "muon_hybrid") else "bf16",
         "data": "synthetic uniform-random tokens, random-init N(0,0.02) weights",
         "impl": "ours",
         "opt_step_ms": opt_step_ms,
