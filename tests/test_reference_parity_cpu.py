@@ -1,0 +1,79 @@
+"""Loss-curve parity with the reference's own optimizer code, on CPU.
+
+The unmodified reference package (installed under ``baseline/_ref``; skipped when that folder is
+absent) and this package train the same small MLP from the same weights on the same batches;
+the two loss curves have to stay within 1% of each other at every step.  Both run their
+torch (non-fused) statements, the path the CUDA kernels of either side are tested against
+(reference ``tests/test_gefen.py`` compares its fused kernels with that statement the same way).
+"""
+import os
+import sys
+
+import pytest
+import torch
+import torch.nn as nn
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref")
+
+pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "gefen")),
+                                reason="the reference package is not installed under baseline/_ref")
+
+
+def _reference():
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    import gefen
+
+    return gefen
+
+
+def _model():
+    torch.manual_seed(0)
+    return nn.Sequential(nn.Linear(32, 64), nn.GELU(), nn.Linear(64, 64), nn.GELU(), nn.Linear(64, 8))
+
+
+def _train(make_opt, steps=150):
+    m = _model()
+    opt = make_opt(m)
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(512, 32, generator=g)
+    y = (x @ torch.randn(32, 8, generator=g)).tanh()
+    out = []
+    for _ in range(steps):
+        i = torch.randint(0, 512, (64,), generator=g)
+        loss = ((m(x[i]) - y[i]) ** 2).mean()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        out.append(loss.item())
+    return torch.tensor(out, dtype=torch.float64)
+
+
+def _assert_curves_agree(a, b, tol=0.01):
+    assert torch.equal(a[:1], b[:1])                      # same start
+    assert a[-20:].mean() < 0.6 * a[0]                    # it did train
+    rel = ((a - b).abs() / a.abs()).max().item()
+    assert rel < tol, rel
+
+
+@pytest.mark.parametrize("kw", [dict(), dict(factored_v_2d=False), dict(weight_decay=0.0, betas=(0.8, 0.95))])
+def test_gefen_loss_curve_matches_the_reference(kw):
+    import gefen_x_b200 as ours
+
+    ref = _reference()
+    base = dict(lr=3e-3, weight_decay=0.01, fused=False)
+    base.update(kw)
+    a = _train(lambda m: ref.Gefen(list(m.named_parameters()), **base))
+    b = _train(lambda m: ours.Gefen(list(m.named_parameters()), **base))
+    _assert_curves_agree(a, b)
+
+
+def test_muon_hybrid_loss_curve_matches_the_reference():
+    import gefen_x_b200 as ours
+
+    ref = _reference()
+    kw = dict(lr=3e-3, weight_decay=0.01, fused=False)
+    a = _train(lambda m: ref.GefenMuonHybrid(m, **kw))
+    b = _train(lambda m: ours.GefenMuonHybrid(m, **kw))
+    _assert_curves_agree(a, b)
