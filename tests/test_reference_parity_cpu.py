@@ -77,3 +77,54 @@ def test_muon_hybrid_loss_curve_matches_the_reference():
     a = _train(lambda m: ref.GefenMuonHybrid(m, **kw))
     b = _train(lambda m: ours.GefenMuonHybrid(m, **kw))
     _assert_curves_agree(a, b)
+
+
+def _train_with_handover(first, second, kw, steps=(20, 20)):
+    """``first``'s optimizer for some steps, its ``state_dict`` loaded into ``second``'s, more steps."""
+    import copy
+
+    m = _model()
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(512, 32, generator=g)
+    y = (x @ torch.randn(32, 8, generator=g)).tanh()
+    out = []
+
+    def run(opt, n):
+        for _ in range(n):
+            i = torch.randint(0, 512, (64,), generator=g)
+            loss = ((m(x[i]) - y[i]) ** 2).mean()
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            out.append(loss.item())
+
+    opt = first.Gefen(list(m.named_parameters()), lr=3e-3, fused=False, **kw)
+    run(opt, steps[0])
+    sd = copy.deepcopy(opt.state_dict())
+    opt2 = second.Gefen(list(m.named_parameters()), lr=3e-3, fused=False, **kw)
+    opt2.load_state_dict(sd)
+    run(opt2, steps[1])
+    return torch.tensor(out, dtype=torch.float64), sd
+
+
+@pytest.mark.parametrize("kw", [dict(), dict(factored_v_2d=False)])
+def test_native_checkpoints_load_across_the_two_packages(kw):
+    """Same top-level keys, same per-parameter state keys, and a checkpoint written by either
+    package resumes in the other as it does in its own (reference schema: src/gefen/gefen.py
+    ``state_dict`` / ``load_state_dict``)."""
+    import gefen_x_b200 as ours
+
+    ref = _reference()
+    rr, sd_r = _train_with_handover(ref, ref, kw)
+    ro, _ = _train_with_handover(ref, ours, kw)
+    oo, sd_o = _train_with_handover(ours, ours, kw)
+    orf, _ = _train_with_handover(ours, ref, kw)
+    assert set(sd_r) == set(sd_o)
+    k = next(iter(sd_r["state"]))
+    assert set(sd_r["state"][k]) == set(sd_o["state"][k])
+    for name in sd_r["state"][k]:
+        a, b = sd_r["state"][k][name], sd_o["state"][k][name]
+        if torch.is_tensor(a):
+            assert a.dtype == b.dtype and a.shape == b.shape, name
+    assert ((rr - ro).abs() / rr).max().item() < 1e-5
+    assert ((oo - orf).abs() / oo).max().item() < 1e-5
