@@ -93,20 +93,33 @@ class GefenMuon(Gefen):
             raise ValueError("Unknown adjust_lr_fn {!r}".format(adjust_lr_fn))
         if ns_steps < 1:
             raise ValueError("ns_steps must be >= 1")
-        NS.resolve_schedule(ns_schedule, ns_coefficients, ns_steps)      # validates
+        # A schedule (a name or an explicit list of (a, b, c)) overrides ns_coefficients / ns_steps
+        # and is stored resolved, so a parameter group carries the reference's keys only
+        # (reference src/gefen/gefen_muon.py:605-626, group keys :716-735).
+        if ns_schedule is not None:
+            sched = (NS.resolve_schedule(ns_schedule, ns_coefficients, ns_steps) if isinstance(ns_schedule, str)
+                     else NS.normalize_schedule(ns_schedule, ns_steps))
+            if not (isinstance(ns_schedule, str) and NS.NS_SCHEDULES[ns_schedule] is None):
+                ns_coefficients, ns_steps = [tuple(c) for c in sched], len(sched)
+        NS.normalize_schedule(ns_coefficients, ns_steps)                  # validates
         if fp8_ns and torch.cuda.is_available() and not NS.fp8_supported():
             warnings.warn("fp8_ns=True but this GPU has no fp8 GEMM (compute capability below 8.9); "
                           "the Newton-Schulz products run in bf16.", RuntimeWarning, stacklevel=2)
-        self._muon_defaults = dict(momentum=momentum, nesterov=nesterov,
-                                   ns_coefficients=tuple(ns_coefficients), ns_steps=ns_steps,
-                                   ns_schedule=ns_schedule, adjust_lr_fn=adjust_lr_fn,
+        coeffs = (tuple(ns_coefficients) if isinstance(ns_coefficients[0], (int, float))
+                  else [tuple(c) for c in ns_coefficients])
+        self._muon_defaults = dict(momentum=momentum, nesterov=nesterov, ns_coefficients=coeffs,
+                                   ns_steps=ns_steps, adjust_lr_fn=adjust_lr_fn, sharded_mode=sharded_mode,
+                                   fp8_ns=fp8_ns, fp8_ns_compile=fp8_ns_compile, batched_ns=batched_ns,
+                                   batched_ns_workspace_bytes=int(batched_ns_workspace_bytes),
                                    normuon=normuon, normuon_beta2=normuon_beta2,
-                                   normuon_eps=normuon_eps, cautious=cautious, muon_eps=eps)
+                                   normuon_eps=normuon_eps, cautious=cautious)
         self.sharded_mode = sharded_mode
         self.fp8_ns, self.fp8_ns_compile = fp8_ns, fp8_ns_compile
         self.batched_ns = batched_ns
         self.batched_ns_workspace_bytes = int(batched_ns_workspace_bytes)
-        super().__init__(params, lr=lr, betas=(momentum, 0.999), eps=1e-8, weight_decay=weight_decay,
+        # the group's `eps` is the Newton-Schulz normalisation epsilon and beta2 is unused (0), as in
+        # the reference's groups
+        super().__init__(params, lr=lr, betas=(momentum, 0.0), eps=eps, weight_decay=weight_decay,
                          fused=fused, factored_v_2d=False, stochastic_round=stochastic_round,
                          deterministic=deterministic, capturable=capturable, verbose=verbose)
 
@@ -233,8 +246,8 @@ class GefenMuon(Gefen):
         return ortho.mul_((frob / denom).to(ortho.dtype))
 
     def _orthogonalize(self, group, m: torch.Tensor) -> torch.Tensor:
-        sched = NS.resolve_schedule(group["ns_schedule"], group["ns_coefficients"], group["ns_steps"])
-        return NS.zeropower_via_newtonschulz(m, sched, len(sched), group["muon_eps"],
+        sched = NS.resolve_schedule(group.get("ns_schedule"), group["ns_coefficients"], group["ns_steps"])
+        return NS.zeropower_via_newtonschulz(m, sched, len(sched), group["eps"],
                                              use_fp8=group.get("fp8_ns", self.fp8_ns))
 
     def _compute_muon_update(self, group, name, p, grad) -> torch.Tensor:
@@ -393,10 +406,10 @@ class GefenMuon(Gefen):
                     self._apply_muon_update(g_, p, self._compute_muon_update(g_, n, p, grad), False, False)
                 continue
             moms = [self._prepare_muon_momentum(g_, n, p, grad) for g_, n, p, grad in members]
-            sched = NS.resolve_schedule(g["ns_schedule"], g["ns_coefficients"], g["ns_steps"])
+            sched = NS.resolve_schedule(g.get("ns_schedule"), g["ns_coefficients"], g["ns_steps"])
             per = max(1, self.batched_ns_workspace_bytes // max(1, 16 * moms[0].numel()))
             for s in range(0, len(moms), per):
-                outs = NS.zeropower_batched(moms[s:s + per], sched, len(sched), g["muon_eps"],
+                outs = NS.zeropower_batched(moms[s:s + per], sched, len(sched), g["eps"],
                                             use_fp8=g.get("fp8_ns", self.fp8_ns))
                 for (g_, n, p, grad), upd in zip(members[s:s + per], outs):
                     self._apply_muon_update(g_, p, upd.contiguous(), False, False)

@@ -160,7 +160,9 @@ def test_hybrid_trains_checkpoints_and_loads_atomically(backup_kind):
     assert losses[-1] < losses[0]
     names = [g.get("param_names") for g in opt.param_groups]
     assert len(opt.param_groups) >= 3                      # muon + decay + no-decay
-    assert opt.param_groups[0]["ns_schedule"] == "tuned3" and opt.param_groups[0]["normuon"] is True
+    # the named schedule is stored resolved (three iterations of tuned coefficients), as the reference does
+    assert opt.param_groups[0]["ns_steps"] == 3 and len(opt.param_groups[0]["ns_coefficients"]) == 3
+    assert "ns_schedule" not in opt.param_groups[0] and opt.param_groups[0]["normuon"] is True
     with pytest.raises(NotImplementedError):
         opt.add_param_group({"params": []})
     # LR schedulers mutate the live group dicts

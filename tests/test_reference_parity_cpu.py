@@ -128,3 +128,53 @@ def test_native_checkpoints_load_across_the_two_packages(kw):
             assert a.dtype == b.dtype and a.shape == b.shape, name
     assert ((rr - ro).abs() / rr).max().item() < 1e-5
     assert ((oo - orf).abs() / oo).max().item() < 1e-5
+
+
+def test_hybrid_checkpoints_and_group_keys_match_the_reference():
+    """GefenMuonHybrid: same sections, same parameter-group keys (a named Newton-Schulz schedule is
+    stored resolved, the group's ``eps`` is the normalisation epsilon), and a checkpoint of either
+    package resumes in the other."""
+    import copy
+
+    import gefen_x_b200 as ours
+
+    ref = _reference()
+
+    def handover(first, second):
+        m = _model()
+        g = torch.Generator().manual_seed(1)
+        x = torch.randn(512, 32, generator=g)
+        y = (x @ torch.randn(32, 8, generator=g)).tanh()
+        out = []
+
+        def run(opt, n):
+            for _ in range(n):
+                i = torch.randint(0, 512, (64,), generator=g)
+                loss = ((m(x[i]) - y[i]) ** 2).mean()
+                opt.zero_grad()
+                loss.backward()
+                opt.step()
+                out.append(loss.item())
+
+        opt = first.GefenMuonHybrid(m, lr=3e-3, fused=False)
+        run(opt, 20)
+        sd = copy.deepcopy(opt.state_dict())
+        opt2 = second.GefenMuonHybrid(m, lr=3e-3, fused=False)
+        opt2.load_state_dict(sd)
+        run(opt2, 20)
+        return torch.tensor(out, dtype=torch.float64), sd
+
+    rr, sd_r = handover(ref, ref)
+    ro, _ = handover(ref, ours)
+    oo, sd_o = handover(ours, ours)
+    orf, _ = handover(ours, ref)
+    assert set(sd_r) == set(sd_o)
+    for part in ("muon", "backup"):
+        assert set(sd_r[part]) == set(sd_o[part]), part
+        gr, go = sd_r[part]["param_groups"][0], sd_o[part]["param_groups"][0]
+        assert set(gr) == set(go), (part, set(gr) ^ set(go))
+        for k in ("ns_steps", "eps", "beta1", "beta2", "momentum", "adjust_lr_fn", "sharded_mode", "fp8_ns"):
+            if k in gr:
+                assert gr[k] == go[k], (part, k, gr[k], go[k])
+    assert ((rr - ro).abs() / rr).max().item() < 1e-3
+    assert ((oo - orf).abs() / oo).max().item() < 1e-3
