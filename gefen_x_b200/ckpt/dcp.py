@@ -184,7 +184,7 @@ class GefenDCPState:
             "deterministic": torch.tensor(int(bool(opt._deterministic)), dtype=torch.uint8),
             "slot_count": torch.tensor(len(self._slots), dtype=torch.int64),
             "group_count": torch.tensor(len(opt.param_groups), dtype=torch.int64),
-            "param_identities": [{"name": n, "group": gi, "shape": tuple(p.shape)}
+            "param_identities": [{"name": n, "group": gi, "shape": [int(d) for d in p.shape]}
                                  for _, gi, n, p in self._slots],
             "param_group_hypers": [{"lr": float(g["lr"]), "beta1": g["beta1"], "beta2": g["beta2"],
                                     "eps": g["eps"], "weight_decay": g["weight_decay"]}

@@ -178,3 +178,101 @@ def test_hybrid_checkpoints_and_group_keys_match_the_reference():
                 assert gr[k] == go[k], (part, k, gr[k], go[k])
     assert ((rr - ro).abs() / rr).max().item() < 1e-3
     assert ((oo - orf).abs() / oo).max().item() < 1e-3
+
+
+_DCP_SHAPES = [("layer.weight", (16, 24)), ("layer.bias", (16,)), ("head.weight", (8, 16))]
+
+
+def _dcp_worker(rank, world, port, path, saver, loader, q):
+    """Train 3 steps with ``saver``'s package on 2 Gloo ranks, save through its DCP wrapper, load
+    into ``loader``'s package, step both once more and report the largest parameter difference."""
+    import torch.distributed as dist
+    import torch.distributed.checkpoint as dcp
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+
+    import gefen_x_b200 as ours
+
+    mods = {"ref": _reference(), "ours": ours}
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        mesh = init_device_mesh("cpu", (world,))
+
+        def full(seed):
+            g = torch.Generator().manual_seed(seed)
+            return {n: torch.randn(s, generator=g) * 0.1 for n, s in _DCP_SHAPES}
+
+        def make(mod):
+            ps = [(n, distribute_tensor(t.clone(), mesh, [Shard(0)]).requires_grad_(True))
+                  for n, t in full(0).items()]
+            return ps, mod.Gefen(ps, lr=1e-2, fused=False, factored_v_2d=False)
+
+        def step(ps, opt, k):
+            for (n, p), t in zip(ps, full(100 + k).values()):
+                p.grad = distribute_tensor(t, mesh, [Shard(0)])
+            opt.step()
+
+        S, L = mods[saver], mods[loader]
+        ps, opt = make(S)
+        for k in range(3):
+            step(ps, opt, k)
+        sd = S.GefenDCPState(opt).state_dict()
+        keys = sorted(sd.keys())
+        dcp.save({"optimizer": sd}, storage_writer=S.GefenFileSystemWriter(path), planner=S.GefenSavePlanner())
+        dist.barrier()
+        ps2, opt2 = make(L)
+        for (_, a), (_, b) in zip(ps, ps2):
+            b.data.copy_(a.data)
+        dcp.load({"optimizer": L.GefenDCPState(opt2)}, checkpoint_id=path)
+        step(ps, opt, 3)
+        step(ps2, opt2, 3)
+        diff = max(float((a.detach().to_local() - b.detach().to_local()).abs().max())
+                   for (_, a), (_, b) in zip(ps, ps2))
+        q.put((rank, dict(keys=keys, diff=diff)))
+    except Exception:  # pragma: no cover - reported to the parent
+        import traceback
+
+        q.put((rank, dict(error=traceback.format_exc())))
+    finally:
+        dist.destroy_process_group()
+
+
+def _dcp_run(saver, loader):
+    import socket
+    import tempfile
+
+    import torch.multiprocessing as mp
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with tempfile.TemporaryDirectory() as d:
+        procs = [ctx.Process(target=_dcp_worker, args=(r, 2, port, os.path.join(d, "ck"), saver, loader, q))
+                 for r in range(2)]
+        for pr in procs:
+            pr.start()
+        res = dict(q.get(timeout=300) for _ in range(2))
+        for pr in procs:
+            pr.join(timeout=60)
+    for r in res:
+        assert "error" not in res[r], res[r].get("error")
+    return res
+
+
+def test_dcp_checkpoints_load_across_the_two_packages():
+    """A DCP checkpoint (``GefenDCPState`` + writer + planner) saved by either package on 2 Gloo
+    ranks loads in the other: same key set, and the step after the load lands where the
+    reference's own save -> load lands (the re-blocking at load is common to both)."""
+    own = _dcp_run("ref", "ref")
+    r2o = _dcp_run("ref", "ours")
+    o2r = _dcp_run("ours", "ref")
+    assert own[0]["keys"] == r2o[0]["keys"] == o2r[0]["keys"]
+    for r in (0, 1):
+        assert abs(r2o[r]["diff"] - own[r]["diff"]) < 1e-6, (r, r2o[r]["diff"], own[r]["diff"])
+        assert abs(o2r[r]["diff"] - own[r]["diff"]) < 1e-6, (r, o2r[r]["diff"], own[r]["diff"])
+        assert own[r]["diff"] < 5e-3
