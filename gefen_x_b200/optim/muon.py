@@ -454,8 +454,8 @@ class GefenMuon(Gefen):
                     entries.append({"saved_id": stable, "name": self._param_name(p),
                                     "shape": tuple(p.shape),
                                     "owner": stable_distributed_owner(stable, max(1, world)),
-                                    "state_keys": sorted(k for k in st if k != "name"),
-                                    "initialized": "step" in st})
+                                    "state_keys": tuple(sorted(str(k) for k in st)),
+                                    "initialized": any(str(k) != "name" for k in st)})
                     stable += 1
                 groups.append({"world_size": max((self._process_group_of(p)[1] for p in g["params"]),
                                                  default=1), "params": entries})
@@ -483,8 +483,8 @@ class GefenMuon(Gefen):
                 for grp in groups:
                     for e in grp["params"]:
                         st = merged.get(e["saved_id"], {})
-                        e["state_keys"] = sorted(k for k in st if k != "name")
-                        e["initialized"] = "step" in st
+                        e["state_keys"] = tuple(sorted(str(k) for k in st))
+                        e["initialized"] = any(str(k) != "name" for k in st)
                 consolidated = True
             sd["gefen_muon_distributed"] = {"version": 2, "ownership": "stable_full_param_index_v1",
                                             "consolidated": consolidated, "groups": groups}

@@ -90,10 +90,13 @@ def _iterate(x: torch.Tensor, schedule: Sequence[Coeffs]) -> torch.Tensor:
             tcgemm.gemm(u, x, b_t=True, alpha=1.0, beta=a, d=x, out=nxt)  # X' = U X + a X
             x, nxt = nxt, x
         return x
+    # same roundings as the kernel path's alpha/beta epilogue (one rounding per product) and as the
+    # reference's addmm / baddbmm chain
+    fused = torch.addmm if x.dim() == 2 else torch.baddbmm
     for a, b, c in schedule:
         g = x @ x.transpose(-1, -2)
-        u = b * g + c * (g @ g)
-        x = a * x + u @ x
+        u = fused(g, g, g, beta=b, alpha=c)
+        x = fused(x, u, x, beta=a)
     return x
 
 

@@ -276,3 +276,111 @@ def test_dcp_checkpoints_load_across_the_two_packages():
         assert abs(r2o[r]["diff"] - own[r]["diff"]) < 1e-6, (r, r2o[r]["diff"], own[r]["diff"])
         assert abs(o2r[r]["diff"] - own[r]["diff"]) < 1e-6, (r, o2r[r]["diff"], own[r]["diff"])
         assert own[r]["diff"] < 5e-3
+
+
+_MUON_SHAPES = [("a.weight", (16, 24)), ("b.weight", (8, 16)), ("c.weight", (24, 8)),
+                ("d.weight", (5, 8)), ("e.weight", (1, 8))]          # uneven and empty row shards
+
+
+def _dmuon_worker(rank, world, port, path, saver, loader, q):
+    """``sharded_mode="distributed"`` on 2 Gloo ranks with ``saver``'s package, consolidated
+    ``state_dict`` to a file, loaded by ``loader``'s package, one more step on both."""
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+
+    import gefen_x_b200 as ours
+
+    mods = {"ref": _reference(), "ours": ours}
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        mesh = init_device_mesh("cpu", (world,))
+
+        def full(seed):
+            g = torch.Generator().manual_seed(seed)
+            return {n: torch.randn(s, generator=g) * 0.1 for n, s in _MUON_SHAPES}
+
+        def make(mod):
+            ps = [(n, distribute_tensor(t.clone(), mesh, [Shard(0)]).requires_grad_(True))
+                  for n, t in full(0).items()]
+            return ps, mod.GefenMuon(ps, lr=2e-2, fused=False, sharded_mode="distributed")
+
+        def step(ps, opt, k):
+            for n, p in ps:
+                p.grad = distribute_tensor(full(100 + k)[n], mesh, [Shard(0)])
+            opt.step()
+
+        S, L = mods[saver], mods[loader]
+        ps, opt = make(S)
+        for k in range(3):
+            step(ps, opt, k)
+        after3 = {n: p.full_tensor().detach().clone() for n, p in ps}
+        sd = opt.state_dict()
+        if rank == 0:
+            torch.save({"sd": sd, "weights": after3}, path)
+        dist.barrier()
+        blob = torch.load(path, weights_only=False)
+        ps2, opt2 = make(L)
+        for n, p in ps2:
+            p.data.copy_(distribute_tensor(blob["weights"][n], mesh, [Shard(0)]))
+        opt2.load_state_dict(blob["sd"])
+        step(ps, opt, 3)
+        step(ps2, opt2, 3)
+        diff = max(float((a.full_tensor().detach() - b.full_tensor().detach()).abs().max())
+                   for (_, a), (_, b) in zip(ps, ps2))
+        man = sd["gefen_muon_distributed"]
+        q.put((rank, dict(diff=diff, after3={n: t.numpy() for n, t in after3.items()},
+                          man_keys=sorted(man), entry_keys=sorted(man["groups"][0]["params"][0]),
+                          owners=[e["owner"] for e in man["groups"][0]["params"]])))
+    except Exception:  # pragma: no cover - reported to the parent
+        import traceback
+
+        q.put((rank, dict(error=traceback.format_exc())))
+    finally:
+        dist.destroy_process_group()
+
+
+def _spawn2(target, *args):
+    import socket
+    import tempfile
+
+    import torch.multiprocessing as mp
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with tempfile.TemporaryDirectory() as d:
+        procs = [ctx.Process(target=target, args=(r, 2, port, os.path.join(d, "ck.pt")) + args + (q,))
+                 for r in range(2)]
+        for pr in procs:
+            pr.start()
+        res = dict(q.get(timeout=300) for _ in range(2))
+        for pr in procs:
+            pr.join(timeout=60)
+    for r in res:
+        assert "error" not in res[r], res[r].get("error")
+    return res
+
+
+def test_distributed_muon_trajectory_and_manifest_match_the_reference():
+    """Owner-computed Muon on 2 ranks: the same parameters as the reference package after three
+    steps (the CPU statements share their roundings), the same manifest fields and owners, and
+    the consolidated checkpoint of either package continues in the other without a difference."""
+    import numpy as np
+
+    rr = _spawn2(_dmuon_worker, "ref", "ref")
+    oo = _spawn2(_dmuon_worker, "ours", "ours")
+    ro = _spawn2(_dmuon_worker, "ref", "ours")
+    orf = _spawn2(_dmuon_worker, "ours", "ref")
+    for n in rr[0]["after3"]:
+        assert np.abs(rr[0]["after3"][n] - oo[0]["after3"][n]).max() < 1e-6, n
+    assert rr[0]["man_keys"] == oo[0]["man_keys"] and rr[0]["entry_keys"] == oo[0]["entry_keys"]
+    assert rr[0]["owners"] == oo[0]["owners"]
+    for res in (rr, oo, ro, orf):
+        for r in (0, 1):
+            assert res[r]["diff"] < 1e-6, res[r]["diff"]
