@@ -48,7 +48,11 @@ FUSE_GEFEN_AUTOMATIC_STEP = True
 FUSE_HISTOGRAM_FOR_EXACT = True
 
 _SYNTH_KEY = "param_names_synthesized"
-_RANK_LOCAL_KEY = "gefen_rank_local"
+_RANK_LOCAL_PAYLOAD_PREFIX = "_gefen_rank_local_payload_"
+_RANK_LOCAL_MEMBER_KEY = "_gefen_rank_local_member"
+_RANK_LOCAL_FORMAT = "rank_local_dtensor_v2"
+_RANK_LOCAL_METADATA_VERSION = 3
+_LOCAL_SNAPSHOT_KEY = "gefen_local_snapshot"
 _META_KEY = "_gefen_checkpoint_metadata"
 _COUNTER_KEYS = ("step", "vmean_step", "factored_step", "normuon_step")
 _SCRATCH_KEYS = ("stepsize", "_h_buf", "_capt_row", "_capt_dev", "_fx_scratch")
@@ -1133,7 +1137,9 @@ class Gefen(torch.optim.Optimizer):
             g[_META_KEY] = meta
         ctx = None if getattr(self, "_local_state_dict_only", False) else self._rank_local_context()
         if ctx is not None:
-            sd = self._attach_rank_local_payloads(sd, *ctx)
+            sd = self._attach_rank_local_payloads(sd, ctx)
+        elif getattr(self, "_local_state_dict_only", False) and self._uses_rank_local_sharded_state():
+            sd[_LOCAL_SNAPSHOT_KEY] = True          # this rank's own state: loadable on this rank only
         return sd
 
     def local_state_dict(self) -> Dict[str, Any]:
@@ -1145,70 +1151,312 @@ class Gefen(torch.optim.Optimizer):
             self._local_state_dict_only = False
 
     # -- rank-local checkpoints of row-sharded (DTensor) parameters ---------------------------
+    #
+    # Schema of the reference (``gefen.py:4183-4556`` save, ``:5205-5454`` load), so that files move
+    # between the two packages: the per-parameter states are replaced by one carrier entry (the
+    # first saved id) holding a ``_gefen_rank_local_payload_<rank>`` uint8 tensor per rank (a
+    # ``torch.save`` of that rank's payload dict) and member markers on the others; every group's
+    # ``_gefen_checkpoint_metadata`` (format_version 3) carries the marker with the world, the mesh
+    # and every rank's parameter signature.  Same topology only.
     def _rank_local_checkpoint_applies(self) -> bool:
         """Whether per-rank state differs between ranks (plain Gefen on shards: yes)."""
         return True
 
-    def _rank_local_context(self):
-        """(process group, world, rank) when parameters are DTensors sharded over more than one
-        rank of a 1-D mesh, else None.  Multi-dimensional meshes are refused (reference
-        ``gefen.py:4127-4131``)."""
+    @staticmethod
+    def _is_dtensor_parameter(p) -> bool:
+        return hasattr(p, "to_local") and hasattr(p, "placements") and hasattr(p, "device_mesh")
+
+    def _uses_rank_local_sharded_state(self) -> bool:
         if not self._rank_local_checkpoint_applies():
-            return None
-        for g in self.param_groups:
-            for p in g["params"]:
-                mesh = getattr(p, "device_mesh", None)
-                if mesh is None:
-                    continue
-                if mesh.ndim != 1:
-                    raise ValueError("Gefen rank-local checkpoints need a 1-D device mesh; use "
-                                     "GefenDCPState for other layouts")
-                if mesh.size(0) > 1:
-                    return mesh.get_group(0), mesh.size(0), mesh.get_local_rank(0)
-        return None
+            return False
+        return any(self._is_dtensor_parameter(p) for g in self.param_groups for p in g["params"])
 
     @staticmethod
-    def _attach_rank_local_payloads(sd, pg, world, rank):
-        """Every rank's whole local checkpoint travels in every rank's state dict, so that the file
-        one rank writes restores all of them on the same topology (format ``rank_local_dtensor_v2``,
-        reference ``gefen.py:4408-4556``).  Collective over ``pg``."""
+    def _placement_signature(placement) -> Dict[str, Any]:
+        out = {"type": type(placement).__name__, "module": type(placement).__module__}
+        for attr in ("dim", "split_factor"):
+            v = getattr(placement, attr, None)
+            if v is not None:
+                out[attr] = int(v)
+        op = getattr(placement, "reduce_op", None)
+        if op is not None:
+            out["reduce_op"] = str(op)
+        return out
+
+    @staticmethod
+    def _mesh_signature(mesh) -> Dict[str, Any]:
+        return {"device_type": str(mesh.device_type), "shape": list(mesh.shape),
+                "dim_names": list(mesh.mesh_dim_names or ()),
+                "ranks": [int(r) for r in mesh.mesh.detach().cpu().reshape(-1).tolist()]}
+
+    def _rank_local_context(self):
+        """World, ranks and mesh of a rank-local checkpoint, or None when the state is not
+        rank-local.  One 1-D mesh spanning the default process group, the same for every DTensor
+        parameter; anything else is refused (reference ``gefen.py:4091-4181``)."""
+        if not self._uses_rank_local_sharded_state():
+            return None
+        import torch.distributed as dist
+
+        if not (dist.is_available() and dist.is_initialized()):
+            raise RuntimeError("Gefen rank-local DTensor checkpointing requires an initialized "
+                               "default distributed process group")
+        dts = [p for g in self.param_groups for p in g["params"] if self._is_dtensor_parameter(p)]
+        mesh = dts[0].device_mesh
+        sig = self._mesh_signature(mesh)
+        if len(sig["shape"]) != 1:
+            raise RuntimeError("Gefen rank-local optimizer checkpoints support only one 1-D DeviceMesh "
+                               "spanning the default process group; use GefenDCPState for other layouts")
+        if any(self._mesh_signature(p.device_mesh) != sig for p in dts[1:]):
+            raise RuntimeError("Gefen rank-local optimizer checkpoints require every DTensor parameter "
+                               "to use the same 1-D DeviceMesh")
+        world = dist.get_world_size()
+        ranks = list(range(world))
+        if sig["shape"] != [world] or sorted(sig["ranks"]) != ranks:
+            raise RuntimeError("Gefen rank-local optimizer checkpoints do not support DeviceMesh "
+                               "subgroups; the one-dimensional mesh must span the default world")
+        pg = mesh.get_group()
+        coord = mesh.get_coordinate()
+        if coord is None:
+            raise RuntimeError("The current rank is not a member of Gefen's checkpoint DeviceMesh")
+        return {"world_size": world, "global_rank": dist.get_rank(),
+                "group_rank": dist.get_group_rank(pg, dist.get_rank()), "world_ranks": ranks,
+                "mesh": sig, "coordinate": [int(c) for c in coord]}
+
+    def _rank_local_signature(self) -> List[Dict[str, Any]]:
+        """What binds a payload to a topology: per parameter its position, name, global and local
+        shape, dtype, placements and mesh (reference ``gefen.py:4219-4274``)."""
+        out = []
+        for gi, g in enumerate(self.param_groups):
+            names = g.get("param_names") or []
+            for pi, p in enumerate(g["params"]):
+                name = str(names[pi] if pi < len(names) else self._param_names.get(p, "")).lower()
+                item = {"identifier": "group_{}_param_{}_{}".format(gi, pi, name), "group": gi, "param": pi,
+                        "name": name}
+                if not self._is_dtensor_parameter(p):
+                    item.update({"sharded": False, "shape": list(p.shape), "local_shape": list(p.shape),
+                                 "dtype": str(p.dtype), "requires_grad": bool(p.requires_grad),
+                                 "sharded_mode": g.get("sharded_mode")})
+                else:
+                    local = _local(p)
+                    coord = p.device_mesh.get_coordinate()
+                    item.update({"sharded": True, "shape": list(p.shape), "local_shape": list(local.shape),
+                                 "dtype": str(p.dtype), "local_dtype": str(local.dtype),
+                                 "requires_grad": bool(p.requires_grad),
+                                 "placements": [self._placement_signature(pl) for pl in p.placements],
+                                 "mesh": self._mesh_signature(p.device_mesh),
+                                 "coordinate": None if coord is None else list(coord),
+                                 "sharded_mode": g.get("sharded_mode")})
+                out.append(item)
+        return out
+
+    @staticmethod
+    def _rank_local_manifest(signature):
+        keys = ("identifier", "group", "param", "name", "sharded", "shape", "dtype", "requires_grad",
+                "sharded_mode")
+        return [{k: item.get(k) for k in keys} for item in signature]
+
+    def _attach_rank_local_payloads(self, sd, ctx):
+        """Replace this rank's states by the rank-indexed payloads of all ranks (collective)."""
         import io
 
         import torch.distributed as dist
 
+        world, rank = ctx["world_size"], ctx["global_rank"]
+        saved_ids = list(sd["state"])
+        signature = self._rank_local_signature()
+        manifest = self._rank_local_manifest(signature)
+        control = {"saved_ids": saved_ids, "manifest": manifest, "signature": signature,
+                   "global_step": int(self._gefen_global_step), "deterministic": bool(self._deterministic)}
+        controls = [None] * world
+        dist.all_gather_object(controls, control)
+        if any(c["saved_ids"] != saved_ids for c in controls):
+            raise RuntimeError("Gefen DTensor checkpoint requires identical optimizer parameter ordering "
+                               "on every rank; got state keys {}".format([c["saved_ids"] for c in controls]))
+        if any(c["manifest"] != manifest for c in controls):
+            raise RuntimeError("Gefen DTensor checkpoint parameter identifiers, names, dtypes, or global "
+                               "shapes differ across ranks")
+        if len({c["global_step"] for c in controls}) != 1:
+            raise RuntimeError("Gefen rank-local checkpoint global_step differs across ranks: {}".format(
+                [c["global_step"] for c in controls]))
+        if len({c["deterministic"] for c in controls}) != 1:
+            raise RuntimeError("Gefen rank-local checkpoint deterministic policy differs across ranks")
+
         def to_cpu(v):
             if torch.is_tensor(v):
-                return v.detach().cpu()
+                return _local(v).detach().cpu().contiguous()
             if isinstance(v, dict):
                 return {k: to_cpu(x) for k, x in v.items()}
             if isinstance(v, (list, tuple)):
                 return type(v)(to_cpu(x) for x in v)
             return v
 
+        payload = {"format": _RANK_LOCAL_FORMAT, "global_rank": rank, "group_rank": ctx["group_rank"],
+                   "world_size": world, "world_ranks": ctx["world_ranks"], "mesh": ctx["mesh"],
+                   "signature": signature, "parameter_manifest": manifest,
+                   "global_step": control["global_step"], "deterministic": control["deterministic"],
+                   "states": [to_cpu(sd["state"][i]) for i in saved_ids],
+                   "codebook": to_cpu(self._gefen_codebook)}
         buf = io.BytesIO()
-        torch.save(to_cpu(sd), buf)
-        payloads = [None] * world
-        dist.all_gather_object(payloads, buf.getvalue(), group=pg)
+        torch.save(payload, buf)
+        blobs = [None] * world
+        dist.all_gather_object(blobs, buf.getvalue())
+        carrier = {"name": 0}
+        for r in ctx["world_ranks"]:
+            carrier[_RANK_LOCAL_PAYLOAD_PREFIX + str(r)] = torch.frombuffer(bytearray(blobs[r]),
+                                                                           dtype=torch.uint8).clone()
         out = dict(sd)
-        out[_RANK_LOCAL_KEY] = {"format": "rank_local_dtensor_v2", "metadata_version": 3,
-                                "world_size": world, "payloads": payloads}
+        out["state"] = {sid: (dict(carrier) if i == 0 else {"name": 0, _RANK_LOCAL_MEMBER_KEY: True})
+                        for i, sid in enumerate(saved_ids)}
+        marker = {"format": _RANK_LOCAL_FORMAT, "world_size": world, "world_ranks": ctx["world_ranks"],
+                  "mesh": ctx["mesh"], "signatures": {str(r): controls[r]["signature"] for r in ctx["world_ranks"]},
+                  "parameter_manifest": manifest, "global_step": control["global_step"],
+                  "deterministic": control["deterministic"]}
+        meta = {"format_version": _RANK_LOCAL_METADATA_VERSION, "global_step": control["global_step"],
+                "codebook": None, "deterministic": control["deterministic"],
+                "device_anchor": torch.zeros(1, dtype=torch.uint8), "rank_local_sharded_state": marker}
+        out["param_groups"] = [dict(g) for g in sd["param_groups"]]
+        for g in out["param_groups"]:
+            g[_META_KEY] = meta
+        # a raw state dict must not carry one rank's codebook as if it applied to every payload
+        out["gefen_codebook"] = None
         return out
 
     def _select_rank_local_payload(self, state_dict):
-        """The local checkpoint of this rank out of a ``rank_local_dtensor_v2`` state dict."""
-        rl = state_dict.get(_RANK_LOCAL_KEY) if isinstance(state_dict, dict) else None
-        if rl is None:
+        """This rank's native state dict out of a ``rank_local_dtensor_v2`` checkpoint, after the
+        topology checks; other checkpoints pass through, except a full / untagged one into
+        rank-local state, which is refused (it would give every rank one rank's blocks)."""
+        if not isinstance(state_dict, dict):
             return state_dict
+        groups = state_dict.get("param_groups", ())
+        metas = [g.get(_META_KEY) for g in groups if isinstance(g, dict)]
+        markers = [m.get("rank_local_sharded_state") for m in metas
+                   if isinstance(m, dict) and m.get("rank_local_sharded_state") is not None]
+        states = state_dict.get("state", {}) or {}
+
+        def wrapped(st):
+            return isinstance(st, dict) and (_RANK_LOCAL_MEMBER_KEY in st or any(
+                isinstance(k, str) and k.startswith(_RANK_LOCAL_PAYLOAD_PREFIX) for k in st))
+
+        if not markers:
+            if any(wrapped(st) for st in states.values()):
+                raise ValueError("Gefen checkpoint carries rank-local DTensor payloads but is missing "
+                                 "their topology metadata")
+            local_snapshot = state_dict.get(_LOCAL_SNAPSHOT_KEY) is True
+            if (not local_snapshot and self._uses_rank_local_sharded_state()
+                    and any(isinstance(st, dict) and "m_codebook" in st for st in states.values())):
+                raise ValueError(
+                    "Cannot safely load an untagged/full Gefen checkpoint into rank-local DTensor "
+                    "optimizer state: it holds one rank's codebook and block state. Re-save from the "
+                    "original run with state_dict() on every rank ({} payloads).".format(_RANK_LOCAL_FORMAT))
+            if local_snapshot:
+                state_dict = {k: v for k, v in state_dict.items() if k != _LOCAL_SNAPSHOT_KEY}
+            return state_dict
+        if len(markers) != len(groups):
+            raise ValueError("Gefen rank-local DTensor checkpoint metadata is present on only some "
+                             "parameter groups")
+        marker = markers[0]
+        if not isinstance(marker, dict) or any(m != marker for m in markers[1:]):
+            raise ValueError("Gefen rank-local checkpoint parameter groups carry inconsistent markers")
+        if marker.get("format") != _RANK_LOCAL_FORMAT:
+            raise ValueError("Unsupported Gefen rank-local checkpoint format: {!r}".format(marker.get("format")))
+        if not self._uses_rank_local_sharded_state():
+            raise ValueError("A rank-local DTensor Gefen checkpoint can only load into the same sharded "
+                             "optimizer topology; use GefenDCPState to reshard")
+        try:
+            ctx = self._rank_local_context()
+        except RuntimeError as exc:
+            raise ValueError(str(exc)) from exc
+        world, rank = ctx["world_size"], ctx["global_rank"]
+        if marker.get("world_size") != world:
+            raise ValueError("Gefen rank-local DTensor checkpoints require the same world size; "
+                             "checkpoint={} current={}".format(marker.get("world_size"), world))
+        if marker.get("world_ranks") != ctx["world_ranks"]:
+            raise ValueError("Gefen rank-local checkpoint default-world rank membership differs")
+        if marker.get("mesh") != ctx["mesh"]:
+            raise ValueError("Gefen rank-local checkpoint DeviceMesh differs")
+        rank_keys = {str(r) for r in ctx["world_ranks"]}
+        signatures = marker.get("signatures")
+        if not isinstance(signatures, dict) or set(signatures) != rank_keys:
+            raise ValueError("Gefen rank-local checkpoint has invalid signatures")
+        signature = self._rank_local_signature()
+        if signatures[str(rank)] != signature:
+            raise ValueError("Gefen rank-local DTensor checkpoint topology differs on rank {}: "
+                             "checkpoint={!r} current={!r}".format(rank, signatures[str(rank)], signature))
+        manifest = self._rank_local_manifest(signature)
+        if marker.get("parameter_manifest") != manifest:
+            raise ValueError("Gefen rank-local checkpoint ordered parameter manifest differs")
+        step, det = marker.get("global_step"), marker.get("deterministic")
+        if type(step) is not int or step < 0:
+            raise ValueError("Gefen rank-local checkpoint has invalid global_step")
+        if type(det) is not bool:
+            raise ValueError("Gefen rank-local checkpoint has invalid deterministic policy")
+        saved_ids = list(chain.from_iterable(g.get("params", ()) for g in groups))
+        if len(set(saved_ids)) != len(saved_ids):
+            raise ValueError("Gefen rank-local checkpoint contains duplicate outer parameter IDs")
+        want_keys = {_RANK_LOCAL_PAYLOAD_PREFIX + str(r) for r in ctx["world_ranks"]}
+        blobs = None
+        for sid in saved_ids:
+            st = states.get(sid)
+            if not isinstance(st, dict):
+                raise ValueError("Gefen rank-local checkpoint is missing parameter state {!r}".format(sid))
+            carrier = {k for k in st if isinstance(k, str) and k.startswith(_RANK_LOCAL_PAYLOAD_PREFIX)}
+            if set(st) - carrier - {_RANK_LOCAL_MEMBER_KEY, "name"} or st.get("name") != 0:
+                raise ValueError("Gefen rank-local checkpoint parameter state has an invalid schema: "
+                                 "{!r}".format(sorted(map(str, st))))
+            if carrier:
+                if _RANK_LOCAL_MEMBER_KEY in st or carrier != want_keys or blobs is not None:
+                    raise ValueError("Gefen rank-local checkpoint carrier has missing, unexpected or "
+                                     "repeated per-rank payload keys")
+                blobs = {str(r): st[_RANK_LOCAL_PAYLOAD_PREFIX + str(r)] for r in ctx["world_ranks"]}
+            elif st.get(_RANK_LOCAL_MEMBER_KEY) is not True:
+                raise ValueError("Gefen rank-local checkpoint has an invalid member marker")
+        if blobs is None or any(not torch.is_tensor(b) for b in blobs.values()):
+            raise ValueError("Gefen rank-local checkpoint has invalid rank payloads")
+        blob = blobs[str(rank)]
+        if blob.dtype != torch.uint8 or blob.dim() != 1:
+            raise ValueError("Gefen rank-local checkpoint payload must be a 1-D uint8 tensor")
         import io
 
-        if rl.get("format") != "rank_local_dtensor_v2":
-            raise ValueError("unknown Gefen rank-local checkpoint format {!r}".format(rl.get("format")))
-        ctx = self._rank_local_context()
-        if ctx is None or ctx[1] != rl["world_size"]:
-            raise ValueError(
-                "this checkpoint holds the rank-local state of {} ranks and restores only on the same "
-                "topology; use GefenDCPState to reshard".format(rl["world_size"]))
-        return torch.load(io.BytesIO(rl["payloads"][ctx[2]]), weights_only=False)
+        try:
+            payload = torch.load(io.BytesIO(blob.detach().cpu().contiguous().numpy().tobytes()),
+                                 map_location="cpu", weights_only=True)
+        except Exception as exc:
+            raise ValueError("Gefen rank-local checkpoint payload is invalid") from exc
+        keys = {"format", "global_rank", "group_rank", "world_size", "world_ranks", "mesh", "signature",
+                "parameter_manifest", "global_step", "deterministic", "states", "codebook"}
+        if not isinstance(payload, dict) or set(payload) != keys:
+            raise ValueError("Gefen rank-local checkpoint payload has an invalid schema")
+        bound = (payload["format"] == _RANK_LOCAL_FORMAT and payload["global_rank"] == rank
+                 and payload["group_rank"] == ctx["group_rank"] and payload["world_size"] == world
+                 and payload["world_ranks"] == ctx["world_ranks"] and payload["mesh"] == ctx["mesh"]
+                 and payload["signature"] == signature and payload["parameter_manifest"] == manifest
+                 and payload["global_step"] == step and payload["deterministic"] == det)
+        if not bound:
+            raise ValueError("Gefen rank-local checkpoint payload rank/topology/parameter binding differs")
+        sel = payload["states"]
+        if not isinstance(sel, list) or len(sel) != len(saved_ids) or any(not isinstance(x, dict) for x in sel):
+            raise ValueError("Gefen rank-local checkpoint payload states do not match the parameters")
+        for st in sel:
+            if "m_codebook" in st:
+                idx, mag = st["m_codebook"], st.get("m_magnitude")
+                if (not torch.is_tensor(idx) or idx.dtype != torch.uint8 or not torch.is_tensor(mag)
+                        or mag.dtype != torch.float32 or "step" not in st or "automatic_period" not in st
+                        or not bool(torch.isfinite(mag).all())):
+                    raise ValueError("Gefen rank-local checkpoint momentum state is incomplete or invalid")
+        out = dict(state_dict)
+        out["state"] = dict(zip(saved_ids, sel))
+        out["gefen_global_step"] = step
+        out["gefen_codebook"] = payload["codebook"]
+        out["gefen_deterministic"] = det
+        out["param_groups"] = []
+        for g in groups:
+            g = dict(g)
+            m = dict(g[_META_KEY])
+            m.update(global_step=step, codebook=payload["codebook"], deterministic=det)
+            m.pop("rank_local_sharded_state", None)
+            g[_META_KEY] = m
+            out["param_groups"].append(g)
+        return out
 
     @staticmethod
     def _same_codebook(a, b) -> bool:

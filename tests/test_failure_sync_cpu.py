@@ -168,7 +168,9 @@ def _rank_local_worker(rank, world, port, path, q):
         for k in range(3):
             step(ps, opt, k)
         sd = opt.state_dict()                                  # collective: carries every rank's payload
-        rl = sd["gefen_rank_local"]
+        rl = sd["param_groups"][0]["_gefen_checkpoint_metadata"]["rank_local_sharded_state"]
+        carrier = sd["state"][sd["param_groups"][0]["params"][0]]
+        n_payloads = sum(1 for k in carrier if str(k).startswith("_gefen_rank_local_payload_"))
         weights = {n: p.full_tensor().detach().clone() for n, p in ps}
         if rank == 0:
             torch.save({"sd": sd, "weights": weights}, path)
@@ -189,7 +191,7 @@ def _rank_local_worker(rank, world, port, path, q):
             Gefen([("w", full(0, (16, 24)).requires_grad_(True))], lr=1e-2, fused=False).load_state_dict(blob["sd"])
         except ValueError as e:
             refused = "same" in str(e)
-        q.put((rank, dict(fmt=rl["format"], world=rl["world_size"], n_payloads=len(rl["payloads"]),
+        q.put((rank, dict(fmt=rl["format"], world=rl["world_size"], n_payloads=n_payloads,
                           same_idx=same_idx, same_w=same_w, refused=refused)))
     except Exception:  # pragma: no cover - reported to the parent
         import traceback

@@ -384,3 +384,138 @@ def test_distributed_muon_trajectory_and_manifest_match_the_reference():
     for res in (rr, oo, ro, orf):
         for r in (0, 1):
             assert res[r]["diff"] < 1e-6, res[r]["diff"]
+
+
+_PERIOD_SHAPES = [(7,), (64,), (100,), (3, 5), (48, 96), (96, 48), (128, 128), (30, 77), (256,), (2, 3, 4), (1,),
+                  (512, 64), (17, 17)]
+
+
+@pytest.mark.parametrize("kw", [dict(), dict(factored_v_2d=False), dict(codebook_refresh_every=1)])
+def test_periods_codebook_and_parameters_match_the_reference_over_shapes(kw):
+    """First-step analysis against the reference package: the same block period for every
+    shape, a bit-identical learned codebook (also after a refresh), parameters within an ulp."""
+    import gefen_x_b200 as ours
+
+    def run(mod):
+        g = torch.Generator().manual_seed(0)
+        ps = [("p%d.weight" % i, (torch.randn(s, generator=g) * 0.1).requires_grad_())
+              for i, s in enumerate(_PERIOD_SHAPES)]
+        opt = mod.Gefen(ps, lr=1e-3, fused=False, **kw)
+        for _ in range(2):
+            for _, p in ps:
+                ramp = 1 + torch.arange(p.shape[-1]).float() / p.shape[-1]      # column structure
+                p.grad = torch.randn(p.shape, generator=g) * ramp
+            opt.step()
+        return [opt.state[p]["automatic_period"] for _, p in ps], [p.detach() for _, p in ps], opt
+
+    pa, wa, oa = run(_reference())
+    pb, wb, ob = run(ours)
+    assert pa == pb
+    assert torch.equal(oa.state_dict()["gefen_codebook"], ob.state_dict()["gefen_codebook"])
+    for a, b in zip(wa, wb):
+        torch.testing.assert_close(a, b, rtol=0, atol=1e-7)
+
+
+def test_muon_parameter_split_matches_the_reference():
+    import importlib
+
+    import gefen_x_b200 as ours
+
+    _reference()
+    ref_params = importlib.import_module("gefen.params")
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj = nn.Linear(8, 8, bias=False)
+            self.norm = nn.LayerNorm(8)
+            self.mlp = nn.Linear(8, 16)
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.embed_tokens = nn.Embedding(10, 8)
+            self.layers = nn.ModuleList([Block(), Block()])
+            self.lm_head = nn.Linear(8, 10, bias=False)
+            self.wte = nn.Embedding(4, 8)
+
+    m = Net()
+
+    def names(parts):
+        return [sorted(n for n, _ in part) for part in parts]
+
+    assert names(ref_params.split_params_for_muon(m)) == names(ours.split_params_for_muon(m))
+
+
+def _rank_local_worker(rank, world, port, path, saver, loader, q):
+    """Plain Gefen on row shards (rank-local codebooks and blocks): ``state_dict`` of ``saver``'s
+    package written by rank 0, loaded on both ranks by ``loader``'s package, one more step."""
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+
+    import gefen_x_b200 as ours
+
+    mods = {"ref": _reference(), "ours": ours}
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        mesh = init_device_mesh("cpu", (world,))
+
+        def full(seed, shape):
+            return torch.randn(shape, generator=torch.Generator().manual_seed(seed)) * 0.1
+
+        def make(mod):
+            ps = [("w", distribute_tensor(full(0, (16, 24)), mesh, [Shard(0)]).requires_grad_(True)),
+                  ("b", distribute_tensor(full(1, (16,)), mesh, [Shard(0)]).requires_grad_(True))]
+            return ps, mod.Gefen(ps, lr=1e-2, fused=False, factored_v_2d=False)
+
+        def step(ps, opt, k):
+            for i, (n, p) in enumerate(ps):
+                p.grad = distribute_tensor(full(100 + 10 * k + i, tuple(p.shape)), mesh, [Shard(0)])
+            opt.step()
+
+        S, L = mods[saver], mods[loader]
+        ps, opt = make(S)
+        for k in range(3):
+            step(ps, opt, k)
+        sd = opt.state_dict()
+        weights = {n: p.full_tensor().detach().clone() for n, p in ps}
+        if rank == 0:
+            torch.save({"sd": sd, "weights": weights}, path)
+        dist.barrier()
+        blob = torch.load(path, weights_only=False)
+        ps2, opt2 = make(L)
+        for n, p in ps2:
+            p.data.copy_(distribute_tensor(blob["weights"][n], mesh, [Shard(0)]))
+        opt2.load_state_dict(blob["sd"])
+        step(ps, opt, 3)
+        step(ps2, opt2, 3)
+        diff = max(float((a.full_tensor().detach() - b.full_tensor().detach()).abs().max())
+                   for (_, a), (_, b) in zip(ps, ps2))
+        meta = sd["param_groups"][0]["_gefen_checkpoint_metadata"]
+        first = sd["state"][sd["param_groups"][0]["params"][0]]
+        q.put((rank, dict(diff=diff, top=sorted(sd), meta=sorted(meta), version=meta["format_version"],
+                          marker=sorted(meta["rank_local_sharded_state"]), carrier=sorted(map(str, first)),
+                          signature=meta["rank_local_sharded_state"]["signatures"])))
+    except Exception:  # pragma: no cover - reported to the parent
+        import traceback
+
+        q.put((rank, dict(error=traceback.format_exc())))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_rank_local_dtensor_checkpoints_load_across_the_two_packages():
+    """``rank_local_dtensor_v2``: the same outer schema (carrier and member entries, marker,
+    metadata version, per-rank signatures) and files of either package restore in the other."""
+    rr = _spawn2(_rank_local_worker, "ref", "ref")
+    oo = _spawn2(_rank_local_worker, "ours", "ours")
+    ro = _spawn2(_rank_local_worker, "ref", "ours")
+    orf = _spawn2(_rank_local_worker, "ours", "ref")
+    for key in ("top", "meta", "version", "marker", "carrier", "signature"):
+        assert rr[0][key] == oo[0][key], key
+    for res in (rr, oo, ro, orf):
+        for r in (0, 1):
+            assert res[r]["diff"] < 1e-6, res[r]["diff"]
