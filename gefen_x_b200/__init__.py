@@ -27,10 +27,19 @@ _EXPORTS = {
     "ModelConfig": ".models.decoder",
 }
 
-__all__ = sorted(_EXPORTS) + ["__version__"]
+# submodules reachable as attributes; ``kernels`` is the name the reference gives its kernel
+# wrappers (``src/gefen/__init__.py:52-58``), here the ``ops`` package
+_SUBMODULES = {"kernels": ".ops", "ops": ".ops", "params": ".optim.params"}
+
+__all__ = sorted(_EXPORTS) + ["kernels", "__version__"]
 
 
 def __getattr__(name):
+    sub = _SUBMODULES.get(name)
+    if sub is not None:
+        value = importlib.import_module(sub, __name__)
+        globals()[name] = value
+        return value
     mod = _EXPORTS.get(name)
     if mod is None:
         raise AttributeError("module 'gefen_x_b200' has no attribute {!r}".format(name))

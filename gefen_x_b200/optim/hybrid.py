@@ -73,7 +73,7 @@ class _MergedState:
         return iter(self)
 
 
-class GefenMuonHybrid:
+class GefenMuonHybrid(torch.optim.Optimizer):
     """See the module docstring.  Call forms: ``(muon_named, backup_named, lr=...)``,
     ``(model, lr=...)`` or ``(named_parameters_iterable, lr=...)``."""
 
@@ -162,8 +162,19 @@ class GefenMuonHybrid:
                     kw["capturable"] = True
                 self.backup = torch.optim.AdamW(groups, lr=b_lr, betas=betas, eps=eps, **kw)
         self.state = _MergedState([self.muon, self.backup])
-        self._pre_hooks: List[Any] = []
-        self._post_hooks: List[Any] = []
+        # torch.optim.Optimizer.__init__ is deliberately not called: groups and state are live views
+        # of the children's, so a scheduler's in-place ``group["lr"] = ...`` reaches them.  The hook
+        # registries that torch.optim, LR schedulers and wrappers introspect are set by hand, and
+        # step / state_dict / load_state_dict below dispatch them (reference ``hybrid.py:566-577``).
+        from collections import OrderedDict
+
+        self.defaults = self.children[0].defaults
+        self._optimizer_step_pre_hooks = OrderedDict()
+        self._optimizer_step_post_hooks = OrderedDict()
+        self._optimizer_state_dict_pre_hooks = OrderedDict()
+        self._optimizer_state_dict_post_hooks = OrderedDict()
+        self._optimizer_load_state_dict_pre_hooks = OrderedDict()
+        self._optimizer_load_state_dict_post_hooks = OrderedDict()
 
     @classmethod
     def from_model(cls, model: nn.Module, **kwargs) -> "GefenMuonHybrid":
@@ -185,6 +196,11 @@ class GefenMuonHybrid:
             out.extend(c.param_groups)
         return out
 
+    @param_groups.setter
+    def param_groups(self, value):
+        raise AttributeError("GefenMuonHybrid.param_groups is a view of the children's groups; mutate the "
+                             "group dicts in place or build a new hybrid")
+
     def add_param_group(self, param_group):
         raise NotImplementedError(
             "GefenMuonHybrid routes parameters at construction; build a new hybrid to add parameters")
@@ -192,14 +208,6 @@ class GefenMuonHybrid:
     def zero_grad(self, set_to_none: bool = True) -> None:
         for c in self.children:
             c.zero_grad(set_to_none=set_to_none)
-
-    def register_step_pre_hook(self, hook):
-        self._pre_hooks.append(hook)
-        return hook
-
-    def register_step_post_hook(self, hook):
-        self._post_hooks.append(hook)
-        return hook
 
     def _process_groups(self):
         pgs, seen = [], set()
@@ -218,8 +226,17 @@ class GefenMuonHybrid:
 
     @torch.no_grad()
     def step(self, closure=None):
-        for h in self._pre_hooks:
-            h(self, (), {})
+        # instance step hooks with torch's calling convention: hook(optimizer, args, kwargs), args
+        # being the raw call arguments (self first); a pre-hook may return replacements
+        args, kwargs = ((self, closure) if closure is not None else (self,)), {}
+        for h in list(self._optimizer_step_pre_hooks.values()):
+            res = h(self, args, kwargs)
+            if res is not None:
+                if not (isinstance(res, tuple) and len(res) == 2):
+                    raise RuntimeError("{}.step pre hook must return None or a tuple of (new_args, new_kwargs), "
+                                       "but got {}.".format(type(self).__name__, res))
+                args, kwargs = res
+        closure = args[1] if len(args) > 1 else kwargs.get("closure")
         loss = None
         if closure is not None:
             with torch.enable_grad():
@@ -257,8 +274,8 @@ class GefenMuonHybrid:
                 for c in self.children:
                     if hasattr(c, attr) and hasattr(self, attr):
                         delattr(c, attr)
-        for h in self._post_hooks:
-            h(self, (), {})
+        for h in list(self._optimizer_step_post_hooks.values()):
+            h(self, args, kwargs)
         return loss
 
     @property
@@ -267,15 +284,26 @@ class GefenMuonHybrid:
 
     # ------------------------------------------------------------------
     def state_dict(self) -> Dict[str, Any]:
-        return {
+        for h in list(self._optimizer_state_dict_pre_hooks.values()):
+            h(self)
+        sd = {
             "muon": self.muon.state_dict() if self.muon is not None else None,
             "backup": self.backup.state_dict() if self.backup is not None else None,
             "backup_optimizer": self.backup_optimizer,
         }
+        for h in list(self._optimizer_state_dict_post_hooks.values()):
+            res = h(self, sd)
+            if res is not None:
+                sd = res
+        return sd
 
     def load_state_dict(self, state_dict) -> None:
         """Two-phase load: both halves are restored on shadow copies first; only when both
         succeeded are the results swapped in."""
+        for h in list(self._optimizer_load_state_dict_pre_hooks.values()):
+            res = h(self, state_dict)
+            if res is not None:
+                state_dict = res
         if not isinstance(state_dict, dict) or "muon" not in state_dict or "backup" not in state_dict:
             raise ValueError("not a GefenMuonHybrid checkpoint (expected keys 'muon' and 'backup')")
         saved_kind = state_dict.get("backup_optimizer", "gefen")
@@ -315,6 +343,8 @@ class GefenMuonHybrid:
         for child, shadow in staged:
             if not isinstance(shadow, tuple):
                 child.__dict__.update(shadow.__dict__)
+        for h in list(self._optimizer_load_state_dict_post_hooks.values()):
+            h(self)
 
     def state_bytes(self) -> int:
         total = 0

@@ -519,3 +519,41 @@ def test_rank_local_dtensor_checkpoints_load_across_the_two_packages():
     for res in (rr, oo, ro, orf):
         for r in (0, 1):
             assert res[r]["diff"] < 1e-6, res[r]["diff"]
+
+
+def test_public_surface_and_scheduler_hooks_match_the_reference():
+    """Every public name, constructor argument and default of the reference exists here; the hybrid
+    is a ``torch.optim.Optimizer`` for LR schedulers and dispatches step / state-dict hooks."""
+    import inspect
+
+    import gefen_x_b200 as ours
+
+    ref = _reference()
+    assert [n for n in ref.__all__ if not hasattr(ours, n)] == []
+    for cls in ("Gefen", "GefenMuon", "GefenMuonHybrid", "GefenDCPState"):
+        ra = inspect.signature(getattr(ref, cls).__init__).parameters
+        oa = inspect.signature(getattr(ours, cls).__init__).parameters
+        assert [k for k in ra if k not in oa] == [], cls
+        assert [(k, ra[k].default, oa[k].default) for k in ra
+                if ra[k].default is not inspect.Parameter.empty and ra[k].default != oa[k].default] == [], cls
+        rm = {n for n, _ in inspect.getmembers(getattr(ref, cls), callable) if not n.startswith("_")}
+        om = {n for n, _ in inspect.getmembers(getattr(ours, cls), callable) if not n.startswith("_")}
+        assert sorted(rm - om) == [], cls
+    m = _model()
+    opt = ours.GefenMuonHybrid(m, lr=3e-3, fused=False)
+    assert isinstance(opt, torch.optim.Optimizer)
+    sched = torch.optim.lr_scheduler.LambdaLR(opt, lambda s: 0.5)
+    calls = []
+    handle = opt.register_step_post_hook(lambda o, a, k: calls.append("step"))
+    opt.register_state_dict_pre_hook(lambda o: calls.append("sd"))
+    opt.register_load_state_dict_post_hook(lambda o: calls.append("loaded"))
+    m(torch.randn(4, 32)).sum().backward()
+    opt.step()
+    sched.step()
+    assert [g["lr"] for g in opt.param_groups] == [1.5e-3] * len(opt.param_groups)
+    assert opt.muon.param_groups[0]["lr"] == 1.5e-3           # the scheduler reached the child
+    opt.load_state_dict(opt.state_dict())
+    assert calls == ["step", "sd", "loaded"]
+    handle.remove()
+    opt.step()
+    assert calls == ["step", "sd", "loaded"]
