@@ -639,3 +639,35 @@ def test_hybrid_on_dtensor_shards_matches_the_reference_in_every_sharded_mode(mo
     for res in (ro, orf):
         for r in (0, 1):
             assert res[r]["diff"] < 1e-6, res[r]["diff"]
+
+
+@pytest.mark.parametrize("kw", [dict(deterministic=True), dict(eps=1e-6, betas=(0.95, 0.99)), dict(weight_decay=0.1),
+                                dict(codebook_refresh_every=5), dict(lr=torch.tensor(3e-3))],
+                         ids=["deterministic", "eps-betas", "decay", "refresh", "tensor-lr"])
+def test_gefen_options_follow_the_reference(kw):
+    import gefen_x_b200 as ours
+
+    ref = _reference()
+    base = dict(lr=3e-3, fused=False)
+    base.update(kw)
+    a = _train(lambda m: ref.Gefen(list(m.named_parameters()), **base), steps=40)
+    b = _train(lambda m: ours.Gefen(list(m.named_parameters()), **base), steps=40)
+    assert ((a - b).abs() / a).max().item() < 2e-3
+
+
+@pytest.mark.parametrize("kw", [dict(nesterov=False), dict(normuon=True), dict(cautious=True),
+                                dict(adjust_lr_fn="original"), dict(ns_schedule="tuned4"), dict(batched_ns=True),
+                                dict(momentum=0.9, weight_decay=0.05)],
+                         ids=["plain-momentum", "normuon", "cautious", "original-lr", "tuned4", "batched", "decay"])
+def test_muon_options_follow_the_reference(kw):
+    import gefen_x_b200 as ours
+
+    ref = _reference()
+
+    def make(mod):
+        return lambda m: mod.GefenMuon([(n, p) for n, p in m.named_parameters() if p.ndim == 2], lr=3e-3,
+                                       fused=False, **kw)
+
+    a = _train(make(ref), steps=40)
+    b = _train(make(ours), steps=40)
+    assert ((a - b).abs() / a).max().item() < 2e-3
