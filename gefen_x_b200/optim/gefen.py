@@ -596,6 +596,35 @@ class Gefen(torch.optim.Optimizer):
         if cb is not None:
             self._set_codebook(cb)
 
+    def _maybe_save_gefen_grad_histogram(self) -> None:
+        """Dump the histogram of the block-normalised gradients at the optimizer steps listed in
+        ``quant.codebook.LIST_STEPS_SAVE_HIST_GRAD`` (off unless set; reference
+        ``gefen.py:3095-3155``).  CUDA gradients are binned by the histogram kernel."""
+        steps = getattr(_cbk, "LIST_STEPS_SAVE_HIST_GRAD", None)
+        if steps is None:
+            return
+        if self.capturable and steps:
+            raise ValueError("capturable=True is incompatible with LIST_STEPS_SAVE_HIST_GRAD: histogram "
+                             "collection and file output are host-driven")
+        if self._gefen_global_step not in steps:
+            return
+        prefix = getattr(_cbk, "SAVE_CODEBOOK_PREFIX", None)
+        if prefix is None:
+            raise ValueError("LIST_STEPS_SAVE_HIST_GRAD requires SAVE_CODEBOOK_PREFIX to be set.")
+        if self._gefen_codebook is None:
+            raise ValueError("Expected Gefen codebook to be initialized before saving gradient histogram.")
+        bins = self._gefen_codebook.numel() * 16
+        counts = torch.zeros(bins, dtype=torch.float32)
+        total = 0
+        for _, flat, period, _ in self._iter_gefen_grad_periods(reuse_existing_periods=True):
+            counts.add_(_cbk.block_normalised_histogram(flat, period, bins).cpu().float())
+            total += flat.numel()
+        if total == 0:
+            raise ValueError("Cannot save Gefen gradient histogram because no gradients were available.")
+        _cbk.save_distribution_histogram_pt_from_counts(
+            hist=counts, prefix=prefix, suffix="grad_hist_step_{}".format(self._gefen_global_step),
+            num_samples=total)
+
     def _refresh_codebook_with_requant(self) -> None:
         """Re-learn the codebook and move every stored index onto it (atomic).
 
@@ -1048,6 +1077,7 @@ class Gefen(torch.optim.Optimizer):
             return loss
         try:
             self._maybe_refresh_gefen_codebook()
+            self._maybe_save_gefen_grad_histogram()
             if (self._codebook_refresh_every and self._gefen_global_step > 0
                     and self._gefen_global_step % self._codebook_refresh_every == 0):
                 self._refresh_codebook_with_requant()

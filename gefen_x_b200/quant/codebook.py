@@ -14,20 +14,56 @@ lower index), ``:337-377`` (dequantise), ``:417-517`` (histogram + solve) and
 from __future__ import annotations
 
 import ctypes
+import logging
 import warnings
 from typing import Iterable, Optional, Tuple
 
 import numpy as np
 import torch
 
+logger = logging.getLogger(__name__)
+
 NUM_CODEWORDS = 256
 HISTOGRAM_BINS = NUM_CODEWORDS * 16
 LUT_BUCKETS = 16384
 
 
+# Optional observability switches (reference ``gefen.py:3095-3155``): when
+# ``LIST_STEPS_SAVE_HIST_GRAD`` holds optimizer step numbers, ``Gefen.step`` writes the histogram of
+# the block-normalised gradients at those steps to ``<SAVE_CODEBOOK_PREFIX>_grad_hist_step_<n>.pt``.
+LIST_STEPS_SAVE_HIST_GRAD = None
+SAVE_CODEBOOK_PREFIX = None
+
+
 # --------------------------------------------------------------------------
 # histogram
 # --------------------------------------------------------------------------
+def save_distribution_histogram_pt_from_counts(hist: torch.Tensor, prefix: str, suffix: str, num_samples: int,
+                                               value_range=(-1.0, 1.0)) -> None:
+    """Write histogram counts with their bin geometry to ``<prefix stem>_<suffix>.pt`` beside
+    ``prefix`` (same dictionary as the reference's ``quantization.py:12-56``)."""
+    from pathlib import Path
+
+    if prefix is None:
+        raise ValueError("Cannot save gradient histogram because SAVE_CODEBOOK_PREFIX is None.")
+    if hist.dim() != 1:
+        raise ValueError("Expected 1D histogram counts, got dim={}.".format(hist.dim()))
+    if hist.numel() <= 0:
+        raise ValueError("Expected at least one histogram bin.")
+    if num_samples < 0:
+        raise ValueError("num_samples must be non-negative, got {}.".format(num_samples))
+    base = Path(prefix).expanduser().resolve()
+    base.parent.mkdir(parents=True, exist_ok=True)
+    path = base.parent / "{}_{}.pt".format(base.stem, suffix)
+    counts = hist.detach().cpu().to(torch.float32)
+    left, right = float(value_range[0]), float(value_range[1])
+    edges = torch.linspace(left, right, steps=counts.numel() + 1, dtype=torch.float32)
+    torch.save({"hist": counts, "bin_edges": edges, "bin_centers": 0.5 * (edges[:-1] + edges[1:]),
+                "bin_width": (right - left) / float(counts.numel()), "range": (left, right),
+                "num_bins": counts.numel(), "num_samples": int(num_samples)}, path)
+    logger.info("Saved distribution histogram data to %s", path)
+
+
 def block_normalised_histogram(flat: torch.Tensor, period: int,
                                bins: int = HISTOGRAM_BINS) -> torch.Tensor:
     """int64 counts of ``g / absmax(block)`` over ``bins`` equal bins of [-1, 1].

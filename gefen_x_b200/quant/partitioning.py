@@ -71,7 +71,8 @@ def divisors(n: int) -> List[int]:
     return lo + hi[::-1]
 
 
-def average_within_block_variance_torch(values: torch.Tensor, period: int) -> float:
+def average_within_block_variance_torch(values: torch.Tensor, period: int, parameter_name=None,
+                                        parameter_shape=None) -> float:
     """``sqrt(mean_b var_b)`` for one candidate period (population variance)."""
     v = values.detach().reshape(-1)
     if v.numel() % period:
@@ -83,7 +84,8 @@ def average_within_block_variance_torch(values: torch.Tensor, period: int) -> fl
     return float(torch.sqrt(blocks.var(dim=1, correction=0).mean()).item())
 
 
-def average_within_block_variance_cpu(list_of_values, period_to_check, **_unused) -> float:
+def average_within_block_variance_cpu(list_of_values, period_to_check, parameter_name=None,
+                                      parameter_shape=None) -> float:
     """Float64 CPU scorer, accepts anything ``torch.as_tensor`` accepts."""
     t = torch.as_tensor(list_of_values, dtype=torch.float64, device="cpu")
     return average_within_block_variance_torch(t, int(period_to_check))

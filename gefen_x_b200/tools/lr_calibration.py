@@ -130,11 +130,24 @@ class RelativeCalibration:
     suggested_lrs: Dict[str, float]
     stats: List[GroupUpdateStats]
 
+    def summary(self) -> str:
+        lines = ["relative lr calibration", "  reference: {}".format(self.reference_label)]
+        for s in self.stats:
+            lines.append("  {:<28} lr={:.3e} unit_rms={:.4e} multiplier={:.4f} suggested_lr={:.3e}".format(
+                s.label, s.lr, s.unit_update_rms, self.multipliers[s.label], self.suggested_lrs[s.label]))
+        return "\n".join(lines)
+
 
 def _pick_reference(stats: List[GroupUpdateStats], reference: str) -> GroupUpdateStats:
     if reference == "median":
         ordered = sorted(stats, key=lambda s: s.unit_update_rms)
         return ordered[len(ordered) // 2]
+    if reference in ("gefen", "muon"):              # first usable group of that kind (reference tool's names)
+        want = "muon" if reference == "muon" else "adam"
+        for s in stats:
+            if ":{}".format(want) in s.label and math.isfinite(s.update_rms) and s.update_rms > 0:
+                return s
+        raise ValueError("no usable {} group found for reference".format(reference))
     for s in stats:
         if s.label == reference or str(s.index) == str(reference) or reference in s.label:
             return s
@@ -164,52 +177,106 @@ def _shadow_adamw_unit_update(m, v, grad, t, beta1, beta2, eps):
 
 @dataclass
 class ParamVsAdamw:
+    """One parameter's applied update RMS against a shadow AdamW fed the same gradients (fields of
+    the reference's record, ``tools/lr_calibration.py:486-499``)."""
     name: str
-    shape: tuple
-    optimizer_unit_rms: float
-    adamw_unit_rms: float
-    ratio: float
+    is_muon: bool
+    rows: int
+    cols: int
+    gefen_rms: float
+    adamw_rms: float
+    ratio: float                 # LR multiplier that makes this parameter's update RMS match AdamW's
+    active_ratio: float          # the adjust_lr_fn ratio in effect (Muon), else 1.0
+    sqrt_max: Optional[float]    # sqrt(max(rows, cols)) for Muon, else None
+
+    @property
+    def shape(self) -> tuple:
+        return (self.rows, self.cols)
 
 
-def calibrate_vs_adamw(optimizer, closure, *, num_steps: int = 20, warmup: int = 3, beta1: float = 0.9,
-                       beta2: float = 0.999, eps: float = 1e-8) -> List[ParamVsAdamw]:
-    """Unit update RMS of every parameter against a shadow AdamW fed the same gradients."""
+def _analytic_ratios(group: dict, p=None) -> Dict[str, Optional[float]]:
+    """The ``adjust_lr_fn`` ratios of a Muon group for ``p`` (or the group's largest matrix)."""
+    none = {"original": None, "match_rms_adamw": None, "active": 1.0}
+    if not _is_muon_group(group):
+        return none
+    mats = [q for q in ([p] if p is not None else group["params"]) if q.ndim >= 2]
+    if not mats:
+        return none
+    big = max(mats, key=lambda q: q.shape[0] * q.shape[1])
+    rows, cols = big.shape[:2]
+    original = math.sqrt(max(1, rows / cols))
+    match = 0.2 * math.sqrt(max(rows, cols))
+    return {"original": original, "match_rms_adamw": match,
+            "active": match if group.get("adjust_lr_fn") == "match_rms_adamw" else original}
+
+
+def _median(xs: Sequence[float]) -> float:
+    ys = sorted(x for x in xs if math.isfinite(x))
+    if not ys:
+        return float("nan")
+    n = len(ys)
+    return ys[n // 2] if n % 2 else 0.5 * (ys[n // 2 - 1] + ys[n // 2])
+
+
+def calibrate_vs_adamw(optimizer, closure, *, betas=(0.9, 0.999), eps: float = 1e-8, num_steps: int = 40,
+                       warmup: int = 5) -> List[ParamVsAdamw]:
+    """Per parameter: the optimizer's applied update RMS against the update a shadow AdamW would
+    have applied at the same lr on the same gradients (the shadow is never applied).  Weight decay
+    is off during the probe; parameters and optimizer state are restored afterwards
+    (reference ``tools/lr_calibration.py:502-625``)."""
+    beta1, beta2 = betas
     snap = _snapshot(optimizer)
-    params = [(g, p) for g in optimizer.param_groups for p in g["params"]]
-    shadow = [(torch.zeros_like(_local(p), dtype=torch.float32), torch.zeros_like(_local(p), dtype=torch.float32))
-              for _, p in params]
-    ours = [[] for _ in params]
-    ref = [[] for _ in params]
-    names = []
+    metas = []
     for g in optimizer.param_groups:
-        gn = g.get("param_names") or [None] * len(g["params"])
-        names.extend(gn)
+        names = g.get("param_names") or []
+        lr = g["lr"]
+        lr = float(lr.item() if torch.is_tensor(lr) else lr)
+        base = g.get("name", "?")
+        for i, p in enumerate(g["params"]):
+            name = names[i] if i < len(names) and names[i] else (base if len(g["params"]) == 1
+                                                                 else "{}.{}".format(base, i))
+            metas.append((p, g, lr, str(name)))
+    m, v, ours, ref = {}, {}, {}, {}
     try:
         for g in optimizer.param_groups:
             if "weight_decay" in g:
                 g["weight_decay"] = 0.0
-        for step in range(1, num_steps + 1):
-            optimizer.zero_grad()
-            closure()
-            before = [_local(p).detach().float().clone() for _, p in params]
-            grads = [None if p.grad is None else _local(p.grad).detach().float().clone() for _, p in params]
-            optimizer.step()
-            for i, ((g, p), b, gr) in enumerate(zip(params, before, grads)):
-                if gr is None:
+        for step in range(num_steps):
+            optimizer.zero_grad(set_to_none=True)
+            loss = closure()
+            if loss is None or not bool(torch.isfinite(torch.as_tensor(loss)).all()):
+                raise RuntimeError("non-finite loss at step {}: {}".format(step, loss))
+            before = {}
+            for p, g, lr, _ in metas:
+                if p.grad is None:
                     continue
-                unit = _shadow_adamw_unit_update(shadow[i][0], shadow[i][1], gr, step, beta1, beta2, eps)
-                if step > warmup:
-                    lr = float(g["lr"])
-                    ours[i].append(_rms(_local(p).detach().float() - b) / lr if lr > 0 else float("nan"))
-                    ref[i].append(_rms(unit))
-        out = []
-        for i, (g, p) in enumerate(params):
-            if not ours[i]:
+                grad = _local(p.grad).detach().float()
+                k = id(p)
+                if k not in m:
+                    m[k], v[k] = torch.zeros_like(grad), torch.zeros_like(grad)
+                unit = _shadow_adamw_unit_update(m[k], v[k], grad, step + 1, beta1, beta2, eps)
+                before[k] = _local(p).detach().clone()
+                if step >= warmup:
+                    ref.setdefault(k, []).append(_rms(unit * lr))
+            optimizer.step()
+            if step < warmup:
                 continue
-            a = sum(ours[i]) / len(ours[i])
-            b = sum(ref[i]) / len(ref[i])
-            out.append(ParamVsAdamw(str(names[i]) if i < len(names) and names[i] else "param_{}".format(i),
-                                    tuple(p.shape), a, b, a / b if b > 0 else float("nan")))
+            for p, g, lr, _ in metas:
+                k = id(p)
+                if k in before:
+                    ours.setdefault(k, []).append(_rms((_local(p).detach() - before[k]).float()))
+        out = []
+        for p, g, lr, name in metas:
+            k = id(p)
+            if k not in ours or k not in ref:
+                continue
+            a, b = _median(ours[k]), _median(ref[k])
+            ar = _analytic_ratios(g, p)
+            out.append(ParamVsAdamw(name=name, is_muon=_is_muon_group(g),
+                                    rows=p.shape[0] if p.ndim >= 1 else 1, cols=p.shape[1] if p.ndim >= 2 else 1,
+                                    gefen_rms=a, adamw_rms=b, ratio=(b / a) if a > 0 else float("nan"),
+                                    active_ratio=ar["active"],
+                                    sqrt_max=(ar["match_rms_adamw"] / 0.2) if ar["match_rms_adamw"] else None))
         return out
     finally:
         _restore(optimizer, snap)
@@ -223,6 +290,11 @@ class LRRangeResult:
     suggested_lr: float
     min_loss_lr: float
     diverged_at: Optional[float]
+
+    def summary(self) -> str:
+        return "lr range test: suggested lr {:.3e}, lowest loss at {:.3e}, {}".format(
+            self.suggested_lr, self.min_loss_lr,
+            "no divergence" if self.diverged_at is None else "diverged at {:.3e}".format(self.diverged_at))
 
 
 def _suggest_from_curve(lrs: Sequence[float], smoothed: Sequence[float]) -> float:

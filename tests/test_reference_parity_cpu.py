@@ -671,3 +671,30 @@ def test_muon_options_follow_the_reference(kw):
     a = _train(make(ref), steps=40)
     b = _train(make(ours), steps=40)
     assert ((a - b).abs() / a).max().item() < 2e-3
+
+
+def test_gradient_histogram_dump_matches_the_reference(tmp_path):
+    """``LIST_STEPS_SAVE_HIST_GRAD`` / ``SAVE_CODEBOOK_PREFIX``: the same file name, dictionary keys
+    and counts as the reference package writes."""
+    import importlib
+
+    import gefen_x_b200 as ours
+
+    ref = _reference()
+    out = {}
+    for tag, mod, qname in (("ref", ref, "gefen.quantization"), ("ours", ours, "gefen_x_b200.quant.codebook")):
+        qm = importlib.import_module(qname)
+        qm.LIST_STEPS_SAVE_HIST_GRAD = [2]
+        qm.SAVE_CODEBOOK_PREFIX = str(tmp_path / tag / "cb")
+        try:
+            _train(lambda m: mod.Gefen(list(m.named_parameters()), lr=3e-3, fused=False), steps=4)
+        finally:
+            qm.LIST_STEPS_SAVE_HIST_GRAD = None
+            qm.SAVE_CODEBOOK_PREFIX = None
+        files = sorted(os.listdir(tmp_path / tag))
+        assert files == ["cb_grad_hist_step_2.pt"]
+        out[tag] = torch.load(tmp_path / tag / files[0])
+    a, b = out["ref"], out["ours"]
+    assert sorted(a) == sorted(b)
+    assert torch.equal(a["hist"], b["hist"]) and a["num_samples"] == b["num_samples"]
+    assert torch.equal(a["bin_edges"], b["bin_edges"]) and a["bin_width"] == b["bin_width"]

@@ -65,3 +65,27 @@ def test_cli_runs(capsys):
     assert main(["--model", "tiny-llama", "--num-iter", "4", "--num-blocks", "12", "--seq-len", "16",
                  "--bs", "2", "--device", "cpu", "--json"]) == 0
     assert '"lr"' in capsys.readouterr().out
+
+
+def test_calibration_records_and_runner_helpers_follow_the_reference_tool():
+    """Record fields of the AdamW comparison, reference selectors, summaries and the name
+    classifier / split of the model runner (reference tools/lr_calibration.py:486-499,
+    tools/run_model_calibration.py:40-103)."""
+    from gefen_x_b200.tools import run_model_calibration as R
+
+    model, opt, closure = _setup(True)
+    vs = calibrate_vs_adamw(opt, closure, betas=(0.9, 0.99), num_steps=6, warmup=2)
+    r = vs[0]
+    assert {"name", "is_muon", "rows", "cols", "gefen_rms", "adamw_rms", "ratio", "active_ratio",
+            "sqrt_max"} <= set(r.__dict__)
+    assert any(v.is_muon and v.sqrt_max for v in vs) and any(not v.is_muon and v.sqrt_max is None for v in vs)
+    assert all(abs(v.ratio - v.adamw_rms / v.gefen_rms) < 1e-9 for v in vs)
+    rel = calibrate_relative(opt, closure, reference="gefen", num_steps=6, warmup=2)
+    assert ":adam" in rel.reference_label and "multiplier" in rel.summary()
+    assert calibrate_relative(opt, closure, reference="muon", num_steps=6, warmup=2).reference_label.count("muon")
+    assert R.classify_param_type("model.layers.0.self_attn.q_proj.weight") == "q_proj"
+    assert R.param_type("model.embed_tokens.weight") == "embed" and R.param_type("lm_head.weight") == "lm_head"
+    assert R.param_type("model.norm.weight") == "norm" and R.param_type("x.bias") == "bias"
+    muon, backup = R.split_params_for_muon(model)
+    assert all(p.ndim == 2 for _, p in muon) and len(muon) + len(backup) == len(list(model.parameters()))
+    assert len(R.CORPUS) == 8
