@@ -184,15 +184,70 @@ def _sweep_worker(device: str, lr_list: List[float], cfg: dict, q) -> None:
         q.put(("ERROR", device, traceback.format_exc()))
 
 
-def find_lr_parallel_sweep(model_factory: Callable[[], nn.Module], train_blocks: torch.Tensor,
-                           eval_blocks: torch.Tensor, *, optimizer: str = "gefen",
+class _HFCausalLM(nn.Module):
+    """A Hugging Face causal LM behind the ``(tokens, targets) -> loss`` call of the decoder presets."""
+
+    def __init__(self, inner):
+        super().__init__()
+        self.inner = inner
+
+    def forward(self, tokens, targets):
+        full = torch.cat([tokens, targets[:, -1:]], dim=1)
+        return self.inner(input_ids=full, labels=full).loss
+
+
+class _HFModelFactory:
+    """Picklable factory of a local Hugging Face checkpoint (workers are spawned)."""
+
+    def __init__(self, path: str, dtype: str):
+        self.path, self.dtype = path, dtype
+
+    def __call__(self) -> nn.Module:
+        from transformers import AutoModelForCausalLM
+
+        inner = AutoModelForCausalLM.from_pretrained(self.path, dtype=getattr(torch, self.dtype),
+                                                     low_cpu_mem_usage=True, local_files_only=True)
+        inner.config.use_cache = False
+        return _HFCausalLM(inner).train()
+
+
+def _hf_blocks(model_path, dataset, split, seq, max_rows, eval_blocks):
+    from types import SimpleNamespace
+
+    from transformers import AutoTokenizer
+
+    tok = AutoTokenizer.from_pretrained(model_path, local_files_only=True)
+    return build_token_stream(tok, SimpleNamespace(dataset=dataset, split=split, seq=seq + 1, max_rows=max_rows,
+                                                   eval_blocks=eval_blocks))
+
+
+def find_lr_parallel_sweep(model_factory, train_blocks=None, eval_blocks=None, *, optimizer: str = "gefen",
                            sweep_lrs: Optional[List[float]] = None, devices: Optional[List[str]] = None,
                            sweep_steps: int = 80, warmup: int = 10, bs: int = 8, seed: int = 0,
-                           weight_decay: float = 0.0, timeout_s: float = 3600.0) -> FindLRResult:
+                           weight_decay: float = 0.0, timeout_s: float = 3600.0, dtype: str = "bfloat16",
+                           dataset: Optional[str] = None, split: str = "train", seq: int = 512,
+                           max_rows: int = 0, fused: bool = True, adjust_lr_fn: str = "match_rms_adamw",
+                           verbose: bool = True, worker_timeout: Optional[float] = None) -> FindLRResult:
     """The sweep of :func:`find_lr` with one spawned worker per device; a worker that fails
-    reports its traceback through the queue and the whole call raises within ``timeout_s``."""
+    reports its traceback through the queue and the whole call raises within ``timeout_s``.
+
+    Two call forms: ``(model_factory, train_blocks, eval_blocks, ...)`` with token blocks in hand,
+    or the reference tool's ``(model_path, devices, dataset=..., seq=..., eval_blocks=N, ...)``
+    (``tools/find_lr.py:351-372``), which loads a local Hugging Face checkpoint in every worker and
+    tokenises ``dataset`` (a local text / json / jsonl file, or an installed dataset name)."""
     import torch.multiprocessing as mp
 
+    if isinstance(model_factory, str):
+        model_path = model_factory
+        if isinstance(train_blocks, (list, tuple)) and devices is None:
+            devices = list(train_blocks)
+        if dataset is None:
+            raise ValueError("the model-path call form needs dataset=<file or installed dataset name>")
+        n_eval = int(eval_blocks) if isinstance(eval_blocks, int) else 48
+        train_blocks, eval_blocks = _hf_blocks(model_path, dataset, split, seq, max_rows, n_eval)
+        model_factory = _HFModelFactory(model_path, dtype)
+    if worker_timeout is not None:
+        timeout_s = worker_timeout
     lrs = list(sweep_lrs) if sweep_lrs else [1e-5, 3e-5, 1e-4, 3e-4, 1e-3, 3e-3]
     if devices is None:
         n = torch.cuda.device_count()
@@ -279,14 +334,38 @@ def _shard_worker(rank: int, world: int, lr: float, cfg: dict, port: str, q) -> 
         q.put(("ERROR", lr, traceback.format_exc()))
 
 
-def find_lr_sharded_sweep(model: str, train_blocks: torch.Tensor, *, world: Optional[int] = None,
+def find_lr_sharded_sweep(model: str, train_blocks=None, *, world: Optional[int] = None,
                           sweep_lrs: Optional[List[float]] = None, sweep_steps: int = 40, warmup: int = 5,
                           bs: int = 1, seed: int = 0, weight_decay: float = 0.0, clip: Optional[float] = 1.0,
-                          overrides: Optional[dict] = None, timeout_s: float = 3600.0) -> FindLRResult:
-    """lr sweep for a decoder preset sharded over ``world`` GPUs; the final training loss of the
-    short run ranks the candidates."""
+                          overrides: Optional[dict] = None, timeout_s: float = 3600.0,
+                          devices: Optional[List[str]] = None, optimizer: str = "gefen", dtype: str = "bfloat16",
+                          dataset: Optional[str] = None, split: str = "train", seq: int = 512, max_rows: int = 0,
+                          eval_blocks: int = 48, fused: bool = True, adjust_lr_fn: str = "match_rms_adamw",
+                          verbose: bool = True, worker_timeout: Optional[float] = None,
+                          tokenizer: Optional[str] = None) -> FindLRResult:
+    """lr sweep for a decoder preset sharded over ``world`` GPUs by ``ShardedTrainer``; the final
+    training loss of the short run ranks the candidates.
+
+    The reference tool's keywords (``tools/find_lr.py:550-571``) are accepted: ``devices`` (second
+    positional or keyword) gives the world size, ``worker_timeout`` the time limit, and with
+    ``dataset`` plus ``tokenizer`` (a local tokenizer folder) the token blocks are built here.
+    ``model`` names a decoder preset: the sharded runtime owns its own model classes, it does not
+    wrap Hugging Face modules; ``optimizer`` must be ``"gefen"``, ``dtype`` ``"bfloat16"``."""
     import torch.multiprocessing as mp
 
+    if isinstance(train_blocks, (list, tuple)) and devices is None:        # (model, devices, ...)
+        devices, train_blocks = list(train_blocks), None
+    if devices is not None and world is None:
+        world = len(devices)
+    if worker_timeout is not None:
+        timeout_s = worker_timeout
+    if optimizer != "gefen" or dtype != "bfloat16":
+        raise ValueError("the sharded sweep runs the fused Gefen update in bf16; got optimizer={!r}, "
+                         "dtype={!r}".format(optimizer, dtype))
+    if train_blocks is None:
+        if dataset is None or tokenizer is None:
+            raise ValueError("pass train_blocks, or dataset= and tokenizer= to build them")
+        train_blocks, _ = _hf_blocks(tokenizer, dataset, split, seq, max_rows, eval_blocks)
     world = world or max(1, torch.cuda.device_count())
     lrs = list(sweep_lrs) if sweep_lrs else [1e-6, 3e-6, 1e-5, 3e-5, 1e-4]
     cfg = dict(model=model, train_blocks=train_blocks, sweep_steps=sweep_steps, warmup=warmup, bs=bs,
@@ -315,6 +394,65 @@ def find_lr_sharded_sweep(model: str, train_blocks: torch.Tensor, *, world: Opti
 
 
 # ---------------------------------------------------------------- command line
+def _row_text(row) -> str:
+    """Text of one dataset row: a string, a ``text``-like field, or instruction / input / output."""
+    if isinstance(row, str):
+        return row
+    if isinstance(row, dict):
+        if row.get("instruction"):
+            return "\n".join(x for x in (row.get("instruction", ""), row.get("input", ""), row.get("output", ""))
+                             if x)
+        for key in ("text", "content", "output", "completion", "body"):
+            if row.get(key):
+                return row[key]
+    return ""
+
+
+def _load_texts(dataset: str, split: str = "train", max_rows: int = 0) -> List[str]:
+    """Texts of a local ``.txt`` / ``.json`` / ``.jsonl`` file, or of an installed Hugging Face
+    dataset when ``dataset`` is not a path (no download is attempted beyond what ``datasets``
+    finds in its cache)."""
+    import json
+    import os
+
+    if os.path.exists(dataset):
+        if dataset.endswith(".jsonl"):
+            with open(dataset) as fh:
+                texts = [_row_text(json.loads(line)) for line in fh if line.strip()]
+        elif dataset.endswith(".json"):
+            with open(dataset) as fh:
+                loaded = json.load(fh)
+            texts = [_row_text(r) for r in (loaded if isinstance(loaded, list) else [loaded])]
+        else:
+            with open(dataset) as fh:
+                texts = [fh.read()]
+    else:
+        from datasets import load_dataset
+
+        texts = [_row_text(r) for r in load_dataset(dataset, split=split)]
+    texts = [t for t in texts if t]
+    return texts[:max_rows] if max_rows and max_rows > 0 else texts
+
+
+def build_token_stream(tok, args):
+    """Tokenise ``args.dataset`` (fields ``dataset, split, max_rows, seq, eval_blocks``), pack the
+    ids into ``[N, seq]`` blocks separated by EOS and hold out the last blocks for evaluation:
+    ``(train_blocks, eval_blocks)`` (reference ``tools/find_lr.py:710-727``)."""
+    seq = int(args.seq)
+    eos = tok.eos_token_id if getattr(tok, "eos_token_id", None) is not None else 0
+    ids: List[int] = []
+    for text in _load_texts(args.dataset, getattr(args, "split", "train"), getattr(args, "max_rows", 0)):
+        ids.extend(tok(text, add_special_tokens=False)["input_ids"])
+        ids.append(eos)
+    n_blocks = len(ids) // seq
+    if n_blocks < 2:
+        raise ValueError("only {} tokens -> {} blocks at seq={}; need >=2. Use a bigger dataset, a smaller "
+                         "seq, or raise max_rows.".format(len(ids), n_blocks, seq))
+    blocks = torch.tensor(ids[:n_blocks * seq], dtype=torch.long).view(n_blocks, seq)
+    n_eval = max(1, min(int(getattr(args, "eval_blocks", 1)), n_blocks // 5))
+    return blocks[:-n_eval], blocks[-n_eval:]
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
     ap = argparse.ArgumentParser(description="Learning-rate finder for the Gefen optimizers")
     ap.add_argument("--model", default="tiny-llama", help="decoder preset (models.decoder.PRESETS)")

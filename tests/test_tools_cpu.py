@@ -89,3 +89,32 @@ def test_calibration_records_and_runner_helpers_follow_the_reference_tool():
     muon, backup = R.split_params_for_muon(model)
     assert all(p.ndim == 2 for _, p in muon) and len(muon) + len(backup) == len(list(model.parameters()))
     assert len(R.CORPUS) == 8
+
+
+def test_build_token_stream_packs_local_files(tmp_path):
+    import json
+    from types import SimpleNamespace
+
+    from gefen_x_b200.tools.find_lr import build_token_stream
+
+    class Tok:
+        eos_token_id = 1
+
+        def __call__(self, text, add_special_tokens=False):
+            return {"input_ids": [2 + (ord(c) % 50) for c in text]}
+
+    path = tmp_path / "rows.jsonl"
+    rows = [{"text": "abcdefgh" * 5}, {"instruction": "sum", "input": "1 2", "output": "3"}, {"other": 1}]
+    path.write_text("\n".join(json.dumps(r) for r in rows))
+    args = SimpleNamespace(dataset=str(path), split="train", max_rows=0, seq=8, eval_blocks=2)
+    train, ev = build_token_stream(Tok(), args)
+    assert train.shape[1] == 8 and ev.shape[1] == 8 and ev.shape[0] == 1 and train.dtype == torch.long
+    total = 40 + 1 + len("sum\n1 2\n3") + 1
+    assert train.shape[0] + ev.shape[0] == total // 8
+    assert int((torch.cat([train, ev]) == 1).sum()) >= 1                # the EOS separators survive packing
+    args.seq = 64
+    try:
+        build_token_stream(Tok(), args)
+        raise AssertionError("expected a ValueError for too little text")
+    except ValueError:
+        pass
