@@ -118,3 +118,29 @@ def test_build_token_stream_packs_local_files(tmp_path):
         raise AssertionError("expected a ValueError for too little text")
     except ValueError:
         pass
+
+
+def _tiny_lm():
+    cfg = get_config("tiny-llama", n_layers=1, hidden=64, ffn=128, vocab_size=128)
+    return DecoderLM(cfg, seed=0)
+
+
+def test_parallel_sweep_runs_spawned_workers_and_reports_worker_failures():
+    from gefen_x_b200.tools.find_lr import find_lr_parallel_sweep
+
+    g = torch.Generator().manual_seed(0)
+    blocks = torch.randint(0, 128, (24, 17), generator=g)
+    res = find_lr_parallel_sweep(_tiny_lm, blocks[4:], blocks[:4], optimizer="gefen", sweep_lrs=[1e-3, 1e-2],
+                                 devices=["cpu"], sweep_steps=3, warmup=1, bs=4, worker_timeout=300)
+    assert res.lr in (1e-3, 1e-2) and len(res.curve) == 2 and res.details["devices"] == ["cpu"]
+    try:
+        find_lr_parallel_sweep(_tiny_lm, blocks[4:], blocks[:4], optimizer="no-such-optimizer", sweep_lrs=[1e-3],
+                               devices=["cpu"], sweep_steps=2, warmup=1, bs=4, worker_timeout=300)
+        raise AssertionError("a failing worker must raise in the parent")
+    except RuntimeError as e:
+        assert "worker on cpu failed" in str(e)
+    try:
+        find_lr_parallel_sweep("/no/such/checkpoint", ["cpu"])
+        raise AssertionError("the model-path form needs a dataset")
+    except ValueError as e:
+        assert "dataset" in str(e)
