@@ -22,6 +22,7 @@ from __future__ import annotations
 
 import logging
 import math
+import os
 import warnings
 from collections import defaultdict
 from itertools import chain
@@ -46,6 +47,13 @@ FIND_PERIOD_BACKEND: Optional[str] = None
 FUSE_AUTOMATIC_VMEAN_UPDATE = True
 FUSE_GEFEN_AUTOMATIC_STEP = True
 FUSE_HISTOGRAM_FOR_EXACT = True
+# Chunk sizes of the reference's torch statements (``gefen.py:206-285``), kept as names for code that
+# reads them; the statements here chunk at ``quant.codebook._SEARCH_CHUNK``.
+GEFEN_CODEBOOK_SEARCH_CHUNK = 1 << 23
+GEFEN_DEQUANT_GATHER_CHUNK = 1 << 23
+GEFEN_EXACT_HISTOGRAM_CHUNK = 1 << 28
+GEFEN_MOMENTUM_UPDATE_CHUNK = 1 << 23
+GEFEN_NONFUSED_FOREACH_BUDGET = int(os.environ.get("GEFEN_NONFUSED_FOREACH_BUDGET", str(1 << 25)))
 
 _SYNTH_KEY = "param_names_synthesized"
 _RANK_LOCAL_PAYLOAD_PREFIX = "_gefen_rank_local_payload_"
@@ -184,6 +192,78 @@ def _ext_available() -> bool:
     from ..ops._ext import available
 
     return available()
+
+
+
+# ---------------------------------------------------------------------------
+# Module-level functions under the reference's names (``gefen.py:97-517``): the
+# single-tensor statements of the optimizer, usable on any device.
+# ---------------------------------------------------------------------------
+def automatic_partition_view(flat_tensor: torch.Tensor, period: int) -> torch.Tensor:
+    """``[numel / period, period]`` view of a flat tensor."""
+    return F_.partition_view(flat_tensor, period)
+
+
+def automatic_partition_reduce(flat_tensor: torch.Tensor, period: int, reduce_op: str) -> torch.Tensor:
+    view = automatic_partition_view(flat_tensor, period)
+    if reduce_op == "mean":
+        return view.mean(dim=1, keepdim=True)
+    if reduce_op == "max":
+        return view.max(dim=1, keepdim=True).values
+    raise ValueError("Unexpected reduce_op: {}".format(reduce_op))
+
+
+def automatic_vmean_update(vmean: torch.Tensor, grad_view: torch.Tensor, beta2: float, *, use_fused: bool) -> None:
+    """``vmean = beta2 * vmean + (1 - beta2) * mean_block(g^2)`` in place.  ``use_fused`` asks for
+    CUDA tensors, as in the reference; the arithmetic is the same statement either way (the
+    fused multi-tensor kernels cover whole optimizer steps, not this one piece)."""
+    if use_fused and (grad_view.device.type != "cuda" or vmean.device.type != "cuda"):
+        raise ValueError("FUSE_AUTOMATIC_VMEAN_UPDATE requires CUDA grad_view and vmean, got {} and {}".format(
+            grad_view.device, vmean.device))
+    F_.block_second_moment_(vmean, grad_view, beta2)
+
+
+def gefen_nearest_codebook_indices(codebook: torch.Tensor, normalized_vals: torch.Tensor) -> torch.Tensor:
+    if codebook.device != normalized_vals.device:
+        raise ValueError("Gefen codebook device {} does not match normalized_vals device {}.".format(
+            codebook.device, normalized_vals.device))
+    return _cbk.nearest_codebook_indices(codebook, normalized_vals)
+
+
+def gefen_dequantize_unpacked_indices(codebook: torch.Tensor, stored_indices: torch.Tensor,
+                                      like_tensor: torch.Tensor) -> torch.Tensor:
+    return _cbk.dequantize_indices(codebook, stored_indices, like_tensor.dtype).to(like_tensor.device)
+
+
+def gefen_set_unpacked_indices(stored_indices: torch.Tensor, indices: torch.Tensor) -> None:
+    stored_indices.copy_(indices.to(torch.uint8))
+
+
+def gefen_automatic_fused_update(*, p: torch.Tensor, grad_view: torch.Tensor, m_codebook: torch.Tensor,
+                                 m_magnitude: torch.Tensor, stepsize: torch.Tensor, codebook: torch.Tensor,
+                                 packed_indices: bool, beta1: float, lr: float) -> None:
+    """One tensor's momentum EMA + requantisation + parameter update for a given ``stepsize``
+    (``[blocks, 1]`` or broadcastable to ``[blocks, period]``).  CUDA tensors only, as in the
+    reference (``gefen.py:382-415``); whole steps go through the multi-tensor kernels instead."""
+    if grad_view.device.type != "cuda":
+        raise ValueError("Fused automatic Gefen update requires CUDA tensors.")
+    if codebook.device != grad_view.device:
+        raise ValueError("Gefen codebook device {} does not match grad_view device {}.".format(
+            codebook.device, grad_view.device))
+    if packed_indices:
+        raise ValueError("packed (sub-byte) indices are not supported: indices are one byte per element")
+    q = F_.momentum_requantize_(codebook, m_codebook, m_magnitude, grad_view, beta1)
+    F_.apply_update_(p, q, stepsize, lr, 1.0)
+
+
+def learn_gefen_exact_codebook_from_grad_periods(*, grad_periods, codebook_device, num_codebooks: int,
+                                                 force_endpoints: bool, verbose: bool,
+                                                 compute_mse_logging: bool = True,
+                                                 use_fused_histogram: Optional[bool] = None):
+    """Exact 1-D k-means codebook over the histogram of ``(name, flat_grad, period, grad)`` items."""
+    return _cbk.learn_codebook_from_grad_periods(grad_periods, codebook_device=codebook_device,
+                                                 num_codebooks=num_codebooks, force_endpoints=force_endpoints,
+                                                 verbose=bool(verbose and compute_mse_logging))
 
 
 class Gefen(torch.optim.Optimizer):

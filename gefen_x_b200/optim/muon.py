@@ -31,6 +31,8 @@ from ..parallel.control import raise_if_any_rank_failed, synchronize_step_failur
 from ..quant import codebook as _cbk
 from . import functional as F_
 from . import newton_schulz as NS
+from .newton_schulz import (DEFAULT_A, DEFAULT_B, DEFAULT_C, DEFAULT_NS_STEPS, FP8_MIN_DIM,  # noqa: F401
+                            NS_SCHEDULE_3STEP, NS_SCHEDULE_4STEP, NS_SCHEDULES)
 from .gefen import Gefen, _local, _assert_gradients_structurally_valid, _amp_prepare_optimizer_step
 
 EPS = NS.EPS

@@ -28,7 +28,7 @@ import torch.nn as nn
 
 from .lr_calibration import lr_range_test
 
-OPTIMIZERS = ("gefen", "gefen_muon", "adamw")
+OPTIMIZERS = ("gefen", "gefen_muon", "hybrid", "adamw")
 
 
 @dataclass
@@ -42,17 +42,28 @@ class FindLRResult:
 
 def build_optimizer(model: nn.Module, optimizer: str, lr: float, *, weight_decay: float = 0.0,
                     fused: bool = True, adjust_lr_fn: str = "match_rms_adamw"):
-    from .. import Gefen, GefenMuonHybrid
+    """The requested optimizer family at ``lr`` (names of the reference tool, ``tools/find_lr.py:80-120``):
+    ``gefen``; ``hybrid`` = GefenMuonHybrid over the whole model; ``gefen_muon`` = GefenMuon on the
+    hidden 2-D matrices only (everything else stays frozen for the probe); ``adamw``."""
+    from .. import Gefen, GefenMuon, GefenMuonHybrid
 
-    use_fused = fused and all(p.is_cuda for p in model.parameters())
-    if optimizer == "gefen":
-        return Gefen(model.named_parameters(), lr=lr, weight_decay=weight_decay, fused=use_fused)
-    if optimizer == "gefen_muon":
-        return GefenMuonHybrid(model, lr=lr, weight_decay=weight_decay, fused=use_fused,
-                               adjust_lr_fn=adjust_lr_fn)
     if optimizer == "adamw":
         return torch.optim.AdamW(model.parameters(), lr=lr, weight_decay=weight_decay)
-    raise ValueError("optimizer must be one of {}".format(OPTIMIZERS))
+    use_fused = fused and all(p.is_cuda for p in model.parameters())
+    if optimizer == "gefen":
+        return Gefen([(n, p) for n, p in model.named_parameters() if p.requires_grad], lr=lr,
+                     weight_decay=weight_decay, fused=use_fused)
+    if optimizer == "hybrid":
+        return GefenMuonHybrid(model, lr=lr, weight_decay=weight_decay, fused=use_fused,
+                               adjust_lr_fn=adjust_lr_fn)
+    if optimizer == "gefen_muon":
+        from .run_model_calibration import split_params_for_muon
+
+        muon, _ = split_params_for_muon(model)
+        if not muon:
+            raise ValueError("gefen_muon: model has no 2D hidden matrices to optimize")
+        return GefenMuon(muon, lr=lr, weight_decay=weight_decay, fused=use_fused, adjust_lr_fn=adjust_lr_fn)
+    raise ValueError("unknown optimizer {!r}; choose from {}".format(optimizer, OPTIMIZERS))
 
 
 def _model_loss(model, tokens):

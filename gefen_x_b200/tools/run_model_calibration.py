@@ -1,6 +1,6 @@
 """Run the lr probes of ``lr_calibration`` on a decoder preset (or a Hugging Face model).
 
-    python -m gefen_x_b200.tools.run_model_calibration --model tiny-llama --optimizer gefen_muon
+    python -m gefen_x_b200.tools.run_model_calibration --model tiny-llama --optimizer hybrid
 
 Counterpart of the reference's HF-model runner (``src/gefen/tools/run_model_calibration.py:106-259``);
 ``--hf PATH`` loads a local ``transformers`` checkpoint instead of a preset (no network access
@@ -195,7 +195,7 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="tiny-llama")
     ap.add_argument("--hf", default=None)
-    ap.add_argument("--optimizer", default="gefen", choices=["gefen", "gefen_muon", "adamw"])
+    ap.add_argument("--optimizer", default="gefen", choices=["gefen", "gefen_muon", "hybrid", "adamw"])
     ap.add_argument("--lr", type=float, default=1e-3)
     ap.add_argument("--steps", type=int, default=12)
     ap.add_argument("--warmup", type=int, default=3)

@@ -698,3 +698,48 @@ def test_gradient_histogram_dump_matches_the_reference(tmp_path):
     assert sorted(a) == sorted(b)
     assert torch.equal(a["hist"], b["hist"]) and a["num_samples"] == b["num_samples"]
     assert torch.equal(a["bin_edges"], b["bin_edges"]) and a["bin_width"] == b["bin_width"]
+
+
+def test_module_level_functions_and_constants_match_the_reference():
+    """Every public constant and function of the reference's modules exists under the same name
+    in its counterpart here, and the single-tensor statements give the same numbers."""
+    import importlib
+    import inspect
+
+    _reference()
+    pairs = [("gefen.gefen", "gefen_x_b200.optim.gefen"), ("gefen.partitioning", "gefen_x_b200.quant.partitioning"),
+             ("gefen.quantization", "gefen_x_b200.quant.codebook"), ("gefen.gefen_muon", "gefen_x_b200.optim.muon"),
+             ("gefen.hybrid", "gefen_x_b200.optim.hybrid"), ("gefen.params", "gefen_x_b200.optim.params"),
+             ("gefen.dcp", "gefen_x_b200.ckpt.dcp"), ("gefen.tools.find_lr", "gefen_x_b200.tools.find_lr"),
+             ("gefen.tools.lr_calibration", "gefen_x_b200.tools.lr_calibration"),
+             ("gefen.tools.run_model_calibration", "gefen_x_b200.tools.run_model_calibration")]
+    for rname, oname in pairs:
+        rm, om = importlib.import_module(rname), importlib.import_module(oname)
+        consts = [n for n, v in vars(rm).items() if n.isupper() and not n.startswith("_")
+                  and isinstance(v, (int, float, str, bool, tuple, type(None)))]
+        assert [n for n in consts if not hasattr(om, n)] == [], rname
+        assert [(n, getattr(rm, n), getattr(om, n)) for n in consts if getattr(rm, n) != getattr(om, n)] == [], rname
+        funcs = [n for n, v in vars(rm).items() if not n.startswith("_") and (inspect.isfunction(v) or inspect.isclass(v))
+                 and v.__module__ == rm.__name__]
+        assert [n for n in funcs if not hasattr(om, n)] == [], rname
+    rg, og = importlib.import_module("gefen.gefen"), importlib.import_module("gefen_x_b200.optim.gefen")
+    g = torch.Generator().manual_seed(5)
+    flat = torch.randn(96, generator=g)
+    for op in ("mean", "max"):
+        assert torch.equal(rg.automatic_partition_reduce(flat, 8, op), og.automatic_partition_reduce(flat, 8, op))
+    cb = torch.sort(torch.cat([torch.tensor([-1.0, 1.0]), torch.rand(254, generator=g) * 2 - 1])).values
+    vals = torch.rand(12, 8, generator=g) * 2 - 1
+    ia, ib = rg.gefen_nearest_codebook_indices(cb, vals), og.gefen_nearest_codebook_indices(cb, vals)
+    assert ia.dtype == ib.dtype == torch.uint8 and torch.equal(ia, ib)
+    like = torch.zeros(1, dtype=torch.bfloat16)
+    assert torch.equal(rg.gefen_dequantize_unpacked_indices(cb, ia, like), og.gefen_dequantize_unpacked_indices(cb, ib, like))
+    va, vb = torch.rand(12, 1, generator=g), None
+    vb = va.clone()
+    rg.automatic_vmean_update(va, vals, 0.99, use_fused=False)
+    og.automatic_vmean_update(vb, vals, 0.99, use_fused=False)
+    torch.testing.assert_close(va, vb, rtol=1e-6, atol=0)
+    items = [("w", flat, 8, flat)]
+    kw = dict(codebook_device=torch.device("cpu"), num_codebooks=256, force_endpoints=True, verbose=False,
+              compute_mse_logging=False)
+    assert torch.equal(rg.learn_gefen_exact_codebook_from_grad_periods(grad_periods=iter(items), **kw),
+                       og.learn_gefen_exact_codebook_from_grad_periods(grad_periods=iter(items), **kw))
