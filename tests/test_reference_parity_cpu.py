@@ -743,3 +743,98 @@ def test_module_level_functions_and_constants_match_the_reference():
               compute_mse_logging=False)
     assert torch.equal(rg.learn_gefen_exact_codebook_from_grad_periods(grad_periods=iter(items), **kw),
                        og.learn_gefen_exact_codebook_from_grad_periods(grad_periods=iter(items), **kw))
+
+
+def _dcp_reshard_worker(rank, world, port, path, pkg, mode, q):
+    """``mode="save"``: 3 steps and a DCP save with ``pkg``; ``mode="load"``: load into ``pkg`` at this
+    world size, one more step, report the full parameters."""
+    import torch.distributed as dist
+    import torch.distributed.checkpoint as dcp
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+
+    import gefen_x_b200 as ours
+
+    mod = {"ref": _reference(), "ours": ours}[pkg]
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        mesh = init_device_mesh("cpu", (world,))
+
+        def full(seed):
+            g = torch.Generator().manual_seed(seed)
+            return {n: torch.randn(s, generator=g) * 0.1 for n, s in _DCP_SHAPES}
+
+        ps = [(n, distribute_tensor(t.clone(), mesh, [Shard(0)]).requires_grad_(True)) for n, t in full(0).items()]
+        opt = mod.Gefen(ps, lr=1e-2, fused=False, factored_v_2d=False)
+
+        def step(k):
+            for (_, p), t in zip(ps, full(100 + k).values()):
+                p.grad = distribute_tensor(t, mesh, [Shard(0)])
+            opt.step()
+
+        if mode == "save":
+            for k in range(3):
+                step(k)
+            dcp.save({"optimizer": mod.GefenDCPState(opt).state_dict()},
+                     storage_writer=mod.GefenFileSystemWriter(path), planner=mod.GefenSavePlanner())
+            weights = {n: p.full_tensor().detach().clone() for n, p in ps}      # collective: every rank
+            if rank == 0:
+                torch.save(weights, path + ".weights")
+            dist.barrier()
+            q.put((rank, "saved"))
+        else:
+            weights = torch.load(path + ".weights")
+            for n, p in ps:
+                p.data.copy_(distribute_tensor(weights[n], mesh, [Shard(0)]))
+            dcp.load({"optimizer": mod.GefenDCPState(opt)}, checkpoint_id=path)
+            step(3)
+            q.put((rank, {n: p.full_tensor().detach().numpy() for n, p in ps}))
+    except Exception:  # pragma: no cover - reported to the parent
+        import traceback
+
+        q.put((rank, dict(error=traceback.format_exc())))
+    finally:
+        dist.destroy_process_group()
+
+
+def _spawn_world(world, target, *args):
+    import socket
+
+    import torch.multiprocessing as mp
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=target, args=(r, world, port) + args + (q,)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    res = dict(q.get(timeout=300) for _ in range(world))
+    for pr in procs:
+        pr.join(timeout=60)
+    for r in res:
+        assert not (isinstance(res[r], dict) and "error" in res[r]), res[r].get("error")
+    return res
+
+
+def test_dcp_resharding_across_packages_matches_the_reference_loader(tmp_path):
+    """A 2-rank DCP checkpoint of the reference resharded to 1 and to 4 ranks by this package
+    lands where the reference's own loader lands; a checkpoint of this package reshards in the
+    reference the same way."""
+    import numpy as np
+
+    path = str(tmp_path / "from_ref")
+    _spawn_world(2, _dcp_reshard_worker, path, "ref", "save")
+    for world in (1, 4):
+        a = _spawn_world(world, _dcp_reshard_worker, path, "ref", "load")[0]
+        b = _spawn_world(world, _dcp_reshard_worker, path, "ours", "load")[0]
+        assert max(float(np.abs(a[n] - b[n]).max()) for n in a) < 1e-6, world
+    path = str(tmp_path / "from_ours")
+    _spawn_world(2, _dcp_reshard_worker, path, "ours", "save")
+    a = _spawn_world(4, _dcp_reshard_worker, path, "ref", "load")[0]
+    b = _spawn_world(4, _dcp_reshard_worker, path, "ours", "load")[0]
+    assert max(float(np.abs(a[n] - b[n]).max()) for n in a) < 1e-6
