@@ -838,3 +838,32 @@ def test_dcp_resharding_across_packages_matches_the_reference_loader(tmp_path):
     a = _spawn_world(4, _dcp_reshard_worker, path, "ref", "load")[0]
     b = _spawn_world(4, _dcp_reshard_worker, path, "ours", "load")[0]
     assert max(float(np.abs(a[n] - b[n]).max()) for n in a) < 1e-6
+
+
+@pytest.mark.parametrize("kw", [dict(backup_optimizer="adamw"), dict(backup_1d_period_one=True),
+                                dict(backup_2d_period_one=True), dict(no_decay_substrings=("bias",), weight_decay=0.1),
+                                dict(muon_lr=1e-3, backup_lr=5e-3), dict(muon_weight_decay=0.2, backup_weight_decay=0.0),
+                                dict(backup_substrings=("0.",)),
+                                dict(nesterov=False, momentum=0.9, ns_steps=4, ns_schedule=None)],
+                         ids=["adamw-backup", "1d-period-one", "2d-period-one", "no-decay", "split-lr", "split-decay",
+                              "routing", "plain-quintic"])
+def test_hybrid_routing_options_follow_the_reference(kw):
+    import gefen_x_b200 as ours
+
+    ref = _reference()
+    a = _train(lambda m: ref.GefenMuonHybrid(m, lr=3e-3, fused=False, **kw), steps=40)
+    b = _train(lambda m: ours.GefenMuonHybrid(m, lr=3e-3, fused=False, **kw), steps=40)
+    assert ((a - b).abs() / a).max().item() < 2e-3
+
+
+@pytest.mark.parametrize("kw", [dict(force_1d_period_one=True), dict(force_2d_period_one=True),
+                                dict(period_one_substrings=("2.",)),
+                                dict(factored_v_2d=False, force_2d_period_one=True)],
+                         ids=["1d", "2d", "substrings", "unfactored-2d"])
+def test_period_one_options_follow_the_reference(kw):
+    import gefen_x_b200 as ours
+
+    ref = _reference()
+    a = _train(lambda m: ref.Gefen(list(m.named_parameters()), lr=3e-3, fused=False, **kw), steps=40)
+    b = _train(lambda m: ours.Gefen(list(m.named_parameters()), lr=3e-3, fused=False, **kw), steps=40)
+    assert ((a - b).abs() / a).max().item() < 2e-3
