@@ -867,3 +867,56 @@ def test_period_one_options_follow_the_reference(kw):
     a = _train(lambda m: ref.Gefen(list(m.named_parameters()), lr=3e-3, fused=False, **kw), steps=40)
     b = _train(lambda m: ours.Gefen(list(m.named_parameters()), lr=3e-3, fused=False, **kw), steps=40)
     assert ((a - b).abs() / a).max().item() < 2e-3
+
+
+def test_misuse_raises_the_same_exception_types_as_the_reference():
+    import gefen_x_b200 as ours
+
+    ref = _reference()
+
+    def p(shape=(4, 8)):
+        return torch.randn(shape).requires_grad_()
+
+    def with_grad(m, grad_of):
+        w = p()
+        opt = m.Gefen([("w", w)], lr=1e-3, fused=False)
+        w.grad = grad_of(w)
+        opt.step()
+
+    def dup(m):
+        w = p()
+        m.Gefen([("a", w), ("b", w)], lr=1e-3, fused=False)
+
+    cases = {
+        "negative lr": lambda m: m.Gefen([("w", p())], lr=-1.0, fused=False),
+        "beta of 1": lambda m: m.Gefen([("w", p())], lr=1e-3, betas=(1.0, 0.9), fused=False),
+        "negative eps": lambda m: m.Gefen([("w", p())], lr=1e-3, eps=-1, fused=False),
+        "negative decay": lambda m: m.Gefen([("w", p())], lr=1e-3, weight_decay=-1, fused=False),
+        "no parameters": lambda m: m.Gefen([], lr=1e-3, fused=False),
+        "unnamed parameters": lambda m: m.Gefen([p()], lr=1e-3, fused=False),
+        "duplicate parameter": dup,
+        "complex parameter": lambda m: m.Gefen([("w", torch.zeros(4, dtype=torch.complex64).requires_grad_())],
+                                               lr=1e-3, fused=False),
+        "negative refresh": lambda m: m.Gefen([("w", p())], lr=1e-3, fused=False, codebook_refresh_every=-2),
+        "muon on a vector": lambda m: m.GefenMuon([("w", p((8,)))], lr=1e-3, fused=False),
+        "muon mode": lambda m: m.GefenMuon([("w", p())], lr=1e-3, fused=False, sharded_mode="x"),
+        "muon schedule": lambda m: m.GefenMuon([("w", p())], lr=1e-3, fused=False, ns_schedule="zzz"),
+        "muon zero iterations": lambda m: m.GefenMuon([("w", p())], lr=1e-3, fused=False, ns_steps=0),
+        "muon momentum": lambda m: m.GefenMuon([("w", p())], lr=1e-3, fused=False, momentum=1.5),
+        "muon lr rule": lambda m: m.GefenMuon([("w", p())], lr=1e-3, fused=False, adjust_lr_fn="zz"),
+        "hybrid backup kind": lambda m: m.GefenMuonHybrid(_model(), lr=1e-3, fused=False, backup_optimizer="sgd"),
+        "hybrid add group": lambda m: m.GefenMuonHybrid(_model(), lr=1e-3, fused=False).add_param_group({"params": []}),
+        "load of an empty dict": lambda m: m.Gefen([("w", p())], lr=1e-3, fused=False).load_state_dict(
+            {"state": {}, "param_groups": []}),
+        "nan gradient": lambda m: with_grad(m, lambda w: torch.full_like(w, float("nan"))),
+        "sparse gradient": lambda m: with_grad(m, lambda w: torch.zeros_like(w).to_sparse()),
+    }
+    for name, fn in cases.items():
+        kinds = []
+        for m in (ref, ours):
+            try:
+                fn(m)
+                kinds.append("ok")
+            except Exception as exc:  # noqa: BLE001
+                kinds.append(type(exc).__name__)
+        assert kinds[0] == kinds[1], (name, kinds)
