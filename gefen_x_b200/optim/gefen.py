@@ -215,12 +215,18 @@ def automatic_partition_reduce(flat_tensor: torch.Tensor, period: int, reduce_op
 
 def automatic_vmean_update(vmean: torch.Tensor, grad_view: torch.Tensor, beta2: float, *, use_fused: bool) -> None:
     """``vmean = beta2 * vmean + (1 - beta2) * mean_block(g^2)`` in place.  ``use_fused`` asks for
-    CUDA tensors, as in the reference; the arithmetic is the same statement either way (the
-    fused multi-tensor kernels cover whole optimizer steps, not this one piece)."""
-    if use_fused and (grad_view.device.type != "cuda" or vmean.device.type != "cuda"):
-        raise ValueError("FUSE_AUTOMATIC_VMEAN_UPDATE requires CUDA grad_view and vmean, got {} and {}".format(
-            grad_view.device, vmean.device))
-    F_.block_second_moment_(vmean, grad_view, beta2)
+    CUDA tensors and squares in fp32 (the rule of the fused kernels and of ``Gefen.step`` here);
+    otherwise the reference's non-fused statement runs (``gefen.py:152-196``)."""
+    if use_fused:
+        if grad_view.device.type != "cuda" or vmean.device.type != "cuda":
+            raise ValueError("FUSE_AUTOMATIC_VMEAN_UPDATE requires CUDA grad_view and vmean, got {} and {}".format(
+                grad_view.device, vmean.device))
+        F_.block_second_moment_(vmean, grad_view, beta2)      # fp32 square, as the fused kernels
+        return
+    # the reference's non-fused statement: the square stays in the gradient's dtype (fp16 is
+    # promoted, its squares overflow), the fp32 running mean absorbs the increment
+    g = grad_view.float() if grad_view.dtype == torch.float16 else grad_view
+    vmean.mul_(beta2).add_(torch.mean(g * g, dim=1, keepdim=True), alpha=1 - beta2)
 
 
 def gefen_nearest_codebook_indices(codebook: torch.Tensor, normalized_vals: torch.Tensor) -> torch.Tensor:
@@ -393,8 +399,8 @@ class Gefen(torch.optim.Optimizer):
             raise ValueError("lr as a Tensor must be 1-element, got numel={}".format(lr.numel()))
         if not 0.0 <= lr:
             raise ValueError("Invalid learning rate: {}".format(lr))
-        if not 0.0 <= eps:
-            raise ValueError("Invalid epsilon value: {}".format(eps))
+        if not math.isfinite(eps) or eps <= 0.0:
+            raise ValueError("Invalid epsilon value (eps must be finite and > 0): {}".format(eps))
         if not 0.0 <= betas[0] < 1.0:
             raise ValueError("Invalid beta parameter at index 0: {}".format(betas[0]))
         if not 0.0 <= betas[1] < 1.0:

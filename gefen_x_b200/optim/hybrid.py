@@ -93,6 +93,15 @@ class GefenMuonHybrid(torch.optim.Optimizer):
             raise TypeError("deterministic must be a bool")
         if backup_optimizer not in ("gefen", "adamw"):
             raise ValueError("backup_optimizer must be 'gefen' or 'adamw', got {!r}".format(backup_optimizer))
+        if adjust_lr_fn in (None, "original"):
+            # Muon-native scaling leaves the matrices on another lr footing than the backup half
+            # (reference hybrid.py:395-412): say so instead of silently mis-scaling one half
+            import warnings
+
+            warnings.warn("GefenMuonHybrid: adjust_lr_fn={!r} uses Muon-native LR scaling, so an AdamW-scale lr "
+                          "will mis-scale the 2D Muon matrices relative to the backup half. Use "
+                          "adjust_lr_fn='match_rms_adamw' (the default) to share one AdamW-scale lr, or set "
+                          "muon_lr explicitly.".format(adjust_lr_fn), stacklevel=2)
         model = None
         if backup_named_params is None:
             subs = DEFAULT_BACKUP_SUBSTRINGS if backup_substrings is None else tuple(backup_substrings)

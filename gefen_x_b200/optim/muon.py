@@ -93,15 +93,25 @@ class GefenMuon(Gefen):
             raise ValueError("Invalid momentum value: {}".format(momentum))
         if adjust_lr_fn not in (None, "original", "match_rms_adamw"):
             raise ValueError("Unknown adjust_lr_fn {!r}".format(adjust_lr_fn))
-        if ns_steps < 1:
-            raise ValueError("ns_steps must be >= 1")
+        if not math.isfinite(eps) or eps <= 0.0:
+            raise ValueError("eps must be finite and > 0 but is: {}".format(eps))
+        if not 0.0 <= normuon_beta2 < 1.0:
+            raise ValueError("normuon_beta2 must be in [0, 1) but is: {}".format(normuon_beta2))
+        if not math.isfinite(normuon_eps) or normuon_eps <= 0.0:
+            raise ValueError("normuon_eps must be finite and > 0 but is: {}".format(normuon_eps))
         # A schedule (a name or an explicit list of (a, b, c)) overrides ns_coefficients / ns_steps
         # and is stored resolved, so a parameter group carries the reference's keys only
         # (reference src/gefen/gefen_muon.py:605-626, group keys :716-735).
         if ns_schedule is not None:
-            sched = (NS.resolve_schedule(ns_schedule, ns_coefficients, ns_steps) if isinstance(ns_schedule, str)
-                     else NS.normalize_schedule(ns_schedule, ns_steps))
-            if not (isinstance(ns_schedule, str) and NS.NS_SCHEDULES[ns_schedule] is None):
+            if isinstance(ns_schedule, str):
+                if ns_schedule not in NS.NS_SCHEDULES:
+                    raise ValueError("Unknown ns_schedule {!r}; choose from {}".format(
+                        ns_schedule, sorted(NS.NS_SCHEDULES)))
+                resolved = NS.NS_SCHEDULES[ns_schedule]
+            else:
+                resolved = ns_schedule
+            if resolved is not None:           # "standard" defers to ns_coefficients / ns_steps
+                sched = NS.normalize_schedule(resolved, ns_steps)
                 ns_coefficients, ns_steps = [tuple(c) for c in sched], len(sched)
         NS.normalize_schedule(ns_coefficients, ns_steps)                  # validates
         if fp8_ns and torch.cuda.is_available() and not NS.fp8_supported():
@@ -127,18 +137,45 @@ class GefenMuon(Gefen):
 
     # ------------------------------------------------------------------
     def add_param_group(self, param_group):
-        extra = dict(getattr(self, "_muon_defaults", {}))
-        for k in list(extra):
-            if k in param_group:
-                extra[k] = param_group[k]
+        """Register a group with every Muon option resolved and validated before anything is
+        mutated: group values override the constructor's, a named or explicit ``ns_schedule`` is
+        stored as ``ns_coefficients`` / ``ns_steps``, ``beta1`` mirrors ``momentum`` and ``beta2``
+        is 0 (reference ``gefen_muon.py:790-880``)."""
+        if not isinstance(param_group, dict):
+            raise TypeError("param_group must be a dict")
         merged = dict(param_group)
-        merged.update(extra)
-        for _, p in self._iter_params_with_names(merged["params"]):
-            if p.ndim != 2:
-                raise ValueError(
-                    "GefenMuon optimizes 2D matrices only; got a {}-D parameter of shape {}. "
-                    "Route embeddings, heads, norms and biases to a backup optimizer "
-                    "(GefenMuonHybrid does this).".format(p.ndim, tuple(p.shape)))
+        for k, v in getattr(self, "_muon_defaults", {}).items():
+            merged.setdefault(k, v)
+        if merged["sharded_mode"] not in _SHARDED_MODES:
+            raise ValueError("sharded_mode must be one of {}, got {!r}".format(_SHARDED_MODES, merged["sharded_mode"]))
+        if merged["adjust_lr_fn"] not in (None, "original", "match_rms_adamw"):
+            raise ValueError("Unknown adjust_lr_fn {!r}".format(merged["adjust_lr_fn"]))
+        if not 0.0 <= merged["momentum"] < 1.0:
+            raise ValueError("Invalid momentum value: {}".format(merged["momentum"]))
+        if not 0.0 <= merged["normuon_beta2"] < 1.0:
+            raise ValueError("normuon_beta2 must be in [0, 1) but is: {}".format(merged["normuon_beta2"]))
+        if not math.isfinite(merged["normuon_eps"]) or merged["normuon_eps"] <= 0.0:
+            raise ValueError("normuon_eps must be finite and > 0 but is: {}".format(merged["normuon_eps"]))
+        schedule = merged.pop("ns_schedule", None)
+        if schedule is not None:
+            if isinstance(schedule, str):
+                if schedule not in NS.NS_SCHEDULES:
+                    raise ValueError("Unknown ns_schedule {!r}; choose from {}".format(schedule, sorted(NS.NS_SCHEDULES)))
+                schedule = NS.NS_SCHEDULES[schedule]
+            if schedule is not None:
+                resolved = NS.normalize_schedule(schedule, merged["ns_steps"])
+                merged["ns_coefficients"], merged["ns_steps"] = [tuple(c) for c in resolved], len(resolved)
+        NS.normalize_schedule(merged["ns_coefficients"], merged["ns_steps"])
+        merged.pop("betas", None)
+        merged["beta1"], merged["beta2"] = merged["momentum"], 0.0
+        params = merged.get("params")
+        if params is not None:
+            for _, p in self._iter_params_with_names(params):
+                if p.ndim != 2:
+                    raise ValueError(
+                        "GefenMuon only supports 2D matrices; got a {}-D parameter of shape {}. "
+                        "Route embeddings, heads, norms and biases to a backup optimizer "
+                        "(GefenMuonHybrid does this).".format(p.ndim, tuple(p.shape)))
         super().add_param_group(merged)
 
     def _is_factored(self, p) -> bool:

@@ -42,18 +42,30 @@ Coeffs = Tuple[float, float, float]
 
 
 def normalize_schedule(ns_coefficients, ns_steps: int) -> List[Coeffs]:
-    """A single (a, b, c) repeated ``ns_steps`` times, or an explicit per-iteration list."""
+    """A single (a, b, c) repeated ``ns_steps`` times (``1 <= ns_steps < 100``), or an explicit
+    per-iteration list of fewer than 100 entries, whose length is the iteration count
+    (``ns_steps`` is then ignored).  Same checks as the reference (``gefen_muon.py:189-233``)."""
     if ns_coefficients is None:
         ns_coefficients = (DEFAULT_A, DEFAULT_B, DEFAULT_C)
     seq = list(ns_coefficients)
-    if len(seq) == 3 and all(isinstance(x, (int, float)) for x in seq):
+    if len(seq) == 0:
+        raise ValueError("ns_coefficients must be non-empty")
+    if isinstance(seq[0], (int, float)):
+        if not 1 <= ns_steps < 100:
+            raise ValueError(
+                "ns_steps must be in [1, 100) but is: {}. 0 or a negative value would produce an empty "
+                "Newton-Schulz schedule (Muon degrades to normalized momentum SGD); 100+ is rejected for "
+                "computational efficiency".format(ns_steps))
+        if len(seq) != 3:
+            raise ValueError("A single coefficient set must be a tuple of exactly 3 values")
         return [tuple(float(x) for x in seq)] * int(ns_steps)
     out = []
     for item in seq:
-        item = tuple(float(x) for x in item)
         if len(item) != 3:
-            raise ValueError("every Newton-Schulz coefficient entry must be (a, b, c)")
-        out.append(item)
+            raise ValueError("Each Newton-Schulz schedule entry must have exactly 3 values")
+        out.append(tuple(float(x) for x in item))
+    if len(out) >= 100:
+        raise ValueError("Newton-Schulz schedule length must be less than 100 for computational efficiency")
     return out
 
 
