@@ -112,12 +112,13 @@ class GefenMuonHybrid(torch.optim.Optimizer):
                 items = list(muon_named_params)
                 if items and isinstance(items[0], torch.Tensor):
                     raise TypeError(
-                        "GefenMuonHybrid cannot route bare tensors; pass (name, param) pairs, a model, "
-                        "or use GefenMuonHybrid.from_model(model, ...)")
+                        "Bare tensors can't be routed by name: pass (name, param) pairs, a model, or use "
+                        "GefenMuonHybrid.from_model(model, ...)")
                 muon_named, backup_named = split_named_for_muon(items, subs)
         else:
             if backup_substrings is not None:
-                raise ValueError("backup_substrings only applies to the single-argument form")
+                raise TypeError("backup_substrings is only valid with the single-argument form (a model or "
+                                "one list of named parameters); the two-list form is already routed")
             muon_named, backup_named = list(muon_named_params), list(backup_named_params)
         muon_named, backup_named = validate_split(muon_named, backup_named, model)
         if not muon_named and not backup_named:
@@ -161,15 +162,14 @@ class GefenMuonHybrid(torch.optim.Optimizer):
             else:
                 groups = []
                 if decay:
-                    groups.append({"params": [p for _, p in decay], "weight_decay": b_wd})
+                    groups.append({"params": [p for _, p in decay], "param_names": [n for n, _ in decay],
+                                   "weight_decay": b_wd})
                 if no_decay:
-                    groups.append({"params": [p for _, p in no_decay], "weight_decay": 0.0})
-                kw = {}
-                if fused and all(p.is_cuda for _, p in backup_named):
-                    kw["fused"] = True
-                if capturable:
-                    kw["capturable"] = True
-                self.backup = torch.optim.AdamW(groups, lr=b_lr, betas=betas, eps=eps, **kw)
+                    groups.append({"params": [p for _, p in no_decay], "param_names": [n for n, _ in no_decay],
+                                   "weight_decay": 0.0})
+                # the execution flags are forwarded as given (reference hybrid.py: AdamW backup)
+                self.backup = torch.optim.AdamW(groups, lr=b_lr, betas=betas, eps=eps, fused=bool(fused),
+                                                capturable=bool(capturable))
         self.state = _MergedState([self.muon, self.backup])
         # torch.optim.Optimizer.__init__ is deliberately not called: groups and state are live views
         # of the children's, so a scheduler's in-place ``group["lr"] = ...`` reaches them.  The hook
@@ -184,6 +184,11 @@ class GefenMuonHybrid(torch.optim.Optimizer):
         self._optimizer_state_dict_post_hooks = OrderedDict()
         self._optimizer_load_state_dict_pre_hooks = OrderedDict()
         self._optimizer_load_state_dict_post_hooks = OrderedDict()
+
+    def __repr__(self) -> str:
+        count = lambda c: 0 if c is None else sum(len(g["params"]) for g in c.param_groups)  # noqa: E731
+        return "{}(muon_params={}, backup_params={}, backup_optimizer={!r})".format(
+            type(self).__name__, count(self.muon), count(self.backup), self.backup_optimizer)
 
     @classmethod
     def from_model(cls, model: nn.Module, **kwargs) -> "GefenMuonHybrid":

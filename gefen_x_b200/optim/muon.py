@@ -127,8 +127,8 @@ class GefenMuon(Gefen):
                                    normuon_eps=normuon_eps, cautious=cautious)
         self.sharded_mode = sharded_mode
         self.fp8_ns, self.fp8_ns_compile = fp8_ns, fp8_ns_compile
-        self.batched_ns = batched_ns
-        self.batched_ns_workspace_bytes = int(batched_ns_workspace_bytes)
+        self.batched_ns = self._batched_ns = batched_ns
+        self.batched_ns_workspace_bytes = self._batched_ns_workspace_bytes = int(batched_ns_workspace_bytes)
         # the group's `eps` is the Newton-Schulz normalisation epsilon and beta2 is unused (0), as in
         # the reference's groups
         super().__init__(params, lr=lr, betas=(momentum, 0.0), eps=eps, weight_decay=weight_decay,

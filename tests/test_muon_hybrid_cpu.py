@@ -205,6 +205,6 @@ def test_hybrid_call_forms():
         assert len(o.muon.param_groups[0]["params"]) == 2
     with pytest.raises(TypeError):
         GefenMuonHybrid([m.fc1.weight], lr=1e-3, fused=False)
-    with pytest.raises(ValueError):
+    with pytest.raises(TypeError, match="backup_substrings is only valid"):      # the reference's type and wording
         GefenMuonHybrid(muon, backup, lr=1e-3, fused=False, backup_substrings=("x",))
     assert a.state[m.fc1.weight] is a.muon.state[m.fc1.weight]
