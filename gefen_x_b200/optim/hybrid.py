@@ -27,50 +27,103 @@ from .params import (DEFAULT_BACKUP_SUBSTRINGS, split_named_for_muon, split_para
                      validate_split)
 
 
-class _MergedState:
-    """Read-mostly view routing ``state[param]`` to the child that owns ``param``."""
+_ZERO_HINT = ("GefenMuonHybrid cannot run under DeepSpeed ZeRO: ZeRO replaces the parameters with flat 1-D fp32 "
+              "partitions that Muon's 2-D Newton-Schulz step cannot use, and it keeps its bookkeeping in "
+              "optimizer.state under those partitions. Use plain Gefen with DeepSpeed ZeRO.")
+
+
+class _MergedState(dict):
+    """``optimizer.state`` of the hybrid: a live view that routes every access to the child that
+    owned the parameter at construction.  Reads of a known parameter auto-create in the owning
+    child (torch's defaultdict behaviour); a key that is not one of the hybrid's parameters
+    raises a ``KeyError`` that names the usual cause, an optimizer wrapper that swapped in flat
+    partitions (reference ``hybrid.py`` state view).  The underlying ``dict`` stays empty."""
 
     def __init__(self, children):
-        self._children = children
+        super().__init__()
+        self._children = [c for c in children if c is not None]
+        self._owner_of = {id(p): (p, c) for c in self._children for g in c.param_groups for p in g["params"]}
 
     def _owner(self, p):
-        for c in self._children:
-            if c is not None and any(p is q for g in c.param_groups for q in g["params"]):
-                return c
-        raise KeyError(p)
+        hit = self._owner_of.get(id(p))
+        if hit is None or hit[0] is not p:
+            raise KeyError("optimizer.state[<{} of shape {}>]: not a parameter of this optimizer. {}".format(
+                type(p).__name__, tuple(getattr(p, "shape", ())), _ZERO_HINT))
+        return hit[1]
+
+    def _known(self, p) -> bool:
+        hit = self._owner_of.get(id(p))
+        return hit is not None and hit[0] is p
 
     def __getitem__(self, p):
         return self._owner(p).state[p]
 
+    def __setitem__(self, p, value):
+        self._owner(p).state[p] = value
+
+    def __delitem__(self, p):
+        del self._owner(p).state[p]
+
     def get(self, p, default=None):
-        try:
-            return self[p]
-        except KeyError:
+        if not self._known(p):
             return default
+        st = self._owner(p).state
+        return st[p] if p in st else default
 
     def __contains__(self, p):
-        return any(c is not None and p in c.state for c in self._children)
+        return self._known(p) and p in self._owner(p).state
 
     def __iter__(self):
         for c in self._children:
-            if c is not None:
-                yield from c.state
+            yield from list(c.state)
 
     def __len__(self):
-        return sum(len(c.state) for c in self._children if c is not None)
+        return sum(len(c.state) for c in self._children)
 
-    def items(self):
-        for c in self._children:
-            if c is not None:
-                yield from c.state.items()
-
-    def values(self):
-        for c in self._children:
-            if c is not None:
-                yield from c.state.values()
+    def __bool__(self):
+        return len(self) > 0
 
     def keys(self):
-        return iter(self)
+        return list(iter(self))
+
+    def items(self):
+        return [(p, st) for c in self._children for p, st in c.state.items()]
+
+    def values(self):
+        return [st for c in self._children for st in c.state.values()]
+
+    def setdefault(self, p, default=None):
+        st = self._owner(p).state
+        if p in st:
+            return st[p]
+        st[p] = default
+        return default
+
+    def update(self, *args, **kwargs):
+        for p, value in dict(*args, **kwargs).items():
+            self[p] = value
+
+    _MISSING = object()
+
+    def pop(self, p, default=_MISSING):
+        st = self._owner(p).state
+        if p in st:
+            value = st[p]
+            del st[p]
+            return value
+        if default is _MergedState._MISSING:
+            raise KeyError(p)
+        return default
+
+    def popitem(self):
+        raise NotImplementedError("popitem is not defined on the hybrid's merged state view")
+
+    def clear(self):
+        for c in self._children:
+            c.state.clear()
+
+    def __repr__(self):
+        return "_MergedState({} entries)".format(len(self))
 
 
 class GefenMuonHybrid(torch.optim.Optimizer):
@@ -123,6 +176,12 @@ class GefenMuonHybrid(torch.optim.Optimizer):
         muon_named, backup_named = validate_split(muon_named, backup_named, model)
         if not muon_named and not backup_named:
             raise ValueError("optimizer got an empty parameter list")
+        every = list(muon_named) + list(backup_named)
+        if not muon_named and every and all(p.numel() == 0 for _, p in every):
+            raise ValueError(
+                "GefenMuonHybrid got only zero-numel parameters: this is what DeepSpeed ZeRO stage 3 "
+                "(zero.Init) leaves before the optimizer is built, and it would silently give a backup-only "
+                "optimizer without the Muon half. Use plain Gefen with ZeRO stage 3.")
 
         self.backup_optimizer = backup_optimizer
         self.defaults = dict(lr=lr, weight_decay=weight_decay)
@@ -212,8 +271,8 @@ class GefenMuonHybrid(torch.optim.Optimizer):
 
     @param_groups.setter
     def param_groups(self, value):
-        raise AttributeError("GefenMuonHybrid.param_groups is a view of the children's groups; mutate the "
-                             "group dicts in place or build a new hybrid")
+        raise TypeError("GefenMuonHybrid.param_groups is a live view of the children's groups and cannot be "
+                        "assigned (DeepSpeed ZeRO's optimizer step does this). " + _ZERO_HINT)
 
     def add_param_group(self, param_group):
         raise NotImplementedError(

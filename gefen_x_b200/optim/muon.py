@@ -378,10 +378,11 @@ class GefenMuon(Gefen):
             for g in self.param_groups:
                 for p in g["params"]:
                     if p.ndim != 2:
-                        raise RuntimeError(
-                            "GefenMuon found a {}-D parameter (shape {}) in its param groups at step "
-                            "time; an optimizer wrapper replaced param_groups[*]['params'] (DeepSpeed "
-                            "ZeRO does this). Use plain Gefen there.".format(p.ndim, tuple(p.shape)))
+                        raise ValueError(
+                            "GefenMuon found a {}-D parameter (shape {}) in its param groups at step time: an "
+                            "optimizer wrapper replaced param_groups[*]['params'] with flat 1-D fp32 partitions "
+                            "(DeepSpeed ZeRO does this). Muon's 2-D Newton-Schulz step cannot be applied to a "
+                            "flat partition. Use plain Gefen with DeepSpeed ZeRO.".format(p.ndim, tuple(p.shape)))
         except Exception as exc:           # noqa: BLE001 - fanned out below
             local_exc = exc
         pgs = []

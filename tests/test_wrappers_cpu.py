@@ -48,7 +48,7 @@ def test_muon_family_refuses_flattened_parameters_before_touching_state():
     flat = torch.cat([p.detach().reshape(-1) for _, p in mats]).requires_grad_()
     opt.param_groups[0]["params"] = [flat]
     flat.grad = torch.ones_like(flat)
-    with pytest.raises(RuntimeError, match="1-D parameter"):
+    with pytest.raises(ValueError, match="1-D parameter"):
         opt.step()
     assert len(opt.state) == 0 or all("step" not in st for st in opt.state.values())
     hyb = GefenMuonHybrid(_model(), lr=1e-2, fused=False)
