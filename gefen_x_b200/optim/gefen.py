@@ -1675,8 +1675,75 @@ class Gefen(torch.optim.Optimizer):
                 "Loading it would reinterpret the restored indices with a different codebook and "
                 "silently corrupt optimizer state. Resume from an unmodified Gefen checkpoint or "
                 "a DCP checkpoint written by a version that preserves _gefen_checkpoint_metadata.")
+        self._validate_native_states(sd.get("state", {}) or {}, cb)
         sd = self._pack_legacy_param_groups_for_load(self.param_groups, sd)
         return sd, step, cb
+
+    @staticmethod
+    def _validate_counter(name: str, value) -> float:
+        """A step counter of a checkpoint: a non-negative whole number held as an int, a float or a
+        one-element non-boolean tensor (reference ``gefen.py:4923-4950``)."""
+        if torch.is_tensor(value):
+            if value.numel() != 1 or value.dtype == torch.bool:
+                raise ValueError("Gefen checkpoint counter {} must be a one-element numeric tensor".format(name))
+            value = value.reshape(()).item()
+        if isinstance(value, bool) or not isinstance(value, (int, float)):
+            raise ValueError("Gefen checkpoint counter {} must be numeric, got {!r}".format(name, type(value)))
+        if not math.isfinite(value) or value < 0 or float(value) != float(int(value)):
+            raise ValueError("Gefen checkpoint counter {} must be a non-negative whole number, got {}".format(
+                name, value))
+        return float(value)
+
+    @classmethod
+    def _validate_native_states(cls, states, codebook) -> None:
+        """Reject a malformed checkpoint before anything live is touched: counters, period, index
+        dtype, magnitudes and second moments finite and non-negative, complete momentum /
+        factored / NorMuon groups of keys, a sorted finite 256-entry codebook in [-1, 1]
+        (reference ``gefen.py:4896-5203``)."""
+
+        def non_negative(name, t):
+            if not torch.is_tensor(t) or not t.is_floating_point() or not bool(torch.isfinite(t).all()) \
+                    or not bool((t >= 0).all()):
+                raise ValueError("Gefen checkpoint {} must be a finite non-negative floating tensor".format(name))
+
+        quantised = False
+        for st in states.values():
+            if not isinstance(st, dict):
+                continue
+            for key in _COUNTER_KEYS:
+                if key in st:
+                    cls._validate_counter(key, st[key])
+            if "automatic_period" in st:
+                period = st["automatic_period"]
+                if isinstance(period, bool) or not isinstance(period, int) or period < 1:
+                    raise ValueError("Gefen checkpoint automatic_period must be a positive int, got {!r}".format(period))
+            has_idx, has_mag = "m_codebook" in st, "m_magnitude" in st
+            if has_idx != has_mag:
+                raise ValueError("Gefen checkpoint momentum state is incomplete")
+            moments = [k for k in ("vmean", "v_row", "v_col", "normuon_v") if k in st]
+            if not has_idx and (moments or "step" in st):
+                raise ValueError("Gefen checkpoint carries optimizer state without its quantized momentum")
+            if has_idx:
+                quantised = True
+                if not torch.is_tensor(st["m_codebook"]) or st["m_codebook"].dtype != torch.uint8:
+                    raise ValueError("Gefen checkpoint m_codebook must be a uint8 tensor")
+                non_negative("m_magnitude", st["m_magnitude"])
+                if "step" not in st or "automatic_period" not in st:
+                    raise ValueError("Gefen checkpoint momentum state is missing step or automatic_period")
+            if ("v_row" in st) != ("v_col" in st) or ("v_row" in st) != ("factored_step" in st):
+                raise ValueError("Gefen checkpoint factored second moment is incomplete")
+            if ("normuon_v" in st) != ("normuon_step" in st):
+                raise ValueError("Gefen checkpoint NorMuon state is incomplete")
+            for key in moments:
+                non_negative(key, st[key])
+        if quantised and codebook is not None:
+            cb = codebook
+            ok = (torch.is_tensor(cb) and cb.dim() == 1 and cb.numel() == _cbk.NUM_CODEWORDS and cb.is_floating_point()
+                  and bool(torch.isfinite(cb).all()) and float(cb.min()) >= -1.0 and float(cb.max()) <= 1.0
+                  and bool((cb[1:] >= cb[:-1]).all()))
+            if not ok:
+                raise ValueError("Gefen checkpoint codebook must be a sorted finite tensor of {} values in "
+                                 "[-1, 1]".format(_cbk.NUM_CODEWORDS))
 
     def _restore_into(self, target: "Gefen", sd, step, cb) -> None:
         """Run the whole load on ``target`` (a shadow of ``self`` during staging)."""
@@ -1749,10 +1816,18 @@ class Gefen(torch.optim.Optimizer):
         so a failing load leaves the live optimizer untouched (reference
         ``gefen.py:4818-4856``).
         """
+        # instance load hooks fire once, on this optimizer: pre-hooks before the transaction (they may
+        # replace the state dict), post-hooks only after a successful commit
+        for hook in list(getattr(self, "_optimizer_load_state_dict_pre_hooks", {}).values()):
+            replaced = hook(self, state_dict)
+            if replaced is not None:
+                state_dict = replaced
         state_dict = self._select_rank_local_payload(state_dict)
         sd, step, cb = self._parse_checkpoint_header(state_dict)
         shadow = object.__new__(type(self))
         shadow.__dict__.update(self.__dict__)
+        shadow._optimizer_load_state_dict_pre_hooks = type(self._optimizer_load_state_dict_pre_hooks)()
+        shadow._optimizer_load_state_dict_post_hooks = type(self._optimizer_load_state_dict_post_hooks)()
         shadow.state = defaultdict(dict)
         for p, st in self.state.items():
             shadow.state[p] = dict(st)
@@ -1768,6 +1843,8 @@ class Gefen(torch.optim.Optimizer):
                      "_capt", "_gefen_codebook", "_gefen_codebook_by_device",
                      "_gefen_codebook_lut_by_device", "_gefen_thresholds_by_device", "_param_names", "_synthesized_param_names"):
             setattr(self, attr, getattr(shadow, attr))
+        for hook in list(self._optimizer_load_state_dict_post_hooks.values()):
+            hook(self)
 
     # ------------------------------------------------------------------
     # introspection
