@@ -199,8 +199,15 @@ def _run(args) -> None:
         "config": {"model": args.model, "layers": spec["num_hidden_layers"], "params": n_params,
                    "global_batch": world * B, "seq_len": S,
                    "parallelism": "fsdp{}".format(world) if world > 1 else "single",
-                   "optimizer": "reference gefen.{} lr6e-6 clip1.0".format(type(opt).__name__),
-                   "model_impl": "transformers {} sdpa".format(kind)},
+                   "optimizer": ("Gefen factored_v_2d lr6e-6 clip1.0"
+                                 if getattr(args, "optimizer", "gefen") == "gefen" else
+                                 "GefenMuonHybrid (Muon NS-5 standard, quantized momentum; Gefen backup) "
+                                 "lr6e-6 clip1.0"),
+                   "l2": "working set per step (weights+grads, GBs) exceeds the 126 MB L2"},
+        # how this arm ran the config (kept out of `config`, which both arms share)
+        "impl_config": {"optimizer_class": "reference gefen.{}".format(type(opt).__name__),
+                        "model_impl": "transformers {} sdpa".format(kind),
+                        "sharding": "torch fully_shard" if world > 1 else "none"},
     }
     if rank == 0:
         print(json.dumps(out), flush=True)

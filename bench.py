@@ -55,6 +55,8 @@ def parse_args():
                     help="gradient reduce-scatter: copy engines + local sum, or peer loads in the kernel")
     ap.add_argument("--attn", default="sdpa", choices=["sdpa", "tcgen05"],
                     help="attention: fused library kernel, or tcgen05 GEMMs + own row kernels")
+    ap.add_argument("--gemm", default="tcgen05", choices=["tcgen05", "library"],
+                    help="layer GEMMs: own tcgen05 kernels with fused epilogues (default), or the vendor library")
     ap.add_argument("--trace", action="store_true",
                     help="after the timed loops, print the per-phase device times of one more step (stderr)")
     return ap.parse_args()
@@ -139,6 +141,9 @@ def run_ours(args):
         from gefen_x_b200.ops import model as _model_ops
 
         _model_ops.set_attention_impl(args.attn)
+    from gefen_x_b200.ops import gemm as _gemm_ops
+
+    _gemm_ops.set_backend(args.gemm)
     over = {"n_layers": args.layers} if args.layers else {}
     cfg = get_config(args.model, **over)
     B = args.batch or BATCH_PER_GPU.get(args.model, 1)
@@ -244,9 +249,11 @@ def run_ours(args):
                    "optimizer": ("Gefen factored_v_2d lr6e-6 clip1.0" if args.optimizer == "gefen" else
                                  "GefenMuonHybrid (Muon NS-5 standard, quantized momentum; Gefen backup) "
                                  "lr6e-6 clip1.0"),
-                   "rs_mode": trainer.rs_mode, "ag_gemm": trainer.ag_gemm, "attention": args.attn,
-                   "gather": trainer.gather_mode, "reduce": trainer.reduce_mode, "reduce_ctas": trainer.reduce_ctas,
                    "l2": "working set per step (weights+grads, GBs) exceeds the 126 MB L2"},
+        # how this implementation ran the config (kept out of `config`, which both arms share)
+        "impl_config": {"rs_mode": trainer.rs_mode, "ag_gemm": trainer.ag_gemm, "attention": args.attn,
+                        "gemm": args.gemm, "gather": trainer.gather_mode, "reduce": trainer.reduce_mode,
+                        "reduce_ctas": trainer.reduce_ctas},
     }
     if rank == 0:
         print(json.dumps(out), flush=True)

@@ -25,6 +25,16 @@ SHAPES = [  # (M, N, K, a_t, b_t)
     (4096, 6144, 4096, False, False), (4096, 28672, 4096, False, False), (8192, 8192, 8192, False, False),
     (4096, 4096, 4096, False, True), (4096, 4096, 4096, True, True), (2048, 151936, 2560, False, False),
 ]
+# every product of one Llama-3-8B step at 4096 tokens per GPU: forward (NT), input gradient (NN),
+# weight gradient (TN)
+LLAMA = [
+    (4096, 6144, 4096, False, False), (4096, 4096, 4096, False, False), (4096, 28672, 4096, False, False),
+    (4096, 4096, 14336, False, False), (4096, 128256, 4096, False, False),
+    (4096, 14336, 4096, False, True), (4096, 4096, 28672, False, True), (4096, 4096, 6144, False, True),
+    (4096, 4096, 128256, False, True),
+    (4096, 14336, 4096, True, True), (28672, 4096, 4096, True, True), (6144, 4096, 4096, True, True),
+    (4096, 4096, 4096, True, True), (128256, 4096, 4096, True, True),
+]
 
 
 def peak_tflops() -> float:
@@ -56,15 +66,23 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--no-library", action="store_true", help="skip the vendor-library timing")
+    ap.add_argument("--set", default="models", choices=("models", "llama"), help="shape list")
+    ap.add_argument("--kernel", default="pair", choices=("pair", "single"),
+                    help="pair: CTA-pair kernel where eligible (default); single: single-CTA kernel only")
+    ap.add_argument("--bn", type=int, default=0, help="force the pair kernel's tile width (128 / 256)")
+    ap.add_argument("--sustained", type=float, default=0.0,
+                    help="seconds: time each implementation back to back for this long under the power cap "
+                         "(with the clocks sampled) instead of a short burst")
     args = ap.parse_args()
-    shapes = SHAPES
+    tcgemm.set_pair_kernel(args.kernel == "pair", args.bn)
+    shapes = LLAMA if args.set == "llama" else SHAPES
     if args.only:
         m, n, k = (int(v) for v in args.only.split(","))
         shapes = [(m, n, k, False, False)]
     dev = torch.device("cuda", 0)
     peak = peak_tflops()
     for m, n, k, a_t, b_t in shapes:
-        n_rot = 3
+        n_rot = 3 if (m * k + n * k) * 2 < (1 << 30) else 2
         a = [torch.randn((k, m) if a_t else (m, k), device=dev).bfloat16() for _ in range(n_rot)]
         b = [torch.randn((k, n) if b_t else (n, k), device=dev).bfloat16() for _ in range(n_rot)]
         out = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
@@ -77,10 +95,24 @@ def main():
             y = b[i] if b_t else b[i].t()
             torch.matmul(x, y, out=out)
 
+        if args.sustained > 0:
+            from gefen_x_b200.utils.clocks import ClockSampler
+
+            for name, fn in (("library", lib), ("ours", ours), ("library", lib), ("ours", ours)):
+                burst = time_fn(fn, n_rot, 5, 3)
+                iters = max(10, int(args.sustained * 1e3 / burst))
+                cs = ClockSampler(0, 100)
+                cs.start()
+                t = time_fn(fn, n_rot, iters, 0)
+                clk = cs.stop()
+                print(json.dumps({"M": m, "N": n, "K": k, "a_t": a_t, "b_t": b_t, "impl": name, "sustained_s": args.sustained,
+                                  "ms": t, "tflops": 2.0 * m * n * k / t / 1e9, "burst_ms": burst, "clocks": clk}),
+                      flush=True)
+            continue
         t_ours = time_fn(ours, n_rot, args.iters, args.warmup)
         t_lib = float("nan") if args.no_library else time_fn(lib, n_rot, args.iters, args.warmup)
         flops = 2.0 * m * n * k
-        print(json.dumps({"M": m, "N": n, "K": k, "a_t": a_t, "b_t": b_t,
+        print(json.dumps({"M": m, "N": n, "K": k, "a_t": a_t, "b_t": b_t, "kernel": args.kernel, "bn": args.bn,
                           "ours_ms": t_ours, "ours_tflops": flops / t_ours / 1e9,
                           "ours_fraction_of_measured_peak": flops / t_ours / 1e9 / peak,
                           "library_ms": t_lib, "library_tflops": flops / t_lib / 1e9}), flush=True)

@@ -12,6 +12,10 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "attention.h"
 #include "comm.h"
 #include "fp8_quant.h"
@@ -46,7 +50,8 @@ int64_t desc_size() { return (int64_t)sizeof(gx::TensorDesc); }
 gx::LaunchCommon make_common(const Tensor& descs, const Tensor& tile_start, int64_t n_tensors,
                              int64_t total_tiles, const Tensor& codebook, const Tensor& thr,
                              const Tensor& lut, const c10::optional<Tensor>& gscale, const c10::optional<Tensor>& status,
-                             int64_t sr_seed, bool stochastic, int64_t wait_iters) {
+                             int64_t sr_seed, bool stochastic, int64_t wait_iters,
+                             const c10::optional<Tensor>& sr_seed_dev = c10::nullopt) {
     TORCH_CHECK(descs.is_cuda() && descs.scalar_type() == at::kByte && descs.is_contiguous(),
                 "descs must be a contiguous CUDA uint8 tensor");
     TORCH_CHECK(descs.numel() >= n_tensors * (int64_t)sizeof(gx::TensorDesc), "descs too small");
@@ -80,6 +85,12 @@ gx::LaunchCommon make_common(const Tensor& descs, const Tensor& tile_start, int6
         c.status = status->data_ptr<int>();
     }
     c.sr_seed = (unsigned long long)sr_seed;
+    c.sr_seed_dev = nullptr;
+    if (sr_seed_dev.has_value() && sr_seed_dev->defined()) {
+        TORCH_CHECK(sr_seed_dev->is_cuda() && sr_seed_dev->scalar_type() == at::kDouble && sr_seed_dev->numel() == 1,
+                    "sr_seed_dev must be a CUDA float64 scalar");
+        c.sr_seed_dev = sr_seed_dev->data_ptr<double>();
+    }
     c.stochastic = stochastic ? 1 : 0;
     c.wait_iters = wait_iters;
     return c;
@@ -88,10 +99,10 @@ gx::LaunchCommon make_common(const Tensor& descs, const Tensor& tile_start, int6
 void block_update(const Tensor& descs, const Tensor& tile_start, int64_t n_tensors, int64_t total_tiles,
                   const Tensor& codebook, const Tensor& thr, const Tensor& lut,
                   const c10::optional<Tensor>& gscale, const c10::optional<Tensor>& status,
-                  int64_t dtype, int64_t sr_seed, bool stochastic) {
+                  int64_t dtype, int64_t sr_seed, bool stochastic, const c10::optional<Tensor>& sr_seed_dev) {
     c10::cuda::CUDAGuard guard(descs.device());
     auto c = make_common(descs, tile_start, n_tensors, total_tiles, codebook, thr, lut, gscale, status,
-                         sr_seed, stochastic, 0);
+                         sr_seed, stochastic, 0, sr_seed_dev);
     check(gx::launch_block_update(c, (int)dtype, sm_count(), stream()), "block_update");
 }
 
@@ -99,11 +110,11 @@ void factored_update(const Tensor& descs, const Tensor& tile_start, int64_t n_te
                      int64_t total_tiles, const Tensor& codebook, const Tensor& thr, const Tensor& lut,
                      const c10::optional<Tensor>& gscale, const c10::optional<Tensor>& status,
                      int64_t dtype, int64_t sr_seed, bool stochastic, int64_t wait_iters,
-                     int64_t phases, int64_t epoch, bool fast) {
+                     int64_t phases, int64_t epoch, bool fast, const c10::optional<Tensor>& sr_seed_dev) {
     // phases bit 0: statistics, bit 1: EMA (+ exchange), bit 2: apply + finalize
     c10::cuda::CUDAGuard guard(descs.device());
     auto c = make_common(descs, tile_start, n_tensors, total_tiles, codebook, thr, lut, gscale, status,
-                         sr_seed, stochastic, wait_iters);
+                         sr_seed, stochastic, wait_iters, sr_seed_dev);
     c.epoch = (uint32_t)epoch;
     c.fast = fast ? 1 : 0;
     const int sms = sm_count();
@@ -288,6 +299,85 @@ void gemm_bf16(const Tensor& a, const Tensor& b, Tensor c, const c10::optional<T
                                reinterpret_cast<const __nv_bfloat16*>(b.data_ptr()), ldof(b), bsof(b), p,
                                sm_count(), stream()),
           "gemm_bf16");
+}
+
+// CTA-pair GEMM (gemm_pair_sm100.cu).  2-D bf16 operands: a [M, K] (or [K, M] when a_t), b [N, K]
+// (or [K, N] when b_t).  epi 0: c0 [M, N] = alpha a b + beta d.  epi 1 (SwiGLU forward): b is the
+// stacked [gate | up] weight (2F rows), c0 = the [M, 2F] gate|up buffer, c1 = act [M, F].
+// epi 2 (SwiGLU derivative): a b = d(act) [M, F]; aux = gate|up [M, 2F]; c0 = d(gate|up) [M, 2F].
+void gemm_pair_bf16(const Tensor& a, const Tensor& b, Tensor c0, const c10::optional<Tensor>& c1,
+                    const c10::optional<Tensor>& d, const c10::optional<Tensor>& aux, bool a_t, bool b_t,
+                    double alpha, double beta, int64_t epi, int64_t bn, const c10::optional<Tensor>& status) {
+    c10::cuda::CUDAGuard guard(a.device());
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && c0.is_cuda(), "gemm_pair_bf16: CUDA tensors required");
+    TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 &&
+                    c0.scalar_type() == at::kBFloat16, "gemm_pair_bf16: bf16 tensors required");
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && c0.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 &&
+                    c0.stride(1) == 1, "gemm_pair_bf16: 2-D operands with unit inner stride required");
+    gx::PairParams p{};
+    p.M = (int)(a_t ? a.size(1) : a.size(0));
+    p.K = (int)(a_t ? a.size(0) : a.size(1));
+    const int64_t b_rows = b_t ? b.size(1) : b.size(0);
+    TORCH_CHECK((b_t ? b.size(0) : b.size(1)) == p.K, "gemm_pair_bf16: inner dimensions differ");
+    p.a_mn_major = a_t ? 1 : 0;
+    p.b_mn_major = b_t ? 1 : 0;
+    p.alpha = (float)alpha;
+    p.beta = (float)beta;
+    p.epi = (int)epi;
+    p.bn = (int)bn;
+    p.status = (status.has_value() && status->defined()) ? status->data_ptr<int>() : nullptr;
+    auto bf = [](const Tensor& t) { return reinterpret_cast<__nv_bfloat16*>(t.data_ptr()); };
+    __nv_bfloat16 *C0 = bf(c0), *C1 = nullptr, *C2 = nullptr;
+    long long ld0 = c0.stride(0), ld1 = 0, ld2 = 0;
+    if (epi == gx::kEpiPlain) {
+        p.N = (int)b_rows;
+        TORCH_CHECK(c0.size(0) == p.M && c0.size(1) == p.N, "gemm_pair_bf16: bad output shape");
+        if (d.has_value() && d->defined() && beta != 0.0) {
+            TORCH_CHECK(d->scalar_type() == at::kBFloat16 && d->sizes() == c0.sizes() && d->stride(1) == 1);
+            p.D = bf(*d);
+            p.ldd = d->stride(0);
+        }
+    } else if (epi == gx::kEpiSwigluFwd) {
+        TORCH_CHECK(b_rows % 2 == 0 && c1.has_value() && c1->defined(), "gemm_pair_bf16: SwiGLU needs c1");
+        p.N = p.F = (int)(b_rows / 2);
+        TORCH_CHECK(c0.size(0) == p.M && c0.size(1) == 2 * p.F && c1->size(0) == p.M && c1->size(1) == p.F &&
+                    c1->stride(1) == 1 && c1->scalar_type() == at::kBFloat16 && p.F % 8 == 0);
+        C1 = C0 + p.F;
+        ld1 = ld0;
+        C2 = bf(*c1);
+        ld2 = c1->stride(0);
+    } else {
+        TORCH_CHECK(epi == gx::kEpiSwigluBwd && aux.has_value() && aux->defined(), "gemm_pair_bf16: bad epilogue");
+        p.N = p.F = (int)b_rows;
+        TORCH_CHECK(c0.size(0) == p.M && c0.size(1) == 2 * p.F && aux->sizes() == c0.sizes() &&
+                    aux->stride(1) == 1 && aux->scalar_type() == at::kBFloat16 && p.F % 8 == 0);
+        C1 = C0 + p.F;
+        ld1 = ld0;
+        p.aux = bf(*aux);
+        p.ldaux = aux->stride(0);
+    }
+    TORCH_CHECK(gx::gemm_pair_supported(p.M, p.N, p.K), "gemm_pair_bf16: shape too small for the pair kernel");
+    // workspace of the K-split tail wave: one per (device, stream), since launches that share it must
+    // be ordered; counters start at zero and every launch leaves them zeroed
+    {
+        static std::mutex mu;
+        static std::map<std::pair<int, cudaStream_t>, std::pair<Tensor, Tensor>> pool;
+        std::lock_guard<std::mutex> lock(mu);
+        auto key = std::make_pair((int)a.get_device(), stream());
+        auto it = pool.find(key);
+        if (it == pool.end()) {
+            auto ws = at::empty({gx::kPairWsFloats}, a.options().dtype(at::kFloat));
+            auto cnt = at::zeros({gx::kPairCounters}, a.options().dtype(at::kInt));
+            it = pool.emplace(key, std::make_pair(ws, cnt)).first;
+        }
+        p.ws = it->second.first.data_ptr<float>();
+        p.ws_floats = gx::kPairWsFloats;
+        p.counters = reinterpret_cast<uint32_t*>(it->second.second.data_ptr<int>());
+        p.n_counters = gx::kPairCounters;
+    }
+    check(gx::launch_gemm_pair_bf16(bf(a), a.stride(0), bf(b), b.stride(0), p, C0, ld0, C1, ld1, C2, ld2,
+                                    sm_count(), stream()),
+          "gemm_pair_bf16");
 }
 
 inline void to_ptrs(at::IntArrayRef v, void** out);
@@ -585,10 +675,11 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("desc_size() -> int", &desc_size);
     m.def("rmsnorm_bwd_partials(int rows, int d) -> int", &rmsnorm_bwd_partials);
     m.def("block_update(Tensor descs, Tensor tile_start, int n_tensors, int total_tiles, Tensor codebook, "
-          "Tensor thr, Tensor lut, Tensor? gscale, Tensor? status, int dtype, int sr_seed, bool stochastic) -> ()");
+          "Tensor thr, Tensor lut, Tensor? gscale, Tensor? status, int dtype, int sr_seed, bool stochastic, "
+          "Tensor? sr_seed_dev) -> ()");
     m.def("factored_update(Tensor descs, Tensor tile_start, int n_tensors, int total_tiles, Tensor codebook, "
           "Tensor thr, Tensor lut, Tensor? gscale, Tensor? status, int dtype, int sr_seed, bool stochastic, "
-          "int wait_iters, int phases, int epoch, bool fast) -> ()");
+          "int wait_iters, int phases, int epoch, bool fast, Tensor? sr_seed_dev) -> ()");
     m.def("reduce_sources(Tensor? out, int[] src_ptrs, int numel, float scale, Tensor? partials, "
           "int dtype, int device_index) -> ()", &reduce_sources);
     m.def("clip_coef(Tensor partials, float max_norm, Tensor(a!) coef) -> ()");
@@ -601,6 +692,8 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("period_errors(Tensor flat, Tensor divisors, bool input_is_squared) -> Tensor");
     m.def("gemm_bf16(Tensor a, Tensor b, Tensor(a!) c, Tensor? d, bool a_t, bool b_t, float alpha, "
           "float beta, Tensor? status) -> ()");
+    m.def("gemm_pair_bf16(Tensor a, Tensor b, Tensor(a!) c0, Tensor(b!)? c1, Tensor? d, Tensor? aux, bool a_t, "
+          "bool b_t, float alpha, float beta, int epi, int bn, Tensor? status) -> ()");
     m.def("gemm_ag_bf16(Tensor a, Tensor(a!) bstage, Tensor(b!) c, int[] peer_bases, Tensor segs, "
           "Tensor seg_meta, Tensor tile_order, Tensor(c!) flags, Tensor(d!) count, int epoch, "
           "int count_target, int fetch_ctas, Tensor? status) -> ()");
@@ -640,6 +733,7 @@ TORCH_LIBRARY_IMPL(gefenx, CUDA, m) {
     m.impl("quantize_rows_e4m3", &quantize_rows_e4m3);
     m.impl("period_errors", &period_errors);
     m.impl("gemm_bf16", &gemm_bf16);
+    m.impl("gemm_pair_bf16", &gemm_pair_bf16);
     m.impl("gemm_ag_bf16", &gemm_ag_bf16);
     m.impl("comm_wait", &comm_wait);
     m.impl("comm_gather", &comm_gather);

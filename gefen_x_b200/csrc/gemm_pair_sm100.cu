@@ -1,0 +1,548 @@
+// bf16 GEMM on CTA pairs: tcgen05.mma.cta_group::2 with a 256 x BN accumulator tile per pair.
+//
+//   C = alpha * op(A) * op(B) + beta * D           (fp32 accumulate in TMEM, bf16 out)
+//
+// Two CTAs on neighbouring SMs (a cluster of two) work on one 256 x BN output tile.  Each
+// CTA fetches its own 128 rows of A and its own half of B (BN / 2 rows) with plain per-CTA
+// TMA tile loads -- no load is shared or multicast -- and holds the 128 x BN half of the
+// accumulator that belongs to its rows in its own tensor memory.  The MMA reads the A tile
+// of each CTA once and both halves of B, so the shared-memory traffic per FLOP is two
+// thirds of the single-CTA kernel's (gemm_sm100.cu), which is what that kernel is bound by.
+//
+// Roles per CTA (192 threads, persistent over the tiles of its pair):
+//   warp 0      TMA producer.  Ring of kStages [A 128x64 | B (BN/2)x64] tiles, 128-byte
+//               swizzle.  The "full" barrier of a stage lives in the leader CTA (rank 0)
+//               and counts the bytes of both CTAs' loads (cp.async.bulk.tensor with
+//               .cta_group::2 lets the peer's loads signal it).
+//   warp 1      leader only: one thread issues tcgen05.mma.cta_group::2 (M 256, N BN,
+//               K 16) and commits to the "empty" / "accumulator full" barriers of both
+//               CTAs at once (tcgen05.commit ... multicast::cluster).  In both CTAs this
+//               warp owns the TMEM allocation.
+//   warps 2-5   epilogue.  tcgen05.ld the finished accumulator (two TMEM buffers, so the
+//               next tile's MMAs run meanwhile), apply the epilogue, pack bf16 rows into a
+//               swizzled shared-memory tile and hand it to a TMA store (clipped at the
+//               matrix edge).  Then arrive on the leader's "accumulator empty" barrier.
+//
+// Epilogues: plain (alpha, beta * D: the residual add of the o_proj / down_proj outputs),
+// SwiGLU forward fused into the gate/up projection (the pair's B halves are the gate rows
+// and the up rows of the same columns; writes [gate | up] and silu(gate) * up), and the
+// SwiGLU derivative fused into the down_proj input-gradient product.
+//
+// Tail wave: with T tiles on P pairs the last T mod P tiles would leave most pairs idle, and a
+// narrower tile does not help (256 x 128 tiles need 1.5x the operand bytes per FLOP and run into
+// the L2 -> SM bandwidth).  Instead the tiles of the tail are split along K over the idle pairs;
+// each split parks its fp32 partial in a workspace, and the split that arrives last (an atomic
+// counter per 32-row slice, nobody waits) sums the partials in split order and runs the epilogue.
+//
+// The reference multiplies through cuBLAS (src/gefen/gefen_muon.py:278-287 and its
+// benchmark model benchmarks/training_matrix/tiny_qwen.py:168-181).  Every mbarrier wait
+// is bounded; on time-out the roles drain, TMEM is freed and kWaitTimeout is recorded.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+#include "gemm_sm100.h"
+#include "sm100_ptx.cuh"
+
+namespace gx {
+namespace {
+
+using namespace ptx;
+
+constexpr int kBM = 128;              // accumulator rows held by one CTA (pair tile: 256)
+constexpr int kBK = 64;               // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kUK = 16;
+constexpr int kPairThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kEpiTile = 32 * 128;          // one warp's staging tile: 32 rows x 64 bf16
+
+struct PairShared {
+    uint64_t full[8];
+    uint64_t empty[8];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <int BN> struct PairTile {
+    static constexpr int kHalfN = BN / 2;
+    static constexpr uint32_t kABytes = kBM * kBK * 2;
+    static constexpr uint32_t kBBytes = kHalfN * kBK * 2;
+    static constexpr int kStages = (BN == 256) ? 6 : 8;
+    static constexpr uint32_t kEpiBytes = 4 * 2 * kEpiTile;
+    static constexpr size_t kSmem = (size_t)kStages * (kABytes + kBBytes) + kEpiBytes + sizeof(PairShared) + 1024;
+};
+
+struct PairMaps {
+    CUtensorMap a, b, c0, c1, c2;
+};
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float lo_f(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float hi_f(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// 64 bf16 of one row (32 packed words) -> row `lane` of a swizzled [32 x 128 B] tile
+__device__ __forceinline__ void write_row_swizzled(unsigned char* tile, int lane, const uint32_t (&w)[32]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        uint4* dst = reinterpret_cast<uint4*>(tile + lane * 128 + ((j ^ (lane & 7)) << 4));
+        *dst = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+    }
+}
+
+// 64 bf16 of row `row` starting at column `col` of a row-major matrix (zero outside it)
+__device__ __forceinline__ void load_row64(const __nv_bfloat16* base, long long ld, int row, int col, int rows,
+                                           int cols, bool vec_ok, uint32_t (&w)[32]) {
+    if (row < rows && col + 64 <= cols && vec_ok) {
+        const uint4* src = reinterpret_cast<const uint4*>(base + (long long)row * ld + col);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint4 v = src[j];
+            w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            float a = 0.f, b = 0.f;
+            if (row < rows && col + 2 * j < cols) a = __bfloat162float(base[(long long)row * ld + col + 2 * j]);
+            if (row < rows && col + 2 * j + 1 < cols) b = __bfloat162float(base[(long long)row * ld + col + 2 * j + 1]);
+            w[j] = pack2(a, b);
+        }
+    }
+}
+
+// One unit of work of a pair: a whole tile, or one K-range of a tile of the tail wave.
+struct Work {
+    int tile, kb0, kb1, split, n_split;
+};
+__device__ __forceinline__ bool get_work(const PairParams& p, int it, int pair, int n_pairs, int k_blocks, Work& w) {
+    const int full_iters = p.full_tiles / n_pairs;
+    if (it < full_iters) {
+        w.tile = pair + it * n_pairs;
+        w.kb0 = 0; w.kb1 = k_blocks; w.split = 0; w.n_split = 1;
+        return true;
+    }
+    if (it == full_iters && pair < p.rem_tiles * p.splits) {
+        w.tile = p.full_tiles + pair / p.splits;
+        w.split = pair % p.splits;
+        w.n_split = p.splits;
+        w.kb0 = (int)((long long)w.split * k_blocks / p.splits);
+        w.kb1 = (int)((long long)(w.split + 1) * k_blocks / p.splits);
+        return true;
+    }
+    return false;
+}
+
+template <int BN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
+    using TL = PairTile<BN>;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* smA = base;
+    unsigned char* smB = smA + TL::kStages * TL::kABytes;
+    unsigned char* smE = smB + TL::kStages * TL::kBBytes;
+    PairShared* ss = reinterpret_cast<PairShared*>(smE + TL::kEpiBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    volatile int* abort_flag = &ss->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < TL::kStages; ++i) { mbar_init(&ss->full[i], 1); mbar_init(&ss->empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&ss->tmem_full[i], 1); mbar_init(&ss->tmem_empty[i], 8); }
+        ss->abort_flag = 0;
+        mbar_init_fence();
+        prefetch_tmap(&maps.a);
+        prefetch_tmap(&maps.b);
+        prefetch_tmap(&maps.c0);
+    }
+    if (warp == 1) tmem_alloc<2>(&ss->tmem_base, kTmemCols);
+    tc_fence_before();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = ss->tmem_base;
+
+    const int k_blocks = (p.K + kBK - 1) / kBK;
+    const int pair = (int)(blockIdx.x >> 1);
+    const int n_pairs = (int)(gridDim.x >> 1);
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            Work wk;
+            for (int it = 0; get_work(p, it, pair, n_pairs, k_blocks, wk); ++it) {
+                const int mt = wk.tile % p.m_tiles, nt = wk.tile / p.m_tiles;
+                const int m0 = mt * 256 + (int)rank * kBM;
+                // plain: this CTA's half of the BN columns.  SwiGLU forward: rank 0 fetches the
+                // gate rows, rank 1 the up rows of the same BN / 2 columns.
+                const int nb0 = (EPI == kEpiSwigluFwd) ? (int)rank * p.F + nt * TL::kHalfN
+                                                       : nt * BN + (int)rank * TL::kHalfN;
+                bool ok = true;
+                for (int kb = wk.kb0; kb < wk.kb1; ++kb) {
+                    if (!mbar_wait(&ss->empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+                    if (rank == 0) mbar_expect_tx(&ss->full[stage], 2 * (TL::kABytes + TL::kBBytes));
+                    const uint32_t bar = mapa(smem_u32(&ss->full[stage]), 0);
+                    unsigned char* a_dst = smA + stage * TL::kABytes;
+                    unsigned char* b_dst = smB + stage * TL::kBBytes;
+                    const int k0 = kb * kBK;
+                    if (!p.a_mn_major) {
+                        tma_load_2d_pair(a_dst, &maps.a, bar, k0, m0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < kBM / 64; ++j)
+                            tma_load_2d_pair(a_dst + j * (kBK * 128), &maps.a, bar, m0 + 64 * j, k0);
+                    }
+                    if (!p.b_mn_major) {
+                        tma_load_2d_pair(b_dst, &maps.b, bar, k0, nb0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < TL::kHalfN / 64; ++j)
+                            tma_load_2d_pair(b_dst + j * (kBK * 128), &maps.b, bar, nb0 + 64 * j, k0);
+                    }
+                    if (++stage == TL::kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == 1) {
+        // --------------------------- MMA issuer (leader CTA) ---------------------------
+        if (rank == 0 && lane == 0) {
+            const uint32_t idesc = make_idesc(256, BN, p.a_mn_major != 0, p.b_mn_major != 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            Work wk;
+            for (int it = 0; ok && get_work(p, it, pair, n_pairs, k_blocks, wk); ++it) {
+                if (!mbar_wait(&ss->tmem_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = wk.kb0; kb < wk.kb1; ++kb) {
+                    if (!mbar_wait(&ss->full[stage], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smA + stage * TL::kABytes);
+                    const uint32_t b_addr = smem_u32(smB + stage * TL::kBBytes);
+#pragma unroll
+                    for (int k = 0; k < kBK / kUK; ++k) {
+                        const uint64_t ad = p.a_mn_major ? make_desc(a_addr + k * (kUK * 128), kBK * 128, 1024)
+                                                         : make_desc(a_addr + k * (kUK * 2), 16, 1024);
+                        const uint64_t bd = p.b_mn_major ? make_desc(b_addr + k * (kUK * 128), kBK * 128, 1024)
+                                                         : make_desc(b_addr + k * (kUK * 2), 16, 1024);
+                        umma_bf16<2>(d_tmem, ad, bd, idesc, (kb > wk.kb0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit_pair(&ss->empty[stage], 3);        // both CTAs may refill the stage
+                    if (++stage == TL::kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit_pair(&ss->tmem_full[acc], 3);          // accumulator complete in both CTAs
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        // --------------------------------- epilogue ----------------------------------
+        const int q = warp & 3;                                    // TMEM lane quadrant of this warp
+        unsigned char* my_stage = smE + (warp - 2) * 2 * kEpiTile;
+        const uint32_t leader_empty0 = mapa(smem_u32(&ss->tmem_empty[0]), 0);
+        const uint32_t leader_empty1 = mapa(smem_u32(&ss->tmem_empty[1]), 0);
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        uint32_t unit = 0;                                         // staging tiles handed to TMA so far
+        // pack 64 fp32 values to bf16, stage them and store the [32 x 64] tile at (col, row0)
+        auto emit = [&](const CUtensorMap* map, const uint32_t (&w)[32], int col, int row0) {
+            unsigned char* tile = my_stage + (unit & 1) * kEpiTile;
+            if (lane == 0) bulk_wait_read<1>();                    // the store that last read this buffer is done
+            __syncwarp();
+            write_row_swizzled(tile, lane, w);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(map, tile, col, row0);
+                bulk_commit();
+            }
+            ++unit;
+        };
+        Work wk;
+        for (int it = 0; get_work(p, it, pair, n_pairs, k_blocks, wk); ++it) {
+            const int mt = wk.tile % p.m_tiles, nt = wk.tile / p.m_tiles;
+            const int row0 = mt * 256 + (int)rank * kBM + q * 32;
+            const int row = row0 + lane;
+            if (!mbar_wait(&ss->tmem_full[acc], acc_phase, abort_flag)) break;
+            tc_fence_after();
+            const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+            // ---- K-split tile: park the partial; only the slice's last arriver goes on ----
+            const float* ws_tile = nullptr;                        // set: sum the parked partials
+            if (wk.n_split > 1) {
+                const int slice = ((wk.tile - p.full_tiles) * 2 + (int)rank) * 4 + q;
+                float* ws_slice = p.ws + (size_t)slice * wk.n_split * (BN * 32);
+                float* mine = ws_slice + (size_t)wk.split * (BN * 32) + lane;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(t_acc + (uint32_t)c, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) __stcg(mine + (c + e) * 32, __uint_as_float(r[e]));
+                }
+                __threadfence();
+                __syncwarp();
+                uint32_t arrived = 0;
+                if (lane == 0) arrived = atomicAdd(p.counters + slice, 1u);
+                arrived = __shfl_sync(0xffffffffu, arrived, 0);
+                if (arrived + 1u == (uint32_t)wk.n_split) {
+                    __threadfence();
+                    if (lane == 0) p.counters[slice] = 0;          // ready for the next launch
+                    ws_tile = ws_slice + lane;
+                } else {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                    continue;
+                }
+            }
+            // 64 accumulator columns starting at `c`: from tensor memory, or the partials in split order
+            auto load_acc64 = [&](int c, uint32_t (&r)[64]) {
+                if (ws_tile == nullptr) {
+                    tmem_ld_32x32b_x32(t_acc + (uint32_t)c, r);
+                    tmem_ld_32x32b_x32(t_acc + (uint32_t)(c + 32), r + 32);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 64; ++e) r[e] = __float_as_uint(__ldcg(ws_tile + (c + e) * 32));
+                    for (int sp = 1; sp < wk.n_split; ++sp) {
+                        const float* part = ws_tile + (size_t)sp * (BN * 32);
+#pragma unroll
+                        for (int e = 0; e < 64; ++e)
+                            r[e] = __float_as_uint(__uint_as_float(r[e]) + __ldcg(part + (c + e) * 32));
+                    }
+                }
+            };
+            if constexpr (EPI == kEpiSwigluFwd) {
+                // accumulator columns [0, BN/2) = gate, [BN/2, BN) = up of output columns nt * BN/2 + ...
+#pragma unroll 1
+                for (int c = 0; c < TL::kHalfN; c += 64) {
+                    uint32_t r[64], g[32], u[32];
+                    load_acc64(c, r);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        g[j] = pack2(__uint_as_float(r[2 * j]) * p.alpha, __uint_as_float(r[2 * j + 1]) * p.alpha);
+                    load_acc64(TL::kHalfN + c, r);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        u[j] = pack2(__uint_as_float(r[2 * j]) * p.alpha, __uint_as_float(r[2 * j + 1]) * p.alpha);
+                    const int col = nt * TL::kHalfN + c;
+                    emit(&maps.c0, g, col, row0);
+                    emit(&maps.c1, u, col, row0);
+                    // silu(gate) * up from the rounded values, as the unfused kernel reads them back
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float g0 = lo_f(g[j]), g1 = hi_f(g[j]);
+                        const float a0 = g0 / (1.f + __expf(-g0)) * lo_f(u[j]);
+                        const float a1 = g1 / (1.f + __expf(-g1)) * hi_f(u[j]);
+                        g[j] = pack2(a0, a1);
+                    }
+                    emit(&maps.c2, g, col, row0);
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 64) {
+                    uint32_t r[64], w[32];
+                    load_acc64(c, r);
+                    const int col = nt * BN + c;
+                    if constexpr (EPI == kEpiPlain) {
+                        if (p.D) {
+                            uint32_t d[32];
+                            load_row64(p.D, p.ldd, row, col, p.M, p.N, p.d_vec_ok != 0, d);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                w[j] = pack2(__uint_as_float(r[2 * j]) * p.alpha + p.beta * lo_f(d[j]),
+                                             __uint_as_float(r[2 * j + 1]) * p.alpha + p.beta * hi_f(d[j]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                w[j] = pack2(__uint_as_float(r[2 * j]) * p.alpha, __uint_as_float(r[2 * j + 1]) * p.alpha);
+                        }
+                        emit(&maps.c0, w, col, row0);
+                    } else {
+                        // SwiGLU derivative: the accumulator is d(act); aux = [gate | up] of the forward pass
+                        uint32_t g[32], u[32];
+                        load_row64(p.aux, p.ldaux, row, col, p.M, p.F, p.d_vec_ok != 0, g);
+                        load_row64(p.aux + p.F, p.ldaux, row, col, p.M, p.F, p.d_vec_ok != 0, u);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            // d(act) rounded to bf16 first, as the unfused path stores it
+                            const uint32_t dzp = pack2(__uint_as_float(r[2 * j]) * p.alpha,
+                                                       __uint_as_float(r[2 * j + 1]) * p.alpha);
+                            float dg[2], du[2];
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                const float gv = h ? hi_f(g[j]) : lo_f(g[j]);
+                                const float uv = h ? hi_f(u[j]) : lo_f(u[j]);
+                                const float dz = h ? hi_f(dzp) : lo_f(dzp);
+                                const float sg = 1.f / (1.f + __expf(-gv));
+                                dg[h] = dz * uv * sg * (1.f + gv * (1.f - sg));
+                                du[h] = dz * (gv * sg);
+                            }
+                            w[j] = pack2(dg[0], dg[1]);
+                            u[j] = pack2(du[0], du[1]);
+                        }
+                        emit(&maps.c0, w, col, row0);
+                        emit(&maps.c1, u, col, row0);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+        if (lane == 0) bulk_wait<0>();                             // all stores of this warp have landed
+    }
+
+    // teardown: both CTAs meet (nobody may leave while the peer can still signal its barriers or
+    // read its operand tiles), then the allocating warps free the tensor memory
+    tc_fence_before();
+    cluster_sync_all();
+    if (threadIdx.x == 0 && ss->abort_flag && p.status) atomicExch(p.status, (int)kWaitTimeout);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<2>(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn pair_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// row-major [outer, inner] bf16 matrix with leading dimension ld (elements)
+bool map2d(CUtensorMap* map, const __nv_bfloat16* base, long long inner, long long outer, long long ld,
+           int box_inner, int box_outer) {
+    EncodeTiledFn fn = pair_encode_fn();
+    if (!fn || inner <= 0 || outer <= 0) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+template <int BN, int EPI>
+cudaError_t launch_pair(const PairMaps& maps, PairParams p, int sm_count, cudaStream_t st) {
+    constexpr size_t smem = PairTile<BN>::kSmem;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    const int n_cols = (EPI == kEpiSwigluFwd) ? PairTile<BN>::kHalfN : BN;   // output columns per tile
+    p.m_tiles = (p.M + 255) / 256;
+    p.n_tiles = (p.N + n_cols - 1) / n_cols;
+    p.total_tiles = p.m_tiles * p.n_tiles;
+    const int max_pairs = sm_count / 2 > 0 ? sm_count / 2 : 1;
+    const int k_blocks = (p.K + kBK - 1) / kBK;
+    int pairs = max_pairs;
+    p.full_tiles = (p.total_tiles / max_pairs) * max_pairs;
+    p.rem_tiles = p.total_tiles - p.full_tiles;
+    p.splits = 1;
+    if (p.rem_tiles > 0 && p.ws != nullptr && p.counters != nullptr) {
+        int sp = max_pairs / p.rem_tiles;                    // idle pairs per tail tile
+        if (sp > kMaxSplits) sp = kMaxSplits;
+        if (sp > k_blocks / 4) sp = k_blocks / 4;            // at least four k-blocks per split
+        if (sp > 1 && (long long)p.rem_tiles * sp * 2 * 4 * BN * 32 <= p.ws_floats &&
+            p.rem_tiles * 2 * 4 <= p.n_counters)
+            p.splits = sp;
+    }
+    if (p.full_tiles == 0) pairs = p.rem_tiles * p.splits;   // fewer tiles than pairs: one unit each
+    gemm_pair_kernel<BN, EPI><<<2 * pairs, kPairThreads, smem, st>>>(maps, p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool gemm_pair_supported(int M, int N, int K) { return M >= 129 && N >= 64 && K >= 64; }
+
+int gemm_pair_pick_bn(int M, int N, int sm_count) {
+    // 256 x 128 tiles fetch 1.5x the operand bytes per FLOP of 256 x 256 tiles and are bound by the
+    // L2 -> SM bandwidth (measured: 0.85 against 1.5 PFLOP/s on 4096^3), so the narrow tile only
+    // serves narrow outputs; the tail wave is balanced by the K-split instead
+    (void)M; (void)sm_count;
+    return N <= 128 ? 128 : 256;
+}
+
+cudaError_t launch_gemm_pair_bf16(const __nv_bfloat16* A, long long lda, const __nv_bfloat16* B, long long ldb,
+                                  PairParams p, __nv_bfloat16* C0, long long ldc0, __nv_bfloat16* C1,
+                                  long long ldc1, __nv_bfloat16* C2, long long ldc2, int sm_count,
+                                  cudaStream_t st) {
+    if (p.M <= 0 || p.N <= 0 || p.K <= 0) return cudaSuccess;
+    if ((lda % 8) || (ldb % 8) || (ldc0 % 8) || !aligned16(A) || !aligned16(B) || !aligned16(C0))
+        return cudaErrorInvalidValue;
+    if (p.epi < kEpiPlain || p.epi > kEpiSwigluBwd) return cudaErrorInvalidValue;
+    const int bn = p.epi == kEpiSwigluFwd ? 256 : (p.bn ? p.bn : gemm_pair_pick_bn(p.M, p.N, sm_count));
+    if (bn != 128 && bn != 256) return cudaErrorInvalidValue;
+    PairMaps maps;
+    bool ok = p.a_mn_major ? map2d(&maps.a, A, p.M, p.K, lda, 64, kBK) : map2d(&maps.a, A, p.K, p.M, lda, kBK, kBM);
+    const long long b_rows = p.epi == kEpiSwigluFwd ? 2ll * p.F : p.N;
+    ok = ok && (p.b_mn_major ? map2d(&maps.b, B, b_rows, p.K, ldb, 64, kBK)
+                             : map2d(&maps.b, B, p.K, b_rows, ldb, kBK, bn / 2));
+    // outputs: every map spans exactly the columns its tiles may touch, so the store clips there
+    ok = ok && map2d(&maps.c0, C0, p.N, p.M, ldc0, 64, 32);
+    maps.c1 = maps.c0;
+    maps.c2 = maps.c0;
+    if (p.epi != kEpiPlain) {
+        if (!C1 || (ldc1 % 8) || !aligned16(C1)) return cudaErrorInvalidValue;
+        ok = ok && map2d(&maps.c1, C1, p.N, p.M, ldc1, 64, 32);
+    }
+    if (p.epi == kEpiSwigluFwd) {
+        if (!C2 || (ldc2 % 8) || !aligned16(C2) || p.b_mn_major || p.F != p.N) return cudaErrorInvalidValue;
+        ok = ok && map2d(&maps.c2, C2, p.N, p.M, ldc2, 64, 32);
+    }
+    if (p.epi == kEpiSwigluBwd) {
+        if (!p.aux || p.F != p.N) return cudaErrorInvalidValue;
+        p.d_vec_ok = (p.ldaux % 8 == 0) && aligned16(p.aux) && (p.F % 8 == 0);
+    } else {
+        p.d_vec_ok = !p.D || ((p.ldd % 8 == 0) && aligned16(p.D));
+    }
+    if (!ok) return cudaErrorInvalidValue;
+    if (p.epi == kEpiSwigluFwd) return launch_pair<256, kEpiSwigluFwd>(maps, p, sm_count, st);
+    if (p.epi == kEpiSwigluBwd)
+        return bn == 256 ? launch_pair<256, kEpiSwigluBwd>(maps, p, sm_count, st)
+                         : launch_pair<128, kEpiSwigluBwd>(maps, p, sm_count, st);
+    return bn == 256 ? launch_pair<256, kEpiPlain>(maps, p, sm_count, st)
+                     : launch_pair<128, kEpiPlain>(maps, p, sm_count, st);
+}
+
+}  // namespace gx

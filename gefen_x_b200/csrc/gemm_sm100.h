@@ -50,6 +50,52 @@ cudaError_t launch_gemm_bf16(const __nv_bfloat16* A, long long lda, long long ba
                              const __nv_bfloat16* B, long long ldb, long long batch_stride_b,
                              GemmParams p, int sm_count, cudaStream_t st);
 
+// ---- CTA-pair GEMM (gemm_pair_sm100.cu): tcgen05.mma.cta_group::2, 256 x BN tile per pair ----
+enum PairEpilogue : int {
+    kEpiPlain = 0,        // C0 = alpha * A B + beta * D
+    kEpiSwigluFwd = 1,    // B = [gate rows | up rows] (2F x K): C0 = gate, C1 = up, C2 = silu(gate) * up
+    kEpiSwigluBwd = 2,    // A B = d(act); aux = [gate | up]: C0 = d(gate), C1 = d(up)
+};
+
+struct PairParams {
+    int M, N, K;                    // N = columns of one output matrix (F for the SwiGLU epilogues)
+    int a_mn_major, b_mn_major;     // 0: operand stored [rows, K]; 1: stored [K, rows]
+    float alpha, beta;
+    const __nv_bfloat16* D;         // optional addend of the plain epilogue (may be null)
+    long long ldd;
+    int epi;                        // PairEpilogue
+    int F;                          // SwiGLU epilogues: width of gate (= N)
+    const __nv_bfloat16* aux;       // kEpiSwigluBwd: [M, 2F] gate | up
+    long long ldaux;
+    int bn;                         // 0: choose; 128 / 256: force the tile width
+    int* status;                    // device status word, may be null
+    // K-split of the tail wave (optional): fp32 workspace and zero-initialised arrival counters that
+    // the kernel leaves zeroed; launches sharing them must be ordered on one stream
+    float* ws;
+    long long ws_floats;
+    uint32_t* counters;
+    int n_counters;
+    int m_tiles, n_tiles, total_tiles;
+    int full_tiles, rem_tiles, splits;     // set by the launcher
+    int d_vec_ok;
+};
+constexpr int kMaxSplits = 8;
+// workspace that always suffices: half of the pairs' tiles, 256 x 256 fp32 each, and their counters
+constexpr long long kPairWsFloats = 74ll * 256 * 256;
+constexpr int kPairCounters = 74 * 8;
+
+// True when the pair kernel can run the product (otherwise use launch_gemm_bf16).
+bool gemm_pair_supported(int M, int N, int K);
+// Tile width (128 / 256) that wastes the least of the last wave of pair tiles.
+int gemm_pair_pick_bn(int M, int N, int sm_count);
+
+// C0 (and C1, C2 for the SwiGLU epilogues; otherwise null) are row-major with leading dimensions
+// ldc*.  Leading dimensions must be multiples of 8 elements and base pointers 16-byte aligned.
+cudaError_t launch_gemm_pair_bf16(const __nv_bfloat16* A, long long lda, const __nv_bfloat16* B, long long ldb,
+                                  PairParams p, __nv_bfloat16* C0, long long ldc0, __nv_bfloat16* C1,
+                                  long long ldc1, __nv_bfloat16* C2, long long ldc2, int sm_count,
+                                  cudaStream_t st);
+
 // Causal attention forward (flash form) on heads-first operands: q [batch, rows, hd] with
 // rows = group * seq (the query heads of one KV head stacked along the rows), k / v
 // [batch, seq, hd], out [batch, rows, hd], lse [batch * rows].  hd in {64, 128}, seq % 128 == 0.

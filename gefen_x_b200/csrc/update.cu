@@ -192,7 +192,11 @@ __device__ __forceinline__ float apply_one(float pf, float q, float step, float 
 template <bool FAST = false>
 __device__ __forceinline__ int quantise(float n, const Smem& s, const LaunchCommon& c, long long elem) {
     if constexpr (FAST) return nearest_index(n, s.q);
-    if (c.stochastic) return stochastic_index(n, s.q, sr_uniform(c.sr_seed, (uint64_t)elem));
+    if (c.stochastic) {
+        const unsigned long long seed =
+            c.sr_seed_dev ? c.sr_seed + (unsigned long long)__ldg(c.sr_seed_dev) : c.sr_seed;
+        return stochastic_index(n, s.q, sr_uniform(seed, (uint64_t)elem));
+    }
     return nearest_index(n, s.q);
 }
 

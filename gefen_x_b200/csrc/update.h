@@ -64,6 +64,8 @@ struct LaunchCommon {
     const float* gscale;              // optional device scalar multiplying every gradient
     int* status;                      // device status word (Status enum), may be null
     unsigned long long sr_seed;
+    const double* sr_seed_dev;        // optional device counter added to sr_seed (CUDA-graph replays draw
+                                      // fresh rounding noise because the counter advances on the device)
     int stochastic;
     long long wait_iters;             // bound of every peer wait
     uint32_t epoch;                   // value the exchange flags must reach in this launch

@@ -154,11 +154,10 @@ def layer_forward(cfg: ModelConfig, w: Dict[str, torch.Tensor], x: torch.Tensor,
         q, k = qr, kr
     a, actx = M.attention_fwd(q, k, v)
     a2d = a.reshape(T, cfg.q_dim)
-    x2 = x2d + G.mm_nt(a2d, w["self_attn.o_proj.weight"])
+    x2 = G.mm_nt_add(a2d, w["self_attn.o_proj.weight"], x2d)       # residual add in the epilogue
     h2, rstd2 = M.rmsnorm_fwd(x2, w["post_attention_layernorm.weight"], cfg.rms_eps)
-    gu = G.mm_nt(h2, w["wgu"])                                      # [T, 2F]
-    act = M.swiglu_fwd(gu)
-    y = x2 + G.mm_nt(act, w["mlp.down_proj.weight"])
+    gu, act = G.mlp_gate_up(h2, w["wgu"])                           # [T, 2F], silu(gate) * up fused
+    y = G.mm_nt_add(act, w["mlp.down_proj.weight"], x2)
     saved = None
     if save:
         saved = dict(x=x2d, rstd1=rstd1, h1=h1, qn=qn_ctx, actx=actx, a=a2d, x2=x2, rstd2=rstd2,
@@ -189,8 +188,7 @@ def layer_backward(cfg: ModelConfig, w: Dict[str, torch.Tensor], gw: Dict[str, t
 
     # MLP
     wgrad("mlp.down_proj.weight", dy2, saved["act"])
-    dact = G.mm_nn(dy2, w["mlp.down_proj.weight"])
-    dgu = M.swiglu_bwd(saved["gu"], dact)
+    dgu = G.mlp_down_dgrad(dy2, w["mlp.down_proj.weight"], saved["gu"])   # SwiGLU derivative fused
     wgrad("wgu", dgu, saved["h2"])
     dh2 = G.mm_nn(dgu, w["wgu"])
     dx2n, dw = M.rmsnorm_bwd(dh2, saved["x2"], w["post_attention_layernorm.weight"], saved["rstd2"])

@@ -1,22 +1,42 @@
-"""tcgen05 / TMEM bf16 GEMM (``csrc/gemm_sm100.cu``).
+"""tcgen05 / TMEM bf16 GEMMs (``csrc/gemm_pair_sm100.cu``, ``csrc/gemm_sm100.cu``).
 
 ``gemm(a, b, ...)`` computes ``alpha * op(a) @ op(b)^T-or-not + beta * d`` on the
 5th-generation tensor cores with TMA-fed operands.  Layout convention: with
 ``a_t=False`` the first operand is ``[M, K]`` (K contiguous), with ``a_t=True`` it
 is stored ``[K, M]``; with ``b_t=False`` the second operand is ``[N, K]`` (so the
 product is ``a @ b.T``), with ``b_t=True`` it is stored ``[K, N]`` (``a @ b``).
-3-D inputs are batches.  The reference uses cuBLAS through torch for the same
-products (reference ``src/gefen/gefen_muon.py:278-287``, ``:353-393``).
+3-D inputs are batches.
+
+Two kernels serve it.  Large 2-D products run on CTA pairs
+(``tcgen05.mma.cta_group::2``, a 256 x 256 or 256 x 128 tile per pair, TMA-store
+epilogue); batches and small products run on the single-CTA kernel.  The pair
+kernel also carries the fused epilogues of the decoder's MLP:
+:func:`gemm_swiglu_fwd` (gate/up projection + ``silu(gate) * up``) and
+:func:`gemm_swiglu_bwd` (input gradient of ``down_proj`` + the SwiGLU derivative).
+
+The reference uses cuBLAS through torch for the same products (reference
+``src/gefen/gefen_muon.py:278-287``, ``:353-393``;
+``benchmarks/training_matrix/tiny_qwen.py:168-181``).
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
 from ._ext import available, ops
 
 _status = {}
+_PAIR = True            # route eligible 2-D products to the CTA-pair kernel
+_FORCE_BN = 0           # 0: choose per shape; 128 / 256: force the pair tile width (benchmarks)
+
+
+def set_pair_kernel(enabled: bool, bn: int = 0) -> None:
+    """Switch the CTA-pair kernel on or off (off: every product uses the single-CTA kernel)."""
+    global _PAIR, _FORCE_BN
+    if bn not in (0, 128, 256):
+        raise ValueError("bn must be 0, 128 or 256")
+    _PAIR, _FORCE_BN = bool(enabled), int(bn)
 
 
 def status_word(device: torch.device) -> torch.Tensor:
@@ -43,19 +63,58 @@ def supports_nt(a: torch.Tensor, b: torch.Tensor) -> bool:
     return supports(a, b) and a.shape[-1] == b.shape[-1]
 
 
+def pair_eligible(m: int, n: int, k: int) -> bool:
+    """Shapes the CTA-pair kernel takes (the rest goes to the single-CTA kernel)."""
+    return _PAIR and m >= 129 and n >= 128 and k >= 64 and n % 8 == 0
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = False,
          alpha: float = 1.0, beta: float = 0.0, d: Optional[torch.Tensor] = None,
          out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """See the module docstring for the layout convention."""
     m = a.shape[-1] if a_t else a.shape[-2]
     n = b.shape[-1] if b_t else b.shape[-2]
+    k = a.shape[-2] if a_t else a.shape[-1]
     if out is None:
         out = torch.empty(*a.shape[:-2], m, n, dtype=torch.bfloat16, device=a.device)
-    ops().gemm_bf16(a, b, out, d if beta != 0.0 else None, bool(a_t), bool(b_t), float(alpha),
-                    float(beta), status_word(a.device))
+    dd = d if beta != 0.0 else None
+    if a.dim() == 2 and pair_eligible(m, n, k) and _ok_operand(out) and (dd is None or _ok_operand(dd)):
+        ops().gemm_pair_bf16(a, b, out, None, dd, None, bool(a_t), bool(b_t), float(alpha), float(beta), 0,
+                             _FORCE_BN, status_word(a.device))
+        return out
+    ops().gemm_bf16(a, b, out, dd, bool(a_t), bool(b_t), float(alpha), float(beta), status_word(a.device))
     return out
 
 
 def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``a [M, K] @ b [N, K]^T``."""
     return gemm(a, b, out=out)
+
+
+def swiglu_eligible(m: int, f: int, k: int) -> bool:
+    return _PAIR and m >= 129 and f >= 128 and f % 8 == 0 and k >= 64
+
+
+def gemm_swiglu_fwd(x: torch.Tensor, w_gate_up: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``gu = x @ w_gate_up^T`` and ``act = silu(gu[:, :F]) * gu[:, F:]`` in one launch.
+
+    ``w_gate_up`` is the stacked ``[2F, K]`` weight (gate rows first).  Returns ``(gu [M, 2F],
+    act [M, F])``; ``act`` is computed from the bf16-rounded ``gu``, exactly as the separate
+    activation kernel would.
+    """
+    m, f = x.shape[0], w_gate_up.shape[0] // 2
+    gu = torch.empty(m, 2 * f, dtype=torch.bfloat16, device=x.device)
+    act = torch.empty(m, f, dtype=torch.bfloat16, device=x.device)
+    ops().gemm_pair_bf16(x, w_gate_up, gu, act, None, None, False, False, 1.0, 0.0, 1, 0, status_word(x.device))
+    return gu, act
+
+
+def gemm_swiglu_bwd(dy: torch.Tensor, w_down: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
+    """``d(gate|up)`` from ``d(act) = dy @ w_down`` without storing ``d(act)``.
+
+    ``w_down`` is ``[H, F]`` (the ``down_proj`` weight), ``gate_up`` the forward's ``[M, 2F]``.
+    """
+    dgu = torch.empty_like(gate_up)
+    ops().gemm_pair_bf16(dy, w_down, dgu, None, None, gate_up, False, True, 1.0, 0.0, 2, _FORCE_BN,
+                         status_word(dy.device))
+    return dgu

@@ -200,6 +200,39 @@ def _pick_tcols(chunks: int) -> int:
     return best
 
 
+def check_state_shapes(st: Dict[str, Any], shape: Tuple[int, ...], period: int, *, factored: bool,
+                       emit: bool = False, what: str = "Gefen state") -> None:
+    """The kernels index the state through raw pointers with sizes derived from the parameter: a state
+    tensor of another size would be read or written out of bounds.  Raises ``ValueError`` unless
+    ``m_codebook`` is a contiguous ``[numel / P, P]`` uint8 tensor, ``m_magnitude`` (and ``vmean``) hold
+    ``numel / P`` values and ``v_row`` / ``v_col`` match the parameter's rows / columns."""
+    numel = 1
+    for d in shape:
+        numel *= int(d)
+    if not isinstance(period, int) or period < 1 or numel % period:
+        raise ValueError("{}: period {!r} does not divide {} elements".format(what, period, numel))
+    nb = numel // period
+    idx, mag = st.get("m_codebook"), st.get("m_magnitude")
+    if not torch.is_tensor(idx) or tuple(idx.shape) != (nb, period) or not idx.is_contiguous():
+        raise ValueError("{}: m_codebook must be a contiguous [{}, {}] tensor, got {}".format(
+            what, nb, period, tuple(idx.shape) if torch.is_tensor(idx) else type(idx)))
+    if not torch.is_tensor(mag) or mag.numel() != nb or not mag.is_contiguous():
+        raise ValueError("{}: m_magnitude must hold {} contiguous values".format(what, nb))
+    if emit:
+        return
+    if factored:
+        if len(shape) != 2:
+            raise ValueError("{}: the factored second moment needs a 2-D parameter".format(what))
+        vr, vc = st.get("v_row"), st.get("v_col")
+        if not torch.is_tensor(vr) or vr.numel() != shape[0] or not vr.is_contiguous() or \
+                not torch.is_tensor(vc) or vc.numel() != shape[1] or not vc.is_contiguous():
+            raise ValueError("{}: v_row / v_col must hold {} / {} contiguous values".format(what, shape[0], shape[1]))
+    else:
+        vm = st.get("vmean")
+        if not torch.is_tensor(vm) or vm.numel() != nb or not vm.is_contiguous():
+            raise ValueError("{}: vmean must hold {} contiguous values".format(what, nb))
+
+
 class Plan:
     """Device tables for one (device, kind, dtype) group of tensors."""
 
@@ -254,6 +287,8 @@ class Plan:
             d = TensorDesc.from_buffer(buf, i * stride)
             p = it.p
             st = it.state
+            check_state_shapes(st, tuple(p.shape), it.period, emit=bool(it.emit),
+                               factored=(kind == "factored" and not it.row_only and not it.emit))
             d.p = p.data_ptr()
             if isinstance(it.grad, PeerGrad):
                 srcs = list(it.grad.ptrs)
@@ -370,13 +405,17 @@ class Plan:
             st = it.state
             sig.append((it.p.data_ptr(), gp, st["m_codebook"].data_ptr(), st["m_magnitude"].data_ptr(),
                         (st["v_row"] if "v_row" in st else st.get("vmean", st["m_magnitude"])).data_ptr(),
+                        st["v_col"].data_ptr() if "v_col" in st else 0,
                         it.period, it.scal_ptr, tuple(it.p.shape), it.beta1, it.beta2, it.eps, it.row_only, it.emit))
         return tuple(sig)
 
     def run(self, items: List[Item], codebook: torch.Tensor, thr: torch.Tensor, lut: torch.Tensor, *,
             gscale: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
             sr_seed: Optional[int] = None, wait_iters: int = DEFAULT_WAIT_ITERS,
-            phases: int = 7, epoch: int = 0) -> None:
+            phases: int = 7, epoch: int = 0, sr_seed_dev: Optional[torch.Tensor] = None) -> None:
+        """``sr_seed`` switches stochastic rounding on; ``sr_seed_dev`` (a float64 device scalar) is
+        added to it inside the kernels, so that CUDA-graph replays, which re-run the launch with
+        the same arguments, still draw fresh noise as long as the counter advances on the device."""
         if self.uses_host_scalars and (phases & 1 or self.kind == "block"):
             # A fresh pageable tensor per step: the runtime stages it before the call
             # returns, so the host may run ahead of the device without racing on it.
@@ -387,10 +426,10 @@ class Plan:
         if self.kind == "factored":
             ops().factored_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, thr, lut,
                                   gscale, status, code, seed, sr_seed is not None, int(wait_iters),
-                                  int(phases), int(epoch) & 0x7FFFFFFF, bool(self.fast))
+                                  int(phases), int(epoch) & 0x7FFFFFFF, bool(self.fast), sr_seed_dev)
         else:
             ops().block_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, thr, lut,
-                               gscale, status, code, seed, sr_seed is not None)
+                               gscale, status, code, seed, sr_seed is not None, sr_seed_dev)
 
 
 class PlanCache:

@@ -356,7 +356,6 @@ class Gefen(torch.optim.Optimizer):
         self._gefen_thresholds_by_device: Dict[torch.device, torch.Tensor] = {}
         self._gefen_global_step = 0
         self._gefen_global_step_by_device: Dict[torch.device, torch.Tensor] = {}
-        self._sr_seed_by_device: Dict[torch.device, torch.Tensor] = {}
         self._capt: Dict[torch.device, Dict[str, Any]] = {}
         self._pending_grad_scale: Optional[float] = None
         # Optional hooks installed by the sharded runtime (parallel.fsdp):
@@ -885,6 +884,21 @@ class Gefen(torch.optim.Optimizer):
     def _kernel_rng_seed(self) -> int:
         return int(self._gefen_global_step)
 
+    def _kernel_rng_seed_on(self, device):
+        """``(host seed, device seed)`` of the stochastic-rounding hash for a launch on ``device``.
+
+        Eager steps pass the global step by value.  A capturable optimizer passes 0 and the
+        device-resident global-step counter instead: a captured launch replays with the same
+        arguments, so a host value would freeze the noise into a per-element bias, while the
+        device counter advances inside the captured region (reference ``gefen.py:1770-1890``
+        keeps a device seed per device for the same reason).  Both give the same seed at the
+        same step."""
+        if not self._stochastic_round:
+            return None, None
+        if self.capturable and device.type == "cuda":
+            return 0, self._ensure_global_step_device(device)
+        return self._kernel_rng_seed(), None
+
     # ------------------------------------------------------------------
     # per-parameter state
     # ------------------------------------------------------------------
@@ -1051,9 +1065,9 @@ class Gefen(torch.optim.Optimizer):
             lut = self._gefen_codebook_lut_on(dev)
             gscale = self._grad_scale_tensor(dev)
             plan = self._plan_cache.get(kind, items)
+            sr_seed, sr_dev = self._kernel_rng_seed_on(dev)
             plan.run(items, cb, self._gefen_thresholds_on(dev), lut, gscale=gscale, status=self._status_word(dev),
-                     sr_seed=self._kernel_rng_seed() if self._stochastic_round else None,
-                     epoch=self._exchange_epoch)
+                     sr_seed=sr_seed, sr_seed_dev=sr_dev, epoch=self._exchange_epoch)
         for dst, work in self._fused_copyback:
             dst.copy_(work)
 
@@ -1106,6 +1120,14 @@ class Gefen(torch.optim.Optimizer):
         if n != f["n_params"]:
             self._fast = None
             return False
+        # The plans hold raw device addresses of the parameters and of their state: every one of
+        # them, and every hyper-parameter baked into the descriptors, must still be what the
+        # optimizer holds (parameters re-assigned with ``p.data = ...``, state paged to the host by
+        # an offload wrapper or reloaded, betas / eps edited in a group all invalidate the plan).
+        for (kind, dev, _dt), plan, items, metas in f["plans"]:
+            if not self._fast_plan_still_valid(plan, items, metas, dev):
+                self._fast = None
+                return False
         for (kind, dev, _dt), plan, items, metas in f["plans"]:
             for it, (p, group, state, vkey, factored) in zip(items, metas):
                 state["step"] += 1
@@ -1120,8 +1142,29 @@ class Gefen(torch.optim.Optimizer):
                      self._gefen_codebook_lut_on(dev),
                      gscale=self._grad_scale_tensor(dev), status=self._status_word(dev),
                      sr_seed=self._kernel_rng_seed() if self._stochastic_round else None,
-                     epoch=self._exchange_epoch)
+                     epoch=self._exchange_epoch)      # never capturable here: host seed
         return True
+
+    @staticmethod
+    def _fast_plan_still_valid(plan, items, metas, dev) -> bool:
+        """Whether the live tensors behind a remembered plan are exactly those it was built on."""
+        from ..ops import update as _u
+
+        live = []
+        for it, (p, group, state, _vkey, _factored) in zip(items, metas):
+            p_local = _local(p)
+            if p_local.device != dev or not p_local.is_contiguous() or p_local.shape != it.p.shape:
+                return False
+            for k in ("m_codebook", "m_magnitude", "vmean", "v_row", "v_col"):
+                t = state.get(k)
+                if t is not None and (not torch.is_tensor(t) or t.device != dev):
+                    return False
+            if "m_codebook" not in state or "m_magnitude" not in state:
+                return False
+            live.append(_u.Item(p=p_local, grad=it.grad, state=state, period=state.get("automatic_period", it.period),
+                                beta1=group["beta1"], beta2=group["beta2"], eps=group["eps"],
+                                scal_ptr=it.scal_ptr, shard=it.shard, row_only=it.row_only, emit=it.emit))
+        return _u.Plan.signature_of(live) == plan.signature
 
     def _grad_scale_tensor(self, device) -> Optional[torch.Tensor]:
         """Device scalar that multiplies every gradient (AMP unscale and/or clip coefficient)."""
@@ -1677,7 +1720,63 @@ class Gefen(torch.optim.Optimizer):
                 "a DCP checkpoint written by a version that preserves _gefen_checkpoint_metadata.")
         self._validate_native_states(sd.get("state", {}) or {}, cb)
         sd = self._pack_legacy_param_groups_for_load(self.param_groups, sd)
+        self._validate_state_shapes(sd)
         return sd, step, cb
+
+    def _state_shape_for(self, p) -> Optional[Tuple[int, ...]]:
+        """Shape the quantised state of ``p`` is laid out for (subclasses whose state follows the
+        full matrix of a sharded parameter return None to skip the check)."""
+        return tuple(_local(p).shape)
+
+    def _validate_state_shapes(self, sd) -> None:
+        """Saved state tensors must fit the live parameters: the update kernels address the state
+        through raw pointers with sizes derived from the parameter, so a checkpoint whose
+        ``m_codebook`` / ``m_magnitude`` / ``vmean`` / ``v_row`` / ``v_col`` have other sizes would be
+        read and written out of bounds on the next step.  Checked before any live mutation
+        (reference ``gefen.py:4986-5190``)."""
+        saved_groups = sd.get("param_groups", ())
+        if len(saved_groups) != len(self.param_groups):
+            return                      # torch's own loader reports the group mismatch
+        states = sd.get("state", {}) or {}
+        for sg, lg in zip(saved_groups, self.param_groups):
+            if len(sg.get("params", ())) != len(lg["params"]):
+                return
+            for pid, p in zip(sg["params"], lg["params"]):
+                st = states.get(pid)
+                if not isinstance(st, dict) or "m_codebook" not in st:
+                    continue
+                shape = self._state_shape_for(p)
+                if shape is None:
+                    continue
+                numel = 1
+                for d in shape:
+                    numel *= int(d)
+                if numel == 0:
+                    continue
+                name = self._param_names.get(p, str(pid))
+                period = st.get("automatic_period")
+                what = "Gefen checkpoint state of {}".format(name)
+                if not isinstance(period, int) or period < 1 or numel % period:
+                    raise ValueError("{}: automatic_period {!r} does not divide the parameter's {} "
+                                     "elements".format(what, period, numel))
+                nb = numel // period
+                idx, mag = st["m_codebook"], st["m_magnitude"]
+                if tuple(idx.shape) != (nb, period):
+                    raise ValueError("{}: m_codebook has shape {}, the parameter needs {}".format(
+                        what, tuple(idx.shape), (nb, period)))
+                if mag.numel() != nb:
+                    raise ValueError("{}: m_magnitude holds {} values, the parameter needs {}".format(
+                        what, mag.numel(), nb))
+                if "vmean" in st and st["vmean"].numel() != nb:
+                    raise ValueError("{}: vmean holds {} values, the parameter needs {}".format(
+                        what, st["vmean"].numel(), nb))
+                if "v_row" in st:
+                    if len(shape) != 2 or st["v_row"].numel() != shape[0] or st["v_col"].numel() != shape[1]:
+                        raise ValueError("{}: v_row / v_col hold {} / {} values, the parameter has shape {}".format(
+                            what, st["v_row"].numel(), st["v_col"].numel(), shape))
+                if "normuon_v" in st and st["normuon_v"].numel() != shape[0]:
+                    raise ValueError("{}: normuon_v holds {} values, the parameter has {} rows".format(
+                        what, st["normuon_v"].numel(), shape[0]))
 
     @staticmethod
     def _validate_counter(name: str, value) -> float:
@@ -1751,7 +1850,6 @@ class Gefen(torch.optim.Optimizer):
         torch.optim.Optimizer.load_state_dict(target, sd)
         target._gefen_global_step = int(step)
         target._gefen_global_step_by_device = {}
-        target._sr_seed_by_device = {}
         target._capt = {}
         target._gefen_codebook = cb
         target._gefen_codebook_by_device = {}
@@ -1839,7 +1937,7 @@ class Gefen(torch.optim.Optimizer):
             self._plan_cache.clear()
         self.state = shadow.state
         self.param_groups = shadow.param_groups
-        for attr in ("_gefen_global_step", "_gefen_global_step_by_device", "_sr_seed_by_device",
+        for attr in ("_gefen_global_step", "_gefen_global_step_by_device",
                      "_capt", "_gefen_codebook", "_gefen_codebook_by_device",
                      "_gefen_codebook_lut_by_device", "_gefen_thresholds_by_device", "_param_names", "_synthesized_param_names"):
             setattr(self, attr, getattr(shadow, attr))

@@ -181,6 +181,12 @@ class GefenMuon(Gefen):
     def _is_factored(self, p) -> bool:
         return False
 
+    def _state_shape_for(self, p):
+        # exact / distributed modes keep the momentum of the FULL matrix of a sharded parameter
+        if hasattr(p, "to_local") and self.sharded_mode != "approx":
+            return tuple(p.shape)
+        return tuple(_local(p).shape)
+
     # ------------------------------------------------------------------
     # momentum
     # ------------------------------------------------------------------

@@ -290,15 +290,95 @@ def test_tcgen05_gemm_matches_fp32(m, n, k, a_t, b_t):
     af = a.float().t() if a_t else a.float()
     bf = b.float() if b_t else b.float().t()
     ref = af @ bf
-    out = tcgemm.gemm(a, b, a_t=a_t, b_t=b_t)
+    tcgemm.set_pair_kernel(False)          # this test covers the single-CTA kernel
+    try:
+        out = tcgemm.gemm(a, b, a_t=a_t, b_t=b_t)
+        out2 = tcgemm.gemm(a, b, a_t=a_t, b_t=b_t, alpha=0.5, beta=-2.0, d=d)
+    finally:
+        tcgemm.set_pair_kernel(True)
     torch.cuda.synchronize()
     assert int(tcgemm.status_word(_dev()).item()) == 0
     err = (out.float() - ref).abs().max().item()
     assert err <= 2e-2 * ref.abs().max().item() + 1e-2, err
-    out2 = tcgemm.gemm(a, b, a_t=a_t, b_t=b_t, alpha=0.5, beta=-2.0, d=d)
     ref2 = 0.5 * ref - 2.0 * d.float()
     err2 = (out2.float() - ref2).abs().max().item()
     assert err2 <= 2e-2 * ref2.abs().max().item() + 1e-2, err2
+
+
+@pytest.mark.parametrize("m,n,k,a_t,b_t,bn", [
+    (512, 512, 256, False, False, 256), (512, 512, 256, False, False, 128), (256, 256, 64, False, False, 0),
+    (1024, 768, 4096, False, False, 0), (300, 264, 200, False, False, 256), (520, 136, 328, True, True, 128),
+    (512, 1024, 512, False, True, 256), (512, 1024, 512, True, False, 128), (768, 640, 1024, True, True, 256),
+    (4096, 4096, 1024, False, False, 0), (129, 128, 64, False, True, 0), (1024, 768, 8192, True, True, 0),
+    (4352, 4352, 512, False, False, 0),
+])
+def test_pair_gemm_matches_fp32(m, n, k, a_t, b_t, bn):
+    """CTA-pair tcgen05 GEMM (cta_group::2) against the fp32 product, all operand layouts, both tile
+    widths, ragged edges, and the alpha / beta * D epilogue."""
+    from gefen_x_b200.ops import tcgemm
+
+    g = torch.Generator().manual_seed(m + n + k + bn)
+    a = torch.randn((k, m) if a_t else (m, k), generator=g).bfloat16().to(_dev())
+    b = torch.randn((k, n) if b_t else (n, k), generator=g).bfloat16().to(_dev())
+    d = torch.randn(m, n, generator=g).bfloat16().to(_dev())
+    af = a.float().t() if a_t else a.float()
+    bf = b.float() if b_t else b.float().t()
+    ref = af @ bf
+    assert tcgemm.pair_eligible(m, n, k)
+    tcgemm.set_pair_kernel(True, bn)
+    try:
+        out = tcgemm.gemm(a, b, a_t=a_t, b_t=b_t)
+        out2 = tcgemm.gemm(a, b, a_t=a_t, b_t=b_t, alpha=0.5, beta=-2.0, d=d)
+        torch.cuda.synchronize()
+    finally:
+        tcgemm.set_pair_kernel(True, 0)
+    assert int(tcgemm.status_word(_dev()).item()) == 0
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item() + 1e-2, err
+    ref2 = 0.5 * ref - 2.0 * d.float()
+    err2 = (out2.float() - ref2).abs().max().item()
+    assert err2 <= 2e-2 * ref2.abs().max().item() + 1e-2, err2
+    # the single-CTA kernel gives the same product
+    tcgemm.set_pair_kernel(False)
+    try:
+        out1 = tcgemm.gemm(a, b, a_t=a_t, b_t=b_t)
+    finally:
+        tcgemm.set_pair_kernel(True, 0)
+    assert (out1.float() - out.float()).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("m,f,k,h", [(512, 512, 256, 384), (300, 264, 320, 384), (1024, 1792, 512, 384),
+                                     (512, 1024, 2048, 1024)])
+def test_pair_gemm_swiglu_epilogues(m, f, k, h):
+    """SwiGLU fused into the gate/up projection and its derivative fused into the down_proj input
+    gradient, against the fp32 statement and against the unfused kernels."""
+    from gefen_x_b200.ops import model as M
+    from gefen_x_b200.ops import tcgemm
+
+    g = torch.Generator().manual_seed(m + f + k)
+    x = (torch.randn(m, k, generator=g) * 0.5).bfloat16().to(_dev())
+    wgu = (torch.randn(2 * f, k, generator=g) * (k ** -0.5)).bfloat16().to(_dev())
+    gu, act = tcgemm.gemm_swiglu_fwd(x, wgu)
+    torch.cuda.synchronize()
+    assert int(tcgemm.status_word(_dev()).item()) == 0
+    gu_ref = x.float() @ wgu.float().t()
+    assert (gu.float() - gu_ref).abs().max().item() <= 2e-2 * gu_ref.abs().max().item() + 1e-2
+    # the activation is computed from the rounded gate / up values, like the separate kernel
+    act_unfused = M.swiglu_fwd(gu)
+    assert (act.float() - act_unfused.float()).abs().max().item() <= 1e-2 * act_unfused.float().abs().max().item() + 1e-3
+    gr, ur = gu.float()[:, :f], gu.float()[:, f:]
+    act_ref = torch.nn.functional.silu(gr) * ur
+    assert (act.float() - act_ref).abs().max().item() <= 1e-2 * act_ref.abs().max().item() + 1e-3
+
+    dy = (torch.randn(m, h, generator=g) * 0.5).bfloat16().to(_dev())
+    wd = (torch.randn(h, f, generator=g) * (h ** -0.5)).bfloat16().to(_dev())
+    dgu = tcgemm.gemm_swiglu_bwd(dy, wd, gu)
+    torch.cuda.synchronize()
+    assert int(tcgemm.status_word(_dev()).item()) == 0
+    dact = (dy.float() @ wd.float()).bfloat16()
+    dgu_unfused = M.swiglu_bwd(gu, dact)
+    scale = dgu_unfused.float().abs().max().item()
+    assert (dgu.float() - dgu_unfused.float()).abs().max().item() <= 2e-2 * scale + 1e-3
 
 
 def test_tcgen05_gemm_batched():

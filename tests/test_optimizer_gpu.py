@@ -158,6 +158,100 @@ def test_stochastic_rounding_is_seeded_by_step_and_stays_close_to_nearest():
     assert moved > 0
 
 
+def test_fast_path_notices_paged_state_and_replaced_parameters_with_stable_gradients():
+    """Gradients accumulated in place keep their addresses from step to step, so only the plan
+    check stands between a remembered launch plan and state / parameter storage that was replaced
+    in the meantime (state parked on the host by an offload wrapper, ``p.data`` re-assigned,
+    betas edited): each of these must send the step back through the full path."""
+    from gefen_x_b200 import Gefen
+
+    pa, pb = _params(), _params()
+    oa = Gefen(pa, lr=1e-2)
+    ob = Gefen(pb, lr=1e-2)
+    for ps in (pa, pb):
+        for _, p in ps:
+            p.grad = torch.zeros_like(p)
+    for step in range(8):
+        gs = _grads(pa, step)
+        for ps in (pa, pb):
+            for (_, p), g in zip(ps, gs):
+                p.grad.copy_(g)                       # in place: the gradient pointers never change
+        if step == 5:
+            for o in (oa, ob):
+                o.param_groups[0]["beta1"] = 0.8
+        oa.step()
+        ob.step()
+        if step >= 2:
+            assert oa._fast is not None               # the undisturbed optimizer stays on the fast path
+        if step in (2, 3):
+            for _, p in pb:                           # park the state on the host, as an offloader does
+                st = ob.state[p]
+                for k, v in list(st.items()):
+                    if torch.is_tensor(v):
+                        st[k] = v.cpu()
+        if step == 4:
+            for _, p in pb:                           # new storage for the parameters, same values
+                p.data = p.data.clone()
+    for (n, a), (_, b) in zip(pa, pb):
+        assert torch.equal(a, b), n
+        assert torch.equal(oa.state[a]["m_codebook"], ob.state[b]["m_codebook"].to(_dev())), n
+        assert torch.equal(oa.state[a]["m_magnitude"], ob.state[b]["m_magnitude"].to(_dev())), n
+    assert all(v == 0 for v in ob.kernel_status().values())
+
+
+def test_stochastic_rounding_under_cuda_graph_replay_draws_fresh_noise():
+    """The rounding seed of a capturable optimizer lives on the device and advances inside the
+    captured region: two replays over the same gradient must not repeat the same rounding
+    decisions, and a replayed run equals the eager capturable run step by step."""
+    from gefen_x_b200 import Gefen
+
+    pa, pb = _params(seed=3), _params(seed=3)
+    oa = Gefen(pa, lr=1e-2, stochastic_round=True, capturable=True)     # eager oracle
+    ob = Gefen(pb, lr=1e-2, stochastic_round=True, capturable=True)     # graph replays
+    for ps in (pa, pb):
+        for _, p in ps:
+            p.grad = torch.zeros_like(p)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for step in range(3):
+            gs = _grads(pa, step)
+            for ps, o in ((pa, oa), (pb, ob)):
+                for (_, p), g in zip(ps, gs):
+                    p.grad.copy_(g)
+                o.step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ob.step()
+    oa.step()                                         # capture records the step without running it
+    graph.replay()
+    torch.cuda.synchronize()
+    fixed = _grads(pa, 50)
+    snaps = []
+    for rep in range(2):
+        for ps in (pa, pb):
+            for (_, p), g in zip(ps, fixed):
+                p.grad.copy_(g)
+        before = {n: ob.state[p]["m_codebook"].clone() for n, p in pb}
+        mags = {n: ob.state[p]["m_magnitude"].clone() for n, p in pb}
+        oa.step()
+        graph.replay()
+        torch.cuda.synchronize()
+        snaps.append({n: ob.state[p]["m_codebook"].clone() for n, p in pb})
+        for (n, a), (_, b) in zip(pa, pb):
+            assert torch.equal(oa.state[a]["m_codebook"], ob.state[b]["m_codebook"]), (rep, n)
+        # restore the momentum so that the second replay quantises exactly the same values
+        if rep == 0:
+            for o, ps in ((oa, pa), (ob, pb)):
+                for n, p in ps:
+                    o.state[p]["m_codebook"].copy_(before[n])
+                    o.state[p]["m_magnitude"].copy_(mags[n])
+    differing = sum(int((snaps[0][n] != snaps[1][n]).sum()) for n, _ in pb)
+    assert differing > 0, "two replays made identical rounding decisions: the seed is frozen in the graph"
+
+
 def test_requantise_and_dense_dequantise_kernels():
     """Index remap onto a new codebook and the dense momentum export against their torch statements."""
     from gefen_x_b200 import Gefen
