@@ -307,7 +307,8 @@ void gemm_bf16(const Tensor& a, const Tensor& b, Tensor c, const c10::optional<T
 // epi 2 (SwiGLU derivative): a b = d(act) [M, F]; aux = gate|up [M, 2F]; c0 = d(gate|up) [M, 2F].
 void gemm_pair_bf16(const Tensor& a, const Tensor& b, Tensor c0, const c10::optional<Tensor>& c1,
                     const c10::optional<Tensor>& d, const c10::optional<Tensor>& aux, bool a_t, bool b_t,
-                    double alpha, double beta, int64_t epi, int64_t bn, const c10::optional<Tensor>& status) {
+                    double alpha, double beta, int64_t epi, int64_t bn, const c10::optional<Tensor>& status,
+                    const c10::optional<Tensor>& sumsq) {
     c10::cuda::CUDAGuard guard(a.device());
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && c0.is_cuda(), "gemm_pair_bf16: CUDA tensors required");
     TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 &&
@@ -326,6 +327,14 @@ void gemm_pair_bf16(const Tensor& a, const Tensor& b, Tensor c0, const c10::opti
     p.epi = (int)epi;
     p.bn = (int)bn;
     p.status = (status.has_value() && status->defined()) ? status->data_ptr<int>() : nullptr;
+    p.sumsq = nullptr;
+    if (sumsq.has_value() && sumsq->defined()) {
+        TORCH_CHECK(epi == gx::kEpiPlain, "gemm_pair_bf16: sumsq is available with the plain epilogue only");
+        TORCH_CHECK(sumsq->is_cuda() && sumsq->scalar_type() == at::kFloat && sumsq->is_contiguous() &&
+                        sumsq->numel() >= gx::kSumsqSlots,
+                    "gemm_pair_bf16: sumsq must be a contiguous CUDA fp32 tensor of at least 2048 slots");
+        p.sumsq = sumsq->data_ptr<float>();
+    }
     auto bf = [](const Tensor& t) { return reinterpret_cast<__nv_bfloat16*>(t.data_ptr()); };
     __nv_bfloat16 *C0 = bf(c0), *C1 = nullptr, *C2 = nullptr;
     long long ld0 = c0.stride(0), ld1 = 0, ld2 = 0;
@@ -693,7 +702,7 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("gemm_bf16(Tensor a, Tensor b, Tensor(a!) c, Tensor? d, bool a_t, bool b_t, float alpha, "
           "float beta, Tensor? status) -> ()");
     m.def("gemm_pair_bf16(Tensor a, Tensor b, Tensor(a!) c0, Tensor(b!)? c1, Tensor? d, Tensor? aux, bool a_t, "
-          "bool b_t, float alpha, float beta, int epi, int bn, Tensor? status) -> ()");
+          "bool b_t, float alpha, float beta, int epi, int bn, Tensor? status, Tensor(c!)? sumsq) -> ()");
     m.def("gemm_ag_bf16(Tensor a, Tensor(a!) bstage, Tensor(b!) c, int[] peer_bases, Tensor segs, "
           "Tensor seg_meta, Tensor tile_order, Tensor(c!) flags, Tensor(d!) count, int epoch, "
           "int count_target, int fetch_ctas, Tensor? status) -> ()");

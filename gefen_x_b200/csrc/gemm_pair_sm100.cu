@@ -57,6 +57,7 @@ constexpr int kUK = 16;
 constexpr int kPairThreads = 192;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kEpiTile = 32 * 128;          // one warp's staging tile: 32 rows x 64 bf16
+constexpr int kEpiBufs = 4;                      // staging tiles per epilogue warp (TMA stores in flight)
 
 struct PairShared {
     uint64_t full[8];
@@ -68,12 +69,14 @@ struct PairShared {
 };
 
 template <int BN> struct PairTile {
+    // 5 x 32 KB (or 6 x 24 KB) of operand stages + 64 KB of epilogue staging + barriers <= 227 KB
     static constexpr int kHalfN = BN / 2;
     static constexpr uint32_t kABytes = kBM * kBK * 2;
     static constexpr uint32_t kBBytes = kHalfN * kBK * 2;
-    static constexpr int kStages = (BN == 256) ? 6 : 8;
-    static constexpr uint32_t kEpiBytes = 4 * 2 * kEpiTile;
+    static constexpr int kStages = (BN == 256) ? 5 : 6;
+    static constexpr uint32_t kEpiBytes = 4 * kEpiBufs * kEpiTile;
     static constexpr size_t kSmem = (size_t)kStages * (kABytes + kBBytes) + kEpiBytes + sizeof(PairShared) + 1024;
+    static_assert(kSmem <= 232448, "shared memory of the pair kernel exceeds 227 KB");
 };
 
 struct PairMaps {
@@ -115,6 +118,32 @@ __device__ __forceinline__ void load_row64(const __nv_bfloat16* base, long long 
             w[j] = pack2(a, b);
         }
     }
+}
+
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+// the `bytes` of row `row` starting at column `col` that an epilogue thread will read later
+__device__ __forceinline__ void prefetch_row(const __nv_bfloat16* base, long long ld, int row, int col, int rows,
+                                             int cols, int n) {
+    if (row >= rows) return;
+    const char* ptr = reinterpret_cast<const char*>(base + (long long)row * ld + col);
+    for (int b = 0; b < n * 2; b += 128)
+        if (col + b / 2 < cols) prefetch_l2(ptr + b);
+}
+
+// Tile index -> (row tile, column tile).  Tiles are visited in groups of `group_m` row tiles,
+// column-major inside a group, so that the ~74 tiles in flight at any time form a near-square
+// block of the output: they share the fewest distinct operand panels, and the panels of a group
+// are fetched from HBM once while the other operand streams past.
+__device__ __forceinline__ void tile_coords(const PairParams& p, int tile, int& mt, int& nt) {
+    const int per_group = p.group_m * p.n_tiles;
+    const int g = tile / per_group;
+    const int first_m = g * p.group_m;
+    const int gsize = min(p.group_m, p.m_tiles - first_m);
+    const int r = tile - g * per_group;
+    mt = first_m + r % gsize;
+    nt = r / gsize;
 }
 
 // One unit of work of a pair: a whole tile, or one K-range of a tile of the tail wave.
@@ -182,7 +211,8 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
             uint32_t phase = 0;
             Work wk;
             for (int it = 0; get_work(p, it, pair, n_pairs, k_blocks, wk); ++it) {
-                const int mt = wk.tile % p.m_tiles, nt = wk.tile / p.m_tiles;
+                int mt, nt;
+                tile_coords(p, wk.tile, mt, nt);
                 const int m0 = mt * 256 + (int)rank * kBM;
                 // plain: this CTA's half of the BN columns.  SwiGLU forward: rank 0 fetches the
                 // gate rows, rank 1 the up rows of the same BN / 2 columns.
@@ -219,6 +249,12 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
         // --------------------------- MMA issuer (leader CTA) ---------------------------
         if (rank == 0 && lane == 0) {
             const uint32_t idesc = make_idesc(256, BN, p.a_mn_major != 0, p.b_mn_major != 0);
+            // descriptors differ from stage to stage and from k-step to k-step only in the start address
+            // (low word, in 16-byte units): keep the constant part and add
+            const uint64_t a_desc0 = p.a_mn_major ? make_desc(smem_u32(smA), kBK * 128, 1024) : make_desc(smem_u32(smA), 16, 1024);
+            const uint64_t b_desc0 = p.b_mn_major ? make_desc(smem_u32(smB), kBK * 128, 1024) : make_desc(smem_u32(smB), 16, 1024);
+            const uint32_t a_kstep = (p.a_mn_major ? kUK * 128 : kUK * 2) >> 4;
+            const uint32_t b_kstep = (p.b_mn_major ? kUK * 128 : kUK * 2) >> 4;
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -232,16 +268,12 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
                 for (int kb = wk.kb0; kb < wk.kb1; ++kb) {
                     if (!mbar_wait(&ss->full[stage], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smA + stage * TL::kABytes);
-                    const uint32_t b_addr = smem_u32(smB + stage * TL::kBBytes);
+                    const uint64_t ad = a_desc0 + (uint64_t)((uint32_t)stage * (TL::kABytes >> 4));
+                    const uint64_t bd = b_desc0 + (uint64_t)((uint32_t)stage * (TL::kBBytes >> 4));
 #pragma unroll
-                    for (int k = 0; k < kBK / kUK; ++k) {
-                        const uint64_t ad = p.a_mn_major ? make_desc(a_addr + k * (kUK * 128), kBK * 128, 1024)
-                                                         : make_desc(a_addr + k * (kUK * 2), 16, 1024);
-                        const uint64_t bd = p.b_mn_major ? make_desc(b_addr + k * (kUK * 128), kBK * 128, 1024)
-                                                         : make_desc(b_addr + k * (kUK * 2), 16, 1024);
-                        umma_bf16<2>(d_tmem, ad, bd, idesc, (kb > wk.kb0 || k > 0) ? 1u : 0u);
-                    }
+                    for (int k = 0; k < kBK / kUK; ++k)
+                        umma_bf16<2>(d_tmem, ad + (uint64_t)(k * a_kstep), bd + (uint64_t)(k * b_kstep), idesc,
+                                     (kb > wk.kb0 || k > 0) ? 1u : 0u);
                     umma_commit_pair(&ss->empty[stage], 3);        // both CTAs may refill the stage
                     if (++stage == TL::kStages) { stage = 0; phase ^= 1; }
                 }
@@ -253,7 +285,7 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
     } else {
         // --------------------------------- epilogue ----------------------------------
         const int q = warp & 3;                                    // TMEM lane quadrant of this warp
-        unsigned char* my_stage = smE + (warp - 2) * 2 * kEpiTile;
+        unsigned char* my_stage = smE + (warp - 2) * kEpiBufs * kEpiTile;
         const uint32_t leader_empty0 = mapa(smem_u32(&ss->tmem_empty[0]), 0);
         const uint32_t leader_empty1 = mapa(smem_u32(&ss->tmem_empty[1]), 0);
         int acc = 0;
@@ -261,8 +293,8 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
         uint32_t unit = 0;                                         // staging tiles handed to TMA so far
         // pack 64 fp32 values to bf16, stage them and store the [32 x 64] tile at (col, row0)
         auto emit = [&](const CUtensorMap* map, const uint32_t (&w)[32], int col, int row0) {
-            unsigned char* tile = my_stage + (unit & 1) * kEpiTile;
-            if (lane == 0) bulk_wait_read<1>();                    // the store that last read this buffer is done
+            unsigned char* tile = my_stage + (unit & (kEpiBufs - 1)) * kEpiTile;
+            if (lane == 0) bulk_wait_read<kEpiBufs - 1>();         // the store that last read this buffer is done
             __syncwarp();
             write_row_swizzled(tile, lane, w);
             fence_async_smem();
@@ -275,12 +307,22 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
         };
         Work wk;
         for (int it = 0; get_work(p, it, pair, n_pairs, k_blocks, wk); ++it) {
-            const int mt = wk.tile % p.m_tiles, nt = wk.tile / p.m_tiles;
+            int mt, nt;
+            tile_coords(p, wk.tile, mt, nt);
             const int row0 = mt * 256 + (int)rank * kBM + q * 32;
             const int row = row0 + lane;
+            // what the epilogue will read from global memory: start it towards L2 while the MMAs run
+            if constexpr (EPI == kEpiPlain) {
+                if (p.D) prefetch_row(p.D, p.ldd, row, nt * BN, p.M, p.N, BN);
+            } else if constexpr (EPI == kEpiSwigluBwd) {
+                prefetch_row(p.aux, p.ldaux, row, nt * BN, p.M, p.F, BN);
+                prefetch_row(p.aux + p.F, p.ldaux, row, nt * BN, p.M, p.F, BN);
+            }
             if (!mbar_wait(&ss->tmem_full[acc], acc_phase, abort_flag)) break;
             tc_fence_after();
             const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+            float sq = 0.f;                                        // this thread's share of sum(C^2) of the tile
+            int sq_slot = (int)blockIdx.x * 4 + q;                 // one slot per epilogue warp of the launch ...
             // ---- K-split tile: park the partial; only the slice's last arriver goes on ----
             const float* ws_tile = nullptr;                        // set: sum the parked partials
             if (wk.n_split > 1) {
@@ -304,6 +346,8 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
                     __threadfence();
                     if (lane == 0) p.counters[slice] = 0;          // ready for the next launch
                     ws_tile = ws_slice + lane;
+                    sq_slot = kSumsqTailBase + slice;              // ... or per slice of a tail tile: whichever
+                                                                   // split arrives last, the same slot gets the sum
                 } else {
                     tc_fence_before();
                     __syncwarp();
@@ -374,6 +418,15 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
                             for (int j = 0; j < 32; ++j)
                                 w[j] = pack2(__uint_as_float(r[2 * j]) * p.alpha, __uint_as_float(r[2 * j + 1]) * p.alpha);
                         }
+                        if (p.sumsq != nullptr && row < p.M) {
+                            // sum of squares of the values as stored (bf16), for the gradient norm
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const float a = lo_f(w[j]), b = hi_f(w[j]);
+                                if (col + 2 * j < p.N) sq = __fmaf_rn(a, a, sq);
+                                if (col + 2 * j + 1 < p.N) sq = __fmaf_rn(b, b, sq);
+                            }
+                        }
                         emit(&maps.c0, w, col, row0);
                     } else {
                         // SwiGLU derivative: the accumulator is d(act); aux = [gate | up] of the forward pass
@@ -407,6 +460,13 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            if constexpr (EPI == kEpiPlain) {
+                if (p.sumsq != nullptr) {
+                    // fixed order: lanes by shuffle tree, tiles of this warp in visiting order, one writer per slot
+                    sq = warp_sum(sq);
+                    if (lane == 0) p.sumsq[sq_slot] += sq;
+                }
+            }
         }
         if (lane == 0) bulk_wait<0>();                             // all stores of this warp have landed
     }
@@ -472,6 +532,9 @@ cudaError_t launch_pair(const PairMaps& maps, PairParams p, int sm_count, cudaSt
     p.m_tiles = (p.M + 255) / 256;
     p.n_tiles = (p.N + n_cols - 1) / n_cols;
     p.total_tiles = p.m_tiles * p.n_tiles;
+    // row-tile group of the visiting order: all rows when A is small enough to stay in L2 (then B
+    // streams through once), otherwise 8 (near-square waves)
+    p.group_m = ((long long)p.M * p.K * 2 <= (48ll << 20) || p.m_tiles <= 8) ? p.m_tiles : 8;
     const int max_pairs = sm_count / 2 > 0 ? sm_count / 2 : 1;
     const int k_blocks = (p.K + kBK - 1) / kBK;
     int pairs = max_pairs;

@@ -69,6 +69,9 @@ struct PairParams {
     long long ldaux;
     int bn;                         // 0: choose; 128 / 256: force the tile width
     int* status;                    // device status word, may be null
+    // plain epilogue, optional: sum of squares of the stored output accumulated into kSumsqSlots fp32
+    // slots (the caller sums them; each slot has one writer per launch, so the total is reproducible)
+    float* sumsq;
     // K-split of the tail wave (optional): fp32 workspace and zero-initialised arrival counters that
     // the kernel leaves zeroed; launches sharing them must be ordered on one stream
     float* ws;
@@ -77,9 +80,12 @@ struct PairParams {
     int n_counters;
     int m_tiles, n_tiles, total_tiles;
     int full_tiles, rem_tiles, splits;     // set by the launcher
+    int group_m;                           // set by the launcher: row tiles per group of the visiting order
     int d_vec_ok;
 };
 constexpr int kMaxSplits = 8;
+constexpr int kSumsqTailBase = 1024;       // slots [0, 1024): per epilogue warp; [1024, 2048): per tail-tile slice
+constexpr int kSumsqSlots = 2048;
 // workspace that always suffices: half of the pairs' tiles, 256 x 256 fp32 each, and their counters
 constexpr long long kPairWsFloats = 74ll * 256 * 256;
 constexpr int kPairCounters = 74 * 8;

@@ -178,13 +178,16 @@ def layer_backward(cfg: ModelConfig, w: Dict[str, torch.Tensor], gw: Dict[str, t
             gw[name].add_(val.to(gw[name].dtype).view(gw[name].shape))
         else:
             gw[name].copy_(val.view(gw[name].shape))
+            if G.grad_sumsq() is not None:
+                G.add_sumsq(gw[name], G.grad_sumsq())
 
     def wgrad(name, a, b):
-        # a^T @ b straight into the gradient view (no temporary) unless accumulating
+        # a^T @ b straight into the gradient view (no temporary) unless accumulating; while a
+        # gradient-norm accumulator is set, the product's epilogue also sums the squares it stores
         if accumulate:
             gw[name].add_(G.mm_tn(a, b))
         else:
-            G.mm_tn(a, b, out=gw[name])
+            G.mm_tn_wgrad(a, b, gw[name])
 
     # MLP
     wgrad("mlp.down_proj.weight", dy2, saved["act"])

@@ -82,6 +82,49 @@ def mm_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) 
     return torch.matmul(a.t(), b, out=out)
 
 
+_GRAD_SUMSQ: Optional[torch.Tensor] = None
+
+
+def set_grad_sumsq(partials: Optional[torch.Tensor]) -> None:
+    """While set (an fp32 tensor of at least 2048 slots), :func:`mm_tn_wgrad` adds the sum of squares
+    of every weight gradient it writes into ``partials`` -- the global gradient norm then needs no
+    extra pass over the gradients (single-GPU runs; with several ranks the norm is that of the
+    reduced gradient and is taken after the reduction)."""
+    global _GRAD_SUMSQ
+    _GRAD_SUMSQ = partials
+
+
+def grad_sumsq() -> Optional[torch.Tensor]:
+    return _GRAD_SUMSQ
+
+
+def mm_tn_wgrad(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Weight gradient ``out = a [T, M]^T @ b [T, N]``, contributing to the gradient norm when
+    :func:`set_grad_sumsq` is active (in the product's epilogue where the kernel allows, by one pass
+    over ``out`` otherwise)."""
+    sq = _GRAD_SUMSQ
+    if sq is None:
+        return mm_tn(a, b, out=out)
+    if _tc(a, b, out):
+        from . import tcgemm
+
+        if tcgemm.pair_eligible(a.shape[1], b.shape[1], a.shape[0]):
+            return tcgemm.gemm(a, b, a_t=True, b_t=True, out=out, sumsq=sq)
+    mm_tn(a, b, out=out)
+    add_sumsq(out, sq)
+    return out
+
+
+def add_sumsq(t: torch.Tensor, partials: torch.Tensor) -> None:
+    """``partials += slot-wise partial sums of t^2`` (one pass over a contiguous tensor)."""
+    from . import update as U
+
+    if t.is_cuda and t.is_contiguous() and t.dtype in U.DTYPE_CODE:
+        U.reduce_sources(None, [t.data_ptr()], t.numel(), 1.0, partials, t.dtype, t.device)
+    else:
+        partials[0] += t.float().square().sum()
+
+
 def mlp_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """``(gu, act)`` with ``gu = h @ w_gate_up^T`` (``[M, 2F]``) and ``act = silu(gate) * up``."""
     from . import model as M

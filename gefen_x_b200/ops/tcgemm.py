@@ -70,8 +70,12 @@ def pair_eligible(m: int, n: int, k: int) -> bool:
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = False,
          alpha: float = 1.0, beta: float = 0.0, d: Optional[torch.Tensor] = None,
-         out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """See the module docstring for the layout convention."""
+         out: Optional[torch.Tensor] = None, sumsq: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """See the module docstring for the layout convention.
+
+    ``sumsq`` (fp32, at least 2048 slots) receives, added slot-wise, the sum of squares of the stored
+    output -- the gradient-norm contribution of a weight-gradient product, computed in its epilogue.
+    Only the CTA-pair kernel provides it: check :func:`pair_eligible` (``gemm`` raises otherwise)."""
     m = a.shape[-1] if a_t else a.shape[-2]
     n = b.shape[-1] if b_t else b.shape[-2]
     k = a.shape[-2] if a_t else a.shape[-1]
@@ -80,8 +84,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     dd = d if beta != 0.0 else None
     if a.dim() == 2 and pair_eligible(m, n, k) and _ok_operand(out) and (dd is None or _ok_operand(dd)):
         ops().gemm_pair_bf16(a, b, out, None, dd, None, bool(a_t), bool(b_t), float(alpha), float(beta), 0,
-                             _FORCE_BN, status_word(a.device))
+                             _FORCE_BN, status_word(a.device), sumsq)
         return out
+    if sumsq is not None:
+        raise ValueError("sumsq needs the CTA-pair kernel; this product does not qualify")
     ops().gemm_bf16(a, b, out, dd, bool(a_t), bool(b_t), float(alpha), float(beta), status_word(a.device))
     return out
 
@@ -105,7 +111,8 @@ def gemm_swiglu_fwd(x: torch.Tensor, w_gate_up: torch.Tensor) -> Tuple[torch.Ten
     m, f = x.shape[0], w_gate_up.shape[0] // 2
     gu = torch.empty(m, 2 * f, dtype=torch.bfloat16, device=x.device)
     act = torch.empty(m, f, dtype=torch.bfloat16, device=x.device)
-    ops().gemm_pair_bf16(x, w_gate_up, gu, act, None, None, False, False, 1.0, 0.0, 1, 0, status_word(x.device))
+    ops().gemm_pair_bf16(x, w_gate_up, gu, act, None, None, False, False, 1.0, 0.0, 1, 0, status_word(x.device),
+                         None)
     return gu, act
 
 
@@ -116,5 +123,5 @@ def gemm_swiglu_bwd(dy: torch.Tensor, w_down: torch.Tensor, gate_up: torch.Tenso
     """
     dgu = torch.empty_like(gate_up)
     ops().gemm_pair_bf16(dy, w_down, dgu, None, None, gate_up, False, True, 1.0, 0.0, 2, _FORCE_BN,
-                         status_word(dy.device))
+                         status_word(dy.device), None)
     return dgu

@@ -146,7 +146,8 @@ class ShardedTrainer:
         self._copy_tables: Dict[tuple, torch.Tensor] = {}
         self.ag_gemm = bool(ag_gemm) and int(world) > 1
         self.ag_fetch_ctas = int(ag_fetch_ctas)
-        self.step_count = 0
+        self.step_count = 0           # optimisation steps taken (restored by a checkpoint)
+        self._epoch = 0               # steps run by this process: the value the arrival flags count up to
         self.process_group = group
         cuda = self.device.type == "cuda"
         esz = torch.empty((), dtype=dtype).element_size()
@@ -603,7 +604,7 @@ class ShardedTrainer:
         ``"early"`` = head and final norm (complete right after the head's backward), ``"rest"`` =
         the token embedding (complete at the very end); each part has its own arrival flags."""
         g = self.all_groups[gi]
-        t = self.step_count
+        t = self._epoch
         code_dev = self.device
         if self.world == 1:
             if self.hybrid:
@@ -616,6 +617,8 @@ class ShardedTrainer:
                 self.muon.reduce_group(gi)
             elif self.clip and self.device.type != "cuda":
                 self.norm_partials[0] += g.full_g.float().square().sum()
+            elif self.clip and getattr(self, "_fused_norm", False):
+                pass            # already summed by the gradient products' epilogues (see step)
             elif self.clip:
                 U.reduce_sources(None, [g.full_g.data_ptr()], g.full_numel, 1.0, self.norm_partials,
                                  self.dtype, code_dev)
@@ -658,7 +661,7 @@ class ShardedTrainer:
             torch.sum(self.norm_partials, dim=0, keepdim=True, out=self.norm_local)
             ops().comm_allreduce_scalar(self.arena.peer_ptrs(self.norm_slot_off),
                                         self.flags.row_ptrs(self.SLOT_NORM), self.rank,
-                                        self.norm_local, self.norm_total, self.step_count,
+                                        self.norm_local, self.norm_total, self._epoch,
                                         self.wait_iters, self.status)
             U.clip_coef(self.norm_total, float(self.clip), self.clip_coef)
 
@@ -733,7 +736,8 @@ class ShardedTrainer:
     def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         cfg, L = self.cfg, self.cfg.n_layers
         self.step_count += 1
-        t = self.step_count
+        self._epoch += 1
+        t = self._epoch
         tok = self._to_device(tokens)
         tgt = self._to_device(targets)
         B, S = tok.shape
@@ -763,6 +767,11 @@ class ShardedTrainer:
             self._ensure_layer(0)
             torch.cuda.current_stream().wait_event(ev)
         head_ready = None
+        # single GPU with clipping: the weight-gradient products add their sums of squares to the norm
+        # partials in their epilogues, so no extra pass over the gradients is needed afterwards
+        fused_norm = bool(self.clip) and not multi and not self.hybrid and self.device.type == "cuda"
+        G.set_grad_sumsq(self.norm_partials if fused_norm else None)
+        self._fused_norm = fused_norm
         self._mark("embed_ready")
         ew = self._embed_views(eg.full_w)
         egrad = self._embed_views(eg.full_g)
@@ -800,12 +809,17 @@ class ShardedTrainer:
         loss = loss_rows.sum() / T
         dhN = G.mm_nn(logits, head_w)
         head_grad = egrad["model.embed_tokens.weight"] if cfg.tie_embeddings else egrad["lm_head.weight"]
-        G.mm_tn(logits, hN, out=head_grad)
+        if cfg.tie_embeddings:
+            G.mm_tn(logits, hN, out=head_grad)        # the token gradients are added below: norm taken after
+        else:
+            G.mm_tn_wgrad(logits, hN, head_grad)
         del logits
         if not cfg.tie_embeddings:
             egrad["model.embed_tokens.weight"].zero_()
         dx2d, dnorm = M.rmsnorm_bwd(dhN, x2d, ew["model.norm.weight"], rstdN)
         egrad["model.norm.weight"].copy_(dnorm)
+        if fused_norm:
+            G.add_sumsq(egrad["model.norm.weight"], self.norm_partials)
         dx = dx2d.view(B, S, cfg.hidden)
         if multi and not cfg.tie_embeddings:
             # the head's and the final norm's gradients are complete: reduce them under backward
@@ -827,6 +841,9 @@ class ShardedTrainer:
             self._mark_layer_done(li)
             self._reduce_group(li)
         egrad["model.embed_tokens.weight"].index_add_(0, tok.reshape(-1), dx.reshape(T, cfg.hidden))
+        if fused_norm:
+            G.add_sumsq(egrad["model.embed_tokens.weight"], self.norm_partials)
+        G.set_grad_sumsq(None)
         self._mark("bwd.end")
         self._reduce_group(len(self.all_groups) - 1,
                            part="rest" if (multi and not cfg.tie_embeddings) else "all")
@@ -847,6 +864,52 @@ class ShardedTrainer:
             self._gather_done.clear()
             self._layer_done.clear()
         return loss
+
+    # ------------------------------------------------------------------
+    # checkpoints
+    # ------------------------------------------------------------------
+    def state_dict(self) -> Dict[str, object]:
+        """This rank's part of the run: its weight shards, its optimizer state (native Gefen format)
+        and the step count.  Same topology only (the same ``world`` and model); a run restored from it
+        continues bit for bit.  For a checkpoint that reloads on another number of ranks use
+        :meth:`save_checkpoint` (reference: native format ``src/gefen/gefen.py:4558-4707``)."""
+        from ..ckpt import trainer as _ck
+
+        return _ck.native_state_dict(self)
+
+    def load_state_dict(self, state: Dict[str, object]) -> None:
+        from ..ckpt import trainer as _ck
+
+        _ck.load_native_state_dict(self, state)
+
+    def save_checkpoint(self, path: str, *, async_save: bool = False):
+        """Write a resharding checkpoint with ``torch.distributed.checkpoint``: weight shards as they
+        are, optimizer state under the GefenDCPState keys as dense tensors that are expanded one slot
+        at a time while writing.  Collective: every rank calls it.  Reloads with
+        :meth:`load_checkpoint` on any number of ranks (reference ``src/gefen/dcp.py:1068-1169``)."""
+        from ..ckpt import trainer as _ck
+
+        return _ck.save_checkpoint(self, path, async_save=async_save)
+
+    def load_checkpoint(self, path: str) -> None:
+        from ..ckpt import trainer as _ck
+
+        _ck.load_checkpoint(self, path)
+
+    def _after_restore(self) -> None:
+        """Make restored shards visible to the peers and restart the parameter-arrival protocol."""
+        self._grad_cache.clear()
+        self.opt._fast = None
+        if self.opt._plan_cache is not None:
+            self.opt._plan_cache.clear()
+        if self.world > 1:
+            self.ring_owner = [-1] * len(self.ring)
+            self._gather_done.clear()
+            self._layer_done.clear()
+            torch.cuda.synchronize(self.device)
+            # the next step waits for "parameters of epoch t - 1 are in place" on every peer
+            self.flags.signal(self.SLOT_PARAMS, self._epoch)
+            self.arena.barrier()
 
     def check_status(self) -> None:
         """Raise if any kernel recorded a timed-out peer wait (reads one int from the device)."""

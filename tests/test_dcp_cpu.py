@@ -20,7 +20,24 @@ def _free_port():
     return p
 
 
-SHAPES = [("layer.weight", (16, 24)), ("layer.bias", (16,)), ("head.weight", (8, 16))]
+SHAPES = [("blocks.{}.weight".format(i), (16, 24)) for i in range(10)] + \
+    [("layer.bias", (16,)), ("head.weight", (8, 16))]
+
+
+def _full(v, world):
+    """Global dense tensor behind one published entry (a stand-in resolved and gathered by rows)."""
+    import torch.distributed as dist
+
+    from gefen_x_b200.ckpt.lazy import LazyShard
+
+    if not isinstance(v, LazyShard):
+        return v.full_tensor() if hasattr(v, "full_tensor") else v
+    local = v.resolve_uncached()
+    if world == 1:
+        return local
+    parts = [None] * world
+    dist.all_gather_object(parts, (v._gx_offsets[0], local))
+    return torch.cat([t for _o, t in sorted(parts, key=lambda x: x[0])], dim=0)
 
 
 def _full_tensors(seed):
@@ -67,22 +84,27 @@ def _worker(rank, world, port, path, mode, q):
             for step in range(3):
                 _set_grads(params, mesh, step)
                 opt.step()
+            from gefen_x_b200.ckpt.lazy import LazyShard
+
             sd = GefenDCPState(opt).state_dict()
+            LazyShard.accounting.reset()
             dcp.save({"optimizer": sd}, storage_writer=GefenFileSystemWriter(path),
                      planner=GefenSavePlanner())
+            peak = LazyShard.accounting.peak
+            own = sum(p.to_local().numel() for _n, p in params)
             dense = {}
             for k, v in sd.items():
                 if k.endswith("momentum") or k.endswith("second_moment"):
-                    dense[k] = v.full_tensor().numpy().copy()
+                    dense[k] = _full(v, world).numpy().copy()
             if rank == 0:
-                q.put(("saved", dense, int(sd["global_step"])))
+                q.put(("saved", dense, int(sd["global_step"]), peak / own))
         else:
             wrapper = GefenDCPState(opt)
             sd = wrapper.state_dict()
             dcp.load({"optimizer": sd}, checkpoint_id=path)
             wrapper.load_state_dict(sd)
             again = GefenDCPState(opt).state_dict()
-            dense = {k: v.full_tensor().numpy().copy() for k, v in again.items()
+            dense = {k: _full(v, world).numpy().copy() for k, v in again.items()
                      if k.endswith("momentum") or k.endswith("second_moment")}
             # the reloaded optimizer must be able to keep stepping
             _set_grads(params, mesh, 7)
@@ -118,8 +140,11 @@ def _run(world, path, mode):
 def _reshard_case(save_world, load_worlds):
     with tempfile.TemporaryDirectory() as d:
         path = os.path.join(d, "ckpt")
-        _tag, saved, step = _run(save_world, path, "save")
+        _tag, saved, step, transient = _run(save_world, path, "save")
         assert step == 3
+        # one slot's dense form at a time (plus the writer's copy of the previous one): far below the
+        # 8 bytes per local parameter of expanding every slot up front
+        assert transient <= 1.0, transient
         for world in load_worlds:
             _tag, loaded, step2 = _run(world, path, "load")
             assert step2 == 4
@@ -143,6 +168,89 @@ def test_reshard_two_to_one_and_four():
 def test_reshard_four_to_two():
     """Save on more ranks, reload on fewer (the 8 -> 4 case of the headline configuration in small)."""
     _reshard_case(4, (2,))
+
+
+def _mismatch_worker(rank, world, port, q):
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+
+    from gefen_x_b200 import Gefen, GefenDCPState
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        mesh = init_device_mesh("cpu", (world,))
+        names = ["a.weight", "b.weight"] if rank == 0 else ["b.weight", "a.weight"]
+        params = [(n, distribute_tensor(torch.zeros(8, 8), mesh, [Shard(0)]).requires_grad_(True)) for n in names]
+        opt = Gefen(params, lr=1e-2, fused=False, factored_v_2d=False)
+        try:
+            GefenDCPState(opt).state_dict()
+            q.put(("no error", rank))
+        except RuntimeError as exc:
+            q.put(("raised", rank, str(exc)))
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_ranks_with_different_layouts_fail_before_planning():
+    """Two ranks presenting the same slots in a different order must both raise from ``state_dict()``."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_mismatch_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    msgs = [q.get(timeout=120) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(m[0] == "raised" and "different parameter layouts" in m[2] for m in msgs), msgs
+
+
+def test_async_save_stages_stand_ins_one_at_a_time(tmp_path):
+    """``async_save`` with the package's writer: the stand-ins are snapshotted to the host while staging;
+    the checkpoint reloads into a fresh optimizer with the same dense state."""
+    import torch.distributed.checkpoint as dcp
+
+    from gefen_x_b200 import Gefen, GefenDCPState, GefenFileSystemWriter, GefenSavePlanner
+    from gefen_x_b200.ckpt.lazy import LazyShard
+
+    def build():
+        g = torch.Generator().manual_seed(0)
+        ps = [("w{}".format(i), (torch.randn(16, 24, generator=g) * 0.1).requires_grad_(True)) for i in range(6)]
+        return ps, Gefen(ps, lr=1e-2, fused=False, factored_v_2d=False)
+
+    ps, opt = build()
+    for step in range(2):
+        g = torch.Generator().manual_seed(10 + step)
+        for _n, p in ps:
+            p.grad = torch.randn(p.shape, generator=g) * 0.01
+        opt.step()
+    sd = GefenDCPState(opt).state_dict()
+    want = {k: v.resolve_uncached().clone() for k, v in sd.items() if isinstance(v, LazyShard)}
+    path = str(tmp_path / "ckpt")
+    fut = dcp.async_save({"optimizer": sd}, storage_writer=GefenFileSystemWriter(path), planner=GefenSavePlanner())
+    getattr(fut, "upload_completion", fut).result()
+    with pytest.raises(RuntimeError, match="cannot be moved"):
+        sd["slot_00000000.momentum"].cpu()
+    with pytest.raises(TypeError, match="cannot be pickled"):
+        import pickle
+
+        pickle.dumps(sd["slot_00000000.momentum"])
+    ps2, opt2 = build()
+    w2 = GefenDCPState(opt2)
+    sd2 = w2.state_dict()
+    dcp.load({"optimizer": sd2}, checkpoint_id=path)
+    w2.load_state_dict(sd2)
+    again = GefenDCPState(opt2).state_dict()
+    for k, v in want.items():
+        got = again[k].resolve_uncached()
+        if k.endswith("momentum"):
+            assert (got - v).abs().max().item() <= 2e-2 * v.abs().max().item() + 1e-9, k
+    assert opt2._gefen_global_step == 2
 
 
 def test_layout_validation_single_process():

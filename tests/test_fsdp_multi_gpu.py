@@ -91,3 +91,61 @@ def test_one_optimizer_over_two_devices_matches_single_device():
         assert torch.equal(oa.state[a]["m_codebook"].cpu(), ob.state[b]["m_codebook"].cpu()), n
         torch.testing.assert_close(a.float().cpu(), b.float().cpu(), rtol=0, atol=1e-3, msg=n)
     assert all(v == 0 for v in ob.kernel_status().values())
+
+
+def _launch(world, script, *args, timeout=600):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    if world == 1:
+        cmd = [sys.executable, os.path.join(ROOT, "tests", script)] + [str(a) for a in args]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+               "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+               os.path.join(ROOT, "tests", script)] + [str(a) for a in args]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+
+
+@pytest.mark.parametrize("save_world,load_world", [(2, 1), (1, 2), (4, 2)])
+def test_trainer_checkpoint_reshards(tmp_path, save_world, load_world):
+    """Resharding checkpoint of the runtime: saved on N ranks, loaded on M; the resumed run continues on
+    the saver's loss trajectory (re-quantisation of the momentum on the new shards is the only
+    difference), and the rank-local native state dict resumes bit for bit (reference
+    tests/test_dcp_resharding.py:320-397)."""
+    if torch.cuda.device_count() < max(save_world, load_world):
+        pytest.skip("needs {} GPUs".format(max(save_world, load_world)))
+    _launch(save_world, "_fsdp_ckpt_worker.py", "save", tmp_path)
+    saved = json.load(open(tmp_path / "save_w{}.json".format(save_world)))
+    assert saved["native_resume_exact"]
+    _launch(load_world, "_fsdp_ckpt_worker.py", "load", tmp_path)
+    loaded = json.load(open(tmp_path / "load_w{}.json".format(load_world)))
+    assert loaded["step_count"] == 9
+    for a, b in zip(saved["continued"], loaded["resumed"]):
+        assert abs(a - b) <= 0.02 * abs(a), (saved, loaded)
+
+
+def test_sharded_optimizer_state_equals_single_gpu_state(tmp_path):
+    """Two ranks fed the same batch reduce to exactly the single-GPU gradient, so the sharded optimizer
+    state, gathered by rows, must be the single-GPU state: factored row / column moments (the column
+    sums cross the shards inside the kernel), weights, and the quantised momentum wherever the two runs
+    chose the same block period."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    _launch(1, "_fsdp_ckpt_worker.py", "state", tmp_path)
+    _launch(2, "_fsdp_ckpt_worker.py", "state", tmp_path)
+    one = torch.load(tmp_path / "state_w1.pt")
+    two = torch.load(tmp_path / "state_w2.pt")
+    assert set(one) == set(two) and one
+    compared_indices = 0
+    for name, a in one.items():
+        b = two[name]
+        torch.testing.assert_close(b["v_row"], a["v_row"], rtol=2e-3, atol=1e-12, msg=name)
+        for vc in b["v_col"]:
+            torch.testing.assert_close(vc, a["v_col"][0], rtol=2e-3, atol=1e-12, msg=name)
+        torch.testing.assert_close(b["v_col"][0], b["v_col"][1], rtol=0, atol=0, msg=name)   # shards agree exactly
+        torch.testing.assert_close(b["w"], a["w"], rtol=0, atol=4e-3, msg=name)
+        if all(p == a["period"] for p in b["periods"]):
+            compared_indices += 1
+            differ = (a["idx"] != b["idx"]).float().mean().item()
+            assert differ <= 0.01, (name, differ)
+            torch.testing.assert_close(b["dense"], a["dense"], rtol=0, atol=2e-2 * a["dense"].abs().max().item())
+    assert compared_indices > 0

@@ -338,6 +338,16 @@ def test_pair_gemm_matches_fp32(m, n, k, a_t, b_t, bn):
     ref2 = 0.5 * ref - 2.0 * d.float()
     err2 = (out2.float() - ref2).abs().max().item()
     assert err2 <= 2e-2 * ref2.abs().max().item() + 1e-2, err2
+    # sum of squares of the stored output from the epilogue: accumulates into the slots, and two runs
+    # agree bit for bit (every slot has one writer, also for the K-split tail tiles)
+    sq, sq2 = torch.zeros(2048, device=_dev()), torch.zeros(2048, device=_dev())
+    out3 = tcgemm.gemm(a, b, a_t=a_t, b_t=b_t, sumsq=sq)
+    tcgemm.gemm(a, b, a_t=a_t, b_t=b_t, sumsq=sq2)
+    want = out3.float().square().sum().item()
+    assert abs(sq.sum().item() - want) <= 1e-4 * want, (sq.sum().item(), want)
+    assert torch.equal(sq, sq2)
+    tcgemm.gemm(a, b, a_t=a_t, b_t=b_t, sumsq=sq)
+    assert abs(sq.sum().item() - 2 * want) <= 2e-4 * want
     # the single-CTA kernel gives the same product
     tcgemm.set_pair_kernel(False)
     try:

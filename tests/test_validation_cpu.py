@@ -185,6 +185,19 @@ CORRUPTIONS = {
     "fractional counter": ("block", lambda sd: _first(sd).__setitem__("step", torch.tensor(1.5))),
     "boolean counter": ("block", lambda sd: _first(sd).__setitem__("step", torch.tensor(True))),
     "negative counter": ("muon", lambda sd: _first(sd).__setitem__("step", torch.tensor(-1.0))),
+    # sizes that do not fit the live parameter: the kernels would index them out of bounds
+    "index rows": ("block", lambda sd: _first(sd).__setitem__(
+        "m_codebook", torch.cat((_first(sd)["m_codebook"], _first(sd)["m_codebook"])))),
+    "index period": ("block", lambda sd: _first(sd).__setitem__(
+        "m_codebook", _first(sd)["m_codebook"].reshape(-1, 2).contiguous())),
+    "magnitude count": ("block", lambda sd: _first(sd).__setitem__("m_magnitude", _first(sd)["m_magnitude"][:-1])),
+    "period not a divisor": ("block", lambda sd: _first(sd).__setitem__("automatic_period", 7)),
+    "vmean count": ("block", lambda sd: _first(sd).__setitem__(
+        "vmean", torch.cat((_first(sd)["vmean"], _first(sd)["vmean"])))),
+    "row moment length": ("factored", lambda sd: _first(sd).__setitem__("v_row", _first(sd)["v_row"][:-1])),
+    "column moment length": ("factored", lambda sd: _first(sd).__setitem__(
+        "v_col", torch.cat((_first(sd)["v_col"], _first(sd)["v_col"])))),
+    "normuon rows": ("muon", lambda sd: _first(sd).__setitem__("normuon_v", _first(sd)["normuon_v"][:-1])),
 }
 
 
