@@ -546,6 +546,35 @@ void comm_allreduce_scalar(at::IntArrayRef slot_ptrs, at::IntArrayRef flag_ptrs,
           "allreduce_scalar");
 }
 
+// out [n_tok, cols] = rows tok[] of a row-sharded table, read from the owners' shards
+void comm_gather_rows(at::IntArrayRef shard_ptrs, int64_t rows_per, int64_t rows, const Tensor& tok, Tensor out) {
+    c10::cuda::CUDAGuard guard(out.device());
+    TORCH_CHECK(tok.is_cuda() && tok.scalar_type() == at::kLong && tok.is_contiguous());
+    TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.dim() == 2 && out.size(0) == tok.numel());
+    const int64_t row_bytes = out.size(1) * out.element_size();
+    TORCH_CHECK(row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(out.data_ptr()) % 16 == 0);
+    void* p[8];
+    to_ptrs(shard_ptrs, p);
+    check(gx::launch_gather_rows(p, (int)shard_ptrs.size(), rows_per, rows, (int)row_bytes,
+                                 reinterpret_cast<const long long*>(tok.data_ptr<int64_t>()), (int)tok.numel(),
+                                 out.data_ptr(), stream()),
+          "gather_rows");
+}
+
+// dst [my_rows, cols] (bf16, zeroed) += scale * every rank's gradient rows of the tokens this rank owns
+void comm_scatter_add_rows(at::IntArrayRef tok_ptrs, at::IntArrayRef grad_ptrs, int64_t n_tok, int64_t row0,
+                           double scale, Tensor dst) {
+    c10::cuda::CUDAGuard guard(dst.device());
+    TORCH_CHECK(dst.is_cuda() && dst.scalar_type() == at::kBFloat16 && dst.is_contiguous() && dst.dim() == 2);
+    TORCH_CHECK(tok_ptrs.size() == grad_ptrs.size());
+    void *t[8], *g[8];
+    to_ptrs(tok_ptrs, t);
+    to_ptrs(grad_ptrs, g);
+    check(gx::launch_scatter_add_rows(t, g, (int)tok_ptrs.size(), (int)n_tok, row0, dst.size(0), (int)dst.size(1),
+                                      (float)scale, dst.data_ptr(), stream()),
+          "scatter_add_rows");
+}
+
 // ---------------------------------------------------------------------------
 // model operators (model_ops.cu)
 // ---------------------------------------------------------------------------
@@ -558,15 +587,29 @@ void rmsnorm_fwd(const Tensor& x, const Tensor& w, Tensor y, Tensor rstd, double
           "rmsnorm_fwd");
 }
 
+// dx = norm backward (+ res), dw = column sums of the per-CTA partials (both kernels of this file)
 void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, Tensor dx,
-                 Tensor dw_partial) {
+                 Tensor dw_partial, const c10::optional<Tensor>& res, const c10::optional<Tensor>& dw) {
     c10::cuda::CUDAGuard guard(x.device());
     TORCH_CHECK(dy.is_contiguous() && x.is_contiguous() && dx.is_contiguous());
     const int64_t d = x.size(-1);
+    const void* r = nullptr;
+    if (res.has_value() && res->defined()) {
+        TORCH_CHECK(res->is_contiguous() && res->scalar_type() == x.scalar_type() && res->numel() == x.numel(),
+                    "rmsnorm_bwd: res must match x");
+        r = res->data_ptr();
+    }
     check(gx::launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(),
                                  dx.data_ptr(), dw_partial.data_ptr<float>(), (int)dw_partial.size(0),
-                                 x.numel() / d, (int)d, dtype_code(x.scalar_type()), stream()),
+                                 x.numel() / d, (int)d, dtype_code(x.scalar_type()), stream(), r),
           "rmsnorm_bwd");
+    if (dw.has_value() && dw->defined()) {
+        TORCH_CHECK(dw->scalar_type() == at::kFloat && dw->is_contiguous() && dw->numel() == d &&
+                    dw_partial.is_contiguous() && dw_partial.size(1) == d);
+        check(gx::launch_colsum(dw_partial.data_ptr<float>(), (int)dw_partial.size(0), (int)d,
+                                dw->data_ptr<float>(), stream()),
+              "rmsnorm_bwd colsum");
+    }
 }
 
 int64_t rmsnorm_bwd_partials(int64_t rows, int64_t d) { return gx::rmsnorm_bwd_partials(rows, (int)d); }
@@ -714,10 +757,14 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("comm_reduce_segments(int world, Tensor segs, int n_segs, Tensor unit_prefix, int total_units, "
           "float scale, Tensor? partials, int ctas, int dtype) -> ()");
     m.def("comm_copy_list(Tensor table, int device_index) -> ()", &comm_copy_list);
+    m.def("comm_gather_rows(int[] shard_ptrs, int rows_per, int rows, Tensor tok, Tensor(a!) out) -> ()");
+    m.def("comm_scatter_add_rows(int[] tok_ptrs, int[] grad_ptrs, int n_tok, int row0, float scale, "
+          "Tensor(a!) dst) -> ()");
     m.def("comm_allreduce_scalar(int[] slot_ptrs, int[] flag_ptrs, int rank, Tensor local_val, "
           "Tensor(a!) out, int epoch, int max_iters, Tensor? status) -> ()");
     m.def("rmsnorm_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!) rstd, float eps) -> ()");
-    m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor(a!) dx, Tensor(b!) dw_partial) -> ()");
+    m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor(a!) dx, Tensor(b!) dw_partial, "
+          "Tensor? res, Tensor(c!)? dw) -> ()");
     m.def("rope(Tensor(a!) dst, Tensor src, Tensor cos, Tensor sin, int seq_len, int n_heads, int head_dim, "
           "bool inverse, bool interleaved) -> ()");
     m.def("flash_attention_fwd(Tensor q, Tensor k, Tensor v, Tensor(a!) out, Tensor(b!) lse, int seq, "
@@ -746,6 +793,8 @@ TORCH_LIBRARY_IMPL(gefenx, CUDA, m) {
     m.impl("gemm_ag_bf16", &gemm_ag_bf16);
     m.impl("comm_wait", &comm_wait);
     m.impl("comm_gather", &comm_gather);
+    m.impl("comm_gather_rows", &comm_gather_rows);
+    m.impl("comm_scatter_add_rows", &comm_scatter_add_rows);
     m.impl("comm_scatter_apply", &comm_scatter_apply);
     m.impl("comm_reduce_segments", &comm_reduce_segments);
     m.impl("comm_allreduce_scalar", &comm_allreduce_scalar);

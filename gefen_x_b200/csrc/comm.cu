@@ -196,6 +196,52 @@ __global__ void __launch_bounds__(256) scatter_apply_kernel(const ApplySeg* __re
     }
 }
 
+
+// ---- sparse embedding: rows of a row-sharded table, fetched from / reduced into their owners ----
+// The token embedding is read at a few thousand rows per step; gathering the whole table from the
+// peers (and reducing a dense gradient of its size) moves a gigabyte for a few megabytes of use.
+// Row r of the table lives on rank r / rows_per, at row r % rows_per of that rank's shard.
+struct RowPeers { const char* base[kMaxSrc]; };
+
+// out[t, :] = table[tok[t], :] read from the owner's shard by peer loads (one CTA per token).
+__global__ void __launch_bounds__(128) gather_rows_kernel(RowPeers shard, long long rows_per, long long rows,
+                                                         int row_units, const long long* __restrict__ tok,
+                                                         uint4* __restrict__ out) {
+    const long long t = blockIdx.x;
+    long long r = tok[t];
+    if (r < 0 || r >= rows) r = 0;          // out-of-range ids read row 0 (as a clamped lookup)
+    const int owner = (int)(r / rows_per);
+    const uint4* src = reinterpret_cast<const uint4*>(shard.base[owner]) + (r - owner * rows_per) * row_units;
+    uint4* dst = out + t * row_units;
+    uint4 v[4];
+    for (int i0 = threadIdx.x; i0 < row_units; i0 += 128 * 4) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) if (i0 + j * 128 < row_units) v[j] = src[i0 + j * 128];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) if (i0 + j * 128 < row_units) dst[i0 + j * 128] = v[j];
+    }
+}
+
+// dst[row - row0, :] += scale * grad_r[t, :] for every rank r and every token t of rank r whose row
+// this rank owns (dst = this rank's bf16 gradient shard, zeroed beforehand).  The token ids and
+// gradient rows of rank r are read from its arena.  bf16x2 atomic adds: tokens may repeat.
+struct TokPeers { const long long* tok[kMaxSrc]; const __nv_bfloat162* grad[kMaxSrc]; };
+
+__global__ void __launch_bounds__(128) scatter_add_rows_kernel(TokPeers peers, int world, int n_tok,
+                                                              long long row0, long long my_rows, int cols2,
+                                                              float scale, __nv_bfloat162* __restrict__ dst) {
+    const int r = blockIdx.x / n_tok, t = blockIdx.x - r * n_tok;
+    if (r >= world) return;
+    const long long row = peers.tok[r][t] - row0;
+    if (row < 0 || row >= my_rows) return;
+    const __nv_bfloat162* src = peers.grad[r] + (long long)t * cols2;
+    __nv_bfloat162* out = dst + row * cols2;
+    for (int i = threadIdx.x; i < cols2; i += 128) {
+        const float2 f = __bfloat1622float2(src[i]);
+        atomicAdd(out + i, __floats2bfloat162_rn(f.x * scale, f.y * scale));
+    }
+}
+
 }  // namespace
 
 cudaError_t launch_scatter_apply(const ApplySeg* segs_dev, int n_segs, const long long* unit_prefix_dev,
@@ -268,6 +314,32 @@ cudaError_t launch_allreduce_scalar(void* const* slot_ptrs, void* const* flag_pt
     PtrList s{}, f{};
     for (int i = 0; i < world; ++i) { s.p[i] = slot_ptrs[i]; f.p[i] = flag_ptrs[i]; }
     allreduce_scalar_kernel<<<1, 32, 0, st>>>(s, f, world, rank, local_val, out, epoch, max_iters, status);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gather_rows(void* const* shard_ptrs, int world, long long rows_per, long long rows,
+                               int row_bytes, const long long* tok_dev, int n_tok, void* out, cudaStream_t st) {
+    if (n_tok <= 0) return cudaSuccess;
+    if (world < 1 || world > kMaxSrc || row_bytes % 16 || rows_per <= 0) return cudaErrorInvalidValue;
+    RowPeers rp{};
+    for (int i = 0; i < world; ++i) rp.base[i] = static_cast<const char*>(shard_ptrs[i]);
+    gather_rows_kernel<<<n_tok, 128, 0, st>>>(rp, rows_per, rows, row_bytes / 16, tok_dev,
+                                               static_cast<uint4*>(out));
+    return cudaGetLastError();
+}
+
+cudaError_t launch_scatter_add_rows(void* const* tok_ptrs, void* const* grad_ptrs, int world, int n_tok,
+                                    long long row0, long long my_rows, int cols, float scale, void* dst,
+                                    cudaStream_t st) {
+    if (n_tok <= 0 || my_rows <= 0) return cudaSuccess;
+    if (world < 1 || world > kMaxSrc || cols % 2) return cudaErrorInvalidValue;
+    TokPeers tp{};
+    for (int i = 0; i < world; ++i) {
+        tp.tok[i] = static_cast<const long long*>(tok_ptrs[i]);
+        tp.grad[i] = static_cast<const __nv_bfloat162*>(grad_ptrs[i]);
+    }
+    scatter_add_rows_kernel<<<world * n_tok, 128, 0, st>>>(tp, world, n_tok, row0, my_rows, cols / 2, scale,
+                                                           static_cast<__nv_bfloat162*>(dst));
     return cudaGetLastError();
 }
 

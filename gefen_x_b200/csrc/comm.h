@@ -52,4 +52,14 @@ cudaError_t launch_allreduce_scalar(void* const* slot_ptrs, void* const* flag_pt
                                     const float* local_val, float* out, unsigned epoch,
                                     long long max_iters, int* status, cudaStream_t st);
 
+// Sparse embedding over a row-sharded table (row r on rank r / rows_per).
+// out[t, :] = table[tok[t], :] by peer loads; shard_ptrs[r] = start of rank r's rows; row_bytes % 16 == 0.
+cudaError_t launch_gather_rows(void* const* shard_ptrs, int world, long long rows_per, long long rows,
+                               int row_bytes, const long long* tok_dev, int n_tok, void* out, cudaStream_t st);
+// dst[tok - row0, :] += scale * grad_r[t, :] over every rank's token list (bf16, dst zeroed by the caller);
+// tok_ptrs[r] / grad_ptrs[r]: rank r's int64 ids [n_tok] and bf16 rows [n_tok, cols] in its arena.
+cudaError_t launch_scatter_add_rows(void* const* tok_ptrs, void* const* grad_ptrs, int world, int n_tok,
+                                    long long row0, long long my_rows, int cols, float scale, void* dst,
+                                    cudaStream_t st);
+
 }  // namespace gx

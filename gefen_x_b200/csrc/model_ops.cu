@@ -70,12 +70,15 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_fwd_kernel(const T* __restri
     }
 }
 
-// dx = rstd * (g - x * rstd^2 * mean(g * x)),  g = dy * w ;  dw += dy * x * rstd
+// dx = rstd * (g - x * rstd^2 * mean(g * x)) [+ res],  g = dy * w ;  dw += dy * x * rstd
+// `res` (optional) is the gradient that bypasses the norm on the residual path: adding it here saves
+// the separate elementwise pass over [rows, d].
 template <typename T, int CH>
 __global__ void __launch_bounds__(kThreads) rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
                                                                const T* __restrict__ w, const float* __restrict__ rstd,
                                                                T* __restrict__ dx, float* __restrict__ dw_partial,
-                                                               long long rows, int d, int lanes) {
+                                                               long long rows, int d, int lanes,
+                                                               const T* __restrict__ res) {
     __shared__ float sh[kThreads / 32];
     const int groups = kThreads / lanes;
     const int gi = threadIdx.x / lanes, lane = threadIdx.x % lanes;
@@ -120,6 +123,12 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_bwd_kernel(const T* __restri
                 Vec8<T>::load(w + c, ww);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) a[e] = rs * (a[e] * ww[e] - b[e] * coef);
+                if (res) {
+                    float rr[8];
+                    Vec8<T>::load(res + r * d + c, rr);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) a[e] += rr[e];
+                }
                 Vec8<T>::store(dx + r * d + c, a);
             }
         }
@@ -132,6 +141,26 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_bwd_kernel(const T* __restri
 #pragma unroll
             for (int e = 0; e < 8; ++e) out[c + e] = dw[k][e];
         }
+    }
+}
+
+// out[c] = sum_r part[r, c]: the per-CTA partial weight gradients of the norm backward.  One CTA per 32
+// columns, 8 row groups per CTA (coalesced 128-byte rows), fixed summation order.
+__global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ part, int n_rows, int d,
+                                                     float* __restrict__ out) {
+    __shared__ float sh[8][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + tx;
+    float acc = 0.f;
+    if (c < d)
+        for (int r = ty; r < n_rows; r += 8) acc += part[(long long)r * d + c];
+    sh[ty][tx] = acc;
+    __syncthreads();
+    if (ty == 0 && c < d) {
+        float t = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t += sh[i][tx];
+        out[c] = t;
     }
 }
 
@@ -370,9 +399,15 @@ cudaError_t launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rst
     return cudaGetLastError();
 }
 
+cudaError_t launch_colsum(const float* part, int n_rows, int d, float* out, cudaStream_t st) {
+    if (d <= 0) return cudaSuccess;
+    colsum_kernel<<<(d + 31) / 32, 256, 0, st>>>(part, n_rows, d, out);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
                                float* dw_partial, int n_partial, long long rows, int d, int dtype,
-                               cudaStream_t st) {
+                               cudaStream_t st, const void* res) {
     if (rows <= 0) return cudaSuccess;
     if (d % 8) return cudaErrorInvalidValue;
     const int lanes = lanes_for(d);
@@ -382,10 +417,10 @@ cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
     const int ch = ((d + 7) / 8 + lanes - 1) / lanes;
     if (ch > 8) return cudaErrorInvalidValue;
     GX_DISPATCH(dtype,
-        if (ch <= 1) rmsnorm_bwd_kernel<T, 1><<<grid, kThreads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_partial, rows, d, lanes);
-        else if (ch <= 2) rmsnorm_bwd_kernel<T, 2><<<grid, kThreads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_partial, rows, d, lanes);
-        else if (ch <= 4) rmsnorm_bwd_kernel<T, 4><<<grid, kThreads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_partial, rows, d, lanes);
-        else rmsnorm_bwd_kernel<T, 8><<<grid, kThreads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_partial, rows, d, lanes));
+        if (ch <= 1) rmsnorm_bwd_kernel<T, 1><<<grid, kThreads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_partial, rows, d, lanes, (const T*)res);
+        else if (ch <= 2) rmsnorm_bwd_kernel<T, 2><<<grid, kThreads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_partial, rows, d, lanes, (const T*)res);
+        else if (ch <= 4) rmsnorm_bwd_kernel<T, 4><<<grid, kThreads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_partial, rows, d, lanes, (const T*)res);
+        else rmsnorm_bwd_kernel<T, 8><<<grid, kThreads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_partial, rows, d, lanes, (const T*)res));
     return cudaGetLastError();
 }
 

@@ -8,9 +8,12 @@ cudaError_t launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rst
                                float eps, int dtype, cudaStream_t st);
 // number of rows the backward kernel writes into dw_partial for this problem
 int rmsnorm_bwd_partials(long long rows, int d);
+// `res` (optional, same shape as dx) is added to dx: the gradient of the residual path.
 cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
                                float* dw_partial, int n_partial, long long rows, int d, int dtype,
-                               cudaStream_t st);
+                               cudaStream_t st, const void* res = nullptr);
+// out[c] = sum over the n_rows rows of part [n_rows, d] (fp32), fixed order.
+cudaError_t launch_colsum(const float* part, int n_rows, int d, float* out, cudaStream_t st);
 // dst / src: [tokens, n_heads, head_dim] with dst_stride / src_stride elements between tokens
 // (dst may alias src)
 cudaError_t launch_rope(void* dst, const void* src, long long dst_stride, long long src_stride,

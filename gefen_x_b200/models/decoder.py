@@ -194,9 +194,9 @@ def layer_backward(cfg: ModelConfig, w: Dict[str, torch.Tensor], gw: Dict[str, t
     dgu = G.mlp_down_dgrad(dy2, w["mlp.down_proj.weight"], saved["gu"])   # SwiGLU derivative fused
     wgrad("wgu", dgu, saved["h2"])
     dh2 = G.mm_nn(dgu, w["wgu"])
-    dx2n, dw = M.rmsnorm_bwd(dh2, saved["x2"], w["post_attention_layernorm.weight"], saved["rstd2"])
+    # the residual branch's gradient (dy2) is added inside the norm's backward kernel
+    dx2, dw = M.rmsnorm_bwd(dh2, saved["x2"], w["post_attention_layernorm.weight"], saved["rstd2"], res=dy2)
     put("post_attention_layernorm.weight", dw)
-    dx2 = dy2 + dx2n
     # attention
     wgrad("self_attn.o_proj.weight", dx2, saved["a"])
     da = G.mm_nn(dx2, w["self_attn.o_proj.weight"]).reshape(B, S, nq, hd)
@@ -220,9 +220,9 @@ def layer_backward(cfg: ModelConfig, w: Dict[str, torch.Tensor], gw: Dict[str, t
         dqkv[:, qd + kd:].copy_(dv.reshape(T, kd))
     wgrad("wqkv", dqkv, saved["h1"])
     dh1 = G.mm_nn(dqkv, w["wqkv"])
-    dx1n, dw = M.rmsnorm_bwd(dh1, saved["x"], w["input_layernorm.weight"], saved["rstd1"])
+    dx, dw = M.rmsnorm_bwd(dh1, saved["x"], w["input_layernorm.weight"], saved["rstd1"], res=dx2)
     put("input_layernorm.weight", dw)
-    return (dx2 + dx1n).reshape(B, S, H)
+    return dx.reshape(B, S, H)
 
 
 class _LayerFn(torch.autograd.Function):

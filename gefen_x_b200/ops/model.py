@@ -42,9 +42,10 @@ def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float) -> Tuple[torch.Ten
     return (xf * rstd * w.float()).to(x.dtype), rstd.reshape(-1)
 
 
-def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor,
-                rstd: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Returns (dx, dw) with dw in fp32."""
+def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor, rstd: torch.Tensor,
+                res: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Returns ``(dx, dw)`` with ``dw`` in fp32.  ``res`` (optional, shaped like ``x``) is added to
+    ``dx`` inside the kernel: the gradient that reaches ``x`` along the residual path."""
     d = x.shape[-1]
     rows = x.numel() // d
     if _use_kernel(x) and d % 8 == 0 and d <= 16384:
@@ -53,12 +54,15 @@ def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor,
         dx = torch.empty_like(x)
         npart = int(ops().rmsnorm_bwd_partials(rows, d))
         part = torch.empty(npart, d, dtype=torch.float32, device=x.device)
-        ops().rmsnorm_bwd(dy, x, w.contiguous(), rstd, dx, part)
-        return dx, part.sum(0)
+        dw = torch.empty(d, dtype=torch.float32, device=x.device)
+        ops().rmsnorm_bwd(dy, x, w.contiguous(), rstd, dx, part, None if res is None else res.contiguous(), dw)
+        return dx, dw
     xf, dyf, wf = x.float().reshape(rows, d), dy.float().reshape(rows, d), w.float()
     r = rstd.reshape(rows, 1)
     g = dyf * wf
     dx = r * (g - xf * (r * r) * (g * xf).sum(-1, keepdim=True) / d)
+    if res is not None:
+        dx = dx + res.float().reshape(rows, d)
     dw = (dyf * xf * r).sum(0)
     return dx.reshape(x.shape).to(x.dtype), dw
 

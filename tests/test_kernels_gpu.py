@@ -192,6 +192,11 @@ def test_model_kernels_match_torch():
         M.rmsnorm_ref(xr, wr, 1e-6).backward(dy.float())
         assert torch.allclose(dx.float(), xr.grad, rtol=3e-2, atol=3e-2)
         assert torch.allclose(dw, wr.grad, rtol=2e-2, atol=5e-2)
+        # the residual-path gradient added inside the kernel
+        res = torch.randn(rows, d, generator=g).bfloat16().to(dev)
+        dx2, dw2 = M.rmsnorm_bwd(dy, x, w, rstd, res=res)
+        assert torch.allclose(dx2.float(), xr.grad + res.float(), rtol=3e-2, atol=3e-2)
+        assert torch.equal(dw2, dw)
     # rope (both layouts, forward then inverse is the identity up to bf16 rounding)
     B, S, n, hd = 2, 33, 4, 128
     cos, sin = M.rope_tables(S, hd, 1e6, dev)
