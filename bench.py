@@ -253,7 +253,7 @@ def run_ours(args):
         # how this implementation ran the config (kept out of `config`, which both arms share)
         "impl_config": {"rs_mode": trainer.rs_mode, "ag_gemm": trainer.ag_gemm, "attention": args.attn,
                         "gemm": args.gemm, "gather": trainer.gather_mode, "reduce": trainer.reduce_mode,
-                        "reduce_ctas": trainer.reduce_ctas},
+                        "reduce_ctas": trainer.reduce_ctas, "sparse_embedding": trainer.sparse_embed},
     }
     if rank == 0:
         print(json.dumps(out), flush=True)

@@ -63,11 +63,23 @@ def native_state_dict(tr) -> Dict[str, Any]:
     for g in tr.all_groups:
         n = g.shard_numel[tr.rank] if tr.world > 1 else g.full_numel
         weights[g.name] = g.shard_w[:n].detach().clone()
+    # a snapshot: the optimizer's own state dict refers to the live state tensors, which the kernels
+    # keep updating in place
     out = {"identity": ident, "step_count": int(tr.step_count), "weights": weights,
-           "optimizer": tr.opt.state_dict()}
+           "optimizer": _snapshot(tr.opt.state_dict())}
     if tr.muon is not None:
-        out["muon"] = tr.muon.opt.state_dict()
+        out["muon"] = _snapshot(tr.muon.opt.state_dict())
     return out
+
+
+def _snapshot(obj):
+    if torch.is_tensor(obj):
+        return obj.detach().clone()
+    if isinstance(obj, dict):
+        return {k: _snapshot(v) for k, v in obj.items()}
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_snapshot(v) for v in obj)
+    return obj
 
 
 def load_native_state_dict(tr, state: Dict[str, Any]) -> None:

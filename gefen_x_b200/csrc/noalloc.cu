@@ -56,6 +56,21 @@ extern "C" int gefenx_clip_coef_noalloc(const void* grad, long long numel, int d
                  numel, (long long)GEFENX_NOALLOC_MAX_ELEMS);
         return 2;
     }
+    // the scratch array is resolved for the current device: both buffers must live there
+    {
+        int dev = -1;
+        cudaPointerAttributes ga{}, ca{};
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaPointerGetAttributes(&ga, grad) != cudaSuccess ||
+            cudaPointerGetAttributes(&ca, coef_out) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(1, "gefenx_clip_coef_noalloc: could not identify the device of grad / coef_out");
+        }
+        const bool g_ok = (ga.type == cudaMemoryTypeDevice || ga.type == cudaMemoryTypeManaged) && ga.device == dev;
+        const bool c_ok = (ca.type == cudaMemoryTypeDevice || ca.type == cudaMemoryTypeManaged) && ca.device == dev;
+        if (!g_ok || !c_ok)
+            return fail(1, "gefenx_clip_coef_noalloc: grad and coef_out must be device memory of the current device");
+    }
     float* partials = scratch_for_current_device();
     if (partials == nullptr)
         return fail(3, "gefenx_clip_coef_noalloc: could not resolve the device scratch array");

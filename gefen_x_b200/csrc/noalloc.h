@@ -12,7 +12,9 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#ifdef __cplusplus
 extern "C" {
+#endif
 
 // Largest input, in elements, that one call accepts (one partial sum per 16384 elements,
 // 65536 partial sums = 256 KiB of static device memory per GPU that loads the library).
@@ -23,14 +25,22 @@ extern "C" {
 //             16-byte aligned
 //   coef_out  device pointer to two floats (written by the call)
 //   stream    stream to run on
-// Returns 0 on success; 1 for a null / misaligned pointer or a bad dtype; 2 when numel
+//             and on the device that is current when the call is made
+// Returns 0 on success; 1 for a null / misaligned pointer, a bad dtype, or a `grad` / `coef_out`
+// that does not live on the current device (the scratch array is per device: with another device
+// current the call would clear and fill the wrong GPU's array); 2 when numel
 // exceeds GEFENX_NOALLOC_MAX_ELEMS (nothing is launched); 3 when the device-side array
 // could not be resolved; 4 when a launch failed.  `gefenx_noalloc_last_error()` returns a
 // text for the last non-zero code of the calling thread.
 //
 // The call allocates nothing: no cudaMalloc / cudaFree and no allocating library routine.
 // The first call on a device resolves the address of the static array for that device
-// (with that device current); make that first call before any stream capture.  Every
+// (with that device current); make that first call before any stream capture.  One thing
+// outside this code's control happens on that first call: with lazy module loading (the CUDA
+// default) the driver loads the library's device image when it is first touched, and that
+// loading takes device memory (the image itself, this array included).  So make the first
+// call on every device while allocation is still allowed -- before the pool is frozen, before
+// the device is filled -- or set CUDA_MODULE_LOADING=EAGER; later calls touch no allocator.  Every
 // call uses the same array, which keeps the previous call's partial sums until the next
 // call clears the part it is going to use, so two calls whose kernels can overlap on the
 // GPU (different streams, no dependency) race: serialise them.
@@ -39,4 +49,6 @@ int gefenx_clip_coef_noalloc(const void* grad, long long numel, int dtype, float
 
 const char* gefenx_noalloc_last_error(void);
 
+#ifdef __cplusplus
 }  // extern "C"
+#endif

@@ -15,7 +15,12 @@ def available(required: bool = False) -> bool:
     False; the CUDA code paths use it so that a missing extension on a GPU box
     is loud rather than a silent fall back to torch ops.
     """
-    return _build.load_cuda(required=required)
+    ok = _build.load_cuda(required=required)
+    if ok:
+        from . import _fake
+
+        _fake.register()
+    return ok
 
 
 # kernels launched by one call of each operator (for launch accounting)

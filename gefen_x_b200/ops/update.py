@@ -278,6 +278,7 @@ class Plan:
                 tile_k //= 2
         self.scratch = torch.zeros(max(total, 1), dtype=torch.float32, device=device)
         self.scal_dev = torch.zeros(self.n, 4, dtype=torch.float32, device=device)
+        self._uploaded_scalars = None          # what scal_dev holds (constant for momentum-emit plans)
         buf = (ctypes.c_ubyte * (stride * self.n))()
         tile_start = [0]
         base = self.scratch.data_ptr()
@@ -417,10 +418,17 @@ class Plan:
         added to it inside the kernels, so that CUDA-graph replays, which re-run the launch with
         the same arguments, still draw fresh noise as long as the counter advances on the device."""
         if self.uses_host_scalars and (phases & 1 or self.kind == "block"):
-            # A fresh pageable tensor per step: the runtime stages it before the call
-            # returns, so the host may run ahead of the device without racing on it.
-            h = torch.tensor([it.scalars for it in items], dtype=torch.float32)
-            self.scal_dev.copy_(h, non_blocking=True)
+            scalars = tuple(tuple(it.scalars) for it in items)
+            if scalars != self._uploaded_scalars:
+                if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():
+                    # a captured host-to-device copy would replay from host memory that is gone
+                    raise RuntimeError("the per-step scalars of this plan live on the host and changed: run the "
+                                       "step with capturable=True (device-resident scalars) to capture it")
+                # A fresh pageable tensor per upload: the runtime stages it before the call
+                # returns, so the host may run ahead of the device without racing on it.
+                h = torch.tensor(scalars, dtype=torch.float32)
+                self.scal_dev.copy_(h, non_blocking=True)
+                self._uploaded_scalars = scalars
         code = DTYPE_CODE[self.dtype]
         seed = 0 if sr_seed is None else int(sr_seed)
         if self.kind == "factored":

@@ -1191,9 +1191,15 @@ class Gefen(torch.optim.Optimizer):
             return True
         return p.grad is not None
 
+    @torch.compiler.disable
     @torch.no_grad()
     def step(self, closure=None):
-        """One optimisation step; ``closure`` (if given) runs first under ``enable_grad``."""
+        """One optimisation step; ``closure`` (if given) runs first under ``enable_grad``.
+
+        Excluded from ``torch.compile`` tracing: inside a compiled training step it runs eagerly (its
+        kernels are launched through pre-built plans of raw device addresses, which a tracer must not
+        reorder or drop); to remove the launch overhead capture it in a CUDA graph with
+        ``capturable=True``."""
         self._assert_capturable_if_capturing()
         loss = None
         if closure is not None:

@@ -297,6 +297,7 @@ class GefenMuonHybrid(torch.optim.Optimizer):
                             pgs.append(pg)
         return pgs
 
+    @torch.compiler.disable
     @torch.no_grad()
     def step(self, closure=None):
         # instance step hooks with torch's calling convention: hook(optimizer, args, kwargs), args

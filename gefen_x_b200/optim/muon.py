@@ -212,8 +212,15 @@ class GefenMuon(Gefen):
         self._colocate_param_state_(state, grad.device)
         return state
 
-    def _prepare_muon_momentum(self, group, name: str, p: torch.Tensor, grad: torch.Tensor) -> torch.Tensor:
-        """Advance the quantised momentum with ``grad``; return the dense Newton–Schulz input."""
+    def _prepare_muon_momentum(self, group, name: str, p: torch.Tensor, grad: torch.Tensor,
+                               private: bool = False) -> torch.Tensor:
+        """Advance the quantised momentum with ``grad``; return the dense Newton–Schulz input.
+
+        The dense momentum is scratch: it is written into one buffer per (shape, dtype, device) that the
+        next matrix of that shape overwrites once Newton–Schulz has consumed it, so the launch plan of
+        a matrix keeps the same addresses from step to step (no rebuild, and nothing to allocate or
+        upload while a CUDA graph is being captured).  ``private=True`` (batched Newton–Schulz, which
+        holds many of them at once) returns a tensor of its own."""
         state = self._muon_state(name, p, grad)
         state["step"] += 1
         beta = group["momentum"]
@@ -225,7 +232,14 @@ class GefenMuon(Gefen):
             from ..ops import update as _u
 
             dev = grad.device
-            out = torch.empty(grad.shape, dtype=grad.dtype, device=dev)
+            if private:
+                out = torch.empty(grad.shape, dtype=grad.dtype, device=dev)
+            else:
+                scratch = self.__dict__.setdefault("_emit_scratch", {})
+                key = (tuple(grad.shape), grad.dtype, dev)
+                out = scratch.get(key)
+                if out is None:
+                    out = scratch[key] = torch.empty(grad.shape, dtype=grad.dtype, device=dev)
             _u.momentum_emit(grad.contiguous(), state, out, cb, self._gefen_thresholds_on(dev),
                              self._gefen_codebook_lut_on(dev), beta=beta, nesterov=bool(group["nesterov"]),
                              gscale=self._grad_scale_tensor(dev))
@@ -321,9 +335,26 @@ class GefenMuon(Gefen):
 
     def _apply_muon_update(self, group, p: torch.Tensor, update: torch.Tensor, sharded: bool,
                            approx: bool) -> None:
-        lr = self._lr_scalar(group)
+        """``p <- p * (1 - lr * wd) - lr * ratio * update`` on this rank's rows.
+
+        A tensor learning rate is never read back to the host: under ``capturable=True`` (and always
+        while a CUDA graph is being captured) the scalars stay on the device, so a captured step
+        follows in-place changes of the lr tensor on replay (reference ``gefen_muon.py:1243-1300``)."""
         ratio = adjust_lr_ratio(group["adjust_lr_fn"], p.shape)
         target = p.to_local() if sharded else p
+        lr = group["lr"]
+        on_device = torch.is_tensor(lr) and (self.capturable or (
+            lr.is_cuda and torch.cuda.is_current_stream_capturing()))
+        if on_device:
+            lr_t = lr.to(device=target.device, dtype=torch.float32).reshape(())
+            if group["weight_decay"] > 0.0:
+                target.mul_((1.0 - lr_t * group["weight_decay"]).to(target.dtype))
+            if target.numel() == 0:
+                return
+            local_update = update if (approx or not sharded) else self._shard_like(update, p)
+            target.sub_((local_update.float() * (lr_t * ratio)).to(target.dtype))
+            return
+        lr = self._lr_scalar(group)
         if group["weight_decay"] > 0.0:
             target.mul_(1 - lr * group["weight_decay"])
         if target.numel() == 0:
@@ -371,6 +402,7 @@ class GefenMuon(Gefen):
                     "GefenMuon: ranks disagree on which sharded parameters have gradients this "
                     "step; refusing to enter the gather collectives")
 
+    @torch.compiler.disable
     @torch.no_grad()
     def step(self, closure=None):
         self._assert_capturable_if_capturing()
@@ -451,7 +483,7 @@ class GefenMuon(Gefen):
                 for g_, n, p, grad in members:
                     self._apply_muon_update(g_, p, self._compute_muon_update(g_, n, p, grad), False, False)
                 continue
-            moms = [self._prepare_muon_momentum(g_, n, p, grad) for g_, n, p, grad in members]
+            moms = [self._prepare_muon_momentum(g_, n, p, grad, private=True) for g_, n, p, grad in members]
             sched = NS.resolve_schedule(g.get("ns_schedule"), g["ns_coefficients"], g["ns_steps"])
             per = max(1, self.batched_ns_workspace_bytes // max(1, 16 * moms[0].numel()))
             for s in range(0, len(moms), per):
@@ -461,18 +493,47 @@ class GefenMuon(Gefen):
                     self._apply_muon_update(g_, p, upd.contiguous(), False, False)
 
     def _step_distributed(self, items, stable) -> None:
-        """Parallel-Muon: owners orthogonalise, the bf16 update is broadcast, everyone keeps its rows."""
+        """Parallel-Muon in buckets of ``world`` matrices (reference ``gefen_muon.py:1821-1900``):
+
+        1. every rank joins the all-gather of every gradient of the bucket and keeps only the
+           matrices it owns (owner = stable parameter index mod world, so a matrix's momentum never
+           moves when unrelated gradients come and go);
+        2. the owners orthogonalise *their* matrices at the same time -- no collective in this
+           phase, which is where the mode gets its parallelism;
+        3. every update is broadcast from its owner (bf16) and each rank keeps its rows.
+        """
         import torch.distributed as dist
 
+        by_pg: Dict[int, Tuple[Any, list]] = {}
         for g, n, p in items:
-            pg, world, rank = self._process_group_of(p)
-            owner = stable_distributed_owner(stable[p], world)
-            full_grad = p.grad.full_tensor().detach()          # all-gather
-            update = torch.empty(full_grad.shape, dtype=torch.bfloat16, device=full_grad.device)
-            if rank == owner:
-                update.copy_(self._compute_muon_update(g, n, p, full_grad))
-            dist.broadcast(update, src=dist.get_global_rank(pg, owner), group=pg)
-            self._apply_muon_update(g, p, update, True, False)
+            pg, _world, _rank = self._process_group_of(p)
+            by_pg.setdefault(id(pg), (pg, []))[1].append((g, n, p))
+        for pg, pg_items in by_pg.values():
+            world = dist.get_world_size(pg)
+            rank = dist.get_rank(pg)
+            for b in range(0, len(pg_items), world):
+                bucket = pg_items[b:b + world]
+                owners = [stable_distributed_owner(stable[p], world) for _g, _n, p in bucket]
+                owned = []
+                for k, (g, n, p) in enumerate(bucket):                 # phase 1: matched gathers only
+                    full_grad = p.grad.full_tensor().detach()
+                    if owners[k] == rank:
+                        owned.append((k, g, n, p, full_grad))
+                    del full_grad
+                updates: Dict[int, torch.Tensor] = {}
+                for k, g, n, p, full_grad in owned:                    # phase 2: owners work concurrently
+                    updates[k] = self._compute_muon_update(g, n, p, full_grad)
+                owned = None
+                for k, (g, n, p) in enumerate(bucket):                 # phase 3: broadcast and apply
+                    if owners[k] == rank:
+                        buf = updates.pop(k).contiguous()
+                        if buf.dtype != torch.bfloat16:
+                            buf = buf.to(torch.bfloat16)
+                    else:
+                        buf = torch.empty(tuple(p.shape), dtype=torch.bfloat16, device=p.to_local().device)
+                    dist.broadcast(buf, src=dist.get_global_rank(pg, owners[k]), group=pg)
+                    self._apply_muon_update(g, p, buf, True, False)
+                    buf = None
 
     # ------------------------------------------------------------------
     # checkpoint: distributed mode keeps momentum on the owner only
@@ -536,11 +597,87 @@ class GefenMuon(Gefen):
                                             "consolidated": consolidated, "groups": groups}
         return sd
 
+    def _validate_distributed_manifest(self, sd, manifest) -> None:
+        """A consolidated ``distributed`` checkpoint says, per matrix, who owned it at which world size
+        and which state it carries.  Everything that can be checked against the live optimizer is
+        checked before the load starts: version and ownership rule, the consolidated flag, one entry
+        per live parameter in order with the same name and global shape, owners that follow the
+        ownership rule, and initialised entries whose momentum is present and sized for the full
+        matrix (reference ``gefen_muon.py:2609-2748``)."""
+        def refuse(why):
+            return ValueError("GefenMuon.load_state_dict refused the distributed checkpoint: " + why)
+
+        if not isinstance(manifest, dict):
+            raise refuse("the manifest is not a mapping")
+        if manifest.get("version") not in (1, 2):
+            raise refuse("manifest version {!r}, expected 1 or 2".format(manifest.get("version")))
+        if manifest.get("ownership") != "stable_full_param_index_v1":
+            raise refuse("ownership scheme {!r}, expected 'stable_full_param_index_v1'".format(
+                manifest.get("ownership")))
+        saved_state = sd.get("state", {})
+        if not isinstance(saved_state, dict):
+            raise refuse("the 'state' payload is not a mapping")
+        if manifest.get("consolidated") is not True:
+            # only the saving rank's own matrices are inside: usable on the same single rank only
+            if any(self._process_group_of(p)[1] > 1 for g in self.param_groups for p in g["params"]):
+                raise refuse("the checkpoint is not consolidated (it holds one rank's momentum only)")
+        if manifest.get("version") == 1:
+            return
+        groups = manifest.get("groups")
+        if not isinstance(groups, (list, tuple)):
+            raise refuse("the owner manifest is missing or is not a list")
+        entries = []
+        for gi, grp in enumerate(groups):
+            if not isinstance(grp, dict) or not isinstance(grp.get("params"), (list, tuple)):
+                raise refuse("manifest group {} is malformed".format(gi))
+            ws = grp.get("world_size")
+            if isinstance(ws, bool) or not isinstance(ws, int) or ws < 1:
+                raise refuse("manifest group {} has world_size {!r}".format(gi, ws))
+            for e in grp["params"]:
+                if not isinstance(e, dict):
+                    raise refuse("manifest group {} holds a malformed parameter entry".format(gi))
+                entries.append((ws, e))
+        live = [p for g in self.param_groups for p in g["params"]]
+        if len(entries) != len(live):
+            raise refuse("the manifest lists {} parameters, the optimizer has {}".format(len(entries), len(live)))
+        saved_ids = [pid for g in sd.get("param_groups", ()) for pid in g.get("params", ())]
+        for pos, ((ws, e), p) in enumerate(zip(entries, live)):
+            sid = e.get("saved_id")
+            if isinstance(sid, bool) or not isinstance(sid, int) or sid != pos:
+                raise refuse("entry {} carries saved_id {!r}".format(pos, sid))
+            if e.get("name") != self._param_name(p):
+                raise refuse("entry {} is {!r}, the live parameter is {!r}".format(
+                    pos, e.get("name"), self._param_name(p)))
+            shape = e.get("shape")
+            if not isinstance(shape, (list, tuple)) or tuple(int(d) for d in shape) != tuple(p.shape):
+                raise refuse("{} was saved with shape {}, the live parameter has {}".format(
+                    e.get("name"), shape, tuple(p.shape)))
+            if e.get("owner") != stable_distributed_owner(pos, ws):
+                raise refuse("{} names owner {!r}; the ownership rule gives {} at world size {}".format(
+                    e.get("name"), e.get("owner"), stable_distributed_owner(pos, ws), ws))
+            keys = e.get("state_keys")
+            if not isinstance(keys, (list, tuple)) or not all(isinstance(k, str) for k in keys):
+                raise refuse("{} has malformed state_keys".format(e.get("name")))
+            st = saved_state.get(saved_ids[pos] if pos < len(saved_ids) else pos)
+            if e.get("initialized"):
+                if not isinstance(st, dict) or "m_codebook" not in st or "m_magnitude" not in st:
+                    raise refuse("{} is marked initialised but its momentum is missing".format(e.get("name")))
+                missing = [k for k in keys if k not in {str(x) for x in st}]
+                if missing:
+                    raise refuse("{} lacks the state keys {}".format(e.get("name"), missing))
+                if torch.is_tensor(st["m_codebook"]) and st["m_codebook"].numel() != p.numel():
+                    raise refuse("the momentum of {} holds {} elements, the full matrix has {}".format(
+                        e.get("name"), st["m_codebook"].numel(), p.numel()))
+            elif isinstance(st, dict) and "m_codebook" in st:
+                raise refuse("{} carries momentum but is marked uninitialised".format(e.get("name")))
+
     def load_state_dict(self, state_dict) -> None:
         """Loads a native checkpoint; after a consolidated ``distributed`` checkpoint every rank
         keeps only the momentum of the matrices it owns at the current world size."""
         sd = dict(state_dict)
-        sd.pop("gefen_muon_distributed", None)
+        manifest = sd.pop("gefen_muon_distributed", None)
+        if manifest is not None:
+            self._validate_distributed_manifest(sd, manifest)     # before anything live is touched
         super().load_state_dict(sd)
         if self.sharded_mode == "distributed":
             stable = 0

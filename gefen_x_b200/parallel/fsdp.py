@@ -124,7 +124,8 @@ class ShardedTrainer:
                  optimizer: str = "gefen", global_codebook: bool = True, gather_ctas: int = 64,
                  wait_iters: int = 8_000_000, opt_kwargs: Optional[dict] = None,
                  ag_gemm: bool = False, ag_fetch_ctas: int = 32, muon_kwargs: Optional[dict] = None,
-                 gather_mode: str = "ce", reduce_ctas: int = 148, reduce_mode: str = "ce"):
+                 gather_mode: str = "ce", reduce_ctas: int = 148, reduce_mode: str = "ce",
+                 sparse_embedding: bool = True, embed_capacity: int = 16384):
         self.cfg = cfg
         self.world, self.rank = int(world), int(rank)
         self.device = torch.device(device if device is not None else
@@ -146,6 +147,12 @@ class ShardedTrainer:
         self._copy_tables: Dict[tuple, torch.Tensor] = {}
         self.ag_gemm = bool(ag_gemm) and int(world) > 1
         self.ag_fetch_ctas = int(ag_fetch_ctas)
+        # Untied token embedding on several ranks: only the rows of the batch's tokens are fetched from
+        # their owners, and only those rows of the gradient are reduced (``embed_capacity`` = the most
+        # tokens a rank may pass to one step); otherwise the table is gathered / reduced densely.
+        self.sparse_embed = (bool(sparse_embedding) and int(world) > 1 and not cfg.tie_embeddings
+                             and dtype == torch.bfloat16 and cfg.hidden % 8 == 0)
+        self.embed_capacity = int(embed_capacity)
         self.step_count = 0           # optimisation steps taken (restored by a checkpoint)
         self._epoch = 0               # steps run by this process: the value the arrival flags count up to
         self.process_group = group
@@ -175,11 +182,13 @@ class ShardedTrainer:
         n2d = sum(1 for g in self.all_groups for sp in g.specs if len(sp.shape) == 2)
         xchg_floats = sum(2 * (sp.cols + 1) for g in self.all_groups for sp in g.specs
                           if len(sp.shape) == 2)
-        n_flag_slots = len(self.all_groups) + 4 + n2d
+        n_flag_slots = len(self.all_groups) + 5 + n2d
         arena_bytes = 0
         if world > 1:
             arena_bytes += sum((g.max_shard + g.full_numel) * esz + 2048 for g in self.all_groups)
             arena_bytes += xchg_floats * 4 + n_flag_slots * world * 4 + n2d * 512 + (1 << 20)
+            if self.sparse_embed:
+                arena_bytes += self.embed_capacity * (cfg.hidden * esz + 8) + 4096
         else:
             arena_bytes = 1 << 12
         self.hybrid = optimizer == "muon_hybrid"
@@ -198,10 +207,11 @@ class ShardedTrainer:
         self.SLOT_NORM = len(self.all_groups) + 1
         self.SLOT_MUON = len(self.all_groups) + 2
         self.SLOT_HEAD = len(self.all_groups) + 3      # arrival of the head's gradients (early reduction)
+        self.SLOT_EMBED = len(self.all_groups) + 4     # token ids + embedding-gradient rows published
         self._muon_region = None
         if self.hybrid:
             self._muon_region, self._muon_region_off = self.arena.alloc(max(muon_region_bytes, 256), torch.uint8)
-        self._next_param_slot = len(self.all_groups) + 4
+        self._next_param_slot = len(self.all_groups) + 5
 
         # ---- buffers -------------------------------------------------------
         for g in self.all_groups:
@@ -222,6 +232,12 @@ class ShardedTrainer:
             self.embed_group.full_w = torch.empty(self.embed_group.full_numel, dtype=dtype,
                                                   device=self.device)
             self.norm_slot, self.norm_slot_off = self.arena.alloc(2, torch.float32)
+            if self.sparse_embed:
+                self._tok_ids, self._tok_ids_off = self.arena.alloc(self.embed_capacity, torch.int64)
+                self._tok_grad, self._tok_grad_off = self.arena.alloc(self.embed_capacity * cfg.hidden, dtype)
+                sp0 = self.embed_group.specs[0]
+                assert sp0.name == "model.embed_tokens.weight"
+                self._embed_grad = torch.zeros(sp0.shard_rows[rank], cfg.hidden, dtype=dtype, device=self.device)
         self._init_weights(seed)
         if world > 1:
             for g in self.all_groups:
@@ -345,7 +361,8 @@ class ShardedTrainer:
             # the untied head (and the final norm) are not needed before the end of forward: their
             # gather is issued behind the first layers', off the critical path of the step start
             late = [sp for sp in g.specs if sp.name in self._LATE_EMBED]
-            g.gather_tables_first = self._gather_table_for(g, [sp for sp in g.specs if sp not in late])
+            first = [] if self.sparse_embed else [sp for sp in g.specs if sp not in late]
+            g.gather_tables_first = self._gather_table_for(g, first)
             g.gather_tables_late = self._gather_table_for(g, late)
 
     def _gather_table_for(self, g: Group, specs):
@@ -359,6 +376,9 @@ class ShardedTrainer:
                 dst_off, _ = g.local_slice(sp, r)
                 segs.append((g.shard_w_off + sp.shard_off[r] * esz, dst_off * esz, r))
                 prefix.append(prefix[-1] + n * esz // 16)
+        if not segs:
+            return (torch.zeros(1, dtype=torch.uint8, device=self.device), 0,
+                    torch.zeros(1, dtype=torch.int64, device=self.device), 0, [])
         arr = (_GatherSeg * len(segs))()
         for i, (so, do, r) in enumerate(segs):
             arr[i].src_off, arr[i].dst_off, arr[i].src_rank = so, do, r
@@ -392,6 +412,8 @@ class ShardedTrainer:
             n = sp.shard_rows[self.rank] * sp.cols
             if n == 0 or sp.name in self._muon_names:
                 continue
+            if self.sparse_embed and sp.name == "model.embed_tokens.weight":
+                continue                    # reduced row-wise from the peers' token lists instead
             if (part == "early" and sp.name not in self._LATE_EMBED) or \
                     (part == "rest" and sp.name in self._LATE_EMBED):
                 continue
@@ -529,6 +551,8 @@ class ShardedTrainer:
         shape = (rows,) + tuple(sp.shape[1:])
         if self.world == 1:
             return _LocalGrad(g.full_g[sp.full_off:sp.full_off + n].view(shape))
+        if self.sparse_embed and sp.name == "model.embed_tokens.weight":
+            return _LocalGrad(self._embed_grad.view(shape))
         if self.rs_mode == "stash":
             off = sp.shard_off[self.rank]
             return _LocalGrad(g.stash_g[off:off + n].view(shape))
@@ -551,6 +575,8 @@ class ShardedTrainer:
         else:
             tables = g.gather_tables_rest if rest_only else g.gather_tables
         segs, n_segs, prefix, total, copies = tables
+        if n_segs == 0:
+            return
         if self.gather_mode == "ce":
             key = (id(g), dst.data_ptr(), bool(rest_only), part)
             table = self._copy_tables.get(key)
@@ -644,6 +670,29 @@ class ShardedTrainer:
                                                self.reduce_ctas, U.DTYPE_CODE[self.dtype])
             if self.hybrid and part != "early":
                 self.muon.reduce_group(gi)
+
+    def _reduce_embedding_rows(self, tok_flat: torch.Tensor, dx2d: torch.Tensor, t: int) -> None:
+        """Sparse reduce-scatter of the token-embedding gradient: every rank publishes its token ids
+        and gradient rows in its arena; every rank then adds, from all ranks' lists, the rows it
+        owns into its (zeroed) gradient shard -- a few megabytes over NVLink instead of the table."""
+        n = tok_flat.numel()
+        self._tok_ids[:n].copy_(tok_flat)
+        self._tok_grad[:n * self.cfg.hidden].copy_(dx2d.reshape(-1))
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        sp0 = self.embed_group.specs[0]
+        with torch.cuda.stream(self.reduce_stream):
+            self.reduce_stream.wait_event(ev)
+            self.flags.signal(self.SLOT_EMBED, t)
+            self.flags.wait(self.SLOT_EMBED, t)
+            self._embed_grad.zero_()
+            ops().comm_scatter_add_rows(self.arena.peer_ptrs(self._tok_ids_off),
+                                        self.arena.peer_ptrs(self._tok_grad_off), n,
+                                        min(sp0.rows, self.rank * sp0.rows_per), 1.0 / self.world,
+                                        self._embed_grad)
+            if self.clip and self._embed_grad.numel():
+                U.reduce_sources(None, [self._embed_grad.data_ptr()], self._embed_grad.numel(), 1.0,
+                                 self.norm_partials, self.dtype, self.device)
 
     def _finish_norm(self) -> None:
         """Global gradient norm -> clip coefficient on the device (no host sync)."""
@@ -755,13 +804,23 @@ class ShardedTrainer:
             else:
                 self.norm_partials.zero_()
         split_embed = False
+        tok_flat = tok.reshape(-1).contiguous()
+        x_rows = torch.empty(T, cfg.hidden, dtype=self.dtype, device=self.device) if self.sparse_embed else None
         if multi:
             with torch.cuda.stream(self.comm_stream):
                 self.comm_stream.wait_stream(torch.cuda.current_stream())
                 if t > 1:
                     self.flags.wait(self.SLOT_PARAMS, t - 1)
                 split_embed = hasattr(eg, "gather_tables_late")
-                self._gather_into(eg, eg.full_w, part="first" if split_embed else "all")
+                if self.sparse_embed:
+                    if T > self.embed_capacity:
+                        raise ValueError("{} tokens per step exceed embed_capacity={}".format(T, self.embed_capacity))
+                    sp0 = eg.specs[0]
+                    esz = x_rows.element_size()
+                    ops().comm_gather_rows(self.arena.peer_ptrs(eg.shard_w_off + sp0.shard_off[self.rank] * esz),
+                                           sp0.rows_per, sp0.rows, tok_flat, x_rows)
+                else:
+                    self._gather_into(eg, eg.full_w, part="first" if split_embed else "all")
                 ev = torch.cuda.Event()
                 ev.record(self.comm_stream)
             self._ensure_layer(0)
@@ -779,7 +838,10 @@ class ShardedTrainer:
         head_w = emb_w if cfg.tie_embeddings else ew["lm_head.weight"]
 
         # ---- forward ---------------------------------------------------
-        x = emb_w.index_select(0, tok.reshape(-1)).view(B, S, cfg.hidden)
+        if self.sparse_embed:
+            x = x_rows.view(B, S, cfg.hidden)
+        else:
+            x = emb_w.index_select(0, tok_flat).view(B, S, cfg.hidden)
         saved: List[Optional[dict]] = []
         fused = self.ag_gemm
         for li in range(L):
@@ -814,7 +876,7 @@ class ShardedTrainer:
         else:
             G.mm_tn_wgrad(logits, hN, head_grad)
         del logits
-        if not cfg.tie_embeddings:
+        if not cfg.tie_embeddings and not self.sparse_embed:
             egrad["model.embed_tokens.weight"].zero_()
         dx2d, dnorm = M.rmsnorm_bwd(dhN, x2d, ew["model.norm.weight"], rstdN)
         egrad["model.norm.weight"].copy_(dnorm)
@@ -840,13 +902,17 @@ class ShardedTrainer:
             self._mark("b.end")
             self._mark_layer_done(li)
             self._reduce_group(li)
-        egrad["model.embed_tokens.weight"].index_add_(0, tok.reshape(-1), dx.reshape(T, cfg.hidden))
+        if self.sparse_embed:
+            self._reduce_embedding_rows(tok_flat, dx.reshape(T, cfg.hidden), t)
+        else:
+            egrad["model.embed_tokens.weight"].index_add_(0, tok_flat, dx.reshape(T, cfg.hidden))
         if fused_norm:
             G.add_sumsq(egrad["model.embed_tokens.weight"], self.norm_partials)
         G.set_grad_sumsq(None)
         self._mark("bwd.end")
-        self._reduce_group(len(self.all_groups) - 1,
-                           part="rest" if (multi and not cfg.tie_embeddings) else "all")
+        if not self.sparse_embed:
+            self._reduce_group(len(self.all_groups) - 1,
+                               part="rest" if (multi and not cfg.tie_embeddings) else "all")
         self._finish_norm()
         if multi:
             torch.cuda.current_stream().wait_stream(self.reduce_stream)

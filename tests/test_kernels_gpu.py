@@ -507,3 +507,77 @@ def test_decoder_trains_with_gemm_composed_attention():
     assert b[-1] < b[0] - 0.3
     for x, y in zip(a, b):
         assert abs(x - y) < 0.05 * max(1.0, abs(x)), (a, b)
+
+
+def test_bounded_wait_runs_out_reports_and_leaves_the_gpu_usable():
+    """A wait on a flag that nobody sets gives up after its iteration budget, records kWaitTimeout in the
+    status word instead of trapping, and the context stays usable; the trainer turns the status word
+    into a host-side error (reference contract: every rank raises, nothing hangs,
+    tests/test_precollective_failure_sync.py:215-239)."""
+    from gefen_x_b200.models.decoder import get_config
+    from gefen_x_b200.ops._ext import ops
+    from gefen_x_b200.parallel.fsdp import ShardedTrainer
+
+    dev = _dev()
+    flags = torch.zeros(4, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops().comm_wait(flags, 4, 7, 2000, status)                 # the flags stay at 0: the budget runs out
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1                             # kWaitTimeout
+    x = torch.arange(1024, device=dev, dtype=torch.float32)
+    assert float((x * 2).sum().item()) == 1023 * 1024          # later kernels run normally
+    status.zero_()
+    flags.fill_(7)
+    ops().comm_wait(flags, 4, 7, 2000, status)                 # a satisfied wait leaves the status alone
+    flags[2] = 9
+    ops().comm_wait(flags, 4, 8, 2000, status)                 # one peer behind: times out again
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1
+    tr = ShardedTrainer(get_config("tiny-llama"), device=dev, dtype=torch.bfloat16)
+    tr.check_status()                                          # clean
+    ops().comm_wait(torch.zeros(1, dtype=torch.int32, device=dev), 1, 5, 1000, tr.status)
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        tr.check_status()
+
+
+def test_operators_trace_under_torch_compile():
+    """Fake implementations are registered for the kernel operators, so a compiled function may call
+    them (no graph break), and a compiled optimizer step gives the eager result."""
+    from gefen_x_b200 import Gefen
+    from gefen_x_b200.ops._ext import ops
+
+    dev = _dev()
+    ops()                                                      # loads the library and registers the fakes
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(64, 256, generator=g).bfloat16().to(dev)
+    w = (1 + 0.1 * torch.randn(256, generator=g)).bfloat16().to(dev)
+
+    def norm(x, w):
+        y = torch.empty_like(x)
+        rstd = torch.empty(x.shape[0], dtype=torch.float32, device=x.device)
+        torch.ops.gefenx.rmsnorm_fwd(x, w, y, rstd, 1e-6)
+        return y * 2
+
+    want = norm(x, w)
+    got = torch.compile(norm, fullgraph=True)(x, w)
+    torch.testing.assert_close(got, want)
+
+    def params():
+        gg = torch.Generator().manual_seed(5)
+        return [("a.weight", (torch.randn(64, 256, generator=gg) * 0.05).bfloat16().to(dev).requires_grad_()),
+                ("b", (torch.randn(512, generator=gg) * 0.05).bfloat16().to(dev).requires_grad_())]
+
+    pa, pb = params(), params()
+    oa, ob = Gefen(pa, lr=1e-2), Gefen(pb, lr=1e-2)
+    compiled = torch.compile(ob.step, mode="reduce-overhead")
+    for step in range(3):
+        gg = torch.Generator().manual_seed(40 + step)
+        for (_, a), (_, b) in zip(pa, pb):
+            gr = (torch.randn(a.shape, generator=gg) * 1e-2).bfloat16().to(dev)
+            a.grad, b.grad = gr.clone(), gr.clone()
+        oa.step()
+        compiled()
+    for (n, a), (_, b) in zip(pa, pb):
+        assert torch.equal(a, b), n
+        assert torch.equal(oa.state[a]["m_codebook"], ob.state[b]["m_codebook"]), n
+

@@ -9,6 +9,7 @@ import os
 import socket
 import tempfile
 
+import pytest
 import torch
 import torch.multiprocessing as mp
 
@@ -136,3 +137,39 @@ def test_distributed_muon_matches_exact_and_checkpoint_is_consolidated():
     single, _ = _oracle(1, load=(blob["sd"], blob["weights"]), start=3)
     for n, _ in SHAPES:
         assert torch.allclose(single[n], ref4[n], atol=2e-5), n
+    # a manifest that contradicts the live optimizer is refused before anything is loaded
+    import copy
+
+    from gefen_x_b200 import GefenMuon
+
+    def fresh():
+        ps = [(n, t.clone().requires_grad_(True)) for n, t in _full(0).items()]
+        return ps, GefenMuon(ps, lr=2e-2, fused=False)
+
+    def tampered(edit):
+        sd = copy.deepcopy(blob["sd"])
+        edit(sd["gefen_muon_distributed"], sd)
+        return sd
+
+    cases = {
+        "version": lambda m, sd: m.__setitem__("version", 7),
+        "ownership": lambda m, sd: m.__setitem__("ownership", "round_robin"),
+        "list": lambda m, sd: m.__setitem__("groups", "nope"),
+        "lists": lambda m, sd: m["groups"][0]["params"].pop(),
+        "is 'zzz'": lambda m, sd: m["groups"][0]["params"][1].__setitem__("name", "zzz"),
+        "shape": lambda m, sd: m["groups"][0]["params"][0].__setitem__("shape", (3, 3)),
+        "owner": lambda m, sd: m["groups"][0]["params"][2].__setitem__("owner", 1),
+        "momentum is missing": lambda m, sd: sd["state"][0].pop("m_codebook"),
+        "state keys": lambda m, sd: m["groups"][0]["params"][0].__setitem__(
+            "state_keys", tuple(m["groups"][0]["params"][0]["state_keys"]) + ("ghost",)),
+    }
+    for needle, edit in cases.items():
+        ps, opt = fresh()
+        before = {n: p.detach().clone() for n, p in ps}
+        with pytest.raises(ValueError, match="refused the distributed checkpoint"):
+            opt.load_state_dict(tampered(edit))
+        assert all("m_codebook" not in st for st in opt.state.values()), needle
+        assert all(torch.equal(p, before[n]) for n, p in ps)
+    ps, opt = fresh()
+    opt.load_state_dict(copy.deepcopy(blob["sd"]))           # the untouched file still loads
+

@@ -361,3 +361,64 @@ def test_e4m3_row_quantisation_kernel_matches_the_torch_statement():
         qr, sr = quantize_rowwise_fp8(x.t().contiguous())
         assert torch.equal(st, sr), (rows, cols)
         assert torch.equal(qt.view(torch.uint8), qr.view(torch.uint8)), (rows, cols)
+
+@pytest.mark.parametrize("kind", ["muon", "hybrid"])
+def test_muon_and_hybrid_cuda_graph_replay_match_eager(kind):
+    """``GefenMuon`` / ``GefenMuonHybrid`` with ``capturable=True``: a captured step replays with the
+    same result as eager steps, the learning rate is a device tensor that is changed in place between
+    replays and never read back to the host (reference ``tests/test_capturable.py``,
+    ``gefen_muon.py:1243-1300``)."""
+    from gefen_x_b200 import GefenMuon, GefenMuonHybrid
+
+    def params():
+        g = torch.Generator().manual_seed(1)
+        shapes = [("layers.0.q.weight", (128, 256)), ("layers.0.up.weight", (256, 128)),
+                  ("layers.1.q.weight", (128, 256))]
+        if kind == "hybrid":
+            shapes += [("embed_tokens.weight", (64, 128)), ("norm.weight", (128,))]
+        return [(n, (torch.randn(s, generator=g) * 0.05).bfloat16().to(_dev()).requires_grad_()) for n, s in shapes]
+
+    def build(ps, lr):
+        if kind == "muon":
+            return GefenMuon(ps, lr=lr, weight_decay=0.05, capturable=True, normuon=True)
+        return GefenMuonHybrid(ps, lr=lr, weight_decay=0.05, capturable=True)
+
+    pa, pb = params(), params()
+    lra = torch.tensor(2e-2, device=_dev())
+    lrb = torch.tensor(2e-2, device=_dev())
+    oa, ob = build(pa, lra), build(pb, lrb)
+    for ps in (pa, pb):
+        for _, p in ps:
+            p.grad = torch.zeros_like(p)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for step in range(2):
+            gs = _grads(pa, step)
+            for ps, o in ((pa, oa), (pb, ob)):
+                for (_, p), g in zip(ps, gs):
+                    p.grad.copy_(g)
+                o.step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ob.step()
+    for step in range(2, 6):
+        if step == 4:
+            lra.fill_(5e-3)
+            lrb.fill_(5e-3)                              # picked up by the replay: the lr is read on the device
+        gs = _grads(pa, step)
+        for ps in (pa, pb):
+            for (_, p), g in zip(ps, gs):
+                p.grad.copy_(g)
+        oa.step()
+        graph.replay()
+    torch.cuda.synchronize()
+    moved = 0.0
+    start = params()
+    for (n, a), (_, b), (_, p0) in zip(pa, pb, start):
+        torch.testing.assert_close(a.float(), b.float(), rtol=0, atol=2e-3, msg=n)
+        moved += (a.float() - p0.float()).abs().max().item()
+    assert moved > 1e-2
+
