@@ -110,13 +110,13 @@ void factored_update(const Tensor& descs, const Tensor& tile_start, int64_t n_te
                      int64_t total_tiles, const Tensor& codebook, const Tensor& thr, const Tensor& lut,
                      const c10::optional<Tensor>& gscale, const c10::optional<Tensor>& status,
                      int64_t dtype, int64_t sr_seed, bool stochastic, int64_t wait_iters,
-                     int64_t phases, int64_t epoch, bool fast, const c10::optional<Tensor>& sr_seed_dev) {
+                     int64_t phases, int64_t epoch, int64_t fast, const c10::optional<Tensor>& sr_seed_dev) {
     // phases bit 0: statistics, bit 1: EMA (+ exchange), bit 2: apply + finalize
     c10::cuda::CUDAGuard guard(descs.device());
     auto c = make_common(descs, tile_start, n_tensors, total_tiles, codebook, thr, lut, gscale, status,
                          sr_seed, stochastic, wait_iters, sr_seed_dev);
     c.epoch = (uint32_t)epoch;
-    c.fast = fast ? 1 : 0;
+    c.fast = (int)fast;
     const int sms = sm_count();
     auto st = stream();
     if (phases & 1) check(gx::launch_factored_stats(c, (int)dtype, sms, st), "factored_stats");
@@ -481,7 +481,7 @@ void comm_gather(at::IntArrayRef src_base, const Tensor& segs, int64_t n_segs, T
 
 void comm_reduce_segments(int64_t world, const Tensor& segs, int64_t n_segs,
                           const Tensor& unit_prefix, int64_t total_units, double scale,
-                          const c10::optional<Tensor>& partials, int64_t ctas, int64_t dtype) {
+                          const c10::optional<Tensor>& partials, int64_t ctas, int64_t dtype, bool multimem) {
     c10::cuda::CUDAGuard guard(segs.device());
     TORCH_CHECK(segs.is_cuda() && segs.scalar_type() == at::kByte && segs.is_contiguous());
     TORCH_CHECK(segs.numel() >= n_segs * (int64_t)sizeof(gx::ReduceSeg));
@@ -496,7 +496,7 @@ void comm_reduce_segments(int64_t world, const Tensor& segs, int64_t n_segs,
     check(gx::launch_reduce_segments((int)world,
                                      reinterpret_cast<const gx::ReduceSeg*>(segs.data_ptr()), (int)n_segs,
                                      reinterpret_cast<const long long*>(unit_prefix.data_ptr<int64_t>()),
-                                     total_units, (float)scale, part, (int)ctas, (int)dtype, stream()),
+                                     total_units, (float)scale, part, (int)ctas, (int)dtype, stream(), multimem),
           "reduce_segments");
 }
 
@@ -731,7 +731,7 @@ TORCH_LIBRARY(gefenx, m) {
           "Tensor? sr_seed_dev) -> ()");
     m.def("factored_update(Tensor descs, Tensor tile_start, int n_tensors, int total_tiles, Tensor codebook, "
           "Tensor thr, Tensor lut, Tensor? gscale, Tensor? status, int dtype, int sr_seed, bool stochastic, "
-          "int wait_iters, int phases, int epoch, bool fast, Tensor? sr_seed_dev) -> ()");
+          "int wait_iters, int phases, int epoch, int fast, Tensor? sr_seed_dev) -> ()");
     m.def("reduce_sources(Tensor? out, int[] src_ptrs, int numel, float scale, Tensor? partials, "
           "int dtype, int device_index) -> ()", &reduce_sources);
     m.def("clip_coef(Tensor partials, float max_norm, Tensor(a!) coef) -> ()");
@@ -755,7 +755,7 @@ TORCH_LIBRARY(gefenx, m) {
           "int total_units, int ctas) -> ()");
     m.def("comm_scatter_apply(Tensor segs, int n_segs, Tensor unit_prefix, int total_units, int ctas) -> ()");
     m.def("comm_reduce_segments(int world, Tensor segs, int n_segs, Tensor unit_prefix, int total_units, "
-          "float scale, Tensor? partials, int ctas, int dtype) -> ()");
+          "float scale, Tensor? partials, int ctas, int dtype, bool multimem) -> ()");
     m.def("comm_copy_list(Tensor table, int device_index) -> ()", &comm_copy_list);
     m.def("comm_gather_rows(int[] shard_ptrs, int rows_per, int rows, Tensor tok, Tensor(a!) out) -> ()");
     m.def("comm_scatter_add_rows(int[] tok_ptrs, int[] grad_ptrs, int n_tok, int row0, float scale, "

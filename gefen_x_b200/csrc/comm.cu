@@ -135,6 +135,58 @@ __global__ void __launch_bounds__(256) reduce_segments_kernel(int world,
     }
 }
 
+// The same reduce-scatter through NVSwitch: src[0] of every segment is the multicast address of the
+// slice, one multimem.ld_reduce per 16 bytes returns the sum over all ranks (bf16, fp32 accumulation
+// in the switch), so a rank receives its shard's bytes once instead of once per peer.
+constexpr int kMcUnroll = 4;
+
+__global__ void __launch_bounds__(256) reduce_segments_mc_kernel(const ReduceSeg* __restrict__ segs, int n_segs,
+                                                                 const long long* __restrict__ unit_prefix,
+                                                                 float scale, float* __restrict__ partials) {
+    __shared__ float red[8];
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long nthreads = (long long)gridDim.x * blockDim.x;
+    float ssq = 0.f;
+    for (int seg = 0; seg < n_segs; ++seg) {
+        const ReduceSeg s = segs[seg];
+        const long long units = unit_prefix[seg + 1] - unit_prefix[seg];
+        uint4* dp = reinterpret_cast<uint4*>(s.dst);
+        const uint4* mc = reinterpret_cast<const uint4*>(s.src[0]);
+        for (long long u0 = tid; u0 < units; u0 += nthreads * kMcUnroll) {
+            uint4 v[kMcUnroll];
+#pragma unroll
+            for (int j = 0; j < kMcUnroll; ++j) {
+                const long long u = u0 + j * nthreads;
+                if (u < units) v[j] = multimem_ld_reduce_bf16x8(mc + u);
+            }
+#pragma unroll
+            for (int j = 0; j < kMcUnroll; ++j) {
+                const long long u = u0 + j * nthreads;
+                if (u >= units) continue;
+                float f[8];
+                Vec8<__nv_bfloat16>::unpack(v[j], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    f[e] = round_to<__nv_bfloat16>(__fmul_rn(f[e], scale));
+                    ssq += f[e] * f[e];
+                }
+                if (dp) Vec8<__nv_bfloat16>::store(reinterpret_cast<__nv_bfloat16*>(dp + u), f);
+            }
+        }
+    }
+    if (partials) {
+        ssq = warp_sum(ssq);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ssq;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t += red[i];
+            partials[blockIdx.x] += t;
+        }
+    }
+}
+
 // out[0] = sum over ranks of slot[rank][epoch & 1] after everybody has published;
 // each rank first stores its own value into its slot (two slots alternate so that a
 // fast rank's next reduction cannot overwrite a value a slow rank still has to read).
@@ -285,9 +337,17 @@ cudaError_t launch_gather(void* const* src_base, int world, const GatherSeg* seg
 
 cudaError_t launch_reduce_segments(int world, const ReduceSeg* segs_dev, int n_segs,
                                    const long long* unit_prefix_dev, long long total_units, float scale,
-                                   float* partials, int ctas, int dtype, cudaStream_t st) {
+                                   float* partials, int ctas, int dtype, cudaStream_t st, bool multimem) {
     if (world < 1 || world > kMaxSrc) return cudaErrorInvalidValue;
     if (n_segs <= 0 || total_units <= 0) return cudaSuccess;
+    if (multimem) {
+        if (dtype != 1) return cudaErrorInvalidValue;           // bf16 only
+        long long want_mc = (total_units + 256 * kMcUnroll - 1) / (256 * kMcUnroll);
+        int grid_mc = (int)(want_mc < ctas ? want_mc : ctas);
+        if (grid_mc < 1) grid_mc = 1;
+        reduce_segments_mc_kernel<<<grid_mc, 256, 0, st>>>(segs_dev, n_segs, unit_prefix_dev, scale, partials);
+        return cudaGetLastError();
+    }
     long long want = (total_units + 256 * kReduceUnroll - 1) / (256 * kReduceUnroll);
     int grid = (int)(want < ctas ? want : ctas);
     if (grid < 1) grid = 1;

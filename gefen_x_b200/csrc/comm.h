@@ -46,7 +46,9 @@ cudaError_t launch_gather(void* const* src_base, int world, const GatherSeg* seg
 // hold at least `ctas` floats).  dtype: 0 fp32, 1 bf16, 2 fp16.
 cudaError_t launch_reduce_segments(int world, const ReduceSeg* segs_dev, int n_segs,
                                    const long long* unit_prefix_dev, long long total_units, float scale,
-                                   float* partials, int ctas, int dtype, cudaStream_t st);
+                                   float* partials, int ctas, int dtype, cudaStream_t st, bool multimem = false);
+// multimem = true: src[0] of every segment is the NVLS multicast address of the slice (bf16 only) and
+// one multimem.ld_reduce per 16 bytes replaces the per-peer loads.
 // out = sum_r value_r ; slot_ptrs[r] / flag_ptrs[r] are rank r's slot and flag array
 cudaError_t launch_allreduce_scalar(void* const* slot_ptrs, void* const* flag_ptrs, int world, int rank,
                                     const float* local_val, float* out, unsigned epoch,

@@ -108,6 +108,19 @@ __device__ __forceinline__ void store_idx8(uint8_t* p, const int (&v)[8]) {
     *reinterpret_cast<uint2*>(p) = r;
 }
 
+// Sum over all ranks of eight bf16 at a multicast address, reduced inside NVSwitch (NVLS): one load
+// brings this rank's share of a reduce-scatter instead of one load per peer.  `mc` is the multicast
+// mapping of a symmetric buffer (16-byte aligned); the sum is accumulated in fp32 in the switch and
+// returned rounded to bf16.  This is a multimem instruction on peer memory, not a TMA load.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+    uint4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(mc)
+                 : "memory");
+    return r;
+}
+
 // Raw (unconverted) chunk of VEC elements: loaded early to keep many requests in
 // flight at a low register cost, converted to fp32 only when consumed.
 template <typename T, int VEC> struct RawVec {
@@ -123,6 +136,15 @@ template <typename T, int VEC> struct RawVec {
             }
         } else {
             w[0] = __float_as_uint(to_f<T>(p[0]));
+        }
+    }
+    // eight bf16 summed over all ranks through the NVLS multicast address `p` (bf16, VEC == 8 only)
+    __device__ __forceinline__ void load_mc(const T* p) {
+        if constexpr (VEC == 8 && sizeof(T) == 2) {
+            const uint4 r = multimem_ld_reduce_bf16x8(p);
+            w[0] = r.x; w[1] = r.y; w[2] = r.z; w[3] = r.w;
+        } else {
+            load(p);
         }
     }
     __device__ __forceinline__ void get(float (&o)[VEC]) const {

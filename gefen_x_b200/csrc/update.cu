@@ -28,7 +28,6 @@
 // small enough for the instruction cache, 80 registers and three CTAs per SM.
 #include "common.cuh"
 #include "update.h"
-#include <cstdlib>
 #include <type_traits>
 
 namespace gx {
@@ -549,7 +548,9 @@ template <typename T> struct StatsChunk {
 constexpr int kFastCtas = 3;     // resident CTAs per SM of the fast kernels
 constexpr int kApplyAhead = 1;
 
-template <typename T, int kStatsAhead>
+// MC: the gradient source is an NVLS multicast address; every chunk is read with one
+// multimem.ld_reduce (sum over all ranks inside NVSwitch) and scaled to the mean, as stored
+template <typename T, int kStatsAhead, bool MC>
 __device__ __forceinline__ void stats_tile_fast(const Hot& d, const Smem& s, const TileCursor& t, float gs,
                                 float (&csum)[8], RunMax& run) {
     const int tx = threadIdx.x % d.tcols, ty = threadIdx.x / d.tcols;
@@ -563,7 +564,7 @@ __device__ __forceinline__ void stats_tile_fast(const Hot& d, const Smem& s, con
     StatsChunk<T> q[kStatsAhead + 1];
     auto fetch = [&](StatsChunk<T>& c) {
         if (act && rf < t.r1) {
-            c.g.load(g0 + it.off);
+            if constexpr (MC) c.g.load_mc(g0 + it.off); else c.g.load(g0 + it.off);
             c.i.load(d.idx + it.off);
             c.mo = d.mag[it.blk];
             c.blk = it.blk;
@@ -586,6 +587,10 @@ __device__ __forceinline__ void stats_tile_fast(const Hot& d, const Smem& s, con
             q[0].g.get(g);
             q[0].i.get(ix);
             const float mo = q[0].mo;
+            if constexpr (MC) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) g[e] = round_to<T>(__fmul_rn(g[e], d.src_scale));
+            }
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const float ge = __fmul_rn(g[e], gs);
@@ -649,7 +654,7 @@ __device__ __forceinline__ float raw_elem(const RawVec<T, 8>& v, int e) {
 }
 
 // MODE 0: parameter update; 2: momentum emit; 3: emit with the Nesterov look-ahead
-template <typename T, int MODE>
+template <typename T, int MODE, bool MC = false>
 __device__ __forceinline__ void apply_tile_fast(const Hot& d, const Smem& s, const TileCursor& t, float gs,
                                 const float (&cf)[8]) {
     const int tx = threadIdx.x % d.tcols, ty = threadIdx.x / d.tcols;
@@ -667,7 +672,7 @@ __device__ __forceinline__ void apply_tile_fast(const Hot& d, const Smem& s, con
     ApplyChunk<T> q0, q1;
     auto fetch = [&](ApplyChunk<T>& c) {
         if (rfetch < t.r1) {
-            c.g.load(g0 + it.off);
+            if constexpr (MC) c.g.load_mc(g0 + it.off); else c.g.load(g0 + it.off);
             c.i.load(d.idx + it.off);
             if (!emit) c.p.load(p + it.off);
             c.blk = it.blk;
@@ -691,6 +696,10 @@ __device__ __forceinline__ void apply_tile_fast(const Hot& d, const Smem& s, con
         c.g.get(g);
         c.i.get(ix);
         if (!emit) c.p.get(pf);
+        if constexpr (MC) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) g[e] = round_to<T>(__fmul_rn(g[e], d.src_scale));
+        }
         uint32_t many = 0;
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -721,7 +730,9 @@ __device__ __forceinline__ void apply_tile_fast(const Hot& d, const Smem& s, con
             // the full search (rare: the buckets are far narrower than the codeword spacing)
 #pragma unroll 1
             for (int e = 0; e < 8; ++e) {
-                const float ge = __fmul_rn(raw_elem<T>(c.g, e), gs);
+                float graw = raw_elem<T>(c.g, e);
+                if constexpr (MC) graw = round_to<T>(__fmul_rn(graw, d.src_scale));
+                const float ge = __fmul_rn(graw, gs);
                 const int i0 = (int)(((e < 4 ? c.i.w[0] : c.i.w[1]) >> (8 * (e & 3))) & 0xffu);
                 const float m = ema_momentum(rep_load(s.cb, i0), mo, ge, b1, omb1);
                 const float v = __fmul_rn(m, inv);
@@ -750,7 +761,7 @@ __device__ __forceinline__ void apply_tile_fast(const Hot& d, const Smem& s, con
 // FAST: every tensor of the plan takes the 8-wide single-source path (checked on the host),
 // so the scalar and multi-source code is not even instantiated: smaller code, fewer registers.
 // AHEAD: rows a thread keeps in flight beyond the current one (fast loops only)
-template <typename T, bool FAST, int AHEAD = 2>
+template <typename T, bool FAST, int AHEAD = 2, bool MC = false>
 __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_stats_kernel(LaunchCommon c) {
     const Smem s = load_tables(c, false);
     const float gs = c.gscale ? *c.gscale : 1.0f;
@@ -770,7 +781,7 @@ __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_stats
         const int n = (int)min(T1 - tile, (long long)(w.n_row_tiles - w.rt));
         const TileCursor t = walk_cursor(w, d, n);
         if constexpr (FAST) {
-            stats_tile_fast<T, AHEAD>(d, s, t, gs, csum8, run);
+            stats_tile_fast<T, AHEAD, MC>(d, s, t, gs, csum8, run);
         } else if (d.vec) {
             if (d.n_src > 1) stats_tile<T, 8, 1>(d, s, t, gs, csum8, run);
             else stats_tile<T, 8, 8>(d, s, t, gs, csum8, run);
@@ -975,7 +986,7 @@ __device__ __forceinline__ void load_cfac(const Hot& d, int ct, float (&cf)[VEC]
     for (int e = 0; e < VEC; ++e) cf[e] = d.row_only ? 1.0f : ((c0 + e < d.cols) ? d.cfac[c0 + e] : 0.f);
 }
 
-template <typename T, bool FAST>
+template <typename T, bool FAST, bool MC = false>
 __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_apply_kernel(LaunchCommon c) {
     const Smem s = load_tables(c, true);
     const float gs = c.gscale ? *c.gscale : 1.0f;
@@ -995,7 +1006,7 @@ __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_apply
         const int n = (int)min(T1 - tile, (long long)(w.n_row_tiles - w.rt));
         const TileCursor t = walk_cursor(w, d, n);
         if constexpr (FAST) {
-            if (d.row_only < 2) apply_tile_fast<T, 0>(d, s, t, gs, cf8);
+            if (d.row_only < 2) apply_tile_fast<T, 0, MC>(d, s, t, gs, cf8);
             else if (d.row_only == 2) apply_tile_fast<T, 2>(d, s, t, gs, cf8);
             else apply_tile_fast<T, 3>(d, s, t, gs, cf8);
         } else if (d.vec) {
@@ -1130,13 +1141,17 @@ cudaError_t launch_factored_stats(const LaunchCommon& c, int dtype, int sm_count
     const int grid = min(c.total_tiles, sm_count * (c.fast ? kFastCtas : 4));
     return dispatch(dtype, [&](auto* tag) {
         using T = std::remove_pointer_t<decltype(tag)>;
-        static const int ahead = []() {
-            const char* e = getenv("GEFENX_STATS_AHEAD");   // tuning knob: 1 (default) or 2 rows in flight
-            return (e && e[0] == '2') ? 2 : 1;
-        }();
-        if (c.fast && ahead == 1) factored_stats_kernel<T, true, 1><<<grid, kThreads, kSmemStats, st>>>(c);
-        else if (c.fast) factored_stats_kernel<T, true, 2><<<grid, kThreads, kSmemStats, st>>>(c);
-        else factored_stats_kernel<T, false><<<grid, kThreads, kSmemStats, st>>>(c);
+        // one row of raw chunks in flight beyond the current one (two were measured no faster)
+        if (c.fast == 2) {
+            if constexpr (std::is_same_v<T, __nv_bfloat16>)
+                factored_stats_kernel<T, true, 1, true><<<grid, kThreads, kSmemStats, st>>>(c);
+            else
+                return cudaErrorInvalidValue;
+        } else if (c.fast) {
+            factored_stats_kernel<T, true, 1><<<grid, kThreads, kSmemStats, st>>>(c);
+        } else {
+            factored_stats_kernel<T, false><<<grid, kThreads, kSmemStats, st>>>(c);
+        }
         return cudaGetLastError();
     });
 }
@@ -1153,7 +1168,17 @@ cudaError_t launch_factored_apply(const LaunchCommon& c, int dtype, int sm_count
     const int grid = min(c.total_tiles, sm_count * (fast ? kFastCtas : 2));
     return dispatch(dtype, [&](auto* tag) {
         using T = std::remove_pointer_t<decltype(tag)>;
-        if (fast) {
+        if (c.fast == 2) {
+            // multicast gradient sources exist only in the fast bf16 kernels (the plan builder makes
+            // sure of it): nearest rounding, 8-wide chunks
+            if constexpr (std::is_same_v<T, __nv_bfloat16>) {
+                if (c.stochastic) return cudaErrorInvalidValue;
+                cudaFuncSetAttribute(factored_apply_kernel<T, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemFull);
+                factored_apply_kernel<T, true, true><<<grid, kThreads, kSmemFull, st>>>(c);
+            } else {
+                return cudaErrorInvalidValue;
+            }
+        } else if (fast) {
             cudaFuncSetAttribute(factored_apply_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemFull);
             factored_apply_kernel<T, true><<<grid, kThreads, kSmemFull, st>>>(c);
         } else {

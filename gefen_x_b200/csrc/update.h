@@ -50,6 +50,8 @@ struct alignas(16) TensorDesc {
     int row_only;                     // 1: second moment per row only (block path as [nb, period]);
                                       // 2 / 3: momentum emit (Muon): no second moment, p receives the dense
                                       // new momentum (3: with the Nesterov look-ahead)
+    int g_multimem;                   // 1: g[0] is an NVLS multicast address (bf16): every 16 bytes are read with
+                                      // multimem.ld_reduce, which returns the sum over all ranks; n_src == 1
     float beta1, omb1, beta2, omb2, eps, src_scale;
 };
 
@@ -69,7 +71,8 @@ struct LaunchCommon {
     int stochastic;
     long long wait_iters;             // bound of every peer wait
     uint32_t epoch;                   // value the exchange flags must reach in this launch
-    int fast;                         // every tensor: 8-wide path, one gradient source
+    int fast;                         // 1: every tensor takes the 8-wide path with one gradient source;
+                                      // 2: the same, and that source is an NVLS multicast address (bf16)
 };
 
 // All launchers return the cudaError_t of the launch.

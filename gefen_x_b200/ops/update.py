@@ -61,6 +61,7 @@ class TensorDesc(ctypes.Structure):
         ("world", ctypes.c_int),
         ("rank", ctypes.c_int),
         ("row_only", ctypes.c_int),
+        ("g_multimem", ctypes.c_int),
         ("beta1", ctypes.c_float),
         ("omb1", ctypes.c_float),
         ("beta2", ctypes.c_float),
@@ -105,6 +106,9 @@ class PeerGrad:
     device: torch.device
     scale: float = 1.0
     _cache: Any = None
+    # NVLS: multicast address of the same slice (0 = none).  The two-phase bf16 kernels then read the
+    # gradient with multimem.ld_reduce (in-switch sum) instead of one peer load per rank.
+    mc_ptr: int = 0
 
     def numel(self) -> int:
         n = 1
@@ -281,6 +285,14 @@ class Plan:
         self._uploaded_scalars = None          # what scal_dev holds (constant for momentum-emit plans)
         buf = (ctypes.c_ubyte * (stride * self.n))()
         tile_start = [0]
+        # NVLS: every gradient of the plan has a multicast address and qualifies for the 8-wide bf16
+        # kernels, which are the ones that can read it (multimem.ld_reduce); otherwise peer loads
+        use_mc = kind == "factored" and dtype == torch.bfloat16 and all(
+            isinstance(it.grad, PeerGrad) and it.grad.mc_ptr and not it.emit and it.grad.mc_ptr % 16 == 0
+            and it.p.numel() < 2 ** 31 - 1 and it.period % 8 == 0 and it.p.data_ptr() % 16 == 0
+            and it.state["m_codebook"].data_ptr() % 8 == 0
+            and ((_row_only_cols(it.period) if it.row_only else it.p.shape[-1]) % 8 == 0)
+            for it in items)
         base = self.scratch.data_ptr()
         cursor = 0
         self._keepalive = []
@@ -291,7 +303,12 @@ class Plan:
             check_state_shapes(st, tuple(p.shape), it.period, emit=bool(it.emit),
                                factored=(kind == "factored" and not it.row_only and not it.emit))
             d.p = p.data_ptr()
-            if isinstance(it.grad, PeerGrad):
+            d.g_multimem = 0
+            if use_mc:
+                srcs = [int(it.grad.mc_ptr)]
+                d.src_scale = float(it.grad.scale)
+                d.g_multimem = 1
+            elif isinstance(it.grad, PeerGrad):
                 srcs = list(it.grad.ptrs)
                 d.src_scale = float(it.grad.scale)
             else:
@@ -392,17 +409,21 @@ class Plan:
         self.tile_start = torch.tensor(tile_start, dtype=torch.int32).to(device)
         self.uses_host_scalars = any(not it.scal_ptr for it in items)
         stride_ = _desc_stride()
-        self.fast = kind == "factored" and all(
+        self.fast = int(kind == "factored" and all(
             TensorDesc.from_buffer(buf, i * stride_).vec == 1 and TensorDesc.from_buffer(buf, i * stride_).n_src == 1
             and TensorDesc.from_buffer(buf, i * stride_).numel < 2 ** 31 - 1
-            for i in range(self.n))
+            for i in range(self.n)))
+        if use_mc:
+            if not self.fast:
+                raise RuntimeError("internal: a multicast plan did not qualify for the fast kernels")
+            self.fast = 2
 
     @staticmethod
     def signature_of(items: List[Item]):
         sig = []
         for it in items:
             g = it.grad
-            gp = tuple(g.ptrs) if isinstance(g, PeerGrad) else (g.data_ptr(),)
+            gp = (tuple(g.ptrs) + (int(g.mc_ptr),)) if isinstance(g, PeerGrad) else (g.data_ptr(),)
             st = it.state
             sig.append((it.p.data_ptr(), gp, st["m_codebook"].data_ptr(), st["m_magnitude"].data_ptr(),
                         (st["v_row"] if "v_row" in st else st.get("vmean", st["m_magnitude"])).data_ptr(),
@@ -434,7 +455,7 @@ class Plan:
         if self.kind == "factored":
             ops().factored_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, thr, lut,
                                   gscale, status, code, seed, sr_seed is not None, int(wait_iters),
-                                  int(phases), int(epoch) & 0x7FFFFFFF, bool(self.fast), sr_seed_dev)
+                                  int(phases), int(epoch) & 0x7FFFFFFF, int(self.fast), sr_seed_dev)
         else:
             ops().block_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, thr, lut,
                                gscale, status, code, seed, sr_seed is not None, sr_seed_dev)

@@ -1012,7 +1012,15 @@ class Gefen(torch.optim.Optimizer):
                 _u.two_phase_block(period, work.numel() // period)
             item = _u.Item(p=work, grad=gsrc, state=state, period=period, beta1=beta1, beta2=beta2,
                            eps=eps, scalars=host, scal_ptr=scal_ptr, shard=shard, row_only=row_only)
-            key = ("factored" if (factored or row_only) else "block", dev, work.dtype)
+            kind = "factored" if (factored or row_only) else "block"
+            mc = bool(getattr(gsrc, "mc_ptr", 0)) and kind == "factored" and not self._stochastic_round
+            if getattr(gsrc, "mc_ptr", 0) and not mc:
+                import dataclasses
+
+                item.grad = dataclasses.replace(gsrc, mc_ptr=0)      # peer loads: this path cannot use multicast
+            # gradients that arrive through an NVLS multicast address form a plan of their own (it runs
+            # the kernel instantiation that reads them with multimem.ld_reduce)
+            key = (kind + ("+mc" if mc else ""), dev, work.dtype)
             self._fused_items.setdefault(key, []).append(item)
             self._fused_meta.setdefault(key, []).append((p, group, state, vkey, factored))
             return
@@ -1064,7 +1072,7 @@ class Gefen(torch.optim.Optimizer):
                 raise ValueError("Expected Gefen codebook to be initialized before the update.")
             lut = self._gefen_codebook_lut_on(dev)
             gscale = self._grad_scale_tensor(dev)
-            plan = self._plan_cache.get(kind, items)
+            plan = self._plan_cache.get_keyed((kind, dev, _dt), kind.split("+")[0], items)
             sr_seed, sr_dev = self._kernel_rng_seed_on(dev)
             plan.run(items, cb, self._gefen_thresholds_on(dev), lut, gscale=gscale, status=self._status_word(dev),
                      sr_seed=sr_seed, sr_seed_dev=sr_dev, epoch=self._exchange_epoch)

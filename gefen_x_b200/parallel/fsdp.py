@@ -125,7 +125,7 @@ class ShardedTrainer:
                  wait_iters: int = 8_000_000, opt_kwargs: Optional[dict] = None,
                  ag_gemm: bool = False, ag_fetch_ctas: int = 32, muon_kwargs: Optional[dict] = None,
                  gather_mode: str = "ce", reduce_ctas: int = 148, reduce_mode: str = "ce",
-                 sparse_embedding: bool = True, embed_capacity: int = 16384):
+                 sparse_embedding: bool = True, embed_capacity: int = 16384, nvls: Optional[bool] = None):
         self.cfg = cfg
         self.world, self.rank = int(world), int(rank)
         self.device = torch.device(device if device is not None else
@@ -199,6 +199,19 @@ class ShardedTrainer:
             muon_region_bytes = owned_bytes(self.all_groups, world, esz)
             arena_bytes += muon_region_bytes + 4096
         self.arena = SymmetricArena(arena_bytes, self.device, world, rank, group)
+        # Gradient reduce-scatter through NVSwitch (multimem.ld_reduce on the arena's multicast mapping):
+        # a rank then receives its shard's bytes once instead of once per peer.  On by default where
+        # the fabric offers a multicast mapping; off with nvls=False, GEFENX_NVLS=0 or NCCL_NVLS_ENABLE=0
+        # (multi-rank failure tests must run without it: a rank that dies while its memory is bound to
+        # a multicast object disturbs the other ranks' GPUs).
+        import os
+
+        env_off = os.environ.get("GEFENX_NVLS", "1") == "0" or os.environ.get("NCCL_NVLS_ENABLE", "1") == "0"
+        want = (not env_off) if nvls is None else bool(nvls)
+        self.nvls = bool(want and self.arena.mc_base and dtype == torch.bfloat16 and world > 1)
+        if nvls and not self.nvls and world > 1:
+            raise RuntimeError("nvls=True, but the symmetric arena has no multicast mapping on this system "
+                               "(or the dtype is not bf16)")
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.flags = FlagBoard(self.arena, n_flag_slots, self.status, wait_iters)
         self.wait_iters = int(wait_iters)
@@ -396,7 +409,7 @@ class ShardedTrainer:
         GEMMs while the bytes cross NVLink), then the same kernel sums local memory."""
         esz = torch.empty((), dtype=self.dtype).element_size()
         base = self.arena.base_ptrs
-        staged = self.reduce_mode == "ce"
+        staged = self.reduce_mode == "ce" and not self.nvls
         if staged and self._reduce_stage is None:
             need = 0
             for gg in self.all_groups:
@@ -425,7 +438,9 @@ class ShardedTrainer:
                 dst = g.stash_g.data_ptr() + off * esz
             srcs = []
             slot = 0
-            for r in range(self.world):
+            if self.nvls:
+                srcs = [self.arena.mc_ptr(arena_off)] + [0] * (self.world - 1)
+            for r in range(self.world if not self.nvls else 0):
                 if r == self.rank or not staged:
                     srcs.append(base[r] + arena_off)
                 else:
@@ -559,8 +574,9 @@ class ShardedTrainer:
         esz = p.element_size()
         src_off, _ = g.local_slice(sp, self.rank)
         ptrs = self.arena.peer_ptrs(g.full_g_off + src_off * esz)
+        mc = self.arena.mc_ptr(g.full_g_off + src_off * esz) if self.nvls else 0
         return U.PeerGrad(ptrs=ptrs, shape=shape, dtype=p.dtype, device=self.device,
-                          scale=1.0 / self.world)
+                          scale=1.0 / self.world, mc_ptr=mc)
 
     # ------------------------------------------------------------------
     # parameter gather (all-gather by peer loads)
@@ -667,7 +683,7 @@ class ShardedTrainer:
                 if n_segs:
                     ops().comm_reduce_segments(self.world, segs, n_segs, prefix, total,
                                                1.0 / self.world, self.norm_partials if self.clip else None,
-                                               self.reduce_ctas, U.DTYPE_CODE[self.dtype])
+                                               self.reduce_ctas, U.DTYPE_CODE[self.dtype], self.nvls)
             if self.hybrid and part != "early":
                 self.muon.reduce_group(gi)
 

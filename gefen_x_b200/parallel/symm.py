@@ -32,6 +32,7 @@ class SymmetricArena:
         self.nbytes = (int(nbytes) + _ALIGN - 1) // _ALIGN * _ALIGN
         self._cursor = 0
         self.handle = None
+        self.mc_base = 0
         if world > 1:
             import torch.distributed as dist
             import torch.distributed._symmetric_memory as symm_mem
@@ -39,10 +40,19 @@ class SymmetricArena:
             grp = group if group is not None else dist.group.WORLD
             self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=self.device)
             self.handle = symm_mem.rendezvous(self.buf, group=grp)
-            self.base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+            off = int(getattr(self.handle, "offset", 0) or 0)      # of this tensor inside its allocation
+            self.base_ptrs = [int(p) + off for p in self.handle.buffer_ptrs]
             if self.base_ptrs[rank] != self.buf.data_ptr():
                 # the local mapping must be the tensor we write through
                 self.base_ptrs[rank] = self.buf.data_ptr()
+            # NVLS: the multicast mapping of the whole arena (0 when the fabric or the driver has none).
+            # A multimem.ld_reduce at mc_base + offset returns the sum of that location over all ranks.
+            try:
+                self.mc_base = int(self.handle.multicast_ptr or 0)
+                if self.mc_base:
+                    self.mc_base += off
+            except Exception:           # pragma: no cover - older symmetric-memory handles
+                self.mc_base = 0
         else:
             self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=self.device)
             self.base_ptrs = [self.buf.data_ptr()]
@@ -76,6 +86,10 @@ class SymmetricArena:
         lines = self.buf[(idx[:, None] + torch.arange(_GUARD, device=self.buf.device)[None, :]).reshape(-1)]
         bad = (lines.view(len(self._guards), _GUARD) != _GUARD_BYTE).any(dim=1).cpu().tolist()
         return [g for g, b in zip(self._guards, bad) if b]
+
+    def mc_ptr(self, byte_offset: int) -> int:
+        """Multicast address of ``byte_offset`` (0 when NVLS is not available)."""
+        return self.mc_base + int(byte_offset) if self.mc_base else 0
 
     def peer_ptrs(self, byte_offset: int) -> List[int]:
         return [b + int(byte_offset) for b in self.base_ptrs]

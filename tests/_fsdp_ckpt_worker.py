@@ -4,8 +4,8 @@ argv[1]: mode, argv[2]: working directory.
   "save"   train 6 steps on a global batch of 4 sequences, write a resharding checkpoint, check that the
            native rank-local state dict resumes on the same trajectory, and record the next 3 losses
   "load"   fresh trainer (other seed) on WORLD_SIZE ranks, load the checkpoint, run the same 3 steps
-  "state"  every rank trains on the SAME batch for 4 steps (the reduced gradient then equals a single
-           GPU's on that batch) and the optimizer state of every matrix is gathered by rows
+  "state"  every rank takes ONE step on the SAME batch (the reduced gradient then equals a single GPU's
+           on that batch) and the optimizer state of every matrix is gathered by rows
 """
 import json
 import os
@@ -104,9 +104,9 @@ def main():
         resumed = [float(tr.step(*batch(s, world, rank, dev)).item()) for s in range(6, 9)]
         result = {"resumed": mean_over_ranks(resumed, dev, world), "step_count": tr.step_count}
     elif mode == "state":
-        for s in range(4):
-            tr.step(*batch(s, world, rank, dev, same=True))
+        tr.step(*batch(0, world, rank, dev, same=True))
         st = gather_state(tr, dev, world, rank)
+        st["__codebook__"] = tr.opt._gefen_codebook.float().cpu()
         if rank == 0:
             torch.save(st, os.path.join(work, "state_w{}.pt".format(world)))
     tr.check_status()

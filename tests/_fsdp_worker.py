@@ -25,6 +25,7 @@ def main():
     ag = len(sys.argv) > 4 and sys.argv[4] == "ag"
     hybrid = len(sys.argv) > 4 and sys.argv[4] == "hybrid"
     kgather = len(sys.argv) > 4 and sys.argv[4] == "kgather"
+    nvls = len(sys.argv) > 4 and sys.argv[4] == "nvls"
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
     local = int(os.environ["LOCAL_RANK"])
@@ -32,12 +33,14 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     cfg = get_config("tiny-llama", qk_norm=True, hidden=256, ffn=512, n_layers=3)
-    tr = ShardedTrainer(cfg, device=dev, dtype=torch.bfloat16, world=world, rank=rank, lr=6e-4,
-                        weight_decay=0.01, clip_grad_norm=None if clip == "none" else float(clip),
-                        rs_mode=rs_mode, seed=5, wait_iters=20_000_000, ag_gemm=ag,
-                        optimizer="muon_hybrid" if hybrid else "gefen",
-                        gather_mode="kernel" if kgather else "ce", reduce_ctas=8 if kgather else 148,
-                        reduce_mode="kernel" if kgather else "ce")
+    try:
+        tr = _build(cfg, dev, world, rank, clip, rs_mode, ag, hybrid, kgather, nvls)
+    except RuntimeError as exc:
+        if nvls and "multicast" in str(exc):
+            dist.barrier()
+            dist.destroy_process_group()
+            sys.exit(77)                        # no NVLS on this system: the test skips
+        raise
     g = torch.Generator().manual_seed(2)
     tok_all = torch.randint(0, cfg.vocab_size, (world * 2, 129), generator=g)
     tok = tok_all[rank * 2:(rank + 1) * 2].to(dev)
@@ -51,9 +54,19 @@ def main():
     if rank == 0:
         mean = torch.stack(gathered).mean(0).tolist()
         with open(out_path, "w") as fh:
-            json.dump({"mean_loss": mean, "state_bytes_per_param": tr.state_bytes_per_param()}, fh)
+            json.dump({"mean_loss": mean, "state_bytes_per_param": tr.state_bytes_per_param(),
+                       "nvls": tr.nvls}, fh)
     dist.barrier()
     dist.destroy_process_group()
+
+
+def _build(cfg, dev, world, rank, clip, rs_mode, ag, hybrid, kgather, nvls):
+    return ShardedTrainer(cfg, device=dev, dtype=torch.bfloat16, world=world, rank=rank, lr=6e-4,
+                        weight_decay=0.01, clip_grad_norm=None if clip == "none" else float(clip),
+                        rs_mode=rs_mode, seed=5, wait_iters=20_000_000, ag_gemm=ag, nvls=True if nvls else False,
+                        optimizer="muon_hybrid" if hybrid else "gefen",
+                        gather_mode="kernel" if kgather else "ce", reduce_ctas=8 if kgather else 148,
+                        reduce_mode="kernel" if kgather else "ce")
 
 
 if __name__ == "__main__":

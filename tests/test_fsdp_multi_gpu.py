@@ -40,7 +40,8 @@ def _single_gpu_losses(world, clip, optimizer="gefen"):
 
 @pytest.mark.parametrize("rs_mode,clip,ag", [("stash", "1.0", "plain"), ("fused", "none", "plain"),
                                              ("stash", "1.0", "ag"), ("stash", "1.0", "hybrid"),
-                                             ("stash", "1.0", "kgather")])
+                                             ("stash", "1.0", "kgather"), ("stash", "1.0", "nvls"),
+                                             ("fused", "1.0", "nvls"), ("fused", "1.0", "plain")])
 def test_two_ranks_track_single_gpu(tmp_path, rs_mode, clip, ag):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
@@ -50,11 +51,14 @@ def test_two_ranks_track_single_gpu(tmp_path, rs_mode, clip, ag):
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(ROOT, "tests", "_fsdp_worker.py"), str(out), rs_mode, clip, ag]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    if ag == "nvls" and not out.exists() and "multicast" in (proc.stdout + proc.stderr):
+        pytest.skip("no NVLS multicast mapping on this system")
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     multi = json.load(open(out))
     ref = _single_gpu_losses(2, None if clip == "none" else float(clip),
                              "muon_hybrid" if ag == "hybrid" else "gefen")
     got = multi["mean_loss"]
+    assert multi.get("nvls", False) == (ag == "nvls")
     assert got[-1] < got[0] - 0.5
     for a, b in zip(ref, got):
         assert abs(a - b) < 0.05 * max(1.0, abs(a)), (ref, got)
@@ -134,18 +138,45 @@ def test_sharded_optimizer_state_equals_single_gpu_state(tmp_path):
     _launch(2, "_fsdp_ckpt_worker.py", "state", tmp_path)
     one = torch.load(tmp_path / "state_w1.pt")
     two = torch.load(tmp_path / "state_w2.pt")
+    cb1, cb2 = one.pop("__codebook__"), two.pop("__codebook__")
+    same_codebook = torch.allclose(cb1, cb2, rtol=0, atol=1e-6)
     assert set(one) == set(two) and one
     compared_indices = 0
     for name, a in one.items():
         b = two[name]
-        torch.testing.assert_close(b["v_row"], a["v_row"], rtol=2e-3, atol=1e-12, msg=name)
+        # after one step v = (1 - beta2) * sums of g^2: only the summation order differs.  The token
+        # embedding's gradient is a scatter-add of bf16 rows (repeated tokens round differently when the
+        # same rows arrive as two halves from two ranks), so it is compared loosely.
+        tol = 5e-2 if "embed_tokens" in name else 1e-4
+        torch.testing.assert_close(b["v_row"], a["v_row"], rtol=tol, atol=1e-12, msg=name)
         for vc in b["v_col"]:
-            torch.testing.assert_close(vc, a["v_col"][0], rtol=2e-3, atol=1e-12, msg=name)
+            torch.testing.assert_close(vc, a["v_col"][0], rtol=tol, atol=1e-12, msg=name)
         torch.testing.assert_close(b["v_col"][0], b["v_col"][1], rtol=0, atol=0, msg=name)   # shards agree exactly
         torch.testing.assert_close(b["w"], a["w"], rtol=0, atol=4e-3, msg=name)
-        if all(p == a["period"] for p in b["periods"]):
+        if same_codebook and all(p == a["period"] for p in b["periods"]):
             compared_indices += 1
             differ = (a["idx"] != b["idx"]).float().mean().item()
-            assert differ <= 0.01, (name, differ)
+            assert differ <= 0.002, (name, differ)
             torch.testing.assert_close(b["dense"], a["dense"], rtol=0, atol=2e-2 * a["dense"].abs().max().item())
-    assert compared_indices > 0
+    # the quantised momentum is comparable wherever both runs chose the same blocks and codebook
+    assert compared_indices > 0 or not same_codebook
+
+
+@pytest.mark.parametrize("kind", ["gefen", "hybrid"])
+def test_optimizers_under_torch_fully_shard(tmp_path, kind):
+    """``Gefen`` and ``GefenMuonHybrid`` on the DTensor parameters that torch's ``fully_shard`` creates
+    (uneven row shards included): the sharded run tracks the single-GPU run on the same global batch,
+    and a state dict taken mid-run (rank-local payloads for plain Gefen) resumes on the same
+    trajectory (reference tests/test_gefen_fsdp2_checkpoint.py, tests/test_fused_fsdp2_noncontig.py)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    one, two = tmp_path / "one.json", tmp_path / "two.json"
+    _launch(1, "_fsdp2_worker.py", one, kind)
+    _launch(2, "_fsdp2_worker.py", two, kind)
+    a, b = json.load(open(one)), json.load(open(two))
+    assert b["local_shape_of_uneven"] == [[148, 512]]          # 296 rows over 2 ranks
+    assert b["losses"][-1] < b["losses"][0]
+    for x, y in zip(a["losses"], b["losses"]):
+        assert abs(x - y) <= 0.05 * max(1e-3, abs(x)), (a["losses"], b["losses"])
+    for x, y in zip(b["continued"], b["resumed"]):
+        assert abs(x - y) <= 0.01 * max(1e-3, abs(x)), (b["continued"], b["resumed"])

@@ -422,3 +422,28 @@ def test_muon_and_hybrid_cuda_graph_replay_match_eager(kind):
         moved += (a.float() - p0.float()).abs().max().item()
     assert moved > 1e-2
 
+
+def test_non_contiguous_parameter_steps_like_its_contiguous_copy():
+    """A parameter that is a transposed view (what a non-contiguous local shard looks like to the
+    optimizer): the kernels run on a contiguous copy and the result is copied back; trajectory and
+    state equal those of a contiguous parameter with the same values (reference ``gefen.py:3703-3732``,
+    tests/test_fused_fsdp2_noncontig.py)."""
+    from gefen_x_b200 import Gefen
+
+    g = torch.Generator().manual_seed(4)
+    base = (torch.randn(256, 128, generator=g) * 0.05).bfloat16().to(_dev())
+    pa = base.clone().t().contiguous().requires_grad_()          # [128, 256] contiguous
+    pb = base.clone().t().requires_grad_()                       # the same values, strides (1, 128)
+    assert not pb.is_contiguous()
+    oa, ob = Gefen([("w", pa)], lr=1e-2, weight_decay=0.01), Gefen([("w", pb)], lr=1e-2, weight_decay=0.01)
+    for step in range(4):
+        gr = (torch.randn(128, 256, generator=torch.Generator().manual_seed(70 + step)) * 1e-2).bfloat16().to(_dev())
+        pa.grad = gr.clone()
+        pb.grad = gr.t().contiguous().t()                        # a non-contiguous gradient as well
+        oa.step()
+        ob.step()
+    assert not pb.is_contiguous()
+    assert torch.equal(pa.detach(), pb.detach())
+    assert torch.equal(oa.state[pa]["m_codebook"], ob.state[pb]["m_codebook"])
+    torch.testing.assert_close(oa.state[pa]["v_row"], ob.state[pb]["v_row"], rtol=1e-5, atol=0)
+
