@@ -46,7 +46,8 @@ def make_opt(kind, model):
 
     if kind == "hybrid":
         return GefenMuonHybrid(model, lr=2e-3, weight_decay=0.01)
-    return Gefen(list(model.named_parameters()), lr=2e-3, weight_decay=0.01)
+    # block second moment in both runs: sharded (DTensor) matrices always take it, as in the reference
+    return Gefen(list(model.named_parameters()), lr=2e-3, weight_decay=0.01, factored_v_2d=False)
 
 
 def run_step(model, opt, step, world, rank, dev):

@@ -20,16 +20,19 @@ sys.path.insert(0, ROOT)
 from gefen_x_b200.models.decoder import get_config  # noqa: E402
 from gefen_x_b200.parallel.fsdp import ShardedTrainer  # noqa: E402
 
-GLOBAL_SEQS = 4
+GLOBAL_SEQS = int(os.environ.get("GX_GLOBAL_SEQS", "4"))      # sequences of the global batch
 
 
 def config():
+    if os.environ.get("GX_CKPT_MODEL"):                 # e.g. "llama3-8b:2": a preset with this many layers
+        name, layers = os.environ["GX_CKPT_MODEL"].split(":")
+        return get_config(name, n_layers=int(layers))
     return get_config("tiny-llama", qk_norm=True, hidden=256, ffn=512, n_layers=2)
 
 
 def batch(step, world, rank, dev, same=False):
     g = torch.Generator().manual_seed(700 + step)
-    tok = torch.randint(0, 1024, (GLOBAL_SEQS, 129), generator=g)
+    tok = torch.randint(0, config().vocab_size, (GLOBAL_SEQS, 129), generator=g)
     if same:
         mine = tok[:2]
     else:

@@ -175,7 +175,6 @@ def test_optimizers_under_torch_fully_shard(tmp_path, kind):
     _launch(2, "_fsdp2_worker.py", two, kind)
     a, b = json.load(open(one)), json.load(open(two))
     assert b["local_shape_of_uneven"] == [[148, 512]]          # 296 rows over 2 ranks
-    assert b["losses"][-1] < b["losses"][0]
     for x, y in zip(a["losses"], b["losses"]):
         assert abs(x - y) <= 0.05 * max(1e-3, abs(x)), (a["losses"], b["losses"])
     for x, y in zip(b["continued"], b["resumed"]):
