@@ -57,6 +57,9 @@ def parse_args():
                     help="attention: fused library kernel, or tcgen05 GEMMs + own row kernels")
     ap.add_argument("--nvls", default="auto", choices=["auto", "on", "off"],
                     help="gradient reduce-scatter through NVSwitch (multimem.ld_reduce) where available")
+    ap.add_argument("--gemm-schedule", default="auto", choices=["auto", "static", "dynamic"],
+                    help="tile schedule of the pair GEMM: fixed assignment, or tiles drawn from a device counter "
+                         "(auto: dynamic with several ranks)")
     ap.add_argument("--gemm", default="tcgen05", choices=["tcgen05", "library"],
                     help="layer GEMMs: own tcgen05 kernels with fused epilogues (default), or the vendor library")
     ap.add_argument("--trace", action="store_true",
@@ -155,6 +158,7 @@ def run_ours(args):
                              rs_mode=args.rs_mode, ag_gemm=args.ag_gemm, optimizer=args.optimizer,
                              gather_mode=args.gather, reduce_ctas=args.reduce_ctas, reduce_mode=args.reduce,
                              nvls={"auto": None, "on": True, "off": False}[args.nvls],
+                             gemm_schedule=args.gemm_schedule,
                              muon_kwargs=dict(ns_schedule="standard", ns_steps=5, fp8_ns=args.fp8_ns)
                              if args.optimizer == "muon_hybrid" else None)
     gen = torch.Generator().manual_seed(1000 + rank)
@@ -256,7 +260,8 @@ def run_ours(args):
         # how this implementation ran the config (kept out of `config`, which both arms share)
         "impl_config": {"rs_mode": trainer.rs_mode, "ag_gemm": trainer.ag_gemm, "attention": args.attn,
                         "gemm": args.gemm, "gather": trainer.gather_mode, "reduce": trainer.reduce_mode,
-                        "reduce_ctas": trainer.reduce_ctas, "sparse_embedding": trainer.sparse_embed, "nvls": trainer.nvls},
+                        "reduce_ctas": trainer.reduce_ctas, "sparse_embedding": trainer.sparse_embed, "nvls": trainer.nvls,
+                        "gemm_schedule": args.gemm_schedule},
     }
     if rank == 0:
         print(json.dumps(out), flush=True)

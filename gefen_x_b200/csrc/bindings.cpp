@@ -308,7 +308,7 @@ void gemm_bf16(const Tensor& a, const Tensor& b, Tensor c, const c10::optional<T
 void gemm_pair_bf16(const Tensor& a, const Tensor& b, Tensor c0, const c10::optional<Tensor>& c1,
                     const c10::optional<Tensor>& d, const c10::optional<Tensor>& aux, bool a_t, bool b_t,
                     double alpha, double beta, int64_t epi, int64_t bn, const c10::optional<Tensor>& status,
-                    const c10::optional<Tensor>& sumsq) {
+                    const c10::optional<Tensor>& sumsq, bool dynamic) {
     c10::cuda::CUDAGuard guard(a.device());
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && c0.is_cuda(), "gemm_pair_bf16: CUDA tensors required");
     TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 &&
@@ -382,7 +382,8 @@ void gemm_pair_bf16(const Tensor& a, const Tensor& b, Tensor c0, const c10::opti
         p.ws = it->second.first.data_ptr<float>();
         p.ws_floats = gx::kPairWsFloats;
         p.counters = reinterpret_cast<uint32_t*>(it->second.second.data_ptr<int>());
-        p.n_counters = gx::kPairCounters;
+        p.n_counters = gx::kPairCounters - 8;
+        p.sched = dynamic ? p.counters + (gx::kPairCounters - 8) : nullptr;
     }
     check(gx::launch_gemm_pair_bf16(bf(a), a.stride(0), bf(b), b.stride(0), p, C0, ld0, C1, ld1, C2, ld2,
                                     sm_count(), stream()),
@@ -745,7 +746,7 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("gemm_bf16(Tensor a, Tensor b, Tensor(a!) c, Tensor? d, bool a_t, bool b_t, float alpha, "
           "float beta, Tensor? status) -> ()");
     m.def("gemm_pair_bf16(Tensor a, Tensor b, Tensor(a!) c0, Tensor(b!)? c1, Tensor? d, Tensor? aux, bool a_t, "
-          "bool b_t, float alpha, float beta, int epi, int bn, Tensor? status, Tensor(c!)? sumsq) -> ()");
+          "bool b_t, float alpha, float beta, int epi, int bn, Tensor? status, Tensor(c!)? sumsq, bool dynamic) -> ()");
     m.def("gemm_ag_bf16(Tensor a, Tensor(a!) bstage, Tensor(b!) c, int[] peer_bases, Tensor segs, "
           "Tensor seg_meta, Tensor tile_order, Tensor(c!) flags, Tensor(d!) count, int epoch, "
           "int count_target, int fetch_ctas, Tensor? status) -> ()");

@@ -34,6 +34,13 @@
 // each split parks its fp32 partial in a workspace, and the split that arrives last (an atomic
 // counter per 32-row slice, nobody waits) sums the partials in split order and runs the epilogue.
 //
+// Schedule: static (pair p takes units p, p + P, ...: reproducible placement) or, when the launch
+// is given a counter, dynamic: the leader's producer thread draws the next unit with an atomic add
+// one unit ahead, publishes it to the other roles of both CTAs through a small ring in shared
+// memory (mbarriers; a plain store into the peer's shared memory for the peer's copy), and every
+// pair simply takes the next unit when it is free.  A pair that shares its SMs with another stream's
+// kernels (reduce-scatter, copies) then falls behind without holding the whole product back.
+//
 // The reference multiplies through cuBLAS (src/gefen/gefen_muon.py:278-287 and its
 // benchmark model benchmarks/training_matrix/tiny_qwen.py:168-181).  Every mbarrier wait
 // is bounded; on time-out the roles drain, TMEM is freed and kWaitTimeout is recorded.
@@ -59,11 +66,16 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kEpiTile = 32 * 128;          // one warp's staging tile: 32 rows x 64 bf16
 constexpr int kEpiBufs = 4;                      // staging tiles per epilogue warp (TMA stores in flight)
 
+constexpr int kRing = 4;                         // work units published ahead of their consumers
+
 struct PairShared {
     uint64_t full[8];
     uint64_t empty[8];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
+    uint64_t ring_full[kRing];       // dynamic schedule: unit published (one arrival, from the leader's producer)
+    uint64_t ring_empty[kRing];      // leader only: every consumer of both CTAs has read the unit (10 arrivals)
+    int ring_unit[kRing];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -168,6 +180,79 @@ __device__ __forceinline__ bool get_work(const PairParams& p, int it, int pair, 
     return false;
 }
 
+__device__ __forceinline__ void decode_unit(const PairParams& p, int unit, int k_blocks, Work& w) {
+    if (unit < p.full_tiles) {
+        w.tile = unit;
+        w.kb0 = 0; w.kb1 = k_blocks; w.split = 0; w.n_split = 1;
+    } else {
+        const int v = unit - p.full_tiles;
+        w.tile = p.full_tiles + v / p.splits;
+        w.split = v % p.splits;
+        w.n_split = p.splits;
+        w.kb0 = (int)((long long)w.split * k_blocks / p.splits);
+        w.kb1 = (int)((long long)(w.split + 1) * k_blocks / p.splits);
+    }
+}
+
+// The sequence of work units of one role.  Static schedule: computed.  Dynamic schedule: the
+// leader's producer thread is the fetcher (atomic counter, one unit ahead, publishes into the ring
+// of both CTAs); every other role reads the ring and acknowledges on the leader's ring_empty.
+struct UnitStream {
+    const PairParams& p;
+    PairShared* ss;
+    volatile int* abort_flag;
+    int pair, n_pairs, k_blocks;
+    uint32_t rank;
+    bool fetcher;        // leader CTA, producer thread
+    bool warp_role;      // called by all 32 lanes of a warp (epilogue): lane 0 acknowledges
+    int it;
+    int pending;         // fetcher: the unit fetched ahead (-2: nothing fetched yet)
+
+    __device__ UnitStream(const PairParams& p_, PairShared* ss_, volatile int* ab, int pair_, int n_pairs_, int kb,
+                          uint32_t rank_, bool fetcher_, bool warp_role_)
+        : p(p_), ss(ss_), abort_flag(ab), pair(pair_), n_pairs(n_pairs_), k_blocks(kb), rank(rank_),
+          fetcher(fetcher_), warp_role(warp_role_), it(0), pending(-2) {}
+
+    __device__ int fetch_and_publish() {
+        const int slot = it % kRing;
+        const uint32_t ph = (uint32_t)((it / kRing) & 1);
+        ++it;
+        if (!mbar_wait_cluster(&ss->ring_empty[slot], ph ^ 1, abort_flag)) return -1;
+        const unsigned n_units = (unsigned)(p.full_tiles + p.rem_tiles * p.splits);
+        const unsigned u = atomicAdd(p.sched, 1u);
+        const int unit = u < n_units ? (int)u : -1;
+        // every pair draws exactly one value past the end; the very last of them rewinds the counter
+        if (unit < 0 && u == n_units + (unsigned)n_pairs - 1u) atomicExch(p.sched, 0u);
+        ss->ring_unit[slot] = unit;
+        st_shared_cluster_u32(mapa(smem_u32(&ss->ring_unit[slot]), 1), (uint32_t)unit);
+        mbar_arrive(&ss->ring_full[slot]);
+        mbar_arrive_cluster(mapa(smem_u32(&ss->ring_full[slot]), 1));
+        return unit;
+    }
+
+    __device__ bool next(Work& w) {
+        if (p.sched == nullptr) return get_work(p, it++, pair, n_pairs, k_blocks, w);
+        int unit;
+        if (fetcher) {
+            if (pending == -2) pending = fetch_and_publish();
+            unit = pending;
+            if (unit >= 0) pending = fetch_and_publish();
+        } else {
+            const int slot = it % kRing;
+            const uint32_t ph = (uint32_t)((it / kRing) & 1);
+            ++it;
+            if (!mbar_wait_cluster(&ss->ring_full[slot], ph, abort_flag)) return false;
+            unit = *reinterpret_cast<volatile int*>(&ss->ring_unit[slot]);
+            if (warp_role) __syncwarp();
+            if (!warp_role || (threadIdx.x & 31) == 0)
+                mbar_arrive_cluster(mapa(smem_u32(&ss->ring_empty[slot]), 0));
+        }
+        if (unit < 0) return false;
+        decode_unit(p, unit, k_blocks, w);
+        return true;
+    }
+};
+
 template <int BN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
@@ -188,6 +273,7 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
     if (threadIdx.x == 0) {
         for (int i = 0; i < TL::kStages; ++i) { mbar_init(&ss->full[i], 1); mbar_init(&ss->empty[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&ss->tmem_full[i], 1); mbar_init(&ss->tmem_empty[i], 8); }
+        for (int i = 0; i < kRing; ++i) { mbar_init(&ss->ring_full[i], 1); mbar_init(&ss->ring_empty[i], 10); }
         ss->abort_flag = 0;
         mbar_init_fence();
         prefetch_tmap(&maps.a);
@@ -210,7 +296,8 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
             int stage = 0;
             uint32_t phase = 0;
             Work wk;
-            for (int it = 0; get_work(p, it, pair, n_pairs, k_blocks, wk); ++it) {
+            UnitStream units(p, ss, abort_flag, pair, n_pairs, k_blocks, rank, rank == 0, false);
+            while (units.next(wk)) {
                 int mt, nt;
                 tile_coords(p, wk.tile, mt, nt);
                 const int m0 = mt * 256 + (int)rank * kBM;
@@ -261,7 +348,8 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
             uint32_t acc_phase = 0;
             bool ok = true;
             Work wk;
-            for (int it = 0; ok && get_work(p, it, pair, n_pairs, k_blocks, wk); ++it) {
+            UnitStream units(p, ss, abort_flag, pair, n_pairs, k_blocks, rank, false, false);
+            while (ok && units.next(wk)) {
                 if (!mbar_wait(&ss->tmem_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -306,7 +394,8 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
             ++unit;
         };
         Work wk;
-        for (int it = 0; get_work(p, it, pair, n_pairs, k_blocks, wk); ++it) {
+        UnitStream units(p, ss, abort_flag, pair, n_pairs, k_blocks, rank, false, true);
+        while (units.next(wk)) {
             int mt, nt;
             tile_coords(p, wk.tile, mt, nt);
             const int row0 = mt * 256 + (int)rank * kBM + q * 32;
@@ -322,7 +411,9 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
             tc_fence_after();
             const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
             float sq = 0.f;                                        // this thread's share of sum(C^2) of the tile
-            int sq_slot = (int)blockIdx.x * 4 + q;                 // one slot per epilogue warp of the launch ...
+            // one slot per epilogue warp of the launch (static schedule: one writer per slot, reproducible
+            // sums), per tile under the dynamic schedule (placement varies: atomic adds) ...
+            int sq_slot = p.sched ? ((wk.tile * 8 + (int)rank * 4 + q) & (kSumsqTailBase - 1)) : (int)blockIdx.x * 4 + q;
             // ---- K-split tile: park the partial; only the slice's last arriver goes on ----
             const float* ws_tile = nullptr;                        // set: sum the parked partials
             if (wk.n_split > 1) {
@@ -464,7 +555,9 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
                 if (p.sumsq != nullptr) {
                     // fixed order: lanes by shuffle tree, tiles of this warp in visiting order, one writer per slot
                     sq = warp_sum(sq);
-                    if (lane == 0) p.sumsq[sq_slot] += sq;
+                    if (lane == 0) {
+                        if (p.sched) atomicAdd(p.sumsq + sq_slot, sq); else p.sumsq[sq_slot] += sq;
+                    }
                 }
             }
         }
@@ -550,6 +643,7 @@ cudaError_t launch_pair(const PairMaps& maps, PairParams p, int sm_count, cudaSt
             p.splits = sp;
     }
     if (p.full_tiles == 0) pairs = p.rem_tiles * p.splits;   // fewer tiles than pairs: one unit each
+    if (pairs < 1) pairs = 1;
     gemm_pair_kernel<BN, EPI><<<2 * pairs, kPairThreads, smem, st>>>(maps, p);
     return cudaGetLastError();
 }

@@ -74,6 +74,9 @@ struct PairParams {
     float* sumsq;
     // K-split of the tail wave (optional): fp32 workspace and zero-initialised arrival counters that
     // the kernel leaves zeroed; launches sharing them must be ordered on one stream
+    // dynamic schedule (optional): a zero-initialised counter that every launch leaves at zero; null =
+    // static schedule.  Launches sharing the counter must be ordered on one stream.
+    uint32_t* sched;
     float* ws;
     long long ws_floats;
     uint32_t* counters;
@@ -88,7 +91,7 @@ constexpr int kSumsqTailBase = 1024;       // slots [0, 1024): per epilogue warp
 constexpr int kSumsqSlots = 2048;
 // workspace that always suffices: half of the pairs' tiles, 256 x 256 fp32 each, and their counters
 constexpr long long kPairWsFloats = 74ll * 256 * 256;
-constexpr int kPairCounters = 74 * 8;
+constexpr int kPairCounters = 74 * 8 + 8;       // + the schedule counter (last 8 words, 32-byte aligned)
 
 // True when the pair kernel can run the product (otherwise use launch_gemm_bf16).
 bool gemm_pair_supported(int M, int N, int K);

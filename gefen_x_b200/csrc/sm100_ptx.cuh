@@ -83,6 +83,37 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     return false;
 }
 
+// The same wait with acquire semantics at cluster scope: for barriers whose arrivals come from the
+// peer CTA after plain stores into this CTA's shared memory (st.shared::cluster + release.cluster).
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (int it = 0;; ++it) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((it & 63) == 63) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitCycles) break;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+// 32-bit store into the shared memory of another CTA of the cluster (address from mapa)
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
 // ---- TMA ------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");

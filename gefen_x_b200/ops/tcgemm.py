@@ -29,6 +29,7 @@ from ._ext import available, ops
 _status = {}
 _PAIR = True            # route eligible 2-D products to the CTA-pair kernel
 _FORCE_BN = 0           # 0: choose per shape; 128 / 256: force the pair tile width (benchmarks)
+_DYNAMIC = False        # pair kernel: draw tiles from a counter instead of the fixed assignment
 
 
 def set_pair_kernel(enabled: bool, bn: int = 0) -> None:
@@ -37,6 +38,16 @@ def set_pair_kernel(enabled: bool, bn: int = 0) -> None:
     if bn not in (0, 128, 256):
         raise ValueError("bn must be 0, 128 or 256")
     _PAIR, _FORCE_BN = bool(enabled), int(bn)
+
+
+def set_dynamic_schedule(enabled: bool) -> None:
+    """Dynamic tile schedule of the pair kernel: pairs draw the next tile from a device counter when
+    they are free, so a pair slowed down by kernels of other streams on its SMs (gradient
+    reduce-scatter, copies: the sharded runtime) does not hold a product back.  The static schedule
+    (default) places every tile on a fixed pair, which makes the fused gradient-norm sums
+    reproducible bit for bit."""
+    global _DYNAMIC
+    _DYNAMIC = bool(enabled)
 
 
 def status_word(device: torch.device) -> torch.Tensor:
@@ -84,7 +95,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     dd = d if beta != 0.0 else None
     if a.dim() == 2 and pair_eligible(m, n, k) and _ok_operand(out) and (dd is None or _ok_operand(dd)):
         ops().gemm_pair_bf16(a, b, out, None, dd, None, bool(a_t), bool(b_t), float(alpha), float(beta), 0,
-                             _FORCE_BN, status_word(a.device), sumsq)
+                             _FORCE_BN, status_word(a.device), sumsq, _DYNAMIC)
         return out
     if sumsq is not None:
         raise ValueError("sumsq needs the CTA-pair kernel; this product does not qualify")
@@ -112,7 +123,7 @@ def gemm_swiglu_fwd(x: torch.Tensor, w_gate_up: torch.Tensor) -> Tuple[torch.Ten
     gu = torch.empty(m, 2 * f, dtype=torch.bfloat16, device=x.device)
     act = torch.empty(m, f, dtype=torch.bfloat16, device=x.device)
     ops().gemm_pair_bf16(x, w_gate_up, gu, act, None, None, False, False, 1.0, 0.0, 1, 0, status_word(x.device),
-                         None)
+                         None, _DYNAMIC)
     return gu, act
 
 
@@ -123,5 +134,5 @@ def gemm_swiglu_bwd(dy: torch.Tensor, w_down: torch.Tensor, gate_up: torch.Tenso
     """
     dgu = torch.empty_like(gate_up)
     ops().gemm_pair_bf16(dy, w_down, dgu, None, None, gate_up, False, True, 1.0, 0.0, 2, _FORCE_BN,
-                         status_word(dy.device), None)
+                         status_word(dy.device), None, _DYNAMIC)
     return dgu

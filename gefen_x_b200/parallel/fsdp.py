@@ -125,7 +125,8 @@ class ShardedTrainer:
                  wait_iters: int = 8_000_000, opt_kwargs: Optional[dict] = None,
                  ag_gemm: bool = False, ag_fetch_ctas: int = 32, muon_kwargs: Optional[dict] = None,
                  gather_mode: str = "ce", reduce_ctas: int = 148, reduce_mode: str = "ce",
-                 sparse_embedding: bool = True, embed_capacity: int = 16384, nvls: Optional[bool] = None):
+                 sparse_embedding: bool = True, embed_capacity: int = 16384, nvls: Optional[bool] = None,
+                 gemm_schedule: str = "auto"):
         self.cfg = cfg
         self.world, self.rank = int(world), int(rank)
         self.device = torch.device(device if device is not None else
@@ -212,6 +213,16 @@ class ShardedTrainer:
         if nvls and not self.nvls and world > 1:
             raise RuntimeError("nvls=True, but the symmetric arena has no multicast mapping on this system "
                                "(or the dtype is not bf16)")
+        if world > 1 and cuda:
+            # with several ranks, kernels of the communication streams (gradient reduce-scatter, copies)
+            # share SMs with the products: let the pairs draw tiles dynamically instead of a fixed split
+            from ..ops import tcgemm as _tcgemm
+
+            _tcgemm.set_dynamic_schedule(gemm_schedule != "static")
+        elif cuda and gemm_schedule == "dynamic":
+            from ..ops import tcgemm as _tcgemm
+
+            _tcgemm.set_dynamic_schedule(True)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.flags = FlagBoard(self.arena, n_flag_slots, self.status, wait_iters)
         self.wait_iters = int(wait_iters)

@@ -581,3 +581,47 @@ def test_operators_trace_under_torch_compile():
         assert torch.equal(a, b), n
         assert torch.equal(oa.state[a]["m_codebook"], ob.state[b]["m_codebook"]), n
 
+
+def test_pair_gemm_dynamic_schedule_matches_static():
+    """The dynamic tile schedule (pairs draw units from a device counter through the shared-memory
+    ring) computes exactly what the static one does: plain, K-split tail, fused SwiGLU epilogues,
+    the gradient-norm sums (same total; placement varies), and the counter is back at zero after
+    every launch (launch after launch on the same stream)."""
+    from gefen_x_b200.ops import tcgemm
+
+    g = torch.Generator().manual_seed(21)
+    dev = _dev()
+    shapes = [(4096, 4096, 1024, False, False), (1024, 768, 8192, True, True), (4352, 4352, 512, False, True),
+              (300, 264, 200, False, False), (2048, 6144, 2560, False, False)]
+    try:
+        for m, n, k, a_t, b_t in shapes:
+            a = torch.randn((k, m) if a_t else (m, k), generator=g).bfloat16().to(dev)
+            b = torch.randn((k, n) if b_t else (n, k), generator=g).bfloat16().to(dev)
+            d = torch.randn(m, n, generator=g).bfloat16().to(dev)
+            tcgemm.set_dynamic_schedule(False)
+            want = tcgemm.gemm(a, b, a_t=a_t, b_t=b_t, alpha=0.5, beta=1.0, d=d)
+            sq0 = torch.zeros(2048, device=dev)
+            tcgemm.gemm(a, b, a_t=a_t, b_t=b_t, sumsq=sq0)
+            tcgemm.set_dynamic_schedule(True)
+            for _ in range(3):                                     # repeated launches reuse the counter
+                got = tcgemm.gemm(a, b, a_t=a_t, b_t=b_t, alpha=0.5, beta=1.0, d=d)
+                assert torch.equal(got, want), (m, n, k)
+            sq1 = torch.zeros(2048, device=dev)
+            tcgemm.gemm(a, b, a_t=a_t, b_t=b_t, sumsq=sq1)
+            assert abs(sq1.sum().item() - sq0.sum().item()) <= 1e-5 * sq0.sum().item()
+        x = (torch.randn(1024, 512, generator=g) * 0.5).bfloat16().to(dev)
+        wgu = (torch.randn(2 * 1792, 512, generator=g) * 0.05).bfloat16().to(dev)
+        dy = (torch.randn(1024, 1024, generator=g) * 0.5).bfloat16().to(dev)
+        wd = (torch.randn(1024, 1792, generator=g) * 0.03).bfloat16().to(dev)
+        tcgemm.set_dynamic_schedule(False)
+        gu0, act0 = tcgemm.gemm_swiglu_fwd(x, wgu)
+        dgu0 = tcgemm.gemm_swiglu_bwd(dy, wd, gu0)
+        tcgemm.set_dynamic_schedule(True)
+        gu1, act1 = tcgemm.gemm_swiglu_fwd(x, wgu)
+        dgu1 = tcgemm.gemm_swiglu_bwd(dy, wd, gu1)
+        assert torch.equal(gu0, gu1) and torch.equal(act0, act1) and torch.equal(dgu0, dgu1)
+        torch.cuda.synchronize()
+        assert int(tcgemm.status_word(dev).item()) == 0
+    finally:
+        tcgemm.set_dynamic_schedule(False)
+
