@@ -261,7 +261,11 @@ def run_ours(args):
         "impl_config": {"rs_mode": trainer.rs_mode, "ag_gemm": trainer.ag_gemm, "attention": args.attn,
                         "gemm": args.gemm, "gather": trainer.gather_mode, "reduce": trainer.reduce_mode,
                         "reduce_ctas": trainer.reduce_ctas, "sparse_embedding": trainer.sparse_embed, "nvls": trainer.nvls,
-                        "gemm_schedule": args.gemm_schedule},
+                        "gemm_schedule": args.gemm_schedule,
+                        # kernel family of the optimizer's launch plans: 1 register-pipelined, 2 NVLS
+                        # sources, 3 streamed through shared-memory rings, 0 generic
+                        "update_plan_kinds": sorted({int(getattr(pl, "fast", -1)) for pl in
+                                                     getattr(getattr(trainer.opt, "_plan_cache", None), "_plans", {}).values()})},
     }
     if rank == 0:
         print(json.dumps(out), flush=True)

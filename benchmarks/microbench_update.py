@@ -52,6 +52,8 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--shapes", default="")
+    ap.add_argument("--no-streaming", action="store_true",
+                    help="ours: the register-pipelined fast kernels instead of the streamed ones")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     if args.impl == "reference":
@@ -61,6 +63,9 @@ def main():
         from gefen import Gefen
     else:
         from gefen_x_b200 import Gefen
+        from gefen_x_b200.ops import update as _update
+
+        _update.set_streaming(not args.no_streaming)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)   # 2x the 126 MB L2
     # A few milliseconds of device work queued ahead of every timed step, so that the host
     # has enqueued the whole step before the device reaches the first event (the events
@@ -99,7 +104,8 @@ def main():
         state_bytes = sum(v.numel() * v.element_size() for v in st.values() if torch.is_tensor(v))
         rec = {"shape": name, "impl": args.impl, "ms_median": med, "ms_min": times[0],
                "gbs": nbytes / med / 1e6, "hbm_fraction_of_measured": nbytes / med / 1e6 / peak,
-               "period": int(st["automatic_period"]), "state_bytes_per_param": state_bytes / p.numel()}
+               "period": int(st["automatic_period"]),
+               "plan_fast": sorted({pl.fast for pl in opt._plan_cache._plans.values()}) if args.impl == "ours" else None, "state_bytes_per_param": state_bytes / p.numel()}
         results.append(rec)
         print(json.dumps(rec), flush=True)
         del opt, p, grads

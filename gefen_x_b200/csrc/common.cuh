@@ -42,11 +42,13 @@ template <typename T> __device__ __forceinline__ float round_to(float v) { retur
 // ---- 8-element vector access -----------------------------------------------
 template <typename T> struct Vec8 {
     // 16-bit types: one 16-byte transaction
-    static __device__ __forceinline__ void load(const T* p, float (&o)[8]) {
-        uint4 r = *reinterpret_cast<const uint4*>(p);
+    static __device__ __forceinline__ void unpack(const uint4& r, float (&o)[8]) {
         const T* e = reinterpret_cast<const T*>(&r);
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = to_f<T>(e[i]);
+    }
+    static __device__ __forceinline__ void load(const T* p, float (&o)[8]) {
+        unpack(*reinterpret_cast<const uint4*>(p), o);
     }
     static __device__ __forceinline__ void store(T* p, const float (&v)[8]) {
         uint4 r;
@@ -183,7 +185,7 @@ template <int VEC> struct RawIdx {
 // thr[i] = fp32((cb[i] + cb[i + 1]) / 2):  index = #{ i : thr[i] < v }, so a value on
 // a threshold goes to the lower codeword.  A 16384-bucket table resolves almost
 // every value with one load: lut[b] = (thresholds in lower buckets) | (thresholds
-// inside bucket b) << 8, with bucket(x) = floor(fma(x, 8192, 8192)) clamped to
+// inside bucket b) << 8, with bucket(x) = rint(sat(fma(x, 0.5, 0.5)) * 16383) in
 // [0, 16383]; only values whose bucket holds a threshold compare against it.
 // NaN maps to index 0.
 //
@@ -200,10 +202,16 @@ __device__ __forceinline__ float rep_load(const float* t, int i) {
     return t[(i << 5) | (threadIdx.x & 31)];
 }
 
+// bucket(x) = round-to-nearest-even(sat(fma(x, 0.5, 0.5)) * 16383): a saturating fma maps [-1, 1]
+// to [0, 1] (NaN to 0), a second fma adds 2^23 so that the rounded product lands in the low mantissa
+// bits; no clamp and no float-to-int conversion.  Monotonic, and the table is built with the same
+// function on the host.
+__device__ __forceinline__ uint32_t lut_bucket_bits(float v) {
+    const float t = __saturatef(__fmaf_rn(v, 0.5f, 0.5f));
+    return __float_as_uint(__fmaf_rn(t, (float)(kLutBuckets - 1), 8388608.0f));
+}
 __device__ __forceinline__ int lut_bucket(float v) {
-    const float t = fminf(fmaxf(__fmaf_rn(v, (float)(kLutBuckets / 2), (float)(kLutBuckets / 2)), 0.0f),
-                          (float)(kLutBuckets - 1));
-    return (int)t;   // NaN: fmaxf(NaN, 0) = 0
+    return (int)(lut_bucket_bits(v) & (uint32_t)(kLutBuckets - 1));
 }
 
 __device__ __forceinline__ int nearest_index(float v, const QuantTables& q) {

@@ -83,6 +83,25 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     return false;
 }
 
+// The same bounded wait for a role that runs far ahead of the others and would otherwise poll for
+// most of the kernel (a producer waiting for a free ring slot): it sleeps between polls, so that it
+// does not take issue slots from the warps that do the arithmetic.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  unsigned sleep_ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (int it = 0;; ++it) {
+        __nanosleep(sleep_ns);
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 15) == 15) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitCycles) break;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+
 // The same wait with acquire semantics at cluster scope: for barriers whose arrivals come from the
 // peer CTA after plain stores into this CTA's shared memory (st.shared::cluster + release.cluster).
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {

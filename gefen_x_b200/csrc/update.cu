@@ -26,7 +26,13 @@
 // all take the 8-wide single-source path run the "fast" tile loops: one row per
 // iteration with the next row's raw chunk prefetched into registers, a loop body
 // small enough for the instruction cache, 80 registers and three CTAs per SM.
+// Plans of 2-byte tensors whose rows start on 16-element boundaries run the "streamed"
+// kernels instead: one CTA per SM holds the tables once and three groups of 256 threads, each
+// with a producer warp that feeds a shared-memory ring of row steps with bulk async copies
+// (cp.async.bulk, mbarrier transaction counts), so that 150 KB per SM are in flight without
+// costing registers and the arithmetic never waits on a global load.
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 #include "update.h"
 #include <type_traits>
 
@@ -1032,6 +1038,536 @@ __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_apply
     }
 }
 
+// ---------------------------------------------------------------------------
+// streamed kernels (fast plans of 2-byte tensors with 16-element row alignment)
+// ---------------------------------------------------------------------------
+// A CTA holds kGroups consumer groups of kThreads threads and one producer warp per group.  A
+// group behaves like one CTA of the fast kernels above (same tile ranges, same thread-to-chunk
+// mapping, same arithmetic and summation order), but its chunks arrive through a ring of
+// shared-memory stages.  One stage is one row step of the group: trows rows of tcols * 8
+// elements, stored so that the chunk of group thread t lies at element t * 8.  The producer warp
+// walks the same tile range and copies one row per lane with cp.async.bulk; the copies complete
+// the stage's "full" mbarrier by byte count, the eight consumer warps release the stage through
+// its "empty" mbarrier as soon as their chunks are in registers.  Every wait is bounded: a wait
+// that runs out raises the CTA's abort flag and the status word, after which no thread waits or
+// computes again but all still walk their ranges, so that the group barriers stay matched.
+constexpr int kGroups = 3;
+constexpr int kStreamThreads = kGroups * (kThreads + 32);
+constexpr int kStatsStages = 8;
+constexpr int kApplyStages = 5;
+constexpr int kChunkBytes2 = kThreads * 8 * 2;            // one row step of 2-byte elements
+constexpr int kStatsStageBytes = kChunkBytes2 + kThreads * 8;          // g, idx
+constexpr int kApplyStageBytes = 2 * kChunkBytes2 + kThreads * 8;      // g, p, idx
+// tables of the streamed kernels: the lane-replicated codebook with one more row of +inf (the
+// "next codeword" of the last one), then the thresholds and the bucket table
+constexpr int kRepFloatsS = (kCodewords + 1) * 32;
+constexpr size_t kTabStats = ((size_t)(16 + kRepFloatsS) * sizeof(float) + 127) / 128 * 128;
+constexpr size_t kTabFull = (kTabStats + kCodewords * sizeof(float) + kLutBuckets * sizeof(uint16_t) + 127) / 128 * 128;
+constexpr size_t kSmemStatsStream = kTabStats + (size_t)kGroups * kStatsStages * kStatsStageBytes;
+constexpr size_t kSmemApplyStream = kTabFull + (size_t)kGroups * kApplyStages * kApplyStageBytes;
+static_assert(kSmemApplyStream <= 232448 && kSmemStatsStream <= 232448, "shared memory of the streamed kernels");
+
+struct StreamShared {
+    uint64_t full[kGroups][8];
+    uint64_t empty[kGroups][8];
+    long long blk[kGroups][kThreads / 32];
+    float val[kGroups][kThreads / 32];
+    float sum[kGroups][kThreads / 32];
+    int abort_flag;
+};
+
+template <int D, int STAGE_BYTES>
+struct Ring {
+    uint64_t* full;
+    uint64_t* empty;
+    unsigned char* base;
+    volatile int* abort_flag;
+    int slot;
+    uint32_t phase;
+    __device__ __forceinline__ unsigned char* stage() const { return base + slot * STAGE_BYTES; }
+    __device__ __forceinline__ void advance() {
+        if (++slot == D) { slot = 0; phase ^= 1u; }
+    }
+};
+
+__device__ __forceinline__ void group_barrier(int group) {
+    asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(kThreads) : "memory");
+}
+
+// runmax_flush_cta for one consumer group (its own named barrier and merge slots)
+__device__ __forceinline__ void runmax_flush_group(RunMax& r, StreamShared& sh, int group, int lt) {
+    const float m = warp_max(r.val);
+    const float t = r.sum_dst ? warp_sum(r.sum) : 0.f;
+    const int w = lt >> 5;
+    if ((lt & 31) == 0) { sh.blk[group][w] = r.blk; sh.val[group][w] = m; sh.sum[group][w] = t; }
+    group_barrier(group);
+    if (lt == 0) {
+        long long cur = -1;
+        float cv = 0.f, cs = 0.f;
+        for (int i = 0; i <= kThreads / 32; ++i) {
+            const long long b = i < kThreads / 32 ? sh.blk[group][i] : -2;
+            if (b == cur && b >= 0) {
+                cv = fmaxf(cv, sh.val[group][i]);
+                cs += sh.sum[group][i];
+                continue;
+            }
+            if (cur >= 0) {
+                atomic_max_nonneg(r.dst + cur, cv);
+                if (r.sum_dst) atomicAdd(r.sum_dst + cur, cs);
+            }
+            cur = b;
+            if (b >= 0) { cv = sh.val[group][i]; cs = sh.sum[group][i]; }
+        }
+    }
+    group_barrier(group);
+    r.blk = -1;
+    r.val = 0.f;
+    r.sum = 0.f;
+}
+
+__device__ __forceinline__ void bulk_load_row(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(ptx::smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(ptx::smem_u32(bar))
+                 : "memory");
+}
+
+// The producer warp of a group: walks tiles [T0, T1) exactly as the consumers do and fills one
+// stage per row step.  APPLY also brings the parameter rows.
+template <typename T, int D, int STAGE_BYTES, bool APPLY>
+__device__ void stream_producer(const LaunchCommon& c, long long T0, long long T1, Ring<D, STAGE_BYTES> ring) {
+    static_assert(sizeof(T) == 2, "the streamed kernels take 2-byte tensors");
+    const int lane = threadIdx.x & 31;
+    Hot d;
+    TileWalk w;
+    walk_begin(c, T0, w, d);
+    for (long long tile = T0; tile < T1;) {
+        const int n = (int)min(T1 - tile, (long long)(w.n_row_tiles - w.rt));
+        const TileCursor t = walk_cursor(w, d, n);
+        const int col0 = t.ct * d.tcols * 8;
+        const int width = min(d.tcols * 8, d.cols - col0);          // elements of a row inside this column tile
+        const char* g0 = reinterpret_cast<const char*>(d.g0);
+        const char* p0 = reinterpret_cast<const char*>(d.p);
+        const char* i0 = reinterpret_cast<const char*>(d.idx);
+        for (int rb = t.r0; rb < t.r1; rb += d.trows) {
+            const int nrows = min(d.trows, t.r1 - rb);
+            if (!ptx::mbar_wait_relaxed(ring.empty + ring.slot, ring.phase ^ 1u, ring.abort_flag, 200u)) {
+                if (lane == 0 && c.status) atomicExch(c.status, (int)kWaitTimeout);
+                return;
+            }
+            if (lane == 0) ptx::mbar_expect_tx(ring.full + ring.slot, (uint32_t)(nrows * width * (APPLY ? 5 : 3)));
+            __syncwarp();
+            if (lane < nrows) {
+                const size_t off = (size_t)(rb + lane) * (size_t)d.cols + (size_t)col0;
+                unsigned char* st = ring.stage();
+                uint64_t* bar = ring.full + ring.slot;
+                bulk_load_row(st + lane * d.tcols * 16, g0 + off * 2, (uint32_t)width * 2u, bar);
+                if constexpr (APPLY) {
+                    bulk_load_row(st + kChunkBytes2 + lane * d.tcols * 16, p0 + off * 2, (uint32_t)width * 2u, bar);
+                    bulk_load_row(st + 2 * kChunkBytes2 + lane * d.tcols * 8, i0 + off, (uint32_t)width, bar);
+                } else {
+                    bulk_load_row(st + kChunkBytes2 + lane * d.tcols * 8, i0 + off, (uint32_t)width, bar);
+                }
+            }
+            ring.advance();
+        }
+        tile += n;
+        w.rt += n;
+        if (w.rt == w.n_row_tiles) {
+            w.rt = 0;
+            if (++w.ct == d.n_col_tiles) {
+                w.ct = 0;
+                if (tile < T1) {
+                    ++w.ti;
+                    d = load_hot(c.descs + w.ti);
+                    w.n_row_tiles = (d.rows + d.rows_per_tile - 1) / d.rows_per_tile;
+                }
+            }
+        }
+    }
+}
+
+// consumer side of one stage: wait for it; release it once this warp has read what it needs
+template <int D, int STAGE_BYTES>
+__device__ __forceinline__ bool stage_wait(Ring<D, STAGE_BYTES>& ring) {
+    return ptx::mbar_wait(ring.full + ring.slot, ring.phase, ring.abort_flag);
+}
+template <int D, int STAGE_BYTES>
+__device__ __forceinline__ void stage_release(Ring<D, STAGE_BYTES>& ring, bool ok, int lt) {
+    __syncwarp();
+    if (ok && (lt & 31) == 0) ptx::mbar_arrive(ring.empty + ring.slot);
+    ring.advance();
+}
+
+// Shared-memory addresses of the tables as 32-bit shared-window addresses, so that a lookup is
+// one address instruction and one load: `cb_lane` points at this lane's copy of codeword 0 (the
+// copies of codeword i lie 128 bytes apart), `lut2` is the bucket table's address minus twice the
+// bit pattern of 2^23 (the bucket arrives as the low mantissa bits of 2^23 + bucket).
+struct StreamTables {
+    uint32_t cb_lane;
+    uint32_t lut2;
+    QuantTables q;      // generic pointers for the rare full search
+};
+
+__device__ __forceinline__ StreamTables load_tables_stream(const LaunchCommon& c, bool full) {
+    float* base = reinterpret_cast<float*>(gx_smem_raw);
+    float* cb = base + 16;
+    float* thr = cb + kRepFloatsS;
+    uint16_t* lut = reinterpret_cast<uint16_t*>(thr + kCodewords);
+    for (int i = threadIdx.x; i <= kCodewords; i += blockDim.x) {
+        const float v = i < kCodewords ? c.codebook[i] : __int_as_float(0x7f800000);
+        float4* row = reinterpret_cast<float4*>(cb + i * 32);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) row[k] = make_float4(v, v, v, v);
+    }
+    if (full) {
+        for (int i = threadIdx.x; i < kCodewords; i += blockDim.x) thr[i] = c.thresholds[i];
+        const uint4* src = reinterpret_cast<const uint4*>(c.lut);
+        uint4* dst = reinterpret_cast<uint4*>(lut);
+        constexpr int kPieces = kLutBuckets * (int)sizeof(uint16_t) / 16;
+        for (int i = threadIdx.x; i < kPieces; i += blockDim.x) dst[i] = src[i];
+    }
+    StreamTables t;
+    t.cb_lane = ptx::smem_u32(cb) + ((threadIdx.x & 31) << 2);
+    t.lut2 = ptx::smem_u32(lut) - 2u * 0x4B000000u;
+    t.q.cb = cb;
+    t.q.thr = full ? thr : nullptr;
+    t.q.lut = full ? lut : nullptr;
+    __syncthreads();
+    return t;
+}
+
+// the tables never change after the set-up barrier: plain (non-volatile) loads the compiler may schedule freely
+__device__ __forceinline__ float lds_f32(uint32_t a) {
+    float v;
+    asm("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float lds_f32_next(uint32_t a) {       // the next codeword's copy
+    float v;
+    asm("ld.shared.f32 %0, [%1+128];" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
+    uint32_t v;
+    asm("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+// codeword of byte k of an index word
+template <int K>
+__device__ __forceinline__ float cb_of_byte(const StreamTables& t, uint32_t w) {
+    return lds_f32(t.cb_lane + (__byte_perm(w, 0u, 0x4440u + K) << 7));
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+template <typename T>
+__device__ __forceinline__ void stats_range_stream(const Hot& d, const StreamTables& s, const TileCursor& t, float gs,
+                                                   float (&csum)[8], RunMax& run,
+                                                   Ring<kStatsStages, kStatsStageBytes>& ring, int lt) {
+    const int tx = lt % d.tcols, ty = lt / d.tcols;
+    const int c0 = (t.ct * d.tcols + tx) * 8;
+    const bool act = c0 < d.cols;
+    const int stride = d.trows;
+    const int n_steps = (t.r1 - t.r0 + stride - 1) / stride;
+    const float b1 = d.beta1, omb1 = d.omb1;
+    // rows of one block only (blocks are whole rows or runs of rows): no per-row agreement needed
+    const bool row_blocks = d.blk_mode == 0 || d.blk_mode == 2;
+    int r = t.r0 + ty;
+    BlockIter it = block_iter(d, r, act ? c0 : 0);
+    float mo_next = (act && r < t.r1) ? d.mag[it.blk] : 0.f;
+#pragma unroll 1
+    for (int step = 0; step < n_steps; ++step, r += stride) {
+        const bool row_ok = r < t.r1;                 // uniform across the warp: a warp shares ty
+        const int blk = (act && row_ok) ? it.blk : -1;
+        const float mo = mo_next;
+        block_iter_next(d, it);
+        mo_next = (act && r + stride < t.r1) ? d.mag[it.blk] : 0.f;
+        uint4 gw = make_uint4(0, 0, 0, 0);
+        uint2 iw = make_uint2(0, 0);
+        const bool ok = stage_wait(ring);
+        if (ok && act && row_ok) {
+            const unsigned char* st = ring.stage();
+            gw = *reinterpret_cast<const uint4*>(st + lt * 16);
+            iw = *reinterpret_cast<const uint2*>(st + kChunkBytes2 + lt * 8);
+        }
+        stage_release(ring, ok, lt);
+        if (!ok || !row_ok) continue;
+        float amax = 0.f, rs = 0.f;
+        if (act) {
+            float g[8];
+            Vec8<T>::unpack(gw, g);
+            float cbv[8];
+            cbv[0] = cb_of_byte<0>(s, iw.x); cbv[1] = cb_of_byte<1>(s, iw.x);
+            cbv[2] = cb_of_byte<2>(s, iw.x); cbv[3] = cb_of_byte<3>(s, iw.x);
+            cbv[4] = cb_of_byte<0>(s, iw.y); cbv[5] = cb_of_byte<1>(s, iw.y);
+            cbv[6] = cb_of_byte<2>(s, iw.y); cbv[7] = cb_of_byte<3>(s, iw.y);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float ge = __fmul_rn(g[e], gs);
+                const float m = ema_momentum(cbv[e], mo, ge, b1, omb1);
+                amax = fmaxf(amax, fabsf(m));
+                rs = __fmaf_rn(ge, ge, rs);
+                csum[e] = __fmaf_rn(ge, ge, csum[e]);
+            }
+        }
+        const float rs_lane = rs;
+        if (!run.sum_dst) {
+            rs = warp_sum(rs);
+            if ((lt & 31) == 0 && act) atomicAdd(d.row_sq + r, rs);
+        }
+        if (row_blocks) {
+            const int b0 = __shfl_sync(0xffffffffu, blk, 0);               // lane 0 has the lowest column
+            if (b0 >= 0) {
+                if ((long long)b0 != run.blk) { runmax_flush(run); run.blk = b0; }
+                run.val = fmaxf(run.val, amax);
+                run.sum += rs_lane;
+            }
+            continue;
+        }
+        const unsigned live = __ballot_sync(0xffffffffu, act);
+        if (live) {
+            const int b0 = __shfl_sync(0xffffffffu, blk, 0);
+            const int b1l = __shfl_sync(0xffffffffu, blk, 31 - __clz((int)live));
+            if (b0 == b1l) {
+                if ((long long)b0 != run.blk) { runmax_flush(run); run.blk = b0; }
+                run.val = fmaxf(run.val, amax);
+                run.sum += rs_lane;
+            } else if (act) {
+                atomic_max_nonneg(run.dst + blk, amax);
+                if (run.sum_dst) atomicAdd(run.sum_dst + blk, rs_lane);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void stream_init(StreamShared& sh) {
+    if (threadIdx.x == 0) {
+        for (int g = 0; g < kGroups; ++g) {
+            for (int k = 0; k < 8; ++k) {
+                ptx::mbar_init(&sh.full[g][k], 1);
+                ptx::mbar_init(&sh.empty[g][k], kThreads / 32);
+            }
+        }
+        sh.abort_flag = 0;
+        ptx::mbar_init_fence();
+    }
+    // the __syncthreads of load_tables, which every thread calls next, publishes the barriers
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kStreamThreads, 1) factored_stats_stream_kernel(LaunchCommon c) {
+    __shared__ StreamShared sh;
+    stream_init(sh);
+    const StreamTables s = load_tables_stream(c, false);
+    const bool producer = threadIdx.x >= kGroups * kThreads;
+    const int group = producer ? (threadIdx.x - kGroups * kThreads) / 32 : threadIdx.x / kThreads;
+    const int lt = threadIdx.x - group * kThreads;              // consumers only
+    const long long v = (long long)blockIdx.x * kGroups + group, nv = (long long)gridDim.x * kGroups;
+    const long long T0 = (long long)c.total_tiles * v / nv;
+    const long long T1 = (long long)c.total_tiles * (v + 1) / nv;
+    if (T0 >= T1) return;
+    Ring<kStatsStages, kStatsStageBytes> ring;
+    ring.full = sh.full[group];
+    ring.empty = sh.empty[group];
+    ring.base = gx_smem_raw + kTabStats + (size_t)group * kStatsStages * kStatsStageBytes;
+    ring.abort_flag = &sh.abort_flag;
+    ring.slot = 0;
+    ring.phase = 0;
+    if (producer) {
+        stream_producer<T, kStatsStages, kStatsStageBytes, false>(c, T0, T1, ring);
+        return;
+    }
+    const float gs = c.gscale ? *c.gscale : 1.0f;
+    float csum8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    RunMax run{nullptr, nullptr, -1, 0.f, 0.f, 1};
+    Hot d;
+    TileWalk w;
+    walk_begin(c, T0, w, d);
+    run.dst = d.mag_new;
+    run.sum_dst = d.row_only ? d.row_sq : nullptr;
+    for (long long tile = T0; tile < T1;) {
+        const int n = (int)min(T1 - tile, (long long)(w.n_row_tiles - w.rt));
+        const TileCursor t = walk_cursor(w, d, n);
+        stats_range_stream<T>(d, s, t, gs, csum8, run, ring, lt);
+        tile += n;
+        w.rt += n;
+        bool col_change = false, tensor_change = false;
+        if (w.rt == w.n_row_tiles) {
+            w.rt = 0;
+            col_change = true;
+            if (++w.ct == d.n_col_tiles) { w.ct = 0; tensor_change = true; }
+        }
+        const bool last = tile == T1;
+        if ((col_change || last) && !d.row_only) {
+            const int ct_done = col_change ? (tensor_change ? d.n_col_tiles - 1 : w.ct - 1) : w.ct;
+            flush_cols<8>(d, ct_done, csum8);
+        }
+        if (tensor_change || last) runmax_flush_group(run, sh, group, lt);
+        if (tensor_change && !last) {
+            ++w.ti;
+            d = load_hot(c.descs + w.ti);
+            w.n_row_tiles = (d.rows + d.rows_per_tile - 1) / d.rows_per_tile;
+            run.dst = d.mag_new;
+            run.sum_dst = d.row_only ? d.row_sq : nullptr;
+        }
+    }
+    if (sh.abort_flag && lt == 0 && c.status) atomicExch(c.status, (int)kWaitTimeout);
+}
+
+// One element of the streamed apply: momentum, nearest codeword, parameter.
+//   m = (cb[i] * mag_old) * b1 + g * (1 - b1)          (the eager roundings: indices stay bit-exact)
+//   v = m / mag_new -> bucket -> lo = thresholds below the bucket; the codewords lo and lo + 1 come
+//   from this lane's copies (128 bytes apart); their midpoint is the decision threshold, computed as
+//   the host computes it (fp32 sum, halved), so the table of thresholds is not read.  The host sends
+//   a plan here only when no bucket holds more than one threshold: one comparison settles it.
+//   p = p * wd - (q * mag_new) * (lr / bc1) / (rf * cf + eps)
+struct ApplyScalars {
+    float gs, mo, mn, inv, rf, b1, omb1, eps, coef, wdf;
+};
+
+template <typename T, bool WD>
+__device__ __forceinline__ void apply_element(const StreamTables& s, const ApplyScalars& a, float g, float cbv, float cf,
+                                              float& pf, uint32_t& knew) {
+    const float ge = __fmul_rn(g, a.gs);
+    const float m = ema_momentum(cbv, a.mo, ge, a.b1, a.omb1);
+    const float v = __fmul_rn(m, a.inv);
+    const uint32_t lo = lds_u16(s.lut2 + (lut_bucket_bits(v) << 1)) & 0xffu;
+    const uint32_t addr = s.cb_lane + (lo << 7);
+    const float clo = lds_f32(addr), chi = lds_f32_next(addr);
+    const float thr = __fmul_rn(__fadd_rn(clo, chi), 0.5f);
+    const bool up = thr < v;
+    knew = lo + (up ? 1u : 0u);
+    const float qv = __fmul_rn(up ? chi : clo, a.mn);
+    const float h = __fmaf_rn(a.rf, cf, a.eps);
+    float pw = pf;
+    if constexpr (WD) pw = round_to<T>(__fmul_rn(pf, a.wdf));
+    pf = __fmaf_rn(-__fmul_rn(qv, a.coef), rcp_approx(h), pw);
+}
+
+template <typename T, bool WD>
+__device__ __forceinline__ void apply_range_stream(const Hot& d, const StreamTables& s, const TileCursor& t, float gs,
+                                                   const float (&cf)[8],
+                                                   Ring<kApplyStages, kApplyStageBytes>& ring, int lt) {
+    const int tx = lt % d.tcols, ty = lt / d.tcols;
+    const int c0 = (t.ct * d.tcols + tx) * 8;
+    const bool act = c0 < d.cols;
+    ApplyScalars a;
+    a.gs = gs;
+    a.b1 = d.beta1; a.omb1 = d.omb1; a.eps = d.eps;
+    a.coef = __fmul_rn(d.scal[0], d.scal[2]);      // lr / bias correction 1
+    a.wdf = d.scal[3];
+    T* p = reinterpret_cast<T*>(d.p);
+    const int stride = d.trows;
+    const int n_steps = (t.r1 - t.r0 + stride - 1) / stride;
+    int r = t.r0 + ty;
+    BlockIter it = block_iter(d, r, act ? c0 : 0);
+    float mo_n = 0.f, mn_n = 0.f, rf_n = 0.f;
+    if (act && r < t.r1) {
+        mo_n = d.mag[it.blk];
+        mn_n = d.mag_new[it.blk];
+        rf_n = d.rfac[d.row_only ? it.blk : r];
+    }
+#pragma unroll 1
+    for (int step = 0; step < n_steps; ++step, r += stride) {
+        const bool valid = act && r < t.r1;
+        const unsigned off = it.off;
+        a.mo = mo_n; a.mn = mn_n; a.rf = rf_n;
+        block_iter_next(d, it);
+        if (act && r + stride < t.r1) {
+            mo_n = d.mag[it.blk];
+            mn_n = d.mag_new[it.blk];
+            rf_n = d.rfac[d.row_only ? it.blk : r + stride];
+        }
+        const bool ok = stage_wait(ring);
+        if (!ok || !valid) {
+            stage_release(ring, ok, lt);
+            continue;
+        }
+        const unsigned char* st = ring.stage();
+        a.inv = a.mn > 0.f ? __frcp_rn(a.mn) : 0.f;
+        const uint4 gw = *reinterpret_cast<const uint4*>(st + lt * 16);
+        const uint4 pwd = *reinterpret_cast<const uint4*>(st + kChunkBytes2 + lt * 16);
+        const uint2 iw = *reinterpret_cast<const uint2*>(st + 2 * kChunkBytes2 + lt * 8);
+        float g[8], pf[8], cbv[8];
+        uint32_t kn[8];
+        Vec8<T>::unpack(gw, g);
+        Vec8<T>::unpack(pwd, pf);
+        cbv[0] = cb_of_byte<0>(s, iw.x); cbv[1] = cb_of_byte<1>(s, iw.x);
+        cbv[2] = cb_of_byte<2>(s, iw.x); cbv[3] = cb_of_byte<3>(s, iw.x);
+        cbv[4] = cb_of_byte<0>(s, iw.y); cbv[5] = cb_of_byte<1>(s, iw.y);
+        cbv[6] = cb_of_byte<2>(s, iw.y); cbv[7] = cb_of_byte<3>(s, iw.y);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) apply_element<T, WD>(s, a, g[e], cbv[e], cf[e], pf[e], kn[e]);
+        uint2 io;
+        io.x = __byte_perm(__byte_perm(kn[0], kn[1], 0x0040), __byte_perm(kn[2], kn[3], 0x0040), 0x5410);
+        io.y = __byte_perm(__byte_perm(kn[4], kn[5], 0x0040), __byte_perm(kn[6], kn[7], 0x0040), 0x5410);
+        *reinterpret_cast<uint2*>(d.idx + off) = io;
+        store_param<T, 8>(p + off, pf);
+        stage_release(ring, true, lt);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kStreamThreads, 1) factored_apply_stream_kernel(LaunchCommon c) {
+    __shared__ StreamShared sh;
+    stream_init(sh);
+    const StreamTables s = load_tables_stream(c, true);
+    const bool producer = threadIdx.x >= kGroups * kThreads;
+    const int group = producer ? (threadIdx.x - kGroups * kThreads) / 32 : threadIdx.x / kThreads;
+    const int lt = threadIdx.x - group * kThreads;
+    const long long v = (long long)blockIdx.x * kGroups + group, nv = (long long)gridDim.x * kGroups;
+    const long long T0 = (long long)c.total_tiles * v / nv;
+    const long long T1 = (long long)c.total_tiles * (v + 1) / nv;
+    if (T0 >= T1) return;
+    Ring<kApplyStages, kApplyStageBytes> ring;
+    ring.full = sh.full[group];
+    ring.empty = sh.empty[group];
+    ring.base = gx_smem_raw + kTabFull + (size_t)group * kApplyStages * kApplyStageBytes;
+    ring.abort_flag = &sh.abort_flag;
+    ring.slot = 0;
+    ring.phase = 0;
+    if (producer) {
+        stream_producer<T, kApplyStages, kApplyStageBytes, true>(c, T0, T1, ring);
+        return;
+    }
+    const float gs = c.gscale ? *c.gscale : 1.0f;
+    float cf8[8];
+    Hot d;
+    TileWalk w;
+    walk_begin(c, T0, w, d);
+    bool reload = true;
+    for (long long tile = T0; tile < T1;) {
+        if (reload) {
+            const int c0 = (w.ct * d.tcols + lt % d.tcols) * 8;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) cf8[e] = d.row_only ? 1.0f : ((c0 + e < d.cols) ? d.cfac[c0 + e] : 0.f);
+            reload = false;
+        }
+        const int n = (int)min(T1 - tile, (long long)(w.n_row_tiles - w.rt));
+        const TileCursor t = walk_cursor(w, d, n);
+        if (d.scal[3] != 1.0f) apply_range_stream<T, true>(d, s, t, gs, cf8, ring, lt);
+        else apply_range_stream<T, false>(d, s, t, gs, cf8, ring, lt);
+        tile += n;
+        w.rt += n;
+        if (w.rt == w.n_row_tiles) {
+            w.rt = 0;
+            reload = true;
+            if (++w.ct == d.n_col_tiles) {
+                w.ct = 0;
+                if (tile < T1) {
+                    ++w.ti;
+                    d = load_hot(c.descs + w.ti);
+                    w.n_row_tiles = (d.rows + d.rows_per_tile - 1) / d.rows_per_tile;
+                }
+            }
+        }
+    }
+    if (sh.abort_flag && lt == 0 && c.status) atomicExch(c.status, (int)kWaitTimeout);
+}
+
 // mag <- mag_new ; mag_new <- 0, for every tensor of the plan
 __global__ void __launch_bounds__(kThreads) finalize_magnitude_kernel(LaunchCommon c) {
     for (int ti = 0; ti < c.n_tensors; ++ti) {
@@ -1142,7 +1678,16 @@ cudaError_t launch_factored_stats(const LaunchCommon& c, int dtype, int sm_count
     return dispatch(dtype, [&](auto* tag) {
         using T = std::remove_pointer_t<decltype(tag)>;
         // one row of raw chunks in flight beyond the current one (two were measured no faster)
-        if (c.fast == 2) {
+        if (c.fast == 3) {
+            if constexpr (sizeof(T) == 2) {
+                cudaFuncSetAttribute(factored_stats_stream_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)kSmemStatsStream);
+                factored_stats_stream_kernel<T><<<min(sm_count, (c.total_tiles + kGroups - 1) / kGroups), kStreamThreads,
+                                                  kSmemStatsStream, st>>>(c);
+            } else {
+                return cudaErrorInvalidValue;
+            }
+        } else if (c.fast == 2) {
             if constexpr (std::is_same_v<T, __nv_bfloat16>)
                 factored_stats_kernel<T, true, 1, true><<<grid, kThreads, kSmemStats, st>>>(c);
             else
@@ -1168,7 +1713,16 @@ cudaError_t launch_factored_apply(const LaunchCommon& c, int dtype, int sm_count
     const int grid = min(c.total_tiles, sm_count * (fast ? kFastCtas : 2));
     return dispatch(dtype, [&](auto* tag) {
         using T = std::remove_pointer_t<decltype(tag)>;
-        if (c.fast == 2) {
+        if (c.fast == 3 && !c.stochastic) {
+            if constexpr (sizeof(T) == 2) {
+                cudaFuncSetAttribute(factored_apply_stream_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)kSmemApplyStream);
+                factored_apply_stream_kernel<T><<<min(sm_count, (c.total_tiles + kGroups - 1) / kGroups), kStreamThreads,
+                                                  kSmemApplyStream, st>>>(c);
+            } else {
+                return cudaErrorInvalidValue;
+            }
+        } else if (c.fast == 2) {
             // multicast gradient sources exist only in the fast bf16 kernels (the plan builder makes
             // sure of it): nearest rounding, 8-wide chunks
             if constexpr (std::is_same_v<T, __nv_bfloat16>) {

@@ -73,6 +73,8 @@ struct LaunchCommon {
     uint32_t epoch;                   // value the exchange flags must reach in this launch
     int fast;                         // 1: every tensor takes the 8-wide path with one gradient source;
                                       // 2: the same, and that source is an NVLS multicast address (bf16)
+                                      // 3: as 1, 2-byte tensors whose rows start on 16-element boundaries:
+                                      //    the streamed kernels (shared-memory rings fed by bulk copies)
 };
 
 // All launchers return the cudaError_t of the launch.

@@ -173,26 +173,68 @@ def two_phase_block(period: int, nb: int) -> bool:
     return period >= 1024 and nb < 2048
 
 
+_STREAMING = True
+
+
+def set_streaming(on: bool) -> None:
+    """Whether new plans of 2-byte tensors may take the streamed kernels (shared-memory rings fed by
+    bulk async copies).  Off: the register-pipelined fast kernels.  Both compute the same values."""
+    global _STREAMING
+    _STREAMING = bool(on)
+
+
+_LUT_SINGLE: Dict[Any, bool] = {}
+
+
+def _lut_single(lut: torch.Tensor) -> bool:
+    """Whether no bucket of the packed search table holds more than one decision threshold.  The
+    streamed apply kernel resolves a value with one comparison and has no full search; a codebook
+    with codewords closer than a bucket (1.2e-4 of the normalised range) goes to the
+    register-pipelined kernels instead.  Cached per table (address and version); reading the answer
+    synchronises once per codebook.  During stream capture an unknown table counts as not single."""
+    key = (lut.data_ptr(), lut._version, lut.device)
+    hit = _LUT_SINGLE.get(key)
+    if hit is None:
+        if lut.is_cuda and torch.cuda.is_current_stream_capturing():
+            return False
+        hit = bool((((lut.to(torch.int32) & 0xFFFF) >> 8).max() <= 1).item())
+        if len(_LUT_SINGLE) > 64:
+            _LUT_SINGLE.clear()
+        _LUT_SINGLE[key] = hit
+    return hit
+
+
 def _aligned(ptr: int, n: int) -> bool:
     return ptr % n == 0
 
 
-def _row_only_cols(period: int) -> int:
-    """Column count of the matrix view of a row-only tensor: a divisor of the period, so that a
-    row never straddles two blocks, near 2048 elements (one 256-thread row of 8-wide chunks)
-    so that long blocks are cut into many rows and every CTA tile holds full 16-row columns."""
-    if period <= 4096 or period % 8:
-        return period
-    best = None
-    for c in range(4096, 255, -8):
-        if period % c == 0:
-            chunks = c // 8
-            waste = min((chunks + t - 1) // t * t - chunks for t in (256, 128, 64, 32))
-            if best is None or waste < best[0]:
-                best = (waste, c)
-                if waste == 0:
-                    break
-    return best[1] if best is not None else period
+def _row_only_cols(period: int, numel: Optional[int] = None) -> int:
+    """Column count of the matrix view of a row-only tensor.
+
+    Long blocks: a divisor of the period, so that a row never straddles two blocks, near 2048
+    elements (one 256-thread row of 8-wide chunks) so that long blocks are cut into many rows and
+    every CTA tile holds full 16-row columns; multiples of 16 are preferred (rows then start where
+    the bulk copies of the streamed kernels may start).  Short blocks (with ``numel`` given): several
+    whole blocks per row, up to 2048 elements, again a multiple of 16 if one exists, so that a
+    tensor of many tiny blocks is not walked as rows of a few elements."""
+    if period > 4096 and period % 8 == 0:
+        best = None
+        for c in range(4096, 255, -8):
+            if period % c == 0:
+                chunks = c // 8
+                waste = min((chunks + t - 1) // t * t - chunks for t in (256, 128, 64, 32))
+                key = (waste, c % 16 != 0)
+                if best is None or key < best[0]:
+                    best = (key, c)
+                    if key == (0, False):
+                        break
+        return best[1] if best is not None else period
+    if numel is not None and period < 1024 and period % 8 == 0 and numel % period == 0:
+        nb = numel // period
+        for k in range(min(nb, 2048 // period), 1, -1):
+            if nb % k == 0 and (period * k) % 16 == 0:
+                return period * k
+    return period
 
 
 def _pick_tcols(chunks: int) -> int:
@@ -254,7 +296,7 @@ class Plan:
             if kind == "factored":
                 nb = it.p.numel() // it.period
                 if it.row_only or it.emit:
-                    cols = _row_only_cols(it.period)
+                    cols = _row_only_cols(it.period, it.p.numel())
                     rows = it.p.numel() // cols
                     sizes.append((nb, nb, cols, nb, cols, rows))   # row statistics are per block
                 else:
@@ -291,7 +333,7 @@ class Plan:
             isinstance(it.grad, PeerGrad) and it.grad.mc_ptr and not it.emit and it.grad.mc_ptr % 16 == 0
             and it.p.numel() < 2 ** 31 - 1 and it.period % 8 == 0 and it.p.data_ptr() % 16 == 0
             and it.state["m_codebook"].data_ptr() % 8 == 0
-            and ((_row_only_cols(it.period) if it.row_only else it.p.shape[-1]) % 8 == 0)
+            and ((_row_only_cols(it.period, it.p.numel()) if it.row_only else it.p.shape[-1]) % 8 == 0)
             for it in items)
         base = self.scratch.data_ptr()
         cursor = 0
@@ -417,6 +459,16 @@ class Plan:
             if not self.fast:
                 raise RuntimeError("internal: a multicast plan did not qualify for the fast kernels")
             self.fast = 2
+        elif self.fast and _STREAMING and dtype in (torch.bfloat16, torch.float16) and all(
+                self._stream_ok(TensorDesc.from_buffer(buf, i * stride_)) for i in range(self.n)):
+            # the streamed kernels: rows are brought into shared memory by bulk async copies, whose
+            # source addresses and sizes must be multiples of 16 bytes for all three arrays
+            self.fast = 3
+
+    @staticmethod
+    def _stream_ok(d) -> bool:
+        ptrs = (d.idx, d.p, d.g[0])            # ctypes gives None for a null pointer
+        return d.row_only < 2 and d.cols % 16 == 0 and all(x is not None and x % 16 == 0 for x in ptrs)
 
     @staticmethod
     def signature_of(items: List[Item]):
@@ -453,9 +505,12 @@ class Plan:
         code = DTYPE_CODE[self.dtype]
         seed = 0 if sr_seed is None else int(sr_seed)
         if self.kind == "factored":
+            fast = int(self.fast)
+            if fast == 3 and not _lut_single(lut):
+                fast = 1
             ops().factored_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, thr, lut,
                                   gscale, status, code, seed, sr_seed is not None, int(wait_iters),
-                                  int(phases), int(epoch) & 0x7FFFFFFF, int(self.fast), sr_seed_dev)
+                                  int(phases), int(epoch) & 0x7FFFFFFF, fast, sr_seed_dev)
         else:
             ops().block_update(self.descs, self.tile_start, self.n, self.total_tiles, codebook, thr, lut,
                                gscale, status, code, seed, sr_seed is not None, sr_seed_dev)

@@ -318,10 +318,12 @@ def dequantize_indices(codebook: torch.Tensor, indices: torch.Tensor,
 
 
 def _bucket(values: torch.Tensor, buckets: int) -> torch.Tensor:
-    """``floor(fma(x, buckets/2, buckets/2))`` clamped to ``[0, buckets - 1]`` (fp32 fma, as on the device)."""
-    half = float(buckets // 2)
-    t = (values.double() * half + half).float()          # exact product and sum, one rounding
-    return t.clamp_(0.0, float(buckets - 1)).floor_().to(torch.long)
+    """``rint(sat(fma(x, 0.5, 0.5)) * (buckets - 1))`` with both fused multiply-adds rounded once to
+    fp32, as on the device (the second one adds 2^23 there, which rounds the product to the nearest
+    integer, ties to even)."""
+    t = (values.double() * 0.5 + 0.5).float().clamp_(0.0, 1.0)      # exact product and sum, one rounding
+    t = torch.nan_to_num(t, nan=0.0)
+    return torch.round(t.double() * float(buckets - 1)).to(torch.long)   # exact product; round half to even
 
 
 def codebook_search_lut(codebook: torch.Tensor, buckets: int = LUT_BUCKETS) -> torch.Tensor:

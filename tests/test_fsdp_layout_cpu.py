@@ -61,6 +61,11 @@ def test_row_only_matrix_view_keeps_rows_inside_blocks():
             assert 256 <= c <= 4096 and c % 8 == 0
         else:
             assert c == period
+    # short blocks: several whole blocks per row, rows that start on 16-element boundaries
+    for period, numel in ((8, 4096), (64, 4096), (24, 4800), (512, 8192)):
+        c = _row_only_cols(period, numel)
+        assert c % period == 0 and numel % c == 0 and c <= 2048 and c % 16 == 0 and c > period
+    assert _row_only_cols(8, 40) == 8 and _row_only_cols(1000, 3000) == 1000
     assert _pick_tcols(512) == 256 and _pick_tcols(48) in (32, 64)
     assert two_phase_block(1 << 20, 4) and not two_phase_block(64, 4) and not two_phase_block(1 << 20, 4096)
 

@@ -447,3 +447,56 @@ def test_non_contiguous_parameter_steps_like_its_contiguous_copy():
     assert torch.equal(oa.state[pa]["m_codebook"], ob.state[pb]["m_codebook"])
     torch.testing.assert_close(oa.state[pa]["v_row"], ob.state[pb]["v_row"], rtol=1e-5, atol=0)
 
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_streamed_update_kernels_match_the_register_pipelined_ones_bit_for_bit(dtype):
+    """Plans of 2-byte tensors with 16-element row alignment run the streamed kernels (rows arrive
+    through shared-memory rings filled by bulk async copies).  They keep the thread-to-chunk mapping
+    and the arithmetic of the register-pipelined kernels, so parameters, indices and magnitudes are
+    bit-identical and the second moments agree to the order of the atomics.  Shapes: a partial last
+    column tile, rows that do not fill the last row step, narrow rows (several rows per step),
+    1-D tensors, and more groups than tiles for the smallest plan."""
+    from gefen_x_b200 import Gefen
+    from gefen_x_b200.ops import update as U
+
+    shapes = [("w0", (96, 2064)), ("w1", (1000, 4096)), ("w2", (2048, 1024)), ("w3", (324, 48)),
+              ("w4", (64, 14336)), ("n0", (8192,)), ("n1", (4096,))]
+    fixed_periods = {"w0": 16512, "w1": 512000, "w2": 2048, "w3": 1296, "w4": 7168, "n0": 1024, "n1": 512}
+
+    def run(streaming, shp):
+        U.set_streaming(streaming)
+        try:
+            g = torch.Generator().manual_seed(3)
+            ps = [(n, (torch.randn(s, generator=g) * 0.05).to(dtype).to(_dev()).requires_grad_()) for n, s in shp]
+            opt = Gefen(ps, lr=1e-2, weight_decay=0.01)
+            # fixed block periods (the search would pick them from the data): one of each kind of
+            # block-to-row relation, all multiples of 8 as the 8-wide kernels need
+            opt._predict_period_from_grad_sq = lambda name, p, grad: fixed_periods[name]
+            for step in range(4):
+                gg = torch.Generator().manual_seed(50 + step)
+                for _, p in ps:
+                    p.grad = (torch.randn(p.shape, generator=gg) * 1e-2).to(dtype).to(_dev())
+                opt.step()
+            torch.cuda.synchronize()
+            assert all(v == 0 for v in opt.kernel_status().values())
+            kinds = sorted({pl.fast for pl in opt._plan_cache._plans.values() if pl.kind == "factored"})
+            return ps, opt, kinds
+        finally:
+            U.set_streaming(True)
+
+    for shp in (shapes, shapes[3:4]):
+        pa, oa, ka = run(True, shp)
+        pb, ob, kb = run(False, shp)
+        periods = {n: int(oa.state[a]["automatic_period"]) for n, a in pa}
+        assert ka == [3] and kb == [1], (ka, kb, periods)
+        for (n, a), (_, b) in zip(pa, pb):
+            # the statistics are summed with atomics in both kernels: a parameter may round the other way
+            torch.testing.assert_close(a.float(), b.float(), rtol=0, atol=1e-3, msg=n)
+            assert (a != b).float().mean().item() < 1e-3, n
+            sa, sb = oa.state[a], ob.state[b]
+            assert torch.equal(sa["m_codebook"], sb["m_codebook"]), n
+            assert torch.equal(sa["m_magnitude"], sb["m_magnitude"]), n
+            for key in ("v_row", "v_col", "vmean"):
+                if key in sa:
+                    torch.testing.assert_close(sa[key], sb[key], rtol=2e-5, atol=1e-12, msg=n + key)
