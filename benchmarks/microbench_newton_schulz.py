@@ -3,7 +3,8 @@
 
 Times five quintic iterations on Llama-3-8B matrix shapes with CUDA events after warm-up, over
 rotating inputs: the bf16 iterations on the own tcgen05 GEMM, the same iterations through the
-library (``torch.matmul``), and the e4m3 iterations (``fp8_ns``).  FLOPs per iteration for an
+library (``torch.matmul``), and the e4m3 iterations (``fp8_ns``) on the own kind::f8f6f4 GEMM and on
+the library's row-scaled fp8 GEMM.  FLOPs per iteration for an
 oriented ``[m, n]`` (m <= n): ``2 m^2 n`` (Gram) + ``2 m^3`` (Gram squared) + ``2 m^2 n`` (update).
 
     python benchmarks/microbench_newton_schulz.py [--iters 5] [--shapes 4096x4096,4096x14336]
@@ -62,7 +63,11 @@ def main():
         timed("bf16, own tcgen05 GEMM", lambda x: NS._iterate(x, sched))
         timed("bf16, library matmul", library)
         if NS.fp8_applies((m, n), True) and NS.fp8_supported(dev):
+            NS.set_fp8_gemm("tcgen05")
+            timed("e4m3, own tcgen05 kind::f8f6f4 GEMM", lambda x: NS._iterate_fp8(x, sched))
+            NS.set_fp8_gemm("library")
             timed("e4m3, library row-scaled GEMM", lambda x: NS._iterate_fp8(x, sched))
+            NS.set_fp8_gemm("tcgen05")
             if args.breakdown:
                 from gefen_x_b200.ops.quant import quantize_cols_e4m3_t as quant_t, quantize_rows_e4m3 as quant
 
@@ -76,9 +81,12 @@ def main():
                 timed("piece: quantise a X + U X, write X", lambda x: quant(x, x2, 3.4, 1.0, want_y=True))
                 timed("piece: quantise X by columns, transposed", lambda x: quant_t(x))
                 timed("piece: quantise b G + c G G", lambda x: quant(g, g, -4.7, 2.0))
-                timed("piece: fp8 GEMM X X^T", lambda x: NS._mm_fp8(xq, sx, xq, sx))
-                timed("piece: fp8 GEMM G G", lambda x: NS._mm_fp8(gq, sg, gq, sg))
-                timed("piece: fp8 GEMM U X", lambda x: NS._mm_fp8(gq, sg, xtq, sxt))
+                for backend in ("tcgen05", "library"):
+                    NS.set_fp8_gemm(backend)
+                    timed("piece: fp8 GEMM X X^T ({})".format(backend), lambda x: NS._mm_fp8(xq, sx, xq, sx))
+                    timed("piece: fp8 GEMM G G ({})".format(backend), lambda x: NS._mm_fp8(gq, sg, gq, sg))
+                    timed("piece: fp8 GEMM U X ({})".format(backend), lambda x: NS._mm_fp8(gq, sg, xtq, sxt))
+                NS.set_fp8_gemm("tcgen05")
 
 
 if __name__ == "__main__":

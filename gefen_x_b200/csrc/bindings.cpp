@@ -305,6 +305,26 @@ void gemm_bf16(const Tensor& a, const Tensor& b, Tensor c, const c10::optional<T
 // (or [K, N] when b_t).  epi 0: c0 [M, N] = alpha a b + beta d.  epi 1 (SwiGLU forward): b is the
 // stacked [gate | up] weight (2F rows), c0 = the [M, 2F] gate|up buffer, c1 = act [M, F].
 // epi 2 (SwiGLU derivative): a b = d(act) [M, F]; aux = gate|up [M, 2F]; c0 = d(gate|up) [M, 2F].
+// workspace of the pair kernel's K-split tail wave and its schedule counter: one per (device, stream),
+// since launches that share it must be ordered; counters start at zero and every launch leaves them zeroed
+static void pair_workspace(const Tensor& like, gx::PairParams& p, bool dynamic) {
+    static std::mutex mu;
+    static std::map<std::pair<int, cudaStream_t>, std::pair<Tensor, Tensor>> pool;
+    std::lock_guard<std::mutex> lock(mu);
+    auto key = std::make_pair((int)like.get_device(), stream());
+    auto it = pool.find(key);
+    if (it == pool.end()) {
+        auto ws = at::empty({gx::kPairWsFloats}, like.options().dtype(at::kFloat));
+        auto cnt = at::zeros({gx::kPairCounters}, like.options().dtype(at::kInt));
+        it = pool.emplace(key, std::make_pair(ws, cnt)).first;
+    }
+    p.ws = it->second.first.data_ptr<float>();
+    p.ws_floats = gx::kPairWsFloats;
+    p.counters = reinterpret_cast<uint32_t*>(it->second.second.data_ptr<int>());
+    p.n_counters = gx::kPairCounters - 8;
+    p.sched = dynamic ? p.counters + (gx::kPairCounters - 8) : nullptr;
+}
+
 void gemm_pair_bf16(const Tensor& a, const Tensor& b, Tensor c0, const c10::optional<Tensor>& c1,
                     const c10::optional<Tensor>& d, const c10::optional<Tensor>& aux, bool a_t, bool b_t,
                     double alpha, double beta, int64_t epi, int64_t bn, const c10::optional<Tensor>& status,
@@ -366,28 +386,40 @@ void gemm_pair_bf16(const Tensor& a, const Tensor& b, Tensor c0, const c10::opti
         p.ldaux = aux->stride(0);
     }
     TORCH_CHECK(gx::gemm_pair_supported(p.M, p.N, p.K), "gemm_pair_bf16: shape too small for the pair kernel");
-    // workspace of the K-split tail wave: one per (device, stream), since launches that share it must
-    // be ordered; counters start at zero and every launch leaves them zeroed
-    {
-        static std::mutex mu;
-        static std::map<std::pair<int, cudaStream_t>, std::pair<Tensor, Tensor>> pool;
-        std::lock_guard<std::mutex> lock(mu);
-        auto key = std::make_pair((int)a.get_device(), stream());
-        auto it = pool.find(key);
-        if (it == pool.end()) {
-            auto ws = at::empty({gx::kPairWsFloats}, a.options().dtype(at::kFloat));
-            auto cnt = at::zeros({gx::kPairCounters}, a.options().dtype(at::kInt));
-            it = pool.emplace(key, std::make_pair(ws, cnt)).first;
-        }
-        p.ws = it->second.first.data_ptr<float>();
-        p.ws_floats = gx::kPairWsFloats;
-        p.counters = reinterpret_cast<uint32_t*>(it->second.second.data_ptr<int>());
-        p.n_counters = gx::kPairCounters - 8;
-        p.sched = dynamic ? p.counters + (gx::kPairCounters - 8) : nullptr;
-    }
+    pair_workspace(a, p, dynamic);
     check(gx::launch_gemm_pair_bf16(bf(a), a.stride(0), bf(b), b.stride(0), p, C0, ld0, C1, ld1, C2, ld2,
                                     sm_count(), stream()),
           "gemm_pair_bf16");
+}
+
+
+// out [M, N] (bf16) = (a [M, K] @ b [N, K]^T) * sa[m] * sb[n] with e4m3 operands on the pair kernel
+void gemm_pair_e4m3(const Tensor& a, const Tensor& b, const Tensor& sa, const Tensor& sb, Tensor out,
+                    const c10::optional<Tensor>& status, bool dynamic) {
+    c10::cuda::CUDAGuard guard(a.device());
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda() && sa.is_cuda() && sb.is_cuda(),
+                "gemm_pair_e4m3: CUDA tensors required");
+    TORCH_CHECK(a.element_size() == 1 && b.element_size() == 1 && out.scalar_type() == at::kBFloat16 &&
+                    sa.scalar_type() == at::kFloat && sb.scalar_type() == at::kFloat,
+                "gemm_pair_e4m3: e4m3 operands, fp32 scales and a bf16 output required");
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 &&
+                    out.stride(1) == 1 && sa.is_contiguous() && sb.is_contiguous(),
+                "gemm_pair_e4m3: 2-D operands with unit inner stride required");
+    gx::PairParams p{};
+    p.M = (int)a.size(0);
+    p.K = (int)a.size(1);
+    p.N = (int)b.size(0);
+    TORCH_CHECK(b.size(1) == p.K && out.size(0) == p.M && out.size(1) == p.N && sa.numel() == p.M && sb.numel() == p.N,
+                "gemm_pair_e4m3: shapes do not fit");
+    TORCH_CHECK(gx::gemm_pair_supported(p.M, p.N, p.K) && p.K >= 128, "gemm_pair_e4m3: shape too small for the pair kernel");
+    p.alpha = 1.f;
+    p.row_scale = sa.data_ptr<float>();
+    p.col_scale = sb.data_ptr<float>();
+    p.status = (status.has_value() && status->defined()) ? status->data_ptr<int>() : nullptr;
+    pair_workspace(a, p, dynamic);
+    check(gx::launch_gemm_pair_e4m3(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), p,
+                                    reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), out.stride(0), sm_count(), stream()),
+          "gemm_pair_e4m3");
 }
 
 inline void to_ptrs(at::IntArrayRef v, void** out);
@@ -747,6 +779,7 @@ TORCH_LIBRARY(gefenx, m) {
           "float beta, Tensor? status) -> ()");
     m.def("gemm_pair_bf16(Tensor a, Tensor b, Tensor(a!) c0, Tensor(b!)? c1, Tensor? d, Tensor? aux, bool a_t, "
           "bool b_t, float alpha, float beta, int epi, int bn, Tensor? status, Tensor(c!)? sumsq, bool dynamic) -> ()");
+    m.def("gemm_pair_e4m3(Tensor a, Tensor b, Tensor sa, Tensor sb, Tensor(a!) out, Tensor? status, bool dynamic) -> ()");
     m.def("gemm_ag_bf16(Tensor a, Tensor(a!) bstage, Tensor(b!) c, int[] peer_bases, Tensor segs, "
           "Tensor seg_meta, Tensor tile_order, Tensor(c!) flags, Tensor(d!) count, int epoch, "
           "int count_target, int fetch_ctas, Tensor? status) -> ()");
@@ -791,6 +824,7 @@ TORCH_LIBRARY_IMPL(gefenx, CUDA, m) {
     m.impl("period_errors", &period_errors);
     m.impl("gemm_bf16", &gemm_bf16);
     m.impl("gemm_pair_bf16", &gemm_pair_bf16);
+    m.impl("gemm_pair_e4m3", &gemm_pair_e4m3);
     m.impl("gemm_ag_bf16", &gemm_ag_bf16);
     m.impl("comm_wait", &comm_wait);
     m.impl("comm_gather", &comm_gather);

@@ -286,7 +286,10 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
     tc_fence_after();
     const uint32_t tmem_base = ss->tmem_base;
 
-    const int k_blocks = (p.K + kBK - 1) / kBK;
+    // a k-block is one 128-byte row of each operand tile: 64 bf16 or 128 e4m3 elements of K
+    constexpr bool kF8 = EPI == kEpiScaledE4m3;
+    constexpr int kKElems = kF8 ? 2 * kBK : kBK;
+    const int k_blocks = (p.K + kKElems - 1) / kKElems;
     const int pair = (int)(blockIdx.x >> 1);
     const int n_pairs = (int)(gridDim.x >> 1);
 
@@ -312,7 +315,7 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
                     const uint32_t bar = mapa(smem_u32(&ss->full[stage]), 0);
                     unsigned char* a_dst = smA + stage * TL::kABytes;
                     unsigned char* b_dst = smB + stage * TL::kBBytes;
-                    const int k0 = kb * kBK;
+                    const int k0 = kb * kKElems;
                     if (!p.a_mn_major) {
                         tma_load_2d_pair(a_dst, &maps.a, bar, k0, m0);
                     } else {
@@ -335,7 +338,8 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
     } else if (warp == 1) {
         // --------------------------- MMA issuer (leader CTA) ---------------------------
         if (rank == 0 && lane == 0) {
-            const uint32_t idesc = make_idesc(256, BN, p.a_mn_major != 0, p.b_mn_major != 0);
+            const uint32_t idesc = kF8 ? make_idesc_e4m3(256, BN)
+                                       : make_idesc(256, BN, p.a_mn_major != 0, p.b_mn_major != 0);
             // descriptors differ from stage to stage and from k-step to k-step only in the start address
             // (low word, in 16-byte units): keep the constant part and add
             const uint64_t a_desc0 = p.a_mn_major ? make_desc(smem_u32(smA), kBK * 128, 1024) : make_desc(smem_u32(smA), 16, 1024);
@@ -359,9 +363,15 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
                     const uint64_t ad = a_desc0 + (uint64_t)((uint32_t)stage * (TL::kABytes >> 4));
                     const uint64_t bd = b_desc0 + (uint64_t)((uint32_t)stage * (TL::kBBytes >> 4));
 #pragma unroll
-                    for (int k = 0; k < kBK / kUK; ++k)
-                        umma_bf16<2>(d_tmem, ad + (uint64_t)(k * a_kstep), bd + (uint64_t)(k * b_kstep), idesc,
-                                     (kb > wk.kb0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < kBK / kUK; ++k) {
+                        // every instruction consumes 32 bytes of K per row: 16 bf16 or 32 e4m3
+                        if constexpr (kF8)
+                            umma_f8_pair(d_tmem, ad + (uint64_t)(k * a_kstep), bd + (uint64_t)(k * b_kstep), idesc,
+                                         (kb > wk.kb0 || k > 0) ? 1u : 0u);
+                        else
+                            umma_bf16<2>(d_tmem, ad + (uint64_t)(k * a_kstep), bd + (uint64_t)(k * b_kstep), idesc,
+                                         (kb > wk.kb0 || k > 0) ? 1u : 0u);
+                    }
                     umma_commit_pair(&ss->empty[stage], 3);        // both CTAs may refill the stage
                     if (++stage == TL::kStages) { stage = 0; phase ^= 1; }
                 }
@@ -496,7 +506,19 @@ gemm_pair_kernel(const __grid_constant__ PairMaps maps, PairParams p) {
                     uint32_t r[64], w[32];
                     load_acc64(c, r);
                     const int col = nt * BN + c;
-                    if constexpr (EPI == kEpiPlain) {
+                    if constexpr (EPI == kEpiScaledE4m3) {
+                        // dequantise: one scale per output row (A's row) and one per column (B's row);
+                        // the column scales are the same addresses for every lane (broadcast loads)
+                        const float sa = row < p.M ? __ldg(p.row_scale + row) : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int c0 = col + 2 * j;
+                            const float s0 = c0 < p.N ? __ldg(p.col_scale + c0) : 0.f;
+                            const float s1 = c0 + 1 < p.N ? __ldg(p.col_scale + c0 + 1) : 0.f;
+                            w[j] = pack2(__uint_as_float(r[2 * j]) * sa * s0, __uint_as_float(r[2 * j + 1]) * sa * s1);
+                        }
+                        emit(&maps.c0, w, col, row0);
+                    } else if constexpr (EPI == kEpiPlain) {
                         if (p.D) {
                             uint32_t d[32];
                             load_row64(p.D, p.ldd, row, col, p.M, p.N, p.d_vec_ok != 0, d);
@@ -609,6 +631,20 @@ bool map2d(CUtensorMap* map, const __nv_bfloat16* base, long long inner, long lo
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// row-major [outer, inner] matrix of 1-byte elements with leading dimension ld (bytes)
+bool map2d_u8(CUtensorMap* map, const void* base, long long inner, long long outer, long long ld,
+              int box_inner, int box_outer) {
+    EncodeTiledFn fn = pair_encode_fn();
+    if (!fn || inner <= 0 || outer <= 0) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)ld};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
 template <int BN, int EPI>
@@ -627,9 +663,10 @@ cudaError_t launch_pair(const PairMaps& maps, PairParams p, int sm_count, cudaSt
     p.total_tiles = p.m_tiles * p.n_tiles;
     // row-tile group of the visiting order: all rows when A is small enough to stay in L2 (then B
     // streams through once), otherwise 8 (near-square waves)
-    p.group_m = ((long long)p.M * p.K * 2 <= (48ll << 20) || p.m_tiles <= 8) ? p.m_tiles : 8;
+    p.group_m = ((long long)p.M * p.K * (EPI == kEpiScaledE4m3 ? 1 : 2) <= (48ll << 20) || p.m_tiles <= 8) ? p.m_tiles : 8;
     const int max_pairs = sm_count / 2 > 0 ? sm_count / 2 : 1;
-    const int k_blocks = (p.K + kBK - 1) / kBK;
+    constexpr int k_elems = (EPI == kEpiScaledE4m3) ? 2 * kBK : kBK;     // elements of K per 128-byte row
+    const int k_blocks = (p.K + k_elems - 1) / k_elems;
     int pairs = max_pairs;
     p.full_tiles = (p.total_tiles / max_pairs) * max_pairs;
     p.rem_tiles = p.total_tiles - p.full_tiles;
@@ -700,6 +737,29 @@ cudaError_t launch_gemm_pair_bf16(const __nv_bfloat16* A, long long lda, const _
                          : launch_pair<128, kEpiSwigluBwd>(maps, p, sm_count, st);
     return bn == 256 ? launch_pair<256, kEpiPlain>(maps, p, sm_count, st)
                      : launch_pair<128, kEpiPlain>(maps, p, sm_count, st);
+}
+
+// C0[M, N] (bf16) = (A[M, K] B[N, K]^T) * row_scale[m] * col_scale[n], A and B e4m3 bytes, fp32 accumulation on
+// the tensor cores (kind::f8f6f4): the row-scaled product of the fp8 Newton-Schulz iteration.
+cudaError_t launch_gemm_pair_e4m3(const void* A, long long lda, const void* B, long long ldb, PairParams p,
+                                  __nv_bfloat16* C0, long long ldc0, int sm_count, cudaStream_t st) {
+    if (p.M <= 0 || p.N <= 0 || p.K <= 0) return cudaSuccess;
+    if ((lda % 16) || (ldb % 16) || (ldc0 % 8) || !aligned16(A) || !aligned16(B) || !aligned16(C0) ||
+        !p.row_scale || !p.col_scale)
+        return cudaErrorInvalidValue;
+    p.epi = kEpiScaledE4m3;
+    p.a_mn_major = p.b_mn_major = 0;
+    p.D = nullptr;
+    p.sumsq = nullptr;
+    p.d_vec_ok = 1;
+    PairMaps maps;
+    bool ok = map2d_u8(&maps.a, A, p.K, p.M, lda, 2 * kBK, kBM);
+    ok = ok && map2d_u8(&maps.b, B, p.K, p.N, ldb, 2 * kBK, 128);
+    ok = ok && map2d(&maps.c0, C0, p.N, p.M, ldc0, 64, 32);
+    if (!ok) return cudaErrorInvalidValue;
+    maps.c1 = maps.c0;
+    maps.c2 = maps.c0;
+    return launch_pair<256, kEpiScaledE4m3>(maps, p, sm_count, st);
 }
 
 }  // namespace gx

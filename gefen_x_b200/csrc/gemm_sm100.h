@@ -55,6 +55,7 @@ enum PairEpilogue : int {
     kEpiPlain = 0,        // C0 = alpha * A B + beta * D
     kEpiSwigluFwd = 1,    // B = [gate rows | up rows] (2F x K): C0 = gate, C1 = up, C2 = silu(gate) * up
     kEpiSwigluBwd = 2,    // A B = d(act); aux = [gate | up]: C0 = d(gate), C1 = d(up)
+    kEpiScaledE4m3 = 3,   // e4m3 operands [rows, K] with one fp32 scale per row: C0 = (A B^T) * sa[row] * sb[col]
 };
 
 struct PairParams {
@@ -67,6 +68,8 @@ struct PairParams {
     int F;                          // SwiGLU epilogues: width of gate (= N)
     const __nv_bfloat16* aux;       // kEpiSwigluBwd: [M, 2F] gate | up
     long long ldaux;
+    const float* row_scale;         // kEpiScaledE4m3: [M] scales of A's rows
+    const float* col_scale;         // kEpiScaledE4m3: [N] scales of B's rows (the output's columns)
     int bn;                         // 0: choose; 128 / 256: force the tile width
     int* status;                    // device status word, may be null
     // plain epilogue, optional: sum of squares of the stored output accumulated into kSumsqSlots fp32
@@ -104,6 +107,11 @@ cudaError_t launch_gemm_pair_bf16(const __nv_bfloat16* A, long long lda, const _
                                   PairParams p, __nv_bfloat16* C0, long long ldc0, __nv_bfloat16* C1,
                                   long long ldc1, __nv_bfloat16* C2, long long ldc2, int sm_count,
                                   cudaStream_t st);
+// Row-scaled e4m3 product on the same kernel: C0 = (A B^T) * row_scale[m] * col_scale[n]; A [M, K] and
+// B [N, K] hold e4m3 bytes (leading dimensions in bytes, multiples of 16), p carries M, N, K, the two
+// scale vectors and the optional K-split / schedule workspaces.
+cudaError_t launch_gemm_pair_e4m3(const void* A, long long lda, const void* B, long long ldb, PairParams p,
+                                  __nv_bfloat16* C0, long long ldc0, int sm_count, cudaStream_t st);
 
 // Causal attention forward (flash form) on heads-first operands: q [batch, rows, hd] with
 // rows = group * seq (the query heads of one KV head stacked along the rows), k / v

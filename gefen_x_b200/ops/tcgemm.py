@@ -108,6 +108,28 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
     return gemm(a, b, out=out)
 
 
+def e4m3_eligible(m: int, n: int, k: int) -> bool:
+    """Shapes the e4m3 variant of the CTA-pair kernel takes: 16-byte rows for the tensor maps."""
+    return _PAIR and m >= 129 and n >= 128 and k >= 128 and k % 16 == 0 and n % 8 == 0
+
+
+def gemm_e4m3(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.Tensor,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[m, n] = sum_k aq[m, k] * bq[n, k] * sa[m] * sb[n]`` in bf16: the row-scaled e4m3 product on
+    the tensor cores (``tcgen05.mma`` of kind f8f6f4 in the CTA-pair kernel, fp32 accumulation, the two
+    scale vectors applied in the epilogue).  ``aq`` [M, K] and ``bq`` [N, K] are ``float8_e4m3fn`` with
+    unit inner stride and rows that start on 16-byte boundaries; ``sa`` / ``sb`` hold M / N fp32 scales."""
+    m, k = aq.shape
+    n = bq.shape[0]
+    if not (aq.is_cuda and e4m3_eligible(m, n, k)):
+        raise ValueError("gemm_e4m3: shape {}x{}x{} is not eligible for the pair kernel".format(m, n, k))
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=aq.device)
+    ops().gemm_pair_e4m3(aq, bq, sa.reshape(-1).contiguous(), sb.reshape(-1).contiguous(), out,
+                         status_word(aq.device), _DYNAMIC)
+    return out
+
+
 def swiglu_eligible(m: int, f: int, k: int) -> bool:
     return _PAIR and m >= 129 and f >= 128 and f % 8 == 0 and k >= 64
 

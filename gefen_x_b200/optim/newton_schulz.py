@@ -118,6 +118,17 @@ FP8_MIN_SCALE = 1e-12
 FP8_MIN_DIM = 1536                   # below this the fp8 products lose to bf16 (reference gefen_muon.py:83-89)
 
 
+_FP8_GEMM = "tcgen05"
+
+
+def set_fp8_gemm(backend: str) -> None:
+    """``"tcgen05"`` (own kernel, default) or ``"library"`` for the products of the fp8 iteration."""
+    global _FP8_GEMM
+    if backend not in ("tcgen05", "library"):
+        raise ValueError("fp8 GEMM backend must be 'tcgen05' or 'library'")
+    _FP8_GEMM = backend
+
+
 def fp8_supported(device=None) -> bool:
     """fp8 tensor-core GEMMs need compute capability 8.9 or later; the CPU statement always runs."""
     if device is not None and torch.device(device).type != "cuda":
@@ -143,9 +154,16 @@ def quantize_rowwise_fp8(x: torch.Tensor):
 def _mm_fp8(aq, sa, bq_rows, sb_rows) -> torch.Tensor:
     """``(aq * sa) @ (bq_rows * sb_rows)^T`` in bf16.  ``bq_rows`` holds the second operand's
     COLUMNS as rows (so its transpose view is the column-major operand the fp8 GEMM reads and
-    ``sb_rows`` its per-column scales).  CUDA: ``torch._scaled_mm`` with row-wise scales; CPU:
-    the same quantised values multiplied in fp32."""
+    ``sb_rows`` its per-column scales).  CUDA: the e4m3 variant of the own CTA-pair kernel (default;
+    ``set_fp8_gemm("library")`` selects ``torch._scaled_mm`` with row-wise scales, which also takes the
+    shapes the pair kernel does not); CPU: the same quantised values multiplied in fp32."""
     if aq.is_cuda:
+        if _FP8_GEMM == "tcgen05":
+            from ..ops import tcgemm
+
+            if tcgemm.e4m3_eligible(aq.shape[0], bq_rows.shape[0], aq.shape[1]) and aq.stride(1) == 1 \
+                    and bq_rows.stride(1) == 1 and aq.stride(0) % 16 == 0 and bq_rows.stride(0) % 16 == 0:
+                return tcgemm.gemm_e4m3(aq, sa, bq_rows, sb_rows)
         return torch._scaled_mm(aq, bq_rows.t(), scale_a=sa, scale_b=sb_rows.t(), out_dtype=torch.bfloat16)
     return ((aq.float() * sa) @ (bq_rows.float() * sb_rows).t()).bfloat16()
 

@@ -625,3 +625,50 @@ def test_pair_gemm_dynamic_schedule_matches_static():
     finally:
         tcgemm.set_dynamic_schedule(False)
 
+
+
+def test_pair_gemm_e4m3_row_scaled_matches_fp32_statement():
+    """The e4m3 variant of the CTA-pair kernel (tcgen05 kind f8f6f4, scales in the epilogue) against the
+    fp32 statement of the same quantised values: full and partial tiles, a K that does not fill its last
+    128-byte row, a K-split tail wave, and both tile schedules."""
+    from gefen_x_b200.ops import tcgemm
+
+    g = torch.Generator().manual_seed(31)
+    dev = _dev()
+    try:
+        for dynamic in (False, True):
+            tcgemm.set_dynamic_schedule(dynamic)
+            for m, n, k in [(4096, 4096, 1024), (300, 264, 208), (4352, 4352, 512), (2048, 1024, 4096), (129, 128, 128)]:
+                a = torch.randn(m, k, generator=g)
+                b = torch.randn(n, k, generator=g)
+                sa = (a.abs().amax(1, keepdim=True) / 448.0).clamp_(min=1e-12)
+                sb = (b.abs().amax(1, keepdim=True) / 448.0).clamp_(min=1e-12)
+                aq = (a / sa).to(torch.float8_e4m3fn).to(dev)
+                bq = (b / sb).to(torch.float8_e4m3fn).to(dev)
+                want = ((aq.float() * sa.to(dev)) @ (bq.float() * sb.to(dev)).t())
+                got = tcgemm.gemm_e4m3(aq, sa.to(dev), bq, sb.to(dev))
+                assert got.dtype == torch.bfloat16 and got.shape == (m, n)
+                err = (got.float() - want).abs().max().item()
+                assert err <= 1e-2 * want.abs().max().item() + 1e-3, (m, n, k, dynamic, err)
+        torch.cuda.synchronize()
+        assert int(tcgemm.status_word(dev).item()) == 0
+    finally:
+        tcgemm.set_dynamic_schedule(False)
+
+
+def test_fp8_newton_schulz_own_gemm_tracks_the_library_gemm():
+    from gefen_x_b200.optim import newton_schulz as NS
+
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(1024, 2048, generator=g).bfloat16().to(_dev())
+    try:
+        NS.set_fp8_gemm("tcgen05")
+        own = NS.zeropower_via_newtonschulz(x, ns_steps=5, use_fp8=True)
+        NS.set_fp8_gemm("library")
+        lib = NS.zeropower_via_newtonschulz(x, ns_steps=5, use_fp8=True)
+    finally:
+        NS.set_fp8_gemm("tcgen05")
+    bf = NS.zeropower_via_newtonschulz(x, ns_steps=5, use_fp8=False)
+    # same quantised operands, fp32 accumulation in both: the results agree far inside the fp8 error
+    assert (own.float() - lib.float()).abs().max().item() <= 2e-2
+    assert (own.float() - bf.float()).abs().mean().item() <= 2e-2
