@@ -366,7 +366,11 @@ class Gefen(torch.optim.Optimizer):
         self._histogram_reducer = None
         self._external_grad_scale: Optional[torch.Tensor] = None
         self._exchange_epoch = 0
+        # called as hook(heavy) before the kernels of a step that went through the full host path;
+        # heavy: this step searched periods or learned / refreshed the codebook (seconds of host work,
+        # at the same step on every rank), as opposed to merely rebuilding a launch plan
         self._pre_launch_hook = None
+        self._heavy_prep = False
         self._fast = None
         self._fused_meta: Dict[Any, list] = {}
         self._slow_params = 0
@@ -597,6 +601,7 @@ class Gefen(torch.optim.Optimizer):
         return self._predict_period_from_grad_sq(name, p, grad)
 
     def _predict_period_from_grad_sq(self, name: str, p: torch.Tensor, grad: torch.Tensor) -> int:
+        self._heavy_prep = True
         g = _local(grad).detach()
         backend = FIND_PERIOD_BACKEND
         if backend is None:
@@ -658,6 +663,7 @@ class Gefen(torch.optim.Optimizer):
 
     def _learn_gefen_exact_codebook(self, reuse_existing_periods: bool = False,
                                     compute_mse_logging: bool = True) -> Optional[torch.Tensor]:
+        self._heavy_prep = True
         return _cbk.learn_codebook_from_grad_periods(
             self._iter_gefen_grad_periods(reuse_existing_periods),
             codebook_device=self._gefen_codebook_device(),
@@ -1065,7 +1071,8 @@ class Gefen(torch.optim.Optimizer):
         if self._plan_cache is None:
             self._plan_cache = _u.PlanCache()
         if self._pre_launch_hook is not None:
-            self._pre_launch_hook()
+            heavy, self._heavy_prep = self._heavy_prep, False
+            self._pre_launch_hook(heavy)
         for (kind, dev, _dt), items in self._fused_items.items():
             cb = self._gefen_codebook_on(dev)
             if cb is None:

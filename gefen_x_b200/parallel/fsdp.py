@@ -514,6 +514,7 @@ class ShardedTrainer:
         self.opt = Gefen(named, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                          factored_v_2d=factored_v_2d, fused=fused, **opt_kwargs)
         self.opt._grad_source = self._grad_source
+        self._align_wanted = True               # first step, and the first one after a restore
         self.opt._pre_launch_hook = self._align_ranks
         self.opt._external_grad_scale = self.clip_coef[0:1] if self.clip else None
         if self.world > 1:
@@ -534,18 +535,22 @@ class ShardedTrainer:
             if global_codebook:
                 self.opt._histogram_reducer = self._host_allreduce
 
-    def _align_ranks(self) -> None:
-        """Host barrier before the kernels of a step whose preparation ran on the host.
+    def _align_ranks(self, heavy: bool = True) -> None:
+        """Host barrier before the kernels of a step whose preparation ran long on the host.
 
-        The first step (period search, codebook learning) and any step that rebuilds the
-        plans can take seconds of host time that differs between ranks; the kernels that
-        follow wait for their peers with a bounded budget, so the ranks are aligned first.
+        The first step (period search, codebook learning), a codebook refresh and the first step
+        after a restore take seconds of host time that differs between ranks; the kernels that
+        follow wait for their peers with a bounded budget, so the ranks are aligned first.  All of
+        these happen at the same step on every rank.  A step that merely rebuilds a launch plan
+        (``heavy`` false) does not meet here: such a rebuild may concern one rank only, the others
+        would never join the barrier, and it is short enough for their bounded waits.
         """
-        if self.world > 1:
+        if self.world > 1 and (heavy or self._align_wanted):
             import torch.distributed as dist
 
             torch.cuda.synchronize(self.device)
             dist.barrier(group=self.process_group)
+        self._align_wanted = False
 
     def _host_allreduce(self, t: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist
@@ -992,6 +997,7 @@ class ShardedTrainer:
     def _after_restore(self) -> None:
         """Make restored shards visible to the peers and restart the parameter-arrival protocol."""
         self._grad_cache.clear()
+        self._align_wanted = True
         self.opt._fast = None
         if self.opt._plan_cache is not None:
             self.opt._plan_cache.clear()

@@ -500,3 +500,28 @@ def test_streamed_update_kernels_match_the_register_pipelined_ones_bit_for_bit(d
             for key in ("v_row", "v_col", "vmean"):
                 if key in sa:
                     torch.testing.assert_close(sa[key], sb[key], rtol=2e-5, atol=1e-12, msg=n + key)
+
+
+def test_pre_launch_hook_tells_heavy_host_preparation_from_a_plan_rebuild():
+    """The sharded runtime aligns its ranks with a host barrier only before steps that all ranks
+    prepare at length (period search, codebook learning); a step that merely rebuilds a launch plan,
+    which can happen on one rank alone, reports ``heavy=False`` so that nobody waits in a barrier the
+    others never enter."""
+    from gefen_x_b200 import Gefen
+
+    ps = _params()
+    opt = Gefen(ps, lr=1e-2)
+    calls = []
+    opt._pre_launch_hook = lambda heavy: calls.append(bool(heavy))
+    for _, p in ps:
+        p.grad = torch.zeros_like(p)
+    for step in range(6):
+        for (_, p), g in zip(ps, _grads(ps, step)):
+            p.grad.copy_(g)
+        if step == 4:
+            for _, p in ps:
+                p.data = p.data.clone()            # invalidates the remembered plan: full path, light
+        opt.step()
+    assert calls[0] is True                        # first step: periods and codebook
+    assert calls[1:] and not any(calls[1:])        # later full-path steps only rebuild plans
+    assert len(calls) < 6                          # the steady state in between took the fast path
