@@ -126,15 +126,24 @@ def main():
         report("all-gather fused into the QKV GEMM (gemm_ag_bf16, {} fetch CTAs)".format(n_fetch),
                timed(lambda: f2(h1)), flops, remote)
 
-    # reduce-scatter of the layer's gradients by peer loads
-    segs, n_segs, prefix, total, _copies = tr._build_reduce_table(grp, "all")
-    own = total * 16
+    # reduce-scatter of the layer's gradients: peer loads, and in-switch reduction (multimem.ld_reduce on
+    # the multicast mapping of the gradient buffers) where the arena has one.  Either way every GPU sends
+    # (world - 1) slices of the size of a shard, which is the link roofline; the in-switch variant
+    # receives one reduced shard instead of (world - 1) slices.
     partials = torch.zeros(2048, dtype=torch.float32, device=dev)
-    for ctas in (148, 592):
-        ms = timed(lambda: ops().comm_reduce_segments(world, segs, n_segs, prefix, total, 1.0 / world, partials,
-                                                      ctas, U.DTYPE_CODE[torch.bfloat16]))
-        report("reduce-scatter by peer loads (reduce_segments_kernel, {} CTAs)".format(ctas), ms, 0.0,
-               own * (world - 1), "shard of {:.0f} MB summed from {} ranks".format(own / 1e6, world))
+    was_nvls = tr.nvls
+    for use_mc in ((False, True) if getattr(tr.arena, "mc_base", 0) else (False,)):
+        tr.nvls = use_mc
+        segs, n_segs, prefix, total, _copies = tr._build_reduce_table(grp, "all")
+        own = total * 16
+        for ctas in (148, 592):
+            ms = timed(lambda: ops().comm_reduce_segments(world, segs, n_segs, prefix, total, 1.0 / world, partials,
+                                                          ctas, U.DTYPE_CODE[torch.bfloat16], use_mc))
+            name = "reduce-scatter by multimem.ld_reduce (reduce_segments_mc_kernel, {} CTAs)" if use_mc else \
+                "reduce-scatter by peer loads (reduce_segments_kernel, {} CTAs)"
+            report(name.format(ctas), ms, 0.0, own * (world - 1),
+                   "shard of {:.0f} MB summed from {} ranks".format(own / 1e6, world))
+    tr.nvls = was_nvls
 
     # parameter all-gather of the layer
     layer_bytes = grp.full_numel * 2

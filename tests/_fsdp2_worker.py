@@ -19,6 +19,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
 DIMS = [(256, 512), (512, 37 * 8), (37 * 8, 256), (256, 64)]
+GLOBAL_BATCH = 16
 
 
 def build(dev):
@@ -33,11 +34,13 @@ def build(dev):
 
 
 def batch(step, world, rank, dev):
+    # the same global batch of 16 rows whatever the world size: a rank takes its slice of it
     g = torch.Generator().manual_seed(900 + step)
-    x = torch.randn(8 * max(world, 1), 256, generator=g)
-    y = torch.randn(8 * max(world, 1), 64, generator=g)
+    x = torch.randn(GLOBAL_BATCH, 256, generator=g)
+    y = torch.randn(GLOBAL_BATCH, 64, generator=g)
     if world > 1:
-        x, y = x[rank * 8:(rank + 1) * 8], y[rank * 8:(rank + 1) * 8]
+        per = GLOBAL_BATCH // world
+        x, y = x[rank * per:(rank + 1) * per], y[rank * per:(rank + 1) * per]
     return x.to(dev).bfloat16(), y.to(dev).bfloat16()
 
 
