@@ -56,7 +56,8 @@ def parse_args():
     ap.add_argument("--attn", default="sdpa", choices=["sdpa", "tcgen05"],
                     help="attention: fused library kernel, or tcgen05 GEMMs + own row kernels")
     ap.add_argument("--nvls", default="auto", choices=["auto", "on", "off"],
-                    help="gradient reduce-scatter through NVSwitch (multimem.ld_reduce) where available")
+                    help="gradient reduce-scatter through NVSwitch (multimem.ld_reduce); auto: off unless GEFENX_NVLS=1 "
+                         "(measured slower on 2 GPUs, level on 8)")
     ap.add_argument("--gemm-schedule", default="auto", choices=["auto", "static", "dynamic"],
                     help="tile schedule of the pair GEMM: fixed assignment, or tiles drawn from a device counter "
                          "(auto: dynamic with several ranks)")

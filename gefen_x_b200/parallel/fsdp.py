@@ -201,14 +201,15 @@ class ShardedTrainer:
             arena_bytes += muon_region_bytes + 4096
         self.arena = SymmetricArena(arena_bytes, self.device, world, rank, group)
         # Gradient reduce-scatter through NVSwitch (multimem.ld_reduce on the arena's multicast mapping):
-        # a rank then receives its shard's bytes once instead of once per peer.  On by default where
-        # the fabric offers a multicast mapping; off with nvls=False, GEFENX_NVLS=0 or NCCL_NVLS_ENABLE=0
-        # (multi-rank failure tests must run without it: a rank that dies while its memory is bound to
-        # a multicast object disturbs the other ranks' GPUs).
+        # a rank then receives its shard's bytes once instead of once per peer.  An option (nvls=True, or
+        # GEFENX_NVLS=1 with nvls=None): measured slower than the staged peer copies on 2 GPUs and level
+        # with them on 8.  NCCL_NVLS_ENABLE=0 also keeps it off (multi-rank failure tests must run without
+        # it: a rank that dies while its memory is bound to a multicast object disturbs the other
+        # ranks' GPUs).
         import os
 
-        env_off = os.environ.get("GEFENX_NVLS", "1") == "0" or os.environ.get("NCCL_NVLS_ENABLE", "1") == "0"
-        want = (not env_off) if nvls is None else bool(nvls)
+        env_on = os.environ.get("GEFENX_NVLS", "0") == "1" and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0"
+        want = env_on if nvls is None else bool(nvls)
         self.nvls = bool(want and self.arena.mc_base and dtype == torch.bfloat16 and world > 1)
         if nvls and not self.nvls and world > 1:
             raise RuntimeError("nvls=True, but the symmetric arena has no multicast mapping on this system "
