@@ -52,6 +52,8 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--shapes", default="")
+    ap.add_argument("--wide", action="store_true",
+                    help="ours: streamed kernels with 16 instead of 8 elements per thread")
     ap.add_argument("--no-streaming", action="store_true",
                     help="ours: the register-pipelined fast kernels instead of the streamed ones")
     args = ap.parse_args()
@@ -66,6 +68,7 @@ def main():
         from gefen_x_b200.ops import update as _update
 
         _update.set_streaming(not args.no_streaming)
+        _update.set_wide_chunks(args.wide)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)   # 2x the 126 MB L2
     # A few milliseconds of device work queued ahead of every timed step, so that the host
     # has enqueued the whole step before the device reaches the first event (the events

@@ -117,6 +117,9 @@ void factored_update(const Tensor& descs, const Tensor& tile_start, int64_t n_te
                          sr_seed, stochastic, wait_iters, sr_seed_dev);
     c.epoch = (uint32_t)epoch;
     c.fast = (int)fast;
+    // the 16-wide streamed kernels read their own tile prefix behind the 8-wide one
+    TORCH_CHECK(fast != 4 || tile_start.numel() >= 2 * (n_tensors + 1),
+                "factored_update: the 16-wide kernels need both tile prefixes in tile_start");
     const int sms = sm_count();
     auto st = stream();
     if (phases & 1) check(gx::launch_factored_stats(c, (int)dtype, sms, st), "factored_stats");

@@ -1041,38 +1041,57 @@ __global__ void __launch_bounds__(kThreads, FAST ? kFastCtas : 2) factored_apply
 // ---------------------------------------------------------------------------
 // streamed kernels (fast plans of 2-byte tensors with 16-element row alignment)
 // ---------------------------------------------------------------------------
-// A CTA holds kGroups consumer groups of kThreads threads and one producer warp per group.  A
-// group behaves like one CTA of the fast kernels above (same tile ranges, same thread-to-chunk
-// mapping, same arithmetic and summation order), but its chunks arrive through a ring of
-// shared-memory stages.  One stage is one row step of the group: trows rows of tcols * 8
-// elements, stored so that the chunk of group thread t lies at element t * 8.  The producer warp
-// walks the same tile range and copies one row per lane with cp.async.bulk; the copies complete
-// the stage's "full" mbarrier by byte count, the eight consumer warps release the stage through
-// its "empty" mbarrier as soon as their chunks are in registers.  Every wait is bounded: a wait
-// that runs out raises the CTA's abort flag and the status word, after which no thread waits or
-// computes again but all still walk their ranges, so that the group barriers stay matched.
-constexpr int kGroups = 3;
-constexpr int kStreamThreads = kGroups * (kThreads + 32);
-constexpr int kStatsStages = 8;
-constexpr int kApplyStages = 5;
-constexpr int kChunkBytes2 = kThreads * 8 * 2;            // one row step of 2-byte elements
-constexpr int kStatsStageBytes = kChunkBytes2 + kThreads * 8;          // g, idx
-constexpr int kApplyStageBytes = 2 * kChunkBytes2 + kThreads * 8;      // g, p, idx
+// A CTA holds G consumer groups of kThreads threads and one producer warp per group.  A group
+// behaves like one CTA of the fast kernels above (contiguous tile range, a thread owns a column
+// chunk and walks its rows), but its chunks arrive through a ring of shared-memory stages.  One
+// stage is one row step of the group: trows rows of tcols * W elements, stored so that the chunk of
+// group thread t lies at element t * W.  The producer warp walks the same tile range and copies one
+// row per lane with cp.async.bulk; the copies complete the stage's "full" mbarrier by byte count,
+// the eight consumer warps release the stage through its "empty" mbarrier.  Every wait is bounded:
+// a wait that runs out raises the CTA's abort flag and the status word, after which no thread waits
+// or computes again but all still walk their ranges, so that the group barriers stay matched.
+//
+// Two widths.  W = 8: three groups per CTA, the tile geometry, thread-to-chunk mapping, arithmetic
+// and summation order of the register-pipelined kernels (bit-identical results).  W = 16 (plans whose
+// block periods are multiples of 16, so that a 16-element chunk lies in one block): two groups per
+// CTA at up to 112 registers, a thread owns 16 contiguous elements of a row, which halves what a row
+// step costs besides its elements (stage wait / release, block bookkeeping, magnitude and row-factor
+// fetches, the row-sum shuffle tree, the per-row agreement on the block).  Its tile geometry is
+// derived on the device from the 8-wide one (same rule as the host's) and its tile prefix follows
+// the 8-wide prefix in the plan's tile table.
+template <int W> struct StreamCfg {
+    static constexpr int kW = W;
+    static constexpr int kG = (W == 8) ? 3 : 2;                       // consumer groups per CTA
+    static constexpr int kCtaThreads = kG * (kThreads + 32);
+    static constexpr int kStatsStages = (W == 8) ? 8 : 5;
+    static constexpr int kApplyStages = (W == 8) ? 5 : 3;
+    static constexpr int kValBytes = kThreads * W * 2;                // g (or p) of one row step
+    static constexpr int kIdxBytes = kThreads * W;
+    static constexpr int kStatsStageBytes = kValBytes + kIdxBytes;
+    static constexpr int kApplyStageBytes = 2 * kValBytes + kIdxBytes;
+};
+constexpr int kMaxGroups = 3;
 // tables of the streamed kernels: the lane-replicated codebook with one more row of +inf (the
 // "next codeword" of the last one), then the thresholds and the bucket table
 constexpr int kRepFloatsS = (kCodewords + 1) * 32;
 constexpr size_t kTabStats = ((size_t)(16 + kRepFloatsS) * sizeof(float) + 127) / 128 * 128;
 constexpr size_t kTabFull = (kTabStats + kCodewords * sizeof(float) + kLutBuckets * sizeof(uint16_t) + 127) / 128 * 128;
-constexpr size_t kSmemStatsStream = kTabStats + (size_t)kGroups * kStatsStages * kStatsStageBytes;
-constexpr size_t kSmemApplyStream = kTabFull + (size_t)kGroups * kApplyStages * kApplyStageBytes;
-static_assert(kSmemApplyStream <= 232448 && kSmemStatsStream <= 232448, "shared memory of the streamed kernels");
+template <int W> constexpr size_t smem_stats_stream() {
+    return kTabStats + (size_t)StreamCfg<W>::kG * StreamCfg<W>::kStatsStages * StreamCfg<W>::kStatsStageBytes;
+}
+template <int W> constexpr size_t smem_apply_stream() {
+    return kTabFull + (size_t)StreamCfg<W>::kG * StreamCfg<W>::kApplyStages * StreamCfg<W>::kApplyStageBytes;
+}
+static_assert(smem_apply_stream<8>() <= 232448 && smem_stats_stream<8>() <= 232448 &&
+              smem_apply_stream<16>() <= 232448 && smem_stats_stream<16>() <= 232448,
+              "shared memory of the streamed kernels");
 
 struct StreamShared {
-    uint64_t full[kGroups][8];
-    uint64_t empty[kGroups][8];
-    long long blk[kGroups][kThreads / 32];
-    float val[kGroups][kThreads / 32];
-    float sum[kGroups][kThreads / 32];
+    uint64_t full[kMaxGroups][8];
+    uint64_t empty[kMaxGroups][8];
+    long long blk[kMaxGroups][kThreads / 32];
+    float val[kMaxGroups][kThreads / 32];
+    float sum[kMaxGroups][kThreads / 32];
     int abort_flag;
 };
 
@@ -1131,20 +1150,62 @@ __device__ __forceinline__ void bulk_load_row(void* smem_dst, const void* gsrc, 
                  : "memory");
 }
 
+// Tile geometry of the 16-wide kernels, derived from the 8-wide fields of the descriptor with the rule
+// the host uses for its tile prefix (ops/update.py: _pick_tcols): the thread columns that waste the
+// fewest chunks of the last column tile, the same rows-per-thread factor as the 8-wide tiles.
+__device__ __forceinline__ void widen_geometry(Hot& h) {
+    const int tile_k = h.rows_per_tile / h.trows;
+    const int chunks = h.cols / 16;
+    int best = 256, waste = (chunks + 255) / 256 * 256 - chunks;
+#pragma unroll
+    for (int t = 128; t >= 32; t >>= 1) {
+        const int w = (chunks + t - 1) / t * t - chunks;
+        if (w < waste) { best = t; waste = w; }
+    }
+    h.tcols = best;
+    h.trows = kThreads / best;
+    h.n_col_tiles = (chunks + best - 1) / best;
+    h.rows_per_tile = h.trows * tile_k;
+    const unsigned long long step = (unsigned long long)h.trows * (unsigned)h.cols;
+    h.step_blk = (unsigned)(step / (unsigned)h.period);
+    h.step_rem = (unsigned)(step % (unsigned)h.period);
+}
+template <int W>
+__device__ __forceinline__ Hot load_hot_w(const TensorDesc* t) {
+    Hot h = load_hot(t);
+    if constexpr (W == 16) widen_geometry(h);
+    return h;
+}
+template <int W>
+__device__ __forceinline__ const int* tile_prefix(const LaunchCommon& c) {
+    return (W == 16) ? c.tile_start + (c.n_tensors + 1) : c.tile_start;
+}
+template <int W>
+__device__ __forceinline__ void walk_begin_w(const LaunchCommon& c, long long tile, TileWalk& w, Hot& d) {
+    const int* start = tile_prefix<W>(c);
+    w.ti = find_tensor(start, c.n_tensors, (int)tile);
+    d = load_hot_w<W>(c.descs + w.ti);
+    const int local = (int)tile - start[w.ti];
+    w.n_row_tiles = (d.rows + d.rows_per_tile - 1) / d.rows_per_tile;
+    w.ct = local / w.n_row_tiles;
+    w.rt = local - w.ct * w.n_row_tiles;
+}
+
 // The producer warp of a group: walks tiles [T0, T1) exactly as the consumers do and fills one
 // stage per row step.  APPLY also brings the parameter rows.
-template <typename T, int D, int STAGE_BYTES, bool APPLY>
-__device__ void stream_producer(const LaunchCommon& c, long long T0, long long T1, Ring<D, STAGE_BYTES> ring) {
+template <typename T, int W, int D, int STAGE_BYTES, bool APPLY>
+__device__ void stream_producer(const LaunchCommon& c, long long T0, long long T1, Ring<D, STAGE_BYTES>& ring) {
     static_assert(sizeof(T) == 2, "the streamed kernels take 2-byte tensors");
+    using Cfg = StreamCfg<W>;
     const int lane = threadIdx.x & 31;
     Hot d;
     TileWalk w;
-    walk_begin(c, T0, w, d);
+    walk_begin_w<W>(c, T0, w, d);
     for (long long tile = T0; tile < T1;) {
         const int n = (int)min(T1 - tile, (long long)(w.n_row_tiles - w.rt));
         const TileCursor t = walk_cursor(w, d, n);
-        const int col0 = t.ct * d.tcols * 8;
-        const int width = min(d.tcols * 8, d.cols - col0);          // elements of a row inside this column tile
+        const int col0 = t.ct * d.tcols * W;
+        const int width = min(d.tcols * W, d.cols - col0);          // elements of a row inside this column tile
         const char* g0 = reinterpret_cast<const char*>(d.g0);
         const char* p0 = reinterpret_cast<const char*>(d.p);
         const char* i0 = reinterpret_cast<const char*>(d.idx);
@@ -1160,12 +1221,12 @@ __device__ void stream_producer(const LaunchCommon& c, long long T0, long long T
                 const size_t off = (size_t)(rb + lane) * (size_t)d.cols + (size_t)col0;
                 unsigned char* st = ring.stage();
                 uint64_t* bar = ring.full + ring.slot;
-                bulk_load_row(st + lane * d.tcols * 16, g0 + off * 2, (uint32_t)width * 2u, bar);
+                bulk_load_row(st + lane * d.tcols * (W * 2), g0 + off * 2, (uint32_t)width * 2u, bar);
                 if constexpr (APPLY) {
-                    bulk_load_row(st + kChunkBytes2 + lane * d.tcols * 16, p0 + off * 2, (uint32_t)width * 2u, bar);
-                    bulk_load_row(st + 2 * kChunkBytes2 + lane * d.tcols * 8, i0 + off, (uint32_t)width, bar);
+                    bulk_load_row(st + Cfg::kValBytes + lane * d.tcols * (W * 2), p0 + off * 2, (uint32_t)width * 2u, bar);
+                    bulk_load_row(st + 2 * Cfg::kValBytes + lane * d.tcols * W, i0 + off, (uint32_t)width, bar);
                 } else {
-                    bulk_load_row(st + kChunkBytes2 + lane * d.tcols * 8, i0 + off, (uint32_t)width, bar);
+                    bulk_load_row(st + Cfg::kValBytes + lane * d.tcols * W, i0 + off, (uint32_t)width, bar);
                 }
             }
             ring.advance();
@@ -1178,7 +1239,7 @@ __device__ void stream_producer(const LaunchCommon& c, long long T0, long long T
                 w.ct = 0;
                 if (tile < T1) {
                     ++w.ti;
-                    d = load_hot(c.descs + w.ti);
+                    d = load_hot_w<W>(c.descs + w.ti);
                     w.n_row_tiles = (d.rows + d.rows_per_tile - 1) / d.rows_per_tile;
                 }
             }
@@ -1205,7 +1266,6 @@ __device__ __forceinline__ void stage_release(Ring<D, STAGE_BYTES>& ring, bool o
 struct StreamTables {
     uint32_t cb_lane;
     uint32_t lut2;
-    QuantTables q;      // generic pointers for the rare full search
 };
 
 __device__ __forceinline__ StreamTables load_tables_stream(const LaunchCommon& c, bool full) {
@@ -1220,7 +1280,6 @@ __device__ __forceinline__ StreamTables load_tables_stream(const LaunchCommon& c
         for (int k = 0; k < 8; ++k) row[k] = make_float4(v, v, v, v);
     }
     if (full) {
-        for (int i = threadIdx.x; i < kCodewords; i += blockDim.x) thr[i] = c.thresholds[i];
         const uint4* src = reinterpret_cast<const uint4*>(c.lut);
         uint4* dst = reinterpret_cast<uint4*>(lut);
         constexpr int kPieces = kLutBuckets * (int)sizeof(uint16_t) / 16;
@@ -1229,9 +1288,6 @@ __device__ __forceinline__ StreamTables load_tables_stream(const LaunchCommon& c
     StreamTables t;
     t.cb_lane = ptx::smem_u32(cb) + ((threadIdx.x & 31) << 2);
     t.lut2 = ptx::smem_u32(lut) - 2u * 0x4B000000u;
-    t.q.cb = cb;
-    t.q.thr = full ? thr : nullptr;
-    t.q.lut = full ? lut : nullptr;
     __syncthreads();
     return t;
 }
@@ -1257,18 +1313,26 @@ template <int K>
 __device__ __forceinline__ float cb_of_byte(const StreamTables& t, uint32_t w) {
     return lds_f32(t.cb_lane + (__byte_perm(w, 0u, 0x4440u + K) << 7));
 }
+__device__ __forceinline__ void cb_of_words(const StreamTables& s, uint32_t w0, uint32_t w1, float (&cbv)[8]) {
+    cbv[0] = cb_of_byte<0>(s, w0); cbv[1] = cb_of_byte<1>(s, w0);
+    cbv[2] = cb_of_byte<2>(s, w0); cbv[3] = cb_of_byte<3>(s, w0);
+    cbv[4] = cb_of_byte<0>(s, w1); cbv[5] = cb_of_byte<1>(s, w1);
+    cbv[6] = cb_of_byte<2>(s, w1); cbv[7] = cb_of_byte<3>(s, w1);
+}
 __device__ __forceinline__ float rcp_approx(float x) {
     float r;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
     return r;
 }
 
-template <typename T>
+template <typename T, int W, int D>
 __device__ __forceinline__ void stats_range_stream(const Hot& d, const StreamTables& s, const TileCursor& t, float gs,
-                                                   float (&csum)[8], RunMax& run,
-                                                   Ring<kStatsStages, kStatsStageBytes>& ring, int lt) {
+                                                   float (&csum)[W], RunMax& run,
+                                                   Ring<D, StreamCfg<W>::kStatsStageBytes>& ring, int lt) {
+    using Cfg = StreamCfg<W>;
+    constexpr int H = W / 8;
     const int tx = lt % d.tcols, ty = lt / d.tcols;
-    const int c0 = (t.ct * d.tcols + tx) * 8;
+    const int c0 = (t.ct * d.tcols + tx) * W;
     const bool act = c0 < d.cols;
     const int stride = d.trows;
     const int n_steps = (t.r1 - t.r0 + stride - 1) / stride;
@@ -1285,32 +1349,34 @@ __device__ __forceinline__ void stats_range_stream(const Hot& d, const StreamTab
         const float mo = mo_next;
         block_iter_next(d, it);
         mo_next = (act && r + stride < t.r1) ? d.mag[it.blk] : 0.f;
-        uint4 gw = make_uint4(0, 0, 0, 0);
-        uint2 iw = make_uint2(0, 0);
+        uint4 gw[H];
+        uint2 iw[H];
         const bool ok = stage_wait(ring);
         if (ok && act && row_ok) {
             const unsigned char* st = ring.stage();
-            gw = *reinterpret_cast<const uint4*>(st + lt * 16);
-            iw = *reinterpret_cast<const uint2*>(st + kChunkBytes2 + lt * 8);
+#pragma unroll
+            for (int h = 0; h < H; ++h) {
+                gw[h] = *reinterpret_cast<const uint4*>(st + lt * (W * 2) + h * 16);
+                iw[h] = *reinterpret_cast<const uint2*>(st + Cfg::kValBytes + lt * W + h * 8);
+            }
         }
         stage_release(ring, ok, lt);
         if (!ok || !row_ok) continue;
         float amax = 0.f, rs = 0.f;
         if (act) {
-            float g[8];
-            Vec8<T>::unpack(gw, g);
-            float cbv[8];
-            cbv[0] = cb_of_byte<0>(s, iw.x); cbv[1] = cb_of_byte<1>(s, iw.x);
-            cbv[2] = cb_of_byte<2>(s, iw.x); cbv[3] = cb_of_byte<3>(s, iw.x);
-            cbv[4] = cb_of_byte<0>(s, iw.y); cbv[5] = cb_of_byte<1>(s, iw.y);
-            cbv[6] = cb_of_byte<2>(s, iw.y); cbv[7] = cb_of_byte<3>(s, iw.y);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const float ge = __fmul_rn(g[e], gs);
-                const float m = ema_momentum(cbv[e], mo, ge, b1, omb1);
-                amax = fmaxf(amax, fabsf(m));
-                rs = __fmaf_rn(ge, ge, rs);
-                csum[e] = __fmaf_rn(ge, ge, csum[e]);
+            for (int h = 0; h < H; ++h) {
+                float g[8], cbv[8];
+                Vec8<T>::unpack(gw[h], g);
+                cb_of_words(s, iw[h].x, iw[h].y, cbv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float ge = __fmul_rn(g[e], gs);
+                    const float m = ema_momentum(cbv[e], mo, ge, b1, omb1);
+                    amax = fmaxf(amax, fabsf(m));
+                    rs = __fmaf_rn(ge, ge, rs);
+                    csum[h * 8 + e] = __fmaf_rn(ge, ge, csum[h * 8 + e]);
+                }
             }
         }
         const float rs_lane = rs;
@@ -1345,7 +1411,7 @@ __device__ __forceinline__ void stats_range_stream(const Hot& d, const StreamTab
 
 __device__ __forceinline__ void stream_init(StreamShared& sh) {
     if (threadIdx.x == 0) {
-        for (int g = 0; g < kGroups; ++g) {
+        for (int g = 0; g < kMaxGroups; ++g) {
             for (int k = 0; k < 8; ++k) {
                 ptx::mbar_init(&sh.full[g][k], 1);
                 ptx::mbar_init(&sh.empty[g][k], kThreads / 32);
@@ -1354,44 +1420,84 @@ __device__ __forceinline__ void stream_init(StreamShared& sh) {
         sh.abort_flag = 0;
         ptx::mbar_init_fence();
     }
-    // the __syncthreads of load_tables, which every thread calls next, publishes the barriers
+    // the __syncthreads of load_tables_stream, which every thread calls next, publishes the barriers
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kStreamThreads, 1) factored_stats_stream_kernel(LaunchCommon c) {
-    __shared__ StreamShared sh;
-    stream_init(sh);
-    const StreamTables s = load_tables_stream(c, false);
-    const bool producer = threadIdx.x >= kGroups * kThreads;
-    const int group = producer ? (threadIdx.x - kGroups * kThreads) / 32 : threadIdx.x / kThreads;
-    const int lt = threadIdx.x - group * kThreads;              // consumers only
-    const long long v = (long long)blockIdx.x * kGroups + group, nv = (long long)gridDim.x * kGroups;
-    const long long T0 = (long long)c.total_tiles * v / nv;
-    const long long T1 = (long long)c.total_tiles * (v + 1) / nv;
-    if (T0 >= T1) return;
-    Ring<kStatsStages, kStatsStageBytes> ring;
+// role of a thread inside a streamed CTA and the tile range of its group
+struct StreamRole {
+    bool producer;
+    int group, lt;
+    long long T0, T1;
+};
+template <int W>
+__device__ __forceinline__ StreamRole stream_role(const LaunchCommon& c) {
+    constexpr int G = StreamCfg<W>::kG;
+    StreamRole r;
+    r.producer = threadIdx.x >= G * kThreads;
+    r.group = r.producer ? (threadIdx.x - G * kThreads) / 32 : threadIdx.x / kThreads;
+    r.lt = threadIdx.x - r.group * kThreads;                    // consumers only
+    const long long total = (W == 16) ? tile_prefix<16>(c)[c.n_tensors] : c.total_tiles;
+    const long long v = (long long)blockIdx.x * G + r.group, nv = (long long)gridDim.x * G;
+    r.T0 = total * v / nv;
+    r.T1 = total * (v + 1) / nv;
+    return r;
+}
+
+template <int D, int STAGE_BYTES>
+__device__ __forceinline__ Ring<D, STAGE_BYTES> make_ring(StreamShared& sh, int group, size_t tables) {
+    Ring<D, STAGE_BYTES> ring;
     ring.full = sh.full[group];
     ring.empty = sh.empty[group];
-    ring.base = gx_smem_raw + kTabStats + (size_t)group * kStatsStages * kStatsStageBytes;
+    ring.base = gx_smem_raw + tables + (size_t)group * D * STAGE_BYTES;
     ring.abort_flag = &sh.abort_flag;
     ring.slot = 0;
     ring.phase = 0;
-    if (producer) {
-        stream_producer<T, kStatsStages, kStatsStageBytes, false>(c, T0, T1, ring);
+    return ring;
+}
+
+template <int VEC>
+__device__ __forceinline__ void flush_cols_w(const Hot& d, int ct, int lt, float (&csum)[VEC]) {
+    const int c0 = (ct * d.tcols + lt % d.tcols) * VEC;
+    if (c0 < d.cols) {
+        // col_sq is 16-byte aligned (the plan aligns every scratch array) and c0 % 8 == 0
+        float4* dst = reinterpret_cast<float4*>(d.col_sq + c0);
+#pragma unroll
+        for (int q = 0; q < VEC / 4; ++q)
+            atomicAdd(dst + q, make_float4(csum[4 * q], csum[4 * q + 1], csum[4 * q + 2], csum[4 * q + 3]));
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) csum[e] = 0.f;
+}
+
+template <typename T, int W>
+__global__ void __launch_bounds__(StreamCfg<W>::kCtaThreads, 1) factored_stats_stream_kernel(LaunchCommon c) {
+    using Cfg = StreamCfg<W>;
+    __shared__ StreamShared sh;
+    stream_init(sh);
+    const StreamTables s = load_tables_stream(c, false);
+    const StreamRole role = stream_role<W>(c);
+    const long long T0 = role.T0, T1 = role.T1;
+    if (T0 >= T1) return;
+    auto ring = make_ring<Cfg::kStatsStages, Cfg::kStatsStageBytes>(sh, role.group, kTabStats);
+    if (role.producer) {
+        stream_producer<T, W, Cfg::kStatsStages, Cfg::kStatsStageBytes, false>(c, T0, T1, ring);
         return;
     }
+    const int group = role.group, lt = role.lt;
     const float gs = c.gscale ? *c.gscale : 1.0f;
-    float csum8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    float csum[W];
+#pragma unroll
+    for (int e = 0; e < W; ++e) csum[e] = 0.f;
     RunMax run{nullptr, nullptr, -1, 0.f, 0.f, 1};
     Hot d;
     TileWalk w;
-    walk_begin(c, T0, w, d);
+    walk_begin_w<W>(c, T0, w, d);
     run.dst = d.mag_new;
     run.sum_dst = d.row_only ? d.row_sq : nullptr;
     for (long long tile = T0; tile < T1;) {
         const int n = (int)min(T1 - tile, (long long)(w.n_row_tiles - w.rt));
         const TileCursor t = walk_cursor(w, d, n);
-        stats_range_stream<T>(d, s, t, gs, csum8, run, ring, lt);
+        stats_range_stream<T, W, Cfg::kStatsStages>(d, s, t, gs, csum, run, ring, lt);
         tile += n;
         w.rt += n;
         bool col_change = false, tensor_change = false;
@@ -1403,12 +1509,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) factored_stats_stream_kerne
         const bool last = tile == T1;
         if ((col_change || last) && !d.row_only) {
             const int ct_done = col_change ? (tensor_change ? d.n_col_tiles - 1 : w.ct - 1) : w.ct;
-            flush_cols<8>(d, ct_done, csum8);
+            flush_cols_w<W>(d, ct_done, lt, csum);
         }
         if (tensor_change || last) runmax_flush_group(run, sh, group, lt);
         if (tensor_change && !last) {
             ++w.ti;
-            d = load_hot(c.descs + w.ti);
+            d = load_hot_w<W>(c.descs + w.ti);
             w.n_row_tiles = (d.rows + d.rows_per_tile - 1) / d.rows_per_tile;
             run.dst = d.mag_new;
             run.sum_dst = d.row_only ? d.row_sq : nullptr;
@@ -1447,12 +1553,14 @@ __device__ __forceinline__ void apply_element(const StreamTables& s, const Apply
     pf = __fmaf_rn(-__fmul_rn(qv, a.coef), rcp_approx(h), pw);
 }
 
-template <typename T, bool WD>
+template <typename T, bool WD, int W, int D>
 __device__ __forceinline__ void apply_range_stream(const Hot& d, const StreamTables& s, const TileCursor& t, float gs,
-                                                   const float (&cf)[8],
-                                                   Ring<kApplyStages, kApplyStageBytes>& ring, int lt) {
+                                                   const float (&cf)[W],
+                                                   Ring<D, StreamCfg<W>::kApplyStageBytes>& ring, int lt) {
+    using Cfg = StreamCfg<W>;
+    constexpr int H = W / 8;
     const int tx = lt % d.tcols, ty = lt / d.tcols;
-    const int c0 = (t.ct * d.tcols + tx) * 8;
+    const int c0 = (t.ct * d.tcols + tx) * W;
     const bool act = c0 < d.cols;
     ApplyScalars a;
     a.gs = gs;
@@ -1488,68 +1596,60 @@ __device__ __forceinline__ void apply_range_stream(const Hot& d, const StreamTab
         }
         const unsigned char* st = ring.stage();
         a.inv = a.mn > 0.f ? __frcp_rn(a.mn) : 0.f;
-        const uint4 gw = *reinterpret_cast<const uint4*>(st + lt * 16);
-        const uint4 pwd = *reinterpret_cast<const uint4*>(st + kChunkBytes2 + lt * 16);
-        const uint2 iw = *reinterpret_cast<const uint2*>(st + 2 * kChunkBytes2 + lt * 8);
-        float g[8], pf[8], cbv[8];
-        uint32_t kn[8];
-        Vec8<T>::unpack(gw, g);
-        Vec8<T>::unpack(pwd, pf);
-        cbv[0] = cb_of_byte<0>(s, iw.x); cbv[1] = cb_of_byte<1>(s, iw.x);
-        cbv[2] = cb_of_byte<2>(s, iw.x); cbv[3] = cb_of_byte<3>(s, iw.x);
-        cbv[4] = cb_of_byte<0>(s, iw.y); cbv[5] = cb_of_byte<1>(s, iw.y);
-        cbv[6] = cb_of_byte<2>(s, iw.y); cbv[7] = cb_of_byte<3>(s, iw.y);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) apply_element<T, WD>(s, a, g[e], cbv[e], cf[e], pf[e], kn[e]);
-        uint2 io;
-        io.x = __byte_perm(__byte_perm(kn[0], kn[1], 0x0040), __byte_perm(kn[2], kn[3], 0x0040), 0x5410);
-        io.y = __byte_perm(__byte_perm(kn[4], kn[5], 0x0040), __byte_perm(kn[6], kn[7], 0x0040), 0x5410);
-        *reinterpret_cast<uint2*>(d.idx + off) = io;
-        store_param<T, 8>(p + off, pf);
+        for (int h = 0; h < H; ++h) {
+            const uint4 gw = *reinterpret_cast<const uint4*>(st + lt * (W * 2) + h * 16);
+            const uint4 pwd = *reinterpret_cast<const uint4*>(st + Cfg::kValBytes + lt * (W * 2) + h * 16);
+            const uint2 iw = *reinterpret_cast<const uint2*>(st + 2 * Cfg::kValBytes + lt * W + h * 8);
+            float g[8], pf[8], cbv[8];
+            uint32_t kn[8];
+            Vec8<T>::unpack(gw, g);
+            Vec8<T>::unpack(pwd, pf);
+            cb_of_words(s, iw.x, iw.y, cbv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) apply_element<T, WD>(s, a, g[e], cbv[e], cf[h * 8 + e], pf[e], kn[e]);
+            uint2 io;
+            io.x = __byte_perm(__byte_perm(kn[0], kn[1], 0x0040), __byte_perm(kn[2], kn[3], 0x0040), 0x5410);
+            io.y = __byte_perm(__byte_perm(kn[4], kn[5], 0x0040), __byte_perm(kn[6], kn[7], 0x0040), 0x5410);
+            *reinterpret_cast<uint2*>(d.idx + off + h * 8) = io;
+            store_param<T, 8>(p + off + h * 8, pf);
+        }
         stage_release(ring, true, lt);
     }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kStreamThreads, 1) factored_apply_stream_kernel(LaunchCommon c) {
+template <typename T, int W>
+__global__ void __launch_bounds__(StreamCfg<W>::kCtaThreads, 1) factored_apply_stream_kernel(LaunchCommon c) {
+    using Cfg = StreamCfg<W>;
     __shared__ StreamShared sh;
     stream_init(sh);
     const StreamTables s = load_tables_stream(c, true);
-    const bool producer = threadIdx.x >= kGroups * kThreads;
-    const int group = producer ? (threadIdx.x - kGroups * kThreads) / 32 : threadIdx.x / kThreads;
-    const int lt = threadIdx.x - group * kThreads;
-    const long long v = (long long)blockIdx.x * kGroups + group, nv = (long long)gridDim.x * kGroups;
-    const long long T0 = (long long)c.total_tiles * v / nv;
-    const long long T1 = (long long)c.total_tiles * (v + 1) / nv;
+    const StreamRole role = stream_role<W>(c);
+    const long long T0 = role.T0, T1 = role.T1;
     if (T0 >= T1) return;
-    Ring<kApplyStages, kApplyStageBytes> ring;
-    ring.full = sh.full[group];
-    ring.empty = sh.empty[group];
-    ring.base = gx_smem_raw + kTabFull + (size_t)group * kApplyStages * kApplyStageBytes;
-    ring.abort_flag = &sh.abort_flag;
-    ring.slot = 0;
-    ring.phase = 0;
-    if (producer) {
-        stream_producer<T, kApplyStages, kApplyStageBytes, true>(c, T0, T1, ring);
+    auto ring = make_ring<Cfg::kApplyStages, Cfg::kApplyStageBytes>(sh, role.group, kTabFull);
+    if (role.producer) {
+        stream_producer<T, W, Cfg::kApplyStages, Cfg::kApplyStageBytes, true>(c, T0, T1, ring);
         return;
     }
+    const int lt = role.lt;
     const float gs = c.gscale ? *c.gscale : 1.0f;
-    float cf8[8];
+    float cf[W];
     Hot d;
     TileWalk w;
-    walk_begin(c, T0, w, d);
+    walk_begin_w<W>(c, T0, w, d);
     bool reload = true;
     for (long long tile = T0; tile < T1;) {
         if (reload) {
-            const int c0 = (w.ct * d.tcols + lt % d.tcols) * 8;
+            const int c0 = (w.ct * d.tcols + lt % d.tcols) * W;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) cf8[e] = d.row_only ? 1.0f : ((c0 + e < d.cols) ? d.cfac[c0 + e] : 0.f);
+            for (int e = 0; e < W; ++e) cf[e] = d.row_only ? 1.0f : ((c0 + e < d.cols) ? d.cfac[c0 + e] : 0.f);
             reload = false;
         }
         const int n = (int)min(T1 - tile, (long long)(w.n_row_tiles - w.rt));
         const TileCursor t = walk_cursor(w, d, n);
-        if (d.scal[3] != 1.0f) apply_range_stream<T, true>(d, s, t, gs, cf8, ring, lt);
-        else apply_range_stream<T, false>(d, s, t, gs, cf8, ring, lt);
+        if (d.scal[3] != 1.0f) apply_range_stream<T, true, W, Cfg::kApplyStages>(d, s, t, gs, cf, ring, lt);
+        else apply_range_stream<T, false, W, Cfg::kApplyStages>(d, s, t, gs, cf, ring, lt);
         tile += n;
         w.rt += n;
         if (w.rt == w.n_row_tiles) {
@@ -1559,7 +1659,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) factored_apply_stream_kerne
                 w.ct = 0;
                 if (tile < T1) {
                     ++w.ti;
-                    d = load_hot(c.descs + w.ti);
+                    d = load_hot_w<W>(c.descs + w.ti);
                     w.n_row_tiles = (d.rows + d.rows_per_tile - 1) / d.rows_per_tile;
                 }
             }
@@ -1678,12 +1778,19 @@ cudaError_t launch_factored_stats(const LaunchCommon& c, int dtype, int sm_count
     return dispatch(dtype, [&](auto* tag) {
         using T = std::remove_pointer_t<decltype(tag)>;
         // one row of raw chunks in flight beyond the current one (two were measured no faster)
-        if (c.fast == 3) {
+        if (c.fast == 3 || c.fast == 4) {
             if constexpr (sizeof(T) == 2) {
-                cudaFuncSetAttribute(factored_stats_stream_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)kSmemStatsStream);
-                factored_stats_stream_kernel<T><<<min(sm_count, (c.total_tiles + kGroups - 1) / kGroups), kStreamThreads,
-                                                  kSmemStatsStream, st>>>(c);
+                // persistent: one CTA per SM, groups without tiles return at once
+                if (c.fast == 4) {
+                    cudaFuncSetAttribute(factored_stats_stream_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem_stats_stream<16>());
+                    factored_stats_stream_kernel<T, 16><<<sm_count, StreamCfg<16>::kCtaThreads, smem_stats_stream<16>(), st>>>(c);
+                } else {
+                    cudaFuncSetAttribute(factored_stats_stream_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem_stats_stream<8>());
+                    factored_stats_stream_kernel<T, 8><<<min(sm_count, (c.total_tiles + 2) / 3), StreamCfg<8>::kCtaThreads,
+                                                         smem_stats_stream<8>(), st>>>(c);
+                }
             } else {
                 return cudaErrorInvalidValue;
             }
@@ -1713,12 +1820,18 @@ cudaError_t launch_factored_apply(const LaunchCommon& c, int dtype, int sm_count
     const int grid = min(c.total_tiles, sm_count * (fast ? kFastCtas : 2));
     return dispatch(dtype, [&](auto* tag) {
         using T = std::remove_pointer_t<decltype(tag)>;
-        if (c.fast == 3 && !c.stochastic) {
+        if ((c.fast == 3 || c.fast == 4) && !c.stochastic) {
             if constexpr (sizeof(T) == 2) {
-                cudaFuncSetAttribute(factored_apply_stream_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)kSmemApplyStream);
-                factored_apply_stream_kernel<T><<<min(sm_count, (c.total_tiles + kGroups - 1) / kGroups), kStreamThreads,
-                                                  kSmemApplyStream, st>>>(c);
+                if (c.fast == 4) {
+                    cudaFuncSetAttribute(factored_apply_stream_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem_apply_stream<16>());
+                    factored_apply_stream_kernel<T, 16><<<sm_count, StreamCfg<16>::kCtaThreads, smem_apply_stream<16>(), st>>>(c);
+                } else {
+                    cudaFuncSetAttribute(factored_apply_stream_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem_apply_stream<8>());
+                    factored_apply_stream_kernel<T, 8><<<min(sm_count, (c.total_tiles + 2) / 3), StreamCfg<8>::kCtaThreads,
+                                                         smem_apply_stream<8>(), st>>>(c);
+                }
             } else {
                 return cudaErrorInvalidValue;
             }

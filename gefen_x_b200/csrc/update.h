@@ -57,7 +57,8 @@ struct alignas(16) TensorDesc {
 
 struct LaunchCommon {
     const TensorDesc* descs;
-    const int* tile_start;            // [n_tensors + 1] prefix of work tiles
+    const int* tile_start;            // [n_tensors + 1] prefix of work tiles (fast == 4: followed by the
+                                      // prefix of the 16-wide tiles)
     int n_tensors;
     int total_tiles;
     const float* codebook;            // [256]
@@ -75,6 +76,9 @@ struct LaunchCommon {
                                       // 2: the same, and that source is an NVLS multicast address (bf16)
                                       // 3: as 1, 2-byte tensors whose rows start on 16-element boundaries:
                                       //    the streamed kernels (shared-memory rings fed by bulk copies)
+                                      // 4: as 3 with block periods that are multiples of 16: the streamed
+                                      //    kernels with 16 elements per thread; tile_start then holds a
+                                      //    second prefix [n_tensors + 1] for their tile geometry
 };
 
 // All launchers return the cudaError_t of the launch.

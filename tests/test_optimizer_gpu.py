@@ -452,9 +452,10 @@ def test_non_contiguous_parameter_steps_like_its_contiguous_copy():
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_streamed_update_kernels_match_the_register_pipelined_ones_bit_for_bit(dtype):
     """Plans of 2-byte tensors with 16-element row alignment run the streamed kernels (rows arrive
-    through shared-memory rings filled by bulk async copies).  They keep the thread-to-chunk mapping
-    and the arithmetic of the register-pipelined kernels, so parameters, indices and magnitudes are
-    bit-identical and the second moments agree to the order of the atomics.  Shapes: a partial last
+    through shared-memory rings filled by bulk async copies), with 16 elements per thread when every
+    block period is a multiple of 16 and 8 otherwise.  They keep the per-element arithmetic of the
+    register-pipelined kernels, so indices and magnitudes are bit-identical and the second moments
+    agree to the order of the atomics.  Shapes: a partial last
     column tile, rows that do not fill the last row step, narrow rows (several rows per step),
     1-D tensors, and more groups than tiles for the smallest plan."""
     from gefen_x_b200 import Gefen
@@ -464,14 +465,15 @@ def test_streamed_update_kernels_match_the_register_pipelined_ones_bit_for_bit(d
               ("w4", (64, 14336)), ("n0", (8192,)), ("n1", (4096,))]
     fixed_periods = {"w0": 16512, "w1": 512000, "w2": 2048, "w3": 1296, "w4": 7168, "n0": 1024, "n1": 512}
 
-    def run(streaming, shp):
+    def run(streaming, shp, wide=True):
         U.set_streaming(streaming)
+        U.set_wide_chunks(wide)
         try:
             g = torch.Generator().manual_seed(3)
             ps = [(n, (torch.randn(s, generator=g) * 0.05).to(dtype).to(_dev()).requires_grad_()) for n, s in shp]
             opt = Gefen(ps, lr=1e-2, weight_decay=0.01)
             # fixed block periods (the search would pick them from the data): one of each kind of
-            # block-to-row relation, all multiples of 8 as the 8-wide kernels need
+            # block-to-row relation, all multiples of 16 as the widest kernels need
             opt._predict_period_from_grad_sq = lambda name, p, grad: fixed_periods[name]
             for step in range(4):
                 gg = torch.Generator().manual_seed(50 + step)
@@ -484,22 +486,25 @@ def test_streamed_update_kernels_match_the_register_pipelined_ones_bit_for_bit(d
             return ps, opt, kinds
         finally:
             U.set_streaming(True)
+            U.set_wide_chunks(False)
 
     for shp in (shapes, shapes[3:4]):
-        pa, oa, ka = run(True, shp)
         pb, ob, kb = run(False, shp)
-        periods = {n: int(oa.state[a]["automatic_period"]) for n, a in pa}
-        assert ka == [3] and kb == [1], (ka, kb, periods)
-        for (n, a), (_, b) in zip(pa, pb):
-            # the statistics are summed with atomics in both kernels: a parameter may round the other way
-            torch.testing.assert_close(a.float(), b.float(), rtol=0, atol=1e-3, msg=n)
-            assert (a != b).float().mean().item() < 1e-3, n
-            sa, sb = oa.state[a], ob.state[b]
-            assert torch.equal(sa["m_codebook"], sb["m_codebook"]), n
-            assert torch.equal(sa["m_magnitude"], sb["m_magnitude"]), n
-            for key in ("v_row", "v_col", "vmean"):
-                if key in sa:
-                    torch.testing.assert_close(sa[key], sb[key], rtol=2e-5, atol=1e-12, msg=n + key)
+        # streamed kernels with 16 and with 8 elements per thread against the register-pipelined ones
+        for wide, want in ((True, [4]), (False, [3])):
+            pa, oa, ka = run(True, shp, wide)
+            periods = {n: int(oa.state[a]["automatic_period"]) for n, a in pa}
+            assert ka == want and kb == [1], (ka, kb, periods)
+            for (n, a), (_, b) in zip(pa, pb):
+                # the statistics are summed with atomics in all kernels: a parameter may round the other way
+                torch.testing.assert_close(a.float(), b.float(), rtol=0, atol=1e-3, msg=n)
+                assert (a != b).float().mean().item() < 1e-3, n
+                sa, sb = oa.state[a], ob.state[b]
+                assert torch.equal(sa["m_codebook"], sb["m_codebook"]), n
+                assert torch.equal(sa["m_magnitude"], sb["m_magnitude"]), n
+                for key in ("v_row", "v_col", "vmean"):
+                    if key in sa:
+                        torch.testing.assert_close(sa[key], sb[key], rtol=2e-5, atol=1e-12, msg=n + key)
 
 
 def test_pre_launch_hook_tells_heavy_host_preparation_from_a_plan_rebuild():
