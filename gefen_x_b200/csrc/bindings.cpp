@@ -21,6 +21,7 @@
 #include "fp8_quant.h"
 #include "gemm_sm100.h"
 #include "model_ops.h"
+#include "muon_ops.h"
 #include "quant.h"
 #include "update.h"
 
@@ -425,6 +426,54 @@ void gemm_pair_e4m3(const Tensor& a, const Tensor& b, const Tensor& sa, const Te
           "gemm_pair_e4m3");
 }
 
+
+// NorMuon row normalisation, cautious mask and (optionally) the parameter update on an orthogonalised
+// Muon update, in place.  scal: device fp32 {1 - beta2^t, lr * ratio, 1 - lr * weight_decay}.
+void muon_epilogue(Tensor update, const c10::optional<Tensor>& grad, const c10::optional<Tensor>& normuon_v,
+                   const c10::optional<Tensor>& param, const Tensor& scal, bool normuon, bool cautious,
+                   double beta2, double eps) {
+    c10::cuda::CUDAGuard guard(update.device());
+    TORCH_CHECK(update.is_cuda() && update.dim() == 2 && update.is_contiguous(), "muon_epilogue: contiguous 2-D CUDA update");
+    TORCH_CHECK(scal.is_cuda() && scal.scalar_type() == at::kFloat && scal.numel() >= 3 && scal.is_contiguous(),
+                "muon_epilogue: scal must be a CUDA fp32 tensor of 3 values");
+    gx::MuonEpilogue e{};
+    e.update = update.data_ptr();
+    e.rows = update.size(0);
+    e.cols = (int)update.size(1);
+    e.normuon = normuon ? 1 : 0;
+    e.cautious = cautious ? 1 : 0;
+    e.beta2 = (float)beta2;
+    e.eps = (float)eps;
+    e.scal = scal.data_ptr<float>();
+    if (cautious) {
+        TORCH_CHECK(grad.has_value() && grad->defined() && grad->is_cuda() && grad->is_contiguous() &&
+                        grad->sizes() == update.sizes() && grad->scalar_type() == update.scalar_type(),
+                    "muon_epilogue: the cautious mask needs a gradient of the update's shape and dtype");
+        e.grad = grad->data_ptr();
+    }
+    if (normuon) {
+        TORCH_CHECK(normuon_v.has_value() && normuon_v->defined() && normuon_v->is_cuda() &&
+                        normuon_v->scalar_type() == at::kFloat && normuon_v->is_contiguous() &&
+                        normuon_v->numel() == e.rows,
+                    "muon_epilogue: normuon_v must hold one fp32 value per row");
+        e.v = normuon_v->data_ptr<float>();
+    }
+    if (param.has_value() && param->defined()) {
+        TORCH_CHECK(param->is_cuda() && param->is_contiguous() && param->sizes() == update.sizes() &&
+                        param->scalar_type() == update.scalar_type(),
+                    "muon_epilogue: the parameter must have the update's shape and dtype");
+        e.param = param->data_ptr();
+    }
+    auto fopt = update.options().dtype(at::kFloat);
+    Tensor row_sq = at::empty({e.rows}, fopt), row_scale = at::empty({e.rows}, fopt), glob = at::empty({2}, fopt);
+    Tensor agree = at::empty({e.rows}, update.options().dtype(at::kInt));
+    e.row_sq = row_sq.data_ptr<float>();
+    e.row_scale = row_scale.data_ptr<float>();
+    e.glob = glob.data_ptr<float>();
+    e.agree = agree.data_ptr<int>();
+    check(gx::launch_muon_epilogue(e, dtype_code(update.scalar_type()), sm_count(), stream()), "muon_epilogue");
+}
+
 inline void to_ptrs(at::IntArrayRef v, void** out);
 
 // c = a [M, K] @ bstage [N, K]^T where bstage is filled inside the launch from the peers'
@@ -782,6 +831,8 @@ TORCH_LIBRARY(gefenx, m) {
           "float beta, Tensor? status) -> ()");
     m.def("gemm_pair_bf16(Tensor a, Tensor b, Tensor(a!) c0, Tensor(b!)? c1, Tensor? d, Tensor? aux, bool a_t, "
           "bool b_t, float alpha, float beta, int epi, int bn, Tensor? status, Tensor(c!)? sumsq, bool dynamic) -> ()");
+    m.def("muon_epilogue(Tensor(a!) update, Tensor? grad, Tensor(b!)? normuon_v, Tensor(c!)? param, Tensor scal, "
+          "bool normuon, bool cautious, float beta2, float eps) -> ()");
     m.def("gemm_pair_e4m3(Tensor a, Tensor b, Tensor sa, Tensor sb, Tensor(a!) out, Tensor? status, bool dynamic) -> ()");
     m.def("gemm_ag_bf16(Tensor a, Tensor(a!) bstage, Tensor(b!) c, int[] peer_bases, Tensor segs, "
           "Tensor seg_meta, Tensor tile_order, Tensor(c!) flags, Tensor(d!) count, int epoch, "
@@ -828,6 +879,7 @@ TORCH_LIBRARY_IMPL(gefenx, CUDA, m) {
     m.impl("gemm_bf16", &gemm_bf16);
     m.impl("gemm_pair_bf16", &gemm_pair_bf16);
     m.impl("gemm_pair_e4m3", &gemm_pair_e4m3);
+    m.impl("muon_epilogue", &muon_epilogue);
     m.impl("gemm_ag_bf16", &gemm_ag_bf16);
     m.impl("comm_wait", &comm_wait);
     m.impl("comm_gather", &comm_gather);

@@ -24,7 +24,7 @@ def available(required: bool = False) -> bool:
 
 
 # kernels launched by one call of each operator (for launch accounting)
-_KERNELS_PER_CALL = {"factored_update": 4, "desc_size": 0, "rmsnorm_bwd_partials": 0}
+_KERNELS_PER_CALL = {"factored_update": 4, "muon_epilogue": 3, "desc_size": 0, "rmsnorm_bwd_partials": 0}
 launch_count = 0
 
 

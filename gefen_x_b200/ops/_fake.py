@@ -19,7 +19,7 @@ import torch
 
 _VOID_OPS = (
     "block_update", "factored_update", "reduce_sources", "clip_coef", "histogram", "remap_indices",
-    "quantize_rows_e4m3", "quantize_cols_e4m3_t", "dequantize", "gemm_bf16", "gemm_pair_bf16", "gemm_pair_e4m3", "gemm_ag_bf16",
+    "quantize_rows_e4m3", "quantize_cols_e4m3_t", "dequantize", "gemm_bf16", "gemm_pair_bf16", "gemm_pair_e4m3", "gemm_ag_bf16", "muon_epilogue",
     "comm_wait", "comm_gather", "comm_scatter_apply", "comm_reduce_segments", "comm_gather_rows",
     "comm_scatter_add_rows", "comm_allreduce_scalar", "rmsnorm_fwd", "rmsnorm_bwd", "rope",
     "flash_attention_fwd", "attn_softmax", "attn_row_dot", "attn_bwd_rows", "swiglu_fwd", "swiglu_bwd",

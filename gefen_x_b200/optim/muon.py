@@ -315,10 +315,52 @@ class GefenMuon(Gefen):
         if not update.is_contiguous():
             update = update.contiguous()
         state = self.state[p]
+        if (group["normuon"] or group["cautious"]) and self._epilogue_kernels_apply(update, grad):
+            return self._muon_epilogue_kernels(state, group, update, grad)
         if group["normuon"]:
             update = self._normuon_normalize(state, update, group["normuon_beta2"], group["normuon_eps"])
         if group["cautious"]:
             update = cautious_mask_(update, grad.to(update.dtype))
+        return update
+
+    @staticmethod
+    def _epilogue_kernels_apply(update: torch.Tensor, grad: torch.Tensor) -> bool:
+        """CUDA matrices in a kernel dtype: NorMuon and the cautious mask run as three launches over the
+        update (row statistics, row factors, finish) instead of the chain of torch ops."""
+        if not (update.is_cuda and update.dim() == 2 and update.is_contiguous()
+                and update.dtype in (torch.float32, torch.bfloat16, torch.float16)
+                and tuple(grad.shape) == tuple(update.shape) and update.numel() > 0):
+            return False
+        from ..ops import _ext
+
+        return _ext.available()
+
+    def _muon_epilogue_kernels(self, state, group, update: torch.Tensor, grad: torch.Tensor) -> torch.Tensor:
+        """Same values as ``_normuon_normalize`` followed by ``cautious_mask_`` (every product rounded
+        where those round it), computed by ``csrc/muon_ops.cu``; the update is rewritten in place."""
+        from ..ops._ext import ops
+
+        dev = update.device
+        v = None
+        bc = 1.0
+        if group["normuon"]:
+            beta2 = group["normuon_beta2"]
+            v = state.get("normuon_v")
+            if v is None or v.shape[0] != update.shape[0]:
+                v = torch.zeros(update.shape[0], 1, dtype=torch.float32, device=dev)
+                state["normuon_v"] = v
+                state["normuon_step"] = self._new_step_counter(dev)
+            state["normuon_step"] += 1
+            bc = 1 - beta2 ** state["normuon_step"]
+        if torch.is_tensor(bc) and bc.is_cuda:        # device-resident step counter (capturable)
+            scal = torch.stack([bc.to(device=dev, dtype=torch.float32).reshape(()),
+                                torch.zeros((), dtype=torch.float32, device=dev),
+                                torch.ones((), dtype=torch.float32, device=dev)])
+        else:
+            scal = torch.tensor([float(bc), 0.0, 1.0], dtype=torch.float32).to(dev, non_blocking=True)
+        g = grad.to(update.dtype).contiguous() if group["cautious"] else None
+        ops().muon_epilogue(update, g, v, None, scal, bool(group["normuon"]), bool(group["cautious"]),
+                            float(group["normuon_beta2"]), float(group["normuon_eps"]))
         return update
 
     @staticmethod

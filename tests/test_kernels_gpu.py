@@ -672,3 +672,70 @@ def test_fp8_newton_schulz_own_gemm_tracks_the_library_gemm():
     # same quantised operands, fp32 accumulation in both: the results agree far inside the fp8 error
     assert (own.float() - lib.float()).abs().max().item() <= 2e-2
     assert (own.float() - bf.float()).abs().mean().item() <= 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_muon_epilogue_kernels_match_the_torch_chain(dtype):
+    """NorMuon row normalisation, the cautious mask and the parameter update in three launches
+    (``csrc/muon_ops.cu``) against the chain of torch ops they replace (``GefenMuon._normuon_normalize``,
+    ``cautious_mask_``, the apply), with the products rounded where torch rounds them: vector and
+    scalar column counts, each feature alone and together, two steps (the second moment carries)."""
+    from gefen_x_b200.ops._ext import ops
+    from gefen_x_b200.optim.muon import cautious_mask_
+
+    dev = _dev()
+    g = torch.Generator().manual_seed(17)
+    beta2, eps, lr_ratio, wdf = 0.95, 1e-8, 3e-3, 0.9997
+    for rows, cols in [(512, 1024), (300, 264), (130, 100)]:
+        for normuon, cautious in [(True, False), (False, True), (True, True)]:
+            p0 = (torch.randn(rows, cols, generator=g) * 0.05).to(dtype).to(dev)
+            p_ref, p_ker = p0.clone(), p0.clone()
+            v_ref = torch.zeros(rows, 1, dtype=torch.float32, device=dev)
+            v_ker = v_ref.clone()
+            for step in (1, 2):
+                u = (torch.randn(rows, cols, generator=g) * 0.3).to(dtype).to(dev)
+                gr = torch.randn(rows, cols, generator=g).to(dtype).to(dev)
+                bc = 1 - beta2 ** step
+                # the torch chain
+                ur = u.clone()
+                if normuon:
+                    row_norm = torch.linalg.vector_norm(ur, dim=1, keepdim=True, dtype=torch.float32)
+                    row_sq = row_norm.square()
+                    v_ref.mul_(beta2).add_(row_sq, alpha=(1 - beta2) / cols)
+                    denom = (v_ref / bc).sqrt_().add_(eps)
+                    frob = row_sq.sum().sqrt_() / torch.linalg.vector_norm(row_norm / denom).clamp(min=1e-38)
+                    ur.mul_((frob / denom).to(dtype))
+                if cautious:
+                    ur = cautious_mask_(ur, gr)
+                p_ref.mul_(wdf)
+                p_ref.add_(ur, alpha=-lr_ratio)
+                # the kernels (update in place, parameter in the same pass)
+                uk = u.clone()
+                scal = torch.tensor([bc, lr_ratio, wdf], dtype=torch.float32, device=dev)
+                ops().muon_epilogue(uk, gr if cautious else None, v_ker if normuon else None, p_ker, scal,
+                                    normuon, cautious, beta2, eps)
+                tol = 1.6e-2 if dtype == torch.bfloat16 else 1e-5
+                torch.testing.assert_close(uk.float(), ur.float(), rtol=tol, atol=1e-6)
+                assert (uk != ur).float().mean().item() < (0.02 if dtype == torch.bfloat16 else 1.0)
+                torch.testing.assert_close(p_ker.float(), p_ref.float(), rtol=tol, atol=1e-5)
+                if normuon:
+                    torch.testing.assert_close(v_ker, v_ref, rtol=1e-5, atol=1e-12)
+
+
+def test_gefen_muon_with_normuon_and_cautious_takes_the_epilogue_kernels():
+    """``GefenMuon(normuon=True, cautious=True)`` on CUDA matrices follows the same optimizer on the CPU
+    (the torch chain) over several steps."""
+    from gefen_x_b200 import GefenMuon
+
+    g = torch.Generator().manual_seed(23)
+    w = torch.randn(64, 128, generator=g) * 0.05
+    grads = [torch.randn(64, 128, generator=g) * 1e-2 for _ in range(4)]
+    outs = []
+    for dev in (torch.device("cpu"), _dev()):
+        p = w.clone().to(dev).requires_grad_()
+        opt = GefenMuon([("w", p)], lr=1e-2, normuon=True, cautious=True)
+        for gr in grads:
+            p.grad = gr.to(dev)
+            opt.step()
+        outs.append(p.detach().cpu())
+    torch.testing.assert_close(outs[0], outs[1], rtol=0, atol=2e-3)
