@@ -58,6 +58,8 @@ def parse_args():
     ap.add_argument("--nvls", default="auto", choices=["auto", "on", "off"],
                     help="gradient reduce-scatter through NVSwitch (multimem.ld_reduce); auto: off unless GEFENX_NVLS=1 "
                          "(measured slower on 2 GPUs, level on 8)")
+    ap.add_argument("--copy-lanes", type=int, default=4,
+                    help="auxiliary streams over which the copy-engine transfers of a gather / reduce are spread")
     ap.add_argument("--gemm-schedule", default="auto", choices=["auto", "static", "dynamic"],
                     help="tile schedule of the pair GEMM: fixed assignment, or tiles drawn from a device counter "
                          "(auto: dynamic with several ranks)")
@@ -159,7 +161,7 @@ def run_ours(args):
                              rs_mode=args.rs_mode, ag_gemm=args.ag_gemm, optimizer=args.optimizer,
                              gather_mode=args.gather, reduce_ctas=args.reduce_ctas, reduce_mode=args.reduce,
                              nvls={"auto": None, "on": True, "off": False}[args.nvls],
-                             gemm_schedule=args.gemm_schedule,
+                             gemm_schedule=args.gemm_schedule, copy_lanes=args.copy_lanes,
                              muon_kwargs=dict(ns_schedule="standard", ns_steps=5, fp8_ns=args.fp8_ns)
                              if args.optimizer == "muon_hybrid" else None)
     gen = torch.Generator().manual_seed(1000 + rank)
@@ -262,7 +264,7 @@ def run_ours(args):
         "impl_config": {"rs_mode": trainer.rs_mode, "ag_gemm": trainer.ag_gemm, "attention": args.attn,
                         "gemm": args.gemm, "gather": trainer.gather_mode, "reduce": trainer.reduce_mode,
                         "reduce_ctas": trainer.reduce_ctas, "sparse_embedding": trainer.sparse_embed, "nvls": trainer.nvls,
-                        "gemm_schedule": args.gemm_schedule,
+                        "gemm_schedule": args.gemm_schedule, "copy_lanes": args.copy_lanes,
                         # kernel family of the optimizer's launch plans: 1 register-pipelined, 2 NVLS
                         # sources, 3 streamed through shared-memory rings, 0 generic
                         "update_plan_kinds": sorted({int(getattr(pl, "fast", -1)) for pl in

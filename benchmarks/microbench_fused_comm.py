@@ -147,10 +147,12 @@ def main():
 
     # parameter all-gather of the layer
     layer_bytes = grp.full_numel * 2
-    for mode in ("kernel", "ce"):
+    for mode, lanes in (("kernel", 1), ("ce", 1), ("ce", 4), ("ce", 8)):
         tr.gather_mode = mode
+        tr.copy_lanes = lanes
         ms = timed(lambda: tr._gather_into(grp, flat))
-        report("parameter all-gather of one layer ({})".format("copy engines" if mode == "ce" else "gather_kernel, 64 CTAs"),
+        report("parameter all-gather of one layer ({})".format(
+                   "copy engines, {} stream(s)".format(lanes) if mode == "ce" else "gather_kernel, 64 CTAs"),
                ms, 0.0, layer_bytes * (world - 1) / world, "{:.0f} MB per layer".format(layer_bytes / 1e6))
     tr.check_status()
     dist.destroy_process_group()

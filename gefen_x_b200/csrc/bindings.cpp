@@ -585,20 +585,62 @@ void comm_reduce_segments(int64_t world, const Tensor& segs, int64_t n_segs,
           "reduce_segments");
 }
 
-// One asynchronous device-to-device copy per row of a host table [n, 3] = (dst, src, bytes) on
-// the current stream: the copies run on the copy engines, so a parameter all-gather from the
-// peers' arenas takes no SM away from the GEMMs it overlaps with.
-void comm_copy_list(const Tensor& table, int64_t device_index) {
+// One asynchronous device-to-device copy per row of a host table [n, 3] = (dst, src, bytes): the
+// copies run on the copy engines, so a parameter all-gather from the peers' arenas takes no SM away
+// from the GEMMs it overlaps with.  With `lanes` > 1 the copies are spread round-robin over that many
+// auxiliary streams that fork from the current stream and join it again (events), so that several
+// copy engines work at once; the call keeps the current stream's ordering either way.
+void comm_copy_list(const Tensor& table, int64_t device_index, int64_t lanes) {
     c10::cuda::CUDAGuard guard((c10::DeviceIndex)device_index);
     TORCH_CHECK(!table.is_cuda() && table.scalar_type() == at::kLong && table.is_contiguous() &&
                 table.dim() == 2 && table.size(1) == 3, "table: CPU int64 [n, 3]");
     const int64_t* t = table.data_ptr<int64_t>();
     cudaStream_t st = stream();
-    for (int64_t i = 0; i < table.size(0); ++i) {
+    const int64_t n = table.size(0);
+    constexpr int kMaxLanes = 8;
+    const int k = (int)std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(lanes, kMaxLanes), n));
+    if (k == 1) {
+        for (int64_t i = 0; i < n; ++i) {
+            if (t[3 * i + 2] <= 0) continue;
+            check(cudaMemcpyAsync(reinterpret_cast<void*>(t[3 * i]), reinterpret_cast<const void*>(t[3 * i + 1]),
+                                  (size_t)t[3 * i + 2], cudaMemcpyDeviceToDevice, st),
+                  "copy_list");
+        }
+        return;
+    }
+    struct Lanes {
+        cudaStream_t s[kMaxLanes];
+        cudaEvent_t done[kMaxLanes];
+        cudaEvent_t start;
+    };
+    static std::mutex mu;
+    static std::map<int, Lanes> pool;
+    Lanes* L;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = pool.find((int)device_index);
+        if (it == pool.end()) {
+            Lanes fresh{};
+            for (int i = 0; i < kMaxLanes; ++i) {
+                check(cudaStreamCreateWithFlags(&fresh.s[i], cudaStreamNonBlocking), "copy_list stream");
+                check(cudaEventCreateWithFlags(&fresh.done[i], cudaEventDisableTiming), "copy_list event");
+            }
+            check(cudaEventCreateWithFlags(&fresh.start, cudaEventDisableTiming), "copy_list event");
+            it = pool.emplace((int)device_index, fresh).first;
+        }
+        L = &it->second;
+    }
+    check(cudaEventRecord(L->start, st), "copy_list fork");
+    for (int i = 0; i < k; ++i) check(cudaStreamWaitEvent(L->s[i], L->start, 0), "copy_list fork");
+    for (int64_t i = 0; i < n; ++i) {
         if (t[3 * i + 2] <= 0) continue;
         check(cudaMemcpyAsync(reinterpret_cast<void*>(t[3 * i]), reinterpret_cast<const void*>(t[3 * i + 1]),
-                              (size_t)t[3 * i + 2], cudaMemcpyDeviceToDevice, st),
+                              (size_t)t[3 * i + 2], cudaMemcpyDeviceToDevice, L->s[i % k]),
               "copy_list");
+    }
+    for (int i = 0; i < k; ++i) {
+        check(cudaEventRecord(L->done[i], L->s[i]), "copy_list join");
+        check(cudaStreamWaitEvent(st, L->done[i], 0), "copy_list join");
     }
 }
 
@@ -844,7 +886,7 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("comm_scatter_apply(Tensor segs, int n_segs, Tensor unit_prefix, int total_units, int ctas) -> ()");
     m.def("comm_reduce_segments(int world, Tensor segs, int n_segs, Tensor unit_prefix, int total_units, "
           "float scale, Tensor? partials, int ctas, int dtype, bool multimem) -> ()");
-    m.def("comm_copy_list(Tensor table, int device_index) -> ()", &comm_copy_list);
+    m.def("comm_copy_list(Tensor table, int device_index, int lanes) -> ()", &comm_copy_list);
     m.def("comm_gather_rows(int[] shard_ptrs, int rows_per, int rows, Tensor tok, Tensor(a!) out) -> ()");
     m.def("comm_scatter_add_rows(int[] tok_ptrs, int[] grad_ptrs, int n_tok, int row0, float scale, "
           "Tensor(a!) dst) -> ()");

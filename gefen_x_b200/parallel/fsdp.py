@@ -126,8 +126,9 @@ class ShardedTrainer:
                  ag_gemm: bool = False, ag_fetch_ctas: int = 32, muon_kwargs: Optional[dict] = None,
                  gather_mode: str = "ce", reduce_ctas: int = 148, reduce_mode: str = "ce",
                  sparse_embedding: bool = True, embed_capacity: int = 16384, nvls: Optional[bool] = None,
-                 gemm_schedule: str = "auto"):
+                 gemm_schedule: str = "auto", copy_lanes: int = 4):
         self.cfg = cfg
+        self.copy_lanes = max(1, int(copy_lanes))   # auxiliary streams of the copy-engine transfers
         self.world, self.rank = int(world), int(rank)
         self.device = torch.device(device if device is not None else
                                    ("cuda" if torch.cuda.is_available() else "cpu"))
@@ -618,7 +619,7 @@ class ShardedTrainer:
                 table = torch.tensor([[dst.data_ptr() + do, base[r] + so, nb] for do, r, so, nb in copies],
                                      dtype=torch.int64).reshape(-1, 3)
                 self._copy_tables[key] = table
-            ops().comm_copy_list(table, self.device.index or 0)
+            ops().comm_copy_list(table, self.device.index or 0, self.copy_lanes)
             return
         ops().comm_gather(self.arena.base_ptrs, segs, n_segs, dst, prefix, total, self.gather_ctas)
 
@@ -696,7 +697,7 @@ class ShardedTrainer:
                     g.reduce_tables[part] = self._build_reduce_table(g, part)
                 segs, n_segs, prefix, total, copy_table = g.reduce_tables[part]
                 if copy_table is not None:
-                    ops().comm_copy_list(copy_table, self.device.index or 0)
+                    ops().comm_copy_list(copy_table, self.device.index or 0, self.copy_lanes)
                 if n_segs:
                     ops().comm_reduce_segments(self.world, segs, n_segs, prefix, total,
                                                1.0 / self.world, self.norm_partials if self.clip else None,
