@@ -332,7 +332,7 @@ static void pair_workspace(const Tensor& like, gx::PairParams& p, bool dynamic) 
 void gemm_pair_bf16(const Tensor& a, const Tensor& b, Tensor c0, const c10::optional<Tensor>& c1,
                     const c10::optional<Tensor>& d, const c10::optional<Tensor>& aux, bool a_t, bool b_t,
                     double alpha, double beta, int64_t epi, int64_t bn, const c10::optional<Tensor>& status,
-                    const c10::optional<Tensor>& sumsq, bool dynamic) {
+                    const c10::optional<Tensor>& sumsq, bool dynamic, bool symmetric) {
     c10::cuda::CUDAGuard guard(a.device());
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && c0.is_cuda(), "gemm_pair_bf16: CUDA tensors required");
     TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 &&
@@ -352,6 +352,8 @@ void gemm_pair_bf16(const Tensor& a, const Tensor& b, Tensor c0, const c10::opti
     p.bn = (int)bn;
     p.status = (status.has_value() && status->defined()) ? status->data_ptr<int>() : nullptr;
     p.sumsq = nullptr;
+    p.symmetric = symmetric ? 1 : 0;
+    TORCH_CHECK(!symmetric || epi == gx::kEpiPlain, "gemm_pair_bf16: the symmetric mode takes the plain epilogue");
     if (sumsq.has_value() && sumsq->defined()) {
         TORCH_CHECK(epi == gx::kEpiPlain, "gemm_pair_bf16: sumsq is available with the plain epilogue only");
         TORCH_CHECK(sumsq->is_cuda() && sumsq->scalar_type() == at::kFloat && sumsq->is_contiguous() &&
@@ -872,7 +874,8 @@ TORCH_LIBRARY(gefenx, m) {
     m.def("gemm_bf16(Tensor a, Tensor b, Tensor(a!) c, Tensor? d, bool a_t, bool b_t, float alpha, "
           "float beta, Tensor? status) -> ()");
     m.def("gemm_pair_bf16(Tensor a, Tensor b, Tensor(a!) c0, Tensor(b!)? c1, Tensor? d, Tensor? aux, bool a_t, "
-          "bool b_t, float alpha, float beta, int epi, int bn, Tensor? status, Tensor(c!)? sumsq, bool dynamic) -> ()");
+          "bool b_t, float alpha, float beta, int epi, int bn, Tensor? status, Tensor(c!)? sumsq, bool dynamic, "
+          "bool symmetric) -> ()");
     m.def("muon_epilogue(Tensor(a!) update, Tensor? grad, Tensor(b!)? normuon_v, Tensor(c!)? param, Tensor scal, "
           "bool normuon, bool cautious, float beta2, float eps) -> ()");
     m.def("gemm_pair_e4m3(Tensor a, Tensor b, Tensor sa, Tensor sb, Tensor(a!) out, Tensor? status, bool dynamic) -> ()");

@@ -149,6 +149,14 @@ __device__ __forceinline__ void prefetch_row(const __nv_bfloat16* base, long lon
 // block of the output: they share the fewest distinct operand panels, and the panels of a group
 // are fetched from HBM once while the other operand streams past.
 __device__ __forceinline__ void tile_coords(const PairParams& p, int tile, int& mt, int& nt) {
+    if (p.symmetric) {
+        // tiles on and below the diagonal, row by row: tile = mt (mt + 1) / 2 + nt, nt <= mt
+        mt = (int)((sqrtf(8.0f * (float)tile + 1.0f) - 1.0f) * 0.5f);
+        while ((mt + 1) * (mt + 2) / 2 <= tile) ++mt;        // the float root can be one off either way
+        while (mt * (mt + 1) / 2 > tile) --mt;
+        nt = tile - mt * (mt + 1) / 2;
+        return;
+    }
     const int per_group = p.group_m * p.n_tiles;
     const int g = tile / per_group;
     const int first_m = g * p.group_m;
@@ -660,7 +668,7 @@ cudaError_t launch_pair(const PairMaps& maps, PairParams p, int sm_count, cudaSt
     const int n_cols = (EPI == kEpiSwigluFwd) ? PairTile<BN>::kHalfN : BN;   // output columns per tile
     p.m_tiles = (p.M + 255) / 256;
     p.n_tiles = (p.N + n_cols - 1) / n_cols;
-    p.total_tiles = p.m_tiles * p.n_tiles;
+    p.total_tiles = p.symmetric ? p.m_tiles * (p.m_tiles + 1) / 2 : p.m_tiles * p.n_tiles;
     // row-tile group of the visiting order: all rows when A is small enough to stay in L2 (then B
     // streams through once), otherwise 8 (near-square waves)
     p.group_m = ((long long)p.M * p.K * (EPI == kEpiScaledE4m3 ? 1 : 2) <= (48ll << 20) || p.m_tiles <= 8) ? p.m_tiles : 8;
@@ -683,6 +691,27 @@ cudaError_t launch_pair(const PairMaps& maps, PairParams p, int sm_count, cudaSt
     if (pairs < 1) pairs = 1;
     gemm_pair_kernel<BN, EPI><<<2 * pairs, kPairThreads, smem, st>>>(maps, p);
     return cudaGetLastError();
+}
+
+// C[j, i] = C[i, j] for every element of the 256 x 256 tiles strictly below the diagonal: completes a
+// symmetric product of which only those tiles and the diagonal ones were computed.  32 x 32 blocks
+// through shared memory, coalesced on both sides.
+__global__ void __launch_bounds__(256) mirror_lower_kernel(__nv_bfloat16* __restrict__ C, long long ldc, int M) {
+    __shared__ __nv_bfloat16 t[32][33];
+    const int bi = blockIdx.y, bj = blockIdx.x;              // 32-row / 32-column block of the source
+    if ((bi >> 3) <= (bj >> 3)) return;                      // its 256-tile lies on or above the diagonal
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int r = bi * 32 + ty + 8 * k, c = bj * 32 + tx;
+        if (r < M && c < M) t[ty + 8 * k][tx] = C[(long long)r * ldc + c];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int r = bj * 32 + ty + 8 * k, c = bi * 32 + tx; // destination row / column
+        if (r < M && c < M) C[(long long)r * ldc + c] = t[tx][ty + 8 * k];
+    }
 }
 
 }  // namespace
@@ -735,6 +764,14 @@ cudaError_t launch_gemm_pair_bf16(const __nv_bfloat16* A, long long lda, const _
     if (p.epi == kEpiSwigluBwd)
         return bn == 256 ? launch_pair<256, kEpiSwigluBwd>(maps, p, sm_count, st)
                          : launch_pair<128, kEpiSwigluBwd>(maps, p, sm_count, st);
+    if (p.symmetric) {
+        if (p.M != p.N || bn != 256 || p.sumsq != nullptr) return cudaErrorInvalidValue;
+        cudaError_t e = launch_pair<256, kEpiPlain>(maps, p, sm_count, st);
+        if (e != cudaSuccess) return e;
+        const int blocks = (p.M + 31) / 32;
+        if (blocks > 8) mirror_lower_kernel<<<dim3(blocks, blocks), 256, 0, st>>>(C0, ldc0, p.M);
+        return cudaGetLastError();
+    }
     return bn == 256 ? launch_pair<256, kEpiPlain>(maps, p, sm_count, st)
                      : launch_pair<128, kEpiPlain>(maps, p, sm_count, st);
 }

@@ -70,6 +70,8 @@ struct PairParams {
     long long ldaux;
     const float* row_scale;         // kEpiScaledE4m3: [M] scales of A's rows
     const float* col_scale;         // kEpiScaledE4m3: [N] scales of B's rows (the output's columns)
+    int symmetric;                  // plain epilogue, M == N, the result (and D) symmetric: only the tiles on and
+                                    // below the diagonal are computed, a second launch mirrors them
     int bn;                         // 0: choose; 128 / 256: force the tile width
     int* status;                    // device status word, may be null
     // plain epilogue, optional: sum of squares of the stored output accumulated into kSumsqSlots fp32

@@ -81,8 +81,14 @@ def pair_eligible(m: int, n: int, k: int) -> bool:
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = False,
          alpha: float = 1.0, beta: float = 0.0, d: Optional[torch.Tensor] = None,
-         out: Optional[torch.Tensor] = None, sumsq: Optional[torch.Tensor] = None) -> torch.Tensor:
+         out: Optional[torch.Tensor] = None, sumsq: Optional[torch.Tensor] = None,
+         symmetric: bool = False) -> torch.Tensor:
     """See the module docstring for the layout convention.
+
+    ``symmetric``: the caller states that the result is a symmetric matrix (``X X^T``, or ``c G G + b G``
+    with ``G`` symmetric).  The CTA-pair kernel then computes only the 256 x 256 tiles on and below the
+    diagonal (T (T + 1) / 2 of T^2) and a small second launch copies them across it; matrices of
+    fewer than 2048 rows and the other kernels ignore the hint.
 
     ``sumsq`` (fp32, at least 2048 slots) receives, added slot-wise, the sum of squares of the stored
     output -- the gradient-norm contribution of a weight-gradient product, computed in its epilogue.
@@ -94,8 +100,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         out = torch.empty(*a.shape[:-2], m, n, dtype=torch.bfloat16, device=a.device)
     dd = d if beta != 0.0 else None
     if a.dim() == 2 and pair_eligible(m, n, k) and _ok_operand(out) and (dd is None or _ok_operand(dd)):
+        # from eight tile rows on (36 of 64 tiles): below that the second launch costs what the tiles save
+        sym = bool(symmetric) and m == n and m >= 2048 and sumsq is None and _FORCE_BN in (0, 256)
         ops().gemm_pair_bf16(a, b, out, None, dd, None, bool(a_t), bool(b_t), float(alpha), float(beta), 0,
-                             _FORCE_BN, status_word(a.device), sumsq, _DYNAMIC)
+                             _FORCE_BN, status_word(a.device), sumsq, _DYNAMIC, sym)
         return out
     if sumsq is not None:
         raise ValueError("sumsq needs the CTA-pair kernel; this product does not qualify")
@@ -145,7 +153,7 @@ def gemm_swiglu_fwd(x: torch.Tensor, w_gate_up: torch.Tensor) -> Tuple[torch.Ten
     gu = torch.empty(m, 2 * f, dtype=torch.bfloat16, device=x.device)
     act = torch.empty(m, f, dtype=torch.bfloat16, device=x.device)
     ops().gemm_pair_bf16(x, w_gate_up, gu, act, None, None, False, False, 1.0, 0.0, 1, 0, status_word(x.device),
-                         None, _DYNAMIC)
+                         None, _DYNAMIC, False)
     return gu, act
 
 
@@ -156,5 +164,5 @@ def gemm_swiglu_bwd(dy: torch.Tensor, w_down: torch.Tensor, gate_up: torch.Tenso
     """
     dgu = torch.empty_like(gate_up)
     ops().gemm_pair_bf16(dy, w_down, dgu, None, None, gate_up, False, True, 1.0, 0.0, 2, _FORCE_BN,
-                         status_word(dy.device), None, _DYNAMIC)
+                         status_word(dy.device), None, _DYNAMIC, False)
     return dgu

@@ -97,8 +97,9 @@ def _iterate(x: torch.Tensor, schedule: Sequence[Coeffs]) -> torch.Tensor:
         u = torch.empty_like(g)
         nxt = torch.empty_like(x)
         for a, b, c in schedule:
-            tcgemm.gemm(x, x, out=g)                                   # G = X X^T
-            tcgemm.gemm(g, g, alpha=c, beta=b, d=g, out=u)             # U = c G G^T + b G
+            # G and U are symmetric: only the tiles on and below the diagonal are computed
+            tcgemm.gemm(x, x, out=g, symmetric=True)                                   # G = X X^T
+            tcgemm.gemm(g, g, alpha=c, beta=b, d=g, out=u, symmetric=True)             # U = c G G^T + b G
             tcgemm.gemm(u, x, b_t=True, alpha=1.0, beta=a, d=x, out=nxt)  # X' = U X + a X
             x, nxt = nxt, x
         return x

@@ -739,3 +739,33 @@ def test_gefen_muon_with_normuon_and_cautious_takes_the_epilogue_kernels():
             opt.step()
         outs.append(p.detach().cpu())
     torch.testing.assert_close(outs[0], outs[1], rtol=0, atol=2e-3)
+
+
+def test_pair_gemm_symmetric_mode_equals_the_full_product():
+    """``symmetric=True`` computes the 256 x 256 tiles on and below the diagonal and mirrors the rest:
+    the result is exactly symmetric and equals the full product up to the order of the K-split sums
+    (the two launches split different tiles of their tail waves: one bf16 ulp); sizes that are and are
+    not multiples of the tile, with and without the addend, both schedules."""
+    from gefen_x_b200.ops import tcgemm
+
+    g = torch.Generator().manual_seed(41)
+    dev = _dev()
+    try:
+        for dynamic in (False, True):
+            tcgemm.set_dynamic_schedule(dynamic)
+            for m, k in [(4096, 1024), (2048, 4096), (2100, 520), (2304, 768), (1024, 128)]:
+                x = (torch.randn(m, k, generator=g) * 0.1).bfloat16().to(dev)
+                full = tcgemm.gemm(x, x)
+                sym = tcgemm.gemm(x, x, symmetric=True)
+                assert torch.equal(sym, sym.t()), (m, k)
+                torch.testing.assert_close(sym.float(), full.float(), rtol=1.6e-2, atol=1e-3, msg=str((m, k)))
+                assert (sym != full).float().mean().item() < 0.05, (m, k)
+                gm = sym                                                   # an exactly symmetric matrix
+                u_full = tcgemm.gemm(gm, gm, alpha=2.0, beta=-4.0, d=gm)
+                u_sym = tcgemm.gemm(gm, gm, alpha=2.0, beta=-4.0, d=gm, symmetric=True)
+                assert torch.equal(u_sym, u_sym.t()), (m, k)
+                torch.testing.assert_close(u_sym.float(), u_full.float(), rtol=1.6e-2, atol=2e-2, msg=str((m, k)))
+        torch.cuda.synchronize()
+        assert int(tcgemm.status_word(dev).item()) == 0
+    finally:
+        tcgemm.set_dynamic_schedule(False)
