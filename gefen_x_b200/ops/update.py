@@ -193,24 +193,22 @@ def set_streaming(on: bool) -> None:
     _STREAMING = bool(on)
 
 
-_LUT_SINGLE: Dict[Any, bool] = {}
-
-
 def _lut_single(lut: torch.Tensor) -> bool:
     """Whether no bucket of the packed search table holds more than one decision threshold.  The
     streamed apply kernel resolves a value with one comparison and has no full search; a codebook
     with codewords closer than a bucket (1.2e-4 of the normalised range) goes to the
-    register-pipelined kernels instead.  Cached per table (address and version); reading the answer
-    synchronises once per codebook.  During stream capture an unknown table counts as not single."""
-    key = (lut.data_ptr(), lut._version, lut.device)
-    hit = _LUT_SINGLE.get(key)
+    register-pipelined kernels instead.  The answer is remembered on the table tensor itself (it
+    lives and dies with it); reading it synchronises once per codebook.  During stream capture an
+    unknown table counts as not single."""
+    hit = getattr(lut, "_gx_single_threshold_buckets", None)
     if hit is None:
         if lut.is_cuda and torch.cuda.is_current_stream_capturing():
             return False
         hit = bool((((lut.to(torch.int32) & 0xFFFF) >> 8).max() <= 1).item())
-        if len(_LUT_SINGLE) > 64:
-            _LUT_SINGLE.clear()
-        _LUT_SINGLE[key] = hit
+        try:
+            lut._gx_single_threshold_buckets = hit
+        except AttributeError:
+            pass
     return hit
 
 

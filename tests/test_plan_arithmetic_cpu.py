@@ -90,3 +90,47 @@ def test_state_of_the_wrong_size_is_refused_when_the_plan_is_built():
     it.state["m_codebook"] = torch.empty(64, 256, dtype=torch.uint8, device="meta")
     with pytest.raises(ValueError, match="m_codebook"):
         U.Plan("factored", [it], torch.device("cpu"), torch.bfloat16)
+
+
+def test_crowded_bucket_tables_are_recognised_and_remembered_on_the_tensor():
+    """The streamed apply kernel settles a value with one comparison, which needs at most one decision
+    threshold per bucket of the search table; the host checks the table once and keeps the answer on
+    the tensor, so a table that later reuses the same address cannot inherit it."""
+    from gefen_x_b200.quant import codebook as C
+
+    torch.manual_seed(5)
+    cb = torch.sort(torch.rand(256) * 2 - 1).values
+    cb[0], cb[-1] = -1.0, 1.0
+    spread = torch.linspace(-1, 1, 256)                       # 7.8e-3 apart: one threshold per bucket at most
+    lut = C.packed_search_lut(spread)
+    assert U._lut_single(lut) and lut._gx_single_threshold_buckets is True
+    crowded = spread.clone()
+    crowded[100] = crowded[99] + 1e-6
+    crowded[101] = crowded[99] + 2e-6                         # three codewords inside one bucket
+    lut2 = C.packed_search_lut(torch.sort(crowded).values)
+    assert not U._lut_single(lut2)
+    assert int(((lut2.int() & 0xFFFF) >> 8).max()) >= 2
+
+
+def test_wide_tile_prefix_follows_the_rule_the_kernels_apply():
+    """Plans that may run the 16-wide streamed kernels carry a second tile prefix behind the 8-wide one;
+    the kernels derive the same geometry from the descriptor (thread columns that waste the fewest
+    16-element chunks, the 8-wide rows-per-thread factor)."""
+    U.set_wide_chunks(True)
+    try:
+        items = [_item(4096, 14336, 524288), _item(2048, 1024, 2048), _item(324, 48, 1296)]
+        plan = U.Plan("factored", items, torch.device("cpu"), torch.bfloat16)
+    finally:
+        U.set_wide_chunks(False)
+    descs = _descs(plan)
+    if plan.fast != 4:                                       # CPU tensors may not be 16-byte aligned
+        return
+    n = len(items)
+    start = plan.tile_start.tolist()
+    assert len(start) == 2 * (n + 1) and start[0] == 0 and start[n + 1] == 0
+    for i, d in enumerate(descs):
+        chunks = d.cols // 16
+        tc = U._pick_tcols(chunks)
+        rows_per_tile = (256 // tc) * (d.rows_per_tile // d.trows)
+        tiles = ((chunks + tc - 1) // tc) * ((d.rows + rows_per_tile - 1) // rows_per_tile)
+        assert start[n + 2 + i] - start[n + 1 + i] == tiles
