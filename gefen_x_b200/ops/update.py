@@ -489,8 +489,8 @@ class Plan:
 
     @staticmethod
     def _stream_ok(d) -> bool:
-        ptrs = (d.idx, d.p, d.g[0])            # ctypes gives None for a null pointer
-        return d.row_only < 2 and d.cols % 16 == 0 and all(x is not None and x % 16 == 0 for x in ptrs)
+        ptrs = (d.idx, d.p, d.g[0])            # ctypes gives None for a null pointer (storage-less test tensors)
+        return d.row_only < 2 and d.cols % 16 == 0 and all((x or 0) % 16 == 0 for x in ptrs)
 
     @staticmethod
     def signature_of(items: List[Item]):
