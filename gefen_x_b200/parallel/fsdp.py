@@ -126,7 +126,12 @@ class ShardedTrainer:
                  ag_gemm: bool = False, ag_fetch_ctas: int = 32, muon_kwargs: Optional[dict] = None,
                  gather_mode: str = "ce", reduce_ctas: int = 148, reduce_mode: str = "ce",
                  sparse_embedding: bool = True, embed_capacity: int = 16384, nvls: Optional[bool] = None,
-                 gemm_schedule: str = "auto", copy_lanes: int = 4):
+                 gemm_schedule: str = "auto", copy_lanes: int = 4, context_parallel: int = 1):
+        if int(context_parallel) != 1:
+            # The hook for splitting a sequence over ranks (ring / blockwise attention): the reference has
+            # no sequence parallelism either and every benchmark configuration is 2048 tokens.
+            raise NotImplementedError("context_parallel > 1 (sequence parallelism) is not implemented; "
+                                      "sequences are processed whole on each rank")
         self.cfg = cfg
         self.copy_lanes = max(1, int(copy_lanes))   # auxiliary streams of the copy-engine transfers
         self.world, self.rank = int(world), int(rank)

@@ -89,3 +89,17 @@ def test_trainer_steps_on_cpu_through_the_same_api():
     tr.check_status()
     with pytest.raises(RuntimeError, match="CUDA"):
         tr.traced_step(tok[:, :-1], tok[:, 1:])
+
+
+def test_context_parallel_hook_is_declared_and_refuses():
+    """Sequence parallelism is a declared, unimplemented hook (the reference has none either)."""
+    import pytest
+    import torch
+
+    from gefen_x_b200.models.decoder import get_config
+    from gefen_x_b200.parallel.fsdp import ShardedTrainer
+
+    cfg = get_config("tiny-llama", n_layers=1)
+    with pytest.raises(NotImplementedError, match="context_parallel"):
+        ShardedTrainer(cfg, device=torch.device("cpu"), dtype=torch.float32, world=1, rank=0, context_parallel=2)
+
