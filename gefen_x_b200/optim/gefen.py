@@ -761,8 +761,20 @@ class Gefen(torch.optim.Optimizer):
         return 0
 
     def _lr_scalar(self, group) -> float:
+        """The group's learning rate as a Python float.  A tensor learning rate is read back (a
+        device-to-host synchronisation for a CUDA tensor) once per value, not once per parameter: the
+        read is cached on the tensor's identity and version counter, which every in-place update of
+        a scheduler bumps (reference ``gefen_muon.py`` ``_lr_scalar`` / ``_lr_scalar_cache``)."""
         lr = group["lr"]
-        return float(lr.item()) if torch.is_tensor(lr) else float(lr)
+        if not torch.is_tensor(lr):
+            return float(lr)
+        cache = self.__dict__.setdefault("_lr_scalar_cache", {})
+        hit = cache.get(id(group))
+        if hit is not None and hit[0] is lr and hit[1] == lr._version:
+            return hit[2]
+        val = float(lr.item())
+        cache[id(group)] = (lr, lr._version, val)        # holding the tensor keeps its identity unique
+        return val
 
     @staticmethod
     def _colocate_param_state_(state, device) -> None:

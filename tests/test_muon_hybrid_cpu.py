@@ -208,3 +208,70 @@ def test_hybrid_call_forms():
     with pytest.raises(TypeError, match="backup_substrings is only valid"):      # the reference's type and wording
         GefenMuonHybrid(muon, backup, lr=1e-3, fused=False, backup_substrings=("x",))
     assert a.state[m.fc1.weight] is a.muon.state[m.fc1.weight]
+
+
+def test_tensor_lr_is_read_back_once_per_value_not_once_per_parameter():
+    """A tensor learning rate costs one ``Tensor.item()`` (a device-to-host synchronisation on CUDA) per
+    value: constant -> no read after the first step; an in-place scheduler update bumps the tensor's
+    version and is picked up; the results equal those of the same schedule given as Python floats
+    (reference tests/test_lr_item_no_sync.py)."""
+    import torch
+
+    from gefen_x_b200 import GefenMuon
+
+    shapes = [(32, 32), (48, 32), (32, 48), (64, 32), (32, 64)]
+
+    def build(lr):
+        torch.manual_seed(7)
+        ps = [("l%d" % i, (torch.randn(r, c) * 0.02).requires_grad_()) for i, (r, c) in enumerate(shapes)]
+        return GefenMuon(ps, lr=lr, ns_steps=2, adjust_lr_fn="match_rms_adamw"), ps
+
+    def grads(ps, gen):
+        for _, p in ps:
+            p.grad = torch.randn(p.shape, generator=gen) * 1e-3
+
+    orig_item = torch.Tensor.item
+    calls = {"n": 0}
+
+    def counting_item(self):
+        calls["n"] += 1
+        return orig_item(self)
+
+    def run(lr, schedule=None, steps=4, count_from=1):
+        opt, ps = build(lr)
+        gen = torch.Generator().manual_seed(3)
+        counted = 0
+        for s in range(steps):
+            grads(ps, gen)
+            if schedule is not None:
+                schedule(opt, s)
+            if s >= count_from:
+                calls["n"] = 0
+                torch.Tensor.item = counting_item
+            try:
+                opt.step()
+            finally:
+                torch.Tensor.item = orig_item
+            if s >= count_from:
+                counted += calls["n"]
+        return [p.detach().clone() for _, p in ps], counted
+
+    base, n_float = run(float(torch.tensor(1e-2, dtype=torch.float32)))    # the fp32 value the tensor holds
+    const, n_tensor = run(torch.tensor(1e-2))
+    assert n_tensor == n_float                                   # no read of a constant tensor after warm-up
+    for a, b in zip(base, const):
+        assert torch.equal(a, b)
+
+    def decay_tensor(opt, s):
+        if s > 0:
+            opt.param_groups[0]["lr"].mul_(0.5)                  # in place: bumps the version
+
+    def decay_float(opt, s):
+        if s > 0:
+            opt.param_groups[0]["lr"] = float(torch.tensor(opt.param_groups[0]["lr"], dtype=torch.float32) * 0.5)
+
+    sched_t, n_sched = run(torch.tensor(1e-2), decay_tensor)
+    sched_f, _ = run(float(torch.tensor(1e-2, dtype=torch.float32)), decay_float)
+    assert n_sched - n_float == 3                                # one read per new value (steps 1..3)
+    for a, b, c in zip(sched_t, sched_f, const):
+        assert torch.equal(a, b) and not torch.equal(a, c)
