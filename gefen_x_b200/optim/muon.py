@@ -416,22 +416,26 @@ class GefenMuon(Gefen):
         return mesh.get_group(0), mesh.size(0), mesh.get_local_rank(0)
 
     def _assert_sharded_grad_presence_consistent(self, items) -> None:
-        """Every rank must step the same matrices in the same order before any collective."""
+        """Every rank must step the same sharded matrices before any collective (reference
+        ``tests/test_muon_grad_presence.py``).  The agreement runs over every sharded parameter of the
+        optimizer, with or without a gradient on this rank, so that a rank whose gradients are all
+        missing still takes part in it (and learns, like the others, that the step is refused)."""
         import torch.distributed as dist
 
+        with_grad = {id(p) for _g, _n, p in items}
+        everyone = [q for g in self.param_groups for q in g["params"]]
         by_pg: Dict[int, Tuple[Any, List[int]]] = {}
-        for idx, (_g, _n, p) in enumerate(items):
-            pg, world, _ = self._process_group_of(p)
+        for idx, q in enumerate(everyone):
+            pg, world, _ = self._process_group_of(q)
             if pg is None or world < 2:
                 continue
             by_pg.setdefault(id(pg), (pg, []))[1].append(idx)
         for pg, idxs in by_pg.values():
-            n_total = sum(len(g["params"]) for g in self.param_groups)
-            mask = torch.zeros(n_total + 1, dtype=torch.int32)
-            pos = {p: i for i, p in enumerate(q for g in self.param_groups for q in g["params"])}
+            mask = torch.zeros(len(everyone) + 1, dtype=torch.int32)
             for i in idxs:
-                mask[pos[items[i][2]]] = 1
-            mask[-1] = len(idxs)
+                if id(everyone[i]) in with_grad:
+                    mask[i] = 1
+            mask[-1] = int(mask.sum())
             from ..parallel.control import control_device
 
             dev = control_device(pg)

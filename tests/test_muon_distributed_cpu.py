@@ -173,3 +173,71 @@ def test_distributed_muon_matches_exact_and_checkpoint_is_consolidated():
     ps, opt = fresh()
     opt.load_state_dict(copy.deepcopy(blob["sd"]))           # the untouched file still loads
 
+
+
+def _presence_worker(rank, world, port, case, q):
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+
+    from gefen_x_b200 import GefenMuon
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        mesh = init_device_mesh("cpu", (world,))
+        ps = [(n, distribute_tensor(t.clone(), mesh, [Shard(0)]).requires_grad_(True)) for n, t in _full(0).items()]
+        opt = GefenMuon(ps, lr=2e-2, fused=False, sharded_mode="distributed")
+        for n, p in ps:                                   # one good step: state exists everywhere
+            p.grad = distribute_tensor(_full(100)[n], mesh, [Shard(0)])
+        opt.step()
+        before_p = {n: p.to_local().detach().clone() for n, p in ps}
+        before_s = {n: {k: (v.detach().clone() if torch.is_tensor(v) else v) for k, v in opt.state.get(p, {}).items()}
+                    for n, p in ps}
+        for n, p in ps:
+            p.grad = distribute_tensor(_full(101)[n], mesh, [Shard(0)])
+        if rank == 1:
+            if case == "one_missing":
+                ps[1][1].grad = None                      # rank 1 alone lacks the gradient of one matrix
+            else:
+                for _, p in ps:                           # rank 1 has no gradient at all
+                    p.grad = None
+        err = None
+        try:
+            opt.step()
+        except RuntimeError as exc:
+            err = str(exc)
+        unchanged = all(torch.equal(p.to_local(), before_p[n]) for n, p in ps)
+        for n, p in ps:
+            st = opt.state.get(p, {})
+            for k, v in before_s[n].items():
+                same = torch.equal(st[k], v) if torch.is_tensor(v) else st[k] == v
+                unchanged = unchanged and bool(same)
+        q.put((rank, {"err": err, "unchanged": unchanged}))
+    except Exception:  # pragma: no cover - reported to the parent
+        import traceback
+
+        q.put((rank, {"error": traceback.format_exc()}))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("case", ["one_missing", "all_missing"])
+def test_ranks_that_disagree_on_gradient_presence_refuse_the_step_together(case):
+    """One rank lacks a gradient the other has (or has none at all): every rank raises before any
+    gather collective, nobody hangs, and neither parameters nor optimizer state have moved
+    (reference tests/test_muon_grad_presence.py)."""
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_presence_worker, args=(r, world, port, case, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=240) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    for r in range(world):
+        assert "error" not in got[r], got[r].get("error")
+        assert got[r]["err"] is not None and "disagree" in got[r]["err"], got[r]
+        assert got[r]["unchanged"], r
