@@ -14,7 +14,7 @@ the real ones), then times, with CUDA events and the maximum over ranks:
 * the parameter all-gather of one layer by the copy engines and by the peer-load kernel.
 
 Roofline of a fused kernel = the slower of FLOPs / measured cuBLAS bf16 throughput and bytes that
-must cross NVLink / 770 GB/s (the measured peer-copy bandwidth per direction on this pool).
+must cross NVLink / 770 GB/s (the measured peer-copy bandwidth per direction of these B200 systems).
 """
 from __future__ import annotations
 
