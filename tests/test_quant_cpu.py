@@ -200,3 +200,19 @@ def test_monotone_exact_dp_equals_the_full_scan():
             b = C.exact_dp(st, k, method="monotone")
             assert torch.equal(a, b)
     assert C.EXACT_DP_METHOD == "monotone"
+
+
+def test_bucket_function_is_monotonic_saturating_and_total():
+    """The bucket of the search table: rint(sat(x / 2 + 1 / 2) * 16383).  It must never decrease with x
+    (the table's bracketing argument rests on that), map everything below -1 to 0 and above 1 to the
+    last bucket, and give NaN a bucket (0, like the saturating fma of the kernels)."""
+    x = torch.cat([torch.linspace(-1.5, 1.5, 200001), torch.tensor([-1.0, 1.0, 0.0, -0.0, 1e-45, -1e-45,
+                                                                  float("inf"), float("-inf")])])
+    x = torch.sort(x).values
+    b = C._bucket(x, C.LUT_BUCKETS)
+    assert int(b.min()) == 0 and int(b.max()) == C.LUT_BUCKETS - 1
+    assert bool((b[1:] >= b[:-1]).all())
+    assert int(C._bucket(torch.tensor([-1.0]), C.LUT_BUCKETS)) == 0
+    assert int(C._bucket(torch.tensor([1.0]), C.LUT_BUCKETS)) == C.LUT_BUCKETS - 1
+    assert int(C._bucket(torch.tensor([0.0]), C.LUT_BUCKETS)) in (8191, 8192)       # 8191.5 rounds to even: 8192
+    assert int(C._bucket(torch.tensor([float("nan")]), C.LUT_BUCKETS)) == 0
